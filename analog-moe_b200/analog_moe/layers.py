@@ -1,0 +1,221 @@
+"""sigma-MoE feed-forward layer and its analog hardware-aware version on the B200 kernels.
+
+`SigmaMoELayer` is a stand-in for the third-party base class the reference layers derive from
+(`sigma_moe.moe_layer.SigmaMoELayer`): same constructor keywords and attributes, `forward`
+returning `(out, aux)` and calling `compute_scores` then `cvmm_wrapper(scores, sel, self.values)`
+(contract: reference moe_layer_aihwkit_lightning.py:220-233, 261-276, 384-410;
+tests/test_moe_layer_aihwkit.py:60-109).  The router matmul stays a torch Linear; everything from
+the gate logits onward runs in the CUDA library.
+
+`AnalogSigmaMoELayer` mirrors the non-traceable `AnalogSigmaMoELayerAIHWKITLightning`
+(moe_layer_aihwkit_lightning.py:134-543): per-expert learnable input ranges [2, E], DAC, weight
+modifier, output noise, and - new here - ADC output quantisation.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor, nn
+
+from . import ops
+from .rpu_config import TorchInferenceRPUConfig, WeightClipType
+from .triton_src.cvmm import CVMM, CVMMExt, CVMMSel, PhiloxNoise, WeightModifier, cvmm_std
+
+
+def _enum_name(v) -> str:
+    return getattr(v, "name", str(v)).split(".")[-1]
+
+
+class SigmaMoELayer(nn.Module):
+    def __init__(self, d_model: int, n_experts: int, expert_size: int, k: int, dropout: float = 0.0,
+                 selection_mode: str = "sigmoid", activation_after_topk: bool = False,
+                 activation: Callable = F.relu, bias: bool = False, v_dim: Optional[int] = None,
+                 sinkhorn_n_iters: int = 3, expert_dropout: float = 0.0, traceable: bool = False):
+        super().__init__()
+        if selection_mode != "sigmoid":
+            raise NotImplementedError("only sigmoid gating is built")
+        if traceable:
+            raise NotImplementedError("traceable mode delegates to third-party per-expert modules; not built")
+        self.k_dim = d_model
+        self.v_dim = v_dim if v_dim is not None else d_model
+        self.n_experts = n_experts
+        self.expert_size = expert_size
+        self.size = n_experts * expert_size
+        self.dropout = dropout
+        self.selection_mode = selection_mode
+        self.activation_after_topk = activation_after_topk
+        self.activation = activation
+        self.sinkhorn_n_iters = sinkhorn_n_iters
+        self.expert_dropout = expert_dropout
+        self.n_heads = k
+        self.traceable = traceable
+        self.keys = nn.Parameter(torch.empty(n_experts, self.k_dim, expert_size))
+        self.values = nn.Parameter(torch.empty(n_experts, expert_size, self.v_dim))
+        self.expert_sel = nn.Linear(self.k_dim, n_experts, bias=False)
+        self.bias = nn.Parameter(torch.zeros(n_experts, expert_size)) if bias else None
+        self.o_bias = nn.Parameter(torch.zeros(self.v_dim)) if bias else None
+        nn.init.normal_(self.keys, std=self.k_dim ** -0.5)
+        nn.init.normal_(self.values, std=expert_size ** -0.5)
+        nn.init.normal_(self.expert_sel.weight, std=self.k_dim ** -0.5)
+
+    # -- the two hooks the analog layer overrides
+    def cvmm_wrapper(self, inputs: Tensor, sel_indices: CVMMSel, weights: Tensor) -> Tensor:
+        class _Off:
+            enable = False
+        return CVMM.apply(inputs, sel_indices.sel_index, sel_indices.sel, weights, -1, None, sel_indices.out_index,
+                          sel_indices.reduction_weight, None, None, None,
+                          CVMMExt(expert_offsets=sel_indices.expert_offsets, precision=self._precision(inputs)))
+
+    def _precision(self, inputs: Tensor) -> int:
+        return ops.default_precision(inputs.dtype)
+
+    def compute_scores(self, inp: Tensor, index: CVMMSel, expert_scores: Optional[Tensor] = None) -> Tensor:
+        if not inp.is_cuda:
+            raise RuntimeError("the sigma-MoE layer runs on CUDA tensors only")
+        scores = self.cvmm_wrapper(inp, index, self.keys)
+        if self.bias is not None:
+            scores = scores + self.bias[index.raw_sel.long()]
+        scores = self.activation(scores)
+        if expert_scores is not None:
+            scores = scores * expert_scores[..., None]
+        if self.dropout > 0:
+            scores = F.dropout(scores, self.dropout, training=self.training)
+        return scores
+
+    def route(self, inp: Tensor) -> Tuple[CVMMSel, Tensor]:
+        """Gate logits -> sigmoid -> top-k -> expert-sorted slot list, one kernel pipeline."""
+        logits = self.expert_sel(inp)
+        bsz, seq, _ = inp.shape
+        r = ops.select_sort(logits.detach(), self.n_heads, apply_sigmoid=True)
+        raw_sel = r.raw_sel.view(bsz, seq, self.n_heads)
+        # gate values with gradient: recompute the k picked sigmoids from the logits (tiny gather)
+        gate = torch.sigmoid(logits.float()).gather(-1, raw_sel.long()).to(inp.dtype)
+        sel = CVMMSel(raw_sel, r.sel.view(bsz, seq, self.n_heads), r.token_index, r.slot_index, None, r.expert_offsets)
+        return sel, gate
+
+    def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
+        sel, gate = self.route(inp)
+        scores = self.compute_scores(inp, sel)
+        down = sel.clone()
+        down.reduction_weight = gate
+        down.sel_index = sel.out_index
+        down.out_index = None
+        out = self.cvmm_wrapper(scores, down, self.values)
+        if self.o_bias is not None:
+            out = out + self.o_bias
+        return out, inp.new_zeros(())
+
+
+class AnalogSigmaMoELayer(SigmaMoELayer):
+    def __init__(self, rpu_config: Optional[TorchInferenceRPUConfig] = None, *args, precision: Optional[int] = None,
+                 noise_seed: int = 0, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.rpu_config = rpu_config if rpu_config is not None else TorchInferenceRPUConfig()
+        fwd = self.rpu_config.forward
+        adc_on = fwd.out_res > 0
+        if adc_on and not fwd.out_bound > 0:
+            raise ValueError("ADC output quantisation (out_res > 0) needs out_bound > 0")
+        assert self.rpu_config.mapping.max_input_size <= 0, "max_input_size must be <= 0"   # lightning :158-160
+        self.precision = precision
+        self.noise_seed = noise_seed
+        self.register_buffer("noise_step", torch.zeros((), dtype=torch.int64), persistent=True)
+        self._noise_calls = 0
+        ir = self.rpu_config.pre_post.input_range
+        self.input_range = None
+        if ir.enable:
+            self.input_range_update_idx = nn.Parameter(torch.tensor(0.0), requires_grad=False)
+            init = torch.full((2, self.n_experts), float(ir.init_value))
+            if ir.learn_input_range:
+                self.input_range = nn.Parameter(init)
+            else:
+                del self.input_range
+                self.register_buffer("input_range", init)
+
+    @classmethod
+    def from_digital(cls, module: SigmaMoELayer, rpu_config: TorchInferenceRPUConfig) -> "AnalogSigmaMoELayer":
+        layer = cls(rpu_config, d_model=module.k_dim, n_experts=module.n_experts, expert_size=module.expert_size,
+                    k=module.n_heads, dropout=module.dropout, selection_mode=module.selection_mode,
+                    activation_after_topk=module.activation_after_topk, activation=module.activation,
+                    bias=module.bias is not None, v_dim=module.v_dim, sinkhorn_n_iters=module.sinkhorn_n_iters,
+                    expert_dropout=module.expert_dropout, traceable=module.traceable)
+        layer.load_state_dict(module.state_dict(), strict=False)
+        return layer.to(module.keys.device)
+
+    def _precision(self, inputs: Tensor) -> int:
+        return self.precision if self.precision is not None else ops.default_precision(inputs.dtype)
+
+    def _weight_modifier(self) -> Optional[WeightModifier]:
+        mod = self.rpu_config.modifier
+        name = _enum_name(mod.type)
+        if name in ("NONE", "None") or not (self.training or mod.enable_during_test):
+            return None
+        per_channel = name.endswith("PER_CHANNEL")
+        disc = float(mod.res) if name.startswith("DISCRETIZE") else -1.0
+        std = float(mod.std_dev) if "ADD_NORMAL" in name else 0.0
+        return WeightModifier(std_dev=std, per_channel=per_channel, discretize_res=disc, seed=self.noise_seed,
+                              offset=self._next_offset())
+
+    def _next_offset(self) -> int:
+        # (step, call) -> Philox offset: a resumed run that restores `noise_step` replays its noise
+        self._noise_calls += 1
+        return (int(self._noise_step_host) * 8 + self._noise_calls) & 0xFFFFFFFF
+
+    def cvmm_wrapper(self, inputs: Tensor, sel_indices: CVMMSel, weights: Tensor) -> Tensor:
+        cfg = self.rpu_config
+        ir_p = cfg.pre_post.input_range
+        bir = None
+        if self.input_range is not None:
+            ir_idx = 0 if inputs.ndim == 3 else 1                                   # lightning :428-429
+            if self.training and ir_p.init_from_data > 0 and float(self.input_range_update_idx) < ir_p.init_from_data:   # lightning :432-445
+                idx = self.input_range_update_idx
+                stds = cvmm_std(inputs, sel_indices.sel_index, sel_indices.sel, self.n_experts)
+                ok = stds > 0.0
+                if bool(ok.any()):
+                    cur = self.input_range.data[ir_idx]
+                    cur[ok] = (cur[ok] * idx + ir_p.init_std_alpha * stds[ok].to(cur.dtype)) / (idx + 1)
+                    self.input_range_update_idx.data += 1
+                self.input_range.data = self.input_range.data.abs()
+            bir = self.input_range[ir_idx][sel_indices.sel.long()]                  # lightning :447-448
+        inp_res = cfg.forward.inp_res
+        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1   # lightning :451-456
+        noise = None
+        if self.training and cfg.forward.out_noise > 0:                             # lightning :471-492
+            noise = PhiloxNoise(float(cfg.forward.out_noise), self.noise_seed, self._next_offset())
+        ext = CVMMExt(noise=noise, modifier=self._weight_modifier(), out_res=float(cfg.forward.out_res),
+                      out_bound=float(cfg.forward.out_bound),
+                      scale_per_channel=bool(getattr(cfg.forward, "out_noise_per_channel", True)),
+                      precision=self._precision(inputs), expert_offsets=sel_indices.expert_offsets)
+        return CVMM.apply(inputs, sel_indices.sel_index, sel_indices.sel, weights, inp_res, bir,
+                          sel_indices.out_index, sel_indices.reduction_weight, None, ir_p, cfg.forward, ext)
+
+    def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
+        self._noise_calls = 0
+        self._noise_step_host = getattr(self, "_noise_step_host", 0)
+        out = super().forward(inp)
+        if self.training:
+            self._noise_step_host += 1
+            self.noise_step += 1
+        return out
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+        self._noise_step_host = int(self.noise_step)
+
+    def post_update_step(self) -> None:
+        if _enum_name(self.rpu_config.clip.type) not in ("NONE", "None"):
+            self.clip_weights()
+
+    @torch.no_grad()
+    def clip_weights(self) -> None:
+        """lightning :519-543: clamp to +-sigma*std per expert (or per column)."""
+        clip = self.rpu_config.clip
+        name = _enum_name(clip.type)
+        if name in ("NONE", "None"):
+            return
+        assert clip.sigma > 0, "Clip sigma must be greater than 0"
+        dims = (1, 2) if clip.type == WeightClipType.LAYER_GAUSSIAN or name == "LAYER_GAUSSIAN" else 1
+        for w in (self.keys, self.values):
+            bound = clip.sigma * w.std(dims, keepdim=True)
+            w.data = torch.maximum(torch.minimum(w.data, bound), -bound)

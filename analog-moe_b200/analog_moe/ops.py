@@ -1,0 +1,332 @@
+"""Tensor-level wrappers over the C ABI.  PyTorch supplies device memory and the current stream;
+all arithmetic happens in the CUDA library."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi as A
+from ._cabi import lib, check, ptr, stream_ptr, dtype_code
+
+
+def i32(t: torch.Tensor) -> torch.Tensor:
+    """Index tensors cross the ABI as contiguous int32."""
+    t = t.reshape(-1)
+    if t.dtype != torch.int32:
+        t = t.to(torch.int32)
+    return t.contiguous()
+
+
+def default_precision(dtype: torch.dtype) -> int:
+    env = os.environ.get("AMOE_PRECISION")
+    if env:
+        return A.PRECISION_NAMES[env.lower()]
+    return A.PREC_BF16X1 if dtype == torch.bfloat16 else A.PREC_SPLIT
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(4, dtype=torch.int32, device=device)
+
+
+def raise_on_device_status(status: torch.Tensor, where: str) -> None:
+    """Synchronises; raises if a kernel recorded a bad index or a wait that ran out."""
+    host = (C.c_int32 * 4)()
+    code = lib.amoe_read_device_status(ptr(status), C.byref(host), stream_ptr())
+    if code != 0:
+        raise A.AmoeError(code, f"{where} (detail {host[1]}, {host[2]}, {host[3]})")
+
+
+# --------------------------------------------------------------------------- routing
+@dataclass
+class Routing:
+    raw_sel: torch.Tensor         # [T,k] int32
+    gate: torch.Tensor            # [T,k] fp32
+    sel: torch.Tensor             # [P] int32 sorted expert ids
+    token_index: torch.Tensor     # [P] int32
+    slot_index: torch.Tensor      # [P] int32
+    expert_offsets: torch.Tensor  # [E+1] int32
+
+
+def select_sort(logits: torch.Tensor, k: int, apply_sigmoid: bool = True) -> Routing:
+    A.require_cuda(logits)
+    logits = logits.reshape(-1, logits.shape[-1]).float().contiguous()
+    T, E = logits.shape
+    dev = logits.device
+    P = T * k
+    raw_sel = torch.empty(T, k, dtype=torch.int32, device=dev)
+    gate = torch.empty(T, k, dtype=torch.float32, device=dev)
+    sel = torch.empty(P, dtype=torch.int32, device=dev)
+    tok = torch.empty(P, dtype=torch.int32, device=dev)
+    slot = torch.empty(P, dtype=torch.int32, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    nbytes = lib.amoe_select_sort_workspace_bytes(T, E, k)
+    ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=dev)
+    check(lib.amoe_select_sort(ptr(logits), T, E, k, int(apply_sigmoid), ptr(raw_sel), ptr(gate), ptr(sel), ptr(tok),
+                               ptr(slot), ptr(off), ptr(ws), nbytes, stream_ptr()), "amoe_select_sort")
+    return Routing(raw_sel, gate, sel, tok, slot, off)
+
+
+def expert_offsets(sel_sorted: torch.Tensor, n_experts: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    sel_sorted = i32(sel_sorted)
+    off = torch.empty(n_experts + 1, dtype=torch.int32, device=sel_sorted.device)
+    check(lib.amoe_expert_offsets(ptr(sel_sorted), sel_sorted.numel(), n_experts, ptr(off), ptr(status), stream_ptr()),
+          "amoe_expert_offsets")
+    return off
+
+
+# --------------------------------------------------------------------------- weights
+@dataclass
+class PreparedWeights:
+    """What the weight pre-pass leaves behind for the CVMM kernels."""
+    E: int
+    K: int
+    N: int
+    col_scale: torch.Tensor                 # [E,N] fp32
+    w: Optional[torch.Tensor] = None        # [E,K,N] fp32/bf16 for the CUDA-core mode (modified weights)
+    fwd_hi: Optional[torch.Tensor] = None
+    fwd_lo: Optional[torch.Tensor] = None
+    bwd_hi: Optional[torch.Tensor] = None
+    bwd_lo: Optional[torch.Tensor] = None
+
+
+def prepared_dims(K: int, N: int) -> Tuple[int, int, int, int]:
+    d = (C.c_int32 * 4)()
+    lib.amoe_prepared_dims(K, N, C.byref(d))
+    return tuple(int(v) for v in d)
+
+
+def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool = True, noise_std: float = 0.0,
+                   noise_per_channel: bool = True, discretize_res: float = -1.0, seed: int = 0, offset: int = 0,
+                   need_fwd: bool = True, need_bwd: bool = True, need_w_out: bool = False) -> PreparedWeights:
+    A.require_cuda(w)
+    E, K, N = w.shape
+    dev = w.device
+    modified = noise_std > 0 or discretize_res > 0
+    col_scale = torch.empty(E, N, dtype=torch.float32, device=dev)
+    a = A.WeightPrepassArgs()
+    a.w, a.w_dtype, a.E, a.K, a.N = ptr(w), dtype_code(w), E, K, N
+    a.w_stride_e, a.w_stride_k, a.w_stride_n = w.stride()
+    a.per_channel_scale = int(per_channel_scale)
+    a.noise_std, a.noise_per_channel = float(noise_std), int(noise_per_channel)
+    a.discretize_res = float(discretize_res)
+    a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
+    a.col_scale = ptr(col_scale)
+    out = PreparedWeights(E, K, N, col_scale)
+    if precision == A.PREC_FP32_SIMT:
+        if modified or need_w_out:
+            out.w = torch.empty(E, K, N, dtype=torch.float32, device=dev)
+            a.w_out = ptr(out.w)
+        else:
+            out.w = w
+    else:
+        # bf16 weights are exact in one term unless the modifier adds fp32 noise on top
+        split = precision == A.PREC_SPLIT and (w.dtype != torch.bfloat16 or modified)
+        npad, kpad, kpad2, npad2 = prepared_dims(K, N)
+        if need_fwd:
+            out.fwd_hi = torch.empty(E, npad, kpad, dtype=torch.bfloat16, device=dev)
+            a.fwd_hi = ptr(out.fwd_hi)
+            if split:
+                out.fwd_lo = torch.empty_like(out.fwd_hi)
+                a.fwd_lo = ptr(out.fwd_lo)
+        if need_bwd:
+            out.bwd_hi = torch.empty(E, kpad2, npad2, dtype=torch.bfloat16, device=dev)
+            a.bwd_hi = ptr(out.bwd_hi)
+            if split:
+                out.bwd_lo = torch.empty_like(out.bwd_hi)
+                a.bwd_lo = ptr(out.bwd_lo)
+        if need_w_out:
+            out.w = torch.empty(E, K, N, dtype=torch.float32, device=dev)
+            a.w_out = ptr(out.w)
+    nbytes = lib.amoe_weight_prepass_workspace_bytes(E, K, N)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    a.workspace, a.workspace_bytes = ptr(ws), nbytes
+    check(lib.amoe_weight_prepass(C.byref(a), stream_ptr()), "amoe_weight_prepass")
+    return out
+
+
+def row_absmax(x2: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(x2.shape[0], dtype=torch.float32, device=x2.device)
+    check(lib.amoe_row_absmax(ptr(x2), dtype_code(x2), x2.shape[0], x2.shape[1], x2.stride(0), ptr(out), stream_ptr()),
+          "amoe_row_absmax")
+    return out
+
+
+# --------------------------------------------------------------------------- the CVMM itself
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    t = t.reshape(-1, t.shape[-1])
+    if t.stride(-1) != 1:
+        t = t.contiguous()
+    return t
+
+
+def _fill_weights(a: A.CvmmArgs, pw: PreparedWeights, precision: int, backward: bool) -> None:
+    if precision == A.PREC_FP32_SIMT:
+        w = pw.w
+        a.w, a.w_dtype = ptr(w), dtype_code(w)
+        a.w_stride_e, a.w_stride_k, a.w_stride_n = w.stride()
+    else:
+        hi, lo = (pw.bwd_hi, pw.bwd_lo) if backward else (pw.fwd_hi, pw.fwd_lo)
+        if hi is None:
+            raise RuntimeError("prepared weights for this direction were not requested from weight_prepass")
+        a.w_hi, a.w_lo = ptr(hi), ptr(lo)
+
+
+def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offsets: torch.Tensor,
+             pw: PreparedWeights, precision: int, *, P: int, dst_rows: int, a_row_div: int = 1,
+             ir: Optional[torch.Tensor] = None, absmax: Optional[torch.Tensor] = None, inp_res: float = -1.0,
+             noise: Optional[torch.Tensor] = None, noise_std: float = 0.0, seed: int = 0, offset: int = 0,
+             out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
+             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None):
+    x2 = _rows(x2)
+    dev = x2.device
+    out = torch.empty(dst_rows, pw.N, dtype=out_dtype or x2.dtype, device=dev)
+    codes = torch.empty(dst_rows, pw.N, dtype=torch.int8, device=dev) if want_codes else None
+    a = A.CvmmArgs()
+    a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
+    a.expert_offsets = ptr(offsets)
+    a.a, a.a_dtype, a.a_stride, a.a_rows = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0]
+    a.a_row, a.a_row_div, a.dst_row, a.dst_rows = ptr(a_row), a_row_div, ptr(dst_row), dst_rows
+    _fill_weights(a, pw, precision, backward=False)
+    a.ir, a.a_absmax, a.inp_res = ptr(ir), ptr(absmax), float(inp_res)
+    if noise is not None:
+        noise = noise.reshape(-1, pw.N).float().contiguous()
+        assert noise.shape[0] == dst_rows
+    a.noise, a.noise_std = ptr(noise), float(noise_std)
+    a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
+    a.col_scale = ptr(pw.col_scale)
+    a.out_res, a.out_bound = float(out_res), float(out_bound)
+    a.out, a.out_dtype, a.out_stride, a.out_codes = ptr(out), dtype_code(out), out.stride(0), ptr(codes)
+    a.dev_status = ptr(status)
+    check(lib.amoe_cvmm_fwd(C.byref(a), stream_ptr()), "amoe_cvmm_fwd")
+    return out, codes
+
+
+def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offsets: torch.Tensor,
+            pw: PreparedWeights, precision: int, *, P: int, dst_rows: int, a_row_div: int = 1,
+            x_ref: Optional[torch.Tensor] = None, x_ref_row: Optional[torch.Tensor] = None,
+            ir: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None, want_ir_grad: bool = False,
+            relative: bool = True, grad_scale: float = 1.0, keep_count: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None):
+    g2 = _rows(g2)
+    dev = g2.device
+    out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev)
+    ir_grad = torch.empty(P, dtype=torch.float32, device=dev) if want_ir_grad else None
+    a = A.CvmmArgs()
+    a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
+    a.expert_offsets = ptr(offsets)
+    a.a, a.a_dtype, a.a_stride, a.a_rows = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0]
+    a.a_row, a.a_row_div, a.dst_row, a.dst_rows = ptr(a_row), a_row_div, ptr(dst_row), dst_rows
+    _fill_weights(a, pw, precision, backward=True)
+    a.inp_res = -1.0
+    a.ir = ptr(ir)
+    a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
+    if x_ref is not None:
+        x_ref = _rows(x_ref)
+        a.x_ref, a.x_ref_dtype, a.x_ref_stride, a.x_ref_row = ptr(x_ref), dtype_code(x_ref), x_ref.stride(0), ptr(x_ref_row)
+        a.x_ref_rows = x_ref.shape[0]
+    a.row_scale, a.ir_grad = ptr(row_scale), ptr(ir_grad)
+    a.ir_grad_relative, a.ir_grad_scale = int(relative), float(grad_scale)
+    a.keep_count = ptr(keep_count)
+    a.dev_status = ptr(status)
+    check(lib.amoe_cvmm_dx(C.byref(a), stream_ptr()), "amoe_cvmm_dx")
+    return out, ir_grad
+
+
+def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torch.Tensor, offsets: torch.Tensor,
+            E: int, precision: int, *, P: int, ir: Optional[torch.Tensor] = None, g_div: int = 1,
+            g_scale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x2, g2 = _rows(x2), _rows(g2)
+    K, N = x2.shape[1], g2.shape[1]
+    dw = torch.empty(E, K, N, dtype=torch.float32, device=x2.device)
+    a = A.DwArgs()
+    a.P, a.E, a.K, a.N, a.precision = P, E, K, N, precision
+    a.expert_offsets = ptr(offsets)
+    a.x, a.x_dtype, a.x_stride, a.x_rows, a.x_row, a.ir = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0], ptr(x_row), ptr(ir)
+    a.g, a.g_dtype, a.g_stride, a.g_rows, a.g_row = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0], ptr(g_row)
+    a.g_div, a.g_scale, a.dw = g_div, ptr(g_scale), ptr(dw)
+    a.dev_status = ptr(status)
+    check(lib.amoe_cvmm_dw(C.byref(a), stream_ptr()), "amoe_cvmm_dw")
+    return dw
+
+
+# --------------------------------------------------------------------------- reductions
+def combine(res: torch.Tensor, w: Optional[torch.Tensor], T: int, k: int, out_dtype=None) -> torch.Tensor:
+    res = _rows(res)
+    N = res.shape[1]
+    y = torch.empty(T, N, dtype=out_dtype or res.dtype, device=res.device)
+    if w is not None:
+        w = w.reshape(-1).float().contiguous()
+    check(lib.amoe_combine(ptr(res), dtype_code(res), res.stride(0), ptr(w), T, k, N, ptr(y), dtype_code(y),
+                           y.stride(0), stream_ptr()), "amoe_combine")
+    return y
+
+
+def combine_codes(codes: torch.Tensor, col_scale: torch.Tensor, raw_sel: torch.Tensor, row_mult: Optional[torch.Tensor],
+                  step: float, w: Optional[torch.Tensor], T: int, k: int, out_dtype=torch.float32) -> torch.Tensor:
+    N = codes.shape[-1]
+    y = torch.empty(T, N, dtype=out_dtype, device=codes.device)
+    if w is not None:
+        w = w.reshape(-1).float().contiguous()
+    check(lib.amoe_combine_codes(ptr(codes), ptr(col_scale), ptr(i32(raw_sel)), ptr(row_mult), float(step), ptr(w), T, k,
+                                 N, ptr(y), dtype_code(y), y.stride(0), stream_ptr()), "amoe_combine_codes")
+    return y
+
+
+def row_dot(res: torch.Tensor, g: torch.Tensor, k: int) -> torch.Tensor:
+    res, g = _rows(res), _rows(g)
+    P, N = res.shape
+    d = torch.empty(P, dtype=torch.float32, device=res.device)
+    check(lib.amoe_row_dot(ptr(res), dtype_code(res), res.stride(0), ptr(g), dtype_code(g), g.stride(0), P, k, N,
+                           ptr(d), stream_ptr()), "amoe_row_dot")
+    return d
+
+
+def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_range: Optional[torch.Tensor], E: int,
+                   decay: float = 0.0, min_percentage: float = 0.95, keep_count: Optional[torch.Tensor] = None,
+                   total_elements: float = 0.0) -> torch.Tensor:
+    out = torch.empty(E, dtype=torch.float32, device=ir_grad_slot.device)
+    check(lib.amoe_ir_grad_reduce(ptr(ir_grad_slot), ptr(offsets), ptr(input_range), E, float(decay),
+                                  float(min_percentage), ptr(keep_count), float(total_elements), ptr(out),
+                                  stream_ptr()), "amoe_ir_grad_reduce")
+    return out
+
+
+def expert_std(x: torch.Tensor, x_row: torch.Tensor, offsets: torch.Tensor, E: int) -> torch.Tensor:
+    x2 = _rows(x)
+    P = x_row.numel()
+    out = torch.empty(E, dtype=torch.float32, device=x2.device)
+    nbytes = lib.amoe_expert_std_workspace_bytes(E)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
+    check(lib.amoe_expert_std(ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[1], ptr(x_row), ptr(offsets), P, E,
+                              ptr(out), ptr(ws), nbytes, stream_ptr()), "amoe_expert_std")
+    return out
+
+
+# --------------------------------------------------------------------------- expert-parallel helpers
+def ep_pack(x: torch.Tensor, src_row: torch.Tensor, ir: Optional[torch.Tensor] = None, inp_res: float = -1.0):
+    """Rows in sorted order; with `ir` and `inp_res` given: (int8 codes, fp32 scale per row)."""
+    x2 = _rows(x)
+    P, K = src_row.numel(), x2.shape[1]
+    if ir is not None and inp_res > 0:
+        codes = torch.empty(P, K, dtype=torch.int8, device=x2.device)
+        scale = torch.empty(P, dtype=torch.float32, device=x2.device)
+        check(lib.amoe_ep_pack(ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, ptr(ir), float(inp_res), None,
+                               ptr(codes), ptr(scale), stream_ptr()), "amoe_ep_pack")
+        return codes, scale
+    rows = torch.empty(P, K, dtype=x2.dtype, device=x2.device)
+    check(lib.amoe_ep_pack(ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, None, -1.0, ptr(rows), None, None,
+                           stream_ptr()), "amoe_ep_pack")
+    return rows, None
+
+
+def ep_unpack(recv: torch.Tensor, dst_row: torch.Tensor, out_rows: int) -> torch.Tensor:
+    recv = recv.contiguous()
+    P, N = recv.shape
+    out = torch.zeros(out_rows, N, dtype=recv.dtype, device=recv.device)
+    check(lib.amoe_ep_unpack(ptr(recv), dtype_code(recv), N, ptr(dst_row), P, ptr(out), out.stride(0), stream_ptr()),
+          "amoe_ep_unpack")
+    return out

@@ -1,0 +1,369 @@
+// Reductions around the CVMM (combine over k, gate gradient, input-range gradient, per-expert
+// std) and the expert-parallel pack/unpack helpers.  All HBM-bound streaming kernels.
+#include "common.cuh"
+
+namespace amoe {
+namespace {
+
+// y[t,n] = sum_j w[t*k+j] * res[t*k+j, n]; thread per (t, 4 columns); j ascending.
+template <typename TR, typename TY>
+__global__ void combine_kernel(const TR* __restrict__ res, int64_t res_stride, const float* __restrict__ w, int64_t T,
+                               int k, int N, TY* __restrict__ y, int64_t y_stride) {
+  const int nq = (N + 3) / 4;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * nq) return;
+  const int64_t t = idx / nq;
+  const int n0 = static_cast<int>(idx % nq) * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < k; ++j) {
+    const int64_t s = t * k + j;
+    const float ws = w ? w[s] : 1.f;
+    const TR* row = res + s * res_stride + n0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (n0 + c < N) acc[c] = w ? acc[c] + ws * to_f32<TR>(row[c]) : acc[c] + to_f32<TR>(row[c]);
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    if (n0 + c < N) {
+      if constexpr (sizeof(TY) == 4)
+        y[t * y_stride + n0 + c] = acc[c];
+      else
+        y[t * y_stride + n0 + c] = __float2bfloat16_rn(acc[c]);
+    }
+}
+
+template <typename TY>
+__global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
+                                     const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
+                                     float step, const float* __restrict__ w, int64_t T, int k, int N,
+                                     TY* __restrict__ y, int64_t y_stride) {
+  const int nq = (N + 3) / 4;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * nq) return;
+  const int64_t t = idx / nq;
+  const int n0 = static_cast<int>(idx % nq) * 4;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int j = 0; j < k; ++j) {
+    const int64_t s = t * k + j;
+    const float ws = w ? w[s] : 1.f;
+    const float rm = row_mult ? row_mult[s] : 1.f;
+    const int e = raw_sel[s];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (n0 + c < N) {
+        float v = (static_cast<float>(codes[s * N + n0 + c]) * step) * col_scale[static_cast<int64_t>(e) * N + n0 + c];
+        v *= rm;
+        acc[c] += ws * v;
+      }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    if (n0 + c < N) {
+      if constexpr (sizeof(TY) == 4)
+        y[t * y_stride + n0 + c] = acc[c];
+      else
+        y[t * y_stride + n0 + c] = __float2bfloat16_rn(acc[c]);
+    }
+}
+
+// d[s] = res[s,:] . g[s/k,:]; one warp per slot.
+template <typename TR, typename TG>
+__global__ void row_dot_kernel(const TR* __restrict__ res, int64_t res_stride, const TG* __restrict__ g,
+                               int64_t g_stride, int64_t P, int k, int N, float* __restrict__ d) {
+  const int lane = threadIdx.x & 31;
+  const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (s >= P) return;
+  const TR* r = res + s * res_stride;
+  const TG* gr = g + (s / k) * g_stride;
+  float acc = 0.f;
+  for (int n = lane; n < N; n += 32) acc = fmaf(to_f32<TR>(r[n]), to_f32<TG>(gr[n]), acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) d[s] = acc;
+}
+
+// One warp per expert: ordered (lane-strided, then butterfly) sum of the expert's slot gradients.
+__global__ void ir_grad_reduce_kernel(const float* __restrict__ slot_grad, const int32_t* __restrict__ offsets,
+                                      const float* __restrict__ input_range, int E, float decay, float min_pct,
+                                      const unsigned long long* __restrict__ keep_count, double total,
+                                      float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (e >= E) return;
+  const int beg = offsets[e], end = offsets[e + 1];
+  float acc = 0.f;
+  for (int i = beg + lane; i < end; i += 32) acc += slot_grad[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    if (decay > 0.f && keep_count != nullptr) {
+      const float pct = static_cast<float>(static_cast<double>(*keep_count) / total);
+      if (pct > min_pct) acc += (decay * input_range[e]) * static_cast<float>(end - beg);
+    }
+    out[e] = acc;
+  }
+}
+
+// ws layout: double sum[E], double sq[E]
+template <typename T>
+__global__ void std_sum_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ x_row,
+                               const int32_t* __restrict__ offsets, int E, int pass, const double* __restrict__ mean,
+                               double* __restrict__ accum) {
+  // one warp per sorted position; block-level reduce per expert would need segmenting, so use one
+  // double atomic per warp (count of atomics = P, all on E addresses; this runs a handful of times
+  // per training run).
+  const int lane = threadIdx.x & 31;
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t P = offsets[E];
+  if (i >= P) return;
+  // expert of position i by binary search in offsets
+  int lo = 0, hi = E;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= i) lo = mid; else hi = mid;
+  }
+  const int e = lo;
+  const T* row = x + static_cast<int64_t>(x_row[i]) * stride;
+  double acc = 0.0;
+  if (pass == 0) {
+    for (int k = lane; k < K; k += 32) acc += static_cast<double>(to_f32<T>(row[k]));
+  } else {
+    const double mu = mean[e];
+    for (int k = lane; k < K; k += 32) {
+      double dlt = static_cast<double>(to_f32<T>(row[k])) - mu;
+      acc += dlt * dlt;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) atomicAdd(accum + e, acc);
+}
+
+__global__ void std_mean_kernel(const double* __restrict__ sum, const int32_t* __restrict__ offsets, int E, int K,
+                                double* __restrict__ mean) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const double cnt = static_cast<double>(offsets[e + 1] - offsets[e]) * K;
+  mean[e] = sum[e] / cnt;   // 0/0 = NaN for an expert without rows
+}
+
+__global__ void std_final_kernel(const double* __restrict__ sq, const int32_t* __restrict__ offsets, int E, int K,
+                                 float* __restrict__ out) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const double cnt = static_cast<double>(offsets[e + 1] - offsets[e]) * K;
+  out[e] = cnt > 0 ? static_cast<float>(sqrt(sq[e] / (cnt - 1.0))) : __int_as_float(0x7fc00000);
+}
+
+// Gather rows in sorted order; optionally apply the DAC and emit int8 codes + per-row scale.
+template <typename T>
+__global__ void ep_pack_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
+                               int64_t P, const float* __restrict__ ir, float inp_res, T* __restrict__ send_rows,
+                               int8_t* __restrict__ send_codes, float* __restrict__ send_scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (i >= P) return;
+  const T* row = x + static_cast<int64_t>(src_row[i]) * stride;
+  if (send_codes) {
+    const float r = ir[i];
+    const float fast = dac_fast_mul(true, r, false, 1.f, inp_res);
+    for (int k = lane; k < K; k += 32) {
+      float c = dac_code(to_f32<T>(row[k]), true, r, false, 1.f, inp_res, fast);
+      send_codes[i * K + k] = static_cast<int8_t>(c);
+    }
+    if (lane == 0) send_scale[i] = r;
+  } else {
+    for (int k = lane; k < K; k += 32) send_rows[i * K + k] = row[k];
+  }
+}
+
+template <typename T>
+__global__ void ep_unpack_kernel(const T* __restrict__ recv, int N, const int32_t* __restrict__ dst_row, int64_t P,
+                                 T* __restrict__ out, int64_t out_stride) {
+  const int lane = threadIdx.x & 31;
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (i >= P) return;
+  T* row = out + static_cast<int64_t>(dst_row[i]) * out_stride;
+  for (int n = lane; n < N; n += 32) row[n] = recv[i * N + n];
+}
+
+inline unsigned blocks_for(int64_t threads, int per_block) {
+  return static_cast<unsigned>((threads + per_block - 1) / per_block);
+}
+
+}  // namespace
+}  // namespace amoe
+
+using namespace amoe;
+
+extern "C" {
+
+int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const float* w, int64_t T, int32_t k,
+                 int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(res && y, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
+  const int64_t n = T * ((N + 3) / 4);
+  const unsigned blocks = blocks_for(n, 256);
+  if (res_dtype == AMOE_F32 && y_dtype == AMOE_F32)
+    combine_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, w, T, k,
+                                                             N, reinterpret_cast<float*>(y), y_stride);
+  else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_BF16)
+    combine_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
+        y_stride);
+  else if (res_dtype == AMOE_F32 && y_dtype == AMOE_BF16)
+    combine_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
+                                                                     w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
+                                                                     y_stride);
+  else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_F32)
+    combine_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
+                                                                     res_stride, w, T, k, N,
+                                                                     reinterpret_cast<float*>(y), y_stride);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("combine");
+  return AMOE_OK;
+}
+
+int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_t* raw_sel, const float* row_mult,
+                       float step, const float* w, int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype,
+                       int64_t y_stride, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(codes && col_scale && raw_sel && y, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
+  const int64_t n = T * ((N + 3) / 4);
+  const unsigned blocks = blocks_for(n, 256);
+  if (y_dtype == AMOE_F32)
+    combine_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
+                                                            reinterpret_cast<float*>(y), y_stride);
+  else if (y_dtype == AMOE_BF16)
+    combine_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T,
+                                                                    k, N, reinterpret_cast<__nv_bfloat16*>(y),
+                                                                    y_stride);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("combine_codes");
+  return AMOE_OK;
+}
+
+int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const void* g, int32_t g_dtype,
+                 int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(res && g && d, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
+  const unsigned blocks = blocks_for(P * 32, 256);
+  if (res_dtype == AMOE_F32 && g_dtype == AMOE_F32)
+    row_dot_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
+                                                             reinterpret_cast<const float*>(g), g_stride, P, k, N, d);
+  else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_BF16)
+    row_dot_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
+        P, k, N, d);
+  else if (res_dtype == AMOE_F32 && g_dtype == AMOE_BF16)
+    row_dot_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
+                                                                     reinterpret_cast<const __nv_bfloat16*>(g),
+                                                                     g_stride, P, k, N, d);
+  else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_F32)
+    row_dot_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
+                                                                     res_stride, reinterpret_cast<const float*>(g),
+                                                                     g_stride, P, k, N, d);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("row_dot");
+  return AMOE_OK;
+}
+
+int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range, int32_t E,
+                        float decay, float min_percentage, const unsigned long long* keep_count,
+                        double total_elements, float* out, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(ir_grad_slot && expert_offsets && out, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(E > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(!(decay > 0.f) || (keep_count && input_range && total_elements > 0), AMOE_ERR_NULL_POINTER);
+  ir_grad_reduce_kernel<<<blocks_for(static_cast<int64_t>(E) * 32, 128), 128, 0, stream>>>(
+      ir_grad_slot, expert_offsets, input_range, E, decay, min_percentage, keep_count, total_elements, out);
+  AMOE_LAUNCH_CHECK("ir_grad_reduce");
+  return AMOE_OK;
+}
+
+size_t amoe_expert_std_workspace_bytes(int32_t E) { return E > 0 ? static_cast<size_t>(E) * 3 * sizeof(double) : 0; }
+
+int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+                    const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out, void* workspace,
+                    size_t workspace_bytes, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && x_row && expert_offsets && std_out, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && E > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(dtype == AMOE_F32 || dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
+  AMOE_REQUIRE(workspace && workspace_bytes >= amoe_expert_std_workspace_bytes(E), AMOE_ERR_WORKSPACE);
+  double* sum = reinterpret_cast<double*>(workspace);
+  double* sq = sum + E;
+  double* mean = sq + E;
+  AMOE_CUDA(cudaMemsetAsync(workspace, 0, static_cast<size_t>(E) * 2 * sizeof(double), stream));
+  const unsigned blocks = blocks_for(P * 32, 256);
+  const unsigned eb = blocks_for(E, 128);
+  for (int pass = 0; pass < 2; ++pass) {
+    if (dtype == AMOE_F32)
+      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_row,
+                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq);
+    else
+      std_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
+                                                                x_row, expert_offsets, E, pass, mean,
+                                                                pass == 0 ? sum : sq);
+    AMOE_LAUNCH_CHECK("std_sum");
+    if (pass == 0) {
+      std_mean_kernel<<<eb, 128, 0, stream>>>(sum, expert_offsets, E, K, mean);
+      AMOE_LAUNCH_CHECK("std_mean");
+    }
+  }
+  std_final_kernel<<<eb, 128, 0, stream>>>(sq, expert_offsets, E, K, std_out);
+  AMOE_LAUNCH_CHECK("std_final");
+  return AMOE_OK;
+}
+
+int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int64_t P,
+                 const float* ir, float inp_res, void* send_rows, int8_t* send_codes, float* send_scale,
+                 amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && src_row, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE((send_codes != nullptr) != (send_rows != nullptr), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!send_codes || (ir && send_scale && inp_res > 0.f && inp_res >= 1.f / 127.5f), AMOE_ERR_UNSUPPORTED);
+  const unsigned blocks = blocks_for(P * 32, 256);
+  if (dtype == AMOE_F32)
+    ep_pack_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, P, ir,
+                                                      inp_res, reinterpret_cast<float*>(send_rows), send_codes,
+                                                      send_scale);
+  else if (dtype == AMOE_BF16)
+    ep_pack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
+                                                              src_row, P, ir, inp_res,
+                                                              reinterpret_cast<__nv_bfloat16*>(send_rows), send_codes,
+                                                              send_scale);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("ep_pack");
+  return AMOE_OK;
+}
+
+int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P, void* out,
+                   int64_t out_stride, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(recv_rows && dst_row && out, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
+  const unsigned blocks = blocks_for(P * 32, 256);
+  if (dtype == AMOE_F32)
+    ep_unpack_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(recv_rows), N, dst_row, P,
+                                                        reinterpret_cast<float*>(out), out_stride);
+  else if (dtype == AMOE_BF16)
+    ep_unpack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(recv_rows), N,
+                                                                dst_row, P, reinterpret_cast<__nv_bfloat16*>(out),
+                                                                out_stride);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("ep_unpack");
+  return AMOE_OK;
+}
+
+}  // extern "C"

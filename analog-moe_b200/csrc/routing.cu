@@ -1,0 +1,232 @@
+// Gate select (sigmoid + top-k) and the stable expert-contiguous slot sort.
+//
+// Four small kernels, no host synchronisation, no atomics on the data path, so the slot order is a
+// pure function of the logits:
+//   topk_kernel      one warp per token: k rounds of warp arg-max over the E gate values
+//   chunk_hist       one warp per chunk of kChunk flat slots: per-expert counts of the chunk
+//   scan_kernel      one CTA: exclusive scan over (expert, chunk) -> expert offsets + chunk bases
+//   scatter_kernel   one warp per chunk: stable rank inside the chunk via match.any
+#include "common.cuh"
+
+namespace amoe {
+namespace {
+
+constexpr int kChunk = 1024;   // flat slots per warp in the sort
+constexpr int kMaxE = 1024;
+constexpr int kMaxK = 32;
+
+__global__ void topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int apply_sigmoid,
+                            int32_t* __restrict__ raw_sel, float* __restrict__ gate) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (t >= T) return;
+  // each lane holds experts lane, lane+32, ...
+  constexpr int kPer = kMaxE / 32;
+  float v[kPer];
+  const float* row = logits + t * E;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    int e = lane + 32 * i;
+    float x = -INFINITY;
+    if (e < E) {
+      x = row[e];
+      if (apply_sigmoid) x = 1.0f / (1.0f + expf(-x));
+    }
+    v[i] = x;
+  }
+  const int per = (E + 31) / 32;
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) {
+      if (i < per) {
+        int e = lane + 32 * i;
+        // NaN never wins; ties go to the lower expert id
+        if (e < E && (v[i] > best || (v[i] == best && e < best_e))) {
+          best = v[i];
+          best_e = e;
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if (best_e == 0x7fffffff) best_e = j;  // all-NaN row: keep indices in range
+    if (lane == 0) {
+      raw_sel[t * k + j] = best_e;
+      gate[t * k + j] = best;
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kPer; ++i)
+        if (i == (best_e >> 5)) v[i] = -INFINITY;
+    }
+  }
+}
+
+__global__ void chunk_hist_kernel(const int32_t* __restrict__ raw_sel, int64_t P, int E,
+                                  int32_t* __restrict__ hist /*[nchunks,E]*/) {
+  extern __shared__ int32_t cnt[];  // [warps_per_block][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  int32_t* my = cnt + warp * E;
+  for (int e = lane; e < E; e += 32) my[e] = 0;
+  __syncwarp();
+  const int64_t s0 = chunk * kChunk;
+  if (s0 < P) {
+    for (int64_t s = s0 + lane; s < s0 + kChunk; s += 32) {
+      bool ok = s < P;
+      int e = ok ? raw_sel[s] : -1;
+      ok = ok && e >= 0 && e < E;
+      unsigned m = __match_any_sync(0xffffffffu, ok ? e : -1);
+      if (ok && (__ffs(m) - 1) == lane) my[e] += __popc(m);
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32) hist[chunk * E + e] = my[e];
+  }
+}
+
+// hist[c][e] -> exclusive position of (e, c) in the sorted list; offsets[E+1].
+__global__ void scan_kernel(int32_t* __restrict__ hist, int64_t nchunks, int E, int32_t* __restrict__ offsets) {
+  __shared__ int32_t total[kMaxE + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t run = 0;
+    for (int64_t c = 0; c < nchunks; ++c) {
+      int32_t h = hist[c * E + e];
+      hist[c * E + e] = run;
+      run += h;
+    }
+    total[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t run = 0;
+    for (int e = 0; e < E; ++e) {
+      int32_t h = total[e];
+      total[e] = run;
+      run += h;
+    }
+    total[E] = run;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = total[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int32_t base = total[e];
+    for (int64_t c = 0; c < nchunks; ++c) hist[c * E + e] += base;
+  }
+}
+
+__global__ void scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t P, int E, int k,
+                               const int32_t* __restrict__ base /*[nchunks,E]*/, int32_t* __restrict__ sel_sorted,
+                               int32_t* __restrict__ token_index, int32_t* __restrict__ slot_index) {
+  extern __shared__ int32_t cnt[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  const int64_t s0 = chunk * kChunk;
+  if (s0 >= P) return;
+  int32_t* my = cnt + warp * E;
+  for (int e = lane; e < E; e += 32) my[e] = base[chunk * E + e];
+  __syncwarp();
+  for (int64_t s = s0 + lane; s < s0 + kChunk; s += 32) {
+    bool ok = s < P;
+    int e = ok ? raw_sel[s] : -1;
+    ok = ok && e >= 0 && e < E;
+    unsigned m = __match_any_sync(0xffffffffu, ok ? e : -1);
+    int pos = 0;
+    if (ok) pos = my[e] + __popc(m & ((1u << lane) - 1u));
+    __syncwarp();
+    if (ok && (__ffs(m) - 1) == lane) my[e] += __popc(m);
+    __syncwarp();
+    if (ok) {
+      sel_sorted[pos] = e;
+      slot_index[pos] = static_cast<int32_t>(s);
+      token_index[pos] = static_cast<int32_t>(s / k);
+    }
+  }
+}
+
+__global__ void offsets_from_sorted_kernel(const int32_t* __restrict__ sel, int64_t P, int E,
+                                           int32_t* __restrict__ offsets, int32_t* status) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i > P) return;
+  int prev = i == 0 ? -1 : sel[i - 1];
+  int cur = i == P ? E : sel[i];
+  if (i < P && (cur < 0 || cur >= E)) {
+    report(status, AMOE_ERR_INDEX_RANGE, 1, static_cast<int>(i), cur);
+    cur = cur < 0 ? 0 : E - 1;
+  }
+  if (prev < -1) prev = -1;
+  if (prev >= E) prev = E - 1;
+  if (cur < prev) {  // not sorted
+    report(status, AMOE_ERR_INDEX_RANGE, 2, static_cast<int>(i), cur);
+    return;
+  }
+  for (int e = prev + 1; e <= cur; ++e) offsets[e] = static_cast<int32_t>(i);
+}
+
+}  // namespace
+}  // namespace amoe
+
+using namespace amoe;
+
+extern "C" {
+
+size_t amoe_select_sort_workspace_bytes(int64_t T, int32_t E, int32_t k) {
+  if (T <= 0 || E <= 0 || k <= 0) return 0;
+  int64_t P = T * k;
+  int64_t nchunks = (P + kChunk - 1) / kChunk;
+  return static_cast<size_t>(nchunks) * E * sizeof(int32_t);
+}
+
+int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32_t apply_sigmoid, int32_t* raw_sel,
+                     float* gate, int32_t* sel_sorted, int32_t* token_index, int32_t* slot_index,
+                     int32_t* expert_offsets, void* workspace, size_t workspace_bytes, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(T > 0 && E > 0 && k > 0 && E <= kMaxE && k <= kMaxK && k <= E, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(T * k < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(logits && raw_sel && gate && sel_sorted && token_index && slot_index && expert_offsets,
+               AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(workspace && workspace_bytes >= amoe_select_sort_workspace_bytes(T, E, k), AMOE_ERR_WORKSPACE);
+  const int64_t P = T * k;
+  const int64_t nchunks = (P + kChunk - 1) / kChunk;
+  int32_t* hist = reinterpret_cast<int32_t*>(workspace);
+  {
+    const int threads = 256;
+    const int64_t blocks = (T * 32 + threads - 1) / threads;
+    topk_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    AMOE_LAUNCH_CHECK("topk");
+  }
+  // warps per block limited by shared memory: E ints per warp
+  int wpb = 8;
+  while (wpb > 1 && static_cast<size_t>(wpb) * E * sizeof(int32_t) > 32 * 1024) wpb >>= 1;
+  const unsigned blocks = static_cast<unsigned>((nchunks + wpb - 1) / wpb);
+  const size_t smem = static_cast<size_t>(wpb) * E * sizeof(int32_t);
+  chunk_hist_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, hist);
+  AMOE_LAUNCH_CHECK("chunk_hist");
+  scan_kernel<<<1, 256, 0, stream>>>(hist, nchunks, E, expert_offsets);
+  AMOE_LAUNCH_CHECK("scan");
+  scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, sel_sorted, token_index, slot_index);
+  AMOE_LAUNCH_CHECK("scatter");
+  return AMOE_OK;
+}
+
+int amoe_expert_offsets(const int32_t* sel_sorted, int64_t P, int32_t E, int32_t* expert_offsets,
+                        int32_t* dev_status, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(P > 0 && E > 0 && P < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(sel_sorted && expert_offsets, AMOE_ERR_NULL_POINTER);
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((P + 1 + threads - 1) / threads);
+  offsets_from_sorted_kernel<<<blocks, threads, 0, stream>>>(sel_sorted, P, E, expert_offsets, dev_status);
+  AMOE_LAUNCH_CHECK("offsets_from_sorted");
+  return AMOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,260 @@
+/*
+ * amoe.h - C ABI of the B200 analog-CVMM library (libamoe_b200.so).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, runs
+ * asynchronously on that stream and returns an `amoe_status`.  Unless a function's
+ * comment says otherwise the library allocates nothing: the caller owns inputs,
+ * outputs and the workspaces whose sizes the `*_workspace_bytes` helpers report.
+ * Index arrays are int32.  Matrices are row-major with the row stride given in
+ * elements.  "Slot" = one routed (token, expert) pair; slots are numbered
+ * token*k + j ("flat slot") and are processed in expert-sorted order ("sorted
+ * position").  P = T*k slots, E experts.
+ *
+ * The functions replace the Triton kernels and their wrappers in the reference's
+ * analog_moe/triton_src/cvmm.py; each comment cites the lines it replaces.
+ */
+#ifndef AMOE_H_
+#define AMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* amoe_stream_t; /* a cudaStream_t */
+
+typedef enum amoe_status {
+  AMOE_OK = 0,
+  AMOE_ERR_BAD_SHAPE = 1,     /* a size is non-positive or violates a documented limit */
+  AMOE_ERR_BAD_DTYPE = 2,
+  AMOE_ERR_NULL_POINTER = 3,  /* a required pointer is NULL */
+  AMOE_ERR_WORKSPACE = 4,     /* workspace missing or too small */
+  AMOE_ERR_CUDA = 5,          /* a CUDA runtime/driver call failed; see amoe_last_error_string */
+  AMOE_ERR_UNSUPPORTED = 6,   /* combination of options not implemented */
+  AMOE_ERR_DEVICE = 7,        /* the current device is not an sm_100 part */
+  AMOE_ERR_INDEX_RANGE = 8,   /* device-side check saw an index out of range (amoe_read_device_status) */
+  AMOE_ERR_WAIT_LIMIT = 9     /* a bounded device-side wait gave up (amoe_read_device_status) */
+} amoe_status;
+
+typedef enum amoe_dtype { AMOE_F32 = 0, AMOE_BF16 = 1 } amoe_dtype;
+
+/* How the contraction is carried out. */
+typedef enum amoe_precision {
+  AMOE_PREC_BF16X1 = 0, /* one tcgen05 bf16 pass; exact when both operands are bf16-representable */
+  AMOE_PREC_SPLIT = 1,  /* fp32 operands split into bf16 hi+lo terms, 2-3 tcgen05 passes, fp32 accumulate */
+  AMOE_PREC_FP32_SIMT = 2 /* CUDA-core fp32 FMA (the arithmetic the reference's fp32 kernel uses) */
+} amoe_precision;
+
+int amoe_version(void);
+const char* amoe_status_string(int status);
+/* Text of the last CUDA error this thread's calls ran into ("" if none). */
+const char* amoe_last_error_string(void);
+/* AMOE_OK if the current CUDA device can run the kernels (compute capability 10.x). */
+int amoe_check_device(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Device status word.  Kernels never trap: an index outside its range or a bounded wait that
+ * ran out is recorded in a caller-provided int32[4] {code, detail0, detail1, detail2} (may be
+ * NULL to disable) and the offending access is skipped.  amoe_read_device_status copies it to
+ * the host (synchronising the stream) and returns the amoe_status it encodes.
+ * ---------------------------------------------------------------------------------------- */
+int amoe_read_device_status(const int32_t* dev_status, int32_t host_copy[4], amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Routing.  Replaces the sigmoid/top-k of the sigma-MoE base layer (restated in the reference at
+ * tests/test_moe_layer_aihwkit.py:71-76) and cvmm_prepare_sel's flatten+sort (cvmm.py:31-34).
+ *
+ * logits [T,E] fp32 -> raw_sel [T,k] (expert ids by descending gate value, lower id first on
+ * ties), gate [T,k] (sigmoid(logit) if apply_sigmoid else logit), and the stable expert-sorted
+ * slot list: sel_sorted [P], token_index [P] (= flat slot / k), slot_index [P] (flat slot),
+ * expert_offsets [E+1].  E <= 1024, k <= 32, k <= E.  Workspace: amoe_select_sort_workspace_bytes.
+ * ---------------------------------------------------------------------------------------- */
+size_t amoe_select_sort_workspace_bytes(int64_t T, int32_t E, int32_t k);
+int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32_t apply_sigmoid,
+                     int32_t* raw_sel, float* gate, int32_t* sel_sorted, int32_t* token_index,
+                     int32_t* slot_index, int32_t* expert_offsets, void* workspace, size_t workspace_bytes,
+                     amoe_stream_t stream);
+
+/* expert_offsets [E+1] from an already sorted expert-id list (a CVMMSel.sel built elsewhere). */
+int amoe_expert_offsets(const int32_t* sel_sorted, int64_t P, int32_t E, int32_t* expert_offsets,
+                        int32_t* dev_status, amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Weight pre-pass.  Replaces modify_weight (moe_layer_aihwkit_lightning.py:313-382,
+ * moe_layer_aihwkit.py:144-196) and the |W| maxima the layers take for the output noise
+ * (moe_layer_aihwkit_lightning.py:480-487), and lays the weights out for the tensor cores.
+ *
+ * W [E,K,N] (strides in elements, any layout) -> col_scale [E,N] fp32 = per-column max|W|
+ * (per_channel_scale) or the per-expert max broadcast; W' = discretise(W) + std*scale*z with z
+ * Philox normals (seed, offset; element (e,k,n) = row e*K+k, column n of the weight stream);
+ * then, for the tcgen05 kernels, bf16 "hi" (and "lo" = bf16(W' - hi) when requested) copies in two
+ * K-major layouts, zero padded: `fwd_*` [E, Npad, Kpad] for x@W and `bwd_*` [E, Kpad2, Npad2]
+ * for g@W^T, where Npad = roundup(N,16), Kpad = roundup(K,64), Kpad2 = roundup(K,16),
+ * Npad2 = roundup(N,64) (amoe_prepared_dims).  `w_out` (optional, [E,K,N] fp32 contiguous) receives W' itself.
+ * Any of the output pointers may be NULL.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct amoe_weight_prepass_args {
+  const void* w; int32_t w_dtype; int32_t E, K, N;
+  int64_t w_stride_e, w_stride_k, w_stride_n;
+  int32_t per_channel_scale;      /* 1: col_scale per column, 0: per expert */
+  float noise_std;                /* <=0: no additive noise */
+  int32_t noise_per_channel;      /* scale of the noise: per column (1) or per expert (0) maximum */
+  float discretize_res;           /* <=0: off; else n_states = max(res, 1/res) */
+  uint64_t seed; uint32_t offset;
+  float* col_scale;               /* [E,N] */
+  float* w_out;                   /* [E,K,N] fp32 or NULL */
+  void* fwd_hi; void* fwd_lo;     /* bf16 [E,Npad,Kpad] or NULL */
+  void* bwd_hi; void* bwd_lo;     /* bf16 [E,Kpad2,Npad2] or NULL */
+  void* workspace; size_t workspace_bytes;  /* amoe_weight_prepass_workspace_bytes */
+} amoe_weight_prepass_args;
+size_t amoe_weight_prepass_workspace_bytes(int32_t E, int32_t K, int32_t N);
+/* Padded extents of the prepared copies: dims[0..1] = {Npad, Kpad} (fwd), dims[2..3] = {Kpad2, Npad2} (bwd). */
+void amoe_prepared_dims(int32_t K, int32_t N, int32_t dims[4]);
+int amoe_weight_prepass(const amoe_weight_prepass_args* args, amoe_stream_t stream);
+
+/* |x| maximum of every row, x [R,K] -> absmax [R].  Replaces x.abs().amax(-1) (cvmm.py:733,737). */
+int amoe_row_absmax(const void* x, int32_t dtype, int64_t R, int32_t K, int64_t stride, float* absmax,
+                    amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * The conditional vector-matrix multiply.
+ *
+ * amoe_cvmm_fwd replaces cvmm_kernel + cvmm_triton_quantized (cvmm.py:37-231, 529-631) including
+ * the noise the layers materialise (moe_layer_aihwkit_lightning.py:471-492), and adds the ADC:
+ *   for sorted position i (expert e, source row r=a_row[i], destination row c=dst_row[i]):
+ *     a   = A[r,:]; clamp to +-ir[i]; /ir[i]; /a_absmax[r]; round(a/inp_res)  (integer DAC code)
+ *     acc = inp_res * sum_k code_k W'[e,k,:]             (fp32 accumulate)
+ *     acc += noise[c,:]  |  noise_std*col_scale[e,:]*z(c,:)            (Philox, seed/offset)
+ *     ADC: q = rint(clamp(acc/col_scale[e,:], +-out_bound) / step), acc = q*step*col_scale[e,:]
+ *     out[c,:] = acc * a_absmax[r] * ir[i];  out_codes[c,:] = q
+ *
+ * amoe_cvmm_dx replaces the second cvmm_triton_quantized call of CVMM.backward and the torch code
+ * after it (cvmm.py:828-881): acc = G[r,:] @ W[e]^T (no DAC), then with x_ref/ir given
+ *     up   = x_ref[xr,:] >= ir[i], low = x_ref[xr,:] <= -ir[i], keep = |x_ref[xr,:]| < ir[i]
+ *     ir_grad[i] = (sum_n min(up*acc*rs,0) - sum_n max(low*acc*rs,0)) * (relative ? ir[i]*grad_scale : 1)
+ *     out[c,:]   = keep * acc * rs        rs = row_scale[c] (the gate, down-projection) or 1
+ *     keep_count += number of kept elements (for the decay term)
+ *
+ * Weights: `w` [E,K,N] fp32/bf16 with strides for AMOE_PREC_FP32_SIMT; the prepared bf16 copies
+ * (see amoe_weight_prepass; fwd_* for amoe_cvmm_fwd, bwd_* for amoe_cvmm_dx) otherwise.
+ * For amoe_cvmm_dx, K and N below are those of the *forward* weight [E,K,N]: A has N columns and
+ * the result has K columns.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct amoe_cvmm_args {
+  int64_t P;                      /* sorted positions */
+  int32_t E, K, N;                /* weight [E,K,N] */
+  int32_t precision;              /* amoe_precision */
+  const int32_t* expert_offsets;  /* [E+1] */
+  const void* a; int32_t a_dtype; int64_t a_stride; int64_t a_rows;   /* input rows */
+  const int32_t* a_row;           /* [P] source row of sorted position i ... */
+  int32_t a_row_div;              /* ... divided by this (>=1; k folds the repeat of a token's row over its slots) */
+  const int32_t* dst_row;         /* [P] destination row of sorted position i */
+  int64_t dst_rows;               /* rows of out */
+  /* weights */
+  const void* w; int32_t w_dtype; int64_t w_stride_e, w_stride_k, w_stride_n;
+  const void* w_hi; const void* w_lo;  /* prepared bf16 copies (lo may be NULL) */
+  /* DAC */
+  const float* ir;                /* [P] by sorted position, or NULL */
+  const float* a_absmax;          /* [a_rows] by source row, or NULL */
+  float inp_res;                  /* <=0: no quantisation */
+  /* output noise */
+  const float* noise;             /* [dst_rows,N] fp32 by destination row, or NULL */
+  float noise_std;                /* >0: Philox noise noise_std*col_scale[e,n]*z */
+  uint64_t seed; uint32_t offset;
+  const float* col_scale;         /* [E,N] (needed for Philox noise and ADC) */
+  /* ADC */
+  float out_res, out_bound;       /* out_res<=0: off */
+  /* outputs */
+  void* out; int32_t out_dtype; int64_t out_stride;
+  int8_t* out_codes;              /* [dst_rows,N] or NULL */
+  /* backward-only (amoe_cvmm_dx) */
+  const void* x_ref; int32_t x_ref_dtype; int64_t x_ref_stride; int64_t x_ref_rows;
+  const int32_t* x_ref_row;       /* [P] row of x_ref for sorted position i */
+  const float* row_scale;         /* [dst_rows] by destination row, or NULL */
+  float* ir_grad;                 /* [P] by sorted position, or NULL */
+  int32_t ir_grad_relative; float ir_grad_scale;
+  unsigned long long* keep_count; /* one counter, incremented; or NULL */
+  /* plumbing */
+  void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
+  int32_t* dev_status;            /* int32[4] or NULL */
+} amoe_cvmm_args;
+size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E);
+int amoe_cvmm_fwd(const amoe_cvmm_args* args, amoe_stream_t stream);
+int amoe_cvmm_dx(const amoe_cvmm_args* args, amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * dW.  Replaces cvmm_backward_kernel3 + cvmm_triton_backward (cvmm.py:234-397, 645-696) and the
+ * outer product that feeds it in the down-projection (cvmm.py:789):
+ *   dW[e] = sum_{i in e} clamp(X[x_row[i],:], +-ir[i])^T (x) (g_scale[g_row[i]] * G[g_src_row(i),:])
+ * where g_src_row(i) = g_row[i] / g_div (g_div = k folds the repeat over the k slots of a token;
+ * 1 otherwise).  One owner per output tile, no atomics: results do not depend on scheduling.
+ * dW is fp32 [E,K,N] contiguous and is fully written (zeros for experts without slots).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct amoe_dw_args {
+  int64_t P; int32_t E, K, N; int32_t precision;
+  const int32_t* expert_offsets;
+  const void* x; int32_t x_dtype; int64_t x_stride; int64_t x_rows;
+  const int32_t* x_row;           /* [P] */
+  const float* ir;                /* [P] or NULL */
+  const void* g; int32_t g_dtype; int64_t g_stride; int64_t g_rows;
+  const int32_t* g_row;           /* [P] */
+  int32_t g_div;                  /* >=1 */
+  const float* g_scale;           /* indexed by g_row[i], or NULL */
+  float* dw;                      /* [E,K,N] */
+  void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
+  int32_t* dev_status;
+} amoe_dw_args;
+int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Reductions around the CVMM.
+ * amoe_combine: y[t,:] = sum_j w[t*k+j] * res[t*k+j,:] in slot order (w NULL = 1).  Replaces the
+ *   gate-weighted reduction (cvmm.py:757-759), its backward (cvmm.py:888) and the sum over k of
+ *   the up-projection's input gradient (cvmm.py:890-891).  With `codes` given instead of `res`
+ *   the rows are rebuilt from ADC codes: codes*step*col_scale[raw_sel[slot],:]*row_mult[slot].
+ * amoe_row_dot: d[s] = res[s,:] . g[s/k,:]  (gate gradient, cvmm.py:889).
+ * amoe_ir_grad_reduce: per-expert sum of the per-slot input-range gradients plus the decay term
+ *   decay*ir_e*count_e*[keep_count/total > min_percentage] (cvmm.py:872-878 followed by autograd's
+ *   index-add of input_range[ir_idx][sel]).  ir_grad_slot [P] sorted; out [E].
+ * ---------------------------------------------------------------------------------------- */
+int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const float* w, int64_t T, int32_t k,
+                 int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream);
+int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_t* raw_sel, const float* row_mult,
+                       float step, const float* w, int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype,
+                       int64_t y_stride, amoe_stream_t stream);
+int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const void* g, int32_t g_dtype,
+                 int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream);
+int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range,
+                        int32_t E, float decay, float min_percentage, const unsigned long long* keep_count,
+                        double total_elements, float* out, amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-expert standard deviation of the routed rows.  Replaces cvmm_std and its two kernels
+ * (cvmm.py:400-526).  x [R,K], x_row [P] by sorted position -> std [E] (NaN for experts without
+ * rows, as in the reference).  Workspace: amoe_expert_std_workspace_bytes(E) bytes, which the call
+ * clears itself.
+ * ---------------------------------------------------------------------------------------- */
+size_t amoe_expert_std_workspace_bytes(int32_t E);
+int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+                    const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out, void* workspace,
+                    size_t workspace_bytes, amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Expert-parallel exchange helpers (no counterpart in the reference, which is single-GPU).
+ * amoe_ep_pack gathers the rows of the sorted slot list into a contiguous send buffer in sorted
+ * order (so that each destination rank's experts form one contiguous block) and can apply the DAC
+ * on the way: int8 codes + one fp32 scale per row instead of the raw rows.
+ * amoe_ep_unpack scatters received rows back to their flat-slot rows.
+ * ---------------------------------------------------------------------------------------- */
+int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int64_t P,
+                 const float* ir, float inp_res, void* send_rows, int8_t* send_codes, float* send_scale,
+                 amoe_stream_t stream);
+int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P,
+                   void* out, int64_t out_stride, amoe_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AMOE_H_ */

@@ -1,0 +1,318 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle and against the
+golden vectors produced by the reference.  Tolerances are written next to each comparison."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import cvmm_oracle as O
+from test_oracle_golden import LAYER_CASES, load
+
+pytestmark = pytest.mark.gpu
+
+PRECS = {"simt": 2, "split": 1, "bf16x1": 0}
+# max abs error relative to max|reference| (scale floored at 1): CUDA-core fp32; bf16 hi+lo split on
+# tensor cores; single bf16 pass (weights and unquantised operands rounded to 8 bits of mantissa).
+TOL = {"simt": 2e-5, "split": 1e-4, "bf16x1": 3e-2}
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from analog_moe import _cabi
+    assert _cabi.lib.amoe_check_device() == 0, "the kernels are built for sm_100a only"
+    return torch.device("cuda:0")
+
+
+class IRP:
+    def __init__(self, enable, decay=0.0, input_min_percentage=0.95):
+        self.enable, self.decay, self.input_min_percentage = enable, decay, input_min_percentage
+
+
+class IOP:
+    pass
+
+
+def run_layer_cuda(c, prec, dev, ext_kw=None):
+    from analog_moe import CVMM, CVMMExt
+    T, k, E = c["T"], c["k"], c["E"]
+    sel = c["sel"].to(dev)
+    perm = c["perm"].to(dev).long()
+    use_ir = bool(c["use_ir"])
+    x = c["x"].to(dev).view(1, T, -1).requires_grad_()
+    keys = c["keys"].to(dev).requires_grad_()
+    values = c["values"].to(dev).requires_grad_()
+    gate = c["gate"].to(dev).view(1, T, k).requires_grad_()
+    ir = c["input_range"].to(dev).requires_grad_()
+    sel3 = sel.view(1, T, k)
+    irp = IRP(use_ir, float(c["decay"]))
+    bir_up = ir[0][sel3.long()] if use_ir else None
+    bir_dn = ir[1][sel3.long()] if use_ir else None
+    n_up = c["noise_up"].to(dev).unsqueeze(0) if "noise_up" in c else None
+    n_dn = c["noise_dn"].to(dev).unsqueeze(0) if "noise_dn" in c else None
+    ext = lambda: CVMMExt(precision=PRECS[prec], check_status=True, **(ext_kw or {}))
+    h_pre = CVMM.apply(x, perm // k, sel3, keys, c["inp_res"], bir_up, perm, None, n_up, irp, IOP(), ext())
+    h_pre.retain_grad()
+    h = torch.relu(h_pre)
+    h.retain_grad()
+    y = CVMM.apply(h, perm, sel3, values, c["inp_res"], bir_dn, None, gate, n_dn, irp, IOP(), ext())
+    (y * c["grad_y"].to(dev).view(1, T, -1)).sum().backward()
+    out = dict(h_pre=h_pre.detach(), y=y.detach(), dh=h.grad, dh_pre=h_pre.grad, dx=x.grad, dkeys=keys.grad,
+               dvalues=values.grad, dgate=gate.grad)
+    if use_ir:
+        out["d_input_range"] = ir.grad
+    return {k_: v.float().cpu() for k_, v in out.items()}
+
+
+@pytest.mark.parametrize("prec", list(PRECS))
+@pytest.mark.parametrize("name", LAYER_CASES)
+def test_layer_cases_vs_reference_golden(golden_dir, dev, name, prec):
+    c = load(golden_dir, name)
+    got = run_layer_cuda(c, prec, dev)
+    for key, val in got.items():
+        ref = c[key]
+        scale = max(1.0, float(ref.abs().max()))
+        err = float((val.reshape(ref.shape) - ref).abs().max())
+        assert err <= TOL[prec] * scale, f"{name}:{key}:{prec} max err {err:.3e} (scale {scale:.3g})"
+
+
+def rand_routing(T, E, k, seed, dev):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    s = O.select_sort(logits, k)
+    return logits, s
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 4, 1), (7, 4, 2), (512, 8, 2), (1000, 64, 8), (4099, 16, 4), (333, 1024, 32)])
+def test_select_sort(dev, T, E, k):
+    from analog_moe import ops
+    logits, s = rand_routing(T, E, k, T + E, dev)
+    r = ops.select_sort(logits.to(dev), k)
+    # bit-exact integer outputs
+    assert torch.equal(r.raw_sel.cpu(), s.raw_sel)
+    assert torch.equal(r.sel.cpu(), s.sel)
+    assert torch.equal(r.token_index.cpu(), s.token_index)
+    assert torch.equal(r.slot_index.cpu(), s.slot_index)
+    assert torch.equal(r.expert_offsets.cpu(), s.expert_offsets)
+    # gate values: sigmoid evaluated by expf on the device vs the host library, 1e-6 absolute
+    assert torch.allclose(r.gate.cpu(), s.gate, atol=1e-6, rtol=0)
+    assert torch.equal(ops.expert_offsets(r.sel, E).cpu(), s.expert_offsets)
+
+
+def test_select_sort_ties_and_skew(dev):
+    from analog_moe import ops
+    logits = torch.zeros(64, 8)
+    logits[:, 5] = 9.0          # everyone picks expert 5 first, then the lowest ids on the tie
+    r = ops.select_sort(logits.to(dev), 3)
+    assert torch.equal(r.raw_sel.cpu(), torch.tensor([[5, 0, 1]], dtype=torch.int32).expand(64, 3))
+    off = r.expert_offsets.cpu().tolist()
+    assert off == [0, 64, 128, 128, 128, 128, 192, 192, 192]
+
+
+def test_dac_codes_bit_exact_with_adversarial_ties(dev):
+    """Integer DAC codes must equal the oracle's bit for bit, including inputs that sit on or next to
+    a rounding tie of the (x/ir)/res chain."""
+    from analog_moe import ops
+    res = 2.0 / 254.0
+    g = torch.Generator().manual_seed(11)
+    P, K = 256, 512
+    ir = torch.rand(P, generator=g) * 3 + 0.3
+    m = torch.randint(-127, 127, (P, K), generator=g).float()
+    x = (m + 0.5) * res * ir.view(-1, 1)                       # nominal ties
+    x = x + (torch.randint(-3, 4, (P, K), generator=g).float() * torch.finfo(torch.float32).eps * x.abs())
+    x[::7] = torch.randn(K, generator=g) * 2                   # ordinary rows, some clipping
+    _, want = O.dac(x, ir, None, res)
+    codes, scale = ops.ep_pack(x.to(dev), torch.arange(P, dtype=torch.int32, device=dev), ir.to(dev), res)
+    assert torch.equal(codes.cpu().float(), want), "DAC code mismatch"
+    assert torch.equal(scale.cpu(), ir)
+
+
+@pytest.mark.parametrize("prec", ["simt", "split", "bf16x1"])
+def test_dac_codes_through_the_gemm(dev, prec):
+    """With identity weights the CVMM output is code*res*ir: the codes come back exactly."""
+    from analog_moe import ops
+    res = 2.0 / 254.0
+    T, K, E = 300, 64, 3
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, K, generator=g) * 1.5
+    logits, s = rand_routing(T, E, 1, 9, dev)
+    ir_e = torch.tensor([1.0, 2.0, 0.5])
+    ir = ir_e[s.sel.long()]
+    W = torch.eye(K).repeat(E, 1, 1)
+    _, want = O.dac(x[s.token_index.long()], ir, None, res)
+    pw = ops.weight_prepass(W.to(dev), PRECS[prec])
+    out, _ = ops.cvmm_fwd(x.to(dev), s.token_index.to(dev), s.slot_index.to(dev), s.expert_offsets.to(dev), pw,
+                          PRECS[prec], P=T, dst_rows=T, ir=ir.to(dev), inp_res=res)
+    got = out.cpu()[s.slot_index.long()] / (res * ir.view(-1, 1))
+    assert torch.equal(torch.round(got), want)
+    assert float((got - want).abs().max()) < 1e-3
+
+
+@pytest.mark.parametrize("prec", ["simt", "split"])
+def test_adc_codes(dev, prec):
+    """ADC codes against the oracle: no mismatch away from rounding ties; near a tie (pre-rounding
+    value within 1e-3 of .5, where fp32 summation order decides) at most one code apart."""
+    from analog_moe import ops
+    T, K, N, E, k = 200, 96, 80, 5, 2
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(T, K, generator=g)
+    W = torch.randn(E, K, N, generator=g) / K ** 0.5
+    logits, s = rand_routing(T, E, k, 3, dev)
+    ir = torch.full((T * k,), 2.5)
+    res = 2.0 / 254.0
+    wmax = O.weight_max(W, True)
+    out_w, _, codes_w = O.cvmm_forward(x, s.token_index, s.sel, W, res, ir, s.slot_index, None, None,
+                                       (254.0, 12.0, wmax), return_codes=True)
+    pw = ops.weight_prepass(W.to(dev), PRECS[prec])
+    out, codes = ops.cvmm_fwd(x.to(dev), s.token_index.to(dev), s.slot_index.to(dev), s.expert_offsets.to(dev), pw,
+                              PRECS[prec], P=T * k, dst_rows=T * k, ir=ir.to(dev), inp_res=res, out_res=254.0,
+                              out_bound=12.0, want_codes=True)
+    codes = codes.cpu().float()
+    # pre-rounding value from the oracle, to classify ties
+    acc = O.cvmm_forward(x, s.token_index, s.sel, W, res, None if False else ir, s.slot_index) / 2.5
+    e_of_slot = torch.empty(T * k, dtype=torch.long)
+    e_of_slot[s.slot_index.long()] = s.sel.long()
+    v = acc / wmax[e_of_slot] / O.adc_step(254.0, 12.0)
+    near_tie = ((v - torch.floor(v)) - 0.5).abs() < 1e-3
+    diff = (codes - codes_w).abs()
+    assert int((diff[~near_tie] != 0).sum()) == 0
+    assert float(diff.max()) <= 1.0
+    assert float(near_tie.float().mean()) < 5e-3
+    same = diff == 0
+    assert torch.allclose(out.cpu()[same], out_w[same], rtol=1e-6, atol=1e-6)
+    assert codes.abs().max() <= 127
+
+
+def test_philox_noise_elementwise_and_statistics(dev):
+    """The in-kernel Philox noise equals the oracle's generator element by element (1e-4: fast-math
+    log/sincos), and its mean/std over a seed sweep are within 2% of the requested values."""
+    from analog_moe import ops
+    T, K, N, E, k = 128, 32, 64, 4, 2
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(T, K, generator=g)
+    W = torch.randn(E, K, N, generator=g) / K ** 0.5
+    logits, s = rand_routing(T, E, k, 4, dev)
+    P = T * k
+    pw = ops.weight_prepass(W.to(dev), 2)
+    args = (x.to(dev), s.token_index.to(dev), s.slot_index.to(dev), s.expert_offsets.to(dev), pw, 2)
+    clean, _ = ops.cvmm_fwd(*args, P=P, dst_rows=P)
+    e_of_slot = torch.empty(P, dtype=torch.long)
+    e_of_slot[s.slot_index.long()] = s.sel.long()
+    wmax = O.weight_max(W, True)[e_of_slot]
+    zs = []
+    for seed in range(8):
+        noisy, _ = ops.cvmm_fwd(*args, P=P, dst_rows=P, noise_std=0.04, seed=1234 + seed, offset=3)
+        z = ((noisy - clean).cpu() / (0.04 * wmax))
+        want = O.philox_normal(1234 + seed, 3, O.STREAM_OUT_NOISE, P, N)
+        assert float((z - want).abs().max()) < 2e-3   # fp32 cancellation in (noisy-clean) on top of 1e-4
+        zs.append(z)
+    z = torch.stack(zs)
+    assert abs(float(z.mean())) < 0.02
+    assert abs(float(z.std()) - 1.0) < 0.02
+
+
+@pytest.mark.parametrize("per_channel", [True, False])
+def test_weight_prepass(dev, per_channel):
+    from analog_moe import ops
+    E, K, N = 3, 70, 52
+    g = torch.Generator().manual_seed(8)
+    W = torch.randn(E, K, N, generator=g) * 0.1
+    pw = ops.weight_prepass(W.to(dev), 1, per_channel_scale=per_channel, noise_std=0.02, noise_per_channel=per_channel,
+                            seed=77, offset=5, need_w_out=True)
+    assert torch.equal(pw.col_scale.cpu(), O.weight_max(W, per_channel))
+    want = O.modify_weight(W, 0.02, per_channel, 77, 5)
+    assert torch.allclose(pw.w.cpu(), want, atol=2e-6, rtol=0)   # |noise| ~ 1e-2, generator agrees to 1e-4
+    # prepared operand copies: hi+lo reproduces W' to 2^-16 relative; padding is zero
+    npad, kpad, kpad2, npad2 = ops.prepared_dims(K, N)
+    f = (pw.fwd_hi.float() + pw.fwd_lo.float()).cpu()
+    assert f.shape == (E, npad, kpad)
+    assert torch.allclose(f[:, :N, :K], pw.w.cpu().transpose(1, 2), rtol=2 ** -15, atol=1e-9)
+    assert float(f[:, N:, :].abs().max()) == 0 and float(f[:, :, K:].abs().max()) == 0
+    b = (pw.bwd_hi.float() + pw.bwd_lo.float()).cpu()
+    assert b.shape == (E, kpad2, npad2)
+    assert torch.allclose(b[:, :K, :N], pw.w.cpu(), rtol=2 ** -15, atol=1e-9)
+    # discretisation
+    pw2 = ops.weight_prepass(W.to(dev), 2, noise_per_channel=per_channel, discretize_res=0.1, need_w_out=True)
+    assert torch.allclose(pw2.w.cpu(), O.modify_weight(W, 0.0, per_channel, 0, 0, 0.1), atol=1e-7, rtol=0)
+
+
+def test_expert_std(golden_dir, dev):
+    from analog_moe import cvmm_std
+    c = load(golden_dir, "expert_std")
+    k = c["k"]
+    sel, perm = c["sel"].to(dev), c["perm"].to(dev).long()
+    up = cvmm_std(c["x"].to(dev), perm // k, sel, c["E"])
+    dn = cvmm_std(c["xs"].to(dev), perm, sel, c["E"])
+    assert torch.allclose(up.cpu(), c["std_up"], rtol=2e-5, atol=0)   # fp64 accumulation here, fp32 atomics there
+    assert torch.allclose(dn.cpu(), c["std_dn"], rtol=2e-5, atol=0)
+
+
+@pytest.mark.parametrize("prec", ["simt", "split"])
+def test_dw_is_deterministic_and_handles_empty_experts(dev, prec):
+    from analog_moe import ops
+    T, K, N, E, k = 500, 130, 72, 6, 2
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(T, K, generator=g)
+    gr = torch.randn(T * k, N, generator=g)
+    logits = torch.randn(T, E, generator=g)
+    logits[:, 2] = -50.0                                   # expert 2 never selected
+    s = O.select_sort(logits, k)
+    ir = torch.full((T * k,), 1.0)
+    want = O.cvmm_dw(x, s.token_index, s.sel, gr, E, ir, s.slot_index)
+    a = [t.to(dev) for t in (x, s.token_index, gr, s.slot_index, s.expert_offsets)]
+    d1 = ops.cvmm_dw(*a, E, PRECS[prec], P=T * k, ir=ir.to(dev))
+    d2 = ops.cvmm_dw(*a, E, PRECS[prec], P=T * k, ir=ir.to(dev))
+    assert torch.equal(d1, d2)
+    assert float(d1[2].abs().max()) == 0.0
+    scale = float(want.abs().max())
+    assert float((d1.cpu() - want).abs().max()) <= TOL[prec] * scale
+
+
+def test_index_out_of_range_is_reported_not_dereferenced(dev):
+    from analog_moe import ops, _cabi
+    T, K, N, E = 64, 32, 32, 2
+    x = torch.randn(T, K, device=dev)
+    W = torch.randn(E, K, N, device=dev)
+    logits, s = rand_routing(T, E, 1, 1, dev)
+    bad = s.token_index.clone()
+    bad[5] = T + 1000
+    st = ops.new_status(dev)
+    pw = ops.weight_prepass(W, 1)
+    for prec in (2, 1):
+        st.zero_()
+        ops.cvmm_fwd(x, bad.to(dev), s.slot_index.to(dev), s.expert_offsets.to(dev), pw if prec == 1 else
+                     ops.weight_prepass(W, 2), prec, P=T, dst_rows=T, status=st)
+        with pytest.raises(_cabi.AmoeError) as ei:
+            ops.raise_on_device_status(st, "test")
+        assert ei.value.status == 8
+
+
+@pytest.mark.parametrize("prec,dtype", [("split", torch.float32), ("bf16x1", torch.bfloat16)])
+def test_layer_module_vs_oracle(dev, prec, dtype):
+    """AnalogSigmaMoELayer end to end (router, select/sort, both CVMMs with DAC, ADC, backward)."""
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig
+    T, D, F, E, k = 256, 128, 64, 8, 2
+    cfg = TorchInferenceRPUConfig()
+    cfg.forward.inp_res = 254.0
+    cfg.pre_post.input_range.init_value = 3.0
+    cfg.pre_post.input_range.decay = 0.0
+    torch.manual_seed(0)
+    layer = AnalogSigmaMoELayer(cfg, d_model=D, n_experts=E, expert_size=F, k=k, precision=PRECS[prec]).to(dev).to(dtype)
+    x = torch.randn(2, T // 2, D, device=dev, dtype=dtype, requires_grad=True)
+    gy = torch.randn(2, T // 2, D, device=dev, dtype=dtype)
+    layer.eval()
+    y, _ = layer(x)
+    (y.float() * gy.float()).sum().backward()
+    f = lambda t: t.detach().float().cpu()
+    lc = O.LayerConfig(k=k, inp_res=2.0 / 254.0, use_ir=True, ir_params=O.IRParams(decay=0.0))
+    yo, go = O.layer_forward_backward(f(x).view(T, D), f(layer.expert_sel.weight), f(layer.keys), f(layer.values),
+                                      f(layer.input_range), lc, f(gy).view(T, D), acc_dtype=torch.float64)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for name, got, want in [("y", f(y).view(T, D), yo), ("dx", f(x.grad).view(T, D), go["dx"]),
+                            ("dkeys", f(layer.keys.grad), go["dkeys"]), ("dvalues", f(layer.values.grad), go["dvalues"]),
+                            ("d_ir", f(layer.input_range.grad), go["d_input_range"]),
+                            ("dgate_w", f(layer.expert_sel.weight.grad), go["dgate_w"])]:
+        scale = max(1.0, float(want.abs().max()))
+        err = float((got - want).abs().max())
+        assert err <= tol * scale, f"{name}: {err:.3e} vs scale {scale:.3g}"
