@@ -442,10 +442,11 @@ class LayerConfig:
     out_bound: float = -1.0
     seed: int = 0
     ir_params: Optional[IRParams] = None
+    act_dtype: torch.dtype = torch.float32   # storage type of activations between the kernels
 
 
 def layer_forward_backward(x, w_gate, keys, values, input_range, cfg: LayerConfig, grad_y=None,
-                           acc_dtype=torch.float32):
+                           acc_dtype=torch.float32, logits=None):
     """One sigma-MoE analog layer, forward and (if grad_y is given) backward, on the CPU.
 
     Order of operations follows SigmaMoELayer.forward as restated in
@@ -457,8 +458,10 @@ def layer_forward_backward(x, w_gate, keys, values, input_range, cfg: LayerConfi
     T, D = x.shape
     E, _, F = keys.shape
     k = cfg.k
-    logits = x.float() @ w_gate.float().T
+    if logits is None:
+        logits = x.float() @ w_gate.float().T
     s = select_sort(logits, k)
+    rnd = (lambda t: t.to(cfg.act_dtype).float()) if cfg.act_dtype != torch.float32 else (lambda t: t)
     ir_up = input_range[0][s.sel.long()] if cfg.use_ir else None
     ir_dn = input_range[1][s.sel.long()] if cfg.use_ir else None
     am_up = None if cfg.use_ir else x.float().abs().amax(-1)
@@ -482,11 +485,13 @@ def layer_forward_backward(x, w_gate, keys, values, input_range, cfg: LayerConfi
     adc_dn = (cfg.out_res, cfg.out_bound, vmax) if cfg.out_res > 0 else None
     h_pre = cvmm_forward(x, s.token_index, s.sel, Kw, cfg.inp_res, ir_up, s.slot_index, am_up,
                          noise(0, kmax, F), adc_up, acc_dtype)
+    h_pre = rnd(h_pre)
     h = torch.relu(h_pre)
     am_dn = None if cfg.use_ir else h.abs().amax(-1)
     res = cvmm_forward(h, s.slot_index, s.sel, Vw, cfg.inp_res, ir_dn, None, am_dn,
                        noise(1, vmax, D), adc_dn, acc_dtype)
-    y = combine(res, s.gate)
+    res = rnd(res)
+    y = rnd(combine(res, rnd(s.gate)))
     if grad_y is None:
         return y, None
     dh, dV, dir_dn, dgate = cvmm_backward(grad_y, h, s.slot_index, s.sel, Vw, ir_dn, None, s.gate, res,
