@@ -1,6 +1,6 @@
 """Builds libamoe_b200.so from csrc/*.cu with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m analog_moe._build        # from the directory that holds the package
+    python analog-moe_b200/analog_moe/_build.py
 
 The library links the CUDA runtime statically and looks the driver's tensor-map encoder up at
 run time, so it loads on machines without a GPU driver (where only the symbol table is of use).

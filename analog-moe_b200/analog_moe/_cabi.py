@@ -110,7 +110,7 @@ def _load() -> C.CDLL:
     path = os.environ.get("AMOE_LIB", _build.LIB_PATH)
     if not os.path.exists(path):
         raise ImportError(
-            f"{path} not found. Build the CUDA library first: `python -m analog_moe._build` "
+            f"{path} not found. Build the CUDA library first: `python analog-moe_b200/analog_moe/_build.py` "
             "(needs nvcc; there is no CPU or PyTorch fallback).")
     lib = C.CDLL(path)
     for name, (res, args) in SIGNATURES.items():

@@ -24,6 +24,25 @@ from .rpu_config import TorchInferenceRPUConfig, WeightClipType
 from .triton_src.cvmm import CVMM, CVMMExt, CVMMSel, PhiloxNoise, WeightModifier, cvmm_std
 
 
+class _BroadcastInputRange(torch.autograd.Function):
+    """input_range_row[sel] for the expert-sorted slot list (reference
+    moe_layer_aihwkit_lightning.py:447-448).  Backward is the per-expert segment sum of the
+    per-slot gradients done by the library (the slots of an expert are contiguous), instead of
+    autograd's generic sort-and-accumulate indexing backward."""
+
+    @staticmethod
+    def forward(ctx, row: Tensor, sel: Tensor, offsets: Tensor) -> Tensor:
+        ctx.save_for_backward(offsets)
+        ctx.n_experts = row.numel()
+        return row[sel.long()]
+
+    @staticmethod
+    def backward(ctx, grad: Tensor):
+        (offsets,) = ctx.saved_tensors
+        g = grad.reshape(-1).float().contiguous()
+        return ops.ir_grad_reduce(g, offsets, None, ctx.n_experts), None, None
+
+
 def _enum_name(v) -> str:
     return getattr(v, "name", str(v)).split(".")[-1]
 
@@ -87,6 +106,8 @@ class SigmaMoELayer(nn.Module):
     def route(self, inp: Tensor) -> Tuple[CVMMSel, Tensor]:
         """Gate logits -> sigmoid -> top-k -> expert-sorted slot list, one kernel pipeline."""
         logits = self.expert_sel(inp)
+        if getattr(self, "router_bias", None) is not None:      # fixed per-expert logit offset (skew studies)
+            logits = logits + self.router_bias
         bsz, seq, _ = inp.shape
         r = ops.select_sort(logits.detach(), self.n_heads, apply_sigmoid=True)
         raw_sel = r.raw_sel.view(bsz, seq, self.n_heads)
@@ -177,7 +198,10 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
                     cur[ok] = (cur[ok] * idx + ir_p.init_std_alpha * stds[ok].to(cur.dtype)) / (idx + 1)
                     self.input_range_update_idx.data += 1
                 self.input_range.data = self.input_range.data.abs()
-            bir = self.input_range[ir_idx][sel_indices.sel.long()]                  # lightning :447-448
+            if sel_indices.expert_offsets is not None and self.input_range.dtype == torch.float32:
+                bir = _BroadcastInputRange.apply(self.input_range[ir_idx], sel_indices.sel, sel_indices.expert_offsets)
+            else:
+                bir = self.input_range[ir_idx][sel_indices.sel.long()]              # lightning :447-448
         inp_res = cfg.forward.inp_res
         inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1   # lightning :451-456
         noise = None

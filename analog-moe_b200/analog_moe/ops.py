@@ -13,6 +13,61 @@ from . import _cabi as A
 from ._cabi import lib, check, ptr, stream_ptr, dtype_code
 
 
+# kernels launched by one call of each entry point (for the launch counter)
+KERNELS_PER_CALL = {"amoe_select_sort": 4, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
+                    "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 1, "amoe_combine": 1,
+                    "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
+                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1}
+
+
+class Trace:
+    """Counts library launches and, when `timed`, brackets each call with CUDA events on the
+    launching stream (used by the bench for per-kernel durations; adds event overhead)."""
+
+    def __init__(self, timed: bool = False):
+        self.timed = timed
+        self.calls = []          # (name, tag, start_event, end_event)
+        self.launches = 0
+
+    def summary(self):
+        torch.cuda.synchronize()
+        agg = {}
+        for name, tag, e0, e1 in self.calls:
+            key = name if not tag else f"{name}[{tag}]"
+            ms = e0.elapsed_time(e1) if e0 is not None else 0.0
+            a = agg.setdefault(key, [0, 0.0])
+            a[0] += 1
+            a[1] += ms
+        return {k: {"calls": v[0], "ms_total": v[1], "ms_avg": v[1] / v[0]} for k, v in agg.items()}
+
+
+TRACE: Optional[Trace] = None
+_TAG = ""
+
+
+def set_tag(tag: str) -> None:
+    global _TAG
+    _TAG = tag
+
+
+def _call(name: str, *args) -> None:
+    tr = TRACE
+    if tr is None:
+        check(getattr(lib, name)(*args), name)
+        return
+    tr.launches += KERNELS_PER_CALL.get(name, 1)
+    if tr.timed:
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        check(getattr(lib, name)(*args), name)
+        e1.record()
+        tr.calls.append((name, _TAG, e0, e1))
+    else:
+        check(getattr(lib, name)(*args), name)
+        tr.calls.append((name, _TAG, None, None))
+
+
 def i32(t: torch.Tensor) -> torch.Tensor:
     """Index tensors cross the ABI as contiguous int32."""
     t = t.reshape(-1)
@@ -65,16 +120,15 @@ def select_sort(logits: torch.Tensor, k: int, apply_sigmoid: bool = True) -> Rou
     off = torch.empty(E + 1, dtype=torch.int32, device=dev)
     nbytes = lib.amoe_select_sort_workspace_bytes(T, E, k)
     ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=dev)
-    check(lib.amoe_select_sort(ptr(logits), T, E, k, int(apply_sigmoid), ptr(raw_sel), ptr(gate), ptr(sel), ptr(tok),
-                               ptr(slot), ptr(off), ptr(ws), nbytes, stream_ptr()), "amoe_select_sort")
+    _call("amoe_select_sort", ptr(logits), T, E, k, int(apply_sigmoid), ptr(raw_sel), ptr(gate), ptr(sel), ptr(tok),
+                               ptr(slot), ptr(off), ptr(ws), nbytes, stream_ptr())
     return Routing(raw_sel, gate, sel, tok, slot, off)
 
 
 def expert_offsets(sel_sorted: torch.Tensor, n_experts: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     sel_sorted = i32(sel_sorted)
     off = torch.empty(n_experts + 1, dtype=torch.int32, device=sel_sorted.device)
-    check(lib.amoe_expert_offsets(ptr(sel_sorted), sel_sorted.numel(), n_experts, ptr(off), ptr(status), stream_ptr()),
-          "amoe_expert_offsets")
+    _call("amoe_expert_offsets", ptr(sel_sorted), sel_sorted.numel(), n_experts, ptr(off), ptr(status), stream_ptr())
     return off
 
 
@@ -144,14 +198,13 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     nbytes = lib.amoe_weight_prepass_workspace_bytes(E, K, N)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
-    check(lib.amoe_weight_prepass(C.byref(a), stream_ptr()), "amoe_weight_prepass")
+    _call("amoe_weight_prepass", C.byref(a), stream_ptr())
     return out
 
 
 def row_absmax(x2: torch.Tensor) -> torch.Tensor:
     out = torch.empty(x2.shape[0], dtype=torch.float32, device=x2.device)
-    check(lib.amoe_row_absmax(ptr(x2), dtype_code(x2), x2.shape[0], x2.shape[1], x2.stride(0), ptr(out), stream_ptr()),
-          "amoe_row_absmax")
+    _call("amoe_row_absmax", ptr(x2), dtype_code(x2), x2.shape[0], x2.shape[1], x2.stride(0), ptr(out), stream_ptr())
     return out
 
 
@@ -201,7 +254,7 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     a.out_res, a.out_bound = float(out_res), float(out_bound)
     a.out, a.out_dtype, a.out_stride, a.out_codes = ptr(out), dtype_code(out), out.stride(0), ptr(codes)
     a.dev_status = ptr(status)
-    check(lib.amoe_cvmm_fwd(C.byref(a), stream_ptr()), "amoe_cvmm_fwd")
+    _call("amoe_cvmm_fwd", C.byref(a), stream_ptr())
     return out, codes
 
 
@@ -232,7 +285,7 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     a.ir_grad_relative, a.ir_grad_scale = int(relative), float(grad_scale)
     a.keep_count = ptr(keep_count)
     a.dev_status = ptr(status)
-    check(lib.amoe_cvmm_dx(C.byref(a), stream_ptr()), "amoe_cvmm_dx")
+    _call("amoe_cvmm_dx", C.byref(a), stream_ptr())
     return out, ir_grad
 
 
@@ -249,7 +302,7 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
     a.g, a.g_dtype, a.g_stride, a.g_rows, a.g_row = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0], ptr(g_row)
     a.g_div, a.g_scale, a.dw = g_div, ptr(g_scale), ptr(dw)
     a.dev_status = ptr(status)
-    check(lib.amoe_cvmm_dw(C.byref(a), stream_ptr()), "amoe_cvmm_dw")
+    _call("amoe_cvmm_dw", C.byref(a), stream_ptr())
     return dw
 
 
@@ -260,8 +313,8 @@ def combine(res: torch.Tensor, w: Optional[torch.Tensor], T: int, k: int, out_dt
     y = torch.empty(T, N, dtype=out_dtype or res.dtype, device=res.device)
     if w is not None:
         w = w.reshape(-1).float().contiguous()
-    check(lib.amoe_combine(ptr(res), dtype_code(res), res.stride(0), ptr(w), T, k, N, ptr(y), dtype_code(y),
-                           y.stride(0), stream_ptr()), "amoe_combine")
+    _call("amoe_combine", ptr(res), dtype_code(res), res.stride(0), ptr(w), T, k, N, ptr(y), dtype_code(y),
+                           y.stride(0), stream_ptr())
     return y
 
 
@@ -271,8 +324,8 @@ def combine_codes(codes: torch.Tensor, col_scale: torch.Tensor, raw_sel: torch.T
     y = torch.empty(T, N, dtype=out_dtype, device=codes.device)
     if w is not None:
         w = w.reshape(-1).float().contiguous()
-    check(lib.amoe_combine_codes(ptr(codes), ptr(col_scale), ptr(i32(raw_sel)), ptr(row_mult), float(step), ptr(w), T, k,
-                                 N, ptr(y), dtype_code(y), y.stride(0), stream_ptr()), "amoe_combine_codes")
+    _call("amoe_combine_codes", ptr(codes), ptr(col_scale), ptr(i32(raw_sel)), ptr(row_mult), float(step), ptr(w), T, k,
+                                 N, ptr(y), dtype_code(y), y.stride(0), stream_ptr())
     return y
 
 
@@ -280,8 +333,8 @@ def row_dot(res: torch.Tensor, g: torch.Tensor, k: int) -> torch.Tensor:
     res, g = _rows(res), _rows(g)
     P, N = res.shape
     d = torch.empty(P, dtype=torch.float32, device=res.device)
-    check(lib.amoe_row_dot(ptr(res), dtype_code(res), res.stride(0), ptr(g), dtype_code(g), g.stride(0), P, k, N,
-                           ptr(d), stream_ptr()), "amoe_row_dot")
+    _call("amoe_row_dot", ptr(res), dtype_code(res), res.stride(0), ptr(g), dtype_code(g), g.stride(0), P, k, N,
+                           ptr(d), stream_ptr())
     return d
 
 
@@ -289,9 +342,9 @@ def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_rang
                    decay: float = 0.0, min_percentage: float = 0.95, keep_count: Optional[torch.Tensor] = None,
                    total_elements: float = 0.0) -> torch.Tensor:
     out = torch.empty(E, dtype=torch.float32, device=ir_grad_slot.device)
-    check(lib.amoe_ir_grad_reduce(ptr(ir_grad_slot), ptr(offsets), ptr(input_range), E, float(decay),
+    _call("amoe_ir_grad_reduce", ptr(ir_grad_slot), ptr(offsets), ptr(input_range), E, float(decay),
                                   float(min_percentage), ptr(keep_count), float(total_elements), ptr(out),
-                                  stream_ptr()), "amoe_ir_grad_reduce")
+                                  stream_ptr())
     return out
 
 
@@ -301,8 +354,8 @@ def expert_std(x: torch.Tensor, x_row: torch.Tensor, offsets: torch.Tensor, E: i
     out = torch.empty(E, dtype=torch.float32, device=x2.device)
     nbytes = lib.amoe_expert_std_workspace_bytes(E)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
-    check(lib.amoe_expert_std(ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[1], ptr(x_row), ptr(offsets), P, E,
-                              ptr(out), ptr(ws), nbytes, stream_ptr()), "amoe_expert_std")
+    _call("amoe_expert_std", ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[1], ptr(x_row), ptr(offsets), P, E,
+                              ptr(out), ptr(ws), nbytes, stream_ptr())
     return out
 
 
@@ -314,12 +367,12 @@ def ep_pack(x: torch.Tensor, src_row: torch.Tensor, ir: Optional[torch.Tensor] =
     if ir is not None and inp_res > 0:
         codes = torch.empty(P, K, dtype=torch.int8, device=x2.device)
         scale = torch.empty(P, dtype=torch.float32, device=x2.device)
-        check(lib.amoe_ep_pack(ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, ptr(ir), float(inp_res), None,
-                               ptr(codes), ptr(scale), stream_ptr()), "amoe_ep_pack")
+        _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, ptr(ir), float(inp_res), None,
+                               ptr(codes), ptr(scale), stream_ptr())
         return codes, scale
     rows = torch.empty(P, K, dtype=x2.dtype, device=x2.device)
-    check(lib.amoe_ep_pack(ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, None, -1.0, ptr(rows), None, None,
-                           stream_ptr()), "amoe_ep_pack")
+    _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, None, -1.0, ptr(rows), None, None,
+                           stream_ptr())
     return rows, None
 
 
@@ -327,6 +380,5 @@ def ep_unpack(recv: torch.Tensor, dst_row: torch.Tensor, out_rows: int) -> torch
     recv = recv.contiguous()
     P, N = recv.shape
     out = torch.zeros(out_rows, N, dtype=recv.dtype, device=recv.device)
-    check(lib.amoe_ep_unpack(ptr(recv), dtype_code(recv), N, ptr(dst_row), P, ptr(out), out.stride(0), stream_ptr()),
-          "amoe_ep_unpack")
+    _call("amoe_ep_unpack", ptr(recv), dtype_code(recv), N, ptr(dst_row), P, ptr(out), out.stride(0), stream_ptr())
     return out

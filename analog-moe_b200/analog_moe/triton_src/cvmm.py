@@ -103,6 +103,7 @@ class CVMM(torch.autograd.Function):
         if torch.is_autocast_enabled():
             raise RuntimeError("autocast is not supported by the B200 CVMM kernels; pass bf16 or fp32 tensors")
         ext = ext or CVMMExt()
+        ops.set_tag("down" if reduction_weight is not None else "up")
         E, K, N = keys.shape
         if x.shape[-1] != K:
             raise ValueError(f"x has {x.shape[-1]} features, weights expect {K}")     # reference cvmm.py:561
@@ -170,6 +171,7 @@ class CVMM(torch.autograd.Function):
         (x, sel_i, sel_index_i, out_index_i, reduction_weight, ir, res_into_reduction, offsets, w_mod, bwd_hi, bwd_lo,
          col_scale) = ctx.saved_tensors
         E, K, N, precision, ir_params, keys_dtype, ir_shape, check_status = ctx.meta
+        ops.set_tag("down" if reduction_weight is not None else "up")
         dev = x.device
         P = sel_i.numel()
         x2 = x.reshape(-1, K)

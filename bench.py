@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""Benchmark of the analog CVMM hot path: one sigma-MoE analog layer, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c2]
+
+Prints ONE JSON line (rank 0).  `value` is tokens/s over all GPUs with inputs resident in HBM;
+`e2e` is the same step fed from pinned host buffers with the result copied back; `roofline`
+describes the dominant kernel (tensor-core bound) timed with CUDA events in a separate pass;
+`cpu_baseline` is the CPU restatement of the reference's arithmetic timed on this box's cores.
+With --impl reference the CPU restatement is the thing measured (the reference has no CPU path
+of its own for this layer and its GPU path needs packages that are not installed).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "analog-moe_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+# BASELINE.json configs: T tokens per GPU, k, D, F, E, dtype, analog settings
+CONFIGS = {
+    "c1": dict(T=512, k=2, D=256, F=64, E=8, dtype="fp32", out_noise=0.0, w_noise=0.0, adc=True, bwd=True),
+    "c2": dict(T=8192, k=4, D=1024, F=128, E=16, dtype="fp32", out_noise=0.04, w_noise=0.02, adc=True, bwd=True),
+    "c3": dict(T=32768, k=8, D=2048, F=256, E=64, dtype="bf16", out_noise=0.0, w_noise=0.0, adc=True, bwd=False),
+    "c4": dict(T=16384, k=4, D=1024, F=128, E=32, dtype="fp32", out_noise=0.04, w_noise=0.02, adc=True, bwd=True,
+               zipf=1.2),
+    "c5": dict(T=8192, k=6, D=1536, F=192, E=48, dtype="bf16", out_noise=0.02, w_noise=0.01, adc=True, bwd=True,
+               out_res=62.0),
+}
+OUT_BOUND = 12.0     # ADC clip in units of the column weight maximum (aihwkit's default out_bound)
+SEED = 1234
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm=d["hbm_gbs"], tf=d["bf16_tflops"], tf_sustained=d.get("bf16_tflops_sustained"), src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Reads SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag, self.ok = index, [], False, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.max = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.samples.append((nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM),
+                                     nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                                     if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons")
+                                     else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)))
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def result(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max, "reasons": ["unavailable"]}
+        clocks = sorted(s[0] for s in self.samples)
+        bits = 0
+        for _, r in self.samples:
+            bits |= r
+        names = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+                 0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+                 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
+        return {"sm_mhz": clocks[len(clocks) // 2], "sm_max_mhz": self.max,
+                "reasons": [n for b, n in names.items() if bits & b and n != "gpu_idle"], "samples": len(clocks)}
+
+
+def make_inputs(cfg, seed, device, dtype, n_sets):
+    g = torch.Generator().manual_seed(seed)
+    T, D = cfg["T"], cfg["D"]
+    xs = [torch.randn(1, T, D, generator=g).to(dtype) for _ in range(n_sets)]
+    gys = [torch.randn(1, T, D, generator=g).to(dtype) for _ in range(n_sets)]
+    return xs, gys
+
+
+def build_layer(cfg, device, dtype, precision, n_experts_local=None, ep_group=None):
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, WeightModifierType
+    rc = TorchInferenceRPUConfig()
+    rc.forward.inp_res = 254.0
+    rc.forward.out_res = cfg.get("out_res", 254.0) if cfg["adc"] else -1.0
+    rc.forward.out_bound = OUT_BOUND if cfg["adc"] else -1.0
+    rc.forward.out_noise = cfg["out_noise"]
+    rc.forward.out_noise_per_channel = True
+    rc.pre_post.input_range.init_value = 3.0
+    rc.pre_post.input_range.decay = 0.01
+    if cfg["w_noise"] > 0:
+        rc.modifier.type = WeightModifierType.ADD_NORMAL_PER_CHANNEL
+        rc.modifier.std_dev = cfg["w_noise"]
+    torch.manual_seed(0)
+    kw = dict(d_model=cfg["D"], n_experts=cfg["E"], expert_size=cfg["F"], k=cfg["k"], precision=precision,
+              noise_seed=SEED)
+    if ep_group is not None:
+        from analog_moe.ep import ExpertParallelAnalogSigmaMoELayer
+        layer = ExpertParallelAnalogSigmaMoELayer(rc, group=ep_group, **kw)
+    else:
+        layer = AnalogSigmaMoELayer(rc, **kw)
+    layer = layer.to(device).to(dtype)
+    if cfg.get("zipf"):
+        # bias the router so that expert popularity follows Zipf(s): logit offset -s*ln(rank)*c
+        with torch.no_grad():
+            rank = torch.arange(1, cfg["E"] + 1, device=device, dtype=torch.float32)
+            layer.router_bias = (-cfg["zipf"] * torch.log(rank) * 1.6).to(dtype)
+    layer.train(cfg["bwd"])
+    return layer
+
+
+def step(layer, x, gy, bwd):
+    if bwd:
+        x.grad = None
+        for p_ in layer.parameters():
+            p_.grad = None
+        y, _ = layer(x)
+        y.backward(gy)
+        return y
+    with torch.no_grad():
+        y, _ = layer(x)
+    return y
+
+
+def run_ours(args, cfg, rank, world, device):
+    from analog_moe import ops, _cabi
+    dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
+    precision = _cabi.PRECISION_NAMES[args.precision] if args.precision else None
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+        group = dist.group.WORLD
+    layer = build_layer(cfg, device, dtype, precision, ep_group=group)
+    n_sets = 8
+    xs_h, gys_h = make_inputs(cfg, 100 + rank, device, dtype, n_sets)
+    xs_h = [t.pin_memory() for t in xs_h]
+    gys_h = [t.pin_memory() for t in gys_h]
+    xs = [t.to(device).requires_grad_(cfg["bwd"]) for t in xs_h]
+    gys = [t.to(device) for t in gys_h]
+    bwd = cfg["bwd"]
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------- device-resident timing
+    ops.TRACE = None
+    for i in range(args.warmup):
+        step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+    barrier()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    ops.TRACE = ops.Trace(timed=False)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+    e1.record()
+    barrier()
+    sampler.stop_flag = True
+    launches = ops.TRACE.launches
+    ops.TRACE = None
+    ms = e0.elapsed_time(e1)
+    t_dev = torch.tensor([ms], device=device)
+
+    # ---------------- end to end: pinned host inputs in, results out, every step
+    x_d = torch.empty_like(xs[0]).requires_grad_(bwd)
+    gy_d = torch.empty_like(gys[0])
+    y_h = torch.empty(xs_h[0].shape, dtype=dtype).pin_memory()
+    dx_h = torch.empty(xs_h[0].shape, dtype=dtype).pin_memory()
+
+    def e2e_step(i):
+        with torch.no_grad():
+            x_d.copy_(xs_h[i % n_sets], non_blocking=True)
+            if bwd:
+                gy_d.copy_(gys_h[i % n_sets], non_blocking=True)
+        y = step(layer, x_d, gy_d, bwd)
+        y_h.copy_(y.detach(), non_blocking=True)
+        if bwd:
+            dx_h.copy_(x_d.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller holds the results on the host
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    k_e2e = max(3, min(args.steps, 50))
+    e0.record()
+    for i in range(k_e2e):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    t_e2e = torch.tensor([ms_e2e], device=device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t_dev, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t_e2e, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(t_dev), float(t_e2e)
+    elem = 4 if dtype == torch.float32 else 2
+    h2d = cfg["T"] * cfg["D"] * elem * (2 if bwd else 1)
+    d2h = cfg["T"] * cfg["D"] * elem * (2 if bwd else 1)
+
+    # ---------------- per-kernel durations (separate pass, CUDA events around every library call)
+    ops.TRACE = ops.Trace(timed=True)
+    n_prof = max(3, min(args.steps, 20))
+    for i in range(n_prof):
+        step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+    summ = ops.TRACE.summary()
+    ops.TRACE = None
+    return dict(ms=ms, ms_e2e=ms_e2e, k_e2e=k_e2e, launches=launches, h2d=h2d, d2h=d2h, kernels=summ,
+                clocks=sampler.result(), dtype=dtype, precision=layer._precision(xs[0]))
+
+
+def run_cpu(cfg, steps, warmup, sample_tokens=None):
+    """CPU restatement of the reference arithmetic (oracle), all host threads, bounded sample."""
+    from oracle import cvmm_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    T = sample_tokens or cfg["T"]
+    g = torch.Generator().manual_seed(7)
+    D, F, E, k = cfg["D"], cfg["F"], cfg["E"], cfg["k"]
+    x = torch.randn(T, D, generator=g)
+    gy = torch.randn(T, D, generator=g)
+    wg = torch.randn(E, D, generator=g) / D ** 0.5
+    keys = torch.randn(E, D, F, generator=g) / D ** 0.5
+    values = torch.randn(E, F, D, generator=g) / F ** 0.5
+    ir = torch.full((2, E), 3.0)
+    lc = O.LayerConfig(k=k, inp_res=2.0 / 254.0, use_ir=True, out_noise=cfg["out_noise"], w_noise=cfg["w_noise"],
+                       out_res=cfg.get("out_res", 254.0) if cfg["adc"] else -1.0, out_bound=OUT_BOUND, seed=SEED,
+                       ir_params=O.IRParams(decay=0.01))
+    for _ in range(warmup):
+        O.layer_forward_backward(x[:64], wg, keys, values, ir, lc, gy[:64] if cfg["bwd"] else None)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        O.layer_forward_backward(x, wg, keys, values, ir, lc, gy if cfg["bwd"] else None)
+    dt = time.perf_counter() - t0
+    return dict(tokens_per_s=T * steps / dt, cores=cores, seconds=dt, tokens=T, steps=steps)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--precision", default=None, help="split | bf16x1 | fp32 (default: split for fp32, bf16x1 for bf16)")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    mode = "fwd+bwd" if cfg["bwd"] else "fwd"
+    flops_per_token = (12 if cfg["bwd"] else 4) * cfg["k"] * cfg["D"] * cfg["F"]
+    workload = (f"{args.config}: one AnalogSigmaMoELayer {mode}, d_model={cfg['D']} experts={cfg['E']} "
+                f"expert_size={cfg['F']} top-k={cfg['k']} tokens/GPU={cfg['T']} {cfg['dtype']}, 8-bit DAC"
+                f"{', ADC out_res=%g out_bound=%g' % (cfg.get('out_res', 254.0), OUT_BOUND) if cfg['adc'] else ''}"
+                f", out_noise={cfg['out_noise']} weight_noise={cfg['w_noise']} (Philox seed {SEED})")
+    base = dict(metric="analog_cvmm_%s_tokens_per_s" % mode.replace("+", "_"), unit="tokens/s", n_gpus=args.gpus,
+                steps=args.steps, warmup=args.warmup, higher_is_better=True, scaling="weak", vs_baseline=None,
+                data="synthetic", config={"workload": workload, "flops_per_token": flops_per_token})
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        k = max(1, min(args.steps, 3))
+        r = run_cpu(cfg, k, min(args.warmup, 1), args.cpu_sample_tokens)
+        line = dict(base, impl="reference", value=r["tokens_per_s"], steps=k, ms_per_step=1e3 * r["seconds"] / k,
+                    dtype="f32", n_gpus=args.gpus,
+                    cpu_baseline=dict(value=r["tokens_per_s"], unit="tokens/s", cores=r["cores"], kind="port",
+                                      sample=f"{k} full step(s) of {r['tokens']} tokens; CPU restatement of the "
+                                             "reference arithmetic (the reference has no CPU path for this layer)"),
+                    e2e=dict(value=r["tokens_per_s"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                    tflops=r["tokens_per_s"] * flops_per_token / 1e12)
+        print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    r = run_ours(args, cfg, rank, world, device)
+    if rank == 0:
+        pk = peaks()
+        ms_step = r["ms"] / args.steps
+        tokens = cfg["T"] * world
+        value = tokens / (ms_step * 1e-3)
+        e2e_val = tokens / (r["ms_e2e"] / r["k_e2e"] * 1e-3)
+        # dominant kernel: the library call with the largest share of device time
+        gemm_flops = 2.0 * cfg["T"] * cfg["k"] * cfg["D"] * cfg["F"]
+        kern = r["kernels"]
+        total_ms = sum(v["ms_total"] for v in kern.values())
+        top = max(kern, key=lambda n: kern[n]["ms_total"])
+        is_gemm = top.startswith(("amoe_cvmm_fwd", "amoe_cvmm_dx", "amoe_cvmm_dw"))
+        if is_gemm:
+            ach = gemm_flops / (kern[top]["ms_avg"] * 1e-3) / 1e12
+            roof = dict(kernel=top, bound="tensor", achieved=ach, peak=pk["tf"], unit="TFLOP/s", frac=ach / pk["tf"],
+                        traffic=None, peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
+        else:
+            roof = dict(kernel=top, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
+                        peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
+        line = dict(base, value=value, ms_per_step=ms_step, dtype="f32" if cfg["dtype"] == "fp32" else "bf16",
+                    tflops=value * flops_per_token / 1e12, tflops_frac_of_peak=value * flops_per_token / 1e12 / pk["tf"] / world,
+                    e2e=dict(value=e2e_val, unit="tokens/s", h2d_bytes_per_step=r["h2d"], d2h_bytes_per_step=r["d2h"]),
+                    gpu_launches=r["launches"], roofline=roof, clocks=r["clocks"],
+                    kernels={k_: round(v["ms_avg"] * 1e3, 1) for k_, v in sorted(kern.items())})
+        line["config"]["l2"] = "inputs rotate over 8 buffer sets (> 126 MB L2) and one step touches > 400 MB"
+        line["config"]["precision"] = {0: "bf16x1", 1: "split (bf16 hi+lo, fp32 accumulate)", 2: "fp32 CUDA cores"}[r["precision"]]
+        if world == 1 and not args.no_cpu_baseline:
+            c = run_cpu(cfg, 1, 1, args.cpu_sample_tokens)
+            line["cpu_baseline"] = dict(value=c["tokens_per_s"], unit="tokens/s", cores=c["cores"], kind="port",
+                                        sample=f"1 full step of {c['tokens']} tokens ({c['seconds']:.1f} s)")
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
