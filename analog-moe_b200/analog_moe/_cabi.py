@@ -101,6 +101,7 @@ SIGNATURES = {
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp,
                                   C.c_size_t, vp]),
+    "amoe_expert_std_static": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp]),
     "amoe_ep_pack": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, C.c_int64, vp, C.c_float, vp, vp, vp, vp]),
     "amoe_ep_unpack": (C.c_int, [vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, C.c_int64, vp]),
 }

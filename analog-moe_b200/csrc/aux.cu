@@ -1,5 +1,7 @@
 // Reductions around the CVMM (combine over k, gate gradient, input-range gradient, per-expert
 // std) and the expert-parallel pack/unpack helpers.  All HBM-bound streaming kernels.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace amoe {
@@ -188,6 +190,11 @@ __global__ void ep_unpack_kernel(const T* __restrict__ recv, int N, const int32_
   for (int n = lane; n < N; n += 32) row[n] = recv[i * N + n];
 }
 
+// Scratch of amoe_expert_std_static: sum[E], sq[E], mean[E] in double precision for up to
+// kStaticStdMaxExperts experts.  Lives in every CUDA context that loads the library (96 KiB).
+constexpr int kStaticStdMaxExperts = 4096;
+static __device__ __align__(256) double g_std_scratch[3 * kStaticStdMaxExperts];
+
 inline unsigned blocks_for(int64_t threads, int per_block) {
   return static_cast<unsigned>((threads + per_block - 1) / per_block);
 }
@@ -302,6 +309,61 @@ int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, con
   double* sq = sum + E;
   double* mean = sq + E;
   AMOE_CUDA(cudaMemsetAsync(workspace, 0, static_cast<size_t>(E) * 2 * sizeof(double), stream));
+  const unsigned blocks = blocks_for(P * 32, 256);
+  const unsigned eb = blocks_for(E, 128);
+  for (int pass = 0; pass < 2; ++pass) {
+    if (dtype == AMOE_F32)
+      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_row,
+                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq);
+    else
+      std_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
+                                                                x_row, expert_offsets, E, pass, mean,
+                                                                pass == 0 ? sum : sq);
+    AMOE_LAUNCH_CHECK("std_sum");
+    if (pass == 0) {
+      std_mean_kernel<<<eb, 128, 0, stream>>>(sum, expert_offsets, E, K, mean);
+      AMOE_LAUNCH_CHECK("std_mean");
+    }
+  }
+  std_final_kernel<<<eb, 128, 0, stream>>>(sq, expert_offsets, E, K, std_out);
+  AMOE_LAUNCH_CHECK("std_final");
+  return AMOE_OK;
+}
+
+int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+                            const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
+                            amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && x_row && expert_offsets && std_out, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && E > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  if (E > kStaticStdMaxExperts) {
+    set_last_error("amoe_expert_std_static: more experts than the built-in scratch holds (4096)", cudaErrorInvalidValue);
+    return AMOE_ERR_BAD_SHAPE;
+  }
+  AMOE_REQUIRE(dtype == AMOE_F32 || dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
+  // Device address of the scratch array, looked up once per device with that device current.
+  // (In host code `g_std_scratch` is only a handle for the symbol, never a device pointer.)
+  constexpr int kMaxDevices = 64;
+  static double* scratch_of_device[kMaxDevices] = {nullptr};
+  static std::mutex lookup_mutex;
+  int dev = -1;
+  AMOE_CUDA(cudaGetDevice(&dev));
+  AMOE_REQUIRE(dev >= 0 && dev < kMaxDevices, AMOE_ERR_DEVICE);
+  double* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(lookup_mutex);
+    if (scratch_of_device[dev] == nullptr) {
+      void* addr = nullptr;
+      AMOE_CUDA(cudaGetSymbolAddress(&addr, g_std_scratch));
+      scratch_of_device[dev] = static_cast<double*>(addr);
+    }
+    scratch = scratch_of_device[dev];
+  }
+  double* sum = scratch;
+  double* sq = scratch + kStaticStdMaxExperts;
+  double* mean = scratch + 2 * kStaticStdMaxExperts;
+  // the array still holds the previous call's sums: clear the two accumulators
+  AMOE_CUDA(cudaMemsetAsync(scratch, 0, static_cast<size_t>(2) * kStaticStdMaxExperts * sizeof(double), stream));
   const unsigned blocks = blocks_for(P * 32, 256);
   const unsigned eb = blocks_for(E, 128);
   for (int pass = 0; pass < 2; ++pass) {

@@ -242,6 +242,33 @@ int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, con
                     size_t workspace_bytes, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
+ * amoe_expert_std_static: the same statistic as amoe_expert_std for callers that must not
+ * allocate device memory.  (No counterpart in the reference.)
+ *
+ * Who needs it: a host that gave all of the GPU's memory to its own arena at start-up, so that a
+ * later cudaMalloc - its own or a framework allocator's - would fail or would have to take memory
+ * back from a running model; and code on a latency-critical path, where an allocation's implicit
+ * device synchronisation is not acceptable.  Such callers own x, the index arrays and std_out, but
+ * have no spare buffer to lend as a workspace.
+ *
+ * The accumulators live in an array that is part of the library image: 3 * 4096 doubles (96 KiB)
+ * held by every GPU context that loads the library, for as long as it is loaded.  Limits and
+ * rules that follow from that:
+ *   - E <= 4096; a larger E returns AMOE_ERR_BAD_SHAPE and amoe_last_error_string says why;
+ *   - no cudaMalloc/cudaFree and no allocating library routine is called; the call only clears
+ *     the accumulators (the array keeps the previous call's contents) and launches kernels;
+ *   - all calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *     (different streams without an ordering between them, or different host threads) race and
+ *     return garbage.  Calls on one stream are safe back to back;
+ *   - the first call on each device looks the array's device address up (with that device
+ *     current).  Make that first call outside any stream capture.
+ * Arguments and result are those of amoe_expert_std without the workspace pair.
+ * ---------------------------------------------------------------------------------------- */
+int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+                           const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
+                           amoe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------
  * Expert-parallel exchange helpers (no counterpart in the reference, which is single-GPU).
  * amoe_ep_pack gathers the rows of the sorted slot list into a contiguous send buffer in sorted
  * order (so that each destination rank's experts form one contiguous block) and can apply the DAC
