@@ -1,0 +1,75 @@
+"""Expert-parallel layer on 2 GPUs (NCCL) against the single-GPU layer holding all experts."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig
+        from analog_moe.ep import ExpertParallelAnalogSigmaMoELayer
+        D, F, E, k, T = 128, 64, 8, 2, 200 + 17 * rank
+        cfg = TorchInferenceRPUConfig()
+        cfg.forward.out_res, cfg.forward.out_bound = 254.0, 12.0      # DAC + ADC, no noise
+        cfg.pre_post.input_range.decay = 0.0
+        torch.manual_seed(0)
+        dense = AnalogSigmaMoELayer(cfg, d_model=D, n_experts=E, expert_size=F, k=k).to(dev).eval()
+        with torch.no_grad():
+            dense.input_range.copy_(torch.linspace(2.0, 3.5, 2 * E).view(2, E))
+        ep = ExpertParallelAnalogSigmaMoELayer(cfg, group=dist.group.WORLD, d_model=D, n_experts=E, expert_size=F,
+                                               k=k).to(dev).eval()
+        ep.load_global_weights(dense.keys.data, dense.values.data, dense.expert_sel.weight.data, dense.input_range.data)
+        g = torch.Generator().manual_seed(10 + rank)
+        x1 = torch.randn(1, T, D, generator=g).to(dev).requires_grad_()
+        x2 = x1.detach().clone().requires_grad_()
+        gy = torch.randn(1, T, D, generator=g).to(dev)
+        y1, _ = dense(x1)
+        (y1 * gy).sum().backward()
+        y2, _ = ep(x2)
+        (y2 * gy).sum().backward()
+        tol = 1e-4
+        assert float((y1 - y2).abs().max()) <= tol * max(1.0, float(y1.abs().max()))
+        assert float((x1.grad - x2.grad).abs().max()) <= tol * max(1.0, float(x1.grad.abs().max()))
+        # the owner's weight / input-range gradients equal the sum over ranks of the dense layers' gradients
+        El = E // world
+        sl = slice(rank * El, (rank + 1) * El)
+        for name in ("keys", "values"):
+            full = getattr(dense, name).grad.clone()
+            dist.all_reduce(full)
+            got = getattr(ep, name).grad
+            assert float((full[sl] - got).abs().max()) <= tol * max(1.0, float(full.abs().max())), name
+        full = dense.input_range.grad.clone()
+        dist.all_reduce(full)
+        assert float((full[:, sl] - ep.input_range.grad).abs().max()) <= tol * max(1.0, float(full.abs().max()))
+        # router gradient: replicated parameter, compare the all-reduced gradients
+        a, b = dense.expert_sel.weight.grad.clone(), ep.expert_sel.weight.grad.clone()
+        dist.all_reduce(a)
+        dist.all_reduce(b)
+        assert float((a - b).abs().max()) <= tol * max(1.0, float(a.abs().max()))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_matches_dense_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
