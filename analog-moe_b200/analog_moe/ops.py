@@ -140,6 +140,7 @@ class PreparedWeights:
     K: int
     N: int
     col_scale: torch.Tensor                 # [E,N] fp32
+    col_inv_scale: Optional[torch.Tensor] = None   # [E,N] fp32 reciprocals
     w: Optional[torch.Tensor] = None        # [E,K,N] fp32/bf16 for the CUDA-core mode (modified weights)
     fwd_hi: Optional[torch.Tensor] = None
     fwd_lo: Optional[torch.Tensor] = None
@@ -168,8 +169,10 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     a.noise_std, a.noise_per_channel = float(noise_std), int(noise_per_channel)
     a.discretize_res = float(discretize_res)
     a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
+    col_inv = torch.empty(E, N, dtype=torch.float32, device=dev)
     a.col_scale = ptr(col_scale)
-    out = PreparedWeights(E, K, N, col_scale)
+    a.col_inv_scale = ptr(col_inv)
+    out = PreparedWeights(E, K, N, col_scale, col_inv)
     if precision == A.PREC_FP32_SIMT:
         if modified or need_w_out:
             out.w = torch.empty(E, K, N, dtype=torch.float32, device=dev)
@@ -251,6 +254,7 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     a.noise, a.noise_std = ptr(noise), float(noise_std)
     a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
     a.col_scale = ptr(pw.col_scale)
+    a.col_inv_scale = ptr(pw.col_inv_scale)
     a.out_res, a.out_bound = float(out_res), float(out_bound)
     a.out, a.out_dtype, a.out_stride, a.out_codes = ptr(out), dtype_code(out), out.stride(0), ptr(codes)
     a.dev_status = ptr(status)

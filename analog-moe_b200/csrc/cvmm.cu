@@ -5,6 +5,8 @@ using namespace amoe;
 
 namespace {
 
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 int check_common(const amoe_cvmm_args* a) {
   AMOE_REQUIRE(a != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->P > 0 && a->E > 0 && a->K > 0 && a->N > 0, AMOE_ERR_BAD_SHAPE);
@@ -41,7 +43,9 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.is_dx = 0; e.n_out = a->N;
   e.noise = a->noise; e.noise_std = a->noise_std; e.seed = a->seed; e.offset = a->offset;
   e.col_scale = a->col_scale;
+  e.col_inv_scale = a->col_inv_scale;
   e.adc = make_adc(a->out_res, a->out_bound);
+  AMOE_REQUIRE(!e.adc.on || a->col_inv_scale != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(!(e.adc.on || a->noise_std > 0.f) || a->col_scale != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(!a->out_codes || e.adc.on, AMOE_ERR_UNSUPPORTED);
   if (e.adc.on) {
@@ -54,6 +58,8 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.acc_mul = 1.f;
   e.out = a->out; e.out_dtype = a->out_dtype; e.out_stride = a->out_stride; e.out_codes = a->out_codes;
   e.status = a->dev_status;
+  e.vec4 = (a->N % 4 == 0) && al16(a->col_scale) && al16(a->col_inv_scale) && al16(a->noise) && al16(a->out) &&
+           (a->out_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(a->out_codes) & 3u) == 0);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, false, e, stream);
   return launch_cvmm_tc(a, false, e, stream);
 }
@@ -78,6 +84,8 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.row_scale = a->row_scale; e.ir_grad = a->ir_grad; e.relative = a->ir_grad_relative;
   e.grad_scale = a->ir_grad_scale; e.keep_count = a->keep_count;
   e.status = a->dev_status;
+  e.vec4 = (a->K % 4 == 0) && al16(a->out) && (a->out_stride % 4 == 0) &&
+           (!a->x_ref || (al16(a->x_ref) && a->x_ref_stride % 4 == 0));
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, true, e, stream);
   return launch_cvmm_tc(a, true, e, stream);
 }

@@ -1,7 +1,8 @@
 // Row-owner epilogue shared by the CUDA-core and the tcgen05 CVMM kernels.
 //
-// One thread owns one output row (one sorted position) and walks its columns four at a time, so
-// that every per-row reduction (the input-range gradient) is a thread-local, order-fixed sum.
+// One thread owns one output row (one sorted position) - or, in the tcgen05 kernel, an interleaved
+// share of that row's 16-column chunks - and walks its columns four at a time, so that every
+// per-row reduction (the input-range gradient) is a fixed-order sum.
 #pragma once
 #include "common.cuh"
 
@@ -10,9 +11,11 @@ namespace amoe {
 struct EpiParams {
   int is_dx;            // 0: forward epilogue, 1: input-gradient epilogue
   int n_out;            // output columns
+  int vec4;             // n_out % 4 == 0 and every per-column / per-row array is 16-byte aligned
   // forward
   const float* noise; float noise_std; uint64_t seed; uint32_t offset;
-  const float* col_scale;  // [E, n_out]
+  const float* col_scale;      // [E, n_out]
+  const float* col_inv_scale;  // [E, n_out], needed by the ADC
   AdcParams adc;
   const float* a_absmax; const float* ir;  // by source row / by sorted position
   const int32_t* a_row; const int32_t* dst_row; int a_div;
@@ -30,7 +33,7 @@ struct RowCtx {
   int valid;       // row takes part (inside the expert's run and all indices in range)
   int e;
   int64_t dst;
-  float ir, post;  // input range of the row, and absmax*... multiplier applied last
+  float ir;
   float absmax;
   float rs;
   int64_t xrow;
@@ -42,7 +45,7 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   RowCtx c;
   c.valid = in_range;
   c.e = e;
-  c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0; c.post = 1.f;
+  c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0;
   if (!in_range) return c;
   c.dst = p.dst_row[i];
   if (c.dst < 0 || c.dst >= p.dst_rows) {
@@ -69,67 +72,101 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   return c;
 }
 
+__device__ __forceinline__ void load4(const float* base, int64_t idx, int n0, int n_out, bool vec, float o[4], float fill) {
+  if (vec) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(base + idx));
+    o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = (n0 + j < n_out) ? base[idx + j] : fill;
+  }
+}
+
 // Four consecutive columns n0..n0+3 (n0 % 4 == 0) of the row; v = raw accumulators.
-__device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, float v[4]) {
+__device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, const float v[4]) {
   if (!c.valid || n0 >= p.n_out) return;
+  const bool vec = p.vec4 != 0;      // implies n0 + 3 < n_out
   float o[4];
   float code[4] = {0.f, 0.f, 0.f, 0.f};
   if (!p.is_dx) {
-    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    const int64_t cidx = static_cast<int64_t>(c.e) * p.n_out + n0;
+    float s[4] = {1.f, 1.f, 1.f, 1.f}, is[4] = {1.f, 1.f, 1.f, 1.f}, nz[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.col_scale) load4(p.col_scale, cidx, n0, p.n_out, vec, s, 1.f);
+    if (p.adc.on) load4(p.col_inv_scale, cidx, n0, p.n_out, vec, is, 0.f);
+    if (p.noise) load4(p.noise, c.dst * p.n_out + n0, n0, p.n_out, vec, nz, 0.f);
     if (p.noise_std > 0.f) {
-      float4 zz = philox_normal4(p.seed, p.offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
-                                 static_cast<uint32_t>(n0 >> 2));
-      z[0] = zz.x; z[1] = zz.y; z[2] = zz.z; z[3] = zz.w;
+      const float4 zz = philox_normal4(p.seed, p.offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
+                                       static_cast<uint32_t>(n0 >> 2));
+      nz[0] += (p.noise_std * s[0]) * zz.x;
+      nz[1] += (p.noise_std * s[1]) * zz.y;
+      nz[2] += (p.noise_std * s[2]) * zz.z;
+      nz[3] += (p.noise_std * s[3]) * zz.w;
     }
+    const float post = c.absmax * c.ir;   // both 1 when absent; only one of the two is used in practice
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int n = n0 + j;
-      if (n < p.n_out) {
-        float acc = v[j] * p.acc_mul;
-        float s = (p.col_scale != nullptr) ? p.col_scale[static_cast<int64_t>(c.e) * p.n_out + n] : 1.f;
-        if (p.noise) acc += p.noise[c.dst * p.n_out + n];
-        if (p.noise_std > 0.f) acc += (p.noise_std * s) * z[j];
-        if (p.adc.on) acc = (s > 0.f) ? adc_apply(acc, s, p.adc, code[j]) : 0.f;
-        if (p.a_absmax) acc *= c.absmax;
-        if (p.ir) acc *= c.ir;
-        o[j] = acc;
-      }
+      float acc = v[j] * p.acc_mul + nz[j];
+      if (p.adc.on) acc = adc_apply(acc, s[j], is[j], p.adc, code[j]);
+      if (p.a_absmax && p.ir) acc = (acc * c.absmax) * c.ir;
+      else acc *= post;
+      o[j] = acc;
     }
   } else {
+    float xr[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.x_ref) {
+      const int64_t xi = c.xrow * p.x_ref_stride + n0;
+      if (vec && p.x_ref_dtype == AMOE_F32) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + xi));
+        xr[0] = t.x; xr[1] = t.y; xr[2] = t.z; xr[3] = t.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n0 + j < p.n_out) xr[j] = load_elem(p.x_ref, p.x_ref_dtype, xi + j);
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int n = n0 + j;
-      if (n < p.n_out) {
-        float g = v[j];
-        float gs = g * c.rs;
-        if (p.x_ref) {
-          float xr = load_elem(p.x_ref, p.x_ref_dtype, c.xrow * p.x_ref_stride + n);
-          bool up = xr >= c.ir, low = xr <= -c.ir, keep = fabsf(xr) < c.ir;
-          if (up) c.dir_acc += fminf(gs, 0.f);
-          if (low) c.dir_acc -= fmaxf(gs, 0.f);
-          c.keep += keep ? 1u : 0u;
-          gs = keep ? gs : 0.f;
-        }
-        o[j] = gs;
+      float gs = v[j] * c.rs;
+      if (p.x_ref && n0 + j < p.n_out) {
+        const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
+        if (up) c.dir_acc += fminf(gs, 0.f);
+        if (low) c.dir_acc -= fmaxf(gs, 0.f);
+        c.keep += keep ? 1u : 0u;
+        gs = keep ? gs : 0.f;
       }
+      o[j] = gs;
     }
   }
   const int64_t base = c.dst * p.out_stride + n0;
-  if (n0 + 3 < p.n_out && p.out_dtype == AMOE_F32 && ((base & 3) == 0)) {
+  if (vec && p.out_dtype == AMOE_F32) {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = make_float4(o[0], o[1], o[2], o[3]);
+  } else if (vec) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) = pk;
   } else {
 #pragma unroll
     for (int j = 0; j < 4; ++j)
       if (n0 + j < p.n_out) store_elem(p.out, p.out_dtype, base + j, o[j]);
   }
   if (p.out_codes) {
+    if (vec) {
+      const uint32_t pk = (static_cast<uint32_t>(static_cast<int>(code[0])) & 0xffu) |
+                          ((static_cast<uint32_t>(static_cast<int>(code[1])) & 0xffu) << 8) |
+                          ((static_cast<uint32_t>(static_cast<int>(code[2])) & 0xffu) << 16) |
+                          ((static_cast<uint32_t>(static_cast<int>(code[3])) & 0xffu) << 24);
+      *reinterpret_cast<uint32_t*>(p.out_codes + c.dst * p.n_out + n0) = pk;
+    } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (n0 + j < p.n_out) p.out_codes[c.dst * p.n_out + n0 + j] = static_cast<int8_t>(code[j]);
+      for (int j = 0; j < 4; ++j)
+        if (n0 + j < p.n_out) p.out_codes[c.dst * p.n_out + n0 + j] = static_cast<int8_t>(code[j]);
+    }
   }
 }
 
-// After the last column: per-row results of the input-gradient epilogue.
+// After the last column: per-row results of the input-gradient epilogue (dir_acc already complete).
 __device__ __forceinline__ void epi_row_end(const EpiParams& p, RowCtx& c, int64_t i) {
   if (!p.is_dx || !c.valid) return;
   if (p.ir_grad) {

@@ -30,10 +30,16 @@ using namespace tc;
 
 constexpr int kBM = 128;          // rows per tile (UMMA M)
 constexpr int kBK = 64;           // bf16 elements per stage along the contraction (128 bytes)
+// dW kernel geometry: 2 control warps, 4 epilogue warps, 8 prologue warps
 constexpr int kProdWarps = 8;
 constexpr int kEpiWarp0 = 2;
 constexpr int kProdWarp0 = 6;
 constexpr int kThreads = (kProdWarp0 + kProdWarps) * 32;  // 448
+// forward / dX kernel geometry: 2 control warps + 16 worker warps whose split between epilogue and
+// prologue is chosen per launch (4, 8 or 12 epilogue warps)
+constexpr int kWorkerWarps = 16;
+constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 576
+constexpr int kMaxEpiGroups = 3;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATile = kBM * kBK * 2;  // 16 KiB
 
@@ -43,7 +49,9 @@ __device__ __forceinline__ uint32_t bar_full_b(uint32_t bars, int s) { return ba
 __device__ __forceinline__ uint32_t bar_empty(uint32_t bars, int s) { return bars + 8u * (2 * kMaxStages + s); }
 __device__ __forceinline__ uint32_t bar_tfull(uint32_t bars, int b) { return bars + 8u * (3 * kMaxStages + b); }
 __device__ __forceinline__ uint32_t bar_tempty(uint32_t bars, int b) { return bars + 8u * (3 * kMaxStages + 2 + b); }
-constexpr int kNumBars = 3 * kMaxStages + 4;
+// warp-group rendezvous points (bounded, unlike bar.sync): prologue warps x2, epilogue warps x2
+__device__ __forceinline__ uint32_t bar_group(uint32_t bars, int i) { return bars + 8u * (3 * kMaxStages + 4 + i); }
+constexpr int kNumBars = 3 * kMaxStages + 8;
 
 struct TileIter {
   const int32_t* off; int E; int e; int64_t before;
@@ -67,6 +75,7 @@ struct TileIter {
 
 struct TcParams {
   int E, Kc, Nout;
+  int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
   int BN, n_tiles, k_chunks, stages;
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
   const int32_t* offsets;
@@ -134,7 +143,8 @@ __device__ __forceinline__ SmemView carve_smem(uint8_t* raw, uint32_t ring_bytes
   return s;
 }
 
-__device__ __forceinline__ void setup_cta(const SmemView& s, int stages, uint32_t tmem_cols, int full_a_count) {
+__device__ __forceinline__ void setup_cta(const SmemView& s, int stages, uint32_t tmem_cols, int full_a_count,
+                                          int tempty_count = 4, int prod_warps = 1, int epi_warps = 1) {
   const int warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
     for (int i = 0; i < stages; ++i) {
@@ -144,8 +154,12 @@ __device__ __forceinline__ void setup_cta(const SmemView& s, int stages, uint32_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull(s.bars, b), 1);
-      mbar_init(bar_tempty(s.bars, b), 4);
+      mbar_init(bar_tempty(s.bars, b), tempty_count);
     }
+    mbar_init(bar_group(s.bars, 0), prod_warps);
+    mbar_init(bar_group(s.bars, 1), prod_warps);
+    mbar_init(bar_group(s.bars, 2), epi_warps);
+    mbar_init(bar_group(s.bars, 3), epi_warps);
     *s.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -172,13 +186,34 @@ __device__ __forceinline__ void teardown_cta(const SmemView& s, uint32_t tmem_ba
 }
 
 // ============================================================================ forward / dX
+// Rendezvous of a group of warps on an mbarrier whose arrival count is the number of warps.
+// `round` counts the uses of this barrier by the calling warp.  Returns false if the wait gave up.
+__device__ __forceinline__ bool group_sync(uint32_t bar, uint32_t round, volatile int* abort_flag, int32_t* status,
+                                           int where) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+  bool ok = mbar_wait(bar, round & 1u, abort_flag, status, where);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// Per-row operand-prologue parameters, staged in shared memory once per tile.
+struct __align__(16) RowMeta {
+  long long src_off;   // element offset of the source row, or -1 if the row is not to be read
+  float ir, am, fast;
+  float pad;
+};
+
 template <bool A_SPLIT, bool B_SPLIT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
+  __shared__ RowMeta s_meta[kBM];
+  __shared__ float s_dir[kMaxEpiGroups][kBM];
+  __shared__ unsigned s_keep[kMaxEpiGroups][kBM];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  setup_cta(sm, p.stages, p.tmem_cols, kProdWarps);
+  const int n_prod = kWorkerWarps - p.n_epi;
+  setup_cta(sm, p.stages, p.tmem_cols, n_prod, p.n_epi, n_prod, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
 
@@ -246,13 +281,20 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         }
       }
     }
-  } else if (warp < kProdWarp0) {
+  } else if (warp < 2 + p.n_epi) {
     // ---------------------------------------------------------------- epilogue
+    // TMEM lane quadrant = warp % 4; the warps of one quadrant ("groups") interleave the 16-column chunks.
+    const int ew = warp - 2;
     const int q = warp & 3;
+    const int grp = ew >> 2;
+    const int groups = p.n_epi >> 2;
+    const int epi_threads = p.n_epi * 32;
     const int r = q * 32 + lane;
+    const int chunks = p.BN / 16;
     TileIter ti(p.offsets, p.E);
-    uint32_t acc_it = 0;
+    uint32_t acc_it = 0, sync_round = 0;
     bool alive = true;
+    (void)epi_threads;
     for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
       int e, row0, rows;
       if (!ti.get(t, e, row0, rows)) break;
@@ -266,62 +308,78 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         if (!ok) { alive = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
-        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        for (int ch = grp; ch < chunks; ch += groups) {
           float v[16];
-          tmem_ld16(taddr + c0, v);
+          tmem_ld16(taddr + ch * 16, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int qd = 0; qd < 4; ++qd) epi_quad(p.epi, ctx, nt * p.BN + c0 + 4 * qd, &v[4 * qd]);
+          for (int qd = 0; qd < 4; ++qd) epi_quad(p.epi, ctx, nt * p.BN + ch * 16 + 4 * qd, &v[4 * qd]);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
       }
-      if (alive) {
-        epi_row_end(p.epi, ctx, i);
-        if (p.epi.is_dx && p.epi.keep_count) {
-          unsigned kc = ctx.valid ? ctx.keep : 0u;
+      if (!alive) break;
+      if (p.epi.is_dx && (p.epi.ir_grad || p.epi.keep_count)) {
+        // fixed-order combination of the groups' partial row sums
+        if (groups > 1) {
+          s_dir[grp][r] = ctx.dir_acc;
+          s_keep[grp][r] = ctx.valid ? ctx.keep : 0u;
+          if (!group_sync(bar_group(sm.bars, 2), sync_round, sm.abort_flag, status, 7)) { alive = false; break; }
+          if (grp == 0) {
+            float d = s_dir[0][r];
+            unsigned kc = s_keep[0][r];
+            for (int g = 1; g < groups; ++g) { d += s_dir[g][r]; kc += s_keep[g][r]; }
+            ctx.dir_acc = d;
+            ctx.keep = kc;
+          }
+          if (!group_sync(bar_group(sm.bars, 3), sync_round, sm.abort_flag, status, 8)) { alive = false; break; }
+          ++sync_round;
+        }
+        if (grp == 0) {
+          epi_row_end(p.epi, ctx, i);
+          if (p.epi.keep_count) {
+            unsigned kc = ctx.valid ? ctx.keep : 0u;
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) kc += __shfl_xor_sync(0xffffffffu, kc, o);
-          if (lane == 0 && kc) atomicAdd(p.epi.keep_count, static_cast<unsigned long long>(kc));
+            for (int o = 16; o > 0; o >>= 1) kc += __shfl_xor_sync(0xffffffffu, kc, o);
+            if (lane == 0 && kc) atomicAdd(p.epi.keep_count, static_cast<unsigned long long>(kc));
+          }
         }
       }
     }
   } else {
     // ---------------------------------------------------------------- operand prologue (A tiles)
-    const int pt = threadIdx.x - kProdWarp0 * 32;  // 0..255
-    const int c = pt & 7;                          // 16-byte chunk inside the 128-byte row
-    const int rbase = pt >> 3;                     // rows rbase, rbase+32, rbase+64, rbase+96
+    const int np = n_prod * 32;
+    const int pt = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np-1
     const bool has_ir = p.dac && p.ir != nullptr, has_am = p.dac && p.a_absmax != nullptr;
     const bool quant = p.dac && p.inp_res > 0.f;
     TileIter ti(p.offsets, p.E);
-    uint32_t it = 0;
+    uint32_t it = 0, sync_round = 0;
     bool alive = true;
     for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
       int e, row0, rows;
       if (!ti.get(t, e, row0, rows)) break;
-      int64_t src_off[4];
-      float r_ir[4], r_am[4], r_fast[4];
-      bool r_ok[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = rbase + 32 * j;
-        r_ok[j] = r < rows;
-        src_off[j] = 0; r_ir[j] = 1.f; r_am[j] = 1.f; r_fast[j] = 1.f;
-        if (r_ok[j]) {
+      // everyone is done with the previous tile's metadata
+      if (!group_sync(bar_group(sm.bars, 0), sync_round, sm.abort_flag, status, 9)) break;
+      for (int r = pt; r < kBM; r += np) {
+        RowMeta m;
+        m.src_off = -1; m.ir = 1.f; m.am = 1.f; m.fast = 1.f; m.pad = 0.f;
+        if (r < rows) {
           const int64_t i = static_cast<int64_t>(row0) + r;
           const int64_t src = p.a_row[i] / p.a_div;
           if (src < 0 || src >= p.a_rows) {
             report(status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(i), static_cast<int>(src));
-            r_ok[j] = false;
           } else {
-            src_off[j] = src * p.a_stride;
-            if (has_ir) r_ir[j] = p.ir[i];
-            if (has_am) r_am[j] = p.a_absmax[src];
-            if (quant) r_fast[j] = dac_fast_mul(has_ir, r_ir[j], has_am, r_am[j], p.inp_res);
+            m.src_off = src * p.a_stride;
+            if (has_ir) m.ir = p.ir[i];
+            if (has_am) m.am = p.a_absmax[src];
+            if (quant) m.fast = dac_fast_mul(has_ir, m.ir, has_am, m.am, p.inp_res);
           }
         }
+        s_meta[r] = m;
       }
+      if (!group_sync(bar_group(sm.bars, 1), sync_round, sm.abort_flag, status, 10)) break;
+      ++sync_round;
       for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
           const int s = it % p.stages;
@@ -331,26 +389,40 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           if (!ok) { alive = false; break; }
           uint8_t* a_hi = sm.base + s * p.stage_bytes;
           uint8_t* a_lo = a_hi + kATile;
-          const int k = kc * kBK + c * 8;
+          // 1024 tasks (128 rows x 8 sixteen-byte chunks), four per thread and round
+          for (int base = pt; base < kBM * 8; base += np * 4) {
+            float v[4][8];
+            RowMeta m[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float v[8];
-            if (r_ok[j] && k < p.Kc) {
-              load8(p.a, p.a_dtype, src_off[j], k, p.Kc, p.vec_ok != 0, v);
-              if (p.dac) {
+            for (int b = 0; b < 4; ++b) {
+              const int task = base + b * np;
+              const int r = task >> 3, c = task & 7;
+              if (task < kBM * 8) m[b] = s_meta[r]; else m[b].src_off = -1;
+              const int k = kc * kBK + c * 8;
+              if (m[b].src_off >= 0 && k < p.Kc) {
+                load8(p.a, p.a_dtype, m[b].src_off, k, p.Kc, p.vec_ok != 0, v[b]);
+              } else {
 #pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                  if (quant)
-                    v[x] = dac_code(v[x], has_ir, r_ir[j], has_am, r_am[j], p.inp_res, r_fast[j]);
-                  else
-                    v[x] = dac_normalise(v[x], has_ir, r_ir[j], has_am, r_am[j]);
-                }
+                for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
               }
-            } else {
-#pragma unroll
-              for (int x = 0; x < 8; ++x) v[x] = 0.f;
             }
-            store8<A_SPLIT>(a_hi, a_lo, sw128_offset(rbase + 32 * j, c), v);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const int task = base + b * np;
+              if (task < kBM * 8) {
+                const int r = task >> 3, c = task & 7;
+                if (p.dac && m[b].src_off >= 0) {
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) {
+                    if (quant)
+                      v[b][x] = dac_code(v[b][x], has_ir, m[b].ir, has_am, m[b].am, p.inp_res, m[b].fast);
+                    else
+                      v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, has_am, m[b].am);
+                  }
+                }
+                store8<A_SPLIT>(a_hi, a_lo, sw128_offset(r, c), v[b]);
+              }
+            }
           }
           fence_proxy_async();
           __syncwarp();
@@ -572,7 +644,7 @@ uint32_t pow2_cols(int need) {
   return c;
 }
 
-constexpr uint32_t kSmemBudget = 200 * 1024;  // ring budget; barriers and alignment slack come on top
+constexpr uint32_t kSmemBudget = 192 * 1024;  // ring budget; barriers and alignment slack come on top
 constexpr uint32_t kSmemExtra = 1024 + 8 * kNumBars + 64;
 
 }  // namespace
@@ -649,6 +721,21 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
+  {
+    // Split the 16 worker warps between epilogue and prologue by estimated instruction counts.
+    const double per_prod = (quant ? 13.0 : (p.dac ? 30.0 : 4.0)) + (a_split ? 6.0 : 2.0);
+    double per_epi = 10.0;
+    if (!is_dx) per_epi += (a->noise_std > 0.f ? 26.0 : 0.0) + (a->noise ? 2.0 : 0.0) + (p.epi.adc.on ? 9.0 : 0.0) +
+                           (a->out_codes ? 3.0 : 0.0);
+    else per_epi += a->x_ref ? 12.0 : 0.0;
+    const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
+    const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
+    double best = 1e300;
+    for (int ne = 4; ne <= 12; ne += 4) {
+      const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
+      if (t < best) { best = t; p.n_epi = ne; }
+    }
+  }
 
   CUtensorMap m_hi, m_lo;
   s = encode_tmap_bf16_3d(&m_hi, a->w_hi, static_cast<uint64_t>(k_pad), static_cast<uint64_t>(n_pad),
@@ -666,7 +753,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
 #define AMOE_LAUNCH_TC(AS, BS)                                                                                  \
   do {                                                                                                          \
     AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    cvmm_tc_kernel<AS, BS><<<grid, kThreads, smem, stream>>>(m_hi, m_lo, p);                                    \
+    cvmm_tc_kernel<AS, BS><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, p);                                 \
   } while (0)
   if (a_split && b_split) AMOE_LAUNCH_TC(true, true);
   else if (a_split) AMOE_LAUNCH_TC(true, false);

@@ -42,10 +42,12 @@ __global__ void expmax_kernel(const float* __restrict__ colmax, int N, float* __
 }
 
 __global__ void fill_scale_kernel(const float* __restrict__ colmax, const float* __restrict__ expmax, int E, int N,
-                                  int per_channel, float* __restrict__ out) {
+                                  int per_channel, float* __restrict__ out, float* __restrict__ inv) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= static_cast<int64_t>(E) * N) return;
-  out[i] = per_channel ? colmax[i] : expmax[i / N];
+  const float s = per_channel ? colmax[i] : expmax[i / N];
+  if (out) out[i] = s;
+  if (inv) inv[i] = s > 0.f ? __frcp_rn(s) : 0.f;
 }
 
 struct PrepassDev {
@@ -184,10 +186,11 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
   AMOE_LAUNCH_CHECK("colmax");
   expmax_kernel<<<a->E, 256, 0, stream>>>(colmax, a->N, expmax);
   AMOE_LAUNCH_CHECK("expmax");
-  if (a->col_scale) {
+  if (a->col_scale || a->col_inv_scale) {
     const int64_t n = static_cast<int64_t>(a->E) * a->N;
     fill_scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(colmax, expmax, a->E, a->N,
-                                                                                  a->per_channel_scale, a->col_scale);
+                                                                                  a->per_channel_scale, a->col_scale,
+                                                                                  a->col_inv_scale);
     AMOE_LAUNCH_CHECK("fill_scale");
   }
   if (a->w_out || a->fwd_hi || a->bwd_hi) {

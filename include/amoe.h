@@ -104,6 +104,7 @@ typedef struct amoe_weight_prepass_args {
   float discretize_res;           /* <=0: off; else n_states = max(res, 1/res) */
   uint64_t seed; uint32_t offset;
   float* col_scale;               /* [E,N] */
+  float* col_inv_scale;           /* [E,N] correctly rounded 1/col_scale (0 where col_scale is 0), or NULL */
   float* w_out;                   /* [E,K,N] fp32 or NULL */
   void* fwd_hi; void* fwd_lo;     /* bf16 [E,Npad,Kpad] or NULL */
   void* bwd_hi; void* bwd_lo;     /* bf16 [E,Kpad2,Npad2] or NULL */
@@ -127,7 +128,7 @@ int amoe_row_absmax(const void* x, int32_t dtype, int64_t R, int32_t K, int64_t 
  *     a   = A[r,:]; clamp to +-ir[i]; /ir[i]; /a_absmax[r]; round(a/inp_res)  (integer DAC code)
  *     acc = inp_res * sum_k code_k W'[e,k,:]             (fp32 accumulate)
  *     acc += noise[c,:]  |  noise_std*col_scale[e,:]*z(c,:)            (Philox, seed/offset)
- *     ADC: q = rint(clamp(acc/col_scale[e,:], +-out_bound) / step), acc = q*step*col_scale[e,:]
+ *     ADC: q = rint(clamp(acc*(1/col_scale[e,:]), +-out_bound) * (1/step)), acc = q*step*col_scale[e,:]
  *     out[c,:] = acc * a_absmax[r] * ir[i];  out_codes[c,:] = q
  *
  * amoe_cvmm_dx replaces the second cvmm_triton_quantized call of CVMM.backward and the torch code
@@ -164,6 +165,7 @@ typedef struct amoe_cvmm_args {
   float noise_std;                /* >0: Philox noise noise_std*col_scale[e,n]*z */
   uint64_t seed; uint32_t offset;
   const float* col_scale;         /* [E,N] (needed for Philox noise and ADC) */
+  const float* col_inv_scale;     /* [E,N] from the weight pre-pass (needed for the ADC) */
   /* ADC */
   float out_res, out_bound;       /* out_res<=0: off */
   /* outputs */

@@ -192,16 +192,21 @@ def adc_codes(acc: torch.Tensor, s_col: torch.Tensor, out_res: float, out_bound:
     it off at moe_layer_aihwkit_lightning.py:152-157).
 
     `acc` [M,N] is the accumulator (+noise) in normalised-input units, `s_col`
-    [M,N] or [M,1] the weight maximum that normalises the column.  v = acc/s is
-    clamped to +-out_bound and rounded half-to-even to a multiple of
-    step = 2*out_bound*res.  Returns (codes, dequantised acc = codes*step*s).
+    [M,N] or [M,1] the weight maximum that normalises the column.  All in fp32:
+    v = acc * (1/s) clamped to +-out_bound; code = round-half-even(v * (1/step)),
+    step = 2*out_bound*res; both reciprocals are correctly rounded fp32 values
+    (1/s := 0 for an all-zero column).  Returns (codes, codes*step*s).
     """
+    one = torch.tensor(1.0, dtype=torch.float32)
     step = torch.tensor(adc_step(out_res, out_bound), dtype=torch.float32)
+    inv_step = one / step
     ob = torch.tensor(out_bound, dtype=torch.float32)
-    v = acc.float() / s_col.float()
+    s = s_col.float()
+    inv_s = torch.where(s > 0, one / torch.where(s > 0, s, one), torch.zeros_like(s))
+    v = acc.float() * inv_s
     v = torch.minimum(torch.maximum(v, -ob), ob)
-    q = torch.round(v / step)
-    return q, (q * step) * s_col.float()
+    q = torch.round(v * inv_step)
+    return q, (q * step) * s
 
 
 # --------------------------------------------------------------------------- #

@@ -225,7 +225,7 @@ def test_adc_codes(dev, prec):
     acc = O.cvmm_forward(x, s.token_index, s.sel, W, res, None if False else ir, s.slot_index) / 2.5
     e_of_slot = torch.empty(T * k, dtype=torch.long)
     e_of_slot[s.slot_index.long()] = s.sel.long()
-    v = acc / wmax[e_of_slot] / O.adc_step(254.0, 12.0)
+    v = acc * (1.0 / wmax[e_of_slot]) * (1.0 / O.adc_step(254.0, 12.0))
     near_tie = ((v - torch.floor(v)) - 0.5).abs() < 1e-3
     diff = (codes - codes_w).abs()
     assert int((diff[~near_tie] != 0).sum()) == 0
