@@ -638,6 +638,212 @@ __global__ void __launch_bounds__(kThreads, 1) dw_tc_kernel(DwParams p) {
   teardown_cta(sm, tmem_base, p.tmem_cols);
 }
 
+// ---------------------------------------------------------------------------- dW, MN-major operands
+// The contraction index of dW is the slot, which is the slow index of both row-major inputs.  The
+// tensor core takes such operands directly ("MN-major"): a stage holds 64 slots as 64 rows of 128 bytes
+// per block of 64 columns, so the prologue converts and stores 16-byte chunks without transposing.
+struct DwMnParams {
+  int E, K, N;
+  int BN, m_tiles, n_tiles, stages;
+  uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;   // a_bytes/b_bytes: one precision term of A / B
+  const int32_t* offsets;
+  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir;
+  const void* g; int g_dtype; int64_t g_stride; int64_t g_rows; const int32_t* g_row; int g_div;
+  const float* g_scale;
+  int x_vec_ok, g_vec_ok;
+  float* dw;
+  int32_t* status;
+};
+
+constexpr int kDwProdWarps = 12;
+constexpr uint32_t kMnBlock = kBK * 128;   // 64 rows x 128 bytes
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(kFwdThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  setup_cta(sm, p.stages, p.tmem_cols, kDwProdWarps, 4);
+  const uint32_t tmem_base = *sm.tmem_ptr;
+  int32_t* status = p.status;
+  const int64_t items = static_cast<int64_t>(p.E) * p.m_tiles * p.n_tiles;
+  const uint32_t a_total = SPLIT ? 2 * p.a_bytes : p.a_bytes;
+
+  if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
+      uint32_t it = 0, acc_it = 0;
+      bool alive = true;
+      for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
+        const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
+        const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
+        if (chunks == 0) continue;
+        const int buf = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 12)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
+        for (int kc = 0; kc < chunks; ++kc, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (it / p.stages) & 1u;
+          if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 13)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
+          const uint64_t da_hi = make_smem_desc_mn_sw128(sa, kMnBlock);
+          const uint64_t da_lo = make_smem_desc_mn_sw128(sa + p.a_bytes, kMnBlock);
+          const uint64_t db_hi = make_smem_desc_mn_sw128(sa + a_total, kMnBlock);
+          const uint64_t db_lo = make_smem_desc_mn_sw128(sa + a_total + p.b_bytes, kMnBlock);
+#pragma unroll
+          for (int k16 = 0; k16 < kBK / 16; ++k16) {
+            const uint64_t adv = static_cast<uint64_t>(k16 * (16 * 128 / 16));  // 16 rows of 128 bytes, >> 4
+            umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
+            if (SPLIT) {
+              umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+              umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
+            }
+          }
+          umma_commit(bar_empty(sm.bars, s));
+        }
+        if (alive) umma_commit(bar_tfull(sm.bars, buf));
+        ++acc_it;
+      }
+    }
+  } else if (warp >= 2 && warp < 6) {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    uint32_t acc_it = 0;
+    bool alive = true;
+    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
+      const int nt = static_cast<int>(w % p.n_tiles);
+      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
+      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
+      const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
+      const int m = mt * kBM + r;
+      const int n0 = nt * p.BN;
+      float* dst = p.dw + (static_cast<int64_t>(e) * p.K + m) * p.N;
+      if (chunks == 0) {
+        if (m < p.K)
+          for (int n = n0; n < min(n0 + p.BN, p.N); ++n) dst[n] = 0.f;
+        continue;
+      }
+      const int buf = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 15);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
+      for (int c0 = 0; c0 < p.BN; c0 += 16) {
+        float v[16];
+        tmem_ld16(taddr + c0, v);
+        tmem_ld_wait();
+        if (m < p.K) {
+          const int n = n0 + c0;
+          if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
+#pragma unroll
+            for (int x = 0; x < 4; ++x)
+              *reinterpret_cast<float4*>(dst + n + 4 * x) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+          } else {
+#pragma unroll
+            for (int x = 0; x < 16; ++x)
+              if (n + x < p.N) dst[n + x] = v[x];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
+      ++acc_it;
+    }
+  } else if (warp >= 6) {
+    constexpr int np = kDwProdWarps * 32;               // 384
+    const int pt = threadIdx.x - 6 * 32;
+    const int a_chunks = kBM / 8;                        // 16 sixteen-byte chunks per slot row of A
+    const int b_chunks = (p.BN + 7) / 8;
+    const int a_tasks = kBK * a_chunks;                  // 1024
+    const int tasks = a_tasks + kBK * b_chunks;
+    uint32_t it = 0;
+    bool alive = true;
+    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
+      const int nt = static_cast<int>(w % p.n_tiles);
+      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
+      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
+      const int beg = p.offsets[e], end = p.offsets[e + 1];
+      const int chunks = (end - beg + kBK - 1) / kBK;
+      for (int kc = 0; kc < chunks; ++kc, ++it) {
+        const int s = it % p.stages;
+        const uint32_t ph = (it / p.stages) & 1u;
+        bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 16);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        uint8_t* stage = sm.base + s * p.stage_bytes;
+        const int i0 = beg + kc * kBK;
+        for (int base = pt; base < tasks; base += np * 3) {
+          float v[3][8];
+          int where[3];       // byte offset inside the operand term, or -1
+          bool isb[3];
+#pragma unroll
+          for (int b = 0; b < 3; ++b) {
+            const int task = base + b * np;
+            where[b] = -1;
+            isb[b] = task >= a_tasks;
+#pragma unroll
+            for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
+            if (task < tasks) {
+              const int tt = isb[b] ? task - a_tasks : task;
+              const int cpr = isb[b] ? b_chunks : a_chunks;
+              const int r = tt / cpr, c = tt - r * cpr;
+              where[b] = (c >> 3) * static_cast<int>(kMnBlock) + static_cast<int>(sw128_offset(r, c & 7));
+              const int i = i0 + r;
+              if (i < end) {
+                if (!isb[b]) {
+                  const int col = mt * kBM + c * 8;
+                  const int64_t xr = p.x_row[i];
+                  if (xr < 0 || xr >= p.x_rows) {
+                    report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
+                  } else if (col < p.K) {
+                    load8(p.x, p.x_dtype, xr * p.x_stride, col, p.K, p.x_vec_ok != 0, v[b]);
+                    if (p.ir) {
+                      const float rr = p.ir[i];
+#pragma unroll
+                      for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], rr);
+                    }
+                  }
+                } else {
+                  const int col = nt * p.BN + c * 8;
+                  const int64_t gr = p.g_row[i];
+                  if (gr < 0 || gr / p.g_div >= p.g_rows) {
+                    report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
+                  } else if (col < p.N) {
+                    load8(p.g, p.g_dtype, (gr / p.g_div) * p.g_stride, col, p.N, p.g_vec_ok != 0, v[b]);
+                    if (p.g_scale) {
+                      const float sc = p.g_scale[gr];
+#pragma unroll
+                      for (int x = 0; x < 8; ++x) v[b][x] *= sc;
+                    }
+                  }
+                }
+              }
+            }
+          }
+#pragma unroll
+          for (int b = 0; b < 3; ++b) {
+            if (where[b] >= 0) {
+              uint8_t* hi = stage + (isb[b] ? a_total : 0u);
+              uint8_t* lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
+              store8<SPLIT>(hi, lo, static_cast<uint32_t>(where[b]), v[b]);
+            }
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
+      }
+    }
+  }
+  teardown_cta(sm, tmem_base, p.tmem_cols);
+}
+
 uint32_t pow2_cols(int need) {
   uint32_t c = 32;
   while (static_cast<int>(c) < need) c <<= 1;
@@ -767,7 +973,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   int s = amoe_check_device();
   if (s != AMOE_OK) return s;
-  DwParams p{};
+  DwMnParams p{};
   p.E = a->E; p.K = a->K; p.N = a->N;
   const int n_pad = round_up(a->N, 16);
   p.n_tiles = (n_pad + 127) / 128;
@@ -783,9 +989,9 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   p.dw = a->dw; p.status = a->dev_status;
   // bf16 inputs are exact in one term; fp32 inputs are split unless the caller asked for the fast mode
   const bool split = a->precision == AMOE_PREC_SPLIT && !(a->x_dtype == AMOE_BF16 && a->g_dtype == AMOE_BF16 && !a->g_scale);
-  p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
-  p.stage_bytes = (split ? 2u : 1u) * (kATile + p.b_bytes);
-  p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
+  p.a_bytes = 2 * kMnBlock;                                             // 128 columns = 2 blocks
+  p.b_bytes = static_cast<uint32_t>((p.BN + 63) / 64) * kMnBlock;
+  p.stage_bytes = (split ? 2u : 1u) * (p.a_bytes + p.b_bytes);
   p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
@@ -794,11 +1000,11 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   const int64_t items = static_cast<int64_t>(a->E) * p.m_tiles * p.n_tiles;
   const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
   if (split) {
-    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_kernel<true><<<grid, kThreads, smem, stream>>>(p);
+    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dw_tc_mn_kernel<true><<<grid, kFwdThreads, smem, stream>>>(p);
   } else {
-    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_kernel<false><<<grid, kThreads, smem, stream>>>(p);
+    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dw_tc_mn_kernel<false><<<grid, kFwdThreads, smem, stream>>>(p);
   }
   AMOE_LAUNCH_CHECK("dw_tc");
   return AMOE_OK;

@@ -142,6 +142,26 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// Instruction descriptor as above but with both operands MN-major (the contraction index is the slow
+// one in shared memory).
+__host__ __device__ constexpr uint32_t make_idesc_bf16_mn(int M, int N) {
+  return make_idesc_bf16(M, N) | (1u << 15) | (1u << 16);
+}
+
+// Shared-memory matrix descriptor for an MN-major operand tile with the 128-byte swizzle: a tile is a
+// sequence of blocks of 64 MN-elements; inside a block the contraction index k selects a 128-byte row
+// (eight rows form a 1024-byte swizzle atom).  `block_bytes` is the distance between blocks
+// (rows_per_block * 128).  Stepping 16 along the contraction adds 16 rows = 2048 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t block_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // start address
+  d |= static_cast<uint64_t>((block_bytes >> 4) & 0x3FFFu) << 16;   // leading byte offset: next 64 MN-elements
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                      // stride byte offset: next 8 k-rows
+  d |= static_cast<uint64_t>(1) << 46;                              // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2) << 61;                              // SWIZZLE_128B
+  return d;
+}
+
 // Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile.
 __device__ __forceinline__ uint32_t sw128_offset(int r, int c) {
   return static_cast<uint32_t>(r) * 128u + (static_cast<uint32_t>(c ^ (r & 7)) << 4);
