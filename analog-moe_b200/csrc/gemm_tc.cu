@@ -2,24 +2,31 @@
 //
 // cvmm_tc_kernel  (forward and input gradient)
 //   Persistent, warp-specialised CTA, one per SM, walking 128-row tiles of the expert-sorted slot
-//   list.  Roles:
+//   list.  18 warps:
 //     warp 0        lane 0 issues the TMA loads of the prepared bf16 weight tiles (128B swizzle)
 //     warp 1        allocates TMEM; lane 0 issues tcgen05.mma (128 x BN x 16, fp32 accumulate in TMEM)
-//     warps 2-5     epilogue: tcgen05.ld of the accumulator, one thread per output row, then noise /
-//                   ADC / rescale (forward) or clip mask / input-range gradient (backward), stores
-//     warps 6-13    operand prologue: gather the tile's rows, clamp / scale / quantise (DAC), convert
-//                   to bf16 (hi, and lo when the operand is split) and write the swizzled A tile
+//     16 workers    split per launch (4/8/12) between
+//       epilogue:   tcgen05.ld of the accumulator, one thread per output row and share of the
+//                   columns, then noise / ADC / rescale (forward) or clip mask / input-range
+//                   gradient (backward), stores
+//       prologue:   gather the tile's rows, clamp / scale / quantise (DAC), convert to bf16 (hi, and
+//                   lo when the operand is split) and write the swizzled K-major A tile
 //   A and B tiles travel through a ring of shared-memory stages guarded by mbarriers; the
 //   accumulator is double-buffered in TMEM so the epilogue of one tile overlaps the MMAs of the next.
 //   Split precision issues up to three MMAs per k-step: hi*hi + hi*lo + lo*hi.
+//   The kernel is instantiated per DAC mode, input type and epilogue family, and rarely taken paths
+//   (exact division chains, Philox rounds, unaligned loads) are out-of-line calls: the hot loops of
+//   the three roles must stay resident in the instruction cache together.
 //
-// dw_tc_kernel (weight gradient)
-//   Same structure; the contraction runs over the slots of one expert, both operands are produced
-//   by the prologue warps (8x8 register transposes turn row-major rows into K-major tiles), and one
-//   CTA owns each (expert, 128 x BN) output tile, so there are no atomics.
+// dw_tc_mn_kernel (weight gradient)
+//   Same structure; the contraction runs over the slots of one expert, both operands are produced by
+//   the prologue warps as MN-major tiles, and one CTA owns each (expert, 128 x BN) output tile, so
+//   there are no atomics.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records AMOE_ERR_WAIT_LIMIT in the status
 // word, stops issuing work, drains and frees its TMEM.
+#include <cstdlib>
+
 #include "gemm_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -30,11 +37,6 @@ using namespace tc;
 
 constexpr int kBM = 128;          // rows per tile (UMMA M)
 constexpr int kBK = 64;           // bf16 elements per stage along the contraction (128 bytes)
-// dW kernel geometry: 2 control warps, 4 epilogue warps, 8 prologue warps
-constexpr int kProdWarps = 8;
-constexpr int kEpiWarp0 = 2;
-constexpr int kProdWarp0 = 6;
-constexpr int kThreads = (kProdWarp0 + kProdWarps) * 32;  // 448
 // forward / dX kernel geometry: 2 control warps + 16 worker warps whose split between epilogue and
 // prologue is chosen per launch (4, 8 or 12 epilogue warps)
 constexpr int kWorkerWarps = 16;
@@ -76,50 +78,87 @@ struct TileIter {
 struct TcParams {
   int E, Kc, Nout;
   int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
+  int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
+  uint32_t cs_off;      // offset of the per-warp column-scale staging area in dynamic shared memory
+  int cs_per_warp;      // floats per warp and array in that area
   const int32_t* offsets;
   const void* a; int a_dtype; int64_t a_stride; int64_t a_rows; const int32_t* a_row; int a_div;
-  const float* ir; const float* a_absmax; float inp_res; int dac; int vec_ok;
+  const float* ir; const float* a_absmax; float inp_res; int vec_ok;
   EpiParams epi;
 };
 
-// Eight consecutive elements of a row starting at column k (zeros past the row end).
-__device__ __forceinline__ void load8(const void* base, int dtype, int64_t row_off, int k, int K, bool vec_ok,
-                                      float v[8]) {
-  if (k + 8 <= K && vec_ok) {
-    if (dtype == AMOE_F32) {
-      const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + row_off + k);
-      float4 x = __ldg(p), y = __ldg(p + 1);
-      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
-    } else {
-      const uint4 x = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + row_off + k));
-      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        v[2 * i] = __uint_as_float(w[i] << 16);
-        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-      }
-    }
+enum { kDacNone = 0, kDacNorm = 1, kDacQuant = 2 };
+// Epilogue families: forward with the vectorised fast path (optional Philox noise / ADC / codes),
+// input gradient with the fast path (optional clip mask), and the general four-column routine.
+enum { kEpiFwd = 0, kEpiDx = 1, kEpiGeneric = 2 };
+
+// Eight consecutive elements of a row starting at column k (zeros past the row end): the general,
+// element-by-element version, kept out of line.
+struct F8 { float4 a, b; };
+static __device__ __noinline__ F8 load8_slow_call(const void* base, int dtype, int64_t row_off, int k, int K) {
+  float t[8];
+  for (int i = 0; i < 8; ++i) t[i] = (k + i < K) ? load_elem(base, dtype, row_off + k + i) : 0.f;
+  F8 r;
+  r.a = make_float4(t[0], t[1], t[2], t[3]);
+  r.b = make_float4(t[4], t[5], t[6], t[7]);
+  return r;
+}
+__device__ __forceinline__ void load8_slow(const void* base, int dtype, int64_t row_off, int k, int K, float v[8]) {
+  const F8 r = load8_slow_call(base, dtype, row_off, k, K);
+  v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w; v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+}
+
+template <bool F32>
+__device__ __forceinline__ void load8_fast(const void* base, int64_t row_off, int k, float v[8]) {
+  if (F32) {
+    const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + row_off + k);
+    const float4 x = __ldg(q), y = __ldg(q + 1);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
   } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = (k + i < K) ? load_elem(base, dtype, row_off + k + i) : 0.f;
+    const uint4 x = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + row_off + k));
+    v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+    v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+    v[4] = __uint_as_float(x.z << 16); v[5] = __uint_as_float(x.z & 0xffff0000u);
+    v[6] = __uint_as_float(x.w << 16); v[7] = __uint_as_float(x.w & 0xffff0000u);
   }
 }
 
+// Dispatching loader used by the dW prologue (dtype known only at run time).
+__device__ __forceinline__ void load8(const void* base, int dtype, int64_t row_off, int k, int K, bool vec_ok,
+                                      float v[8]) {
+  if (k + 8 <= K && vec_ok) {
+    if (dtype == AMOE_F32) load8_fast<true>(base, row_off, k, v);
+    else load8_fast<false>(base, row_off, k, v);
+  } else {
+    load8_slow(base, dtype, row_off, k, K, v);
+  }
+}
+
+__device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Eight values -> one 16-byte chunk of bf16 (and a second chunk with the rounding residuals).
+__device__ __forceinline__ void store8_rt(uint8_t* tile_hi, uint8_t* tile_lo, uint32_t off, const float v[8], bool split) {
+  uint32_t h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = cvt_bf16x2(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(tile_hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+  if (split) {
+    uint32_t l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      l[i] = cvt_bf16x2(v[2 * i] - __uint_as_float(h[i] << 16), v[2 * i + 1] - __uint_as_float(h[i] & 0xffff0000u));
+    *reinterpret_cast<uint4*>(tile_lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
 template <bool SPLIT>
 __device__ __forceinline__ void store8(uint8_t* tile_hi, uint8_t* tile_lo, uint32_t off, const float v[8]) {
-  __nv_bfloat16 hi[8], lo[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    hi[i] = __float2bfloat16_rn(v[i]);
-    if (SPLIT) lo[i] = __float2bfloat16_rn(v[i] - __bfloat162float(hi[i]));
-  }
-  *reinterpret_cast<uint4*>(tile_hi + off) =
-      make_uint4(pack_bf16x2(hi[0], hi[1]), pack_bf16x2(hi[2], hi[3]), pack_bf16x2(hi[4], hi[5]), pack_bf16x2(hi[6], hi[7]));
-  if (SPLIT)
-    *reinterpret_cast<uint4*>(tile_lo + off) = make_uint4(pack_bf16x2(lo[0], lo[1]), pack_bf16x2(lo[2], lo[3]),
-                                                          pack_bf16x2(lo[4], lo[5]), pack_bf16x2(lo[6], lo[7]));
+  store8_rt(tile_hi, tile_lo, off, v, SPLIT);
 }
 
 struct SmemView {
@@ -186,6 +225,12 @@ __device__ __forceinline__ void teardown_cta(const SmemView& s, uint32_t tmem_ba
 }
 
 // ============================================================================ forward / dX
+#ifdef AMOE_TIMELINE
+__device__ long long g_timeline[4][512][4];
+#define TL(role, idx, k) do { if (blockIdx.x == 0 && (idx) < 512) g_timeline[role][idx][k] = clock64(); } while (0)
+#else
+#define TL(role, idx, k) do { } while (0)
+#endif
 // Rendezvous of a group of warps on an mbarrier whose arrival count is the number of warps.
 // `round` counts the uses of this barrier by the calling warp.  Returns false if the wait gave up.
 __device__ __forceinline__ bool group_sync(uint32_t bar, uint32_t round, volatile int* abort_flag, int32_t* status,
@@ -203,7 +248,90 @@ struct __align__(16) RowMeta {
   float pad;
 };
 
-template <bool A_SPLIT, bool B_SPLIT>
+// ---- epilogue of one 16-column chunk, fast families (everything 16-byte aligned, n_out % 4 == 0,
+// chunk entirely inside the row)
+__device__ __forceinline__ void store16(const EpiParams& p, int64_t base, const float o[16]) {
+  if (p.out_dtype == AMOE_F32) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      dst[j] = make_uint4(cvt_bf16x2(o[8 * j], o[8 * j + 1]), cvt_bf16x2(o[8 * j + 2], o[8 * j + 3]),
+                          cvt_bf16x2(o[8 * j + 4], o[8 * j + 5]), cvt_bf16x2(o[8 * j + 6], o[8 * j + 7]));
+  }
+}
+
+// cs / cis: this chunk's 16 column scales and reciprocals in shared memory (staged by the warp).
+__device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, int n0, float v[16],
+                                              const float* cs, const float* cis) {
+  const bool noise = p.noise_std > 0.f, adc = p.adc.on;
+  const float post = c.absmax * c.ir;
+  float code[16];
+#pragma unroll
+  for (int qd = 0; qd < 4; ++qd) {
+    float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
+    if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
+    if (adc) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
+    if (noise) z = philox_normal4_inline(p.seed, p.offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
+                                         static_cast<uint32_t>((n0 >> 2) + qd));
+    const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w}, zv[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float acc = v[4 * qd + j] * p.acc_mul;
+      if (noise) acc += (p.noise_std * sv[j]) * zv[j];
+      code[4 * qd + j] = 0.f;
+      if (adc) acc = adc_apply(acc, sv[j], iv[j], p.adc, code[4 * qd + j]);
+      v[4 * qd + j] = acc * post;
+    }
+  }
+  store16(p, c.dst * p.out_stride + n0, v);
+  if (p.out_codes) {
+    uint32_t pk[4];
+#pragma unroll
+    for (int qd = 0; qd < 4; ++qd)
+      pk[qd] = (static_cast<uint32_t>(static_cast<int>(code[4 * qd])) & 0xffu) |
+               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 1])) & 0xffu) << 8) |
+               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 2])) & 0xffu) << 16) |
+               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 3])) & 0xffu) << 24);
+    *reinterpret_cast<uint4*>(p.out_codes + c.dst * p.n_out + n0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+}
+
+__device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, int n0, float v[16]) {
+  if (p.x_ref) {
+    float xr[16];
+    if (p.x_ref_dtype == AMOE_F32) {
+      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + c.xrow * p.x_ref_stride + n0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 t = __ldg(src + j);
+        xr[4 * j] = t.x; xr[4 * j + 1] = t.y; xr[4 * j + 2] = t.z; xr[4 * j + 3] = t.w;
+      }
+    } else {
+      load8_fast<false>(p.x_ref, c.xrow * p.x_ref_stride, n0, xr);
+      load8_fast<false>(p.x_ref, c.xrow * p.x_ref_stride, n0 + 8, xr + 8);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float gs = v[j] * c.rs;
+      const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
+      if (up) c.dir_acc += fminf(gs, 0.f);
+      if (low) c.dir_acc -= fmaxf(gs, 0.f);
+      c.keep += keep ? 1u : 0u;
+      v[j] = keep ? gs : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] *= c.rs;
+  }
+  store16(p, c.dst * p.out_stride + n0, v);
+}
+
+template <int DAC, bool A_F32, int EPI>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -221,7 +349,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     // ---------------------------------------------------------------- weight tiles by TMA
     if (lane == 0) {
       tma_prefetch_desc(&tmap_hi);
-      if (B_SPLIT) tma_prefetch_desc(&tmap_lo);
+      if (p.b_split) tma_prefetch_desc(&tmap_lo);
       TileIter ti(p.offsets, p.E);
       uint32_t it = 0;
       bool alive = true;
@@ -234,9 +362,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             const uint32_t ph = (it / p.stages) & 1u;
             if (!mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 1)) { alive = false; break; }
             const uint32_t dst = sm.base_u32 + s * p.stage_bytes + p.a_bytes;
-            mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (B_SPLIT ? 2u : 1u));
+            mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (p.b_split ? 2u : 1u));
             tma_load_3d(dst, &tmap_hi, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
-            if (B_SPLIT) tma_load_3d(dst + p.b_bytes, &tmap_lo, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
+            if (p.b_split) tma_load_3d(dst + p.b_bytes, &tmap_lo, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
           }
         }
       }
@@ -260,8 +388,11 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
             const int s = it % p.stages;
             const uint32_t ph = (it / p.stages) & 1u;
-            if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3) ||
-                !mbar_wait(bar_full_b(sm.bars, s), ph, sm.abort_flag, status, 4)) { alive = false; break; }
+            TL(1, it, 0);
+            if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
+            TL(1, it, 1);
+            if (!mbar_wait(bar_full_b(sm.bars, s), ph, sm.abort_flag, status, 4)) { alive = false; break; }
+            TL(1, it, 2);
             tc_fence_after();
             const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
             const uint64_t da_hi = make_smem_desc_sw128(sa);
@@ -272,10 +403,11 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             for (int k16 = 0; k16 < kBK / 16; ++k16) {
               const uint64_t adv = static_cast<uint64_t>(k16 * 2);  // 32 bytes >> 4
               umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
-              if (B_SPLIT) umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
-              if (A_SPLIT) umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
+              if (p.b_split) umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+              if (p.a_split) umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
             }
             umma_commit(bar_empty(sm.bars, s));
+            TL(1, it, 3);
           }
           if (alive) umma_commit(bar_tfull(sm.bars, buf));
         }
@@ -288,13 +420,14 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     const int q = warp & 3;
     const int grp = ew >> 2;
     const int groups = p.n_epi >> 2;
-    const int epi_threads = p.n_epi * 32;
     const int r = q * 32 + lane;
     const int chunks = p.BN / 16;
+    float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
+    float* cis_smem = cs_smem + p.cs_per_warp;
+    const bool need_cs = EPI == kEpiFwd && (p.epi.noise_std > 0.f || p.epi.adc.on);
     TileIter ti(p.offsets, p.E);
     uint32_t acc_it = 0, sync_round = 0;
     bool alive = true;
-    (void)epi_threads;
     for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
       int e, row0, rows;
       if (!ti.get(t, e, row0, rows)) break;
@@ -303,21 +436,51 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       for (int nt = 0; nt < p.n_tiles && alive; ++nt, ++acc_it) {
         const int buf = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
+        if (need_cs) {
+          // this warp's chunks of col_scale / col_inv_scale, staged while the MMAs are still running
+          __syncwarp();
+          int slot = 0;
+          for (int ch = grp; ch < chunks; ch += groups, ++slot) {
+            const int n = nt * p.BN + ch * 16 + (lane & 15);
+            if (n < p.epi.n_out) {
+              const int64_t ci = static_cast<int64_t>(e) * p.epi.n_out + n;
+              if (lane < 16) cs_smem[slot * 16 + lane] = p.epi.col_scale[ci];
+              else if (p.epi.adc.on) cis_smem[slot * 16 + lane - 16] = p.epi.col_inv_scale[ci];
+            }
+          }
+          __syncwarp();
+        }
+        if (ew == 0 && lane == 0) TL(3, acc_it, 0);
         bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 5);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
+        if (ew == 0 && lane == 0) TL(3, acc_it, 1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
-        for (int ch = grp; ch < chunks; ch += groups) {
+        int slot = 0;
+#pragma unroll 1
+        for (int ch = grp; ch < chunks; ch += groups, ++slot) {
           float v[16];
           tmem_ld16(taddr + ch * 16, v);
           tmem_ld_wait();
+          const int n0 = nt * p.BN + ch * 16;
+          if (EPI == kEpiGeneric || n0 + 16 > p.epi.n_out) {
+#pragma unroll 1
+            for (int qd = 0; qd < 4; ++qd) {
+              const float w4[4] = {v[0], v[1], v[2], v[3]};
+              epi_quad(p.epi, ctx, n0 + 4 * qd, w4);
 #pragma unroll
-          for (int qd = 0; qd < 4; ++qd) epi_quad(p.epi, ctx, nt * p.BN + ch * 16 + 4 * qd, &v[4 * qd]);
+              for (int j = 0; j < 12; ++j) v[j] = v[j + 4];   // rotate the next four columns in
+            }
+          } else if (ctx.valid) {
+            if (EPI == kEpiFwd) epi_chunk_fwd(p.epi, ctx, n0, v, cs_smem + slot * 16, cis_smem + slot * 16);
+            else epi_chunk_dx(p.epi, ctx, n0, v);
+          }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
+        if (ew == 0 && lane == 0) TL(3, acc_it, 2);
       }
       if (!alive) break;
       if (p.epi.is_dx && (p.epi.ir_grad || p.epi.keep_count)) {
@@ -351,8 +514,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     // ---------------------------------------------------------------- operand prologue (A tiles)
     const int np = n_prod * 32;
     const int pt = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np-1
-    const bool has_ir = p.dac && p.ir != nullptr, has_am = p.dac && p.a_absmax != nullptr;
-    const bool quant = p.dac && p.inp_res > 0.f;
+    const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
+    const bool a_split = p.a_split != 0;
     TileIter ti(p.offsets, p.E);
     uint32_t it = 0, sync_round = 0;
     bool alive = true;
@@ -373,7 +536,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             m.src_off = src * p.a_stride;
             if (has_ir) m.ir = p.ir[i];
             if (has_am) m.am = p.a_absmax[src];
-            if (quant) m.fast = dac_fast_mul(has_ir, m.ir, has_am, m.am, p.inp_res);
+            if (DAC == kDacQuant) m.fast = dac_fast_mul(has_ir, m.ir, has_am, m.am, p.inp_res);
           }
         }
         s_meta[r] = m;
@@ -384,254 +547,55 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1u;
+          if (pt == 0) TL(2, it, 0);
           bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 6);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
+          if (pt == 0) TL(2, it, 1);
           uint8_t* a_hi = sm.base + s * p.stage_bytes;
           uint8_t* a_lo = a_hi + kATile;
-          // 1024 tasks (128 rows x 8 sixteen-byte chunks), four per thread and round
-          for (int base = pt; base < kBM * 8; base += np * 4) {
-            float v[4][8];
-            RowMeta m[4];
+          const bool full_k = (kc + 1) * kBK <= p.Kc && p.vec_ok;
+          // 1024 tasks (128 rows x 8 sixteen-byte chunks), two per thread and round
+#pragma unroll 1
+          for (int base = pt; base < kBM * 8; base += np * 2) {
+            float v[2][8];
+            RowMeta m[2];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
-              const int r = task >> 3, c = task & 7;
-              if (task < kBM * 8) m[b] = s_meta[r]; else m[b].src_off = -1;
-              const int k = kc * kBK + c * 8;
-              if (m[b].src_off >= 0 && k < p.Kc) {
-                load8(p.a, p.a_dtype, m[b].src_off, k, p.Kc, p.vec_ok != 0, v[b]);
+              m[b].src_off = -1;
+              if (task < kBM * 8) m[b] = s_meta[task >> 3];
+              const int k = kc * kBK + (task & 7) * 8;
+              if (m[b].src_off >= 0 && full_k) {
+                load8_fast<A_F32>(p.a, m[b].src_off, k, v[b]);
+              } else if (m[b].src_off >= 0 && k < p.Kc) {
+                load8_slow(p.a, p.a_dtype, m[b].src_off, k, p.Kc, v[b]);
               } else {
+                m[b].src_off = -1;
 #pragma unroll
                 for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
               }
             }
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
               if (task < kBM * 8) {
-                const int r = task >> 3, c = task & 7;
-                if (p.dac && m[b].src_off >= 0) {
+                if (DAC == kDacQuant && m[b].src_off >= 0) {
+                  dac_code8(v[b], has_ir, m[b].ir, has_am, m[b].am, p.inp_res, m[b].fast);
+                } else if (DAC == kDacNorm && m[b].src_off >= 0) {
 #pragma unroll
-                  for (int x = 0; x < 8; ++x) {
-                    if (quant)
-                      v[b][x] = dac_code(v[b][x], has_ir, m[b].ir, has_am, m[b].am, p.inp_res, m[b].fast);
-                    else
-                      v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, has_am, m[b].am);
-                  }
+                  for (int x = 0; x < 8; ++x) v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, has_am, m[b].am);
                 }
-                store8<A_SPLIT>(a_hi, a_lo, sw128_offset(r, c), v[b]);
+                store8_rt(a_hi, a_lo, sw128_offset(task >> 3, task & 7), v[b], a_split);
               }
             }
           }
+          if (pt == 0) TL(2, it, 2);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
+          if (pt == 0) TL(2, it, 3);
         }
-      }
-    }
-  }
-  teardown_cta(sm, tmem_base, p.tmem_cols);
-}
-
-// ============================================================================ dW
-struct DwParams {
-  int E, K, N;
-  int BN, m_tiles, n_tiles, stages;
-  uint32_t tmem_cols, stage_bytes, b_bytes;
-  const int32_t* offsets;
-  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir;
-  const void* g; int g_dtype; int64_t g_stride; int64_t g_rows; const int32_t* g_row; int g_div;
-  const float* g_scale;
-  int x_vec_ok, g_vec_ok;
-  float* dw;
-  int32_t* status;
-};
-
-// Loads an 8(slot) x 8(column) block, transposes it in registers and writes eight 16-byte chunks
-// (one per column, eight consecutive slots each) into a K-major swizzled tile.
-template <bool SPLIT>
-__device__ __forceinline__ void produce_block(const float v[8][8], uint8_t* tile_hi, uint8_t* tile_lo, int row_base,
-                                              int sg) {
-#pragma unroll
-  for (int m = 0; m < 8; ++m) {
-    float col[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) col[j] = v[j][m];
-    store8<SPLIT>(tile_hi, tile_lo, sw128_offset(row_base + m, sg), col);
-  }
-}
-
-template <bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1) dw_tc_kernel(DwParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // full_a is the only "data ready" barrier here (both operands come from the prologue warps)
-  setup_cta(sm, p.stages, p.tmem_cols, kProdWarps);
-  const uint32_t tmem_base = *sm.tmem_ptr;
-  int32_t* status = p.status;
-  const int64_t items = static_cast<int64_t>(p.E) * p.m_tiles * p.n_tiles;
-  const uint32_t a_total = SPLIT ? 2 * kATile : kATile;
-
-  if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(kBM, p.BN);
-      uint32_t it = 0, acc_it = 0;
-      bool alive = true;
-      for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-        const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-        const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
-        if (chunks == 0) continue;
-        const int buf = acc_it & 1u;
-        const uint32_t aph = (acc_it >> 1) & 1u;
-        if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 12)) { alive = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
-        for (int kc = 0; kc < chunks; ++kc, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
-          if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 13)) { alive = false; break; }
-          tc_fence_after();
-          const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
-          const uint64_t da_hi = make_smem_desc_sw128(sa);
-          const uint64_t da_lo = make_smem_desc_sw128(sa + kATile);
-          const uint64_t db_hi = make_smem_desc_sw128(sa + a_total);
-          const uint64_t db_lo = make_smem_desc_sw128(sa + a_total + p.b_bytes);
-#pragma unroll
-          for (int k16 = 0; k16 < kBK / 16; ++k16) {
-            const uint64_t adv = static_cast<uint64_t>(k16 * 2);
-            umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
-            if (SPLIT) {
-              umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
-              umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
-            }
-          }
-          umma_commit(bar_empty(sm.bars, s));
-        }
-        if (alive) umma_commit(bar_tfull(sm.bars, buf));
-        ++acc_it;
-      }
-    }
-  } else if (warp >= kEpiWarp0 && warp < kProdWarp0) {
-    const int q = warp & 3;
-    const int r = q * 32 + lane;
-    uint32_t acc_it = 0;
-    bool alive = true;
-    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-      const int nt = static_cast<int>(w % p.n_tiles);
-      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
-      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-      const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
-      const int m = mt * kBM + r;
-      const int n0 = nt * p.BN;
-      float* dst = p.dw + (static_cast<int64_t>(e) * p.K + m) * p.N;
-      if (chunks == 0) {
-        if (m < p.K)
-          for (int n = n0; n < min(n0 + p.BN, p.N); ++n) dst[n] = 0.f;
-        continue;
-      }
-      const int buf = acc_it & 1u;
-      const uint32_t aph = (acc_it >> 1) & 1u;
-      bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 15);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { alive = false; break; }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
-      for (int c0 = 0; c0 < p.BN; c0 += 16) {
-        float v[16];
-        tmem_ld16(taddr + c0, v);
-        tmem_ld_wait();
-        if (m < p.K) {
-          const int n = n0 + c0;
-          if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
-#pragma unroll
-            for (int x = 0; x < 4; ++x)
-              *reinterpret_cast<float4*>(dst + n + 4 * x) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
-          } else {
-#pragma unroll
-            for (int x = 0; x < 16; ++x)
-              if (n + x < p.N) dst[n + x] = v[x];
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
-      ++acc_it;
-    }
-  } else if (warp >= kProdWarp0) {
-    const int pt = threadIdx.x - kProdWarp0 * 32;  // 0..255
-    const bool is_b = pt >= 128;
-    const int u = pt & 127;
-    const int sg = u & 7;    // slot group: slots sg*8 .. sg*8+7 of the stage
-    const int cg = u >> 3;   // column group: columns cg*8 .. cg*8+7 of the tile
-    uint32_t it = 0;
-    bool alive = true;
-    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-      const int nt = static_cast<int>(w % p.n_tiles);
-      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
-      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-      const int beg = p.offsets[e], end = p.offsets[e + 1];
-      const int chunks = (end - beg + kBK - 1) / kBK;
-      const int col0 = is_b ? nt * p.BN + cg * 8 : mt * kBM + cg * 8;
-      const int col_lim = is_b ? p.N : p.K;
-      const bool active = is_b ? (cg * 8 < p.BN) : true;
-      for (int kc = 0; kc < chunks; ++kc, ++it) {
-        const int s = it % p.stages;
-        const uint32_t ph = (it / p.stages) & 1u;
-        bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 16);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { alive = false; break; }
-        uint8_t* stage = sm.base + s * p.stage_bytes;
-        if (active) {
-          float v[8][8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int i = beg + kc * kBK + sg * 8 + j;
-            bool okr = i < end && col0 < col_lim;
-            if (okr) {
-              if (!is_b) {
-                const int64_t xr = p.x_row[i];
-                if (xr < 0 || xr >= p.x_rows) {
-                  report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
-                  okr = false;
-                } else {
-                  load8(p.x, p.x_dtype, xr * p.x_stride, col0, p.K, p.x_vec_ok != 0, v[j]);
-                  if (p.ir) {
-                    const float r = p.ir[i];
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) v[j][x] = clamp_ir(v[j][x], r);
-                  }
-                }
-              } else {
-                const int64_t gr = p.g_row[i];
-                if (gr < 0 || gr / p.g_div >= p.g_rows) {
-                  report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
-                  okr = false;
-                } else {
-                  load8(p.g, p.g_dtype, (gr / p.g_div) * p.g_stride, col0, p.N, p.g_vec_ok != 0, v[j]);
-                  if (p.g_scale) {
-                    const float sc = p.g_scale[gr];
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) v[j][x] *= sc;
-                  }
-                }
-              }
-            }
-            if (!okr) {
-#pragma unroll
-              for (int x = 0; x < 8; ++x) v[j][x] = 0.f;
-            }
-          }
-          if (!is_b)
-            produce_block<SPLIT>(v, stage, stage + kATile, cg * 8, sg);
-          else
-            produce_block<SPLIT>(v, stage + a_total, stage + a_total + p.b_bytes, cg * 8, sg);
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
       }
     }
   }
@@ -850,7 +814,7 @@ uint32_t pow2_cols(int need) {
   return c;
 }
 
-constexpr uint32_t kSmemBudget = 192 * 1024;  // ring budget; barriers and alignment slack come on top
+constexpr uint32_t kSmemBudget = 196 * 1024;  // ring budget; barriers and alignment slack come on top
 constexpr uint32_t kSmemExtra = 1024 + 8 * kNumBars + 64;
 
 }  // namespace
@@ -903,20 +867,21 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   p.offsets = a->expert_offsets;
   p.a = a->a; p.a_dtype = a->a_dtype; p.a_stride = a->a_stride; p.a_rows = a->a_rows; p.a_row = a->a_row;
   p.a_div = a->a_row_div < 1 ? 1 : a->a_row_div;
-  p.dac = is_dx ? 0 : 1;
   p.ir = is_dx ? nullptr : a->ir;
   p.a_absmax = is_dx ? nullptr : a->a_absmax;
   p.inp_res = is_dx ? -1.f : a->inp_res;
   const int esz = a->a_dtype == AMOE_F32 ? 4 : 2;
   p.vec_ok = aligned16(a->a) && ((a->a_stride * esz) % 16 == 0);
   p.epi = epi_in;
-  const bool quant = p.dac && p.inp_res > 0.f;
+  const bool dac = !is_dx;
+  const bool quant = dac && p.inp_res > 0.f;
   // Integer DAC codes up to 256 in magnitude are exact in bf16; anything else needs the hi+lo pair
   // when split precision is asked for.  bf16 inputs that are not quantised are exact as they are.
   bool a_split = a->precision == AMOE_PREC_SPLIT;
   if (quant && p.inp_res >= 1.0f / 256.0f) a_split = false;
-  if (!p.dac && a->a_dtype == AMOE_BF16) a_split = false;
+  if (!quant && a->a_dtype == AMOE_BF16 && !(dac && (p.ir || p.a_absmax))) a_split = false;
   const bool b_split = a->precision == AMOE_PREC_SPLIT && a->w_lo != nullptr;
+  p.a_split = a_split; p.b_split = b_split;
   p.epi.acc_mul = quant ? p.inp_res : 1.f;
 
   p.a_bytes = a_split ? 2 * kATile : kATile;
@@ -929,8 +894,8 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   p.tmem_cols = pow2_cols(2 * p.BN);
   {
     // Split the 16 worker warps between epilogue and prologue by estimated instruction counts.
-    const double per_prod = (quant ? 13.0 : (p.dac ? 30.0 : 4.0)) + (a_split ? 6.0 : 2.0);
-    double per_epi = 10.0;
+    const double per_prod = (quant ? 13.0 : (dac && (p.ir || p.a_absmax) ? 18.0 : 3.0)) + (a_split ? 5.0 : 2.0);
+    double per_epi = 8.0;
     if (!is_dx) per_epi += (a->noise_std > 0.f ? 26.0 : 0.0) + (a->noise ? 2.0 : 0.0) + (p.epi.adc.on ? 9.0 : 0.0) +
                            (a->out_codes ? 3.0 : 0.0);
     else per_epi += a->x_ref ? 12.0 : 0.0;
@@ -942,6 +907,13 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       if (t < best) { best = t; p.n_epi = ne; }
     }
   }
+  // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
+  {
+    const int groups = p.n_epi / 4;
+    p.cs_per_warp = ((p.BN / 16 + groups - 1) / groups) * 16;
+    p.cs_off = static_cast<uint32_t>(p.stages) * p.stage_bytes + 8u * kNumBars + 64u;
+  }
+  const uint32_t cs_bytes = static_cast<uint32_t>(p.n_epi) * 2u * p.cs_per_warp * sizeof(float);
 
   CUtensorMap m_hi, m_lo;
   s = encode_tmap_bf16_3d(&m_hi, a->w_hi, static_cast<uint64_t>(k_pad), static_cast<uint64_t>(n_pad),
@@ -953,22 +925,44 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
                             static_cast<uint64_t>(a->E), kBK, static_cast<uint32_t>(p.BN));
     if (s != AMOE_OK) return s;
   }
-  const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra;
+  const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra + cs_bytes;
   const int64_t max_tiles = (a->P + kBM - 1) / kBM + a->E;
   const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
-#define AMOE_LAUNCH_TC(AS, BS)                                                                                  \
-  do {                                                                                                          \
-    AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    cvmm_tc_kernel<AS, BS><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, p);                                 \
+  const bool f32 = a->a_dtype == AMOE_F32;
+  // epilogue family: the fast routines need 16-byte alignment everywhere and no materialised noise
+  int epi = kEpiGeneric;
+  if (p.epi.vec4 && !is_dx && a->noise == nullptr) epi = kEpiFwd;
+  if (p.epi.vec4 && is_dx && (a->x_ref == nullptr || a->x_ref_dtype == AMOE_F32 || a->x_ref_stride % 8 == 0)) epi = kEpiDx;
+  const int dacm = is_dx ? kDacNone : (quant ? kDacQuant : kDacNorm);
+#define AMOE_LAUNCH_TC(DAC, F32, EPI)                                                                                  \
+  do {                                                                                                                 \
+    AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<DAC, F32, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    cvmm_tc_kernel<DAC, F32, EPI><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, p);                                 \
   } while (0)
-  if (a_split && b_split) AMOE_LAUNCH_TC(true, true);
-  else if (a_split) AMOE_LAUNCH_TC(true, false);
-  else if (b_split) AMOE_LAUNCH_TC(false, true);
-  else AMOE_LAUNCH_TC(false, false);
+#define AMOE_LAUNCH_TC_DT(DAC, EPI) \
+  do { if (f32) AMOE_LAUNCH_TC(DAC, true, EPI); else AMOE_LAUNCH_TC(DAC, false, EPI); } while (0)
+  if (is_dx) {
+    if (epi == kEpiDx) AMOE_LAUNCH_TC_DT(kDacNone, kEpiDx); else AMOE_LAUNCH_TC_DT(kDacNone, kEpiGeneric);
+  } else if (dacm == kDacQuant) {
+    if (epi == kEpiFwd) AMOE_LAUNCH_TC_DT(kDacQuant, kEpiFwd); else AMOE_LAUNCH_TC_DT(kDacQuant, kEpiGeneric);
+  } else {
+    if (epi == kEpiFwd) AMOE_LAUNCH_TC_DT(kDacNorm, kEpiFwd); else AMOE_LAUNCH_TC_DT(kDacNorm, kEpiGeneric);
+  }
+#undef AMOE_LAUNCH_TC_DT
 #undef AMOE_LAUNCH_TC
   AMOE_LAUNCH_CHECK("cvmm_tc");
   return AMOE_OK;
 }
+
+#ifdef AMOE_TIMELINE
+extern "C" int amoe_debug_timeline(long long* host, int clear) {
+  if (clear) {
+    static long long zeros[4 * 512 * 4] = {0};
+    return cudaMemcpyToSymbol(g_timeline, zeros, sizeof(zeros)) == cudaSuccess ? 0 : 5;
+  }
+  return cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * 4 * 512 * 4) == cudaSuccess ? 0 : 5;
+}
+#endif
 
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   int s = amoe_check_device();
