@@ -35,7 +35,7 @@ class WeightPrepassArgs(C.Structure):
         ("w", vp), ("w_dtype", C.c_int32), ("E", C.c_int32), ("K", C.c_int32), ("N", C.c_int32),
         ("w_stride_e", C.c_int64), ("w_stride_k", C.c_int64), ("w_stride_n", C.c_int64),
         ("per_channel_scale", C.c_int32), ("noise_std", C.c_float), ("noise_per_channel", C.c_int32),
-        ("discretize_res", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32),
+        ("discretize_res", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32), ("step_dev", vp),
         ("col_scale", vp), ("col_inv_scale", vp), ("w_out", vp), ("fwd_hi", vp), ("fwd_lo", vp), ("bwd_hi", vp), ("bwd_lo", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t),
     ]
@@ -50,7 +50,8 @@ class CvmmArgs(C.Structure):
         ("w", vp), ("w_dtype", C.c_int32), ("w_stride_e", C.c_int64), ("w_stride_k", C.c_int64),
         ("w_stride_n", C.c_int64), ("w_hi", vp), ("w_lo", vp),
         ("ir", vp), ("a_absmax", vp), ("inp_res", C.c_float),
-        ("noise", vp), ("noise_std", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32), ("col_scale", vp),
+        ("noise", vp), ("noise_std", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32), ("step_dev", vp),
+        ("col_scale", vp),
         ("col_inv_scale", vp), ("out_res", C.c_float), ("out_bound", C.c_float),
         ("out", vp), ("out_dtype", C.c_int32), ("out_stride", C.c_int64), ("out_codes", vp),
         ("x_ref", vp), ("x_ref_dtype", C.c_int32), ("x_ref_stride", C.c_int64), ("x_ref_rows", C.c_int64),

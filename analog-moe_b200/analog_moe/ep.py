@@ -180,7 +180,6 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
 
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
         self._noise_calls = 0
-        self._noise_step_host = getattr(self, "_noise_step_host", 0)
         bsz, seq, D = inp.shape
         T, k = bsz * seq, self.n_heads
         logits = self.expert_sel(inp)
@@ -205,6 +204,5 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         res = _ScatterToSlots.apply(back, r.slot_index)
         y = _CombineGate.apply(res, gate)
         if self.training:
-            self._noise_step_host += 1
             self.noise_step += 1
         return y.view(bsz, seq, self.v_dim), inp.new_zeros(())

@@ -176,12 +176,14 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         disc = float(mod.res) if name.startswith("DISCRETIZE") else -1.0
         std = float(mod.std_dev) if "ADD_NORMAL" in name else 0.0
         return WeightModifier(std_dev=std, per_channel=per_channel, discretize_res=disc, seed=self.noise_seed,
-                              offset=self._next_offset())
+                              offset=self._next_offset(), step=self.noise_step)
 
     def _next_offset(self) -> int:
-        # (step, call) -> Philox offset: a resumed run that restores `noise_step` replays its noise
+        # Philox offset = call index inside the step + 8 * noise_step, where noise_step is a device
+        # counter the kernels read: a CUDA graph of the step draws fresh noise on every replay, and
+        # a resumed run that restores `noise_step` replays its noise.
         self._noise_calls += 1
-        return (int(self._noise_step_host) * 8 + self._noise_calls) & 0xFFFFFFFF
+        return self._noise_calls & 7
 
     def cvmm_wrapper(self, inputs: Tensor, sel_indices: CVMMSel, weights: Tensor) -> Tensor:
         cfg = self.rpu_config
@@ -206,7 +208,7 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1   # lightning :451-456
         noise = None
         if self.training and cfg.forward.out_noise > 0:                             # lightning :471-492
-            noise = PhiloxNoise(float(cfg.forward.out_noise), self.noise_seed, self._next_offset())
+            noise = PhiloxNoise(float(cfg.forward.out_noise), self.noise_seed, self._next_offset(), self.noise_step)
         ext = CVMMExt(noise=noise, modifier=self._weight_modifier(), out_res=float(cfg.forward.out_res),
                       out_bound=float(cfg.forward.out_bound),
                       scale_per_channel=bool(getattr(cfg.forward, "out_noise_per_channel", True)),
@@ -216,16 +218,10 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
 
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
         self._noise_calls = 0
-        self._noise_step_host = getattr(self, "_noise_step_host", 0)
         out = super().forward(inp)
         if self.training:
-            self._noise_step_host += 1
             self.noise_step += 1
         return out
-
-    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
-        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
-        self._noise_step_host = int(self.noise_step)
 
     def post_update_step(self) -> None:
         if _enum_name(self.rpu_config.clip.type) not in ("NONE", "None"):

@@ -156,7 +156,7 @@ def prepared_dims(K: int, N: int) -> Tuple[int, int, int, int]:
 
 def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool = True, noise_std: float = 0.0,
                    noise_per_channel: bool = True, discretize_res: float = -1.0, seed: int = 0, offset: int = 0,
-                   need_fwd: bool = True, need_bwd: bool = True, need_w_out: bool = False) -> PreparedWeights:
+                   step_dev: Optional[torch.Tensor] = None, need_fwd: bool = True, need_bwd: bool = True, need_w_out: bool = False) -> PreparedWeights:
     A.require_cuda(w)
     E, K, N = w.shape
     dev = w.device
@@ -169,6 +169,7 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     a.noise_std, a.noise_per_channel = float(noise_std), int(noise_per_channel)
     a.discretize_res = float(discretize_res)
     a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
+    a.step_dev = ptr(step_dev)
     col_inv = torch.empty(E, N, dtype=torch.float32, device=dev)
     a.col_scale = ptr(col_scale)
     a.col_inv_scale = ptr(col_inv)
@@ -235,7 +236,7 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
              pw: PreparedWeights, precision: int, *, P: int, dst_rows: int, a_row_div: int = 1,
              ir: Optional[torch.Tensor] = None, absmax: Optional[torch.Tensor] = None, inp_res: float = -1.0,
              noise: Optional[torch.Tensor] = None, noise_std: float = 0.0, seed: int = 0, offset: int = 0,
-             out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
+             step_dev: Optional[torch.Tensor] = None, out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
              out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None):
     x2 = _rows(x2)
     dev = x2.device
@@ -253,6 +254,7 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
         assert noise.shape[0] == dst_rows
     a.noise, a.noise_std = ptr(noise), float(noise_std)
     a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
+    a.step_dev = ptr(step_dev)
     a.col_scale = ptr(pw.col_scale)
     a.col_inv_scale = ptr(pw.col_inv_scale)
     a.out_res, a.out_bound = float(out_res), float(out_bound)

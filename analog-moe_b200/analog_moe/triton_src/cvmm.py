@@ -59,6 +59,7 @@ class PhiloxNoise:
     std: float
     seed: int
     offset: int = 0
+    step: Optional[torch.Tensor] = None     # int64 device scalar; the offset in effect is offset + 8*step
 
 
 @dataclass
@@ -69,6 +70,7 @@ class WeightModifier:
     discretize_res: float = -1.0
     seed: int = 0
     offset: int = 0
+    step: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -130,21 +132,21 @@ class CVMM(torch.autograd.Function):
             keys, precision, per_channel_scale=ext.scale_per_channel,
             noise_std=mod.std_dev if mod else 0.0, noise_per_channel=mod.per_channel if mod else True,
             discretize_res=mod.discretize_res if mod else -1.0, seed=mod.seed if mod else 0,
-            offset=mod.offset if mod else 0, need_fwd=True, need_bwd=any(ctx.needs_input_grad[:1]) or True)
+            offset=mod.offset if mod else 0, step_dev=mod.step if mod else None, need_fwd=True, need_bwd=any(ctx.needs_input_grad[:1]) or True)
 
-        noise_t, noise_std, seed, offset = None, 0.0, 0, 0
+        noise_t, noise_std, seed, offset, step_dev = None, 0.0, 0, 0, None
         if isinstance(out_noise, PhiloxNoise):
             ext = CVMMExt(**{**ext.__dict__, "noise": out_noise})
         elif out_noise is not None:
             noise_t = out_noise
         if ext.noise is not None and ext.noise.std > 0:
-            noise_std, seed, offset = ext.noise.std, ext.noise.seed, ext.noise.offset
+            noise_std, seed, offset, step_dev = ext.noise.std, ext.noise.seed, ext.noise.offset, ext.noise.step
 
         dst = sel_index_i if out_index_i is None else out_index_i
         adc_on = ext.out_res > 0 and ext.out_bound > 0
         res, codes = ops.cvmm_fwd(
             x2, sel_index_i, dst, offsets, pw, precision, P=P, dst_rows=P, ir=ir, absmax=absmax,
-            inp_res=float(inp_res), noise=noise_t, noise_std=noise_std, seed=seed, offset=offset,
+            inp_res=float(inp_res), noise=noise_t, noise_std=noise_std, seed=seed, offset=offset, step_dev=step_dev,
             out_res=ext.out_res if adc_on else -1.0, out_bound=ext.out_bound if adc_on else -1.0,
             want_codes=adc_on and ext.save_codes, status=status)
         if ext.save_codes:

@@ -13,7 +13,7 @@ struct EpiParams {
   int n_out;            // output columns
   int vec4;             // n_out % 4 == 0 and every per-column / per-row array is 16-byte aligned
   // forward
-  const float* noise; float noise_std; uint64_t seed; uint32_t offset;
+  const float* noise; float noise_std; uint64_t seed; uint32_t offset; const long long* step_dev;
   const float* col_scale;      // [E, n_out]
   const float* col_inv_scale;  // [E, n_out], needed by the ADC
   AdcParams adc;
@@ -39,6 +39,7 @@ struct RowCtx {
   int64_t xrow;
   float dir_acc;
   unsigned keep;
+  uint32_t noise_offset;   // Philox offset in effect (argument + 8 * device step counter)
 };
 
 __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, int e, bool in_range) {
@@ -46,6 +47,8 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   c.valid = in_range;
   c.e = e;
   c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0;
+  c.noise_offset = p.offset;
+  if (p.noise_std > 0.f && p.step_dev) c.noise_offset += static_cast<uint32_t>(*p.step_dev) * 8u;
   if (!in_range) return c;
   c.dst = p.dst_row[i];
   if (c.dst < 0 || c.dst >= p.dst_rows) {
@@ -95,7 +98,7 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
     if (p.adc.on) load4(p.col_inv_scale, cidx, n0, p.n_out, vec, is, 0.f);
     if (p.noise) load4(p.noise, c.dst * p.n_out + n0, n0, p.n_out, vec, nz, 0.f);
     if (p.noise_std > 0.f) {
-      const float4 zz = philox_normal4(p.seed, p.offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
+      const float4 zz = philox_normal4(p.seed, c.noise_offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
                                        static_cast<uint32_t>(n0 >> 2));
       nz[0] += (p.noise_std * s[0]) * zz.x;
       nz[1] += (p.noise_std * s[1]) * zz.y;

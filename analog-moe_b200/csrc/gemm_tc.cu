@@ -39,9 +39,9 @@ constexpr int kBM = 128;          // rows per tile (UMMA M)
 constexpr int kBK = 64;           // bf16 elements per stage along the contraction (128 bytes)
 // forward / dX kernel geometry: 2 control warps + 16 worker warps whose split between epilogue and
 // prologue is chosen per launch (4, 8 or 12 epilogue warps)
-constexpr int kWorkerWarps = 16;
-constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 576
-constexpr int kMaxEpiGroups = 3;
+constexpr int kWorkerWarps = 30;
+constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 1024
+constexpr int kMaxEpiGroups = 6;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATile = kBM * kBK * 2;  // 16 KiB
 
@@ -53,7 +53,8 @@ __device__ __forceinline__ uint32_t bar_tfull(uint32_t bars, int b) { return bar
 __device__ __forceinline__ uint32_t bar_tempty(uint32_t bars, int b) { return bars + 8u * (3 * kMaxStages + 2 + b); }
 // warp-group rendezvous points (bounded, unlike bar.sync): prologue warps x2, epilogue warps x2
 __device__ __forceinline__ uint32_t bar_group(uint32_t bars, int i) { return bars + 8u * (3 * kMaxStages + 4 + i); }
-constexpr int kNumBars = 3 * kMaxStages + 8;
+constexpr int kMaxProdGroups = 1;
+constexpr int kNumBars = 3 * kMaxStages + 4 + 2 * kMaxProdGroups + 2;
 
 struct TileIter {
   const int32_t* off; int E; int e; int64_t before;
@@ -78,6 +79,7 @@ struct TileIter {
 struct TcParams {
   int E, Kc, Nout;
   int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
+  int prod_groups;   // the prologue warps form this many groups; group g fills stages g, g+groups, ...
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
@@ -143,21 +145,22 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
 }
 
 // Eight values -> one 16-byte chunk of bf16 (and a second chunk with the rounding residuals).
-__device__ __forceinline__ void store8_rt(uint8_t* tile_hi, uint8_t* tile_lo, uint32_t off, const float v[8], bool split) {
+// tile_hi / tile_lo are shared-memory addresses.
+__device__ __forceinline__ void store8_rt(uint32_t tile_hi, uint32_t tile_lo, uint32_t off, const float v[8], bool split) {
   uint32_t h[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) h[i] = cvt_bf16x2(v[2 * i], v[2 * i + 1]);
-  *reinterpret_cast<uint4*>(tile_hi + off) = make_uint4(h[0], h[1], h[2], h[3]);
+  sts128(tile_hi + off, h[0], h[1], h[2], h[3]);
   if (split) {
     uint32_t l[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       l[i] = cvt_bf16x2(v[2 * i] - __uint_as_float(h[i] << 16), v[2 * i + 1] - __uint_as_float(h[i] & 0xffff0000u));
-    *reinterpret_cast<uint4*>(tile_lo + off) = make_uint4(l[0], l[1], l[2], l[3]);
+    sts128(tile_lo + off, l[0], l[1], l[2], l[3]);
   }
 }
 template <bool SPLIT>
-__device__ __forceinline__ void store8(uint8_t* tile_hi, uint8_t* tile_lo, uint32_t off, const float v[8]) {
+__device__ __forceinline__ void store8(uint32_t tile_hi, uint32_t tile_lo, uint32_t off, const float v[8]) {
   store8_rt(tile_hi, tile_lo, off, v, SPLIT);
 }
 
@@ -195,10 +198,9 @@ __device__ __forceinline__ void setup_cta(const SmemView& s, int stages, uint32_
       mbar_init(bar_tfull(s.bars, b), 1);
       mbar_init(bar_tempty(s.bars, b), tempty_count);
     }
-    mbar_init(bar_group(s.bars, 0), prod_warps);
-    mbar_init(bar_group(s.bars, 1), prod_warps);
-    mbar_init(bar_group(s.bars, 2), epi_warps);
-    mbar_init(bar_group(s.bars, 3), epi_warps);
+    for (int g = 0; g < 2 * kMaxProdGroups; ++g) mbar_init(bar_group(s.bars, g), prod_warps);
+    mbar_init(bar_group(s.bars, 2 * kMaxProdGroups), epi_warps);
+    mbar_init(bar_group(s.bars, 2 * kMaxProdGroups + 1), epi_warps);
     *s.abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -243,9 +245,8 @@ __device__ __forceinline__ bool group_sync(uint32_t bar, uint32_t round, volatil
 
 // Per-row operand-prologue parameters, staged in shared memory once per tile.
 struct __align__(16) RowMeta {
-  long long src_off;   // element offset of the source row, or -1 if the row is not to be read
+  int src;             // source row, or -1 if the row is not to be read
   float ir, am, fast;
-  float pad;
 };
 
 // ---- epilogue of one 16-column chunk, fast families (everything 16-byte aligned, n_out % 4 == 0,
@@ -276,7 +277,7 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
     float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
     if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
     if (adc) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
-    if (noise) z = philox_normal4_inline(p.seed, p.offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
+    if (noise) z = philox_normal4_inline(p.seed, c.noise_offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
                                          static_cast<uint32_t>((n0 >> 2) + qd));
     const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w}, zv[4] = {z.x, z.y, z.z, z.w};
 #pragma unroll
@@ -335,13 +336,14 @@ template <int DAC, bool A_F32, int EPI>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ RowMeta s_meta[kBM];
+  __shared__ RowMeta s_meta[kMaxProdGroups][kBM];
   __shared__ float s_dir[kMaxEpiGroups][kBM];
   __shared__ unsigned s_keep[kMaxEpiGroups][kBM];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_prod = kWorkerWarps - p.n_epi;
-  setup_cta(sm, p.stages, p.tmem_cols, n_prod, p.n_epi, n_prod, p.n_epi);
+  const int wpg = n_prod / p.prod_groups;   // prologue warps per group
+  setup_cta(sm, p.stages, p.tmem_cols, wpg, p.n_epi, wpg, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
 
@@ -360,7 +362,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
             const int s = it % p.stages;
             const uint32_t ph = (it / p.stages) & 1u;
-            if (!mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 1)) { alive = false; break; }
+            if (!mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 1, 64)) { alive = false; break; }
             const uint32_t dst = sm.base_u32 + s * p.stage_bytes + p.a_bytes;
             mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (p.b_split ? 2u : 1u));
             tma_load_3d(dst, &tmap_hi, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
@@ -451,7 +453,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           __syncwarp();
         }
         if (ew == 0 && lane == 0) TL(3, acc_it, 0);
-        bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 5);
+        bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 5, 128);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         if (ew == 0 && lane == 0) TL(3, acc_it, 1);
@@ -488,7 +490,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         if (groups > 1) {
           s_dir[grp][r] = ctx.dir_acc;
           s_keep[grp][r] = ctx.valid ? ctx.keep : 0u;
-          if (!group_sync(bar_group(sm.bars, 2), sync_round, sm.abort_flag, status, 7)) { alive = false; break; }
+          if (!group_sync(bar_group(sm.bars, 2 * kMaxProdGroups), sync_round, sm.abort_flag, status, 7)) { alive = false; break; }
           if (grp == 0) {
             float d = s_dir[0][r];
             unsigned kc = s_keep[0][r];
@@ -496,7 +498,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             ctx.dir_acc = d;
             ctx.keep = kc;
           }
-          if (!group_sync(bar_group(sm.bars, 3), sync_round, sm.abort_flag, status, 8)) { alive = false; break; }
+          if (!group_sync(bar_group(sm.bars, 2 * kMaxProdGroups + 1), sync_round, sm.abort_flag, status, 8)) { alive = false; break; }
           ++sync_round;
         }
         if (grp == 0) {
@@ -512,8 +514,14 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- operand prologue (A tiles)
-    const int np = n_prod * 32;
-    const int pt = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np-1
+    // The prologue warps form groups; group g fills ring stages g, g+G, g+2G, ... on its own, so
+    // that the global-load latency of G stages overlaps.
+    const int pw = warp - 2 - p.n_epi;
+    const int grp = pw / wpg;
+    const int np = wpg * 32;
+    const int pt = (pw - grp * wpg) * 32 + lane;      // thread index inside the group
+    const int G = p.prod_groups;
+    RowMeta* meta = s_meta[grp];
     const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
     const bool a_split = p.a_split != 0;
     TileIter ti(p.offsets, p.E);
@@ -522,29 +530,34 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
       int e, row0, rows;
       if (!ti.get(t, e, row0, rows)) break;
-      // everyone is done with the previous tile's metadata
-      if (!group_sync(bar_group(sm.bars, 0), sync_round, sm.abort_flag, status, 9)) break;
+      // does this group own a stage of this tile at all?
+      const uint32_t n_it = static_cast<uint32_t>(p.n_tiles * p.k_chunks);
+      const uint32_t first = (G - it % G + grp) % G;   // offset of the first owned stage
+      if (first >= n_it) { it += n_it; continue; }
+      // the group is done with the previous tile's metadata
+      if (!group_sync(bar_group(sm.bars, 2 * grp), sync_round, sm.abort_flag, status, 9)) break;
       for (int r = pt; r < kBM; r += np) {
         RowMeta m;
-        m.src_off = -1; m.ir = 1.f; m.am = 1.f; m.fast = 1.f; m.pad = 0.f;
+        m.src = -1; m.ir = 1.f; m.am = 1.f; m.fast = 1.f;
         if (r < rows) {
           const int64_t i = static_cast<int64_t>(row0) + r;
           const int64_t src = p.a_row[i] / p.a_div;
           if (src < 0 || src >= p.a_rows) {
             report(status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(i), static_cast<int>(src));
           } else {
-            m.src_off = src * p.a_stride;
+            m.src = static_cast<int>(src);
             if (has_ir) m.ir = p.ir[i];
             if (has_am) m.am = p.a_absmax[src];
             if (DAC == kDacQuant) m.fast = dac_fast_mul(has_ir, m.ir, has_am, m.am, p.inp_res);
           }
         }
-        s_meta[r] = m;
+        meta[r] = m;
       }
-      if (!group_sync(bar_group(sm.bars, 1), sync_round, sm.abort_flag, status, 10)) break;
+      if (!group_sync(bar_group(sm.bars, 2 * grp + 1), sync_round, sm.abort_flag, status, 10)) break;
       ++sync_round;
       for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
+          if (static_cast<int>(it % G) != grp) continue;
           const int s = it % p.stages;
           const uint32_t ph = (it / p.stages) & 1u;
           if (pt == 0) TL(2, it, 0);
@@ -552,8 +565,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
           if (pt == 0) TL(2, it, 1);
-          uint8_t* a_hi = sm.base + s * p.stage_bytes;
-          uint8_t* a_lo = a_hi + kATile;
+          const uint32_t a_hi = sm.base_u32 + s * p.stage_bytes;
+          const uint32_t a_lo = a_hi + kATile;
           const bool full_k = (kc + 1) * kBK <= p.Kc && p.vec_ok;
           // 1024 tasks (128 rows x 8 sixteen-byte chunks), two per thread and round
 #pragma unroll 1
@@ -563,15 +576,16 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
-              m[b].src_off = -1;
-              if (task < kBM * 8) m[b] = s_meta[task >> 3];
+              m[b].src = -1;
+              if (task < kBM * 8) m[b] = meta[task >> 3];
               const int k = kc * kBK + (task & 7) * 8;
-              if (m[b].src_off >= 0 && full_k) {
-                load8_fast<A_F32>(p.a, m[b].src_off, k, v[b]);
-              } else if (m[b].src_off >= 0 && k < p.Kc) {
-                load8_slow(p.a, p.a_dtype, m[b].src_off, k, p.Kc, v[b]);
+              const int64_t off = static_cast<int64_t>(m[b].src) * p.a_stride;
+              if (m[b].src >= 0 && full_k) {
+                load8_fast<A_F32>(p.a, off, k, v[b]);
+              } else if (m[b].src >= 0 && k < p.Kc) {
+                load8_slow(p.a, p.a_dtype, off, k, p.Kc, v[b]);
               } else {
-                m[b].src_off = -1;
+                m[b].src = -1;
 #pragma unroll
                 for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
               }
@@ -580,9 +594,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
               if (task < kBM * 8) {
-                if (DAC == kDacQuant && m[b].src_off >= 0) {
+                if (DAC == kDacQuant && m[b].src >= 0) {
                   dac_code8(v[b], has_ir, m[b].ir, has_am, m[b].am, p.inp_res, m[b].fast);
-                } else if (DAC == kDacNorm && m[b].src_off >= 0) {
+                } else if (DAC == kDacNorm && m[b].src >= 0) {
 #pragma unroll
                   for (int x = 0; x < 8; ++x) v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, has_am, m[b].am);
                 }
@@ -592,9 +606,11 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           }
           if (pt == 0) TL(2, it, 2);
           fence_proxy_async();
+          if (pt == 0) TL(0, it, 0);
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
           if (pt == 0) TL(2, it, 3);
+          if (pt == np - 1) TL(0, it, 1);
         }
       }
     }
@@ -620,10 +636,11 @@ struct DwMnParams {
 };
 
 constexpr int kDwProdWarps = 12;
+constexpr int kDwThreads = (6 + kDwProdWarps) * 32;   // 2 control + 4 epilogue + 12 prologue warps
 constexpr uint32_t kMnBlock = kBK * 128;   // 64 rows x 128 bytes
 
 template <bool SPLIT>
-__global__ void __launch_bounds__(kFwdThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
+__global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -692,7 +709,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) dw_tc_mn_kernel(DwMnParams p) 
       }
       const int buf = acc_it & 1u;
       const uint32_t aph = (acc_it >> 1) & 1u;
-      bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 15);
+      bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 15, 128);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
@@ -740,7 +757,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) dw_tc_mn_kernel(DwMnParams p) 
         bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 16);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
-        uint8_t* stage = sm.base + s * p.stage_bytes;
+        const uint32_t stage = sm.base_u32 + s * p.stage_bytes;
         const int i0 = beg + kc * kBK;
         for (int base = pt; base < tasks; base += np * 3) {
           float v[3][8];
@@ -793,8 +810,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) dw_tc_mn_kernel(DwMnParams p) 
 #pragma unroll
           for (int b = 0; b < 3; ++b) {
             if (where[b] >= 0) {
-              uint8_t* hi = stage + (isb[b] ? a_total : 0u);
-              uint8_t* lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
+              const uint32_t hi = stage + (isb[b] ? a_total : 0u);
+              const uint32_t lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
               store8<SPLIT>(hi, lo, static_cast<uint32_t>(where[b]), v[b]);
             }
           }
@@ -902,10 +919,13 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
     double best = 1e300;
-    for (int ne = 4; ne <= 12; ne += 4) {
+    for (int ne = 4; ne <= 24; ne += 4) {
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
+  }
+  {
+    p.prod_groups = 1;
   }
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
@@ -995,10 +1015,10 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
   if (split) {
     AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_mn_kernel<true><<<grid, kFwdThreads, smem, stream>>>(p);
+    dw_tc_mn_kernel<true><<<grid, kDwThreads, smem, stream>>>(p);
   } else {
     AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_mn_kernel<false><<<grid, kFwdThreads, smem, stream>>>(p);
+    dw_tc_mn_kernel<false><<<grid, kDwThreads, smem, stream>>>(p);
   }
   AMOE_LAUNCH_CHECK("dw_tc");
   return AMOE_OK;

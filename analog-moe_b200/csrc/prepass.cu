@@ -54,7 +54,7 @@ struct PrepassDev {
   const void* w; int dtype; int E, K, N; int64_t se, sk, sn;
   const float* colmax; const float* expmax;
   int noise_per_channel; float noise_std; float n_states;  // n_states<=0: no discretisation
-  uint64_t seed; uint32_t offset;
+  uint64_t seed; uint32_t offset; const long long* step_dev;
   float* w_out;
   __nv_bfloat16 *fwd_hi, *fwd_lo, *bwd_hi, *bwd_lo;
   int Npad, Kpad, Kpad2, Npad2;
@@ -75,7 +75,8 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
     if (k < p.K && n < p.N) {
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (p.noise_std > 0.f) {
-        float4 zz = philox_normal4(p.seed, p.offset, kStreamWeightNoise, static_cast<uint32_t>(e * p.K + k),
+        const uint32_t off = p.offset + (p.step_dev ? static_cast<uint32_t>(*p.step_dev) * 8u : 0u);
+        float4 zz = philox_normal4(p.seed, off, kStreamWeightNoise, static_cast<uint32_t>(e * p.K + k),
                                    static_cast<uint32_t>(n >> 2));
         z[0] = zz.x; z[1] = zz.y; z[2] = zz.z; z[3] = zz.w;
       }
@@ -200,7 +201,7 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
     p.colmax = colmax; p.expmax = expmax;
     p.noise_per_channel = a->noise_per_channel; p.noise_std = a->noise_std;
     p.n_states = a->discretize_res > 0.f ? fmaxf(a->discretize_res, 1.0f / a->discretize_res) : -1.f;
-    p.seed = a->seed; p.offset = a->offset;
+    p.seed = a->seed; p.offset = a->offset; p.step_dev = a->step_dev;
     p.w_out = a->w_out;
     p.fwd_hi = reinterpret_cast<__nv_bfloat16*>(a->fwd_hi); p.fwd_lo = reinterpret_cast<__nv_bfloat16*>(a->fwd_lo);
     p.bwd_hi = reinterpret_cast<__nv_bfloat16*>(a->bwd_hi); p.bwd_lo = reinterpret_cast<__nv_bfloat16*>(a->bwd_lo);

@@ -46,13 +46,16 @@ __device__ __forceinline__ void fence_proxy_async() {
 // Bounded wait: gives up after ~2 s of GPU clock (or as soon as another thread of the CTA gave
 // up), records where, and lets the caller unwind.  A healthy pipeline never gets near the limit.
 constexpr long long kWaitLimitCycles = 4000000000LL;
+// `backoff_ns` > 0 makes the waiter sleep between polls (for long, non-critical waits, so that it does
+// not compete for issue slots with the warps that are doing the work).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int where) {
+                                          int where, unsigned backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -160,6 +163,11 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, 
   d |= static_cast<uint64_t>(1) << 46;                              // descriptor version (sm_100)
   d |= static_cast<uint64_t>(2) << 61;                              // SWIZZLE_128B
   return d;
+}
+
+// 16-byte store to a shared-memory address (st.shared instead of a generic store).
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 // Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a swizzled tile.

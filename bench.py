@@ -170,6 +170,42 @@ def run_ours(args, cfg, rank, world, device):
     for i in range(args.warmup):
         step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
     barrier()
+    # One CUDA graph per input set (whole step: routing, both projections, backward).  The Philox
+    # offsets come from a device counter that the graph itself advances, so replays draw new noise.
+    # Expert-parallel runs stay eager: the exchange plan needs one host read per step.
+    graphs, ys, launches_per_step = None, None, None
+    if args.graph and world == 1:
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step(layer, xs[0], gys[0], bwd)
+            torch.cuda.current_stream().wait_stream(side)
+            pool = torch.cuda.graph_pool_handle()
+            graphs, ys = [], []
+            for i in range(n_sets):
+                g = torch.cuda.CUDAGraph()
+                ops.TRACE = ops.Trace(timed=False)
+                with torch.cuda.graph(g, pool=pool):
+                    ys.append(step(layer, xs[i], gys[i], bwd))
+                launches_per_step = ops.TRACE.launches
+                ops.TRACE = None
+                graphs.append(g)
+            for g in graphs[:3]:
+                g.replay()
+        except Exception as exc:          # capture not possible: measure eagerly and say so
+            print(f"bench: CUDA graph capture failed ({exc!r}); running eagerly", file=sys.stderr)
+            graphs = None
+            ops.TRACE = None
+            torch.cuda.synchronize()
+
+    def run_step(i):
+        if graphs is not None:
+            graphs[i % n_sets].replay()
+            return ys[i % n_sets]
+        return step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+
+    barrier()
     sampler = ClockSampler(device.index or 0)
     sampler.start()
     ops.TRACE = ops.Trace(timed=False)
@@ -177,18 +213,21 @@ def run_ours(args, cfg, rank, world, device):
     barrier()
     e0.record()
     for i in range(args.steps):
-        step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+        run_step(i)
     e1.record()
     barrier()
     sampler.stop_flag = True
-    launches = ops.TRACE.launches
+    launches = ops.TRACE.launches if graphs is None else launches_per_step * args.steps
     ops.TRACE = None
     ms = e0.elapsed_time(e1)
     t_dev = torch.tensor([ms], device=device)
 
     # ---------------- end to end: pinned host inputs in, results out, every step
-    x_d = torch.empty_like(xs[0]).requires_grad_(bwd)
-    gy_d = torch.empty_like(gys[0])
+    if graphs is not None:
+        x_d, gy_d = xs[0], gys[0]                     # the static buffers of graph 0
+    else:
+        x_d = torch.empty_like(xs[0]).requires_grad_(bwd)
+        gy_d = torch.empty_like(gys[0])
     y_h = torch.empty(xs_h[0].shape, dtype=dtype).pin_memory()
     dx_h = torch.empty(xs_h[0].shape, dtype=dtype).pin_memory()
 
@@ -197,7 +236,11 @@ def run_ours(args, cfg, rank, world, device):
             x_d.copy_(xs_h[i % n_sets], non_blocking=True)
             if bwd:
                 gy_d.copy_(gys_h[i % n_sets], non_blocking=True)
-        y = step(layer, x_d, gy_d, bwd)
+        if graphs is not None:
+            graphs[0].replay()
+            y = ys[0]
+        else:
+            y = step(layer, x_d, gy_d, bwd)
         y_h.copy_(y.detach(), non_blocking=True)
         if bwd:
             dx_h.copy_(x_d.grad, non_blocking=True)
@@ -231,6 +274,7 @@ def run_ours(args, cfg, rank, world, device):
     summ = ops.TRACE.summary()
     ops.TRACE = None
     return dict(ms=ms, ms_e2e=ms_e2e, k_e2e=k_e2e, launches=launches, h2d=h2d, d2h=d2h, kernels=summ,
+                graph=graphs is not None,
                 clocks=sampler.result(), dtype=dtype, precision=layer._precision(xs[0]))
 
 
@@ -270,6 +314,8 @@ def main():
     ap.add_argument("--precision", default=None, help="split | bf16x1 | fp32 (default: split for fp32, bf16x1 for bf16)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="launch every step eagerly instead of replaying a CUDA graph of the step")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", 0))
@@ -333,6 +379,7 @@ def main():
                     gpu_launches=r["launches"], roofline=roof, clocks=r["clocks"],
                     kernels={k_: round(v["ms_avg"] * 1e3, 1) for k_, v in sorted(kern.items())})
         line["config"]["l2"] = "inputs rotate over 8 buffer sets (> 126 MB L2) and one step touches > 400 MB"
+        line["config"]["cuda_graph"] = r["graph"]
         line["config"]["precision"] = {0: "bf16x1", 1: "split (bf16 hi+lo, fp32 accumulate)", 2: "fp32 CUDA cores"}[r["precision"]]
         if world == 1 and not args.no_cpu_baseline:
             c = run_cpu(cfg, 1, 1, args.cpu_sample_tokens)

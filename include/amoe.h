@@ -103,6 +103,7 @@ typedef struct amoe_weight_prepass_args {
   int32_t noise_per_channel;      /* scale of the noise: per column (1) or per expert (0) maximum */
   float discretize_res;           /* <=0: off; else n_states = max(res, 1/res) */
   uint64_t seed; uint32_t offset;
+  const long long* step_dev;      /* optional device counter: the Philox offset used is offset + 8 * (*step_dev) */
   float* col_scale;               /* [E,N] */
   float* col_inv_scale;           /* [E,N] correctly rounded 1/col_scale (0 where col_scale is 0), or NULL */
   float* w_out;                   /* [E,K,N] fp32 or NULL */
@@ -164,6 +165,8 @@ typedef struct amoe_cvmm_args {
   const float* noise;             /* [dst_rows,N] fp32 by destination row, or NULL */
   float noise_std;                /* >0: Philox noise noise_std*col_scale[e,n]*z */
   uint64_t seed; uint32_t offset;
+  const long long* step_dev;      /* optional device counter: the Philox offset used is offset + 8 * (*step_dev),
+                                     so a captured CUDA graph draws fresh noise on every replay */
   const float* col_scale;         /* [E,N] (needed for Philox noise and ADC) */
   const float* col_inv_scale;     /* [E,N] from the weight pre-pass (needed for the ADC) */
   /* ADC */
