@@ -169,9 +169,9 @@ __global__ void ep_pack_kernel(const T* __restrict__ x, int64_t stride, int K, c
   const T* row = x + static_cast<int64_t>(src_row[i]) * stride;
   if (send_codes) {
     const float r = ir[i];
-    const float fast = dac_fast_mul(true, r, false, 1.f, inp_res);
+    const float rr = __frcp_rn(r), rcp_res = quant_rcp(inp_res);
     for (int k = lane; k < K; k += 32) {
-      float c = dac_code(to_f32<T>(row[k]), true, r, false, 1.f, inp_res, fast);
+      float c = dac_code(to_f32<T>(row[k]), true, r, rr, false, 1.f, 1.f, inp_res, rcp_res);
       send_codes[i * K + k] = static_cast<int8_t>(c);
     }
     if (lane == 0) send_scale[i] = r;

@@ -38,7 +38,8 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
   const int64_t li = static_cast<int64_t>(row0) + lr;
   bool l_ok = lr < rows;
   int64_t l_src = 0;
-  float l_ir = 1.f, l_am = 1.f, l_fast = 1.f;
+  float l_ir = 1.f, l_am = 1.f, l_rir = 1.f, l_ram = 1.f;
+  const float rcp_res = quant_rcp(p.inp_res);
   const bool has_ir = p.dac && p.ir != nullptr, has_am = p.dac && p.a_absmax != nullptr;
   const bool quant = p.dac && p.inp_res > 0.f;
   if (l_ok) {
@@ -47,9 +48,8 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
       report(p.epi.status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(li), static_cast<int>(l_src));
       l_ok = false;
     } else {
-      if (has_ir) l_ir = p.ir[li];
-      if (has_am) l_am = p.a_absmax[l_src];
-      if (quant) l_fast = dac_fast_mul(has_ir, l_ir, has_am, l_am, p.inp_res);
+      if (has_ir) { l_ir = p.ir[li]; l_rir = __frcp_rn(l_ir); }
+      if (has_am) { l_am = p.a_absmax[l_src]; l_ram = __frcp_rn(l_am); }
     }
   }
   // B-load role
@@ -75,9 +75,9 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
           v = load_elem(p.a, p.a_dtype, l_src * p.a_stride + k);
           if (p.dac) {
             if (quant)
-              v = dac_code(v, has_ir, l_ir, has_am, l_am, p.inp_res, l_fast) * p.inp_res;
+              v = dac_code(v, has_ir, l_ir, l_rir, has_am, l_am, l_ram, p.inp_res, rcp_res) * p.inp_res;
             else
-              v = dac_normalise(v, has_ir, l_ir, has_am, l_am);
+              v = dac_normalise(v, has_ir, l_ir, l_rir, has_am, l_am, l_ram);
           }
         }
         As[lk + j][lr] = v;

@@ -56,6 +56,13 @@ __device__ __forceinline__ uint32_t bar_group(uint32_t bars, int i) { return bar
 constexpr int kMaxProdGroups = 1;
 constexpr int kNumBars = 3 * kMaxStages + 4 + 2 * kMaxProdGroups + 2;
 
+// Position in the ring of stages, advanced without integer division.
+struct RingPos {
+  int s; uint32_t ph; int stages;
+  __device__ explicit RingPos(int n) : s(0), ph(0), stages(n) {}
+  __device__ __forceinline__ void next() { if (++s == stages) { s = 0; ph ^= 1u; } }
+};
+
 struct TileIter {
   const int32_t* off; int E; int e; int64_t before;
   __device__ TileIter(const int32_t* o, int E_) : off(o), E(E_), e(0), before(0) {}
@@ -79,7 +86,6 @@ struct TileIter {
 struct TcParams {
   int E, Kc, Nout;
   int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
-  int prod_groups;   // the prologue warps form this many groups; group g fills stages g, g+groups, ...
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
@@ -246,7 +252,8 @@ __device__ __forceinline__ bool group_sync(uint32_t bar, uint32_t round, volatil
 // Per-row operand-prologue parameters, staged in shared memory once per tile.
 struct __align__(16) RowMeta {
   int src;             // source row, or -1 if the row is not to be read
-  float ir, am, fast;
+  float ir, rcp_ir;    // input range and its correctly rounded reciprocal
+  float am;            // abs-max divisor (its reciprocal is recomputed where it is used: rare mode)
 };
 
 // ---- epilogue of one 16-column chunk, fast families (everything 16-byte aligned, n_out % 4 == 0,
@@ -342,8 +349,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_prod = kWorkerWarps - p.n_epi;
-  const int wpg = n_prod / p.prod_groups;   // prologue warps per group
-  setup_cta(sm, p.stages, p.tmem_cols, wpg, p.n_epi, wpg, p.n_epi);
+  setup_cta(sm, p.stages, p.tmem_cols, n_prod, p.n_epi, n_prod, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
 
@@ -353,15 +359,15 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       tma_prefetch_desc(&tmap_hi);
       if (p.b_split) tma_prefetch_desc(&tmap_lo);
       TileIter ti(p.offsets, p.E);
-      uint32_t it = 0;
+      RingPos rp(p.stages);
       bool alive = true;
       for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
         int e, row0, rows;
         if (!ti.get(t, e, row0, rows)) break;
         for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
-          for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
-            const int s = it % p.stages;
-            const uint32_t ph = (it / p.stages) & 1u;
+          for (int kc = 0; kc < p.k_chunks; ++kc, rp.next()) {
+            const int s = rp.s;
+            const uint32_t ph = rp.ph;
             if (!mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 1, 64)) { alive = false; break; }
             const uint32_t dst = sm.base_u32 + s * p.stage_bytes + p.a_bytes;
             mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (p.b_split ? 2u : 1u));
@@ -376,6 +382,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16(kBM, p.BN);
       TileIter ti(p.offsets, p.E);
+      RingPos rp(p.stages);
       uint32_t it = 0, acc_it = 0;
       bool alive = true;
       for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
@@ -387,9 +394,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 2)) { alive = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
-          for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
-            const int s = it % p.stages;
-            const uint32_t ph = (it / p.stages) & 1u;
+          for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
+            const int s = rp.s;
+            const uint32_t ph = rp.ph;
             TL(1, it, 0);
             if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
             TL(1, it, 1);
@@ -514,31 +521,24 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- operand prologue (A tiles)
-    // The prologue warps form groups; group g fills ring stages g, g+G, g+2G, ... on its own, so
-    // that the global-load latency of G stages overlaps.
-    const int pw = warp - 2 - p.n_epi;
-    const int grp = pw / wpg;
-    const int np = wpg * 32;
-    const int pt = (pw - grp * wpg) * 32 + lane;      // thread index inside the group
-    const int G = p.prod_groups;
-    RowMeta* meta = s_meta[grp];
+    const int np = n_prod * 32;
+    const int pt = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np-1
     const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
     const bool a_split = p.a_split != 0;
+    const float rcp_res = quant_rcp(p.inp_res);
+    RowMeta* meta = s_meta[0];
     TileIter ti(p.offsets, p.E);
+    RingPos rp(p.stages);
     uint32_t it = 0, sync_round = 0;
     bool alive = true;
     for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
       int e, row0, rows;
       if (!ti.get(t, e, row0, rows)) break;
-      // does this group own a stage of this tile at all?
-      const uint32_t n_it = static_cast<uint32_t>(p.n_tiles * p.k_chunks);
-      const uint32_t first = (G - it % G + grp) % G;   // offset of the first owned stage
-      if (first >= n_it) { it += n_it; continue; }
-      // the group is done with the previous tile's metadata
-      if (!group_sync(bar_group(sm.bars, 2 * grp), sync_round, sm.abort_flag, status, 9)) break;
+      // everyone is done with the previous tile's metadata
+      if (!group_sync(bar_group(sm.bars, 0), sync_round, sm.abort_flag, status, 9)) break;
       for (int r = pt; r < kBM; r += np) {
         RowMeta m;
-        m.src = -1; m.ir = 1.f; m.am = 1.f; m.fast = 1.f;
+        m.src = -1; m.ir = 1.f; m.rcp_ir = 1.f; m.am = 1.f;
         if (r < rows) {
           const int64_t i = static_cast<int64_t>(row0) + r;
           const int64_t src = p.a_row[i] / p.a_div;
@@ -546,22 +546,19 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             report(status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(i), static_cast<int>(src));
           } else {
             m.src = static_cast<int>(src);
-            if (has_ir) m.ir = p.ir[i];
+            if (has_ir) { m.ir = p.ir[i]; m.rcp_ir = __frcp_rn(m.ir); }
             if (has_am) m.am = p.a_absmax[src];
-            if (DAC == kDacQuant) m.fast = dac_fast_mul(has_ir, m.ir, has_am, m.am, p.inp_res);
           }
         }
         meta[r] = m;
       }
-      if (!group_sync(bar_group(sm.bars, 2 * grp + 1), sync_round, sm.abort_flag, status, 10)) break;
+      if (!group_sync(bar_group(sm.bars, 1), sync_round, sm.abort_flag, status, 10)) break;
       ++sync_round;
       for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
-        for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
-          if (static_cast<int>(it % G) != grp) continue;
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
+        for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
+          const int s = rp.s;
           if (pt == 0) TL(2, it, 0);
-          bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 6);
+          bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 6);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
           if (pt == 0) TL(2, it, 1);
@@ -594,11 +591,15 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
               if (task < kBM * 8) {
-                if (DAC == kDacQuant && m[b].src >= 0) {
-                  dac_code8(v[b], has_ir, m[b].ir, has_am, m[b].am, p.inp_res, m[b].fast);
-                } else if (DAC == kDacNorm && m[b].src >= 0) {
+                if (DAC != kDacNone && m[b].src >= 0) {
+                  const float rcp_am = has_am ? __frcp_rn(m[b].am) : 1.f;
 #pragma unroll
-                  for (int x = 0; x < 8; ++x) v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, has_am, m[b].am);
+                  for (int x = 0; x < 8; ++x) {
+                    if (DAC == kDacQuant)
+                      v[b][x] = dac_code(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am, p.inp_res, rcp_res);
+                    else
+                      v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am);
+                  }
                 }
                 store8_rt(a_hi, a_lo, sw128_offset(task >> 3, task & 7), v[b], a_split);
               }
@@ -606,11 +607,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           }
           if (pt == 0) TL(2, it, 2);
           fence_proxy_async();
-          if (pt == 0) TL(0, it, 0);
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
           if (pt == 0) TL(2, it, 3);
-          if (pt == np - 1) TL(0, it, 1);
         }
       }
     }
@@ -653,7 +652,8 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
-      uint32_t it = 0, acc_it = 0;
+      RingPos rp(p.stages);
+      uint32_t acc_it = 0;
       bool alive = true;
       for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
         const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
@@ -664,9 +664,9 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
         if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 12)) { alive = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
-        for (int kc = 0; kc < chunks; ++kc, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1u;
+        for (int kc = 0; kc < chunks; ++kc, rp.next()) {
+          const int s = rp.s;
+          const uint32_t ph = rp.ph;
           if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 13)) { alive = false; break; }
           tc_fence_after();
           const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
@@ -743,7 +743,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
     const int b_chunks = (p.BN + 7) / 8;
     const int a_tasks = kBK * a_chunks;                  // 1024
     const int tasks = a_tasks + kBK * b_chunks;
-    uint32_t it = 0;
+    RingPos rp(p.stages);
     bool alive = true;
     for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
       const int nt = static_cast<int>(w % p.n_tiles);
@@ -751,9 +751,9 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
       const int beg = p.offsets[e], end = p.offsets[e + 1];
       const int chunks = (end - beg + kBK - 1) / kBK;
-      for (int kc = 0; kc < chunks; ++kc, ++it) {
-        const int s = it % p.stages;
-        const uint32_t ph = (it / p.stages) & 1u;
+      for (int kc = 0; kc < chunks; ++kc, rp.next()) {
+        const int s = rp.s;
+        const uint32_t ph = rp.ph;
         bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 16);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
@@ -923,9 +923,6 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
-  }
-  {
-    p.prod_groups = 1;
   }
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {

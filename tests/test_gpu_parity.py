@@ -180,6 +180,28 @@ def test_dac_codes_bit_exact_with_adversarial_ties(dev):
     assert torch.equal(scale.cpu(), ir)
 
 
+@pytest.mark.parametrize("res", [2.0 / 254.0, 2.0 / 62.0, 2.0 / 1022.0, 0.1])
+def test_dac_codes_bit_exact_large_random_sample(dev, res):
+    """The kernels divide with two fused multiply-adds on a correctly rounded reciprocal; this must
+    reproduce IEEE division bit for bit (4M values, irregular input ranges, several resolutions)."""
+    from analog_moe import ops
+    g = torch.Generator().manual_seed(int(res * 1e6))
+    P, K = 4096, 1024
+    ir = torch.rand(P, generator=g) * 7.9 + 0.013
+    ir[::3] = torch.exp(torch.randn(P, generator=g)[::3] * 2)          # a few decades of magnitudes
+    x = torch.randn(P, K, generator=g) * ir.view(-1, 1) * 0.8
+    x[:, ::5] = (torch.randint(-int(1 / res), int(1 / res) + 1, (P, K), generator=g).float()[:, ::5] + 0.5) \
+        * res * ir.view(-1, 1)                                          # nominal ties
+    _, want = O.dac(x, ir, None, res)
+    if abs(want).max() > 127:
+        keep = want.abs().amax(1) <= 127                                # int8 transport of ep_pack
+        x, ir, want = x[keep], ir[keep], want[keep]
+    if res < 1 / 127.5:
+        pytest.skip("codes do not fit the int8 transport used to read them back")
+    codes, _ = ops.ep_pack(x.to(dev), torch.arange(x.shape[0], dtype=torch.int32, device=dev), ir.to(dev), res)
+    assert torch.equal(codes.cpu().float(), want)
+
+
 @pytest.mark.parametrize("prec", ["simt", "split", "bf16x1"])
 def test_dac_codes_through_the_gemm(dev, prec):
     """With identity weights the CVMM output is code*res*ir: the codes come back exactly."""
