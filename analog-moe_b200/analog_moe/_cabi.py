@@ -91,6 +91,7 @@ SIGNATURES = {
     "amoe_cvmm_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "amoe_cvmm_fwd": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dx": (C.c_int, [C.POINTER(CvmmArgs), vp]),
+    "amoe_cvmm_dw_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "amoe_cvmm_dw": (C.c_int, [C.POINTER(DwArgs), vp]),
     "amoe_combine": (C.c_int, [vp, C.c_int32, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
                                C.c_int64, vp]),

@@ -307,6 +307,9 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
     a.x, a.x_dtype, a.x_stride, a.x_rows, a.x_row, a.ir = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0], ptr(x_row), ptr(ir)
     a.g, a.g_dtype, a.g_stride, a.g_rows, a.g_row = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0], ptr(g_row)
     a.g_div, a.g_scale, a.dw = g_div, ptr(g_scale), ptr(dw)
+    nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device) if nbytes else None
+    a.workspace, a.workspace_bytes = ptr(ws), nbytes
     a.dev_status = ptr(status)
     _call("amoe_cvmm_dw", C.byref(a), stream_ptr())
     return dw

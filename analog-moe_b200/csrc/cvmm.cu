@@ -35,6 +35,11 @@ size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E) {
   return 0;  // the kernels find their tiles from expert_offsets; nothing is staged in global memory
 }
 
+size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision) {
+  if (precision == AMOE_PREC_FP32_SIMT || P <= 0 || E <= 0 || K <= 0 || N <= 0) return 0;
+  return dw_tc_workspace_bytes(P, E, K, N);
+}
+
 int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   int s = check_common(a);

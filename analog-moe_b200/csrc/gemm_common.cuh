@@ -27,5 +27,6 @@ int launch_cvmm_simt(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi, 
 int launch_dw_simt(const amoe_dw_args* a, cudaStream_t stream);
 int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi, cudaStream_t stream);
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream);
+size_t dw_tc_workspace_bytes(int64_t P, int E, int K, int N);
 
 }  // namespace amoe

@@ -624,19 +624,43 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 struct DwMnParams {
   int E, K, N;
   int BN, m_tiles, n_tiles, stages;
+  int seg;              // slots per work segment (multiple of 64); 0: one segment per expert
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;   // a_bytes/b_bytes: one precision term of A / B
   const int32_t* offsets;
   const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir;
   const void* g; int g_dtype; int64_t g_stride; int64_t g_rows; const int32_t* g_row; int g_div;
   const float* g_scale;
   int x_vec_ok, g_vec_ok;
-  float* dw;
+  float* dw;            // [E,K,N]
+  float* partials;      // [segments,K,N] when the slot range of an expert is split, else NULL
   int32_t* status;
 };
 
-constexpr int kDwProdWarps = 12;
-constexpr int kDwThreads = (6 + kDwProdWarps) * 32;   // 2 control + 4 epilogue + 12 prologue warps
+constexpr int kDwProdWarps = 26;
+constexpr int kDwThreads = (6 + kDwProdWarps) * 32;   // 2 control + 4 epilogue + 26 prologue warps
 constexpr uint32_t kMnBlock = kBK * 128;   // 64 rows x 128 bytes
+
+// Segment number `idx` of the slot list: expert e owns ceil(count_e / seg) segments (seg == 0: exactly
+// one segment per expert, possibly empty).
+struct SegIter {
+  const int32_t* off; int E, seg; int e; int64_t before;
+  __device__ SegIter(const int32_t* o, int E_, int seg_) : off(o), E(E_), seg(seg_), e(0), before(0) {}
+  __device__ bool get(int64_t idx, int& ex, int& beg, int& end) {
+    while (e < E) {
+      const int b = off[e], en = off[e + 1];
+      const int ns = seg > 0 ? (en - b + seg - 1) / seg : 1;
+      if (idx < before + ns) {
+        ex = e;
+        beg = seg > 0 ? b + static_cast<int>(idx - before) * seg : b;
+        end = seg > 0 ? min(beg + seg, en) : en;
+        return true;
+      }
+      before += ns;
+      ++e;
+    }
+    return false;
+  }
+};
 
 template <bool SPLIT>
 __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
@@ -646,18 +670,20 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   setup_cta(sm, p.stages, p.tmem_cols, kDwProdWarps, 4);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.status;
-  const int64_t items = static_cast<int64_t>(p.E) * p.m_tiles * p.n_tiles;
+  const int tps = p.m_tiles * p.n_tiles;        // output tiles per segment
   const uint32_t a_total = SPLIT ? 2 * p.a_bytes : p.a_bytes;
 
   if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
       RingPos rp(p.stages);
+      SegIter si(p.offsets, p.E, p.seg);
       uint32_t acc_it = 0;
       bool alive = true;
-      for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-        const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-        const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
+      for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+        int e, beg, end;
+        if (!si.get(w / tps, e, beg, end)) break;
+        const int chunks = (end - beg + kBK - 1) / kBK;
         if (chunks == 0) continue;
         const int buf = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
@@ -666,8 +692,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
         for (int kc = 0; kc < chunks; ++kc, rp.next()) {
           const int s = rp.s;
-          const uint32_t ph = rp.ph;
-          if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 13)) { alive = false; break; }
+          if (!mbar_wait(bar_full_a(sm.bars, s), rp.ph, sm.abort_flag, status, 13)) { alive = false; break; }
           tc_fence_after();
           const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
           const uint64_t da_hi = make_smem_desc_mn_sw128(sa, kMnBlock);
@@ -692,17 +717,21 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   } else if (warp >= 2 && warp < 6) {
     const int q = warp & 3;
     const int r = q * 32 + lane;
+    SegIter si(p.offsets, p.E, p.seg);
     uint32_t acc_it = 0;
     bool alive = true;
-    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-      const int nt = static_cast<int>(w % p.n_tiles);
-      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
-      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-      const int chunks = (p.offsets[e + 1] - p.offsets[e] + kBK - 1) / kBK;
+    for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+      int e, beg, end;
+      const int64_t seg_idx = w / tps;
+      if (!si.get(seg_idx, e, beg, end)) break;
+      const int sub = static_cast<int>(w - seg_idx * tps);
+      const int nt = sub % p.n_tiles, mt = sub / p.n_tiles;
+      const int chunks = (end - beg + kBK - 1) / kBK;
       const int m = mt * kBM + r;
       const int n0 = nt * p.BN;
-      float* dst = p.dw + (static_cast<int64_t>(e) * p.K + m) * p.N;
-      if (chunks == 0) {
+      float* dst = (p.partials ? p.partials + (seg_idx * p.K + m) * p.N
+                               : p.dw + (static_cast<int64_t>(e) * p.K + m) * p.N);
+      if (chunks == 0) {   // only without segment splitting: an expert nobody was routed to
         if (m < p.K)
           for (int n = n0; n < min(n0 + p.BN, p.N); ++n) dst[n] = 0.f;
         continue;
@@ -714,6 +743,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       if (!ok) { alive = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
+#pragma unroll 1
       for (int c0 = 0; c0 < p.BN; c0 += 16) {
         float v[16];
         tmem_ld16(taddr + c0, v);
@@ -737,34 +767,36 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       ++acc_it;
     }
   } else if (warp >= 6) {
-    constexpr int np = kDwProdWarps * 32;               // 384
+    constexpr int np = kDwProdWarps * 32;
     const int pt = threadIdx.x - 6 * 32;
     const int a_chunks = kBM / 8;                        // 16 sixteen-byte chunks per slot row of A
     const int b_chunks = (p.BN + 7) / 8;
     const int a_tasks = kBK * a_chunks;                  // 1024
     const int tasks = a_tasks + kBK * b_chunks;
     RingPos rp(p.stages);
+    SegIter si(p.offsets, p.E, p.seg);
     bool alive = true;
-    for (int64_t w = blockIdx.x; w < items && alive; w += gridDim.x) {
-      const int nt = static_cast<int>(w % p.n_tiles);
-      const int mt = static_cast<int>((w / p.n_tiles) % p.m_tiles);
-      const int e = static_cast<int>(w / (p.m_tiles * p.n_tiles));
-      const int beg = p.offsets[e], end = p.offsets[e + 1];
+    for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+      int e, beg, end;
+      const int64_t seg_idx = w / tps;
+      if (!si.get(seg_idx, e, beg, end)) break;
+      const int sub = static_cast<int>(w - seg_idx * tps);
+      const int nt = sub % p.n_tiles, mt = sub / p.n_tiles;
       const int chunks = (end - beg + kBK - 1) / kBK;
       for (int kc = 0; kc < chunks; ++kc, rp.next()) {
         const int s = rp.s;
-        const uint32_t ph = rp.ph;
-        bool ok = mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 16);
+        bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 16);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         const uint32_t stage = sm.base_u32 + s * p.stage_bytes;
         const int i0 = beg + kc * kBK;
-        for (int base = pt; base < tasks; base += np * 3) {
-          float v[3][8];
-          int where[3];       // byte offset inside the operand term, or -1
-          bool isb[3];
+#pragma unroll 1
+        for (int base = pt; base < tasks; base += np * 2) {
+          float v[2][8];
+          int where[2];       // byte offset inside the operand term, or -1
+          bool isb[2];
 #pragma unroll
-          for (int b = 0; b < 3; ++b) {
+          for (int b = 0; b < 2; ++b) {
             const int task = base + b * np;
             where[b] = -1;
             isb[b] = task >= a_tasks;
@@ -808,7 +840,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
             }
           }
 #pragma unroll
-          for (int b = 0; b < 3; ++b) {
+          for (int b = 0; b < 2; ++b) {
             if (where[b] >= 0) {
               const uint32_t hi = stage + (isb[b] ? a_total : 0u);
               const uint32_t lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
@@ -823,6 +855,41 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
     }
   }
   teardown_cta(sm, tmem_base, p.tmem_cols);
+}
+
+// dW[e] = sum over the expert's segments, in segment order (fixed order: bit-reproducible).
+__global__ void dw_reduce_kernel(const float* __restrict__ partials, const int32_t* __restrict__ offsets, int E, int seg,
+                                 int64_t kn, float* __restrict__ dw) {
+  __shared__ int s_first, s_count;
+  const int e = blockIdx.y;
+  if (threadIdx.x == 0) {
+    int first = 0;
+    for (int x = 0; x < e; ++x) first += (offsets[x + 1] - offsets[x] + seg - 1) / seg;
+    s_first = first;
+    s_count = (offsets[e + 1] - offsets[e] + seg - 1) / seg;
+  }
+  __syncthreads();
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (i >= kn) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sgm = 0; sgm < s_count; ++sgm) {
+    const float4 v = *reinterpret_cast<const float4*>(partials + (static_cast<int64_t>(s_first) + sgm) * kn + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  *reinterpret_cast<float4*>(dw + static_cast<int64_t>(e) * kn + i) = acc;
+}
+
+// Slots per segment for the split, or 0 when the work is too small to be worth splitting.
+int dw_segment_slots(int64_t P, int K, int N) {
+  if (P <= 4096 || (static_cast<int64_t>(K) * N) % 4 != 0) return 0;
+  const int n_pad = round_up(N, 16);
+  const int n_tiles = (n_pad + 127) / 128;
+  const int m_tiles = (K + kBM - 1) / kBM;
+  int64_t seg = P * m_tiles * n_tiles / (4 * 148);
+  seg = (seg + 63) / 64 * 64;
+  if (seg < 256) seg = 256;
+  if (seg > 4096) seg = 4096;
+  return static_cast<int>(seg);
 }
 
 uint32_t pow2_cols(int need) {
@@ -981,6 +1048,12 @@ extern "C" int amoe_debug_timeline(long long* host, int clear) {
 }
 #endif
 
+size_t dw_tc_workspace_bytes(int64_t P, int E, int K, int N) {
+  const int seg = dw_segment_slots(P, K, N);
+  if (seg == 0) return 0;
+  return static_cast<size_t>((P + seg - 1) / seg + E) * K * N * sizeof(float);
+}
+
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   int s = amoe_check_device();
   if (s != AMOE_OK) return s;
@@ -998,6 +1071,14 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   p.x_vec_ok = aligned16(a->x) && ((a->x_stride * (a->x_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.g_vec_ok = aligned16(a->g) && ((a->g_stride * (a->g_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.dw = a->dw; p.status = a->dev_status;
+  // Large problems: cut every expert's slot range into segments so that the work items outnumber the
+  // SMs and a popular expert does not become one long item; the partial tiles go to the workspace and
+  // are summed in segment order afterwards.
+  p.seg = dw_segment_slots(a->P, a->K, a->N);
+  const size_t need = dw_tc_workspace_bytes(a->P, a->E, a->K, a->N);
+  if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
+    p.seg = 0;   // no (usable) workspace: one owner per expert tile
+  p.partials = p.seg > 0 ? reinterpret_cast<float*>(a->workspace) : nullptr;
   // bf16 inputs are exact in one term; fp32 inputs are split unless the caller asked for the fast mode
   const bool split = a->precision == AMOE_PREC_SPLIT && !(a->x_dtype == AMOE_BF16 && a->g_dtype == AMOE_BF16 && !a->g_scale);
   p.a_bytes = 2 * kMnBlock;                                             // 128 columns = 2 blocks
@@ -1008,7 +1089,8 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
   const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra;
-  const int64_t items = static_cast<int64_t>(a->E) * p.m_tiles * p.n_tiles;
+  const int64_t segs = p.seg > 0 ? (a->P + p.seg - 1) / p.seg + a->E : a->E;
+  const int64_t items = segs * p.m_tiles * p.n_tiles;
   const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
   if (split) {
     AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -1018,6 +1100,12 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
     dw_tc_mn_kernel<false><<<grid, kDwThreads, smem, stream>>>(p);
   }
   AMOE_LAUNCH_CHECK("dw_tc");
+  if (p.seg > 0) {
+    const int64_t kn = static_cast<int64_t>(a->K) * a->N;
+    dim3 rg(static_cast<unsigned>((kn / 4 + 255) / 256), a->E);
+    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw);
+    AMOE_LAUNCH_CHECK("dw_reduce");
+  }
   return AMOE_OK;
 }
 

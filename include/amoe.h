@@ -196,6 +196,9 @@ int amoe_cvmm_dx(const amoe_cvmm_args* args, amoe_stream_t stream);
  * where g_src_row(i) = g_row[i] / g_div (g_div = k folds the repeat over the k slots of a token;
  * 1 otherwise).  One owner per output tile, no atomics: results do not depend on scheduling.
  * dW is fp32 [E,K,N] contiguous and is fully written (zeros for experts without slots).
+ * With a workspace of amoe_cvmm_dw_workspace_bytes (optional; 0 bytes for small problems) the tensor-core
+ * kernel cuts each expert's slots into segments, one work item per segment and tile, and sums the
+ * partial tiles in segment order afterwards: same determinism, balanced under skewed routing.
  * ---------------------------------------------------------------------------------------- */
 typedef struct amoe_dw_args {
   int64_t P; int32_t E, K, N; int32_t precision;
@@ -208,9 +211,10 @@ typedef struct amoe_dw_args {
   int32_t g_div;                  /* >=1 */
   const float* g_scale;           /* indexed by g_row[i], or NULL */
   float* dw;                      /* [E,K,N] */
-  void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
+  void* workspace; size_t workspace_bytes;  /* amoe_cvmm_dw_workspace_bytes, or NULL */
   int32_t* dev_status;
 } amoe_dw_args;
+size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision);
 int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------

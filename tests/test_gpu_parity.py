@@ -343,6 +343,31 @@ def test_dw_is_deterministic_and_handles_empty_experts(dev, prec):
     assert float((d1.cpu() - want).abs().max()) <= TOL[prec] * scale
 
 
+def test_dw_segmented_under_skewed_routing(dev):
+    """Large slot counts take the segmented path (partial tiles + ordered reduction).  Zipf-like skew,
+    one expert with no slots, sizes that are not multiples of the tile: result vs oracle, and two runs
+    bit-identical."""
+    from analog_moe import ops, _cabi
+    T, K, N, E, k = 6000, 200, 136, 8, 2
+    assert _cabi.lib.amoe_cvmm_dw_workspace_bytes(T * k, E, K, N, 1) > 0
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(T, K, generator=g)
+    gr = torch.randn(T * k, N, generator=g)
+    logits = torch.randn(T, E, generator=g) - 1.5 * torch.log(torch.arange(1, E + 1).float())
+    logits[:, 5] = -50.0
+    s = O.select_sort(logits, k)
+    counts = (s.expert_offsets[1:] - s.expert_offsets[:-1]).float()
+    assert counts.max() > 3 * counts[counts > 0].min()
+    ir = torch.full((T * k,), 1.5)
+    want = O.cvmm_dw(x, s.token_index, s.sel, gr, E, ir, s.slot_index)
+    a = [t.to(dev) for t in (x, s.token_index, gr, s.slot_index, s.expert_offsets)]
+    d1 = ops.cvmm_dw(*a, E, 1, P=T * k, ir=ir.to(dev))
+    d2 = ops.cvmm_dw(*a, E, 1, P=T * k, ir=ir.to(dev))
+    assert torch.equal(d1, d2)
+    assert float(d1[5].abs().max()) == 0.0
+    assert float((d1.cpu() - want).abs().max()) <= TOL["split"] * float(want.abs().max())
+
+
 def test_index_out_of_range_is_reported_not_dereferenced(dev):
     from analog_moe import ops, _cabi
     T, K, N, E = 64, 32, 32, 2
