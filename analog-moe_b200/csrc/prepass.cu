@@ -4,22 +4,28 @@
 namespace amoe {
 namespace {
 
-// colmax[e,n] = max_k |W[e,k,n]|.  Block = 32 columns x 8 k-lanes.
+// colmax[e,n] = max_k |W[e,k,n]|.  Block = 32 columns x 8 k-lanes over a slice of K; the slices meet
+// through an integer atomic max on the bit patterns of the (non-negative) floats, which is exact
+// and order-independent.  colmax must be zero-filled before the launch.
+constexpr int kColmaxSlice = 128;
 __global__ void colmax_kernel(const void* __restrict__ w, int dtype, int E, int K, int N, int64_t se, int64_t sk,
                               int64_t sn, float* __restrict__ colmax) {
   __shared__ float red[8][33];
   const int e = blockIdx.y;
   const int n = blockIdx.x * 32 + threadIdx.x;
+  const int kb = blockIdx.z * kColmaxSlice;
+  const int ke = min(K, kb + kColmaxSlice);
   float m = 0.f;
   if (n < N) {
-    for (int k = threadIdx.y; k < K; k += 8) m = fmaxf(m, fabsf(load_elem(w, dtype, e * se + k * sk + n * sn)));
+    for (int k = kb + threadIdx.y; k < ke; k += 8) m = fmaxf(m, fabsf(load_elem(w, dtype, e * se + k * sk + n * sn)));
   }
   red[threadIdx.y][threadIdx.x] = m;
   __syncthreads();
   if (threadIdx.y == 0 && n < N) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i][threadIdx.x]);
-    colmax[static_cast<int64_t>(e) * N + n] = m;
+    if (m == m) atomicMax(reinterpret_cast<int*>(colmax) + static_cast<int64_t>(e) * N + n, __float_as_int(m));
+    else colmax[static_cast<int64_t>(e) * N + n] = m;   // NaN weights: propagate
   }
 }
 
@@ -62,80 +68,105 @@ struct PrepassDev {
 
 constexpr int kTK = 32, kTN = 128;
 
-// Block (32,8): tile of 32 k-rows x 128 n-columns of expert blockIdx.z.
+__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// Block (32,8): tile of 32 k-rows x 128 n-columns of expert blockIdx.z.  Loads, the modifier and the
+// natural-orientation copy work on four consecutive columns per thread (16-byte loads, 8-byte bf16
+// stores); the transposed copy goes through shared memory and leaves as 16-byte stores of eight
+// consecutive k.
 __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
   __shared__ float tile[kTK][kTN + 1];
   const int e = blockIdx.z;
   const int k0 = blockIdx.y * kTK, n0 = blockIdx.x * kTN;
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int n = n0 + tx * 4;
+  const bool vec_in = p.dtype == AMOE_F32 && p.sn == 1 && (p.sk % 4 == 0) && (p.se % 4 == 0) &&
+                      ((reinterpret_cast<uintptr_t>(p.w) & 15u) == 0) && n + 3 < p.N;
+  const uint32_t off = p.offset + (p.step_dev ? static_cast<uint32_t>(*p.step_dev) * 8u : 0u);
   for (int r = ty; r < kTK; r += 8) {
     const int k = k0 + r;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (k < p.K && n < p.N) {
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (p.noise_std > 0.f) {
-        const uint32_t off = p.offset + (p.step_dev ? static_cast<uint32_t>(*p.step_dev) * 8u : 0u);
-        float4 zz = philox_normal4(p.seed, off, kStreamWeightNoise, static_cast<uint32_t>(e * p.K + k),
-                                   static_cast<uint32_t>(n >> 2));
+        const float4 zz = philox_normal4_inline(p.seed, off, kStreamWeightNoise, static_cast<uint32_t>(e * p.K + k),
+                                                static_cast<uint32_t>(n >> 2));
         z[0] = zz.x; z[1] = zz.y; z[2] = zz.z; z[3] = zz.w;
+      }
+      float x[4] = {0.f, 0.f, 0.f, 0.f};
+      if (vec_in) {
+        const float4 t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.w) + e * p.se + k * p.sk + n));
+        x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.N) x[j] = load_elem(p.w, p.dtype, e * p.se + k * p.sk + (n + j) * p.sn);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (n + j < p.N) {
-          float x = load_elem(p.w, p.dtype, e * p.se + k * p.sk + (n + j) * p.sn);
-          float s = p.noise_per_channel ? p.colmax[static_cast<int64_t>(e) * p.N + n + j] : p.expmax[e];
+          float xv = x[j];
+          const float s = p.noise_per_channel ? p.colmax[static_cast<int64_t>(e) * p.N + n + j] : p.expmax[e];
           if (p.n_states > 0.f) {
-            float res = __fdiv_rn(s, p.n_states);
+            const float res = __fdiv_rn(s, p.n_states);
             if (res > 0.f) {
-              x = rintf(__fdiv_rn(x, res)) * res;
-              x = fminf(fmaxf(x, -s), s);
+              xv = rintf(__fdiv_rn(xv, res)) * res;
+              xv = fminf(fmaxf(xv, -s), s);
             }
           }
-          if (p.noise_std > 0.f) x = x + (p.noise_std * s) * z[j];
-          v[j] = x;
+          if (p.noise_std > 0.f) xv = xv + (p.noise_std * s) * z[j];
+          v[j] = xv;
         }
       }
       if (p.w_out) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (n + j < p.N) p.w_out[(static_cast<int64_t>(e) * p.K + k) * p.N + n + j] = v[j];
+        float* dst = p.w_out + (static_cast<int64_t>(e) * p.K + k) * p.N + n;
+        if (n + 3 < p.N && (p.N % 4 == 0)) *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+        else
+          for (int j = 0; j < 4; ++j)
+            if (n + j < p.N) dst[j] = v[j];
       }
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) tile[r][tx * 4 + j] = v[j];
-    // natural orientation: row k, n contiguous
-    if (p.bwd_hi && k < p.Kpad2) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (n + j < p.Npad2) {
-          __nv_bfloat16 hi, lo;
-          split_bf16(v[j], hi, lo);
-          const int64_t o = (static_cast<int64_t>(e) * p.Kpad2 + k) * p.Npad2 + n + j;
-          p.bwd_hi[o] = hi;
-          if (p.bwd_lo) p.bwd_lo[o] = lo;
-        }
+    // natural orientation: row k, n contiguous (Npad2 is a multiple of 64, so whole quads fit)
+    if (p.bwd_hi && k < p.Kpad2 && n < p.Npad2) {
+      const uint32_t h0 = pack2_bf16(v[0], v[1]), h1 = pack2_bf16(v[2], v[3]);
+      const int64_t o = (static_cast<int64_t>(e) * p.Kpad2 + k) * p.Npad2 + n;
+      *reinterpret_cast<uint2*>(p.bwd_hi + o) = make_uint2(h0, h1);
+      if (p.bwd_lo) {
+        const uint32_t l0 = pack2_bf16(v[0] - __uint_as_float(h0 << 16), v[1] - __uint_as_float(h0 & 0xffff0000u));
+        const uint32_t l1 = pack2_bf16(v[2] - __uint_as_float(h1 << 16), v[3] - __uint_as_float(h1 & 0xffff0000u));
+        *reinterpret_cast<uint2*>(p.bwd_lo + o) = make_uint2(l0, l1);
       }
     }
   }
   __syncthreads();
   if (p.fwd_hi) {
-    // transposed orientation: row n, k contiguous.  256 threads: column = tid/2, 16 k-values each.
+    // transposed orientation: row n, k contiguous.  256 threads: column = tid/2, 16 k-values each
+    // (Kpad is a multiple of 64, so the 32-row tile lies inside the padded extent or entirely outside).
     const int tid = ty * 32 + tx;
     const int c = tid >> 1, half = tid & 1;
     const int nn = n0 + c;
-    if (nn < p.Npad) {
-#pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int r = half * 16 + i;
-        const int k = k0 + r;
-        if (k < p.Kpad) {
-          __nv_bfloat16 hi, lo;
-          split_bf16(tile[r][c], hi, lo);
-          const int64_t o = (static_cast<int64_t>(e) * p.Npad + nn) * p.Kpad + k;
-          p.fwd_hi[o] = hi;
-          if (p.fwd_lo) p.fwd_lo[o] = lo;
-        }
+    const int kb = k0 + half * 16;
+    if (nn < p.Npad && kb < p.Kpad) {
+      uint32_t h[8], l[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float a = tile[half * 16 + 2 * i][c], b2 = tile[half * 16 + 2 * i + 1][c];
+        h[i] = pack2_bf16(a, b2);
+        l[i] = pack2_bf16(a - __uint_as_float(h[i] << 16), b2 - __uint_as_float(h[i] & 0xffff0000u));
+      }
+      const int64_t o = (static_cast<int64_t>(e) * p.Npad + nn) * p.Kpad + kb;
+      uint4* dh = reinterpret_cast<uint4*>(p.fwd_hi + o);
+      dh[0] = make_uint4(h[0], h[1], h[2], h[3]);
+      dh[1] = make_uint4(h[4], h[5], h[6], h[7]);
+      if (p.fwd_lo) {
+        uint4* dl = reinterpret_cast<uint4*>(p.fwd_lo + o);
+        dl[0] = make_uint4(l[0], l[1], l[2], l[3]);
+        dl[1] = make_uint4(l[4], l[5], l[6], l[7]);
       }
     }
   }
@@ -181,7 +212,8 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
   AMOE_REQUIRE(!(a->fwd_lo && !a->fwd_hi) && !(a->bwd_lo && !a->bwd_hi), AMOE_ERR_NULL_POINTER);
   float* colmax = reinterpret_cast<float*>(a->workspace);
   float* expmax = colmax + static_cast<size_t>(a->E) * a->N;
-  colmax_kernel<<<dim3((a->N + 31) / 32, a->E), dim3(32, 8), 0, stream>>>(a->w, a->w_dtype, a->E, a->K, a->N,
+  AMOE_CUDA(cudaMemsetAsync(colmax, 0, static_cast<size_t>(a->E) * a->N * sizeof(float), stream));
+  colmax_kernel<<<dim3((a->N + 31) / 32, a->E, (a->K + kColmaxSlice - 1) / kColmaxSlice), dim3(32, 8), 0, stream>>>(a->w, a->w_dtype, a->E, a->K, a->N,
                                                                           a->w_stride_e, a->w_stride_k,
                                                                           a->w_stride_n, colmax);
   AMOE_LAUNCH_CHECK("colmax");
