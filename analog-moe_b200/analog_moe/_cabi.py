@@ -93,18 +93,20 @@ SIGNATURES = {
     "amoe_cvmm_dx": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dw_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "amoe_cvmm_dw": (C.c_int, [C.POINTER(DwArgs), vp]),
-    "amoe_combine": (C.c_int, [vp, C.c_int32, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
+    "amoe_combine": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
                                C.c_int64, vp]),
     "amoe_combine_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
                                      C.c_int64, vp]),
-    "amoe_row_dot": (C.c_int, [vp, C.c_int32, C.c_int64, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+    "amoe_row_dot": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
                                vp, vp]),
     "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, vp]),
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp,
                                   C.c_size_t, vp]),
     "amoe_expert_std_static": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp]),
-    "amoe_ep_pack": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, C.c_int64, vp, C.c_float, vp, vp, vp, vp]),
+    "amoe_ep_pack": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, C.c_int32, vp, C.c_int64, vp, C.c_float, vp, vp,
+                               vp, vp]),
+    "amoe_invert_index": (C.c_int, [vp, C.c_int64, vp, vp]),
     "amoe_ep_unpack": (C.c_int, [vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, C.c_int64, vp]),
 }
 

@@ -9,8 +9,8 @@ The reference is single-GPU; this module is new.  Per rank and step:
   dispatch                                    all_to_all_single   (rows land in local HBM)
   up-projection -> activation -> down         the same CVMM kernels on the rank's experts
   return                                      all_to_all_single
-  scatter to flat-slot order, gate-weighted   amoe_ep_unpack, amoe_combine
-  sum over k
+  gate-weighted sum over k, reading the       amoe_combine with a row index
+  sorted rows through the inverse permutation
 
 dW and the input-range gradients need no collective: every slot of an expert arrives at its owner.
 The exchange plan (split sizes and the regrouping of received rows by local expert) is plain host
@@ -99,54 +99,40 @@ class _AllToAllRows(torch.autograd.Function):
 
 class _GatherSorted(torch.autograd.Function):
     """x [T, D] -> rows [P, D] in expert-sorted order; backward sums a token's k slot gradients in
-    slot order (deterministic)."""
+    slot order (deterministic), reading the sorted rows through the inverse permutation."""
 
     @staticmethod
-    def forward(ctx, x2: Tensor, token_index: Tensor, slot_index: Tensor, k: int):
-        ctx.save_for_backward(slot_index)
+    def forward(ctx, x2: Tensor, token_index: Tensor, inv_index: Tensor, k: int):
+        ctx.save_for_backward(inv_index)
         ctx.k, ctx.T = k, x2.shape[0]
         rows, _ = ops.ep_pack(x2, token_index)
         return rows
 
     @staticmethod
     def backward(ctx, g: Tensor):
-        (slot_index,) = ctx.saved_tensors
-        flat = ops.ep_unpack(g.contiguous(), slot_index, g.shape[0])
-        return ops.combine(flat, None, ctx.T, ctx.k), None, None, None
+        (inv_index,) = ctx.saved_tensors
+        return ops.combine(g.contiguous(), None, ctx.T, ctx.k, row_index=inv_index), None, None, None
 
 
-class _ScatterToSlots(torch.autograd.Function):
-    """rows [P, N] in sorted order -> [P, N] in flat-slot order."""
-
-    @staticmethod
-    def forward(ctx, rows: Tensor, slot_index: Tensor):
-        ctx.save_for_backward(slot_index)
-        return ops.ep_unpack(rows.contiguous(), slot_index, rows.shape[0])
+class _CombineSorted(torch.autograd.Function):
+    """y[t] = sum_j gate[t, j] * rows[inv[t*k + j]] for rows kept in expert-sorted order
+    (reference cvmm.py:757-759; backward :888-889)."""
 
     @staticmethod
-    def backward(ctx, g: Tensor):
-        (slot_index,) = ctx.saved_tensors
-        rows, _ = ops.ep_pack(g.contiguous(), slot_index)
-        return rows, None
-
-
-class _CombineGate(torch.autograd.Function):
-    """y[t] = sum_j gate[t, j] * res[t*k + j]  (reference cvmm.py:757-759 and :888-889)."""
-
-    @staticmethod
-    def forward(ctx, res: Tensor, gate: Tensor):
+    def forward(ctx, rows: Tensor, gate: Tensor, slot_index: Tensor, inv_index: Tensor):
         T, k = gate.shape
-        ctx.save_for_backward(res, gate)
-        return ops.combine(res, gate, T, k)
+        ctx.save_for_backward(rows, gate, slot_index, inv_index)
+        return ops.combine(rows, gate, T, k, row_index=inv_index)
 
     @staticmethod
     def backward(ctx, gy: Tensor):
-        res, gate = ctx.saved_tensors
+        rows, gate, slot_index, inv_index = ctx.saved_tensors
         T, k = gate.shape
         gy = gy.contiguous()
-        dres = gate.reshape(-1, 1).to(gy.dtype) * gy.repeat_interleave(k, 0)
-        dgate = ops.row_dot(res, gy, k).view(T, k).to(gate.dtype)
-        return dres, dgate
+        # d rows[i] = gate[slot_i] * gy[slot_i // k], written directly in sorted order
+        drows, _ = ops.ep_pack(gy, slot_index, src_div=k, row_scale=gate.reshape(-1).float().contiguous())
+        dgate = ops.row_dot(rows, gy, k, row_index=inv_index).view(T, k).to(gate.dtype)
+        return drows, dgate, None, None
 
 
 class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
@@ -189,7 +175,8 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         gate = torch.sigmoid(logits.float()).view(T, -1).gather(-1, r.raw_sel.long()).to(inp.dtype)
         plan = make_plan(r.expert_offsets, self.world, self.group)
         dev = inp.device
-        rows = _GatherSorted.apply(inp.reshape(T, D), r.token_index, r.slot_index, k)
+        inv = ops.invert_index(r.slot_index)
+        rows = _GatherSorted.apply(inp.reshape(T, D), r.token_index, inv, k)
         recv = _AllToAllRows.apply(rows, plan.send_splits, plan.recv_splits, self.group)
         R = plan.n_recv
         if R > 0:
@@ -201,8 +188,7 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         else:
             out = recv.new_zeros((0, self.v_dim)) + 0.0 * recv.sum()
         back = _AllToAllRows.apply(out, plan.recv_splits, plan.send_splits, self.group)
-        res = _ScatterToSlots.apply(back, r.slot_index)
-        y = _CombineGate.apply(res, gate)
+        y = _CombineSorted.apply(back, gate, r.slot_index, inv)
         if self.training:
             self.noise_step += 1
         return y.view(bsz, seq, self.v_dim), inp.new_zeros(())

@@ -14,7 +14,7 @@ from ._cabi import lib, check, ptr, stream_ptr, dtype_code
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-KERNELS_PER_CALL = {"amoe_select_sort": 4, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
+KERNELS_PER_CALL = {"amoe_invert_index": 1, "amoe_select_sort": 4, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
                     "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 1, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
                     "amoe_ep_pack": 1, "amoe_ep_unpack": 1}
@@ -316,13 +316,14 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
 
 
 # --------------------------------------------------------------------------- reductions
-def combine(res: torch.Tensor, w: Optional[torch.Tensor], T: int, k: int, out_dtype=None) -> torch.Tensor:
+def combine(res: torch.Tensor, w: Optional[torch.Tensor], T: int, k: int, out_dtype=None,
+            row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     res = _rows(res)
     N = res.shape[1]
     y = torch.empty(T, N, dtype=out_dtype or res.dtype, device=res.device)
     if w is not None:
         w = w.reshape(-1).float().contiguous()
-    _call("amoe_combine", ptr(res), dtype_code(res), res.stride(0), ptr(w), T, k, N, ptr(y), dtype_code(y),
+    _call("amoe_combine", ptr(res), dtype_code(res), res.stride(0), ptr(row_index), ptr(w), T, k, N, ptr(y), dtype_code(y),
                            y.stride(0), stream_ptr())
     return y
 
@@ -338,11 +339,11 @@ def combine_codes(codes: torch.Tensor, col_scale: torch.Tensor, raw_sel: torch.T
     return y
 
 
-def row_dot(res: torch.Tensor, g: torch.Tensor, k: int) -> torch.Tensor:
+def row_dot(res: torch.Tensor, g: torch.Tensor, k: int, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     res, g = _rows(res), _rows(g)
     P, N = res.shape
     d = torch.empty(P, dtype=torch.float32, device=res.device)
-    _call("amoe_row_dot", ptr(res), dtype_code(res), res.stride(0), ptr(g), dtype_code(g), g.stride(0), P, k, N,
+    _call("amoe_row_dot", ptr(res), dtype_code(res), res.stride(0), ptr(row_index), ptr(g), dtype_code(g), g.stride(0), P, k, N,
                            ptr(d), stream_ptr())
     return d
 
@@ -369,25 +370,33 @@ def expert_std(x: torch.Tensor, x_row: torch.Tensor, offsets: torch.Tensor, E: i
 
 
 # --------------------------------------------------------------------------- expert-parallel helpers
-def ep_pack(x: torch.Tensor, src_row: torch.Tensor, ir: Optional[torch.Tensor] = None, inp_res: float = -1.0):
-    """Rows in sorted order; with `ir` and `inp_res` given: (int8 codes, fp32 scale per row)."""
+def ep_pack(x: torch.Tensor, src_row: torch.Tensor, ir: Optional[torch.Tensor] = None, inp_res: float = -1.0,
+            src_div: int = 1, row_scale: Optional[torch.Tensor] = None):
+    """Rows x[src_row[i] // src_div] (times row_scale[src_row[i]]) in the order of src_row; with `ir` and
+    `inp_res` given: (int8 DAC codes, fp32 scale per row) instead."""
     x2 = _rows(x)
     P, K = src_row.numel(), x2.shape[1]
     if ir is not None and inp_res > 0:
         codes = torch.empty(P, K, dtype=torch.int8, device=x2.device)
         scale = torch.empty(P, dtype=torch.float32, device=x2.device)
-        _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, ptr(ir), float(inp_res), None,
-                               ptr(codes), ptr(scale), stream_ptr())
+        _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), src_div, None, P, ptr(ir),
+              float(inp_res), None, ptr(codes), ptr(scale), stream_ptr())
         return codes, scale
     rows = torch.empty(P, K, dtype=x2.dtype, device=x2.device)
-    _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), P, None, -1.0, ptr(rows), None, None,
-                           stream_ptr())
+    _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), src_div, ptr(row_scale), P, None, -1.0,
+          ptr(rows), None, None, stream_ptr())
     return rows, None
+
+
+def invert_index(idx: torch.Tensor) -> torch.Tensor:
+    inv = torch.empty_like(idx)
+    _call("amoe_invert_index", ptr(idx), idx.numel(), ptr(inv), stream_ptr())
+    return inv
 
 
 def ep_unpack(recv: torch.Tensor, dst_row: torch.Tensor, out_rows: int) -> torch.Tensor:
     recv = recv.contiguous()
     P, N = recv.shape
-    out = torch.zeros(out_rows, N, dtype=recv.dtype, device=recv.device)
+    out = (torch.empty if out_rows == P else torch.zeros)(out_rows, N, dtype=recv.dtype, device=recv.device)
     _call("amoe_ep_unpack", ptr(recv), dtype_code(recv), N, ptr(dst_row), P, ptr(out), out.stride(0), stream_ptr())
     return out

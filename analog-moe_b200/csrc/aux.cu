@@ -9,8 +9,9 @@ namespace {
 
 // y[t,n] = sum_j w[t*k+j] * res[t*k+j, n]; thread per (t, 4 columns); j ascending.
 template <typename TR, typename TY>
-__global__ void combine_kernel(const TR* __restrict__ res, int64_t res_stride, const float* __restrict__ w, int64_t T,
-                               int k, int N, TY* __restrict__ y, int64_t y_stride) {
+__global__ void combine_kernel(const TR* __restrict__ res, int64_t res_stride, const int32_t* __restrict__ row_index,
+                               const float* __restrict__ w, int64_t T, int k, int N, TY* __restrict__ y,
+                               int64_t y_stride) {
   const int nq = (N + 3) / 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * nq) return;
@@ -20,7 +21,8 @@ __global__ void combine_kernel(const TR* __restrict__ res, int64_t res_stride, c
   for (int j = 0; j < k; ++j) {
     const int64_t s = t * k + j;
     const float ws = w ? w[s] : 1.f;
-    const TR* row = res + s * res_stride + n0;
+    const int64_t rr = row_index ? row_index[s] : s;
+    const TR* row = res + rr * res_stride + n0;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
       if (n0 + c < N) acc[c] = w ? acc[c] + ws * to_f32<TR>(row[c]) : acc[c] + to_f32<TR>(row[c]);
@@ -71,12 +73,13 @@ __global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const flo
 
 // d[s] = res[s,:] . g[s/k,:]; one warp per slot.
 template <typename TR, typename TG>
-__global__ void row_dot_kernel(const TR* __restrict__ res, int64_t res_stride, const TG* __restrict__ g,
-                               int64_t g_stride, int64_t P, int k, int N, float* __restrict__ d) {
+__global__ void row_dot_kernel(const TR* __restrict__ res, int64_t res_stride, const int32_t* __restrict__ row_index,
+                               const TG* __restrict__ g, int64_t g_stride, int64_t P, int k, int N,
+                               float* __restrict__ d) {
   const int lane = threadIdx.x & 31;
   const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (s >= P) return;
-  const TR* r = res + s * res_stride;
+  const TR* r = res + (row_index ? static_cast<int64_t>(row_index[s]) : s) * res_stride;
   const TG* gr = g + (s / k) * g_stride;
   float acc = 0.f;
   for (int n = lane; n < N; n += 32) acc = fmaf(to_f32<TR>(r[n]), to_f32<TG>(gr[n]), acc);
@@ -161,12 +164,14 @@ __global__ void std_final_kernel(const double* __restrict__ sq, const int32_t* _
 // Gather rows in sorted order; optionally apply the DAC and emit int8 codes + per-row scale.
 template <typename T>
 __global__ void ep_pack_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
-                               int64_t P, const float* __restrict__ ir, float inp_res, T* __restrict__ send_rows,
+                               int src_div, const float* __restrict__ row_scale, int64_t P,
+                               const float* __restrict__ ir, float inp_res, T* __restrict__ send_rows,
                                int8_t* __restrict__ send_codes, float* __restrict__ send_scale) {
   const int lane = threadIdx.x & 31;
   const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (i >= P) return;
-  const T* row = x + static_cast<int64_t>(src_row[i]) * stride;
+  const int64_t sr = src_row[i];
+  const T* row = x + (sr / src_div) * stride;
   if (send_codes) {
     const float r = ir[i];
     const float rr = __frcp_rn(r), rcp_res = quant_rcp(inp_res);
@@ -175,9 +180,22 @@ __global__ void ep_pack_kernel(const T* __restrict__ x, int64_t stride, int K, c
       send_codes[i * K + k] = static_cast<int8_t>(c);
     }
     if (lane == 0) send_scale[i] = r;
+  } else if (row_scale) {
+    const float sc = row_scale[sr];
+    for (int k = lane; k < K; k += 32) {
+      if constexpr (sizeof(T) == 4) send_rows[i * K + k] = sc * row[k];
+      else send_rows[i * K + k] = __float2bfloat16_rn(sc * __bfloat162float(row[k]));
+    }
   } else {
     for (int k = lane; k < K; k += 32) send_rows[i * K + k] = row[k];
   }
+}
+
+__global__ void invert_index_kernel(const int32_t* __restrict__ idx, int64_t P, int32_t* __restrict__ inv) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= P) return;
+  const int32_t j = idx[i];
+  if (j >= 0 && j < P) inv[j] = static_cast<int32_t>(i);
 }
 
 template <typename T>
@@ -206,27 +224,26 @@ using namespace amoe;
 
 extern "C" {
 
-int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const float* w, int64_t T, int32_t k,
-                 int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream_) {
+int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const float* w,
+                 int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(res && y, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = blocks_for(n, 256);
   if (res_dtype == AMOE_F32 && y_dtype == AMOE_F32)
-    combine_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, w, T, k,
+    combine_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index, w, T, k,
                                                              N, reinterpret_cast<float*>(y), y_stride);
   else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_BF16)
     combine_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
+        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, row_index, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
         y_stride);
   else if (res_dtype == AMOE_F32 && y_dtype == AMOE_BF16)
-    combine_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
-                                                                     w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
+    combine_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
                                                                      y_stride);
   else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_F32)
     combine_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
-                                                                     res_stride, w, T, k, N,
+                                                                     res_stride, row_index, w, T, k, N,
                                                                      reinterpret_cast<float*>(y), y_stride);
   else
     return AMOE_ERR_BAD_DTYPE;
@@ -255,26 +272,26 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
   return AMOE_OK;
 }
 
-int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const void* g, int32_t g_dtype,
-                 int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream_) {
+int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const void* g,
+                 int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(res && g && d, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const unsigned blocks = blocks_for(P * 32, 256);
   if (res_dtype == AMOE_F32 && g_dtype == AMOE_F32)
-    row_dot_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
+    row_dot_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index,
                                                              reinterpret_cast<const float*>(g), g_stride, P, k, N, d);
   else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_BF16)
     row_dot_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
+        reinterpret_cast<const __nv_bfloat16*>(res), res_stride, row_index, reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
         P, k, N, d);
   else if (res_dtype == AMOE_F32 && g_dtype == AMOE_BF16)
-    row_dot_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride,
+    row_dot_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index,
                                                                      reinterpret_cast<const __nv_bfloat16*>(g),
                                                                      g_stride, P, k, N, d);
   else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_F32)
     row_dot_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
-                                                                     res_stride, reinterpret_cast<const float*>(g),
+                                                                     res_stride, row_index, reinterpret_cast<const float*>(g),
                                                                      g_stride, P, k, N, d);
   else
     return AMOE_ERR_BAD_DTYPE;
@@ -385,22 +402,33 @@ int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t
   return AMOE_OK;
 }
 
-int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int64_t P,
-                 const float* ir, float inp_res, void* send_rows, int8_t* send_codes, float* send_scale,
-                 amoe_stream_t stream_) {
+int amoe_invert_index(const int32_t* idx, int64_t P, int32_t* inv, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(idx && inv, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0, AMOE_ERR_BAD_SHAPE);
+  invert_index_kernel<<<blocks_for(P, 256), 256, 0, stream>>>(idx, P, inv);
+  AMOE_LAUNCH_CHECK("invert_index");
+  return AMOE_OK;
+}
+
+int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int32_t src_div,
+                 const float* row_scale, int64_t P, const float* ir, float inp_res, void* send_rows,
+                 int8_t* send_codes, float* send_scale, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(x && src_row, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  if (src_div < 1) src_div = 1;
   AMOE_REQUIRE((send_codes != nullptr) != (send_rows != nullptr), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(!send_codes || (ir && send_scale && inp_res > 0.f && inp_res >= 1.f / 127.5f), AMOE_ERR_UNSUPPORTED);
   const unsigned blocks = blocks_for(P * 32, 256);
   if (dtype == AMOE_F32)
-    ep_pack_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, P, ir,
+    ep_pack_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div,
+                                                      row_scale, P, ir,
                                                       inp_res, reinterpret_cast<float*>(send_rows), send_codes,
                                                       send_scale);
   else if (dtype == AMOE_BF16)
     ep_pack_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
-                                                              src_row, P, ir, inp_res,
+                                                              src_row, src_div, row_scale, P, ir, inp_res,
                                                               reinterpret_cast<__nv_bfloat16*>(send_rows), send_codes,
                                                               send_scale);
   else

@@ -34,6 +34,10 @@ CONFIGS = {
     "c5": dict(T=8192, k=6, D=1536, F=192, E=48, dtype="bf16", out_noise=0.02, w_noise=0.01, adc=True, bwd=True,
                out_res=62.0),
 }
+# DRAM bytes (read + write) per launch of the config-2 kernels from the ncu capture summarised in
+# profiles/cvmm_tc_kernel_c2_ncu_full.md; other configs have no capture (traffic stays null).
+NCU_TRAFFIC_C2 = {"amoe_cvmm_fwd[up]": 44.5e6, "amoe_cvmm_fwd[down]": 117.3e6, "amoe_cvmm_dw[down]": 59.6e6,
+                  "amoe_cvmm_dx[down]": 62.3e6, "amoe_cvmm_dw[up]": 57.4e6, "amoe_cvmm_dx[up]": 163.9e6}
 OUT_BOUND = 12.0     # ADC clip in units of the column weight maximum (aihwkit's default out_bound)
 SEED = 1234
 
@@ -369,7 +373,8 @@ def main():
         if is_gemm:
             ach = gemm_flops / (kern[top]["ms_avg"] * 1e-3) / 1e12
             roof = dict(kernel=top, bound="tensor", achieved=ach, peak=pk["tf"], unit="TFLOP/s", frac=ach / pk["tf"],
-                        traffic=None, peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
+                        traffic=NCU_TRAFFIC_C2.get(top) if args.config == "c2" and world == 1 else None,
+                        peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
         else:
             roof = dict(kernel=top, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
                         peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)

@@ -219,22 +219,23 @@ int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Reductions around the CVMM.
- * amoe_combine: y[t,:] = sum_j w[t*k+j] * res[t*k+j,:] in slot order (w NULL = 1).  Replaces the
+ * amoe_combine: y[t,:] = sum_j w[t*k+j] * res[row(t*k+j),:] in slot order (w NULL = 1), where
+ *   row(s) = row_index[s] if row_index is given (rows kept in another order, e.g. expert-sorted), else s.  Replaces the
  *   gate-weighted reduction (cvmm.py:757-759), its backward (cvmm.py:888) and the sum over k of
  *   the up-projection's input gradient (cvmm.py:890-891).  With `codes` given instead of `res`
  *   the rows are rebuilt from ADC codes: codes*step*col_scale[raw_sel[slot],:]*row_mult[slot].
- * amoe_row_dot: d[s] = res[s,:] . g[s/k,:]  (gate gradient, cvmm.py:889).
+ * amoe_row_dot: d[s] = res[row(s),:] . g[s/k,:]  (gate gradient, cvmm.py:889).
  * amoe_ir_grad_reduce: per-expert sum of the per-slot input-range gradients plus the decay term
  *   decay*ir_e*count_e*[keep_count/total > min_percentage] (cvmm.py:872-878 followed by autograd's
  *   index-add of input_range[ir_idx][sel]).  ir_grad_slot [P] sorted; out [E].
  * ---------------------------------------------------------------------------------------- */
-int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const float* w, int64_t T, int32_t k,
-                 int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream);
+int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const float* w,
+                 int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream);
 int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_t* raw_sel, const float* row_mult,
                        float step, const float* w, int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype,
                        int64_t y_stride, amoe_stream_t stream);
-int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const void* g, int32_t g_dtype,
-                 int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream);
+int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const void* g,
+                 int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream);
 int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range,
                         int32_t E, float decay, float min_percentage, const unsigned long long* keep_count,
                         double total_elements, float* out, amoe_stream_t stream);
@@ -279,14 +280,17 @@ int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t
 
 /* ------------------------------------------------------------------------------------------
  * Expert-parallel exchange helpers (no counterpart in the reference, which is single-GPU).
- * amoe_ep_pack gathers the rows of the sorted slot list into a contiguous send buffer in sorted
+ * amoe_ep_pack gathers rows x[src_row[i] / src_div] (optionally times row_scale[src_row[i]]) of the
+ * sorted slot list into a contiguous send buffer in sorted
  * order (so that each destination rank's experts form one contiguous block) and can apply the DAC
  * on the way: int8 codes + one fp32 scale per row instead of the raw rows.
  * amoe_ep_unpack scatters received rows back to their flat-slot rows.
  * ---------------------------------------------------------------------------------------- */
-int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int64_t P,
-                 const float* ir, float inp_res, void* send_rows, int8_t* send_codes, float* send_scale,
-                 amoe_stream_t stream);
+int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int32_t src_div,
+                 const float* row_scale, int64_t P, const float* ir, float inp_res, void* send_rows,
+                 int8_t* send_codes, float* send_scale, amoe_stream_t stream);
+/* inv[idx[i]] = i for a permutation idx of 0..P-1. */
+int amoe_invert_index(const int32_t* idx, int64_t P, int32_t* inv, amoe_stream_t stream);
 int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P,
                    void* out, int64_t out_stride, amoe_stream_t stream);
 
