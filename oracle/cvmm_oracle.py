@@ -73,10 +73,11 @@ def philox4x32_10(c0, c1, c2, c3, k0, k1):
 
 
 def _box_muller(u_a: np.ndarray, u_b: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
-    """Two uint32 words -> two standard normals (fp32 arithmetic, 24-bit uniforms)."""
-    f = np.float32(2.0 ** -24)
-    ua = ((u_a >> np.uint32(8)).astype(np.float32) + np.float32(0.5)) * f
-    ub = ((u_b >> np.uint32(8)).astype(np.float32) + np.float32(0.5)) * f
+    """Two uint32 words -> two standard normals (fp32 arithmetic).  The uniforms are the 23-bit
+    values (k + 0.5) * 2^-23: exact in fp32 and strictly inside (0, 1)."""
+    f = np.float32(2.0 ** -23)
+    ua = ((u_a >> np.uint32(9)).astype(np.float32) + np.float32(0.5)) * f
+    ub = ((u_b >> np.uint32(9)).astype(np.float32) + np.float32(0.5)) * f
     r = np.sqrt(np.float32(-2.0) * np.log(ua)).astype(np.float32)
     th = (np.float32(2.0 * math.pi) * ub).astype(np.float32)
     return (r * np.cos(th)).astype(np.float32), (r * np.sin(th)).astype(np.float32)

@@ -101,6 +101,14 @@ def test_philox_known_answer():
     assert [int(v) for v in out] == [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
 
 
+def test_box_muller_extreme_words_are_finite():
+    for a in (0, 0xFFFFFFFF, 0x80000000):
+        for b in (0, 0xFFFFFFFF):
+            z0, z1 = O._box_muller(np.array([a], dtype=np.uint32), np.array([b], dtype=np.uint32))
+            assert np.isfinite(z0).all() and np.isfinite(z1).all()
+            assert abs(float(z0[0])) < 6.0 and abs(float(z1[0])) < 6.0
+
+
 def test_philox_normal_moments():
     z = O.philox_normal(1234, 0, O.STREAM_OUT_NOISE, 2048, 256)
     assert abs(float(z.mean())) < 5e-3
