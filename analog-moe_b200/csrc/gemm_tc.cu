@@ -257,27 +257,67 @@ struct __align__(16) RowMeta {
 };
 
 // ---- epilogue of one 16-column chunk, fast families (everything 16-byte aligned, n_out % 4 == 0,
-// chunk entirely inside the row)
-__device__ __forceinline__ void store16(const EpiParams& p, int64_t base, const float o[16]) {
-  if (p.out_dtype == AMOE_F32) {
-    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base);
+// chunk entirely inside the row).
+//
+// A thread owns one row of the accumulator, so a plain vector store would touch 32 different cache
+// lines per instruction.  Instead the four threads of a quad exchange 4x4 blocks (two butterfly
+// rounds of shuffles): afterwards thread j of the quad holds columns 4j..4j+3 of the quad's four rows
+// and every store instruction writes 64 contiguous bytes per row, eight rows at a time.  The same
+// exchange (it is its own inverse) turns coalesced loads of the clip reference into the row-owner
+// layout.  All 32 lanes take part; rows that must not be written carry dst = -1.
+__device__ __forceinline__ void quad_transpose(float v[16], int lane) {
+  const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) dst[j] = make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-  } else {
-    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base);
+  for (int pr = 0; pr < 2; ++pr) {          // blocks (0,1) and (2,3) across lanes differing in bit 0
+    const int lo = 8 * pr, hi = 8 * pr + 4;
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
-      dst[j] = make_uint4(cvt_bf16x2(o[8 * j], o[8 * j + 1]), cvt_bf16x2(o[8 * j + 2], o[8 * j + 3]),
-                          cvt_bf16x2(o[8 * j + 4], o[8 * j + 5]), cvt_bf16x2(o[8 * j + 6], o[8 * j + 7]));
+    for (int c = 0; c < 4; ++c) {
+      const float send = b0 ? v[lo + c] : v[hi + c];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      if (b0) v[lo + c] = recv; else v[hi + c] = recv;
+    }
+  }
+#pragma unroll
+  for (int pr = 0; pr < 2; ++pr) {          // blocks (0,2) and (1,3) across lanes differing in bit 1
+    const int lo = 4 * pr, hi = 4 * pr + 8;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float send = b1 ? v[lo + c] : v[hi + c];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 2);
+      if (b1) v[lo + c] = recv; else v[hi + c] = recv;
+    }
+  }
+}
+
+// Rows of the quad this lane belongs to: destination rows (or -1) and clip-reference rows.
+struct QuadRows {
+  int dst[4];
+  int xrow[4];
+};
+
+__device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr, int n0, float v[16], int lane) {
+  quad_transpose(v, lane);
+  const int col = n0 + 4 * (lane & 3);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (qr.dst[i] >= 0) {
+      const int64_t base = static_cast<int64_t>(qr.dst[i]) * p.out_stride + col;
+      if (p.out_dtype == AMOE_F32)
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) =
+            make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      else
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) =
+            make_uint2(cvt_bf16x2(v[4 * i], v[4 * i + 1]), cvt_bf16x2(v[4 * i + 2], v[4 * i + 3]));
+    }
   }
 }
 
 // cs / cis: this chunk's 16 column scales and reciprocals in shared memory (staged by the warp).
-__device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, int n0, float v[16],
-                                              const float* cs, const float* cis) {
+__device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
+                                              float v[16], const float* cs, const float* cis, int lane) {
   const bool noise = p.noise_std > 0.f, adc = p.adc.on;
   const float post = c.absmax * c.ir;
-  float code[16];
+  uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
   for (int qd = 0; qd < 4; ++qd) {
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -291,38 +331,38 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
     for (int j = 0; j < 4; ++j) {
       float acc = v[4 * qd + j] * p.acc_mul;
       if (noise) acc += (p.noise_std * sv[j]) * zv[j];
-      code[4 * qd + j] = 0.f;
-      if (adc) acc = adc_apply(acc, sv[j], iv[j], p.adc, code[4 * qd + j]);
+      float code = 0.f;
+      if (adc) acc = adc_apply(acc, sv[j], iv[j], p.adc, code);
+      pk[qd] |= (static_cast<uint32_t>(static_cast<int>(code)) & 0xffu) << (8 * j);
       v[4 * qd + j] = acc * post;
     }
   }
-  store16(p, c.dst * p.out_stride + n0, v);
-  if (p.out_codes) {
-    uint32_t pk[4];
-#pragma unroll
-    for (int qd = 0; qd < 4; ++qd)
-      pk[qd] = (static_cast<uint32_t>(static_cast<int>(code[4 * qd])) & 0xffu) |
-               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 1])) & 0xffu) << 8) |
-               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 2])) & 0xffu) << 16) |
-               ((static_cast<uint32_t>(static_cast<int>(code[4 * qd + 3])) & 0xffu) << 24);
+  if (p.out_codes && c.valid)
     *reinterpret_cast<uint4*>(p.out_codes + c.dst * p.n_out + n0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-  }
+  store16_t(p, qr, n0, v, lane);
 }
 
-__device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, int n0, float v[16]) {
+__device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
+                                             int lane) {
   if (p.x_ref) {
     float xr[16];
-    if (p.x_ref_dtype == AMOE_F32) {
-      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + c.xrow * p.x_ref_stride + n0);
+    const int col = n0 + 4 * (lane & 3);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float4 t = __ldg(src + j);
-        xr[4 * j] = t.x; xr[4 * j + 1] = t.y; xr[4 * j + 2] = t.z; xr[4 * j + 3] = t.w;
+    for (int i = 0; i < 4; ++i) {
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (qr.xrow[i] >= 0) {
+        const int64_t xi = static_cast<int64_t>(qr.xrow[i]) * p.x_ref_stride + col;
+        if (p.x_ref_dtype == AMOE_F32) {
+          t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + xi));
+        } else {
+          const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.x_ref) + xi));
+          t = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                          __uint_as_float(u.y & 0xffff0000u));
+        }
       }
-    } else {
-      load8_fast<false>(p.x_ref, c.xrow * p.x_ref_stride, n0, xr);
-      load8_fast<false>(p.x_ref, c.xrow * p.x_ref_stride, n0 + 8, xr + 8);
+      xr[4 * i] = t.x; xr[4 * i + 1] = t.y; xr[4 * i + 2] = t.z; xr[4 * i + 3] = t.w;
     }
+    quad_transpose(xr, lane);     // back to "my row, 16 columns"
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       float gs = v[j] * c.rs;
@@ -336,7 +376,7 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, int 
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] *= c.rs;
   }
-  store16(p, c.dst * p.out_stride + n0, v);
+  store16_t(p, qr, n0, v, lane);
 }
 
 template <int DAC, bool A_F32, int EPI>
@@ -442,6 +482,16 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       if (!ti.get(t, e, row0, rows)) break;
       const int64_t i = static_cast<int64_t>(row0) + r;
       RowCtx ctx = epi_row_begin(p.epi, i, e, r < rows);
+      QuadRows qr;
+      if (EPI != kEpiGeneric) {
+        const int my_dst = ctx.valid ? static_cast<int>(ctx.dst) : -1;
+        const int my_x = (ctx.valid && p.epi.is_dx && p.epi.x_ref) ? static_cast<int>(ctx.xrow) : -1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          qr.dst[j] = __shfl_sync(0xffffffffu, my_dst, (lane & ~3) + j);
+          qr.xrow[j] = __shfl_sync(0xffffffffu, my_x, (lane & ~3) + j);
+        }
+      }
       for (int nt = 0; nt < p.n_tiles && alive; ++nt, ++acc_it) {
         const int buf = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
@@ -481,9 +531,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 #pragma unroll
               for (int j = 0; j < 12; ++j) v[j] = v[j + 4];   // rotate the next four columns in
             }
-          } else if (ctx.valid) {
-            if (EPI == kEpiFwd) epi_chunk_fwd(p.epi, ctx, n0, v, cs_smem + slot * 16, cis_smem + slot * 16);
-            else epi_chunk_dx(p.epi, ctx, n0, v);
+          } else {   // all 32 lanes: the quad exchange needs every lane, invalid rows are masked inside
+            if (EPI == kEpiFwd) epi_chunk_fwd(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+            else epi_chunk_dx(p.epi, ctx, qr, n0, v, lane);
           }
         }
         tc_fence_before();
