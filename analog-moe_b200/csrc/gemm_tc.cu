@@ -712,7 +712,8 @@ struct SegIter {
   }
 };
 
-template <bool SPLIT>
+// IN: 0 = x and g fp32 with 16-byte aligned rows, 1 = both bf16 aligned, 2 = anything (run-time dispatch)
+template <bool SPLIT, int IN>
 __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
@@ -819,9 +820,9 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   } else if (warp >= 6) {
     constexpr int np = kDwProdWarps * 32;
     const int pt = threadIdx.x - 6 * 32;
-    const int a_chunks = kBM / 8;                        // 16 sixteen-byte chunks per slot row of A
+    constexpr int a_tasks = kBK * (kBM / 8);             // 64 slots x 16 sixteen-byte chunks of A
     const int b_chunks = (p.BN + 7) / 8;
-    const int a_tasks = kBK * a_chunks;                  // 1024
+    const int b_shift = (b_chunks & (b_chunks - 1)) == 0 ? __ffs(b_chunks) - 1 : -1;
     const int tasks = a_tasks + kBK * b_chunks;
     RingPos rp(p.stages);
     SegIter si(p.offsets, p.E, p.seg);
@@ -833,6 +834,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       const int sub = static_cast<int>(w - seg_idx * tps);
       const int nt = sub % p.n_tiles, mt = sub / p.n_tiles;
       const int chunks = (end - beg + kBK - 1) / kBK;
+      const int a_col0 = mt * kBM, b_col0 = nt * p.BN;
       for (int kc = 0; kc < chunks; ++kc, rp.next()) {
         const int s = rp.s;
         bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 16);
@@ -841,62 +843,56 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
         const uint32_t stage = sm.base_u32 + s * p.stage_bytes;
         const int i0 = beg + kc * kBK;
 #pragma unroll 1
-        for (int base = pt; base < tasks; base += np * 2) {
-          float v[2][8];
-          int where[2];       // byte offset inside the operand term, or -1
-          bool isb[2];
+        for (int task = pt; task < tasks; task += np) {
+          float v[8];
 #pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            const int task = base + b * np;
-            where[b] = -1;
-            isb[b] = task >= a_tasks;
+          for (int x = 0; x < 8; ++x) v[x] = 0.f;
+          const bool isb = task >= a_tasks;
+          int r, c;
+          if (!isb) { r = task >> 4; c = task & 15; }
+          else {
+            const int tt = task - a_tasks;
+            if (b_shift >= 0) { r = tt >> b_shift; c = tt & (b_chunks - 1); }
+            else { r = tt / b_chunks; c = tt - r * b_chunks; }
+          }
+          const int i = i0 + r;
+          if (i < end) {
+            if (!isb) {
+              const int col = a_col0 + c * 8;
+              const int64_t xr = p.x_row[i];
+              if (xr < 0 || xr >= p.x_rows) {
+                report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
+              } else if (col < p.K) {
+                if (IN == 0 && col + 8 <= p.K) load8_fast<true>(p.x, xr * p.x_stride, col, v);
+                else if (IN == 1 && col + 8 <= p.K) load8_fast<false>(p.x, xr * p.x_stride, col, v);
+                else load8(p.x, p.x_dtype, xr * p.x_stride, col, p.K, IN != 2 || p.x_vec_ok != 0, v);
+                if (p.ir) {
+                  const float rr = p.ir[i];
 #pragma unroll
-            for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
-            if (task < tasks) {
-              const int tt = isb[b] ? task - a_tasks : task;
-              const int cpr = isb[b] ? b_chunks : a_chunks;
-              const int r = tt / cpr, c = tt - r * cpr;
-              where[b] = (c >> 3) * static_cast<int>(kMnBlock) + static_cast<int>(sw128_offset(r, c & 7));
-              const int i = i0 + r;
-              if (i < end) {
-                if (!isb[b]) {
-                  const int col = mt * kBM + c * 8;
-                  const int64_t xr = p.x_row[i];
-                  if (xr < 0 || xr >= p.x_rows) {
-                    report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
-                  } else if (col < p.K) {
-                    load8(p.x, p.x_dtype, xr * p.x_stride, col, p.K, p.x_vec_ok != 0, v[b]);
-                    if (p.ir) {
-                      const float rr = p.ir[i];
+                  for (int x = 0; x < 8; ++x) v[x] = clamp_ir(v[x], rr);
+                }
+              }
+            } else {
+              const int col = b_col0 + c * 8;
+              const int64_t gr = p.g_row[i];
+              const int64_t gsrc = p.g_div == 1 ? gr : gr / p.g_div;
+              if (gr < 0 || gsrc >= p.g_rows) {
+                report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
+              } else if (col < p.N) {
+                if (IN == 0 && col + 8 <= p.N) load8_fast<true>(p.g, gsrc * p.g_stride, col, v);
+                else if (IN == 1 && col + 8 <= p.N) load8_fast<false>(p.g, gsrc * p.g_stride, col, v);
+                else load8(p.g, p.g_dtype, gsrc * p.g_stride, col, p.N, IN != 2 || p.g_vec_ok != 0, v);
+                if (p.g_scale) {
+                  const float sc = p.g_scale[gr];
 #pragma unroll
-                      for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], rr);
-                    }
-                  }
-                } else {
-                  const int col = nt * p.BN + c * 8;
-                  const int64_t gr = p.g_row[i];
-                  if (gr < 0 || gr / p.g_div >= p.g_rows) {
-                    report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
-                  } else if (col < p.N) {
-                    load8(p.g, p.g_dtype, (gr / p.g_div) * p.g_stride, col, p.N, p.g_vec_ok != 0, v[b]);
-                    if (p.g_scale) {
-                      const float sc = p.g_scale[gr];
-#pragma unroll
-                      for (int x = 0; x < 8; ++x) v[b][x] *= sc;
-                    }
-                  }
+                  for (int x = 0; x < 8; ++x) v[x] *= sc;
                 }
               }
             }
           }
-#pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            if (where[b] >= 0) {
-              const uint32_t hi = stage + (isb[b] ? a_total : 0u);
-              const uint32_t lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
-              store8<SPLIT>(hi, lo, static_cast<uint32_t>(where[b]), v[b]);
-            }
-          }
+          const uint32_t hi = stage + (isb ? a_total : 0u);
+          const uint32_t lo = hi + (isb ? p.b_bytes : p.a_bytes);
+          store8<SPLIT>(hi, lo, static_cast<uint32_t>((c >> 3) * static_cast<int>(kMnBlock)) + sw128_offset(r, c & 7), v);
         }
         fence_proxy_async();
         __syncwarp();
@@ -1142,13 +1138,20 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   const int64_t segs = p.seg > 0 ? (a->P + p.seg - 1) / p.seg + a->E : a->E;
   const int64_t items = segs * p.m_tiles * p.n_tiles;
   const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
+  int in_class = 2;
+  if (p.x_vec_ok && p.g_vec_ok && a->x_dtype == AMOE_F32 && a->g_dtype == AMOE_F32) in_class = 0;
+  if (p.x_vec_ok && p.g_vec_ok && a->x_dtype == AMOE_BF16 && a->g_dtype == AMOE_BF16) in_class = 1;
+#define AMOE_LAUNCH_DW(SP, IN)                                                                                       \
+  do {                                                                                                               \
+    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<SP, IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));    \
+    dw_tc_mn_kernel<SP, IN><<<grid, kDwThreads, smem, stream>>>(p);                                                  \
+  } while (0)
   if (split) {
-    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_mn_kernel<true><<<grid, kDwThreads, smem, stream>>>(p);
+    if (in_class == 0) AMOE_LAUNCH_DW(true, 0); else if (in_class == 1) AMOE_LAUNCH_DW(true, 1); else AMOE_LAUNCH_DW(true, 2);
   } else {
-    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_mn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    dw_tc_mn_kernel<false><<<grid, kDwThreads, smem, stream>>>(p);
+    if (in_class == 0) AMOE_LAUNCH_DW(false, 0); else if (in_class == 1) AMOE_LAUNCH_DW(false, 1); else AMOE_LAUNCH_DW(false, 2);
   }
+#undef AMOE_LAUNCH_DW
   AMOE_LAUNCH_CHECK("dw_tc");
   if (p.seg > 0) {
     const int64_t kn = static_cast<int64_t>(a->K) * a->N;

@@ -11,7 +11,7 @@
 namespace amoe {
 namespace {
 
-constexpr int kChunk = 1024;   // flat slots per warp in the sort
+constexpr int kChunk = 256;    // flat slots per warp in the sort
 constexpr int kMaxE = 1024;
 constexpr int kMaxK = 32;
 
