@@ -14,7 +14,7 @@ from ._cabi import lib, check, ptr, stream_ptr, dtype_code
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-KERNELS_PER_CALL = {"amoe_invert_index": 1, "amoe_select_sort": 4, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
+KERNELS_PER_CALL = {"amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
                     "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 1, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
                     "amoe_ep_pack": 1, "amoe_ep_unpack": 1}

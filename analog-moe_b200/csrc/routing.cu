@@ -1,10 +1,11 @@
 // Gate select (sigmoid + top-k) and the stable expert-contiguous slot sort.
 //
-// Four small kernels, no host synchronisation, no atomics on the data path, so the slot order is a
+// Five small kernels, no host synchronisation, no atomics on the data path, so the slot order is a
 // pure function of the logits:
 //   topk_kernel      one warp per token: k rounds of warp arg-max over the E gate values
 //   chunk_hist       one warp per chunk of kChunk flat slots: per-expert counts of the chunk
-//   scan_kernel      one CTA: exclusive scan over (expert, chunk) -> expert offsets + chunk bases
+//   chunk_scan       one warp per expert: exclusive prefix of its counts over the chunks
+//   offsets_kernel   one CTA: exclusive scan of the expert totals -> expert_offsets
 //   scatter_kernel   one warp per chunk: stable rank inside the chunk via match.any
 #include "common.cuh"
 
@@ -15,13 +16,14 @@ constexpr int kChunk = 256;    // flat slots per warp in the sort
 constexpr int kMaxE = 1024;
 constexpr int kMaxK = 32;
 
+// kPer = experts per lane (E <= 32 * kPer): the arg-max loops are unrolled over exactly that many.
+template <int kPer>
 __global__ void topk_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int apply_sigmoid,
                             int32_t* __restrict__ raw_sel, float* __restrict__ gate) {
   const int lane = threadIdx.x & 31;
   const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (t >= T) return;
   // each lane holds experts lane, lane+32, ...
-  constexpr int kPer = kMaxE / 32;
   float v[kPer];
   const float* row = logits + t * E;
 #pragma unroll
@@ -34,7 +36,7 @@ __global__ void topk_kernel(const float* __restrict__ logits, int64_t T, int E, 
     }
     v[i] = x;
   }
-  const int per = (E + 31) / 32;
+  constexpr int per = kPer;
   for (int j = 0; j < k; ++j) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -93,38 +95,59 @@ __global__ void chunk_hist_kernel(const int32_t* __restrict__ raw_sel, int64_t P
   }
 }
 
-// hist[c][e] -> exclusive position of (e, c) in the sorted list; offsets[E+1].
-__global__ void scan_kernel(int32_t* __restrict__ hist, int64_t nchunks, int E, int32_t* __restrict__ offsets) {
-  __shared__ int32_t total[kMaxE + 1];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int32_t run = 0;
-    for (int64_t c = 0; c < nchunks; ++c) {
-      int32_t h = hist[c * E + e];
-      hist[c * E + e] = run;
-      run += h;
+// Per expert (one warp each): exclusive prefix of its counts over the chunks, in place, and its total.
+__global__ void chunk_scan_kernel(int32_t* __restrict__ hist, int64_t nchunks, int E, int32_t* __restrict__ total) {
+  const int lane = threadIdx.x & 31;
+  const int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (e >= E) return;
+  int32_t carry = 0;
+  for (int64_t c0 = 0; c0 < nchunks; c0 += 32) {
+    const int64_t c = c0 + lane;
+    const int32_t h = c < nchunks ? hist[c * E + e] : 0;
+    int32_t incl = h;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
     }
-    total[e] = run;
+    if (c < nchunks) hist[c * E + e] = carry + incl - h;
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) total[e] = carry;
+}
+
+// offsets[E+1] = exclusive scan of the per-expert totals (one CTA; E <= 1024).
+__global__ void offsets_kernel(const int32_t* __restrict__ total, int E, int32_t* __restrict__ offsets) {
+  __shared__ int32_t warp_sum[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int e = threadIdx.x;
+  const int32_t h = e < E ? total[e] : 0;
+  int32_t incl = h;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int32_t w = warp_sum[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += up;
+    }
+    warp_sum[lane] = w;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int32_t run = 0;
-    for (int e = 0; e < E; ++e) {
-      int32_t h = total[e];
-      total[e] = run;
-      run += h;
-    }
-    total[E] = run;
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = total[e];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int32_t base = total[e];
-    for (int64_t c = 0; c < nchunks; ++c) hist[c * E + e] += base;
-  }
+  const int32_t base = warp > 0 ? warp_sum[warp - 1] : 0;
+  if (e < E) offsets[e] = base + incl - h;
+  if (e == E - 1) offsets[E] = base + incl;
 }
 
 __global__ void scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t P, int E, int k,
-                               const int32_t* __restrict__ base /*[nchunks,E]*/, int32_t* __restrict__ sel_sorted,
+                               const int32_t* __restrict__ base /*[nchunks,E] prefix inside the expert*/,
+                               const int32_t* __restrict__ offsets, int32_t* __restrict__ sel_sorted,
                                int32_t* __restrict__ token_index, int32_t* __restrict__ slot_index) {
   extern __shared__ int32_t cnt[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,7 +155,7 @@ __global__ void scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t P, i
   const int64_t s0 = chunk * kChunk;
   if (s0 >= P) return;
   int32_t* my = cnt + warp * E;
-  for (int e = lane; e < E; e += 32) my[e] = base[chunk * E + e];
+  for (int e = lane; e < E; e += 32) my[e] = offsets[e] + base[chunk * E + e];
   __syncwarp();
   for (int64_t s = s0 + lane; s < s0 + kChunk; s += 32) {
     bool ok = s < P;
@@ -182,7 +205,7 @@ size_t amoe_select_sort_workspace_bytes(int64_t T, int32_t E, int32_t k) {
   if (T <= 0 || E <= 0 || k <= 0) return 0;
   int64_t P = T * k;
   int64_t nchunks = (P + kChunk - 1) / kChunk;
-  return static_cast<size_t>(nchunks) * E * sizeof(int32_t);
+  return (static_cast<size_t>(nchunks) * E + E) * sizeof(int32_t);
 }
 
 int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32_t apply_sigmoid, int32_t* raw_sel,
@@ -200,7 +223,12 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
   {
     const int threads = 256;
     const int64_t blocks = (T * 32 + threads - 1) / threads;
-    topk_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    const unsigned nb = static_cast<unsigned>(blocks);
+    if (E <= 32) topk_kernel<1><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    else if (E <= 64) topk_kernel<2><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    else if (E <= 128) topk_kernel<4><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    else if (E <= 256) topk_kernel<8><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
+    else topk_kernel<kMaxE / 32><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
     AMOE_LAUNCH_CHECK("topk");
   }
   // warps per block limited by shared memory: E ints per warp
@@ -210,9 +238,13 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
   const size_t smem = static_cast<size_t>(wpb) * E * sizeof(int32_t);
   chunk_hist_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, hist);
   AMOE_LAUNCH_CHECK("chunk_hist");
-  scan_kernel<<<1, 256, 0, stream>>>(hist, nchunks, E, expert_offsets);
-  AMOE_LAUNCH_CHECK("scan");
-  scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, sel_sorted, token_index, slot_index);
+  int32_t* total = hist + nchunks * E;
+  chunk_scan_kernel<<<(E * 32 + 255) / 256, 256, 0, stream>>>(hist, nchunks, E, total);
+  AMOE_LAUNCH_CHECK("chunk_scan");
+  offsets_kernel<<<1, 1024, 0, stream>>>(total, E, expert_offsets);
+  AMOE_LAUNCH_CHECK("offsets");
+  scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, expert_offsets, sel_sorted, token_index,
+                                                     slot_index);
   AMOE_LAUNCH_CHECK("scatter");
   return AMOE_OK;
 }

@@ -65,7 +65,7 @@ def test_host_validation_without_gpu():
     assert lib.amoe_cvmm_fwd(ctypes.byref(a), None) == 3
     d = _cabi.DwArgs()
     assert lib.amoe_cvmm_dw(ctypes.byref(d), None) == 1
-    assert lib.amoe_select_sort_workspace_bytes(1024, 16, 4) == 16 * 16 * 4   # 16 chunks of 256 slots
+    assert lib.amoe_select_sort_workspace_bytes(1024, 16, 4) == (16 * 16 + 16) * 4   # 16 chunks of 256 slots x 16 experts + totals
     assert lib.amoe_expert_std_workspace_bytes(8) == 8 * 3 * 8
 
 
