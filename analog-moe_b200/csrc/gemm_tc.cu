@@ -674,6 +674,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 struct DwMnParams {
   int E, K, N;
   int BN, m_tiles, n_tiles, stages;
+  int MB, NB;           // a work item owns MB x NB (= 1x1, 2x1 or 1x2) output tiles that share operand tiles
   int seg;              // slots per work segment (multiple of 64); 0: one segment per expert
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;   // a_bytes/b_bytes: one precision term of A / B
   const int32_t* offsets;
@@ -713,6 +714,11 @@ struct SegIter {
 };
 
 // IN: 0 = x and g fp32 with 16-byte aligned rows, 1 = both bf16 aligned, 2 = anything (run-time dispatch)
+//
+// A work item = (slot segment, block of MB x NB output tiles).  With two tiles per item the operand
+// tile they share is converted once instead of twice (the prologue, not the tensor pipe, bounds this
+// kernel).  Stage layout: MB A-tiles (hi, lo) then NB B-tiles (hi, lo); TMEM: two buffers of MB*NB
+// accumulators.
 template <bool SPLIT, int IN>
 __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -721,8 +727,12 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   setup_cta(sm, p.stages, p.tmem_cols, kDwProdWarps, 4);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.status;
-  const int tps = p.m_tiles * p.n_tiles;        // output tiles per segment
-  const uint32_t a_total = SPLIT ? 2 * p.a_bytes : p.a_bytes;
+  const int mb_tiles = (p.m_tiles + p.MB - 1) / p.MB, nb_tiles = (p.n_tiles + p.NB - 1) / p.NB;
+  const int tps = mb_tiles * nb_tiles;          // tile blocks per segment
+  const int n_acc = p.MB * p.NB;
+  const uint32_t a_tile = (SPLIT ? 2u : 1u) * p.a_bytes;   // one A tile, all precision terms
+  const uint32_t b_tile = (SPLIT ? 2u : 1u) * p.b_bytes;
+  const uint32_t b_region = static_cast<uint32_t>(p.MB) * a_tile;
 
   if (warp == 1) {
     if (lane == 0) {
@@ -740,23 +750,28 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
         const uint32_t aph = (acc_it >> 1) & 1u;
         if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 12)) { alive = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
+        const uint32_t d_base = tmem_base + static_cast<uint32_t>(buf * n_acc * p.BN);
         for (int kc = 0; kc < chunks; ++kc, rp.next()) {
           const int s = rp.s;
           if (!mbar_wait(bar_full_a(sm.bars, s), rp.ph, sm.abort_flag, status, 13)) { alive = false; break; }
           tc_fence_after();
           const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
-          const uint64_t da_hi = make_smem_desc_mn_sw128(sa, kMnBlock);
-          const uint64_t da_lo = make_smem_desc_mn_sw128(sa + p.a_bytes, kMnBlock);
-          const uint64_t db_hi = make_smem_desc_mn_sw128(sa + a_total, kMnBlock);
-          const uint64_t db_lo = make_smem_desc_mn_sw128(sa + a_total + p.b_bytes, kMnBlock);
+          for (int acc = 0; acc < n_acc; ++acc) {
+            const int ma = acc / p.NB, nb = acc - ma * p.NB;
+            const uint32_t at = sa + ma * a_tile, bt = sa + b_region + nb * b_tile;
+            const uint64_t da_hi = make_smem_desc_mn_sw128(at, kMnBlock);
+            const uint64_t da_lo = make_smem_desc_mn_sw128(at + p.a_bytes, kMnBlock);
+            const uint64_t db_hi = make_smem_desc_mn_sw128(bt, kMnBlock);
+            const uint64_t db_lo = make_smem_desc_mn_sw128(bt + p.b_bytes, kMnBlock);
+            const uint32_t d_tmem = d_base + static_cast<uint32_t>(acc * p.BN);
 #pragma unroll
-          for (int k16 = 0; k16 < kBK / 16; ++k16) {
-            const uint64_t adv = static_cast<uint64_t>(k16 * (16 * 128 / 16));  // 16 rows of 128 bytes, >> 4
-            umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
-            if (SPLIT) {
-              umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
-              umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
+            for (int k16 = 0; k16 < kBK / 16; ++k16) {
+              const uint64_t adv = static_cast<uint64_t>(k16 * (16 * 128 / 16));  // 16 rows of 128 bytes, >> 4
+              umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
+              if (SPLIT) {
+                umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+                umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
+              }
             }
           }
           umma_commit(bar_empty(sm.bars, s));
@@ -776,15 +791,16 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       const int64_t seg_idx = w / tps;
       if (!si.get(seg_idx, e, beg, end)) break;
       const int sub = static_cast<int>(w - seg_idx * tps);
-      const int nt = sub % p.n_tiles, mt = sub / p.n_tiles;
+      const int nbk = sub % nb_tiles, mbk = sub / nb_tiles;
       const int chunks = (end - beg + kBK - 1) / kBK;
-      const int m = mt * kBM + r;
-      const int n0 = nt * p.BN;
-      float* dst = (p.partials ? p.partials + (seg_idx * p.K + m) * p.N
-                               : p.dw + (static_cast<int64_t>(e) * p.K + m) * p.N);
+      float* out_base = p.partials ? p.partials + seg_idx * p.K * p.N : p.dw + static_cast<int64_t>(e) * p.K * p.N;
       if (chunks == 0) {   // only without segment splitting: an expert nobody was routed to
-        if (m < p.K)
-          for (int n = n0; n < min(n0 + p.BN, p.N); ++n) dst[n] = 0.f;
+        for (int acc = 0; acc < n_acc; ++acc) {
+          const int ma = acc / p.NB, nb = acc - ma * p.NB;
+          const int m = (mbk * p.MB + ma) * kBM + r, n0 = (nbk * p.NB + nb) * p.BN;
+          if (m < p.K)
+            for (int n = n0; n < min(n0 + p.BN, p.N); ++n) out_base[static_cast<int64_t>(m) * p.N + n] = 0.f;
+        }
         continue;
       }
       const int buf = acc_it & 1u;
@@ -793,22 +809,28 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
+      for (int acc = 0; acc < n_acc; ++acc) {
+        const int ma = acc / p.NB, nb = acc - ma * p.NB;
+        const int m = (mbk * p.MB + ma) * kBM + r, n0 = (nbk * p.NB + nb) * p.BN;
+        float* dst = out_base + static_cast<int64_t>(m) * p.N;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                               static_cast<uint32_t>((buf * n_acc + acc) * p.BN);
 #pragma unroll 1
-      for (int c0 = 0; c0 < p.BN; c0 += 16) {
-        float v[16];
-        tmem_ld16(taddr + c0, v);
-        tmem_ld_wait();
-        if (m < p.K) {
+        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          tmem_ld_wait();
           const int n = n0 + c0;
-          if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
+          if (m < p.K && n < p.N) {
+            if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
 #pragma unroll
-            for (int x = 0; x < 4; ++x)
-              *reinterpret_cast<float4*>(dst + n + 4 * x) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
-          } else {
+              for (int x = 0; x < 4; ++x)
+                *reinterpret_cast<float4*>(dst + n + 4 * x) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+            } else {
 #pragma unroll
-            for (int x = 0; x < 16; ++x)
-              if (n + x < p.N) dst[n + x] = v[x];
+              for (int x = 0; x < 16; ++x)
+                if (n + x < p.N) dst[n + x] = v[x];
+            }
           }
         }
       }
@@ -820,10 +842,12 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   } else if (warp >= 6) {
     constexpr int np = kDwProdWarps * 32;
     const int pt = threadIdx.x - 6 * 32;
-    constexpr int a_tasks = kBK * (kBM / 8);             // 64 slots x 16 sixteen-byte chunks of A
+    constexpr int a_tile_tasks = kBK * (kBM / 8);        // 64 slots x 16 sixteen-byte chunks per A tile
     const int b_chunks = (p.BN + 7) / 8;
     const int b_shift = (b_chunks & (b_chunks - 1)) == 0 ? __ffs(b_chunks) - 1 : -1;
-    const int tasks = a_tasks + kBK * b_chunks;
+    const int b_tile_tasks = kBK * b_chunks;
+    const int a_tasks = p.MB * a_tile_tasks;
+    const int tasks = a_tasks + p.NB * b_tile_tasks;
     RingPos rp(p.stages);
     SegIter si(p.offsets, p.E, p.seg);
     bool alive = true;
@@ -832,9 +856,8 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
       const int64_t seg_idx = w / tps;
       if (!si.get(seg_idx, e, beg, end)) break;
       const int sub = static_cast<int>(w - seg_idx * tps);
-      const int nt = sub % p.n_tiles, mt = sub / p.n_tiles;
+      const int nbk = sub % nb_tiles, mbk = sub / nb_tiles;
       const int chunks = (end - beg + kBK - 1) / kBK;
-      const int a_col0 = mt * kBM, b_col0 = nt * p.BN;
       for (int kc = 0; kc < chunks; ++kc, rp.next()) {
         const int s = rp.s;
         bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 16);
@@ -843,56 +866,86 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
         const uint32_t stage = sm.base_u32 + s * p.stage_bytes;
         const int i0 = beg + kc * kBK;
 #pragma unroll 1
-        for (int task = pt; task < tasks; task += np) {
-          float v[8];
+        for (int base = pt; base < tasks; base += 2 * np) {
+          // two tasks per round: first both index lookups, then both row loads, then convert + store,
+          // so that the two global-load latencies of a task overlap with the other task's
+          float v[2][8];
+          int r[2], c[2], tile[2], col[2];
+          bool isb[2], live[2];
+          int64_t row_off[2];
+          float aux[2];          // input range (A) or gate scale (B)
 #pragma unroll
-          for (int x = 0; x < 8; ++x) v[x] = 0.f;
-          const bool isb = task >= a_tasks;
-          int r, c;
-          if (!isb) { r = task >> 4; c = task & 15; }
-          else {
-            const int tt = task - a_tasks;
-            if (b_shift >= 0) { r = tt >> b_shift; c = tt & (b_chunks - 1); }
-            else { r = tt / b_chunks; c = tt - r * b_chunks; }
-          }
-          const int i = i0 + r;
-          if (i < end) {
-            if (!isb) {
-              const int col = a_col0 + c * 8;
-              const int64_t xr = p.x_row[i];
-              if (xr < 0 || xr >= p.x_rows) {
-                report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
-              } else if (col < p.K) {
-                if (IN == 0 && col + 8 <= p.K) load8_fast<true>(p.x, xr * p.x_stride, col, v);
-                else if (IN == 1 && col + 8 <= p.K) load8_fast<false>(p.x, xr * p.x_stride, col, v);
-                else load8(p.x, p.x_dtype, xr * p.x_stride, col, p.K, IN != 2 || p.x_vec_ok != 0, v);
-                if (p.ir) {
-                  const float rr = p.ir[i];
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) v[x] = clamp_ir(v[x], rr);
-                }
+          for (int b = 0; b < 2; ++b) {
+            const int task = base + b * np;
+            live[b] = false;
+            isb[b] = task >= a_tasks;
+            r[b] = 0; c[b] = 0; tile[b] = 0; col[b] = 0; row_off[b] = 0; aux[b] = 1.f;
+            if (task < tasks) {
+              if (!isb[b]) { tile[b] = task >> 10; r[b] = (task >> 4) & 63; c[b] = task & 15; }
+              else {
+                int tt = task - a_tasks;
+                tile[b] = tt >= b_tile_tasks ? 1 : 0;
+                tt -= tile[b] * b_tile_tasks;
+                if (b_shift >= 0) { r[b] = tt >> b_shift; c[b] = tt & (b_chunks - 1); }
+                else { r[b] = tt / b_chunks; c[b] = tt - r[b] * b_chunks; }
               }
-            } else {
-              const int col = b_col0 + c * 8;
-              const int64_t gr = p.g_row[i];
-              const int64_t gsrc = p.g_div == 1 ? gr : gr / p.g_div;
-              if (gr < 0 || gsrc >= p.g_rows) {
-                report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
-              } else if (col < p.N) {
-                if (IN == 0 && col + 8 <= p.N) load8_fast<true>(p.g, gsrc * p.g_stride, col, v);
-                else if (IN == 1 && col + 8 <= p.N) load8_fast<false>(p.g, gsrc * p.g_stride, col, v);
-                else load8(p.g, p.g_dtype, gsrc * p.g_stride, col, p.N, IN != 2 || p.g_vec_ok != 0, v);
-                if (p.g_scale) {
-                  const float sc = p.g_scale[gr];
-#pragma unroll
-                  for (int x = 0; x < 8; ++x) v[x] *= sc;
+              const int i = i0 + r[b];
+              if (i < end) {
+                if (!isb[b]) {
+                  col[b] = (mbk * p.MB + tile[b]) * kBM + c[b] * 8;
+                  const int64_t xr = p.x_row[i];
+                  if (xr < 0 || xr >= p.x_rows) report(status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
+                  else if (col[b] < p.K) {
+                    live[b] = true;
+                    row_off[b] = xr * p.x_stride;
+                    if (p.ir) aux[b] = p.ir[i];
+                  }
+                } else {
+                  col[b] = (nbk * p.NB + tile[b]) * p.BN + c[b] * 8;
+                  const int64_t gr = p.g_row[i];
+                  const int64_t gsrc = p.g_div == 1 ? gr : gr / p.g_div;
+                  if (gr < 0 || gsrc >= p.g_rows) report(status, AMOE_ERR_INDEX_RANGE, 31, i, static_cast<int>(gr));
+                  else if (col[b] < p.N && c[b] * 8 < p.BN) {
+                    live[b] = true;
+                    row_off[b] = gsrc * p.g_stride;
+                    if (p.g_scale) aux[b] = p.g_scale[gr];
+                  }
                 }
               }
             }
           }
-          const uint32_t hi = stage + (isb ? a_total : 0u);
-          const uint32_t lo = hi + (isb ? p.b_bytes : p.a_bytes);
-          store8<SPLIT>(hi, lo, static_cast<uint32_t>((c >> 3) * static_cast<int>(kMnBlock)) + sw128_offset(r, c & 7), v);
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+#pragma unroll
+            for (int x = 0; x < 8; ++x) v[b][x] = 0.f;
+            if (live[b]) {
+              const void* src = isb[b] ? p.g : p.x;
+              const int lim = isb[b] ? p.N : p.K;
+              if (IN == 0 && col[b] + 8 <= lim) load8_fast<true>(src, row_off[b], col[b], v[b]);
+              else if (IN == 1 && col[b] + 8 <= lim) load8_fast<false>(src, row_off[b], col[b], v[b]);
+              else load8(src, isb[b] ? p.g_dtype : p.x_dtype, row_off[b], col[b], lim,
+                         IN != 2 || (isb[b] ? p.g_vec_ok : p.x_vec_ok) != 0, v[b]);
+            }
+          }
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            if (base + b * np < tasks) {
+              if (live[b]) {
+                if (!isb[b]) {
+                  if (p.ir) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], aux[b]);
+                  }
+                } else if (p.g_scale) {
+#pragma unroll
+                  for (int x = 0; x < 8; ++x) v[b][x] *= aux[b];
+                }
+              }
+              const uint32_t hi = stage + (isb[b] ? b_region + tile[b] * b_tile : tile[b] * a_tile);
+              const uint32_t lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
+              store8<SPLIT>(hi, lo, static_cast<uint32_t>((c[b] >> 3) * static_cast<int>(kMnBlock)) + sw128_offset(r[b], c[b] & 7), v[b]);
+            }
+          }
         }
         fence_proxy_async();
         __syncwarp();
@@ -1129,14 +1182,18 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   const bool split = a->precision == AMOE_PREC_SPLIT && !(a->x_dtype == AMOE_BF16 && a->g_dtype == AMOE_BF16 && !a->g_scale);
   p.a_bytes = 2 * kMnBlock;                                             // 128 columns = 2 blocks
   p.b_bytes = static_cast<uint32_t>((p.BN + 63) / 64) * kMnBlock;
-  p.stage_bytes = (split ? 2u : 1u) * (p.a_bytes + p.b_bytes);
+  // two output tiles per work item along the longer tile dimension, when there are at least two
+  p.MB = 1; p.NB = 1;
+  if (p.m_tiles >= 2 && p.m_tiles >= p.n_tiles) p.MB = 2;
+  else if (p.n_tiles >= 2) p.NB = 2;
+  p.stage_bytes = (split ? 2u : 1u) * (p.MB * p.a_bytes + p.NB * p.b_bytes);
   p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
-  p.tmem_cols = pow2_cols(2 * p.BN);
+  p.tmem_cols = pow2_cols(2 * p.MB * p.NB * p.BN);
   const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra;
   const int64_t segs = p.seg > 0 ? (a->P + p.seg - 1) / p.seg + a->E : a->E;
-  const int64_t items = segs * p.m_tiles * p.n_tiles;
+  const int64_t items = segs * ((p.m_tiles + p.MB - 1) / p.MB) * ((p.n_tiles + p.NB - 1) / p.NB);
   const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
   int in_class = 2;
   if (p.x_vec_ok && p.g_vec_ok && a->x_dtype == AMOE_F32 && a->g_dtype == AMOE_F32) in_class = 0;
