@@ -54,6 +54,7 @@ class CvmmArgs(C.Structure):
         ("col_scale", vp),
         ("col_inv_scale", vp), ("out_res", C.c_float), ("out_bound", C.c_float),
         ("out", vp), ("out_dtype", C.c_int32), ("out_stride", C.c_int64), ("out_codes", vp),
+        ("out_row_scale", vp), ("out_row_expert", vp),
         ("x_ref", vp), ("x_ref_dtype", C.c_int32), ("x_ref_stride", C.c_int64), ("x_ref_rows", C.c_int64),
         ("x_ref_row", vp),
         ("row_scale", vp), ("ir_grad", vp), ("ir_grad_relative", C.c_int32), ("ir_grad_scale", C.c_float),
@@ -99,6 +100,8 @@ SIGNATURES = {
                                      C.c_int64, vp]),
     "amoe_row_dot": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
                                vp, vp]),
+    "amoe_row_dot_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+                                     vp, vp]),
     "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, vp]),
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp,

@@ -14,7 +14,7 @@ from ._cabi import lib, check, ptr, stream_ptr, dtype_code
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-KERNELS_PER_CALL = {"amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
+KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
                     "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 1, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
                     "amoe_ep_pack": 1, "amoe_ep_unpack": 1}
@@ -237,11 +237,17 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
              ir: Optional[torch.Tensor] = None, absmax: Optional[torch.Tensor] = None, inp_res: float = -1.0,
              noise: Optional[torch.Tensor] = None, noise_std: float = 0.0, seed: int = 0, offset: int = 0,
              step_dev: Optional[torch.Tensor] = None, out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
-             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None):
+             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
+             want_out: bool = True, row_meta: Optional[dict] = None):
+    """Returns (out or None, codes or None).  `row_meta` (a dict) receives `row_scale` [dst_rows] and
+    `row_expert` [dst_rows], from which, with the codes, the output rows can be rebuilt."""
     x2 = _rows(x2)
     dev = x2.device
-    out = torch.empty(dst_rows, pw.N, dtype=out_dtype or x2.dtype, device=dev)
+    out = torch.empty(dst_rows, pw.N, dtype=out_dtype or x2.dtype, device=dev) if want_out else None
     codes = torch.empty(dst_rows, pw.N, dtype=torch.int8, device=dev) if want_codes else None
+    if row_meta is not None:
+        row_meta["row_scale"] = torch.empty(dst_rows, dtype=torch.float32, device=dev)
+        row_meta["row_expert"] = torch.empty(dst_rows, dtype=torch.int32, device=dev)
     a = A.CvmmArgs()
     a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
     a.expert_offsets = ptr(offsets)
@@ -258,7 +264,11 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     a.col_scale = ptr(pw.col_scale)
     a.col_inv_scale = ptr(pw.col_inv_scale)
     a.out_res, a.out_bound = float(out_res), float(out_bound)
-    a.out, a.out_dtype, a.out_stride, a.out_codes = ptr(out), dtype_code(out), out.stride(0), ptr(codes)
+    if out is not None:
+        a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
+    a.out_codes = ptr(codes)
+    if row_meta is not None:
+        a.out_row_scale, a.out_row_expert = ptr(row_meta["row_scale"]), ptr(row_meta["row_expert"])
     a.dev_status = ptr(status)
     _call("amoe_cvmm_fwd", C.byref(a), stream_ptr())
     return out, codes
@@ -346,6 +356,23 @@ def row_dot(res: torch.Tensor, g: torch.Tensor, k: int, row_index: Optional[torc
     _call("amoe_row_dot", ptr(res), dtype_code(res), res.stride(0), ptr(row_index), ptr(g), dtype_code(g), g.stride(0), P, k, N,
                            ptr(d), stream_ptr())
     return d
+
+
+def row_dot_codes(codes: torch.Tensor, col_scale: torch.Tensor, row_expert: torch.Tensor, row_scale: torch.Tensor,
+                  step: float, g: torch.Tensor, k: int) -> torch.Tensor:
+    g = _rows(g)
+    P, N = codes.shape
+    d = torch.empty(P, dtype=torch.float32, device=codes.device)
+    _call("amoe_row_dot_codes", ptr(codes), ptr(col_scale), ptr(row_expert), ptr(row_scale), float(step), ptr(g),
+          dtype_code(g), g.stride(0), P, k, N, ptr(d), stream_ptr())
+    return d
+
+
+def adc_step(out_res: float, out_bound: float) -> float:
+    """2 * out_bound * res in fp32 arithmetic (the value the kernels use)."""
+    f = torch.tensor
+    res = (f(1.0, dtype=torch.float32) / f(out_res, dtype=torch.float32)) if out_res > 1.0 else f(out_res, dtype=torch.float32)
+    return float(f(2.0, dtype=torch.float32) * f(out_bound, dtype=torch.float32) * res)
 
 
 def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_range: Optional[torch.Tensor], E: int,

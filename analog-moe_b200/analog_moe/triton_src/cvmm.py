@@ -85,6 +85,8 @@ class CVMMExt:
     save_codes: bool = False                # keep ADC codes (int8) on `last_codes`
     last_codes: Optional[torch.Tensor] = field(default=None, repr=False)
     check_status: bool = False              # synchronise and raise on device-side index/wait errors
+    adc_codes_path: bool = True             # with ADC and a gate-weighted reduction keep the per-slot rows as int8
+                                            # codes (4x less HBM traffic); False materialises them in x.dtype
 
 
 def _uses_abs_max(ir_params, io_params) -> bool:
@@ -144,35 +146,47 @@ class CVMM(torch.autograd.Function):
 
         dst = sel_index_i if out_index_i is None else out_index_i
         adc_on = ext.out_res > 0 and ext.out_bound > 0
+        codes_path = adc_on and reduction_weight is not None and ext.adc_codes_path
+        row_meta = {} if codes_path else None
         res, codes = ops.cvmm_fwd(
             x2, sel_index_i, dst, offsets, pw, precision, P=P, dst_rows=P, ir=ir, absmax=absmax,
             inp_res=float(inp_res), noise=noise_t, noise_std=noise_std, seed=seed, offset=offset, step_dev=step_dev,
             out_res=ext.out_res if adc_on else -1.0, out_bound=ext.out_bound if adc_on else -1.0,
-            want_codes=adc_on and ext.save_codes, status=status)
+            want_codes=codes_path or (adc_on and ext.save_codes), status=status, want_out=not codes_path,
+            row_meta=row_meta)
         if ext.save_codes:
             ext.last_codes = codes
 
+        res_into_reduction = None
+        row_scale = row_expert = None
+        adc_step = ops.adc_step(ext.out_res, ext.out_bound) if adc_on else 0.0
         if reduction_weight is not None:
             k = reduction_weight.shape[-1]
-            res_into_reduction = res.view(*reduction_weight.shape, N)
-            out = ops.combine(res, reduction_weight, P // k, k).view(*reduction_weight.shape[:-1], N)   # cvmm.py:757-759
+            if codes_path:
+                # y[t] = sum_j gate * ((code*step)*col_scale)*row_scale, straight from the int8 codes
+                row_scale, row_expert = row_meta["row_scale"], row_meta["row_expert"]
+                out = ops.combine_codes(codes, pw.col_scale, row_expert, row_scale, adc_step, reduction_weight, P // k, k,
+                                        out_dtype=x.dtype).view(*reduction_weight.shape[:-1], N)
+            else:
+                res_into_reduction = res.view(*reduction_weight.shape, N)
+                out = ops.combine(res, reduction_weight, P // k, k).view(*reduction_weight.shape[:-1], N)   # cvmm.py:757-759
         else:
-            res_into_reduction = None
             out = res.view(*sel.shape, N)
         if status is not None:
             ops.raise_on_device_status(status, "CVMM.forward")
 
         ctx.save_for_backward(x, sel_i, sel_index_i, out_index_i, reduction_weight, ir, res_into_reduction, offsets,
-                              pw.w if precision == A.PREC_FP32_SIMT else None, pw.bwd_hi, pw.bwd_lo, pw.col_scale)
+                              pw.w if precision == A.PREC_FP32_SIMT else None, pw.bwd_hi, pw.bwd_lo, pw.col_scale,
+                              codes if codes_path else None, row_scale, row_expert)
         ctx.meta = (E, K, N, precision, ir_params, keys.dtype, broadcasted_input_ranges.shape if ir is not None else None,
-                    ext.check_status)
+                    ext.check_status, adc_step)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
         (x, sel_i, sel_index_i, out_index_i, reduction_weight, ir, res_into_reduction, offsets, w_mod, bwd_hi, bwd_lo,
-         col_scale) = ctx.saved_tensors
-        E, K, N, precision, ir_params, keys_dtype, ir_shape, check_status = ctx.meta
+         col_scale, codes, row_scale, row_expert) = ctx.saved_tensors
+        E, K, N, precision, ir_params, keys_dtype, ir_shape, check_status, adc_step = ctx.meta
         ops.set_tag("down" if reduction_weight is not None else "up")
         dev = x.device
         P = sel_i.numel()
@@ -231,7 +245,11 @@ class CVMM(torch.autograd.Function):
                     ir_slot = ir_slot + decay * ir * (pct > ir_params.input_min_percentage).float()
                 grad_ir = ir_slot.view(ir_shape)
         if down and ctx.needs_input_grad[7]:
-            grad_gate = ops.row_dot(res_into_reduction, g, k).view_as(reduction_weight).to(reduction_weight.dtype)  # cvmm.py:889
+            if codes is not None:
+                d = ops.row_dot_codes(codes, col_scale, row_expert, row_scale, adc_step, g, k)
+            else:
+                d = ops.row_dot(res_into_reduction, g, k)                                     # cvmm.py:889
+            grad_gate = d.view_as(reduction_weight).to(reduction_weight.dtype)
         if status is not None:
             ops.raise_on_device_status(status, "CVMM.backward")
         return (grad_x if need_x else None, None, None, grad_w, None, grad_ir if need_ir else None, None, grad_gate,

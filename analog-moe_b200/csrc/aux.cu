@@ -88,6 +88,29 @@ __global__ void row_dot_kernel(const TR* __restrict__ res, int64_t res_stride, c
   if (lane == 0) d[s] = acc;
 }
 
+// d[s] = sum_n ((code*step)*col_scale[e,n])*row_scale[s] * g[s/k,n]; one warp per slot.
+template <typename TG>
+__global__ void row_dot_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
+                                     const int32_t* __restrict__ row_expert, const float* __restrict__ row_scale,
+                                     float step, const TG* __restrict__ g, int64_t g_stride, int64_t P, int k, int N,
+                                     float* __restrict__ d) {
+  const int lane = threadIdx.x & 31;
+  const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (s >= P) return;
+  const int8_t* r = codes + s * N;
+  const float* cs = col_scale + static_cast<int64_t>(row_expert[s]) * N;
+  const float rs = row_scale ? row_scale[s] : 1.f;
+  const TG* gr = g + (s / k) * g_stride;
+  float acc = 0.f;
+  for (int n = lane; n < N; n += 32) {
+    const float v = ((static_cast<float>(r[n]) * step) * cs[n]) * rs;
+    acc = fmaf(v, to_f32<TG>(gr[n]), acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) d[s] = acc;
+}
+
 // One warp per expert: ordered (lane-strided, then butterfly) sum of the expert's slot gradients.
 __global__ void ir_grad_reduce_kernel(const float* __restrict__ slot_grad, const int32_t* __restrict__ offsets,
                                       const float* __restrict__ input_range, int E, float decay, float min_pct,
@@ -296,6 +319,26 @@ int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const i
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("row_dot");
+  return AMOE_OK;
+}
+
+int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_t* row_expert, const float* row_scale,
+                       float step, const void* g, int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N,
+                       float* d, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(codes && col_scale && row_expert && g && d, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
+  const unsigned blocks = blocks_for(P * 32, 256);
+  if (g_dtype == AMOE_F32)
+    row_dot_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
+                                                            reinterpret_cast<const float*>(g), g_stride, P, k, N, d);
+  else if (g_dtype == AMOE_BF16)
+    row_dot_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
+                                                                    reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
+                                                                    P, k, N, d);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("row_dot_codes");
   return AMOE_OK;
 }
 

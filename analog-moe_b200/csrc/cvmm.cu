@@ -11,7 +11,7 @@ int check_common(const amoe_cvmm_args* a) {
   AMOE_REQUIRE(a != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->P > 0 && a->E > 0 && a->K > 0 && a->N > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(a->P < (int64_t{1} << 31) && a->E <= 65535, AMOE_ERR_BAD_SHAPE);
-  AMOE_REQUIRE(a->expert_offsets && a->a && a->a_row && a->dst_row && a->out, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(a->expert_offsets && a->a && a->a_row && a->dst_row && (a->out || a->out_codes), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->a_dtype == AMOE_F32 || a->a_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->out_dtype == AMOE_F32 || a->out_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->a_rows > 0 && a->dst_rows > 0, AMOE_ERR_BAD_SHAPE);
@@ -62,9 +62,10 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.a_rows = a->a_rows; e.dst_rows = a->dst_rows;
   e.acc_mul = 1.f;
   e.out = a->out; e.out_dtype = a->out_dtype; e.out_stride = a->out_stride; e.out_codes = a->out_codes;
+  e.out_row_scale = a->out_row_scale; e.out_row_expert = a->out_row_expert;
   e.status = a->dev_status;
   e.vec4 = (a->N % 4 == 0) && al16(a->col_scale) && al16(a->col_inv_scale) && al16(a->noise) && al16(a->out) &&
-           (a->out_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(a->out_codes) & 3u) == 0);
+           (a->out_stride % 4 == 0) && al16(a->out_codes);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, false, e, stream);
   return launch_cvmm_tc(a, false, e, stream);
 }
@@ -88,6 +89,7 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   AMOE_REQUIRE(!a->ir_grad || a->x_ref, AMOE_ERR_NULL_POINTER);
   e.row_scale = a->row_scale; e.ir_grad = a->ir_grad; e.relative = a->ir_grad_relative;
   e.grad_scale = a->ir_grad_scale; e.keep_count = a->keep_count;
+  AMOE_REQUIRE(a->out != nullptr, AMOE_ERR_NULL_POINTER);
   e.status = a->dev_status;
   e.vec4 = (a->K % 4 == 0) && al16(a->out) && (a->out_stride % 4 == 0) &&
            (!a->x_ref || (al16(a->x_ref) && a->x_ref_stride % 4 == 0));

@@ -22,6 +22,7 @@ struct EpiParams {
   int64_t a_rows, dst_rows;
   float acc_mul;        // multiplies the raw accumulator (the DAC resolution when A holds integer codes)
   void* out; int out_dtype; int64_t out_stride; int8_t* out_codes;
+  float* out_row_scale; int32_t* out_row_expert;
   // input gradient
   const void* x_ref; int x_ref_dtype; int64_t x_ref_stride; int64_t x_ref_rows; const int32_t* x_ref_row;
   const float* row_scale; float* ir_grad; int relative; float grad_scale;
@@ -141,7 +142,9 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
     }
   }
   const int64_t base = c.dst * p.out_stride + n0;
-  if (vec && p.out_dtype == AMOE_F32) {
+  if (p.out == nullptr) {
+    // codes only
+  } else if (vec && p.out_dtype == AMOE_F32) {
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = make_float4(o[0], o[1], o[2], o[3]);
   } else if (vec) {
     __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
@@ -167,6 +170,13 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
         if (n0 + j < p.n_out) p.out_codes[c.dst * p.n_out + n0 + j] = static_cast<int8_t>(code[j]);
     }
   }
+}
+
+// Per-row side outputs of the forward epilogue (written once per row by its owner).
+__device__ __forceinline__ void epi_row_side_outputs(const EpiParams& p, const RowCtx& c) {
+  if (p.is_dx || !c.valid) return;
+  if (p.out_row_scale) p.out_row_scale[c.dst] = c.absmax * c.ir;
+  if (p.out_row_expert) p.out_row_expert[c.dst] = c.e;
 }
 
 // After the last column: per-row results of the input-gradient epilogue (dir_acc already complete).

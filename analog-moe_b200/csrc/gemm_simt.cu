@@ -58,7 +58,10 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
   const int ty = tid >> 4, tx = tid & 15;
   // row-owner role
   RowCtx ctx;
-  if (tid < kTM) ctx = epi_row_begin(p.epi, static_cast<int64_t>(row0) + tid, e, tid < rows);
+  if (tid < kTM) {
+    ctx = epi_row_begin(p.epi, static_cast<int64_t>(row0) + tid, e, tid < rows);
+    epi_row_side_outputs(p.epi, ctx);
+  }
 
   for (int n0 = 0; n0 < p.Nout; n0 += kTN) {
     float acc[4][4];

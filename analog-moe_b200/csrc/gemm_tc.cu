@@ -296,6 +296,7 @@ struct QuadRows {
 };
 
 __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr, int n0, float v[16], int lane) {
+  if (p.out == nullptr) return;     // codes only (uniform across the kernel)
   quad_transpose(v, lane);
   const int col = n0 + 4 * (lane & 3);
 #pragma unroll
@@ -337,8 +338,16 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
       v[4 * qd + j] = acc * post;
     }
   }
-  if (p.out_codes && c.valid)
-    *reinterpret_cast<uint4*>(p.out_codes + c.dst * p.n_out + n0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  if (p.out_codes && c.valid) {
+    // 16 codes of the row; a row starts on a 16-byte boundary only if n_out is a multiple of 16
+    int8_t* dstc = p.out_codes + c.dst * p.n_out + n0;
+    if ((p.n_out & 15) == 0) {
+      *reinterpret_cast<uint4*>(dstc) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    } else {
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) *reinterpret_cast<uint32_t*>(dstc + 4 * qd) = pk[qd];   // n_out % 4 == 0
+    }
+  }
   store16_t(p, qr, n0, v, lane);
 }
 
@@ -482,6 +491,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       if (!ti.get(t, e, row0, rows)) break;
       const int64_t i = static_cast<int64_t>(row0) + r;
       RowCtx ctx = epi_row_begin(p.epi, i, e, r < rows);
+      if (grp == 0) epi_row_side_outputs(p.epi, ctx);
       QuadRows qr;
       if (EPI != kEpiGeneric) {
         const int my_dst = ctx.valid ? static_cast<int>(ctx.dst) : -1;

@@ -172,8 +172,11 @@ typedef struct amoe_cvmm_args {
   /* ADC */
   float out_res, out_bound;       /* out_res<=0: off */
   /* outputs */
-  void* out; int32_t out_dtype; int64_t out_stride;
+  void* out; int32_t out_dtype; int64_t out_stride;   /* may be NULL when out_codes is given */
   int8_t* out_codes;              /* [dst_rows,N] or NULL */
+  float* out_row_scale;           /* [dst_rows] or NULL: absmax*ir of the row, so that
+                                     out[c,n] = ((code*step)*col_scale[e,n])*out_row_scale[c] */
+  int32_t* out_row_expert;        /* [dst_rows] or NULL: expert of the row */
   /* backward-only (amoe_cvmm_dx) */
   const void* x_ref; int32_t x_ref_dtype; int64_t x_ref_stride; int64_t x_ref_rows;
   const int32_t* x_ref_row;       /* [P] row of x_ref for sorted position i */
@@ -236,6 +239,11 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
                        int64_t y_stride, amoe_stream_t stream);
 int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const void* g,
                  int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream);
+/* amoe_row_dot_codes: the same gate gradient with the rows given as ADC codes:
+ *   d[s] = sum_n ((codes[s,n]*step)*col_scale[row_expert[s],n])*row_scale[s] * g[s/k,n]. */
+int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_t* row_expert, const float* row_scale,
+                       float step, const void* g, int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N,
+                       float* d, amoe_stream_t stream);
 int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range,
                         int32_t E, float decay, float min_percentage, const unsigned long long* keep_count,
                         double total_elements, float* out, amoe_stream_t stream);
