@@ -49,14 +49,14 @@ class CvmmArgs(C.Structure):
         ("a_row", vp), ("a_row_div", C.c_int32), ("dst_row", vp), ("dst_rows", C.c_int64),
         ("w", vp), ("w_dtype", C.c_int32), ("w_stride_e", C.c_int64), ("w_stride_k", C.c_int64),
         ("w_stride_n", C.c_int64), ("w_hi", vp), ("w_lo", vp),
-        ("ir", vp), ("a_absmax", vp), ("inp_res", C.c_float),
+        ("ir", vp), ("ir_by_expert", C.c_int32), ("a_absmax", vp), ("inp_res", C.c_float),
         ("noise", vp), ("noise_std", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32), ("step_dev", vp),
         ("col_scale", vp),
         ("col_inv_scale", vp), ("out_res", C.c_float), ("out_bound", C.c_float),
         ("out", vp), ("out_dtype", C.c_int32), ("out_stride", C.c_int64), ("out_codes", vp),
-        ("out_row_scale", vp), ("out_row_expert", vp),
+        ("out_row_scale", vp), ("out_row_expert", vp), ("out_relu", C.c_int32),
         ("x_ref", vp), ("x_ref_dtype", C.c_int32), ("x_ref_stride", C.c_int64), ("x_ref_rows", C.c_int64),
-        ("x_ref_row", vp),
+        ("x_ref_row", vp), ("x_ref_relu", C.c_int32),
         ("row_scale", vp), ("ir_grad", vp), ("ir_grad_relative", C.c_int32), ("ir_grad_scale", C.c_float),
         ("keep_count", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
@@ -67,7 +67,7 @@ class DwArgs(C.Structure):
     _fields_ = [
         ("P", C.c_int64), ("E", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("precision", C.c_int32),
         ("expert_offsets", vp),
-        ("x", vp), ("x_dtype", C.c_int32), ("x_stride", C.c_int64), ("x_rows", C.c_int64), ("x_row", vp), ("ir", vp),
+        ("x", vp), ("x_dtype", C.c_int32), ("x_stride", C.c_int64), ("x_rows", C.c_int64), ("x_row", vp), ("ir", vp), ("ir_by_expert", C.c_int32),
         ("g", vp), ("g_dtype", C.c_int32), ("g_stride", C.c_int64), ("g_rows", C.c_int64), ("g_row", vp),
         ("g_div", C.c_int32), ("g_scale", vp), ("dw", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
@@ -84,6 +84,7 @@ SIGNATURES = {
     "amoe_select_sort_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "amoe_select_sort": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp, vp, vp, vp, vp, vp,
                                    C.c_size_t, vp]),
+    "amoe_gate_backward": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
     "amoe_expert_offsets": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "amoe_weight_prepass_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "amoe_prepared_dims": (None, [C.c_int32, C.c_int32, C.POINTER(C.c_int32 * 4)]),

@@ -47,6 +47,177 @@ def _enum_name(v) -> str:
     return getattr(v, "name", str(v)).split(".")[-1]
 
 
+def _is_relu(fn) -> bool:
+    return fn in (F.relu, torch.relu) or isinstance(fn, nn.ReLU)
+
+
+class _FusedAnalogStep(torch.autograd.Function):
+    """The whole layer (router matmul excepted: it stays a torch matmul) as one autograd node that calls the
+    library directly.  Same arithmetic as the composition route() -> CVMM (up) -> ReLU -> CVMM (down), with
+    the glue that the composition leaves to torch folded into the kernels:
+
+      * input ranges are read per expert inside the kernels (no per-slot broadcast tensor),
+      * the ReLU runs in the up-projection's epilogue and its backward in the down-projection's input-gradient
+        epilogue,
+      * the input-range decay term and the per-expert sum are one reduction kernel,
+      * the gate gradient goes back to the logits in one kernel.
+
+    Reference lines as for CVMM.forward / CVMM.backward (cvmm.py:700-897) and the layer's forward
+    (moe_layer_aihwkit_lightning.py:384-410, 412-517)."""
+
+    @staticmethod
+    def forward(ctx, layer, x, w_sel, keys, values, input_range):
+        import os
+        cfg = layer.rpu_config
+        fwd, ir_p = cfg.forward, cfg.pre_post.input_range
+        bsz, seq, D = x.shape
+        k, E = layer.n_heads, layer.n_experts
+        T = bsz * seq
+        P = T * k
+        x2 = x.reshape(T, D)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        precision = layer._precision(x)
+        logits = F.linear(x2, w_sel)
+        if getattr(layer, "router_bias", None) is not None:
+            logits = logits + layer.router_bias
+        logits = logits.float()
+        ops.set_tag("up")
+        r = ops.select_sort(logits, k, apply_sigmoid=True)
+        inp_res = fwd.inp_res
+        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
+        if os.environ.get("_AIHWKIT_NO_ROUNDING", False):
+            assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
+            inp_res = -1.0
+        adc_on = fwd.out_res > 0 and fwd.out_bound > 0
+        out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
+        per_channel = bool(getattr(fwd, "out_noise_per_channel", True))
+        has_ir = input_range is not None
+        ir_all = input_range.detach().float().contiguous() if has_ir else None
+
+        def prepass(w, mod):
+            return ops.weight_prepass(
+                w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
+                noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,
+                seed=mod.seed if mod else 0, offset=mod.offset if mod else 0, step_dev=mod.step if mod else None,
+                need_fwd=True, need_bwd=True)
+
+        def noise_args():
+            if layer.training and fwd.out_noise > 0:
+                return dict(noise_std=float(fwd.out_noise), seed=layer.noise_seed, offset=layer._next_offset(),
+                            step_dev=layer.noise_step)
+            return {}
+
+        # ---- up-projection (+ ReLU)
+        nz = noise_args()
+        pw_up = prepass(keys, layer._weight_modifier())
+        ir_up = ir_all[0] if has_ir else None
+        am_up = None if has_ir else ops.row_absmax(x2)
+        h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
+                            ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
+                            out_bound=out_bound, out_relu=True, **nz)
+        # ---- down-projection and the gate-weighted sum over k
+        ops.set_tag("down")
+        nz = noise_args()
+        pw_dn = prepass(values, layer._weight_modifier())
+        ir_dn = ir_all[1] if has_ir else None
+        am_dn = None if has_ir else ops.row_absmax(h)
+        # the composition hands the gate over in the activation dtype (rounded for bf16 layers)
+        gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
+        N = values.shape[-1]
+        adc_step = ops.adc_step(out_res, out_bound) if adc_on else 0.0
+        res = codes = row_scale = row_expert = None
+        if adc_on:
+            meta = {}
+            _, codes = ops.cvmm_fwd(h, r.slot_index, r.slot_index, r.expert_offsets, pw_dn, precision, P=P, dst_rows=P,
+                                    ir=ir_dn, ir_by_expert=True, absmax=am_dn, inp_res=inp_res, out_res=out_res,
+                                    out_bound=out_bound, want_codes=True, want_out=False, row_meta=meta, **nz)
+            row_scale, row_expert = meta["row_scale"], meta["row_expert"]
+            y = ops.combine_codes(codes, pw_dn.col_scale, row_expert, row_scale, adc_step, gate, T, k, out_dtype=x.dtype)
+        else:
+            res, _ = ops.cvmm_fwd(h, r.slot_index, r.slot_index, r.expert_offsets, pw_dn, precision, P=P, dst_rows=P,
+                                  ir=ir_dn, ir_by_expert=True, absmax=am_dn, inp_res=inp_res, **nz)
+            y = ops.combine(res, gate, T, k)
+        simt = precision == ops.A.PREC_FP32_SIMT
+        ctx.save_for_backward(x2, w_sel, h, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, ir_all,
+                              pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
+                              pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
+                              codes, row_scale, row_expert, res)
+        ctx.meta = (x.shape, E, k, precision, ir_p, keys.dtype, values.dtype, adc_step, keys.shape, values.shape,
+                    input_range.dtype if has_ir else None)
+        return y.view(bsz, seq, N)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (x2, w_sel, h, gate, raw_sel, token_index, slot_index, offsets, ir_all, w_up, up_hi, up_lo, up_cs,
+         w_dn, dn_hi, dn_lo, dn_cs, codes, row_scale, row_expert, res) = ctx.saved_tensors
+        x_shape, E, k, precision, ir_p, keys_dtype, values_dtype, adc_step, kshape, vshape, ir_dtype = ctx.meta
+        T, D = x2.shape
+        P = T * k
+        Fh, N = vshape[1], vshape[2]
+        need_x, need_sel, need_keys, need_values, need_ir = (ctx.needs_input_grad[i] for i in (1, 2, 3, 4, 5))
+        has_ir = ir_all is not None
+        need_ir = need_ir and has_ir
+        g = gy.reshape(T, N)
+        if g.stride(-1) != 1:
+            g = g.contiguous()
+        pw_up = ops.PreparedWeights(E, kshape[1], kshape[2], up_cs, w=w_up, bwd_hi=up_hi, bwd_lo=up_lo)
+        pw_dn = ops.PreparedWeights(E, vshape[1], vshape[2], dn_cs, w=w_dn, bwd_hi=dn_hi, bwd_lo=dn_lo)
+        decay = float(getattr(ir_p, "decay", 0.0) or 0.0) if has_ir else 0.0
+        min_pct = float(getattr(ir_p, "input_min_percentage", 0.95))
+        relative = bool(getattr(ir_p, "gradient_relative", True))
+        gscale = float(getattr(ir_p, "gradient_scale", 1.0)) if relative else 1.0
+        keeps = torch.zeros(2, dtype=torch.int64, device=x2.device) if (has_ir and decay > 0) else None
+        ir_up, ir_dn = (ir_all[0], ir_all[1]) if has_ir else (None, None)
+
+        # ---- down-projection
+        ops.set_tag("down")
+        grad_values = None
+        if need_values:
+            grad_values = ops.cvmm_dw(h, slot_index, g, slot_index, offsets, E, precision, P=P, ir=ir_dn,
+                                      ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1)).to(values_dtype)
+        dh, irs_dn = ops.cvmm_dx(g, slot_index, slot_index, offsets, pw_dn, precision, P=P, dst_rows=P, a_row_div=k,
+                                 x_ref=h, x_ref_row=slot_index, ir=ir_dn, ir_by_expert=True, row_scale=gate.reshape(-1),
+                                 want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
+                                 keep_count=keeps[1:] if keeps is not None else None, out_dtype=h.dtype,
+                                 x_ref_relu=True)
+        if codes is not None:
+            dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
+        else:
+            dgate = ops.row_dot(res, g, k)
+        # ---- up-projection
+        ops.set_tag("up")
+        grad_keys = None
+        if need_keys:
+            grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
+                                    ir_by_expert=True).to(keys_dtype)
+        grad_x = irs_up = None
+        if need_x or need_ir:
+            dxr, irs_up = ops.cvmm_dx(dh, slot_index, slot_index, offsets, pw_up, precision, P=P, dst_rows=P,
+                                      x_ref=x2 if has_ir else None, x_ref_row=token_index if has_ir else None,
+                                      ir=ir_up, ir_by_expert=True, want_ir_grad=has_ir, relative=relative,
+                                      grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
+                                      out_dtype=x2.dtype)
+            if need_x:
+                grad_x = ops.combine(dxr, None, T, k)
+        # ---- router
+        grad_sel = None
+        if need_sel or need_x:
+            dlogits = ops.gate_backward(dgate, gate, raw_sel, w_sel.shape[0]).to(x2.dtype)
+            if need_sel:
+                grad_sel = dlogits.t() @ x2
+            if need_x:
+                grad_x.addmm_(dlogits, w_sel)
+        grad_ir = None
+        if need_ir:
+            grad_ir = torch.stack([
+                ops.ir_grad_reduce(irs_up, offsets, ir_up, E, decay, min_pct, keeps[:1] if keeps is not None else None,
+                                   float(P) * D),
+                ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
+                                   float(P) * Fh)]).to(ir_dtype)
+        return (None, grad_x.view(x_shape) if need_x else None, grad_sel, grad_keys, grad_values, grad_ir)
+
+
 class SigmaMoELayer(nn.Module):
     def __init__(self, d_model: int, n_experts: int, expert_size: int, k: int, dropout: float = 0.0,
                  selection_mode: str = "sigmoid", activation_after_topk: bool = False,
@@ -142,6 +313,8 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.precision = precision
         self.noise_seed = noise_seed
         self.register_buffer("noise_step", torch.zeros((), dtype=torch.int64), persistent=True)
+        self.register_buffer("_aux_zero", torch.zeros(()), persistent=False)
+        self.fused = True          # one autograd node for the whole layer when the configuration allows it
         self._noise_calls = 0
         ir = self.rpu_config.pre_post.input_range
         self.input_range = None
@@ -216,9 +389,29 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         return CVMM.apply(inputs, sel_indices.sel_index, sel_indices.sel, weights, inp_res, bir,
                           sel_indices.out_index, sel_indices.reduction_weight, None, ir_p, cfg.forward, ext)
 
+    def _fused_ok(self, inp: Tensor) -> bool:
+        """The single-node path covers the common configuration; anything else takes the composition."""
+        if not self.fused or type(self).cvmm_wrapper is not AnalogSigmaMoELayer.cvmm_wrapper:
+            return False
+        if not (inp.is_cuda and inp.ndim == 3 and _is_relu(self.activation)) or self.bias is not None:
+            return False
+        if self.dropout > 0 and self.training:
+            return False
+        if torch.is_autocast_enabled() or inp.dtype not in (torch.float32, torch.bfloat16):
+            return False
+        ir_p = self.rpu_config.pre_post.input_range
+        if self.input_range is not None and self.training and ir_p.init_from_data > 0 and \
+                float(self.input_range_update_idx) < ir_p.init_from_data:
+            return False          # the data-driven initialisation of the input ranges runs in the composition
+        return True
+
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
         self._noise_calls = 0
-        out = super().forward(inp)
+        if self._fused_ok(inp):
+            y = _FusedAnalogStep.apply(self, inp, self.expert_sel.weight, self.keys, self.values, self.input_range)
+            out = (y, self._aux_zero)
+        else:
+            out = super().forward(inp)
         if self.training:
             self.noise_step += 1
         return out

@@ -125,6 +125,16 @@ def select_sort(logits: torch.Tensor, k: int, apply_sigmoid: bool = True) -> Rou
     return Routing(raw_sel, gate, sel, tok, slot, off)
 
 
+def gate_backward(dgate: torch.Tensor, gate: torch.Tensor, raw_sel: torch.Tensor, E: int,
+                  apply_sigmoid: bool = True) -> torch.Tensor:
+    """dlogits [T,E] fp32 from the gradient of the k picked gate values."""
+    k = raw_sel.shape[-1]
+    T = raw_sel.numel() // k
+    dl = torch.empty(T, E, dtype=torch.float32, device=raw_sel.device)
+    _call("amoe_gate_backward", ptr(dgate), ptr(gate), ptr(raw_sel), T, E, k, int(apply_sigmoid), ptr(dl), stream_ptr())
+    return dl
+
+
 def expert_offsets(sel_sorted: torch.Tensor, n_experts: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     sel_sorted = i32(sel_sorted)
     off = torch.empty(n_experts + 1, dtype=torch.int32, device=sel_sorted.device)
@@ -238,7 +248,8 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
              noise: Optional[torch.Tensor] = None, noise_std: float = 0.0, seed: int = 0, offset: int = 0,
              step_dev: Optional[torch.Tensor] = None, out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
              out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
-             want_out: bool = True, row_meta: Optional[dict] = None):
+             want_out: bool = True, row_meta: Optional[dict] = None, ir_by_expert: bool = False,
+             out_relu: bool = False):
     """Returns (out or None, codes or None).  `row_meta` (a dict) receives `row_scale` [dst_rows] and
     `row_expert` [dst_rows], from which, with the codes, the output rows can be rebuilt."""
     x2 = _rows(x2)
@@ -255,6 +266,7 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     a.a_row, a.a_row_div, a.dst_row, a.dst_rows = ptr(a_row), a_row_div, ptr(dst_row), dst_rows
     _fill_weights(a, pw, precision, backward=False)
     a.ir, a.a_absmax, a.inp_res = ptr(ir), ptr(absmax), float(inp_res)
+    a.ir_by_expert, a.out_relu = int(ir_by_expert), int(out_relu)
     if noise is not None:
         noise = noise.reshape(-1, pw.N).float().contiguous()
         assert noise.shape[0] == dst_rows
@@ -279,7 +291,8 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             x_ref: Optional[torch.Tensor] = None, x_ref_row: Optional[torch.Tensor] = None,
             ir: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None, want_ir_grad: bool = False,
             relative: bool = True, grad_scale: float = 1.0, keep_count: Optional[torch.Tensor] = None,
-            out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None):
+            out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
+            ir_by_expert: bool = False, x_ref_relu: bool = False):
     g2 = _rows(g2)
     dev = g2.device
     out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev)
@@ -292,6 +305,7 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     _fill_weights(a, pw, precision, backward=True)
     a.inp_res = -1.0
     a.ir = ptr(ir)
+    a.ir_by_expert, a.x_ref_relu = int(ir_by_expert), int(x_ref_relu)
     a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
     if x_ref is not None:
         x_ref = _rows(x_ref)
@@ -307,7 +321,8 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
 
 def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torch.Tensor, offsets: torch.Tensor,
             E: int, precision: int, *, P: int, ir: Optional[torch.Tensor] = None, g_div: int = 1,
-            g_scale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+            g_scale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+            ir_by_expert: bool = False) -> torch.Tensor:
     x2, g2 = _rows(x2), _rows(g2)
     K, N = x2.shape[1], g2.shape[1]
     dw = torch.empty(E, K, N, dtype=torch.float32, device=x2.device)
@@ -317,6 +332,7 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
     a.x, a.x_dtype, a.x_stride, a.x_rows, a.x_row, a.ir = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0], ptr(x_row), ptr(ir)
     a.g, a.g_dtype, a.g_stride, a.g_rows, a.g_row = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0], ptr(g_row)
     a.g_div, a.g_scale, a.dw = g_div, ptr(g_scale), ptr(dw)
+    a.ir_by_expert = int(ir_by_expert)
     nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device) if nbytes else None
     a.workspace, a.workspace_bytes = ptr(ws), nbytes

@@ -57,7 +57,8 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
     float res = a->out_res > 1.f ? 1.f / a->out_res : a->out_res;
     AMOE_REQUIRE(!a->out_codes || res >= 1.f / 254.5f, AMOE_ERR_UNSUPPORTED);  // codes must fit int8
   }
-  e.a_absmax = a->a_absmax; e.ir = a->ir; e.a_row = a->a_row; e.dst_row = a->dst_row;
+  e.a_absmax = a->a_absmax; e.ir = a->ir; e.ir_by_expert = a->ir_by_expert; e.a_row = a->a_row; e.dst_row = a->dst_row;
+  e.out_relu = a->out_relu;
   e.a_div = a->a_row_div < 1 ? 1 : a->a_row_div;
   e.a_rows = a->a_rows; e.dst_rows = a->dst_rows;
   e.acc_mul = 1.f;
@@ -77,16 +78,18 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   EpiParams e{};
   e.is_dx = 1; e.n_out = a->K;
   e.adc.on = false;
-  e.ir = a->ir; e.a_row = a->a_row; e.dst_row = a->dst_row; e.a_rows = a->a_rows; e.dst_rows = a->dst_rows;
+  e.ir = a->ir; e.ir_by_expert = a->ir_by_expert; e.a_row = a->a_row; e.dst_row = a->dst_row; e.a_rows = a->a_rows; e.dst_rows = a->dst_rows;
+  e.x_ref_relu = a->x_ref_relu;
   e.a_div = a->a_row_div < 1 ? 1 : a->a_row_div;
   e.acc_mul = 1.f;
   e.out = a->out; e.out_dtype = a->out_dtype; e.out_stride = a->out_stride; e.out_codes = nullptr;
   e.x_ref = a->x_ref; e.x_ref_dtype = a->x_ref_dtype; e.x_ref_stride = a->x_ref_stride; e.x_ref_row = a->x_ref_row;
   e.x_ref_rows = a->x_ref_rows;
-  AMOE_REQUIRE(!a->x_ref || (a->x_ref_row && a->ir), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!a->x_ref || (a->x_ref_row && (a->ir || a->x_ref_relu)), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!a->x_ref_relu || a->x_ref, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(!a->x_ref || a->x_ref_rows > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!a->x_ref || a->x_ref_dtype == AMOE_F32 || a->x_ref_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
-  AMOE_REQUIRE(!a->ir_grad || a->x_ref, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!a->ir_grad || (a->x_ref && a->ir), AMOE_ERR_NULL_POINTER);
   e.row_scale = a->row_scale; e.ir_grad = a->ir_grad; e.relative = a->ir_grad_relative;
   e.grad_scale = a->ir_grad_scale; e.keep_count = a->keep_count;
   AMOE_REQUIRE(a->out != nullptr, AMOE_ERR_NULL_POINTER);

@@ -17,7 +17,10 @@ struct EpiParams {
   const float* col_scale;      // [E, n_out]
   const float* col_inv_scale;  // [E, n_out], needed by the ADC
   AdcParams adc;
-  const float* a_absmax; const float* ir;  // by source row / by sorted position
+  const float* a_absmax; const float* ir;  // by source row / by sorted position (by expert if ir_by_expert)
+  int ir_by_expert;
+  int out_relu;         // forward: clamp the result at zero
+  int x_ref_relu;       // input gradient: also zero the result where x_ref <= 0
   const int32_t* a_row; const int32_t* dst_row; int a_div;
   int64_t a_rows, dst_rows;
   float acc_mul;        // multiplies the raw accumulator (the DAC resolution when A holds integer codes)
@@ -57,7 +60,7 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
     c.valid = 0;
     return c;
   }
-  if (p.ir) c.ir = p.ir[i];
+  if (p.ir) c.ir = p.ir[p.ir_by_expert ? e : i];
   if (!p.is_dx) {
     if (p.a_absmax) {
       int64_t r = p.a_row[i] / p.a_div;
@@ -113,6 +116,7 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
       if (p.adc.on) acc = adc_apply(acc, s[j], is[j], p.adc, code[j]);
       if (p.a_absmax && p.ir) acc = (acc * c.absmax) * c.ir;
       else acc *= post;
+      if (p.out_relu) acc = fmaxf(acc, 0.f);
       o[j] = acc;
     }
   } else {
@@ -132,11 +136,14 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
     for (int j = 0; j < 4; ++j) {
       float gs = v[j] * c.rs;
       if (p.x_ref && n0 + j < p.n_out) {
-        const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
-        if (up) c.dir_acc += fminf(gs, 0.f);
-        if (low) c.dir_acc -= fmaxf(gs, 0.f);
-        c.keep += keep ? 1u : 0u;
-        gs = keep ? gs : 0.f;
+        if (p.ir) {
+          const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
+          if (up) c.dir_acc += fminf(gs, 0.f);
+          if (low) c.dir_acc -= fmaxf(gs, 0.f);
+          c.keep += keep ? 1u : 0u;
+          gs = keep ? gs : 0.f;
+        }
+        if (p.x_ref_relu && !(xr[j] > 0.f)) gs = 0.f;
       }
       o[j] = gs;
     }

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
       report(p.epi.status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(li), static_cast<int>(l_src));
       l_ok = false;
     } else {
-      if (has_ir) { l_ir = p.ir[li]; l_rir = __frcp_rn(l_ir); }
+      if (has_ir) { l_ir = p.ir[p.epi.ir_by_expert ? e : li]; l_rir = __frcp_rn(l_ir); }
       if (has_am) { l_am = p.a_absmax[l_src]; l_ram = __frcp_rn(l_am); }
     }
   }
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(256) cvmm_simt_kernel(SimtParams p) {
 struct SimtDwParams {
   int E, K, N;
   const int32_t* offsets;
-  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir;
+  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir; int ir_by_expert;
   const void* g; int g_dtype; int64_t g_stride; int64_t g_rows; const int32_t* g_row; int g_div;
   const float* g_scale;
   float* dw;
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(256) dw_simt_kernel(SimtDwParams p) {
         report(p.status, AMOE_ERR_INDEX_RANGE, 30, i, static_cast<int>(xr));
         ok = false;
       } else {
-        if (p.ir) ir = p.ir[i];
+        if (p.ir) ir = p.ir[p.ir_by_expert ? e : i];
         if (p.g_scale) gs = p.g_scale[gr];
         gr /= p.g_div;
       }
@@ -238,7 +238,7 @@ int launch_dw_simt(const amoe_dw_args* a, cudaStream_t stream) {
   SimtDwParams p;
   p.E = a->E; p.K = a->K; p.N = a->N; p.offsets = a->expert_offsets;
   p.x = a->x; p.x_dtype = a->x_dtype; p.x_stride = a->x_stride; p.x_rows = a->x_rows; p.x_row = a->x_row;
-  p.ir = a->ir;
+  p.ir = a->ir; p.ir_by_expert = a->ir_by_expert;
   p.g = a->g; p.g_dtype = a->g_dtype; p.g_stride = a->g_stride; p.g_rows = a->g_rows; p.g_row = a->g_row;
   p.g_div = a->g_div < 1 ? 1 : a->g_div; p.g_scale = a->g_scale;
   p.dw = a->dw; p.status = a->dev_status;

@@ -335,7 +335,7 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
       float code = 0.f;
       if (adc) acc = adc_apply(acc, sv[j], iv[j], p.adc, code);
       pk[qd] |= (static_cast<uint32_t>(static_cast<int>(code)) & 0xffu) << (8 * j);
-      v[4 * qd + j] = acc * post;
+      v[4 * qd + j] = p.out_relu ? fmaxf(acc * post, 0.f) : acc * post;
     }
   }
   if (p.out_codes && c.valid) {
@@ -372,14 +372,23 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
       xr[4 * i] = t.x; xr[4 * i + 1] = t.y; xr[4 * i + 2] = t.z; xr[4 * i + 3] = t.w;
     }
     quad_transpose(xr, lane);     // back to "my row, 16 columns"
+    if (p.ir) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float gs = v[j] * c.rs;
-      const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
-      if (up) c.dir_acc += fminf(gs, 0.f);
-      if (low) c.dir_acc -= fmaxf(gs, 0.f);
-      c.keep += keep ? 1u : 0u;
-      v[j] = keep ? gs : 0.f;
+      for (int j = 0; j < 16; ++j) {
+        float gs = v[j] * c.rs;
+        const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
+        if (up) c.dir_acc += fminf(gs, 0.f);
+        if (low) c.dir_acc -= fmaxf(gs, 0.f);
+        c.keep += keep ? 1u : 0u;
+        v[j] = keep ? gs : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= c.rs;
+    }
+    if (p.x_ref_relu) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = xr[j] > 0.f ? v[j] : 0.f;
     }
   } else {
 #pragma unroll
@@ -606,7 +615,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             report(status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(i), static_cast<int>(src));
           } else {
             m.src = static_cast<int>(src);
-            if (has_ir) { m.ir = p.ir[i]; m.rcp_ir = __frcp_rn(m.ir); }
+            if (has_ir) { m.ir = p.ir[p.epi.ir_by_expert ? e : i]; m.rcp_ir = __frcp_rn(m.ir); }
             if (has_am) m.am = p.a_absmax[src];
           }
         }
@@ -688,7 +697,7 @@ struct DwMnParams {
   int seg;              // slots per work segment (multiple of 64); 0: one segment per expert
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;   // a_bytes/b_bytes: one precision term of A / B
   const int32_t* offsets;
-  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir;
+  const void* x; int x_dtype; int64_t x_stride; int64_t x_rows; const int32_t* x_row; const float* ir; int ir_by_expert;
   const void* g; int g_dtype; int64_t g_stride; int64_t g_rows; const int32_t* g_row; int g_div;
   const float* g_scale;
   int x_vec_ok, g_vec_ok;
@@ -908,7 +917,7 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
                   else if (col[b] < p.K) {
                     live[b] = true;
                     row_off[b] = xr * p.x_stride;
-                    if (p.ir) aux[b] = p.ir[i];
+                    if (p.ir) aux[b] = p.ir[p.ir_by_expert ? e : i];
                   }
                 } else {
                   col[b] = (nbk * p.NB + tile[b]) * p.BN + c[b] * 8;
@@ -1174,7 +1183,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   p.m_tiles = (a->K + kBM - 1) / kBM;
   p.offsets = a->expert_offsets;
   p.x = a->x; p.x_dtype = a->x_dtype; p.x_stride = a->x_stride; p.x_rows = a->x_rows; p.x_row = a->x_row;
-  p.ir = a->ir;
+  p.ir = a->ir; p.ir_by_expert = a->ir_by_expert;
   p.g = a->g; p.g_dtype = a->g_dtype; p.g_stride = a->g_stride; p.g_rows = a->g_rows; p.g_row = a->g_row;
   p.g_div = a->g_div < 1 ? 1 : a->g_div; p.g_scale = a->g_scale;
   p.x_vec_ok = aligned16(a->x) && ((a->x_stride * (a->x_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);

@@ -194,6 +194,24 @@ __global__ void offsets_from_sorted_kernel(const int32_t* __restrict__ sel, int6
   for (int e = prev + 1; e <= cur; ++e) offsets[e] = static_cast<int32_t>(i);
 }
 
+// dlogits[t,e] = dgate[t,j] * dsigmoid for the slot j of token t that picked expert e, else 0.
+__global__ void gate_backward_kernel(const float* __restrict__ dgate, const float* __restrict__ gate,
+                                     const int32_t* __restrict__ raw_sel, int64_t T, int E, int k, int apply_sigmoid,
+                                     float* __restrict__ dlogits) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= T * E) return;
+  const int64_t t = i / E;
+  const int e = static_cast<int>(i - t * E);
+  float v = 0.f;
+  for (int j = 0; j < k; ++j) {
+    if (raw_sel[t * k + j] == e) {
+      const float g = gate[t * k + j];
+      v = apply_sigmoid ? (dgate[t * k + j] * (1.f - g)) * g : dgate[t * k + j];
+    }
+  }
+  dlogits[i] = v;
+}
+
 }  // namespace
 }  // namespace amoe
 
@@ -246,6 +264,18 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
   scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, expert_offsets, sel_sorted, token_index,
                                                      slot_index);
   AMOE_LAUNCH_CHECK("scatter");
+  return AMOE_OK;
+}
+
+int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw_sel, int64_t T, int32_t E, int32_t k,
+                       int32_t apply_sigmoid, float* dlogits, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(T > 0 && E > 0 && k > 0 && k <= E, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(dgate && gate && raw_sel && dlogits, AMOE_ERR_NULL_POINTER);
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((T * E + threads - 1) / threads);
+  gate_backward_kernel<<<blocks, threads, 0, stream>>>(dgate, gate, raw_sel, T, E, k, apply_sigmoid, dlogits);
+  AMOE_LAUNCH_CHECK("gate_backward");
   return AMOE_OK;
 }
 

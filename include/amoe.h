@@ -77,6 +77,12 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
                      int32_t* slot_index, int32_t* expert_offsets, void* workspace, size_t workspace_bytes,
                      amoe_stream_t stream);
 
+/* Backward of the gate selection: dlogits [T,E] = 0 except dlogits[t, raw_sel[t,j]] = dgate[t,j]*(1-g)*g with
+ * g = gate[t,j] (apply_sigmoid) or dgate[t,j].  Replaces autograd's gather/sigmoid backward of the base layer's
+ * `sigmoid(logits).gather(raw_sel)`; every element of dlogits is written. */
+int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw_sel, int64_t T, int32_t E, int32_t k,
+                       int32_t apply_sigmoid, float* dlogits, amoe_stream_t stream);
+
 /* expert_offsets [E+1] from an already sorted expert-id list (a CVMMSel.sel built elsewhere). */
 int amoe_expert_offsets(const int32_t* sel_sorted, int64_t P, int32_t E, int32_t* expert_offsets,
                         int32_t* dev_status, amoe_stream_t stream);
@@ -159,6 +165,7 @@ typedef struct amoe_cvmm_args {
   const void* w_hi; const void* w_lo;  /* prepared bf16 copies (lo may be NULL) */
   /* DAC */
   const float* ir;                /* [P] by sorted position, or NULL */
+  int32_t ir_by_expert;           /* non-zero: ir holds E values, one per expert (no per-slot broadcast needed) */
   const float* a_absmax;          /* [a_rows] by source row, or NULL */
   float inp_res;                  /* <=0: no quantisation */
   /* output noise */
@@ -177,9 +184,12 @@ typedef struct amoe_cvmm_args {
   float* out_row_scale;           /* [dst_rows] or NULL: absmax*ir of the row, so that
                                      out[c,n] = ((code*step)*col_scale[e,n])*out_row_scale[c] */
   int32_t* out_row_expert;        /* [dst_rows] or NULL: expert of the row */
+  int32_t out_relu;               /* amoe_cvmm_fwd: out = max(out, 0) (the activation between the projections) */
   /* backward-only (amoe_cvmm_dx) */
   const void* x_ref; int32_t x_ref_dtype; int64_t x_ref_stride; int64_t x_ref_rows;
   const int32_t* x_ref_row;       /* [P] row of x_ref for sorted position i */
+  int32_t x_ref_relu;             /* amoe_cvmm_dx: additionally zero out[c,n] where x_ref <= 0 (backward of a ReLU
+                                     that produced x_ref; applied after the input-range gradient is taken) */
   const float* row_scale;         /* [dst_rows] by destination row, or NULL */
   float* ir_grad;                 /* [P] by sorted position, or NULL */
   int32_t ir_grad_relative; float ir_grad_scale;
@@ -209,6 +219,7 @@ typedef struct amoe_dw_args {
   const void* x; int32_t x_dtype; int64_t x_stride; int64_t x_rows;
   const int32_t* x_row;           /* [P] */
   const float* ir;                /* [P] or NULL */
+  int32_t ir_by_expert;           /* non-zero: ir holds E values, one per expert */
   const void* g; int32_t g_dtype; int64_t g_stride; int64_t g_rows;
   const int32_t* g_row;           /* [P] */
   int32_t g_div;                  /* >=1 */

@@ -444,3 +444,55 @@ def test_layer_module_vs_oracle(dev, prec, dtype):
         scale = max(1.0, float(want.abs().max()))
         err = float((got - want).abs().max())
         assert err <= tol * scale, f"{name}: {err:.3e} vs scale {scale:.3g}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prec,dtype,use_ir", [("simt", torch.float32, True), ("split", torch.float32, True),
+                                               ("split", torch.float32, False), ("bf16x1", torch.bfloat16, True)])
+def test_fused_layer_step_equals_the_composition(dev, prec, dtype, use_ir):
+    """The single-node layer step (ReLU, per-expert input ranges, decay term and gate backward folded into the
+    kernels) against the composition route() -> CVMM -> ReLU -> CVMM with every non-ideality on: same Philox
+    draws, same kernels, so everything but summation-order effects of the glue must agree exactly."""
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, WeightModifierType
+    T, D, F, E, k = 384, 160, 96, 8, 3
+    cfg = TorchInferenceRPUConfig()
+    cfg.forward.inp_res = 254.0
+    cfg.forward.out_res = 254.0
+    cfg.forward.out_bound = 12.0
+    cfg.forward.out_noise = 0.03
+    cfg.pre_post.input_range.enable = use_ir
+    cfg.pre_post.input_range.init_value = 2.5
+    cfg.pre_post.input_range.decay = 0.01
+    cfg.pre_post.input_range.input_min_percentage = 0.5
+    cfg.modifier.type = WeightModifierType.ADD_NORMAL_PER_CHANNEL
+    cfg.modifier.std_dev = 0.02
+    torch.manual_seed(3)
+    layer = AnalogSigmaMoELayer(cfg, d_model=D, n_experts=E, expert_size=F, k=k, precision=PRECS[prec],
+                                noise_seed=77).to(dev).to(dtype)
+    layer.train()
+    x0 = torch.randn(2, T // 2, D, device=dev, dtype=dtype)
+    gy = torch.randn(2, T // 2, D, device=dev, dtype=dtype)
+    results = {}
+    for fused in (True, False):
+        layer.fused = fused
+        layer.noise_step.zero_()
+        for p_ in layer.parameters():
+            p_.grad = None
+        x = x0.clone().requires_grad_()
+        y, aux = layer(x)
+        assert float(aux) == 0.0
+        y.backward(gy)
+        torch.cuda.synchronize()
+        results[fused] = dict(y=y.detach().float(), dx=x.grad.float(), dkeys=layer.keys.grad.float(),
+                              dvalues=layer.values.grad.float(), dsel=layer.expert_sel.weight.grad.float(),
+                              dir=layer.input_range.grad.float() if use_ir else torch.zeros(1, device=dev))
+    assert int(layer.noise_step) == 1
+    # the gate comes from the select kernel's sigmoid in one path and from torch.sigmoid in the other (an ulp),
+    # and the router's input gradient is added in a different order
+    tol = 2e-6 if dtype == torch.float32 else 2e-2
+    for key in results[True]:
+        a, b = results[True][key], results[False][key]
+        assert torch.isfinite(a).all(), key
+        scale = max(1.0, float(b.abs().max()))
+        err = float((a - b).abs().max())
+        assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"
