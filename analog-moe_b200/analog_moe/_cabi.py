@@ -150,8 +150,34 @@ def ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_LAUNCH_STREAM = None      # torch.cuda.Stream that overrides the current stream for library launches
+
+
 def stream_ptr() -> int:
+    if _LAUNCH_STREAM is not None:
+        return _LAUNCH_STREAM.cuda_stream
     return torch.cuda.current_stream().cuda_stream
+
+
+class launch_on:
+    """Library calls inside the block are launched on `stream` while torch keeps allocating on the current
+    stream: memory stays owned by the current stream, so its reuse is ordered by the join
+    (`current.wait_stream(stream)`) the caller does afterwards.  The caller also orders `stream` after the
+    current stream before entering (`stream.wait_stream(current)`)."""
+
+    def __init__(self, stream):
+        self.stream = stream
+
+    def __enter__(self):
+        global _LAUNCH_STREAM
+        self.prev = _LAUNCH_STREAM
+        _LAUNCH_STREAM = self.stream
+        return self
+
+    def __exit__(self, *exc):
+        global _LAUNCH_STREAM
+        _LAUNCH_STREAM = self.prev
+        return False
 
 
 def require_cuda(*tensors) -> None:

@@ -78,22 +78,7 @@ class _FusedAnalogStep(torch.autograd.Function):
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         precision = layer._precision(x)
-        logits = F.linear(x2, w_sel)
-        if getattr(layer, "router_bias", None) is not None:
-            logits = logits + layer.router_bias
-        logits = logits.float()
-        ops.set_tag("up")
-        r = ops.select_sort(logits, k, apply_sigmoid=True)
-        inp_res = fwd.inp_res
-        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
-        if os.environ.get("_AIHWKIT_NO_ROUNDING", False):
-            assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
-            inp_res = -1.0
-        adc_on = fwd.out_res > 0 and fwd.out_bound > 0
-        out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
         per_channel = bool(getattr(fwd, "out_noise_per_channel", True))
-        has_ir = input_range is not None
-        ir_all = input_range.detach().float().contiguous() if has_ir else None
 
         def prepass(w, mod):
             return ops.weight_prepass(
@@ -108,9 +93,38 @@ class _FusedAnalogStep(torch.autograd.Function):
                             step_dev=layer.noise_step)
             return {}
 
+        # The two weight pre-passes depend on nothing but the weights: they run on a second stream beside the
+        # router matmul and the select/sort (small kernels that leave most of the GPU idle).
+        nz_up = noise_args()
+        mod_up = layer._weight_modifier()
+        nz_dn = noise_args()
+        mod_dn = layer._weight_modifier()
+        main, side = torch.cuda.current_stream(), ops.side_stream(x.device)
+        side.wait_stream(main)
+        with ops.launch_on(side):
+            ops.set_tag("up")
+            pw_up = prepass(keys, mod_up)
+            ops.set_tag("down")
+            pw_dn = prepass(values, mod_dn)
+        logits = F.linear(x2, w_sel)
+        if getattr(layer, "router_bias", None) is not None:
+            logits = logits + layer.router_bias
+        logits = logits.float()
+        ops.set_tag("up")
+        r = ops.select_sort(logits, k, apply_sigmoid=True)
+        inp_res = fwd.inp_res
+        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
+        if os.environ.get("_AIHWKIT_NO_ROUNDING", False):
+            assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
+            inp_res = -1.0
+        adc_on = fwd.out_res > 0 and fwd.out_bound > 0
+        out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
+        has_ir = input_range is not None
+        ir_all = input_range.detach().float().contiguous() if has_ir else None
+        main.wait_stream(side)
+
         # ---- up-projection (+ ReLU)
-        nz = noise_args()
-        pw_up = prepass(keys, layer._weight_modifier())
+        nz = nz_up
         ir_up = ir_all[0] if has_ir else None
         am_up = None if has_ir else ops.row_absmax(x2)
         h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
@@ -118,8 +132,7 @@ class _FusedAnalogStep(torch.autograd.Function):
                             out_bound=out_bound, out_relu=True, **nz)
         # ---- down-projection and the gate-weighted sum over k
         ops.set_tag("down")
-        nz = noise_args()
-        pw_dn = prepass(values, layer._weight_modifier())
+        nz = nz_dn
         ir_dn = ir_all[1] if has_ir else None
         am_dn = None if has_ir else ops.row_absmax(h)
         # the composition hands the gate over in the activation dtype (rounded for bf16 layers)

@@ -10,12 +10,12 @@ from typing import Optional, Tuple
 import torch
 
 from . import _cabi as A
-from ._cabi import lib, check, ptr, stream_ptr, dtype_code
+from ._cabi import lib, check, ptr, stream_ptr, dtype_code, launch_on
 
 
 # kernels launched by one call of each entry point (for the launch counter)
-KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 4, "amoe_row_absmax": 1,
-                    "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 1, "amoe_combine": 1,
+KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 3, "amoe_row_absmax": 1,
+                    "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 2, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
                     "amoe_ep_pack": 1, "amoe_ep_unpack": 1}
 
@@ -59,13 +59,26 @@ def _call(name: str, *args) -> None:
     if tr.timed:
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
+        st = A._LAUNCH_STREAM if A._LAUNCH_STREAM is not None else torch.cuda.current_stream()
+        e0.record(st)
         check(getattr(lib, name)(*args), name)
-        e1.record()
+        e1.record(st)
         tr.calls.append((name, _TAG, e0, e1))
     else:
         check(getattr(lib, name)(*args), name)
         tr.calls.append((name, _TAG, None, None))
+
+
+_SIDE_STREAMS = {}
+
+
+def side_stream(device: torch.device) -> torch.cuda.Stream:
+    """One extra stream per device for work that can run beside the main chain (the weight pre-passes)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=key)
+    return st
 
 
 def i32(t: torch.Tensor) -> torch.Tensor:
@@ -156,6 +169,7 @@ class PreparedWeights:
     fwd_lo: Optional[torch.Tensor] = None
     bwd_hi: Optional[torch.Tensor] = None
     bwd_lo: Optional[torch.Tensor] = None
+    workspace: Optional[torch.Tensor] = None
 
 
 def prepared_dims(K: int, N: int) -> Tuple[int, int, int, int]:
@@ -213,6 +227,7 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     _call("amoe_weight_prepass", C.byref(a), stream_ptr())
+    out.workspace = ws       # stays alive with the result: the launch stream may differ from the allocating one
     return out
 
 

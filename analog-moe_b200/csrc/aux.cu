@@ -7,93 +7,141 @@
 namespace amoe {
 namespace {
 
-// y[t,n] = sum_j w[t*k+j] * res[t*k+j, n]; thread per (t, 4 columns); j ascending.
+// Four consecutive elements starting at p (16-byte / 8-byte / 4-byte vector load when `vec`, else element by
+// element with `valid` of them inside the row; the rest read as zero).
+template <typename T>
+__device__ __forceinline__ void ld4(const T* p, bool vec, int valid, float o[4]) {
+  if (vec) {
+    if constexpr (sizeof(T) == 4) {
+      const float4 t = __ldg(reinterpret_cast<const float4*>(p));
+      o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+    } else {
+      const uint2 u = __ldg(reinterpret_cast<const uint2*>(p));
+      o[0] = __uint_as_float(u.x << 16); o[1] = __uint_as_float(u.x & 0xffff0000u);
+      o[2] = __uint_as_float(u.y << 16); o[3] = __uint_as_float(u.y & 0xffff0000u);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[c] = c < valid ? to_f32<T>(p[c]) : 0.f;
+  }
+}
+__device__ __forceinline__ void ld4_codes(const int8_t* p, bool vec, int valid, float o[4]) {
+  if (vec) {
+    const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(p));
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[c] = static_cast<float>(static_cast<int8_t>((u >> (8 * c)) & 0xffu));
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[c] = c < valid ? static_cast<float>(p[c]) : 0.f;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void st4(T* p, bool vec, int valid, const float v[4]) {
+  if (vec) {
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+      *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (c < valid) {
+        if constexpr (sizeof(T) == 4) p[c] = v[c];
+        else p[c] = __float2bfloat16_rn(v[c]);
+      }
+  }
+}
+
+// y[t,n] = sum_j w[t*k+j] * res[row(t*k+j), n]; thread per (t, 4 columns); j ascending.
 template <typename TR, typename TY>
 __global__ void combine_kernel(const TR* __restrict__ res, int64_t res_stride, const int32_t* __restrict__ row_index,
                                const float* __restrict__ w, int64_t T, int k, int N, TY* __restrict__ y,
-                               int64_t y_stride) {
+                               int64_t y_stride, int vec) {
   const int nq = (N + 3) / 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * nq) return;
   const int64_t t = idx / nq;
-  const int n0 = static_cast<int>(idx % nq) * 4;
+  const int n0 = static_cast<int>(idx - t * nq) * 4;
+  const int valid = N - n0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
   for (int j = 0; j < k; ++j) {
     const int64_t s = t * k + j;
     const float ws = w ? w[s] : 1.f;
     const int64_t rr = row_index ? row_index[s] : s;
-    const TR* row = res + rr * res_stride + n0;
+    float v[4];
+    ld4<TR>(res + rr * res_stride + n0, vec != 0, valid, v);
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
-      if (n0 + c < N) acc[c] = w ? acc[c] + ws * to_f32<TR>(row[c]) : acc[c] + to_f32<TR>(row[c]);
+    for (int c = 0; c < 4; ++c) acc[c] = w ? fmaf(ws, v[c], acc[c]) : acc[c] + v[c];
   }
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
-    if (n0 + c < N) {
-      if constexpr (sizeof(TY) == 4)
-        y[t * y_stride + n0 + c] = acc[c];
-      else
-        y[t * y_stride + n0 + c] = __float2bfloat16_rn(acc[c]);
-    }
+  st4<TY>(y + t * y_stride + n0, vec != 0, valid, acc);
 }
 
 template <typename TY>
 __global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
                                      const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
                                      float step, const float* __restrict__ w, int64_t T, int k, int N,
-                                     TY* __restrict__ y, int64_t y_stride) {
+                                     TY* __restrict__ y, int64_t y_stride, int vec) {
   const int nq = (N + 3) / 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * nq) return;
   const int64_t t = idx / nq;
-  const int n0 = static_cast<int>(idx % nq) * 4;
+  const int n0 = static_cast<int>(idx - t * nq) * 4;
+  const int valid = N - n0;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
   for (int j = 0; j < k; ++j) {
     const int64_t s = t * k + j;
     const float ws = w ? w[s] : 1.f;
     const float rm = row_mult ? row_mult[s] : 1.f;
     const int e = raw_sel[s];
+    float cd[4], cs[4];
+    ld4_codes(codes + s * N + n0, vec != 0, valid, cd);
+    ld4<float>(col_scale + static_cast<int64_t>(e) * N + n0, vec != 0, valid, cs);
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
-      if (n0 + c < N) {
-        float v = (static_cast<float>(codes[s * N + n0 + c]) * step) * col_scale[static_cast<int64_t>(e) * N + n0 + c];
-        v *= rm;
-        acc[c] += ws * v;
-      }
-  }
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
-    if (n0 + c < N) {
-      if constexpr (sizeof(TY) == 4)
-        y[t * y_stride + n0 + c] = acc[c];
-      else
-        y[t * y_stride + n0 + c] = __float2bfloat16_rn(acc[c]);
+    for (int c = 0; c < 4; ++c) {
+      const float v = __fmul_rn(__fmul_rn(__fmul_rn(cd[c], step), cs[c]), rm);   // the row value, rounded as the kernel rounds it
+      acc[c] = fmaf(ws, v, acc[c]);
     }
+  }
+  st4<TY>(y + t * y_stride + n0, vec != 0, valid, acc);
 }
 
-// d[s] = res[s,:] . g[s/k,:]; one warp per slot.
+// d[s] = res[row(s),:] . g[s/k,:]; one warp per slot; lane l walks the column quads l, l+32, ... and adds their
+// four products in column order into one accumulator (the same order in the kernel below, so that rows rebuilt
+// from codes give the same bits as materialised rows).
 template <typename TR, typename TG>
 __global__ void row_dot_kernel(const TR* __restrict__ res, int64_t res_stride, const int32_t* __restrict__ row_index,
                                const TG* __restrict__ g, int64_t g_stride, int64_t P, int k, int N,
-                               float* __restrict__ d) {
+                               float* __restrict__ d, int vec) {
   const int lane = threadIdx.x & 31;
   const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (s >= P) return;
   const TR* r = res + (row_index ? static_cast<int64_t>(row_index[s]) : s) * res_stride;
   const TG* gr = g + (s / k) * g_stride;
+  const int nq = (N + 3) / 4;
   float acc = 0.f;
-  for (int n = lane; n < N; n += 32) acc = fmaf(to_f32<TR>(r[n]), to_f32<TG>(gr[n]), acc);
+#pragma unroll 4
+  for (int q = lane; q < nq; q += 32) {
+    float a[4], b[4];
+    ld4<TR>(r + 4 * q, vec != 0, N - 4 * q, a);
+    ld4<TG>(gr + 4 * q, vec != 0, N - 4 * q, b);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc = fmaf(a[c], b[c], acc);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) d[s] = acc;
 }
 
-// d[s] = sum_n ((code*step)*col_scale[e,n])*row_scale[s] * g[s/k,n]; one warp per slot.
+// d[s] = sum_n ((code*step)*col_scale[e,n])*row_scale[s] * g[s/k,n]; one warp per slot, order as above.
 template <typename TG>
 __global__ void row_dot_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
                                      const int32_t* __restrict__ row_expert, const float* __restrict__ row_scale,
                                      float step, const TG* __restrict__ g, int64_t g_stride, int64_t P, int k, int N,
-                                     float* __restrict__ d) {
+                                     float* __restrict__ d, int vec) {
   const int lane = threadIdx.x & 31;
   const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (s >= P) return;
@@ -101,30 +149,46 @@ __global__ void row_dot_codes_kernel(const int8_t* __restrict__ codes, const flo
   const float* cs = col_scale + static_cast<int64_t>(row_expert[s]) * N;
   const float rs = row_scale ? row_scale[s] : 1.f;
   const TG* gr = g + (s / k) * g_stride;
+  const int nq = (N + 3) / 4;
   float acc = 0.f;
-  for (int n = lane; n < N; n += 32) {
-    const float v = ((static_cast<float>(r[n]) * step) * cs[n]) * rs;
-    acc = fmaf(v, to_f32<TG>(gr[n]), acc);
+#pragma unroll 4
+  for (int q = lane; q < nq; q += 32) {
+    float cd[4], sc[4], b[4];
+    ld4_codes(r + 4 * q, vec != 0, N - 4 * q, cd);
+    ld4<float>(cs + 4 * q, vec != 0, N - 4 * q, sc);
+    ld4<TG>(gr + 4 * q, vec != 0, N - 4 * q, b);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float v = __fmul_rn(__fmul_rn(__fmul_rn(cd[c], step), sc[c]), rs);
+      acc = fmaf(v, b[c], acc);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) d[s] = acc;
 }
 
-// One warp per expert: ordered (lane-strided, then butterfly) sum of the expert's slot gradients.
-__global__ void ir_grad_reduce_kernel(const float* __restrict__ slot_grad, const int32_t* __restrict__ offsets,
-                                      const float* __restrict__ input_range, int E, float decay, float min_pct,
-                                      const unsigned long long* __restrict__ keep_count, double total,
-                                      float* __restrict__ out) {
-  const int lane = threadIdx.x & 31;
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (e >= E) return;
+// One CTA of 256 threads per expert: fixed-order (thread-strided, butterfly inside each warp, then across the
+// eight warps) sum of the expert's slot gradients.
+__global__ void __launch_bounds__(256) ir_grad_reduce_kernel(const float* __restrict__ slot_grad,
+                                                             const int32_t* __restrict__ offsets,
+                                                             const float* __restrict__ input_range, int E, float decay,
+                                                             float min_pct,
+                                                             const unsigned long long* __restrict__ keep_count,
+                                                             double total, float* __restrict__ out) {
+  __shared__ float red[8];
+  const int e = blockIdx.x;
   const int beg = offsets[e], end = offsets[e + 1];
   float acc = 0.f;
-  for (int i = beg + lane; i < end; i += 32) acc += slot_grad[i];
+  for (int i = beg + threadIdx.x; i < end; i += 256) acc += slot_grad[i];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (lane == 0) {
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    acc = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) acc += red[w];
     if (decay > 0.f && keep_count != nullptr) {
       const float pct = static_cast<float>(static_cast<double>(*keep_count) / total);
       if (pct > min_pct) acc += (decay * input_range[e]) * static_cast<float>(end - beg);
@@ -236,6 +300,7 @@ __global__ void ep_unpack_kernel(const T* __restrict__ recv, int N, const int32_
 constexpr int kStaticStdMaxExperts = 4096;
 static __device__ __align__(256) double g_std_scratch[3 * kStaticStdMaxExperts];
 
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline unsigned blocks_for(int64_t threads, int per_block) {
   return static_cast<unsigned>((threads + per_block - 1) / per_block);
 }
@@ -254,20 +319,21 @@ int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const i
   AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = blocks_for(n, 256);
+  const int vec = (N % 4 == 0) && (res_stride % 4 == 0) && (y_stride % 4 == 0) && al16(res) && al16(y);
   if (res_dtype == AMOE_F32 && y_dtype == AMOE_F32)
     combine_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index, w, T, k,
-                                                             N, reinterpret_cast<float*>(y), y_stride);
+                                                             N, reinterpret_cast<float*>(y), y_stride, vec);
   else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_BF16)
     combine_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(res), res_stride, row_index, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
-        y_stride);
+        y_stride, vec);
   else if (res_dtype == AMOE_F32 && y_dtype == AMOE_BF16)
     combine_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index, w, T, k, N, reinterpret_cast<__nv_bfloat16*>(y),
-                                                                     y_stride);
+                                                                     y_stride, vec);
   else if (res_dtype == AMOE_BF16 && y_dtype == AMOE_F32)
     combine_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
                                                                      res_stride, row_index, w, T, k, N,
-                                                                     reinterpret_cast<float*>(y), y_stride);
+                                                                     reinterpret_cast<float*>(y), y_stride, vec);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("combine");
@@ -282,13 +348,14 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
   AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = blocks_for(n, 256);
+  const int vec = (N % 4 == 0) && (y_stride % 4 == 0) && al16(y) && al16(col_scale) && al16(codes);
   if (y_dtype == AMOE_F32)
     combine_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
-                                                            reinterpret_cast<float*>(y), y_stride);
+                                                            reinterpret_cast<float*>(y), y_stride, vec);
   else if (y_dtype == AMOE_BF16)
     combine_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T,
                                                                     k, N, reinterpret_cast<__nv_bfloat16*>(y),
-                                                                    y_stride);
+                                                                    y_stride, vec);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("combine_codes");
@@ -301,21 +368,22 @@ int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const i
   AMOE_REQUIRE(res && g && d, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const unsigned blocks = blocks_for(P * 32, 256);
+  const int vec = (N % 4 == 0) && (res_stride % 4 == 0) && (g_stride % 4 == 0) && al16(res) && al16(g);
   if (res_dtype == AMOE_F32 && g_dtype == AMOE_F32)
     row_dot_kernel<float, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index,
-                                                             reinterpret_cast<const float*>(g), g_stride, P, k, N, d);
+                                                             reinterpret_cast<const float*>(g), g_stride, P, k, N, d, vec);
   else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_BF16)
     row_dot_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(res), res_stride, row_index, reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
-        P, k, N, d);
+        P, k, N, d, vec);
   else if (res_dtype == AMOE_F32 && g_dtype == AMOE_BF16)
     row_dot_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(res), res_stride, row_index,
                                                                      reinterpret_cast<const __nv_bfloat16*>(g),
-                                                                     g_stride, P, k, N, d);
+                                                                     g_stride, P, k, N, d, vec);
   else if (res_dtype == AMOE_BF16 && g_dtype == AMOE_F32)
     row_dot_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(res),
                                                                      res_stride, row_index, reinterpret_cast<const float*>(g),
-                                                                     g_stride, P, k, N, d);
+                                                                     g_stride, P, k, N, d, vec);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("row_dot");
@@ -329,13 +397,14 @@ int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_
   AMOE_REQUIRE(codes && col_scale && row_expert && g && d, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const unsigned blocks = blocks_for(P * 32, 256);
+  const int vec = (N % 4 == 0) && (g_stride % 4 == 0) && al16(g) && al16(col_scale) && al16(codes);
   if (g_dtype == AMOE_F32)
     row_dot_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
-                                                            reinterpret_cast<const float*>(g), g_stride, P, k, N, d);
+                                                            reinterpret_cast<const float*>(g), g_stride, P, k, N, d, vec);
   else if (g_dtype == AMOE_BF16)
     row_dot_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
                                                                     reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
-                                                                    P, k, N, d);
+                                                                    P, k, N, d, vec);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("row_dot_codes");
@@ -349,7 +418,7 @@ int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets
   AMOE_REQUIRE(ir_grad_slot && expert_offsets && out, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(E > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!(decay > 0.f) || (keep_count && input_range && total_elements > 0), AMOE_ERR_NULL_POINTER);
-  ir_grad_reduce_kernel<<<blocks_for(static_cast<int64_t>(E) * 32, 128), 128, 0, stream>>>(
+  ir_grad_reduce_kernel<<<static_cast<unsigned>(E), 256, 0, stream>>>(
       ir_grad_slot, expert_offsets, input_range, E, decay, min_percentage, keep_count, total_elements, out);
   AMOE_LAUNCH_CHECK("ir_grad_reduce");
   return AMOE_OK;

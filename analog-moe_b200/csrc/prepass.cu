@@ -29,31 +29,35 @@ __global__ void colmax_kernel(const void* __restrict__ w, int dtype, int E, int 
   }
 }
 
-// expmax[e] = max_n colmax[e,n]; one block per expert.
-__global__ void expmax_kernel(const float* __restrict__ colmax, int N, float* __restrict__ expmax) {
-  __shared__ float red[32];
+// One block per expert: expmax[e] = max_n colmax[e,n], then the output scales (per column or per expert) and
+// their correctly rounded reciprocals.
+__global__ void __launch_bounds__(256) scales_kernel(const float* __restrict__ colmax, int N, int per_channel,
+                                                     float* __restrict__ expmax, float* __restrict__ out,
+                                                     float* __restrict__ inv) {
+  __shared__ float red[8];
+  __shared__ float s_max;
   const int e = blockIdx.x;
+  const float* cm = colmax + static_cast<int64_t>(e) * N;
   float m = 0.f;
-  for (int n = threadIdx.x; n < N; n += blockDim.x) m = fmaxf(m, colmax[static_cast<int64_t>(e) * N + n]);
+  for (int n = threadIdx.x; n < N; n += 256) m = fmaxf(m, cm[n]);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
   __syncthreads();
-  if (threadIdx.x < 32) {
-    m = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+  if (threadIdx.x == 0) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (threadIdx.x == 0) expmax[e] = m;
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    expmax[e] = m;
+    s_max = m;
   }
-}
-
-__global__ void fill_scale_kernel(const float* __restrict__ colmax, const float* __restrict__ expmax, int E, int N,
-                                  int per_channel, float* __restrict__ out, float* __restrict__ inv) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= static_cast<int64_t>(E) * N) return;
-  const float s = per_channel ? colmax[i] : expmax[i / N];
-  if (out) out[i] = s;
-  if (inv) inv[i] = s > 0.f ? __frcp_rn(s) : 0.f;
+  __syncthreads();
+  const float em = s_max;
+  for (int n = threadIdx.x; n < N; n += 256) {
+    const float s = per_channel ? cm[n] : em;
+    const int64_t i = static_cast<int64_t>(e) * N + n;
+    if (out) out[i] = s;
+    if (inv) inv[i] = s > 0.f ? __frcp_rn(s) : 0.f;
+  }
 }
 
 struct PrepassDev {
@@ -217,15 +221,8 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
                                                                           a->w_stride_e, a->w_stride_k,
                                                                           a->w_stride_n, colmax);
   AMOE_LAUNCH_CHECK("colmax");
-  expmax_kernel<<<a->E, 256, 0, stream>>>(colmax, a->N, expmax);
-  AMOE_LAUNCH_CHECK("expmax");
-  if (a->col_scale || a->col_inv_scale) {
-    const int64_t n = static_cast<int64_t>(a->E) * a->N;
-    fill_scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(colmax, expmax, a->E, a->N,
-                                                                                  a->per_channel_scale, a->col_scale,
-                                                                                  a->col_inv_scale);
-    AMOE_LAUNCH_CHECK("fill_scale");
-  }
+  scales_kernel<<<a->E, 256, 0, stream>>>(colmax, a->N, a->per_channel_scale, expmax, a->col_scale, a->col_inv_scale);
+  AMOE_LAUNCH_CHECK("scales");
   if (a->w_out || a->fwd_hi || a->bwd_hi) {
     PrepassDev p;
     p.w = a->w; p.dtype = a->w_dtype; p.E = a->E; p.K = a->K; p.N = a->N;
