@@ -59,6 +59,7 @@ class CvmmArgs(C.Structure):
         ("x_ref_row", vp), ("x_ref_relu", C.c_int32),
         ("row_scale", vp), ("ir_grad", vp), ("ir_grad_relative", C.c_int32), ("ir_grad_scale", C.c_float),
         ("keep_count", vp),
+        ("a_cache_hi", vp), ("a_cache_lo", vp), ("a_cache_scale", vp), ("out_cache_hi", vp), ("out_cache_lo", vp), ("cache_rows", C.c_int64),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]
 
@@ -70,6 +71,7 @@ class DwArgs(C.Structure):
         ("x", vp), ("x_dtype", C.c_int32), ("x_stride", C.c_int64), ("x_rows", C.c_int64), ("x_row", vp), ("ir", vp), ("ir_by_expert", C.c_int32),
         ("g", vp), ("g_dtype", C.c_int32), ("g_stride", C.c_int64), ("g_rows", C.c_int64), ("g_row", vp),
         ("g_div", C.c_int32), ("g_scale", vp), ("dw", vp),
+        ("x_hi", vp), ("x_lo", vp), ("g_hi", vp), ("g_lo", vp), ("cache_rows", C.c_int64),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]
 
@@ -91,6 +93,7 @@ SIGNATURES = {
     "amoe_weight_prepass": (C.c_int, [C.POINTER(WeightPrepassArgs), vp]),
     "amoe_row_absmax": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp]),
     "amoe_cvmm_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
+    "amoe_padded_rows": (C.c_int64, [C.c_int64, C.c_int32]),
     "amoe_cvmm_fwd": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dx": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dw_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

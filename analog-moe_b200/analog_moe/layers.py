@@ -127,9 +127,17 @@ class _FusedAnalogStep(torch.autograd.Function):
         nz = nz_up
         ir_up = ir_all[0] if has_ir else None
         am_up = None if has_ir else ops.row_absmax(x2)
+        # operands of the two weight gradients, written while the forward kernels hold the rows anyway
+        N = values.shape[-1]
+        Fh = keys.shape[-1]
+        cached = layer.operand_caches and ops.operand_cache_ok(precision, D, Fh, N) and \
+            any(ctx.needs_input_grad[3:5])
+        split = precision == ops.A.PREC_SPLIT
+        xc = ops.OperandCache.empty(P, E, D, split, x.device) if cached else None
+        hs = ops.OperandCache.empty(P, E, Fh, split, x.device) if cached else None
         h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
                             ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
-                            out_bound=out_bound, out_relu=True, **nz)
+                            out_bound=out_bound, out_relu=True, a_cache=xc, **nz)
         # ---- down-projection and the gate-weighted sum over k
         ops.set_tag("down")
         nz = nz_dn
@@ -137,25 +145,27 @@ class _FusedAnalogStep(torch.autograd.Function):
         am_dn = None if has_ir else ops.row_absmax(h)
         # the composition hands the gate over in the activation dtype (rounded for bf16 layers)
         gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
-        N = values.shape[-1]
+        cache_kw = dict(a_cache=hs, a_cache_scale=gate.reshape(-1)) if cached else {}
         adc_step = ops.adc_step(out_res, out_bound) if adc_on else 0.0
         res = codes = row_scale = row_expert = None
         if adc_on:
             meta = {}
             _, codes = ops.cvmm_fwd(h, r.slot_index, r.slot_index, r.expert_offsets, pw_dn, precision, P=P, dst_rows=P,
                                     ir=ir_dn, ir_by_expert=True, absmax=am_dn, inp_res=inp_res, out_res=out_res,
-                                    out_bound=out_bound, want_codes=True, want_out=False, row_meta=meta, **nz)
+                                    out_bound=out_bound, want_codes=True, want_out=False, row_meta=meta, **cache_kw,
+                                    **nz)
             row_scale, row_expert = meta["row_scale"], meta["row_expert"]
             y = ops.combine_codes(codes, pw_dn.col_scale, row_expert, row_scale, adc_step, gate, T, k, out_dtype=x.dtype)
         else:
             res, _ = ops.cvmm_fwd(h, r.slot_index, r.slot_index, r.expert_offsets, pw_dn, precision, P=P, dst_rows=P,
-                                  ir=ir_dn, ir_by_expert=True, absmax=am_dn, inp_res=inp_res, **nz)
+                                  ir=ir_dn, ir_by_expert=True, absmax=am_dn, inp_res=inp_res, **cache_kw, **nz)
             y = ops.combine(res, gate, T, k)
         simt = precision == ops.A.PREC_FP32_SIMT
         ctx.save_for_backward(x2, w_sel, h, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, ir_all,
                               pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
-                              codes, row_scale, row_expert, res)
+                              codes, row_scale, row_expert, res,
+                              *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)))
         ctx.meta = (x.shape, E, k, precision, ir_p, keys.dtype, values.dtype, adc_step, keys.shape, values.shape,
                     input_range.dtype if has_ir else None)
         return y.view(bsz, seq, N)
@@ -163,7 +173,8 @@ class _FusedAnalogStep(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gy):
         (x2, w_sel, h, gate, raw_sel, token_index, slot_index, offsets, ir_all, w_up, up_hi, up_lo, up_cs,
-         w_dn, dn_hi, dn_lo, dn_cs, codes, row_scale, row_expert, res) = ctx.saved_tensors
+         w_dn, dn_hi, dn_lo, dn_cs, codes, row_scale, row_expert, res, xc_hi, xc_lo, hs_hi, hs_lo) = ctx.saved_tensors
+        cached = xc_hi is not None
         x_shape, E, k, precision, ir_p, keys_dtype, values_dtype, adc_step, kshape, vshape, ir_dtype = ctx.meta
         T, D = x2.shape
         P = T * k
@@ -186,14 +197,21 @@ class _FusedAnalogStep(torch.autograd.Function):
         # ---- down-projection
         ops.set_tag("down")
         grad_values = None
-        if need_values:
+        if need_values and not cached:
             grad_values = ops.cvmm_dw(h, slot_index, g, slot_index, offsets, E, precision, P=P, ir=ir_dn,
                                       ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1)).to(values_dtype)
+        split = xc_lo is not None
+        gc = ops.OperandCache.empty(P, E, N, split, x2.device) if cached and need_values else None
+        dhc = ops.OperandCache.empty(P, E, Fh, split, x2.device) if cached and need_keys else None
         dh, irs_dn = ops.cvmm_dx(g, slot_index, slot_index, offsets, pw_dn, precision, P=P, dst_rows=P, a_row_div=k,
                                  x_ref=h, x_ref_row=slot_index, ir=ir_dn, ir_by_expert=True, row_scale=gate.reshape(-1),
                                  want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                  keep_count=keeps[1:] if keeps is not None else None, out_dtype=h.dtype,
-                                 x_ref_relu=True)
+                                 x_ref_relu=True, a_cache=gc, out_cache=dhc)
+        if need_values and cached:
+            # dW = sum_slots (gate * clamp(h))^T (x) gy: both operands straight from the caches
+            grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision,
+                                             P=P).to(values_dtype)
         if codes is not None:
             dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
         else:
@@ -201,7 +219,9 @@ class _FusedAnalogStep(torch.autograd.Function):
         # ---- up-projection
         ops.set_tag("up")
         grad_keys = None
-        if need_keys:
+        if need_keys and cached:
+            grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P).to(keys_dtype)
+        elif need_keys:
             grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
                                     ir_by_expert=True).to(keys_dtype)
         grad_x = irs_up = None
@@ -328,6 +348,7 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.register_buffer("noise_step", torch.zeros((), dtype=torch.int64), persistent=True)
         self.register_buffer("_aux_zero", torch.zeros(()), persistent=False)
         self.fused = True          # one autograd node for the whole layer when the configuration allows it
+        self.operand_caches = True  # forward / dX kernels leave bf16 copies of the dW operands (fused path)
         self._noise_calls = 0
         ir = self.rpu_config.pre_post.input_range
         self.input_range = None

@@ -264,7 +264,8 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
              step_dev: Optional[torch.Tensor] = None, out_res: float = -1.0, out_bound: float = -1.0, want_codes: bool = False,
              out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
              want_out: bool = True, row_meta: Optional[dict] = None, ir_by_expert: bool = False,
-             out_relu: bool = False):
+             out_relu: bool = False, a_cache: Optional["OperandCache"] = None,
+             a_cache_scale: Optional[torch.Tensor] = None):
     """Returns (out or None, codes or None).  `row_meta` (a dict) receives `row_scale` [dst_rows] and
     `row_expert` [dst_rows], from which, with the codes, the output rows can be rebuilt."""
     x2 = _rows(x2)
@@ -282,6 +283,9 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     _fill_weights(a, pw, precision, backward=False)
     a.ir, a.a_absmax, a.inp_res = ptr(ir), ptr(absmax), float(inp_res)
     a.ir_by_expert, a.out_relu = int(ir_by_expert), int(out_relu)
+    if a_cache is not None:
+        a.a_cache_hi, a.a_cache_lo, a.a_cache_scale = ptr(a_cache.hi), ptr(a_cache.lo), ptr(a_cache_scale)
+        a.cache_rows = a_cache.rows
     if noise is not None:
         noise = noise.reshape(-1, pw.N).float().contiguous()
         assert noise.shape[0] == dst_rows
@@ -307,7 +311,8 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             ir: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None, want_ir_grad: bool = False,
             relative: bool = True, grad_scale: float = 1.0, keep_count: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
-            ir_by_expert: bool = False, x_ref_relu: bool = False):
+            ir_by_expert: bool = False, x_ref_relu: bool = False, a_cache: Optional["OperandCache"] = None,
+            out_cache: Optional["OperandCache"] = None):
     g2 = _rows(g2)
     dev = g2.device
     out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev)
@@ -321,6 +326,12 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     a.inp_res = -1.0
     a.ir = ptr(ir)
     a.ir_by_expert, a.x_ref_relu = int(ir_by_expert), int(x_ref_relu)
+    if a_cache is not None:
+        a.a_cache_hi, a.a_cache_lo = ptr(a_cache.hi), ptr(a_cache.lo)
+        a.cache_rows = a_cache.rows
+    if out_cache is not None:
+        a.out_cache_hi, a.out_cache_lo = ptr(out_cache.hi), ptr(out_cache.lo)
+        a.cache_rows = out_cache.rows
     a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
     if x_ref is not None:
         x_ref = _rows(x_ref)
@@ -350,6 +361,50 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
     a.ir_by_expert = int(ir_by_expert)
     nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device) if nbytes else None
+    a.workspace, a.workspace_bytes = ptr(ws), nbytes
+    a.dev_status = ptr(status)
+    _call("amoe_cvmm_dw", C.byref(a), stream_ptr())
+    return dw
+
+
+@dataclass
+class OperandCache:
+    """One CVMM operand as bf16 hi (+ lo) terms in padded tile-row order, written by a forward / input-gradient
+    kernel and read by the weight-gradient kernel through TMA."""
+    hi: torch.Tensor              # [ceil(cols/64), rows, 64] bf16
+    lo: Optional[torch.Tensor]
+    cols: int = 0
+
+    @property
+    def rows(self) -> int:
+        return self.hi.shape[1]
+
+    @staticmethod
+    def empty(P: int, E: int, cols: int, split: bool, device) -> "OperandCache":
+        rows = int(lib.amoe_padded_rows(P, E))
+        hi = torch.empty((cols + 63) // 64, rows, 64, dtype=torch.bfloat16, device=device)
+        return OperandCache(hi, torch.empty_like(hi) if split else None, cols)
+
+
+def operand_cache_ok(precision: int, *cols: int) -> bool:
+    return precision != A.PREC_FP32_SIMT and all(c % 16 == 0 for c in cols)
+
+
+def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.Tensor, E: int, precision: int, *,
+                   P: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dW [E,K,N] from two operand caches ([rows,K] and [rows,N])."""
+    K, N = x_cache.cols, g_cache.cols
+    dev = x_cache.hi.device
+    dw = torch.empty(E, K, N, dtype=torch.float32, device=dev)
+    a = A.DwArgs()
+    a.P, a.E, a.K, a.N, a.precision = P, E, K, N, precision
+    a.expert_offsets = ptr(offsets)
+    a.x_hi, a.x_lo, a.g_hi, a.g_lo = ptr(x_cache.hi), ptr(x_cache.lo), ptr(g_cache.hi), ptr(g_cache.lo)
+    a.cache_rows = x_cache.rows
+    a.g_div = 1
+    a.dw = ptr(dw)
+    nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     a.dev_status = ptr(status)
     _call("amoe_cvmm_dw", C.byref(a), stream_ptr())

@@ -35,6 +35,11 @@ size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E) {
   return 0;  // the kernels find their tiles from expert_offsets; nothing is staged in global memory
 }
 
+int64_t amoe_padded_rows(int64_t P, int32_t E) {
+  if (P <= 0 || E <= 0) return 0;
+  return (P / 128 + E) * 128;
+}
+
 size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision) {
   if (precision == AMOE_PREC_FP32_SIMT || P <= 0 || E <= 0 || K <= 0 || N <= 0) return 0;
   return dw_tc_workspace_bytes(P, E, K, N);
@@ -67,6 +72,8 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.status = a->dev_status;
   e.vec4 = (a->N % 4 == 0) && al16(a->col_scale) && al16(a->col_inv_scale) && al16(a->noise) && al16(a->out) &&
            (a->out_stride % 4 == 0) && al16(a->out_codes);
+  AMOE_REQUIRE(!(a->a_cache_hi || a->out_cache_hi) || a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
+  AMOE_REQUIRE(!a->out_cache_hi, AMOE_ERR_UNSUPPORTED);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, false, e, stream);
   return launch_cvmm_tc(a, false, e, stream);
 }
@@ -96,6 +103,11 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.status = a->dev_status;
   e.vec4 = (a->K % 4 == 0) && al16(a->out) && (a->out_stride % 4 == 0) &&
            (!a->x_ref || (al16(a->x_ref) && a->x_ref_stride % 4 == 0));
+  AMOE_REQUIRE(!(a->a_cache_hi || a->out_cache_hi) || a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
+  e.out_cache_hi = reinterpret_cast<__nv_bfloat16*>(a->out_cache_hi);
+  e.out_cache_lo = reinterpret_cast<__nv_bfloat16*>(a->out_cache_lo);
+  e.out_cache_stride = a->cache_rows;
+  AMOE_REQUIRE(!a->out_cache_hi || (a->K % 16 == 0 && al16(a->out_cache_hi) && al16(a->out_cache_lo)), AMOE_ERR_BAD_SHAPE);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, true, e, stream);
   return launch_cvmm_tc(a, true, e, stream);
 }
@@ -105,7 +117,14 @@ int amoe_cvmm_dw(const amoe_dw_args* a, amoe_stream_t stream_) {
   AMOE_REQUIRE(a != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->P > 0 && a->E > 0 && a->K > 0 && a->N > 0 && a->E <= 65535, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(a->P < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
-  AMOE_REQUIRE(a->expert_offsets && a->x && a->x_row && a->g && a->g_row && a->dw, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(a->expert_offsets && a->dw, AMOE_ERR_NULL_POINTER);
+  if (a->x_hi || a->g_hi) {
+    AMOE_REQUIRE(a->x_hi && a->g_hi, AMOE_ERR_NULL_POINTER);
+    AMOE_REQUIRE(a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
+    AMOE_REQUIRE(a->cache_rows >= amoe_padded_rows(a->P, a->E) && a->K % 8 == 0 && a->N % 8 == 0, AMOE_ERR_BAD_SHAPE);
+    return launch_dw_tc(a, stream);
+  }
+  AMOE_REQUIRE(a->x && a->x_row && a->g && a->g_row, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE((a->x_dtype == AMOE_F32 || a->x_dtype == AMOE_BF16) && (a->g_dtype == AMOE_F32 || a->g_dtype == AMOE_BF16),
                AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->x_rows > 0 && a->g_rows > 0 && a->g_div >= 1, AMOE_ERR_BAD_SHAPE);

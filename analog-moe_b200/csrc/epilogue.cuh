@@ -30,6 +30,8 @@ struct EpiParams {
   const void* x_ref; int x_ref_dtype; int64_t x_ref_stride; int64_t x_ref_rows; const int32_t* x_ref_row;
   const float* row_scale; float* ir_grad; int relative; float grad_scale;
   unsigned long long* keep_count;
+  // input gradient, optional: the result rows once more as bf16 hi (+ lo) terms, by padded tile row
+  __nv_bfloat16* out_cache_hi; __nv_bfloat16* out_cache_lo; int64_t out_cache_stride;
   int32_t* status;
 };
 
@@ -44,6 +46,7 @@ struct RowCtx {
   float dir_acc;
   unsigned keep;
   uint32_t noise_offset;   // Philox offset in effect (argument + 8 * device step counter)
+  int64_t pad_row;         // tile index * 128 + row in tile (row of the operand caches)
 };
 
 __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, int e, bool in_range) {
@@ -52,6 +55,7 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   c.e = e;
   c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0;
   c.noise_offset = p.offset;
+  c.pad_row = 0;
   if (p.noise_std > 0.f && p.step_dev) c.noise_offset += static_cast<uint32_t>(*p.step_dev) * 8u;
   if (!in_range) return c;
   c.dst = p.dst_row[i];

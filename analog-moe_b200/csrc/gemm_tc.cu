@@ -94,6 +94,8 @@ struct TcParams {
   const int32_t* offsets;
   const void* a; int a_dtype; int64_t a_stride; int64_t a_rows; const int32_t* a_row; int a_div;
   const float* ir; const float* a_absmax; float inp_res; int vec_ok;
+  // optional operand cache: split(clamp(a, ir) * cache_scale[a_row[i]]) by padded tile row, [tiles*128, cache_stride]
+  __nv_bfloat16* cache_hi; __nv_bfloat16* cache_lo; int64_t cache_stride /* rows of the cache */; const float* cache_scale;
   EpiParams epi;
 };
 
@@ -394,6 +396,26 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] *= c.rs;
   }
+  if (p.out_cache_hi) {
+    // the row once more as bf16 hi (+ lo) terms at its padded tile row: the B operand of the next dW
+    // layout [64-column block][padded row][64]; n0 is a multiple of 16, so the chunk stays inside one block
+    const int64_t co = (((n0 >> 6) * p.out_cache_stride + c.pad_row) << 6) + (n0 & 63);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t h[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) h[x] = c.valid ? cvt_bf16x2(v[8 * half + 2 * x], v[8 * half + 2 * x + 1]) : 0u;
+      *reinterpret_cast<uint4*>(p.out_cache_hi + co + 8 * half) = make_uint4(h[0], h[1], h[2], h[3]);
+      if (p.out_cache_lo) {
+        uint32_t l[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+          l[x] = c.valid ? cvt_bf16x2(v[8 * half + 2 * x] - __uint_as_float(h[x] << 16),
+                                      v[8 * half + 2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u)) : 0u;
+        *reinterpret_cast<uint4*>(p.out_cache_lo + co + 8 * half) = make_uint4(l[0], l[1], l[2], l[3]);
+      }
+    }
+  }
   store16_t(p, qr, n0, v, lane);
 }
 
@@ -402,6 +424,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ RowMeta s_meta[kMaxProdGroups][kBM];
+  __shared__ float s_cscale[kBM];
   __shared__ float s_dir[kMaxEpiGroups][kBM];
   __shared__ unsigned s_keep[kMaxEpiGroups][kBM];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
@@ -500,6 +523,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       if (!ti.get(t, e, row0, rows)) break;
       const int64_t i = static_cast<int64_t>(row0) + r;
       RowCtx ctx = epi_row_begin(p.epi, i, e, r < rows);
+      ctx.pad_row = t * kBM + r;
       if (grp == 0) epi_row_side_outputs(p.epi, ctx);
       QuadRows qr;
       if (EPI != kEpiGeneric) {
@@ -608,9 +632,12 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       for (int r = pt; r < kBM; r += np) {
         RowMeta m;
         m.src = -1; m.ir = 1.f; m.rcp_ir = 1.f; m.am = 1.f;
+        float csc = 0.f;
         if (r < rows) {
           const int64_t i = static_cast<int64_t>(row0) + r;
-          const int64_t src = p.a_row[i] / p.a_div;
+          const int64_t raw = p.a_row[i];
+          const int64_t src = raw / p.a_div;
+          if (p.cache_scale && src >= 0 && src < p.a_rows) csc = p.cache_scale[raw];
           if (src < 0 || src >= p.a_rows) {
             report(status, AMOE_ERR_INDEX_RANGE, 20, static_cast<int>(i), static_cast<int>(src));
           } else {
@@ -620,10 +647,12 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           }
         }
         meta[r] = m;
+        if (p.cache_scale) s_cscale[r] = csc;
       }
       if (!group_sync(bar_group(sm.bars, 1), sync_round, sm.abort_flag, status, 10)) break;
       ++sync_round;
       for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
+        const bool do_cache = p.cache_hi != nullptr && nt == 0;
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
           const int s = rp.s;
           if (pt == 0) TL(2, it, 0);
@@ -660,17 +689,63 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             for (int b = 0; b < 2; ++b) {
               const int task = base + b * np;
               if (task < kBM * 8) {
-                if (DAC != kDacNone && m[b].src >= 0) {
-                  const float rcp_am = has_am ? __frcp_rn(m[b].am) : 1.f;
+                const int kk = kc * kBK + (task & 7) * 8;
+                const bool cache_now = do_cache && kk < p.Kc;
+                // cache layout: [64-column block][padded row][64]
+                const int64_t co = cache_now ? ((kc * p.cache_stride + t * kBM + (task >> 3)) << 6) + (task & 7) * 8 : 0;
+                const uint32_t soff = sw128_offset(task >> 3, task & 7);
+                if (DAC == kDacNone) {
+                  // the tile and the cache hold the same terms: convert once, store twice
+                  uint32_t h[4], l[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                  for (int x = 0; x < 8; ++x) {
-                    if (DAC == kDacQuant)
-                      v[b][x] = dac_code(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am, p.inp_res, rcp_res);
-                    else
-                      v[b][x] = dac_normalise(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am);
+                  for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(v[b][2 * x], v[b][2 * x + 1]);
+                  if (a_split || (cache_now && p.cache_lo)) {
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+                      l[x] = cvt_bf16x2(v[b][2 * x] - __uint_as_float(h[x] << 16),
+                                        v[b][2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u));
                   }
+                  sts128(a_hi + soff, h[0], h[1], h[2], h[3]);
+                  if (a_split) sts128(a_lo + soff, l[0], l[1], l[2], l[3]);
+                  if (cache_now) {
+                    *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
+                    if (p.cache_lo) *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
+                  }
+                } else {
+                  if (has_ir && m[b].src >= 0) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], m[b].ir);
+                  }
+                  if (cache_now) {
+                    // the operand as dW wants it: clamped (not quantised), times the per-row scale, hi (+ lo) bf16
+                    float c8[8];
+                    const float sc = p.cache_scale ? s_cscale[task >> 3] : 1.f;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) c8[x] = p.cache_scale ? v[b][x] * sc : v[b][x];
+                    uint32_t h[4];
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(c8[2 * x], c8[2 * x + 1]);
+                    *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
+                    if (p.cache_lo) {
+                      uint32_t l[4];
+#pragma unroll
+                      for (int x = 0; x < 4; ++x)
+                        l[x] = cvt_bf16x2(c8[2 * x] - __uint_as_float(h[x] << 16), c8[2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u));
+                      *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
+                    }
+                  }
+                  if (m[b].src >= 0) {
+                    const float rcp_am = has_am ? __frcp_rn(m[b].am) : 1.f;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                      if (DAC == kDacQuant)
+                        v[b][x] = dac_code_clamped(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am, p.inp_res, rcp_res);
+                      else
+                        v[b][x] = dac_normalise_clamped(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am);
+                    }
+                  }
+                  store8_rt(a_hi, a_lo, soff, v[b], a_split);
                 }
-                store8_rt(a_hi, a_lo, sw128_offset(task >> 3, task & 7), v[b], a_split);
               }
             }
           }
@@ -975,16 +1050,231 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   teardown_cta(sm, tmem_base, p.tmem_cols);
 }
 
-// dW[e] = sum over the expert's segments, in segment order (fixed order: bit-reproducible).
+
+// ---------------------------------------------------------------------------- dW from cached operands
+// Both operands already exist in HBM as bf16 hi (+ lo) terms in padded tile-row order (written by the
+// prologue of the forward kernel and by the prologue / epilogue of the input-gradient kernels): rows
+// [128*t, 128*t+128) belong to tile t of the expert-sorted slot list, rows past an expert's last slot
+// are zero.  The contraction runs over those rows, so the tiles come straight from TMA as MN-major
+// operands and no thread touches the data before the tensor core does: six warps per CTA (TMA, MMA,
+// four epilogue warps).
+
+struct DwTmaParams {
+  int E, K, N;
+  int BN, m_tiles, n_tiles, stages;
+  int MB, NB;
+  int seg;              // padded rows per work segment (multiple of 64); 0: one segment per expert
+  uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
+  const int32_t* offsets;
+  float* dw;
+  float* partials;
+  int32_t* status;
+};
+
+// Segment `idx` in padded row space: expert e owns ceil(count_e/128)*128 padded rows.
+struct PadSegIter {
+  const int32_t* off; int E, seg; int e; int64_t before; int64_t pad_base;
+  __device__ PadSegIter(const int32_t* o, int E_, int seg_) : off(o), E(E_), seg(seg_), e(0), before(0), pad_base(0) {}
+  __device__ bool get(int64_t idx, int& ex, int64_t& beg, int64_t& end) {
+    while (e < E) {
+      const int len = (off[e + 1] - off[e] + kBM - 1) / kBM * kBM;
+      const int ns = seg > 0 ? (len + seg - 1) / seg : 1;
+      if (idx < before + ns) {
+        ex = e;
+        beg = seg > 0 ? pad_base + (idx - before) * seg : pad_base;
+        end = seg > 0 ? min(beg + seg, pad_base + len) : pad_base + len;
+        return true;
+      }
+      before += ns;
+      pad_base += len;
+      ++e;
+    }
+    return false;
+  }
+};
+
+constexpr int kDwTmaThreads = 6 * 32;
+
+template <bool SPLIT>
+__global__ void __launch_bounds__(kDwTmaThreads, 1)
+dw_tc_tma_kernel(const __grid_constant__ CUtensorMap ta_hi, const __grid_constant__ CUtensorMap ta_lo,
+                 const __grid_constant__ CUtensorMap tb_hi, const __grid_constant__ CUtensorMap tb_lo, DwTmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  setup_cta(sm, p.stages, p.tmem_cols, 1, 4);
+  const uint32_t tmem_base = *sm.tmem_ptr;
+  int32_t* status = p.status;
+  const int mb_tiles = (p.m_tiles + p.MB - 1) / p.MB, nb_tiles = (p.n_tiles + p.NB - 1) / p.NB;
+  const int tps = mb_tiles * nb_tiles;
+  const int n_acc = p.MB * p.NB;
+  const uint32_t a_tile = (SPLIT ? 2u : 1u) * p.a_bytes;
+  const uint32_t b_tile = (SPLIT ? 2u : 1u) * p.b_bytes;
+  const uint32_t b_region = static_cast<uint32_t>(p.MB) * a_tile;
+  const int b_blocks = static_cast<int>(p.b_bytes / kMnBlock);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&ta_hi); tma_prefetch_desc(&tb_hi);
+      if (SPLIT) { tma_prefetch_desc(&ta_lo); tma_prefetch_desc(&tb_lo); }
+      RingPos rp(p.stages);
+      PadSegIter si(p.offsets, p.E, p.seg);
+      const uint32_t tx_bytes = (SPLIT ? 2u : 1u) * (p.MB * 2u + p.NB * static_cast<uint32_t>(b_blocks)) * kMnBlock;
+      bool alive = true;
+      for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+        int e; int64_t beg, end;
+        const int64_t seg_idx = w / tps;
+        if (!si.get(seg_idx, e, beg, end)) break;
+        const int sub = static_cast<int>(w - seg_idx * tps);
+        const int nbk = sub % nb_tiles, mbk = sub / nb_tiles;
+        const int chunks = static_cast<int>((end - beg) / kBK);
+        for (int kc = 0; kc < chunks; ++kc, rp.next()) {
+          const int s = rp.s;
+          if (!mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 16, 32)) { alive = false; break; }
+          const uint32_t stage = sm.base_u32 + s * p.stage_bytes;
+          const uint32_t bar = bar_full_b(sm.bars, s);
+          const int row = static_cast<int>(beg) + kc * kBK;
+          mbar_arrive_expect_tx(bar, tx_bytes);
+          for (int ma = 0; ma < p.MB; ++ma) {
+            const int col = (mbk * p.MB + ma) * kBM;
+            const uint32_t dst = stage + ma * a_tile;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              tma_load_3d(dst + blk * kMnBlock, &ta_hi, bar, 0, row, (col >> 6) + blk);
+              if (SPLIT) tma_load_3d(dst + p.a_bytes + blk * kMnBlock, &ta_lo, bar, 0, row, (col >> 6) + blk);
+            }
+          }
+          for (int nb = 0; nb < p.NB; ++nb) {
+            const int col = (nbk * p.NB + nb) * p.BN;
+            const uint32_t dst = stage + b_region + nb * b_tile;
+            for (int blk = 0; blk < b_blocks; ++blk) {
+              tma_load_3d(dst + blk * kMnBlock, &tb_hi, bar, 0, row, (col >> 6) + blk);
+              if (SPLIT) tma_load_3d(dst + p.b_bytes + blk * kMnBlock, &tb_lo, bar, 0, row, (col >> 6) + blk);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
+      RingPos rp(p.stages);
+      PadSegIter si(p.offsets, p.E, p.seg);
+      uint32_t acc_it = 0;
+      bool alive = true;
+      for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+        int e; int64_t beg, end;
+        if (!si.get(w / tps, e, beg, end)) break;
+        const int chunks = static_cast<int>((end - beg) / kBK);
+        if (chunks == 0) continue;
+        const int buf = acc_it & 1u;
+        const uint32_t aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 12)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t d_base = tmem_base + static_cast<uint32_t>(buf * n_acc * p.BN);
+        for (int kc = 0; kc < chunks; ++kc, rp.next()) {
+          const int s = rp.s;
+          if (!mbar_wait(bar_full_b(sm.bars, s), rp.ph, sm.abort_flag, status, 13)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
+          for (int acc = 0; acc < n_acc; ++acc) {
+            const int ma = acc / p.NB, nb = acc - ma * p.NB;
+            const uint32_t at = sa + ma * a_tile, bt = sa + b_region + nb * b_tile;
+            const uint64_t da_hi = make_smem_desc_mn_sw128(at, kMnBlock);
+            const uint64_t da_lo = make_smem_desc_mn_sw128(at + p.a_bytes, kMnBlock);
+            const uint64_t db_hi = make_smem_desc_mn_sw128(bt, kMnBlock);
+            const uint64_t db_lo = make_smem_desc_mn_sw128(bt + p.b_bytes, kMnBlock);
+            const uint32_t d_tmem = d_base + static_cast<uint32_t>(acc * p.BN);
+#pragma unroll
+            for (int k16 = 0; k16 < kBK / 16; ++k16) {
+              const uint64_t adv = static_cast<uint64_t>(k16 * (16 * 128 / 16));
+              umma_bf16(d_tmem, da_hi + adv, db_hi + adv, idesc, (kc | k16) != 0 ? 1u : 0u);
+              if (SPLIT) {
+                umma_bf16(d_tmem, da_hi + adv, db_lo + adv, idesc, 1u);
+                umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
+              }
+            }
+          }
+          umma_commit(bar_empty(sm.bars, s));
+        }
+        if (alive) umma_commit(bar_tfull(sm.bars, buf));
+        ++acc_it;
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    PadSegIter si(p.offsets, p.E, p.seg);
+    uint32_t acc_it = 0;
+    bool alive = true;
+    for (int64_t w = blockIdx.x; alive; w += gridDim.x) {
+      int e; int64_t beg, end;
+      const int64_t seg_idx = w / tps;
+      if (!si.get(seg_idx, e, beg, end)) break;
+      const int sub = static_cast<int>(w - seg_idx * tps);
+      const int nbk = sub % nb_tiles, mbk = sub / nb_tiles;
+      const int chunks = static_cast<int>((end - beg) / kBK);
+      float* out_base = p.partials ? p.partials + seg_idx * p.K * p.N : p.dw + static_cast<int64_t>(e) * p.K * p.N;
+      if (chunks == 0) {   // only without segment splitting: an expert nobody was routed to
+        for (int acc = 0; acc < n_acc; ++acc) {
+          const int ma = acc / p.NB, nb = acc - ma * p.NB;
+          const int m = (mbk * p.MB + ma) * kBM + r, n0 = (nbk * p.NB + nb) * p.BN;
+          if (m < p.K)
+            for (int n = n0; n < min(n0 + p.BN, p.N); ++n) out_base[static_cast<int64_t>(m) * p.N + n] = 0.f;
+        }
+        continue;
+      }
+      const int buf = acc_it & 1u;
+      const uint32_t aph = (acc_it >> 1) & 1u;
+      bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 15, 64);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      tc_fence_after();
+      for (int acc = 0; acc < n_acc; ++acc) {
+        const int ma = acc / p.NB, nb = acc - ma * p.NB;
+        const int m = (mbk * p.MB + ma) * kBM + r, n0 = (nbk * p.NB + nb) * p.BN;
+        float* dst = out_base + static_cast<int64_t>(m) * p.N;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                               static_cast<uint32_t>((buf * n_acc + acc) * p.BN);
+#pragma unroll 1
+        for (int c0 = 0; c0 < p.BN; c0 += 16) {
+          float v[16];
+          tmem_ld16(taddr + c0, v);
+          tmem_ld_wait();
+          const int n = n0 + c0;
+          if (m < p.K && n < p.N) {
+            if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
+#pragma unroll
+              for (int x = 0; x < 4; ++x)
+                *reinterpret_cast<float4*>(dst + n + 4 * x) = make_float4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
+            } else {
+#pragma unroll
+              for (int x = 0; x < 16; ++x)
+                if (n + x < p.N) dst[n + x] = v[x];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
+      ++acc_it;
+    }
+  }
+  teardown_cta(sm, tmem_base, p.tmem_cols);
+}
+
+// dW[e] = sum over the expert's segments, in segment order (fixed order: bit-reproducible).  `pad`: the
+// segments were cut in padded row space (every expert's count rounded up to a multiple of `pad`).
 __global__ void dw_reduce_kernel(const float* __restrict__ partials, const int32_t* __restrict__ offsets, int E, int seg,
-                                 int64_t kn, float* __restrict__ dw) {
+                                 int64_t kn, float* __restrict__ dw, int pad) {
   __shared__ int s_first, s_count;
   const int e = blockIdx.y;
   if (threadIdx.x == 0) {
     int first = 0;
-    for (int x = 0; x < e; ++x) first += (offsets[x + 1] - offsets[x] + seg - 1) / seg;
+    for (int x = 0; x < e; ++x) first += ((offsets[x + 1] - offsets[x] + pad - 1) / pad * pad + seg - 1) / seg;
     s_first = first;
-    s_count = (offsets[e + 1] - offsets[e] + seg - 1) / seg;
+    s_count = ((offsets[e + 1] - offsets[e] + pad - 1) / pad * pad + seg - 1) / seg;
   }
   __syncthreads();
   const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
@@ -1085,6 +1375,11 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   const bool b_split = a->precision == AMOE_PREC_SPLIT && a->w_lo != nullptr;
   p.a_split = a_split; p.b_split = b_split;
   p.epi.acc_mul = quant ? p.inp_res : 1.f;
+  p.cache_hi = reinterpret_cast<__nv_bfloat16*>(a->a_cache_hi);
+  p.cache_lo = reinterpret_cast<__nv_bfloat16*>(a->a_cache_lo);
+  p.cache_stride = a->cache_rows; p.cache_scale = a->a_cache_scale;
+  AMOE_REQUIRE(!(p.cache_hi || p.epi.out_cache_hi) || a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(!p.cache_hi || (p.Kc % 8 == 0 && aligned16(p.cache_hi) && aligned16(p.cache_lo)), AMOE_ERR_BAD_SHAPE);
 
   p.a_bytes = a_split ? 2 * kATile : kATile;
   p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
@@ -1096,7 +1391,8 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   p.tmem_cols = pow2_cols(2 * p.BN);
   {
     // Split the 16 worker warps between epilogue and prologue by estimated instruction counts.
-    const double per_prod = (quant ? 13.0 : (dac && (p.ir || p.a_absmax) ? 18.0 : 3.0)) + (a_split ? 5.0 : 2.0);
+    const double per_prod = (quant ? 13.0 : (dac && (p.ir || p.a_absmax) ? 18.0 : 3.0)) + (a_split ? 5.0 : 2.0) +
+                            (p.cache_hi ? (dac ? 6.0 : 2.0) : 0.0);
     double per_epi = 8.0;
     if (!is_dx) per_epi += (a->noise_std > 0.f ? 26.0 : 0.0) + (a->noise ? 2.0 : 0.0) + (p.epi.adc.on ? 9.0 : 0.0) +
                            (a->out_codes ? 3.0 : 0.0);
@@ -1135,6 +1431,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   int epi = kEpiGeneric;
   if (p.epi.vec4 && !is_dx && a->noise == nullptr) epi = kEpiFwd;
   if (p.epi.vec4 && is_dx && (a->x_ref == nullptr || a->x_ref_dtype == AMOE_F32 || a->x_ref_stride % 8 == 0)) epi = kEpiDx;
+  AMOE_REQUIRE(!p.epi.out_cache_hi || epi == kEpiDx, AMOE_ERR_UNSUPPORTED);
   const int dacm = is_dx ? kDacNone : (quant ? kDacQuant : kDacNorm);
 #define AMOE_LAUNCH_TC(DAC, F32, EPI)                                                                                  \
   do {                                                                                                                 \
@@ -1169,7 +1466,69 @@ extern "C" int amoe_debug_timeline(long long* host, int clear) {
 size_t dw_tc_workspace_bytes(int64_t P, int E, int K, int N) {
   const int seg = dw_segment_slots(P, K, N);
   if (seg == 0) return 0;
-  return static_cast<size_t>((P + seg - 1) / seg + E) * K * N * sizeof(float);
+  // segments are cut per expert, in padded row space when the operands come from the caches
+  return static_cast<size_t>((P + static_cast<int64_t>(kBM) * E + seg - 1) / seg + E) * K * N * sizeof(float);
+}
+
+static int launch_dw_tma(const amoe_dw_args* a, cudaStream_t stream) {
+  DwTmaParams p{};
+  p.E = a->E; p.K = a->K; p.N = a->N;
+  // output tiles start on 64-column blocks of the cache layout
+  p.BN = a->N > 64 ? 128 : 64;
+  p.n_tiles = (a->N + p.BN - 1) / p.BN;
+  p.m_tiles = (a->K + kBM - 1) / kBM;
+  p.offsets = a->expert_offsets;
+  p.dw = a->dw; p.status = a->dev_status;
+  p.seg = dw_segment_slots(a->P, a->K, a->N);
+  const size_t need = dw_tc_workspace_bytes(a->P, a->E, a->K, a->N);
+  if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
+    p.seg = 0;
+  p.partials = p.seg > 0 ? reinterpret_cast<float*>(a->workspace) : nullptr;
+  const bool split = a->x_lo != nullptr && a->g_lo != nullptr;
+  AMOE_REQUIRE(split || (a->x_lo == nullptr && a->g_lo == nullptr), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(aligned16(a->x_hi) && aligned16(a->x_lo) && aligned16(a->g_hi) && aligned16(a->g_lo), AMOE_ERR_BAD_SHAPE);
+  p.a_bytes = 2 * kMnBlock;
+  p.b_bytes = static_cast<uint32_t>((p.BN + 63) / 64) * kMnBlock;
+  p.MB = 1; p.NB = 1;
+  if (p.m_tiles >= 2 && p.m_tiles >= p.n_tiles) p.MB = 2;
+  else if (p.n_tiles >= 2) p.NB = 2;
+  p.stage_bytes = (split ? 2u : 1u) * (p.MB * p.a_bytes + p.NB * p.b_bytes);
+  p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
+  p.tmem_cols = pow2_cols(2 * p.MB * p.NB * p.BN);
+  const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra;
+  const int64_t pad_rows = a->P + static_cast<int64_t>(kBM) * a->E;
+  const int64_t segs = p.seg > 0 ? (pad_rows + p.seg - 1) / p.seg + a->E : a->E;
+  const int64_t items = segs * ((p.m_tiles + p.MB - 1) / p.MB) * ((p.n_tiles + p.NB - 1) / p.NB);
+  const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
+  CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
+  int s = encode_tmap_bf16_3d(&ta_hi, a->x_hi, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>((a->K + 63) / 64), 64, kBK);
+  if (s != AMOE_OK) return s;
+  s = encode_tmap_bf16_3d(&tb_hi, a->g_hi, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>((a->N + 63) / 64), 64, kBK);
+  if (s != AMOE_OK) return s;
+  ta_lo = ta_hi; tb_lo = tb_hi;
+  if (split) {
+    s = encode_tmap_bf16_3d(&ta_lo, a->x_lo, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>((a->K + 63) / 64), 64, kBK);
+    if (s != AMOE_OK) return s;
+    s = encode_tmap_bf16_3d(&tb_lo, a->g_lo, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>((a->N + 63) / 64), 64, kBK);
+    if (s != AMOE_OK) return s;
+  }
+  if (split) {
+    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dw_tc_tma_kernel<true><<<grid, kDwTmaThreads, smem, stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, p);
+  } else {
+    AMOE_CUDA(cudaFuncSetAttribute(dw_tc_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dw_tc_tma_kernel<false><<<grid, kDwTmaThreads, smem, stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, p);
+  }
+  AMOE_LAUNCH_CHECK("dw_tc_tma");
+  if (p.seg > 0) {
+    const int64_t kn = static_cast<int64_t>(a->K) * a->N;
+    dim3 rg(static_cast<unsigned>((kn / 4 + 255) / 256), a->E);
+    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, kBM);
+    AMOE_LAUNCH_CHECK("dw_reduce");
+  }
+  return AMOE_OK;
 }
 
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
@@ -1189,6 +1548,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   p.x_vec_ok = aligned16(a->x) && ((a->x_stride * (a->x_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.g_vec_ok = aligned16(a->g) && ((a->g_stride * (a->g_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.dw = a->dw; p.status = a->dev_status;
+  if (a->x_hi != nullptr) return launch_dw_tma(a, stream);
   // Large problems: cut every expert's slot range into segments so that the work items outnumber the
   // SMs and a popular expert does not become one long item; the partial tiles go to the workspace and
   // are summed in segment order afterwards.
@@ -1232,7 +1592,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   if (p.seg > 0) {
     const int64_t kn = static_cast<int64_t>(a->K) * a->N;
     dim3 rg(static_cast<unsigned>((kn / 4 + 255) / 256), a->E);
-    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw);
+    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, 1);
     AMOE_LAUNCH_CHECK("dw_reduce");
   }
   return AMOE_OK;

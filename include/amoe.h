@@ -194,11 +194,24 @@ typedef struct amoe_cvmm_args {
   float* ir_grad;                 /* [P] by sorted position, or NULL */
   int32_t ir_grad_relative; float ir_grad_scale;
   unsigned long long* keep_count; /* one counter, incremented; or NULL */
+  /* Operand caches for amoe_cvmm_dw (tensor-core precisions only; optional).  Rows are indexed by padded tile row:
+   * the 128-row tiles of the expert-sorted slot list are numbered through all experts, tile t owns rows
+   * [128t, 128t+128), rows past an expert's last slot are written as zeros.  Arrays are bf16, laid out as
+   * [ceil(cols/64)][cache_rows][64] (64-column blocks, so that a 64 x 64 tile is one contiguous 8 KiB piece), with
+   * cache_rows >= amoe_padded_rows(P,E); `lo` arrays hold the rounding residual of `hi` and may be NULL.
+   *   a_cache_*  [rows, cols of A]: clamp(A[r,:], +-ir) * a_cache_scale[a_row[i]]   (needs cols % 8 == 0)
+   *   out_cache_* (amoe_cvmm_dx) [rows, cols of out]: the result row                 (needs cols % 16 == 0)
+   * No counterpart in the reference: its dW kernel re-reads and re-converts fp32 rows. */
+  void* a_cache_hi; void* a_cache_lo; const float* a_cache_scale;
+  void* out_cache_hi; void* out_cache_lo;
+  int64_t cache_rows;
   /* plumbing */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
   int32_t* dev_status;            /* int32[4] or NULL */
 } amoe_cvmm_args;
 size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E);
+/* Rows to allocate for an operand cache: (P/128 + E) * 128, an upper bound on the padded tile rows. */
+int64_t amoe_padded_rows(int64_t P, int32_t E);
 int amoe_cvmm_fwd(const amoe_cvmm_args* args, amoe_stream_t stream);
 int amoe_cvmm_dx(const amoe_cvmm_args* args, amoe_stream_t stream);
 
@@ -225,6 +238,10 @@ typedef struct amoe_dw_args {
   int32_t g_div;                  /* >=1 */
   const float* g_scale;           /* indexed by g_row[i], or NULL */
   float* dw;                      /* [E,K,N] */
+  /* Alternative inputs (tensor-core precisions): both operands as cached bf16 hi (+ lo) terms in padded tile-row
+   * order (see amoe_cvmm_args).  With x_hi and g_hi given, x/g/x_row/g_row/ir/g_scale are not read: clamp and
+   * scale are already in the caches.  Layout [ceil(cols/64)][cache_rows][64]; cache_rows >= amoe_padded_rows. */
+  const void* x_hi; const void* x_lo; const void* g_hi; const void* g_lo; int64_t cache_rows;
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_dw_workspace_bytes, or NULL */
   int32_t* dev_status;
 } amoe_dw_args;
