@@ -88,6 +88,8 @@ struct TcParams {
   int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
+  int prod_groups;      // 1, or 2: the prologue warps form two groups that take alternate stages, so that one
+                        // group's global-load latency overlaps the other group's arithmetic
   uint32_t tmem_cols, stage_bytes, a_bytes, b_bytes;
   uint32_t cs_off;      // offset of the per-warp column-scale staging area in dynamic shared memory
   int cs_per_warp;      // floats per warp and array in that area
@@ -430,7 +432,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_prod = kWorkerWarps - p.n_epi;
-  setup_cta(sm, p.stages, p.tmem_cols, n_prod, p.n_epi, n_prod, p.n_epi);
+  setup_cta(sm, p.stages, p.tmem_cols, n_prod / p.prod_groups, p.n_epi, n_prod, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
 
@@ -614,8 +616,13 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- operand prologue (A tiles)
-    const int np = n_prod * 32;
-    const int pt = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np-1
+    const int np_all = n_prod * 32;
+    const int pt_all = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np_all-1
+    const int pw = warp - (2 + p.n_epi);
+    const bool two = p.prod_groups == 2;
+    const uint32_t grp = two ? static_cast<uint32_t>(pw & 1) : 0u;
+    const int np = two ? (n_prod >> 1) * 32 : np_all;      // threads that share one stage
+    const int pt = two ? (pw >> 1) * 32 + lane : pt_all;
     const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
     const bool a_split = p.a_split != 0;
     const float rcp_res = quant_rcp(p.inp_res);
@@ -629,7 +636,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       if (!ti.get(t, e, row0, rows)) break;
       // everyone is done with the previous tile's metadata
       if (!group_sync(bar_group(sm.bars, 0), sync_round, sm.abort_flag, status, 9)) break;
-      for (int r = pt; r < kBM; r += np) {
+      for (int r = pt_all; r < kBM; r += np_all) {
         RowMeta m;
         m.src = -1; m.ir = 1.f; m.rcp_ir = 1.f; m.am = 1.f;
         float csc = 0.f;
@@ -654,6 +661,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
         const bool do_cache = p.cache_hi != nullptr && nt == 0;
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
+          if (two && (it & 1u) != grp) continue;
           const int s = rp.s;
           if (pt == 0) TL(2, it, 0);
           bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 6);
@@ -1389,6 +1397,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
+  p.prod_groups = 1;
   {
     // Split the 16 worker warps between epilogue and prologue by estimated instruction counts.
     const double per_prod = (quant ? 13.0 : (dac && (p.ir || p.a_absmax) ? 18.0 : 3.0)) + (a_split ? 5.0 : 2.0) +
@@ -1404,6 +1413,12 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
+  }
+  // two prologue groups on alternate stages need a ring with an even number of stages (a stage then always
+  // belongs to the same group) and enough stages per tile to alternate on
+  if (p.stages >= 4 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr) {
+    p.prod_groups = 2;
+    p.stages &= ~1;
   }
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
