@@ -87,6 +87,13 @@ SIGNATURES = {
     "amoe_select_sort": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp, vp, vp, vp, vp, vp,
                                    C.c_size_t, vp]),
     "amoe_gate_backward": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
+    "amoe_router_logits": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, C.c_int32, C.c_int32, vp, C.c_int32,
+                                     vp, vp]),
+    "amoe_router_backward_w_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
+    "amoe_router_backward_w": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, vp, C.c_int32, vp, vp, vp, vp,
+                                         C.c_int64, C.c_int32, vp, vp, C.c_size_t, vp]),
+    "amoe_combine_router": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32, vp, vp, C.c_int32, vp, vp,
+                                      C.c_int32, C.c_int32, vp, C.c_int32, C.c_int64, vp]),
     "amoe_expert_offsets": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "amoe_weight_prepass_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "amoe_prepared_dims": (None, [C.c_int32, C.c_int32, C.POINTER(C.c_int32 * 4)]),

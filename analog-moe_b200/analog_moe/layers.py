@@ -106,11 +106,8 @@ class _FusedAnalogStep(torch.autograd.Function):
             pw_up = prepass(keys, mod_up)
             ops.set_tag("down")
             pw_dn = prepass(values, mod_dn)
-        logits = F.linear(x2, w_sel)
-        if getattr(layer, "router_bias", None) is not None:
-            logits = logits + layer.router_bias
-        logits = logits.float()
         ops.set_tag("up")
+        logits = ops.router_logits(x2, w_sel, getattr(layer, "router_bias", None))
         r = ops.select_sort(logits, k, apply_sigmoid=True)
         inp_res = fwd.inp_res
         inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
@@ -232,15 +229,13 @@ class _FusedAnalogStep(torch.autograd.Function):
                                       grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
                                       out_dtype=x2.dtype)
             if need_x:
-                grad_x = ops.combine(dxr, None, T, k)
+                # sum over k plus the router's own input gradient in one pass
+                grad_x = ops.combine_router(dxr, T, k, dgate, gate, raw_sel, w_sel)
         # ---- router
         grad_sel = None
-        if need_sel or need_x:
-            dlogits = ops.gate_backward(dgate, gate, raw_sel, w_sel.shape[0]).to(x2.dtype)
-            if need_sel:
-                grad_sel = dlogits.t() @ x2
-            if need_x:
-                grad_x.addmm_(dlogits, w_sel)
+        if need_sel:
+            grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
+                                             raw_sel=raw_sel).to(w_sel.dtype)
         grad_ir = None
         if need_ir:
             grad_ir = torch.stack([

@@ -17,7 +17,7 @@ from ._cabi import lib, check, ptr, stream_ptr, dtype_code, launch_on
 KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 3, "amoe_row_absmax": 1,
                     "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 2, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
-                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1}
+                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1, "amoe_router_backward_w": 2}
 
 
 class Trace:
@@ -136,6 +136,47 @@ def select_sort(logits: torch.Tensor, k: int, apply_sigmoid: bool = True) -> Rou
     _call("amoe_select_sort", ptr(logits), T, E, k, int(apply_sigmoid), ptr(raw_sel), ptr(gate), ptr(sel), ptr(tok),
                                ptr(slot), ptr(off), ptr(ws), nbytes, stream_ptr())
     return Routing(raw_sel, gate, sel, tok, slot, off)
+
+
+def router_logits(x2: torch.Tensor, w_sel: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 gate logits [T,E] of x2 [T,D] and w_sel [E,D] (rounded through bf16 when x2 is bf16)."""
+    x2 = _rows(x2)
+    w = w_sel.contiguous()
+    T, D = x2.shape
+    E = w.shape[0]
+    out = torch.empty(T, E, dtype=torch.float32, device=x2.device)
+    b = None if bias is None else bias.float().contiguous()
+    _call("amoe_router_logits", ptr(x2), dtype_code(x2), x2.stride(0), T, D, ptr(w), dtype_code(w), E, ptr(b),
+          int(x2.dtype == torch.bfloat16), ptr(out), stream_ptr())
+    return out
+
+
+def router_backward_w(x2: torch.Tensor, dgate: torch.Tensor, gate: torch.Tensor, token_index: torch.Tensor,
+                      slot_index: torch.Tensor, offsets: torch.Tensor, E: int, apply_sigmoid: bool = True,
+                      raw_sel: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gradient [E,D] fp32 of the router weight from the gradient of the k picked gate values."""
+    x2 = _rows(x2)
+    T, D = x2.shape
+    P = token_index.numel()
+    out = torch.empty(E, D, dtype=torch.float32, device=x2.device)
+    nbytes = lib.amoe_router_backward_w_workspace_bytes(P, E, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
+    _call("amoe_router_backward_w", ptr(x2), dtype_code(x2), x2.stride(0), T, D, ptr(dgate), ptr(gate), int(apply_sigmoid),
+          ptr(token_index), ptr(slot_index), ptr(offsets), ptr(raw_sel), P, E, ptr(out), ptr(ws), nbytes, stream_ptr())
+    return out
+
+
+def combine_router(res: torch.Tensor, T: int, k: int, dgate: torch.Tensor, gate: torch.Tensor, raw_sel: torch.Tensor,
+                   w_sel: torch.Tensor, apply_sigmoid: bool = True) -> torch.Tensor:
+    """sum over k of the rows [T*k,N] plus the router's input-gradient term, [T,N] in the rows' dtype."""
+    res = _rows(res)
+    w = w_sel.contiguous()
+    N = res.shape[1]
+    y = torch.empty(T, N, dtype=res.dtype, device=res.device)
+    _call("amoe_combine_router", ptr(res), dtype_code(res), res.stride(0), T, k, N, ptr(dgate), ptr(gate),
+          int(apply_sigmoid), ptr(raw_sel), ptr(w), dtype_code(w), w.shape[0], ptr(y), dtype_code(y), y.stride(0),
+          stream_ptr())
+    return y
 
 
 def gate_backward(dgate: torch.Tensor, gate: torch.Tensor, raw_sel: torch.Tensor, E: int,

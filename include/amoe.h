@@ -83,6 +83,30 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
 int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw_sel, int64_t T, int32_t E, int32_t k,
                        int32_t apply_sigmoid, float* dlogits, amoe_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------
+ * The router around the path (the base layer's `F.linear(input, expert_sel.weight)`, restated in the reference at
+ * tests/test_moe_layer_aihwkit.py:71-76, and its autograd backward).
+ * amoe_router_logits: logits[t,e] = sum_d x[t,d]*w[e,d] (+ bias[e]), fp32 accumulate; round_bf16 rounds the result
+ *   (and the sum with the bias) to bf16 the way a bf16 linear layer would.  w is [E,D] contiguous.
+ * amoe_router_backward_w: dw_sel[e,:] = sum over the slots i of expert e of c_i * x[token_index[i],:], with
+ *   c = dgate*(1-g)*g (apply_sigmoid) or dgate, dgate/gate indexed by flat slot (slot_index[i]).  Fixed summation order.
+ *   raw_sel [T,k] (optional) enables a token-major variant that reads x once when the [E,D] gradient fits in shared memory.
+ * amoe_combine_router: y[t,:] = sum_j res[t*k+j,:] + sum_j c[t,j] * w_sel[raw_sel[t,j],:]: the sum over k of the
+ *   up-projection's input gradient (cvmm.py:890-891) and the router's own input gradient in one pass.
+ * ---------------------------------------------------------------------------------------- */
+int amoe_router_logits(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const void* w,
+                       int32_t w_dtype, int32_t E, const float* bias, int32_t round_bf16, float* logits,
+                       amoe_stream_t stream);
+size_t amoe_router_backward_w_workspace_bytes(int64_t P, int32_t E, int32_t D);
+int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const float* dgate,
+                           const float* gate, int32_t apply_sigmoid, const int32_t* token_index,
+                           const int32_t* slot_index, const int32_t* expert_offsets, const int32_t* raw_sel, int64_t P,
+                           int32_t E, float* dw_sel, void* workspace, size_t workspace_bytes, amoe_stream_t stream);
+int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, int64_t T, int32_t k, int32_t N,
+                        const float* dgate, const float* gate, int32_t apply_sigmoid, const int32_t* raw_sel,
+                        const void* w_sel, int32_t w_dtype, int32_t E, void* y, int32_t y_dtype, int64_t y_stride,
+                        amoe_stream_t stream);
+
 /* expert_offsets [E+1] from an already sorted expert-id list (a CVMMSel.sel built elsewhere). */
 int amoe_expert_offsets(const int32_t* sel_sorted, int64_t P, int32_t E, int32_t* expert_offsets,
                         int32_t* dev_status, amoe_stream_t stream);

@@ -494,7 +494,8 @@ def test_fused_layer_step_equals_the_composition(dev, prec, dtype, use_ir):
     for key in results[True]:
         a, b = results[True][key], results[False][key]
         assert torch.isfinite(a).all(), key
-        tol = 2e-2 if dtype != torch.float32 else (3e-5 if key in ("dkeys", "dvalues") and prec != "simt" else 2e-6)
+        # (and the gate logits come from two different matmul kernels, so the gates differ in their last bits)
+        tol = 2e-2 if dtype != torch.float32 else (3e-5 if key in ("dkeys", "dvalues") and prec != "simt" else 1e-5)
         scale = max(1.0, float(b.abs().max()))
         err = float((a - b).abs().max())
         assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"
@@ -536,3 +537,44 @@ def test_dw_from_operand_caches_equals_dw_from_rows(dev, prec, dtype):
         tol = 3e-5 if dtype == torch.float32 else 1e-2     # the split's own 2^-16, see the docstring
         assert float((a - b).abs().max()) <= tol * scale
     assert float(res[True][3][4].abs().max()) == 0.0      # the expert nobody was routed to
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,D,E,k,dtype", [(300, 136, 5, 2, torch.float32), (1000, 1024, 16, 4, torch.float32),
+                                           (257, 96, 64, 8, torch.float32), (129, 70, 3, 1, torch.float32),
+                                           (512, 256, 40, 4, torch.bfloat16)])
+def test_router_kernels_vs_torch(dev, T, D, E, k, dtype):
+    """Gate logits, router weight gradient and the fused (sum over k + router input gradient) against torch."""
+    from analog_moe import ops
+    g = torch.Generator().manual_seed(T + E)
+    x = torch.randn(T, D, generator=g).to(dev).to(dtype)
+    w = (torch.randn(E, D, generator=g) / D ** 0.5).to(dev).to(dtype)
+    bias = torch.randn(E, generator=g).to(dev).to(dtype)
+    logits = ops.router_logits(x, w, bias)
+    ref = (x.double() @ w.double().t())
+    if dtype == torch.bfloat16:
+        ref = (ref.to(dtype).double() + bias.double()).to(dtype).double()
+        assert float((logits.double() - ref).abs().max()) <= 0.04      # an ulp of bf16 at |logit| < 8
+    else:
+        ref = ref + bias.double()
+        assert float((logits.double() - ref).abs().max()) <= 1e-5
+    r = ops.select_sort(logits, k, apply_sigmoid=True)
+    dgate = torch.randn(T * k, generator=g).to(dev)
+    gate = r.gate
+    c = (dgate * (1 - gate.reshape(-1)) * gate.reshape(-1)).double()
+    dl = torch.zeros(T, E, dtype=torch.float64, device=dev)
+    dl.scatter_(1, r.raw_sel.long(), c.view(T, k))
+    # weight gradient
+    dw = ops.router_backward_w(x, dgate, gate, r.token_index, r.slot_index, r.expert_offsets, E)
+    ref_dw = dl.t() @ x.double()
+    assert float((dw.double() - ref_dw).abs().max()) <= 1e-4 * max(1.0, float(ref_dw.abs().max()))
+    dw2 = ops.router_backward_w(x, dgate, gate, r.token_index, r.slot_index, r.expert_offsets, E)
+    assert torch.equal(dw, dw2)                                           # fixed summation order
+    dw3 = ops.router_backward_w(x, dgate, gate, r.token_index, r.slot_index, r.expert_offsets, E, raw_sel=r.raw_sel)
+    assert float((dw3.double() - ref_dw).abs().max()) <= 1e-4 * max(1.0, float(ref_dw.abs().max()))   # token-major variant
+    # sum over k + router term
+    rows = torch.randn(T * k, D, generator=g).to(dev).to(dtype)
+    y = ops.combine_router(rows, T, k, dgate, gate, r.raw_sel, w)
+    ref_y = rows.double().view(T, k, D).sum(1) + dl @ w.double()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert float((y.double() - ref_y).abs().max()) <= tol * max(1.0, float(ref_y.abs().max()))
