@@ -109,6 +109,46 @@ __global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const flo
   st4<TY>(y + t * y_stride + n0, vec != 0, valid, acc);
 }
 
+// The same sum for rows of 16-byte aligned codes with N % 16 == 0: a thread owns 16 columns (one 16-byte load of
+// codes per slot), which amortises the per-slot scalars; per element the arithmetic and its order are unchanged.
+template <typename TY>
+__global__ void combine_codes16_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
+                                       const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
+                                       float step, const float* __restrict__ w, int64_t T, int k, int N,
+                                       TY* __restrict__ y, int64_t y_stride) {
+  const int ng = N / 16;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * ng) return;
+  const int64_t t = idx / ng;
+  const int n0 = static_cast<int>(idx - t * ng) * 16;
+  float acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+#pragma unroll 2
+  for (int j = 0; j < k; ++j) {
+    const int64_t s = t * k + j;
+    const float ws = w ? w[s] : 1.f;
+    const float rm = row_mult ? row_mult[s] : 1.f;
+    const int e = raw_sel[s];
+    const uint4 cd = __ldg(reinterpret_cast<const uint4*>(codes + s * N + n0));
+    const float4* csp = reinterpret_cast<const float4*>(col_scale + static_cast<int64_t>(e) * N + n0);
+    const uint32_t cw[4] = {cd.x, cd.y, cd.z, cd.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 cs = __ldg(csp + q);
+      const float csv[4] = {cs.x, cs.y, cs.z, cs.w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float cdv = static_cast<float>(static_cast<int8_t>((cw[q] >> (8 * c)) & 0xffu));
+        const float v = __fmul_rn(__fmul_rn(__fmul_rn(cdv, step), csv[c]), rm);
+        acc[4 * q + c] = fmaf(ws, v, acc[4 * q + c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) st4<TY>(y + t * y_stride + n0 + 4 * q, true, 4, acc + 4 * q);
+}
+
 // d[s] = res[row(s),:] . g[s/k,:]; one warp per slot; lane l walks the column quads l, l+32, ... and adds their
 // four products in column order into one accumulator (the same order in the kernel below, so that rows rebuilt
 // from codes give the same bits as materialised rows).
@@ -349,6 +389,17 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = blocks_for(n, 256);
   const int vec = (N % 4 == 0) && (y_stride % 4 == 0) && al16(y) && al16(col_scale) && al16(codes);
+  if (vec && N % 16 == 0 && (y_dtype == AMOE_F32 || y_dtype == AMOE_BF16)) {
+    const unsigned b16 = blocks_for(T * (N / 16), 128);
+    if (y_dtype == AMOE_F32)
+      combine_codes16_kernel<float><<<b16, 128, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
+                                                             reinterpret_cast<float*>(y), y_stride);
+    else
+      combine_codes16_kernel<__nv_bfloat16><<<b16, 128, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
+                                                                     reinterpret_cast<__nv_bfloat16*>(y), y_stride);
+    AMOE_LAUNCH_CHECK("combine_codes16");
+    return AMOE_OK;
+  }
   if (y_dtype == AMOE_F32)
     combine_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
                                                             reinterpret_cast<float*>(y), y_stride, vec);

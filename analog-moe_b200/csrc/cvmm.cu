@@ -52,6 +52,7 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   EpiParams e{};
   e.is_dx = 0; e.n_out = a->N;
   e.noise = a->noise; e.noise_std = a->noise_std; e.seed = a->seed; e.offset = a->offset; e.step_dev = a->step_dev;
+  philox_key_schedule(a->seed, e.pkeys);
   e.col_scale = a->col_scale;
   e.col_inv_scale = a->col_inv_scale;
   e.adc = make_adc(a->out_res, a->out_bound);

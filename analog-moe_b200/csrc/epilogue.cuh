@@ -14,6 +14,7 @@ struct EpiParams {
   int vec4;             // n_out % 4 == 0 and every per-column / per-row array is 16-byte aligned
   // forward
   const float* noise; float noise_std; uint64_t seed; uint32_t offset; const long long* step_dev;
+  uint32_t pkeys[20];   // Philox round keys of `seed`
   const float* col_scale;      // [E, n_out]
   const float* col_inv_scale;  // [E, n_out], needed by the ADC
   AdcParams adc;

@@ -318,8 +318,13 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 }
 
 // cs / cis: this chunk's 16 column scales and reciprocals in shared memory (staged by the warp).
+// kValue = false: only the ADC codes leave the kernel, the dequantised values are not formed.
+// The ADC code rint(x) is taken as (x + 1.5*2^23) - 1.5*2^23 (exact round-to-nearest-even for |x| < 2^22; codes are
+// at most 127 in magnitude), whose low mantissa byte is the code in two's complement.
+template <bool kValue>
 __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
                                               float v[16], const float* cs, const float* cis, int lane) {
+  constexpr float kMagic = 12582912.f;
   const bool noise = p.noise_std > 0.f, adc = p.adc.on;
   const float post = c.absmax * c.ir;
   uint32_t pk[4] = {0u, 0u, 0u, 0u};
@@ -329,18 +334,29 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
     float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
     if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
     if (adc) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
-    if (noise) z = philox_normal4_inline(p.seed, c.noise_offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
-                                         static_cast<uint32_t>((n0 >> 2) + qd));
+    if (noise) {
+      const uint4 w = philox4x32_10_keys(static_cast<uint32_t>(c.dst), static_cast<uint32_t>((n0 >> 2) + qd), kStreamOutNoise,
+                                         c.noise_offset, p.pkeys);
+      box_muller(w.x, w.y, z.x, z.y);
+      box_muller(w.z, w.w, z.z, z.w);
+    }
     const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w}, zv[4] = {z.x, z.y, z.z, z.w};
+    float tb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float acc = v[4 * qd + j] * p.acc_mul;
       if (noise) acc += (p.noise_std * sv[j]) * zv[j];
-      float code = 0.f;
-      if (adc) acc = adc_apply(acc, sv[j], iv[j], p.adc, code);
-      pk[qd] |= (static_cast<uint32_t>(static_cast<int>(code)) & 0xffu) << (8 * j);
-      v[4 * qd + j] = p.out_relu ? fmaxf(acc * post, 0.f) : acc * post;
+      if (adc) {
+        float x = acc * iv[j];
+        x = fminf(fmaxf(x, -p.adc.out_bound), p.adc.out_bound);
+        tb[j] = __fadd_rn(__fmul_rn(x, p.adc.inv_step), kMagic);
+        if (kValue) acc = ((tb[j] - kMagic) * p.adc.step) * sv[j];
+      }
+      if (kValue) v[4 * qd + j] = p.out_relu ? fmaxf(acc * post, 0.f) : acc * post;
     }
+    if (adc)
+      pk[qd] = __byte_perm(__byte_perm(__float_as_uint(tb[0]), __float_as_uint(tb[1]), 0x0040),
+                           __byte_perm(__float_as_uint(tb[2]), __float_as_uint(tb[3]), 0x0040), 0x5410);
   }
   if (p.out_codes && c.valid) {
     // 16 codes of the row; a row starts on a 16-byte boundary only if n_out is a multiple of 16
@@ -352,7 +368,7 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
       for (int qd = 0; qd < 4; ++qd) *reinterpret_cast<uint32_t*>(dstc + 4 * qd) = pk[qd];   // n_out % 4 == 0
     }
   }
-  store16_t(p, qr, n0, v, lane);
+  if (kValue) store16_t(p, qr, n0, v, lane);
 }
 
 __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
@@ -577,7 +593,10 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
               for (int j = 0; j < 12; ++j) v[j] = v[j + 4];   // rotate the next four columns in
             }
           } else {   // all 32 lanes: the quad exchange needs every lane, invalid rows are masked inside
-            if (EPI == kEpiFwd) epi_chunk_fwd(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+            if (EPI == kEpiFwd) {
+              if (p.epi.out != nullptr) epi_chunk_fwd<true>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+              else epi_chunk_fwd<false>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+            }
             else epi_chunk_dx(p.epi, ctx, qr, n0, v, lane);
           }
         }

@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(256) router_logits_smem_kernel(const TX* __res
 // threads x 4 columns per pass over D; the segment sums go to the workspace and a second kernel adds the
 // segments of each expert in order: no atomics, bit-reproducible.
 constexpr int kRwSeg = 64;
-constexpr int kRwMaxBlocks = 160;          // blocks of the token-major variant (one per SM, at most this many)
+constexpr int kRwMaxBlocks = 320;          // blocks of the token-major variant (two per SM, at most this many)
 constexpr size_t kRwSmemLimit = 200 * 1024;
 
 __device__ __forceinline__ bool find_segment(const int32_t* off, int E, int64_t idx, int& e, int& beg, int& end) {
@@ -335,15 +335,32 @@ __global__ void __launch_bounds__(256) router_dw_token_kernel(const TX* __restri
     *reinterpret_cast<float4*>(out + i) = *reinterpret_cast<const float4*>(s_acc + i);
 }
 
-__global__ void router_dw_block_reduce_kernel(const float* __restrict__ partials, int nb, int64_t n, float* __restrict__ dw) {
-  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
-  if (i >= n) return;
+// Block (32, 8): 32 column quads x 8 slices of the per-block results; a slice adds its contiguous range of blocks in
+// order, then the eight slice sums are added in slice order.
+__global__ void __launch_bounds__(256) router_dw_block_reduce_kernel(const float* __restrict__ partials, int nb, int64_t n,
+                                                                     float* __restrict__ dw) {
+  __shared__ float4 s_part[8][32];
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * 32 + threadIdx.x) * 4;
+  const int per = (nb + 7) / 8;
+  const int b0 = threadIdx.y * per, b1 = min(nb, b0 + per);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int b = 0; b < nb; ++b) {
-    const float4 v = *reinterpret_cast<const float4*>(partials + static_cast<int64_t>(b) * n + i);
-    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  if (i < n) {
+#pragma unroll 4
+    for (int b = b0; b < b1; ++b) {
+      const float4 v = *reinterpret_cast<const float4*>(partials + static_cast<int64_t>(b) * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
   }
-  *reinterpret_cast<float4*>(dw + i) = acc;
+  s_part[threadIdx.y][threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.y == 0 && i < n) {
+#pragma unroll
+    for (int sl = 1; sl < 8; ++sl) {
+      const float4 v = s_part[sl][threadIdx.x];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(dw + i) = acc;
+  }
 }
 
 // ------------------------------------------------------------------------------------ combine + router term
@@ -477,7 +494,8 @@ int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int
   // dgate/gate/raw_sel, which is what token_index/slot_index describe when P = T*k)
   const int k = static_cast<int>(P / T);
   if (raw_sel != nullptr && vec && static_cast<int64_t>(k) * T == P) {
-    int nb = sm_count() < kRwMaxBlocks ? sm_count() : kRwMaxBlocks;
+    const int per_sm = static_cast<size_t>(E) * D * sizeof(float) <= 100 * 1024 ? 2 : 1;
+    int nb = per_sm * sm_count() < kRwMaxBlocks ? per_sm * sm_count() : kRwMaxBlocks;
     if (nb > T) nb = static_cast<int>(T);
     const int tpb = static_cast<int>((T + nb - 1) / nb);
     nb = static_cast<int>((T + tpb - 1) / tpb);
@@ -496,7 +514,7 @@ int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int
       }
       AMOE_LAUNCH_CHECK("router_dw_token");
       const int64_t n = static_cast<int64_t>(E) * D;
-      router_dw_block_reduce_kernel<<<static_cast<unsigned>((n / 4 + 255) / 256), 256, 0, stream>>>(partials, nb, n, dw_sel);
+      router_dw_block_reduce_kernel<<<static_cast<unsigned>((n / 4 + 31) / 32), dim3(32, 8), 0, stream>>>(partials, nb, n, dw_sel);
       AMOE_LAUNCH_CHECK("router_dw_block_reduce");
       return AMOE_OK;
     }
