@@ -92,7 +92,7 @@ SIGNATURES = {
     "amoe_router_backward_w_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "amoe_router_backward_w": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, vp, C.c_int32, vp, vp, vp, vp,
                                          C.c_int64, C.c_int32, vp, vp, C.c_size_t, vp]),
-    "amoe_combine_router": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32, vp, vp, C.c_int32, vp, vp,
+    "amoe_combine_router": (C.c_int, [vp, C.c_int32, C.c_int64, vp, C.c_int64, C.c_int32, C.c_int32, vp, vp, C.c_int32, vp, vp,
                                       C.c_int32, C.c_int32, vp, C.c_int32, C.c_int64, vp]),
     "amoe_expert_offsets": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "amoe_weight_prepass_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
@@ -121,6 +121,7 @@ SIGNATURES = {
     "amoe_ep_pack": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, C.c_int32, vp, C.c_int64, vp, C.c_float, vp, vp,
                                vp, vp]),
     "amoe_invert_index": (C.c_int, [vp, C.c_int64, vp, vp]),
+    "amoe_ep_local_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
     "amoe_ep_unpack": (C.c_int, [vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, C.c_int64, vp]),
 }
 

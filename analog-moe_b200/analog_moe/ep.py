@@ -19,6 +19,7 @@ local memory.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import List, Optional, Tuple
 
@@ -135,6 +136,305 @@ class _CombineSorted(torch.autograd.Function):
         return drows, dgate, None, None
 
 
+@dataclass
+class StepPlan:
+    """Host-side view of one step's exchange, from the all-gathered count matrix C[source, destination, local expert]."""
+    send_n: List[int]            # rows this rank sends to each rank
+    recv_n: List[int]            # rows it receives from each rank
+    send_off: List[int]          # start of each destination's block in this rank's sorted slot list
+    recv_off: List[int]          # start of each source's block in this rank's receive buffer
+    off_in: List[int]            # start of this rank's block in each destination's receive buffer
+    back_off: List[int]          # start of this rank's block in each source's sorted slot list
+    p_max: int                   # largest slot count over the ranks
+    recv_counts: Tensor          # [G, El] int32 on the device
+
+    @property
+    def n_recv(self) -> int:
+        return int(sum(self.recv_n))
+
+
+def step_plan(counts: Tensor, rank: int, group=None) -> StepPlan:
+    """counts [G, El]: this rank's slots per (destination rank, local expert).  One all-gather and the step's only
+    device->host copy."""
+    G, El = counts.shape
+    gathered = torch.empty((G, G, El), dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
+    tot = gathered.sum(-1).cpu()                                  # [source, destination] row counts
+    tot_l = [[int(v) for v in row] for row in tot]
+    send_n = tot_l[rank]
+    recv_n = [tot_l[s][rank] for s in range(G)]
+    cum = lambda xs: [sum(xs[:i]) for i in range(len(xs))]
+    return StepPlan(send_n, recv_n, cum(send_n), cum(recv_n),
+                    [sum(tot_l[s][d] for s in range(rank)) for d in range(G)],
+                    [sum(tot_l[s][d] for d in range(rank)) for s in range(G)],
+                    max(sum(row) for row in tot_l), gathered[:, rank, :].contiguous())
+
+
+class PeerExchange:
+    """Rows travel by plain stores into the destination rank's receive buffer (symmetric memory over NVLink), written
+    by the same gather kernel that would otherwise fill a send buffer: no send buffer, no separate collective, no
+    self-copy.  A one-element NCCL all-reduce after the writes is the cross-rank ordering point (it is stream-ordered
+    after this rank's writes and completes only once every rank has reached it).  Buffers are sized for the worst case
+    (every slot of every rank routed to one rank) and reused every step; reuse across steps is ordered by the next
+    step's count all-gather.  One forward/backward pair may be in flight per layer."""
+
+    def __init__(self, group, device):
+        import torch.distributed._symmetric_memory as symm
+        self.symm, self.group, self.device = symm, group, device
+        self.G, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.buffers = {}
+        self.p_cap = 0
+        self.token = torch.zeros(1, device=device)
+        self.arange = None
+
+    def ensure(self, p_max: int, shapes: dict, dtype) -> None:
+        """shapes: name -> (rows, cols); every rank calls this with the same arguments (they follow from the gathered
+        counts), so the collective allocation stays in step."""
+        key = tuple(sorted(shapes.items())) + (dtype,)
+        if self.buffers.get("_key") == key:
+            return
+        self.buffers = {"_key": key}
+        for name, (rows, cols) in shapes.items():
+            t = self.symm.empty(max(rows, 1), cols, dtype=dtype, device=self.device)
+            self.buffers[name] = (self.symm.rendezvous(t, self.group), t)
+        self.p_cap = p_max
+        n = max(r for r, _ in shapes.values())
+        self.arange = torch.arange(n, dtype=torch.int32, device=self.device)
+
+    def _barrier(self) -> None:
+        dist.all_reduce(self.token, group=self.group)
+
+    def _put(self, name: str, src: Tensor, index: Tensor, blocks, src_div: int, row_scale: Optional[Tensor]) -> None:
+        hdl, buf = self.buffers[name]
+        cols, esz = buf.shape[1], buf.element_size()
+        src = src.reshape(-1, src.shape[-1])
+        assert src.shape[1] == cols and src.dtype == buf.dtype and src.stride(-1) == 1
+        for peer, first, n, dst_row in blocks:
+            if n == 0:
+                continue
+            ops._call("amoe_ep_pack", ops.ptr(src), ops.dtype_code(src), src.stride(0), cols,
+                      index.data_ptr() + 4 * first, src_div, ops.ptr(row_scale), n, None, -1.0,
+                      hdl.buffer_ptrs[peer] + dst_row * cols * esz, None, None, ops.stream_ptr())
+        self._barrier()
+
+    def dispatch(self, name: str, src: Tensor, index: Tensor, plan: StepPlan, src_div: int = 1,
+                 row_scale: Optional[Tensor] = None) -> Tensor:
+        """Rows src[index[i] // src_div] (* row_scale[index[i]]) of this rank's sorted slot list to their owners; returns
+        this rank's receive buffer [R, cols]."""
+        blocks = [(d, plan.send_off[d], plan.send_n[d], plan.off_in[d]) for d in range(self.G)]
+        self._put(name, src, index, blocks, src_div, row_scale)
+        return self.buffers[name][1][:plan.n_recv]
+
+    def give_back(self, name: str, rows: Tensor, plan: StepPlan, n_own: int) -> Tensor:
+        """Rows in receive order back to their sources' sorted slot lists; returns this rank's buffer [n_own, cols]."""
+        blocks = [(s, plan.recv_off[s], plan.recv_n[s], plan.back_off[s]) for s in range(self.G)]
+        self._put(name, rows, self.arange, blocks, 1, None)
+        return self.buffers[name][1][:n_own]
+
+
+class _ExpertParallelStep(torch.autograd.Function):
+    """The expert-parallel layer step as one autograd node: router, select/sort, one count exchange with the step's
+    only host read, rows out, both projections on the owner (the same kernels and operand caches as the single-GPU
+    step, rows addressed through `local_order`), rows back, gate-weighted sum; the backward mirrors it.  Needs ReLU,
+    no bias, no dropout (the composition in `forward_composed` covers the rest)."""
+
+    @staticmethod
+    def forward(ctx, layer, x, w_sel, keys, values, input_range):
+        cfg = layer.rpu_config
+        fwd, ir_p = cfg.forward, cfg.pre_post.input_range
+        group, G = layer.group, layer.world
+        bsz, seq, D = x.shape
+        k, El = layer.n_heads, layer.n_experts
+        T = bsz * seq
+        P = T * k
+        x2 = x.reshape(T, D)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        dev = x.device
+        precision = layer._precision(x)
+        per_channel = bool(getattr(fwd, "out_noise_per_channel", True))
+
+        def prepass(w, mod):
+            return ops.weight_prepass(
+                w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
+                noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,
+                seed=mod.seed if mod else 0, offset=mod.offset if mod else 0, step_dev=mod.step if mod else None,
+                need_fwd=True, need_bwd=True)
+
+        def noise_args():
+            if layer.training and fwd.out_noise > 0:
+                return dict(noise_std=float(fwd.out_noise), seed=layer.noise_seed, offset=layer._next_offset(),
+                            step_dev=layer.noise_step)
+            return {}
+
+        nz_up, mod_up = noise_args(), layer._weight_modifier()
+        nz_dn, mod_dn = noise_args(), layer._weight_modifier()
+        main, side = torch.cuda.current_stream(), ops.side_stream(dev)
+        side.wait_stream(main)
+        with ops.launch_on(side):
+            ops.set_tag("up")
+            pw_up = prepass(keys, mod_up)
+            ops.set_tag("down")
+            pw_dn = prepass(values, mod_dn)
+        ops.set_tag("up")
+        logits = ops.router_logits(x2, w_sel, getattr(layer, "router_bias", None))
+        r = ops.select_sort(logits, k, apply_sigmoid=True)
+        gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
+        # ---- exchange plan: counts both ways, one host read
+        counts = (r.expert_offsets[1:] - r.expert_offsets[:-1]).view(G, El).contiguous()
+        plan = step_plan(counts, layer.rank, group)
+        send_splits, recv_splits = plan.send_n, plan.recv_n
+        R = plan.n_recv
+        local_order, local_offsets = ops.ep_local_plan(plan.recv_counts, R)
+        inv = ops.invert_index(r.slot_index)
+        N, Fh = values.shape[-1], keys.shape[-1]
+        xchg = layer._peer_exchange(plan, D, N, x.dtype)
+        # ---- rows to their owners
+        if xchg is not None:
+            recv = xchg.dispatch("x", x2, r.token_index, plan)
+        else:
+            rows, _ = ops.ep_pack(x2, r.token_index)
+            recv = rows.new_empty((R, D))
+            dist.all_to_all_single(recv, rows, recv_splits, send_splits, group=group)
+            del rows
+        inp_res = fwd.inp_res
+        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
+        adc_on = fwd.out_res > 0 and fwd.out_bound > 0
+        out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
+        has_ir = input_range is not None
+        ir_all = input_range.detach().float().contiguous() if has_ir else None
+        main.wait_stream(side)
+        cached = R > 0 and layer.operand_caches and ops.operand_cache_ok(precision, D, Fh, N) and \
+            any(ctx.needs_input_grad[3:5])
+        split = precision == ops.A.PREC_SPLIT
+        xc = ops.OperandCache.empty(R, El, D, split, dev) if cached else None
+        hs = ops.OperandCache.empty(R, El, Fh, split, dev) if cached else None
+        if R > 0:
+            am_up = None if has_ir else ops.row_absmax(recv)
+            h, _ = ops.cvmm_fwd(recv, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
+                                ir=ir_all[0] if has_ir else None, ir_by_expert=True, absmax=am_up, inp_res=inp_res,
+                                out_res=out_res, out_bound=out_bound, out_relu=True, a_cache=xc, **nz_up)
+            ops.set_tag("down")
+            am_dn = None if has_ir else ops.row_absmax(h)
+            out, _ = ops.cvmm_fwd(h, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
+                                  ir=ir_all[1] if has_ir else None, ir_by_expert=True, absmax=am_dn, inp_res=inp_res,
+                                  out_res=out_res, out_bound=out_bound, a_cache=hs, **nz_dn)
+        else:
+            h = recv.new_zeros((0, Fh))
+            out = recv.new_zeros((0, N))
+        # ---- rows back, gate-weighted sum over k in slot order
+        if xchg is not None:
+            back = xchg.give_back("y", out, plan, P)
+        else:
+            back = out.new_empty((P, N))
+            dist.all_to_all_single(back, out, send_splits, recv_splits, group=group)
+        y = ops.combine(back, gate, T, k, row_index=inv)
+        simt = precision == ops.A.PREC_FP32_SIMT
+        ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv,
+                              local_order, local_offsets, ir_all,
+                              pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
+                              pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
+                              *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)))
+        ctx.meta = (x.shape, El, k, precision, ir_p, keys.dtype, values.dtype, keys.shape, values.shape,
+                    input_range.dtype if has_ir else None, send_splits, recv_splits, group, plan, xchg)
+        return y.view(bsz, seq, N)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, local_order, local_offsets, ir_all,
+         w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo) = ctx.saved_tensors
+        (x_shape, El, k, precision, ir_p, keys_dtype, values_dtype, kshape, vshape, ir_dtype, send_splits, recv_splits,
+         group, plan, xchg) = ctx.meta
+        T, D = x2.shape
+        P, R = T * k, recv.shape[0]
+        Fh, N = vshape[1], vshape[2]
+        need_x, need_sel, need_keys, need_values, need_ir = (ctx.needs_input_grad[i] for i in (1, 2, 3, 4, 5))
+        has_ir = ir_all is not None
+        need_ir = need_ir and has_ir
+        cached = xc_hi is not None
+        dev = x2.device
+        g = gy.reshape(T, N)
+        if g.stride(-1) != 1:
+            g = g.contiguous()
+        pw_up = ops.PreparedWeights(El, kshape[1], kshape[2], up_cs, w=w_up, bwd_hi=up_hi, bwd_lo=up_lo)
+        pw_dn = ops.PreparedWeights(El, vshape[1], vshape[2], dn_cs, w=w_dn, bwd_hi=dn_hi, bwd_lo=dn_lo)
+        decay = float(getattr(ir_p, "decay", 0.0) or 0.0) if has_ir else 0.0
+        min_pct = float(getattr(ir_p, "input_min_percentage", 0.95))
+        relative = bool(getattr(ir_p, "gradient_relative", True))
+        gscale = float(getattr(ir_p, "gradient_scale", 1.0)) if relative else 1.0
+        keeps = torch.zeros(2, dtype=torch.int64, device=dev) if (has_ir and decay > 0) else None
+        ir_up, ir_dn = (ir_all[0], ir_all[1]) if has_ir else (None, None)
+        gate_flat = gate.reshape(-1)
+        # ---- gate gradient at the source, gate * gy rows to the owners
+        ops.set_tag("down")
+        dgate = ops.row_dot(back, g, k, row_index=inv)
+        if xchg is not None:
+            g_recv = xchg.dispatch("g", g, slot_index, plan, src_div=k, row_scale=gate_flat)
+        else:
+            drows, _ = ops.ep_pack(g, slot_index, src_div=k, row_scale=gate_flat)
+            g_recv = drows.new_empty((R, N))
+            dist.all_to_all_single(g_recv, drows, recv_splits, send_splits, group=group)
+            del drows
+        grad_keys = grad_values = None
+        if R > 0:
+            split = xc_lo is not None
+            gc = ops.OperandCache.empty(R, El, N, split, dev) if cached and need_values else None
+            dhc = ops.OperandCache.empty(R, El, Fh, split, dev) if cached and need_keys else None
+            if need_values and not cached:
+                grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
+                                          ir_by_expert=True).to(values_dtype)
+            dh, irs_dn = ops.cvmm_dx(g_recv, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
+                                     x_ref=h, x_ref_row=local_order, ir=ir_dn, ir_by_expert=True, want_ir_grad=has_ir,
+                                     relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
+                                     out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc)
+            if need_values and cached:
+                grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, local_offsets, El, precision,
+                                                 P=R).to(values_dtype)
+            ops.set_tag("up")
+            if need_keys and cached:
+                grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, local_offsets, El, precision,
+                                               P=R).to(keys_dtype)
+            elif need_keys:
+                grad_keys = ops.cvmm_dw(recv, local_order, dh, local_order, local_offsets, El, precision, P=R, ir=ir_up,
+                                        ir_by_expert=True).to(keys_dtype)
+            dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
+                                      x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
+                                      ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
+                                      keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype)
+        else:
+            dxr = recv.new_zeros((0, D))
+            irs_up = irs_dn = None
+            if need_keys:
+                grad_keys = torch.zeros(kshape, dtype=keys_dtype, device=dev)
+            if need_values:
+                grad_values = torch.zeros(vshape, dtype=values_dtype, device=dev)
+        # ---- input-gradient rows back to the source; sum over k plus the router's term
+        ops.set_tag("up")
+        grad_x = None
+        if need_x:
+            if xchg is not None:
+                dback = xchg.give_back("dx", dxr, plan, P)
+            else:
+                dback = dxr.new_empty((P, D))
+                dist.all_to_all_single(dback, dxr, send_splits, recv_splits, group=group)
+            grad_x = ops.combine_router(dback, T, k, dgate, gate, raw_sel, w_sel, row_index=inv).view(x_shape)
+        grad_sel = None
+        if need_sel:
+            grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
+                                             raw_sel=raw_sel).to(w_sel.dtype)
+        grad_ir = None
+        if need_ir:
+            if R > 0:
+                grad_ir = torch.stack([
+                    ops.ir_grad_reduce(irs_up, local_offsets, ir_up, El, decay, min_pct,
+                                       keeps[:1] if keeps is not None else None, float(R) * D),
+                    ops.ir_grad_reduce(irs_dn, local_offsets, ir_dn, El, decay, min_pct,
+                                       keeps[1:] if keeps is not None else None, float(R) * Fh)]).to(ir_dtype)
+            else:
+                grad_ir = torch.zeros(2, El, dtype=ir_dtype, device=dev)
+        return (None, grad_x, grad_sel, grad_keys, grad_values, grad_ir)
+
+
 class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
     """`n_experts` is the global number; this rank holds experts [rank*E/G, (rank+1)*E/G)."""
 
@@ -144,6 +444,8 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         self.rank = dist.get_rank(group)
         assert n_experts % self.world == 0
         self.n_experts_global = n_experts
+        self.peer_exchange = os.environ.get("AMOE_EP_NCCL") is None    # rows by stores into peer memory (else NCCL)
+        self._xchg = None
         if kwargs.get("bias"):
             raise NotImplementedError("expert-parallel layer: bias is not built")
         d_model = kwargs["d_model"]
@@ -153,6 +455,25 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         self.expert_sel = torch.nn.Linear(d_model, n_experts, bias=False)
         with torch.no_grad():
             self.expert_sel.weight.copy_(torch.randn(n_experts, d_model, generator=g) * d_model ** -0.5)
+
+    def _peer_exchange(self, plan: "StepPlan", D: int, N: int, dtype) -> Optional["PeerExchange"]:
+        """The symmetric-memory exchange, (re)allocated when a step needs more rows than the buffers hold; None when
+        peer access is off (`peer_exchange=False`, or symmetric memory could not be set up: NCCL all-to-all then)."""
+        if not self.peer_exchange:
+            return None
+        try:
+            if self._xchg is None:
+                self._xchg = PeerExchange(self.group, self.keys.device)
+            x = self._xchg
+            p_cap = max(plan.p_max, x.p_cap)
+            x.ensure(p_cap, {"x": (self.world * p_cap, D), "g": (self.world * p_cap, N), "y": (p_cap, N),
+                             "dx": (p_cap, D)}, dtype)
+            return x
+        except Exception as exc:       # no symmetric memory on this system: say so once, use NCCL from now on
+            import warnings
+            warnings.warn(f"expert-parallel peer exchange unavailable ({exc!r}); using NCCL all-to-all")
+            self.peer_exchange = False
+            return None
 
     def load_global_weights(self, keys: Tensor, values: Tensor, router: Tensor, input_range: Optional[Tensor] = None):
         El = self.n_experts
@@ -165,6 +486,21 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
                 self.input_range.copy_(input_range[:, sl])
 
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
+        from .layers import _is_relu
+        ir_p = self.rpu_config.pre_post.input_range
+        single_node = self.fused and _is_relu(self.activation) and not (self.dropout > 0 and self.training) and \
+            not (self.input_range is not None and self.training and ir_p.init_from_data > 0 and
+                 float(self.input_range_update_idx) < ir_p.init_from_data)
+        if not single_node:
+            return self.forward_composed(inp)
+        self._noise_calls = 0
+        y = _ExpertParallelStep.apply(self, inp, self.expert_sel.weight, self.keys, self.values, self.input_range)
+        if self.training:
+            self.noise_step += 1
+        return y, self._aux_zero
+
+    def forward_composed(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
+        """The same step composed from autograd functions around CVMM.apply (any activation, dropout)."""
         self._noise_calls = 0
         bsz, seq, D = inp.shape
         T, k = bsz * seq, self.n_heads

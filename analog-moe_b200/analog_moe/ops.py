@@ -167,13 +167,13 @@ def router_backward_w(x2: torch.Tensor, dgate: torch.Tensor, gate: torch.Tensor,
 
 
 def combine_router(res: torch.Tensor, T: int, k: int, dgate: torch.Tensor, gate: torch.Tensor, raw_sel: torch.Tensor,
-                   w_sel: torch.Tensor, apply_sigmoid: bool = True) -> torch.Tensor:
+                   w_sel: torch.Tensor, apply_sigmoid: bool = True, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     """sum over k of the rows [T*k,N] plus the router's input-gradient term, [T,N] in the rows' dtype."""
     res = _rows(res)
     w = w_sel.contiguous()
     N = res.shape[1]
     y = torch.empty(T, N, dtype=res.dtype, device=res.device)
-    _call("amoe_combine_router", ptr(res), dtype_code(res), res.stride(0), T, k, N, ptr(dgate), ptr(gate),
+    _call("amoe_combine_router", ptr(res), dtype_code(res), res.stride(0), ptr(row_index), T, k, N, ptr(dgate), ptr(gate),
           int(apply_sigmoid), ptr(raw_sel), ptr(w), dtype_code(w), w.shape[0], ptr(y), dtype_code(y), y.stride(0),
           stream_ptr())
     return y
@@ -540,6 +540,16 @@ def ep_pack(x: torch.Tensor, src_row: torch.Tensor, ir: Optional[torch.Tensor] =
     _call("amoe_ep_pack", ptr(x2), dtype_code(x2), x2.stride(0), K, ptr(src_row), src_div, ptr(row_scale), P, None, -1.0,
           ptr(rows), None, None, stream_ptr())
     return rows, None
+
+
+def ep_local_plan(recv_counts: torch.Tensor, R: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """recv_counts [G,El] int32 on the device -> (local_order [R], local_offsets [El+1])."""
+    G, El = recv_counts.shape
+    dev = recv_counts.device
+    order = torch.empty(max(R, 1), dtype=torch.int32, device=dev)[:R]
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    _call("amoe_ep_local_plan", ptr(recv_counts), G, El, R, ptr(order), ptr(offsets), stream_ptr())
+    return order, offsets
 
 
 def invert_index(idx: torch.Tensor) -> torch.Tensor:

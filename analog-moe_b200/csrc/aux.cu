@@ -345,6 +345,38 @@ inline unsigned blocks_for(int64_t threads, int per_block) {
   return static_cast<unsigned>((threads + per_block - 1) / per_block);
 }
 
+// The receive buffer of an expert-parallel rank holds, for source g = 0..G-1, that source's rows for local experts
+// 0..El-1 in order: block (g, e) has recv_counts[g*El + e] rows.  Expert-sorted order is: for e, for g, block (g, e).
+// local_order[sorted position] = row of the receive buffer; local_offsets[e] = first sorted position of expert e.
+constexpr int kEpMaxBlocks = 4096;
+__global__ void __launch_bounds__(256) ep_local_plan_kernel(const int32_t* __restrict__ recv_counts, int G, int El, int R,
+                                                            int32_t* __restrict__ local_order,
+                                                            int32_t* __restrict__ local_offsets) {
+  __shared__ int s_recv_start[kEpMaxBlocks + 1];    // by receive order  (g major)
+  __shared__ int s_sorted_start[kEpMaxBlocks];      // by receive order, value = start in sorted order
+  const int nb = G * El;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int b = 0; b < nb; ++b) { s_recv_start[b] = acc; acc += recv_counts[b]; }
+    s_recv_start[nb] = acc;
+    acc = 0;
+    for (int e = 0; e < El; ++e) {
+      if (blockIdx.x == 0) local_offsets[e] = acc;
+      for (int g = 0; g < G; ++g) { s_sorted_start[g * El + e] = acc; acc += recv_counts[g * El + e]; }
+    }
+    if (blockIdx.x == 0) local_offsets[El] = acc;
+  }
+  __syncthreads();
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < R; r += gridDim.x * blockDim.x) {
+    int lo = 0, hi = nb;               // last block whose start is <= r (empty blocks share a start: take the last)
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_recv_start[mid] <= r) lo = mid; else hi = mid;
+    }
+    local_order[s_sorted_start[lo] + (r - s_recv_start[lo])] = r;
+  }
+}
+
 }  // namespace
 }  // namespace amoe
 
@@ -562,6 +594,18 @@ int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t
   }
   std_final_kernel<<<eb, 128, 0, stream>>>(sq, expert_offsets, E, K, std_out);
   AMOE_LAUNCH_CHECK("std_final");
+  return AMOE_OK;
+}
+
+int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_t R, int32_t* local_order,
+                       int32_t* local_offsets, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(recv_counts && local_order && local_offsets, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(G > 0 && El > 0 && R >= 0 && G * El <= kEpMaxBlocks && R < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
+  const unsigned blocks = R > 0 ? blocks_for(R, 256) : 1u;
+  ep_local_plan_kernel<<<blocks > 1024u ? 1024u : blocks, 256, 0, stream>>>(recv_counts, G, El, static_cast<int>(R), local_order,
+                                                                           local_offsets);
+  AMOE_LAUNCH_CHECK("ep_local_plan");
   return AMOE_OK;
 }
 

@@ -366,7 +366,8 @@ __global__ void __launch_bounds__(256) router_dw_block_reduce_kernel(const float
 // ------------------------------------------------------------------------------------ combine + router term
 // y[t,:] = sum_j res[t*k+j,:]  +  sum_j c[t,j] * w_sel[raw_sel[t,j],:]      (j ascending, rows first)
 template <typename TR, typename TW, typename TY>
-__global__ void combine_router_kernel(const TR* __restrict__ res, int64_t res_stride, int64_t T, int k, int N,
+__global__ void combine_router_kernel(const TR* __restrict__ res, int64_t res_stride, const int32_t* __restrict__ row_index,
+                                      int64_t T, int k, int N,
                                       const float* __restrict__ dgate, const float* __restrict__ gate,
                                       int apply_sigmoid, const int32_t* __restrict__ raw_sel,
                                       const TW* __restrict__ w_sel, int E, TY* __restrict__ y, int64_t y_stride, int vec) {
@@ -379,7 +380,8 @@ __global__ void combine_router_kernel(const TR* __restrict__ res, int64_t res_st
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
   for (int j = 0; j < k; ++j) {
-    const float4 v = ldg4<TR>(res + (t * k + j) * res_stride + n0, vec != 0, valid);
+    const int64_t rr = row_index ? row_index[t * k + j] : t * k + j;
+    const float4 v = ldg4<TR>(res + rr * res_stride + n0, vec != 0, valid);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
 #pragma unroll 4
@@ -537,7 +539,8 @@ int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int
   return AMOE_OK;
 }
 
-int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, int64_t T, int32_t k, int32_t N,
+int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, int64_t T,
+                        int32_t k, int32_t N,
                         const float* dgate, const float* gate, int32_t apply_sigmoid, const int32_t* raw_sel,
                         const void* w_sel, int32_t w_dtype, int32_t E, void* y, int32_t y_dtype, int64_t y_stride,
                         amoe_stream_t stream_) {
@@ -551,7 +554,7 @@ int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, 
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
 #define AMOE_CR(TR, TW)                                                                                               \
-  combine_router_kernel<TR, TW, TR><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TR*>(res), res_stride, T, k, N, dgate, \
+  combine_router_kernel<TR, TW, TR><<<blocks, 256, 0, stream>>>(reinterpret_cast<const TR*>(res), res_stride, row_index, T, k, N, dgate, \
                                                                 gate, apply_sigmoid, raw_sel, reinterpret_cast<const TW*>(w_sel), \
                                                                 E, reinterpret_cast<TR*>(y), y_stride, vec)
   if (res_dtype == AMOE_F32 && w_dtype == AMOE_F32) AMOE_CR(float, float);

@@ -91,7 +91,8 @@ int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw
  * amoe_router_backward_w: dw_sel[e,:] = sum over the slots i of expert e of c_i * x[token_index[i],:], with
  *   c = dgate*(1-g)*g (apply_sigmoid) or dgate, dgate/gate indexed by flat slot (slot_index[i]).  Fixed summation order.
  *   raw_sel [T,k] (optional) enables a token-major variant that reads x once when the [E,D] gradient fits in shared memory.
- * amoe_combine_router: y[t,:] = sum_j res[t*k+j,:] + sum_j c[t,j] * w_sel[raw_sel[t,j],:]: the sum over k of the
+ * amoe_combine_router: y[t,:] = sum_j res[row(t*k+j),:] + sum_j c[t,j] * w_sel[raw_sel[t,j],:] (row() as in
+ *   amoe_combine): the sum over k of the
  *   up-projection's input gradient (cvmm.py:890-891) and the router's own input gradient in one pass.
  * ---------------------------------------------------------------------------------------- */
 int amoe_router_logits(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const void* w,
@@ -102,7 +103,8 @@ int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int
                            const float* gate, int32_t apply_sigmoid, const int32_t* token_index,
                            const int32_t* slot_index, const int32_t* expert_offsets, const int32_t* raw_sel, int64_t P,
                            int32_t E, float* dw_sel, void* workspace, size_t workspace_bytes, amoe_stream_t stream);
-int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, int64_t T, int32_t k, int32_t N,
+int amoe_combine_router(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, int64_t T,
+                        int32_t k, int32_t N,
                         const float* dgate, const float* gate, int32_t apply_sigmoid, const int32_t* raw_sel,
                         const void* w_sel, int32_t w_dtype, int32_t E, void* y, int32_t y_dtype, int64_t y_stride,
                         amoe_stream_t stream);
@@ -349,6 +351,11 @@ int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t
 int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* src_row, int32_t src_div,
                  const float* row_scale, int64_t P, const float* ir, float inp_res, void* send_rows,
                  int8_t* send_codes, float* send_scale, amoe_stream_t stream);
+/* Regrouping of an expert-parallel receive buffer by local expert.  The buffer holds, for source rank g = 0..G-1, that
+ * source's rows for local experts 0..El-1 in order (recv_counts [G,El], R rows in total).  local_order [R]: row of the
+ * buffer for each expert-sorted position (for e, for g); local_offsets [El+1].  G*El <= 4096. */
+int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_t R, int32_t* local_order,
+                       int32_t* local_offsets, amoe_stream_t stream);
 /* inv[idx[i]] = i for a permutation idx of 0..P-1. */
 int amoe_invert_index(const int32_t* idx, int64_t P, int32_t* inv, amoe_stream_t stream);
 int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P,
