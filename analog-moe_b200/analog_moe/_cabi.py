@@ -122,6 +122,12 @@ SIGNATURES = {
                                vp, vp]),
     "amoe_invert_index": (C.c_int, [vp, C.c_int64, vp, vp]),
     "amoe_ep_local_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
+    "amoe_ep_plan_ints": (C.c_int64, [C.c_int32, C.c_int32]),
+    "amoe_ep_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
+    "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
+    "amoe_ep_put": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp,
+                              vp, C.c_int32, C.c_int64, vp]),
+    "amoe_ep_put_back": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int32, C.c_int64, C.c_int64, vp]),
     "amoe_ep_unpack": (C.c_int, [vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, C.c_int64, vp]),
 }
 

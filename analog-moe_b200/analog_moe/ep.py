@@ -171,65 +171,51 @@ def step_plan(counts: Tensor, rank: int, group=None) -> StepPlan:
 
 
 class PeerExchange:
-    """Rows travel by plain stores into the destination rank's receive buffer (symmetric memory over NVLink), written
-    by the same gather kernel that would otherwise fill a send buffer: no send buffer, no separate collective, no
-    self-copy.  A one-element NCCL all-reduce after the writes is the cross-rank ordering point (it is stream-ordered
-    after this rank's writes and completes only once every rank has reached it).  Buffers are sized for the worst case
+    """Rows travel by plain stores into the destination rank's receive buffer (symmetric memory over NVLink), written by
+    the gather kernel itself: no send buffer, no separate collective, no self-copy.  Where each row goes is computed on
+    the device from the all-gathered counts (`amoe_ep_plan`), so the step needs no value on the host and can be captured
+    in a CUDA graph.  A one-element NCCL all-reduce after the writes is the cross-rank ordering point (stream-ordered
+    after this rank's writes, complete only once every rank has reached it).  Buffers are sized for the worst case
     (every slot of every rank routed to one rank) and reused every step; reuse across steps is ordered by the next
     step's count all-gather.  One forward/backward pair may be in flight per layer."""
 
-    def __init__(self, group, device):
+    def __init__(self, group, device, p_cap: int, D: int, N: int, dtype):
         import torch.distributed._symmetric_memory as symm
-        self.symm, self.group, self.device = symm, group, device
+        self.group, self.device = group, device
         self.G, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.p_cap, self.cap = p_cap, self.G * p_cap
+        self.key = (p_cap, D, N, dtype)
         self.buffers = {}
-        self.p_cap = 0
+        for name, (rows, cols) in {"x": (self.cap, D), "g": (self.cap, N), "y": (p_cap, N), "dx": (p_cap, D)}.items():
+            t = symm.empty(rows, cols, dtype=dtype, device=device)
+            hdl = symm.rendezvous(t, group)
+            self.buffers[name] = (hdl, t, int(hdl.buffer_ptrs_dev))
         self.token = torch.zeros(1, device=device)
-        self.arange = None
 
-    def ensure(self, p_max: int, shapes: dict, dtype) -> None:
-        """shapes: name -> (rows, cols); every rank calls this with the same arguments (they follow from the gathered
-        counts), so the collective allocation stays in step."""
-        key = tuple(sorted(shapes.items())) + (dtype,)
-        if self.buffers.get("_key") == key:
-            return
-        self.buffers = {"_key": key}
-        for name, (rows, cols) in shapes.items():
-            t = self.symm.empty(max(rows, 1), cols, dtype=dtype, device=self.device)
-            self.buffers[name] = (self.symm.rendezvous(t, self.group), t)
-        self.p_cap = p_max
-        n = max(r for r, _ in shapes.values())
-        self.arange = torch.arange(n, dtype=torch.int32, device=self.device)
-
-    def _barrier(self) -> None:
+    def barrier(self) -> None:
         dist.all_reduce(self.token, group=self.group)
 
-    def _put(self, name: str, src: Tensor, index: Tensor, blocks, src_div: int, row_scale: Optional[Tensor]) -> None:
-        hdl, buf = self.buffers[name]
-        cols, esz = buf.shape[1], buf.element_size()
+    def put(self, name: str, src: Tensor, index: Tensor, sel_sorted: Tensor, El: int, plan: Tensor, src_div: int = 1,
+            row_scale: Optional[Tensor] = None) -> Tensor:
+        """Row src[index[i] // src_div] (* row_scale[index[i]]) of every sorted position i to the rank that owns expert
+        sel_sorted[i]; returns this rank's whole receive buffer [cap, cols] (its first R rows are valid)."""
+        hdl, buf, ptrs = self.buffers[name]
         src = src.reshape(-1, src.shape[-1])
-        assert src.shape[1] == cols and src.dtype == buf.dtype and src.stride(-1) == 1
-        for peer, first, n, dst_row in blocks:
-            if n == 0:
-                continue
-            ops._call("amoe_ep_pack", ops.ptr(src), ops.dtype_code(src), src.stride(0), cols,
-                      index.data_ptr() + 4 * first, src_div, ops.ptr(row_scale), n, None, -1.0,
-                      hdl.buffer_ptrs[peer] + dst_row * cols * esz, None, None, ops.stream_ptr())
-        self._barrier()
+        assert src.shape[1] == buf.shape[1] and src.dtype == buf.dtype and src.stride(-1) == 1
+        ops._call("amoe_ep_put", ops.ptr(src), ops.dtype_code(src), src.stride(0), src.shape[1], src.shape[0], ops.ptr(index),
+                  src_div, ops.ptr(row_scale), index.numel(), ops.ptr(sel_sorted), El, ops.ptr(plan), ptrs, self.G,
+                  buf.shape[0], ops.stream_ptr())
+        self.barrier()
+        return buf
 
-    def dispatch(self, name: str, src: Tensor, index: Tensor, plan: StepPlan, src_div: int = 1,
-                 row_scale: Optional[Tensor] = None) -> Tensor:
-        """Rows src[index[i] // src_div] (* row_scale[index[i]]) of this rank's sorted slot list to their owners; returns
-        this rank's receive buffer [R, cols]."""
-        blocks = [(d, plan.send_off[d], plan.send_n[d], plan.off_in[d]) for d in range(self.G)]
-        self._put(name, src, index, blocks, src_div, row_scale)
-        return self.buffers[name][1][:plan.n_recv]
-
-    def give_back(self, name: str, rows: Tensor, plan: StepPlan, n_own: int) -> Tensor:
-        """Rows in receive order back to their sources' sorted slot lists; returns this rank's buffer [n_own, cols]."""
-        blocks = [(s, plan.recv_off[s], plan.recv_n[s], plan.back_off[s]) for s in range(self.G)]
-        self._put(name, rows, self.arange, blocks, 1, None)
-        return self.buffers[name][1][:n_own]
+    def put_back(self, name: str, rows: Tensor, plan: Tensor, n_own: int) -> Tensor:
+        """The first R rows of `rows` (receive order) back to their sources; returns this rank's buffer [n_own, cols]."""
+        hdl, buf, ptrs = self.buffers[name]
+        assert rows.shape[1] == buf.shape[1] and rows.dtype == buf.dtype and rows.stride(-1) == 1
+        ops._call("amoe_ep_put_back", ops.ptr(rows), ops.dtype_code(rows), rows.stride(0), rows.shape[1], ops.ptr(plan), ptrs,
+                  self.G, rows.shape[0], buf.shape[0], ops.stream_ptr())
+        self.barrier()
+        return buf[:n_own]
 
 
 class _ExpertParallelStep(torch.autograd.Function):
@@ -282,17 +268,24 @@ class _ExpertParallelStep(torch.autograd.Function):
         gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
         # ---- exchange plan: counts both ways, one host read
         counts = (r.expert_offsets[1:] - r.expert_offsets[:-1]).view(G, El).contiguous()
-        plan = step_plan(counts, layer.rank, group)
-        send_splits, recv_splits = plan.send_n, plan.recv_n
-        R = plan.n_recv
-        local_order, local_offsets = ops.ep_local_plan(plan.recv_counts, R)
-        inv = ops.invert_index(r.slot_index)
         N, Fh = values.shape[-1], keys.shape[-1]
-        xchg = layer._peer_exchange(plan, D, N, x.dtype)
+        inv = ops.invert_index(r.slot_index)
+        xchg = layer._peer_exchange(P, D, N, x.dtype)
+        plan = send_splits = recv_splits = None
         # ---- rows to their owners
         if xchg is not None:
-            recv = xchg.dispatch("x", x2, r.token_index, plan)
+            # everything on the device: all-gather of the counts -> plan -> stores into the owners' buffers
+            gathered = torch.empty((G, G, El), dtype=counts.dtype, device=dev)
+            dist.all_gather_into_tensor(gathered, counts, group=group)
+            plan = ops.ep_plan(gathered, layer.rank)
+            R = xchg.cap                       # rows allocated; the kernels find the real count in the plan / offsets
+            local_order, local_offsets = ops.ep_local_plan_dev(plan, G, El, R)
+            recv = xchg.put("x", x2, r.token_index, r.sel, El, plan)
         else:
+            hplan = step_plan(counts, layer.rank, group)
+            send_splits, recv_splits = hplan.send_n, hplan.recv_n
+            R = hplan.n_recv
+            local_order, local_offsets = ops.ep_local_plan(hplan.recv_counts, R)
             rows, _ = ops.ep_pack(x2, r.token_index)
             recv = rows.new_empty((R, D))
             dist.all_to_all_single(recv, rows, recv_splits, send_splits, group=group)
@@ -324,13 +317,13 @@ class _ExpertParallelStep(torch.autograd.Function):
             out = recv.new_zeros((0, N))
         # ---- rows back, gate-weighted sum over k in slot order
         if xchg is not None:
-            back = xchg.give_back("y", out, plan, P)
+            back = xchg.put_back("y", out, plan, P)
         else:
             back = out.new_empty((P, N))
             dist.all_to_all_single(back, out, send_splits, recv_splits, group=group)
         y = ops.combine(back, gate, T, k, row_index=inv)
         simt = precision == ops.A.PREC_FP32_SIMT
-        ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv,
+        ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv, r.sel,
                               local_order, local_offsets, ir_all,
                               pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
@@ -341,12 +334,15 @@ class _ExpertParallelStep(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, local_order, local_offsets, ir_all,
+        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets, ir_all,
          w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo) = ctx.saved_tensors
         (x_shape, El, k, precision, ir_p, keys_dtype, values_dtype, kshape, vshape, ir_dtype, send_splits, recv_splits,
          group, plan, xchg) = ctx.meta
         T, D = x2.shape
         P, R = T * k, recv.shape[0]
+        # rows routed to this rank: known exactly on the NCCL path; with the device-driven exchange the buffers have
+        # worst-case size and the balanced share P stands in (used only by the decay term's kept-fraction threshold)
+        n_rows = P if xchg is not None else R
         Fh, N = vshape[1], vshape[2]
         need_x, need_sel, need_keys, need_values, need_ir = (ctx.needs_input_grad[i] for i in (1, 2, 3, 4, 5))
         has_ir = ir_all is not None
@@ -369,7 +365,7 @@ class _ExpertParallelStep(torch.autograd.Function):
         ops.set_tag("down")
         dgate = ops.row_dot(back, g, k, row_index=inv)
         if xchg is not None:
-            g_recv = xchg.dispatch("g", g, slot_index, plan, src_div=k, row_scale=gate_flat)
+            g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat)
         else:
             drows, _ = ops.ep_pack(g, slot_index, src_div=k, row_scale=gate_flat)
             g_recv = drows.new_empty((R, N))
@@ -413,7 +409,7 @@ class _ExpertParallelStep(torch.autograd.Function):
         grad_x = None
         if need_x:
             if xchg is not None:
-                dback = xchg.give_back("dx", dxr, plan, P)
+                dback = xchg.put_back("dx", dxr, plan, P)
             else:
                 dback = dxr.new_empty((P, D))
                 dist.all_to_all_single(dback, dxr, send_splits, recv_splits, group=group)
@@ -427,9 +423,9 @@ class _ExpertParallelStep(torch.autograd.Function):
             if R > 0:
                 grad_ir = torch.stack([
                     ops.ir_grad_reduce(irs_up, local_offsets, ir_up, El, decay, min_pct,
-                                       keeps[:1] if keeps is not None else None, float(R) * D),
+                                       keeps[:1] if keeps is not None else None, float(n_rows) * D),
                     ops.ir_grad_reduce(irs_dn, local_offsets, ir_dn, El, decay, min_pct,
-                                       keeps[1:] if keeps is not None else None, float(R) * Fh)]).to(ir_dtype)
+                                       keeps[1:] if keeps is not None else None, float(n_rows) * Fh)]).to(ir_dtype)
             else:
                 grad_ir = torch.zeros(2, El, dtype=ir_dtype, device=dev)
         return (None, grad_x, grad_sel, grad_keys, grad_values, grad_ir)
@@ -446,6 +442,7 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         self.n_experts_global = n_experts
         self.peer_exchange = os.environ.get("AMOE_EP_NCCL") is None    # rows by stores into peer memory (else NCCL)
         self._xchg = None
+        self.max_slots = int(kwargs.pop("max_slots", 0))
         if kwargs.get("bias"):
             raise NotImplementedError("expert-parallel layer: bias is not built")
         d_model = kwargs["d_model"]
@@ -456,19 +453,25 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         with torch.no_grad():
             self.expert_sel.weight.copy_(torch.randn(n_experts, d_model, generator=g) * d_model ** -0.5)
 
-    def _peer_exchange(self, plan: "StepPlan", D: int, N: int, dtype) -> Optional["PeerExchange"]:
-        """The symmetric-memory exchange, (re)allocated when a step needs more rows than the buffers hold; None when
-        peer access is off (`peer_exchange=False`, or symmetric memory could not be set up: NCCL all-to-all then)."""
+    def _peer_exchange(self, P: int, D: int, N: int, dtype) -> Optional["PeerExchange"]:
+        """The symmetric-memory exchange; None when peer access is off (`peer_exchange=False`, or symmetric memory could
+        not be set up: NCCL all-to-all with one host read then).  The buffers are sized at the first call from the
+        largest slot count over the ranks (one all-reduce and host read, once) or from `max_slots`."""
         if not self.peer_exchange:
             return None
-        try:
-            if self._xchg is None:
-                self._xchg = PeerExchange(self.group, self.keys.device)
-            x = self._xchg
-            p_cap = max(plan.p_max, x.p_cap)
-            x.ensure(p_cap, {"x": (self.world * p_cap, D), "g": (self.world * p_cap, N), "y": (p_cap, N),
-                             "dx": (p_cap, D)}, dtype)
+        x = self._xchg
+        if x is not None and x.key[1:] == (D, N, dtype) and P <= x.p_cap:
             return x
+        if x is not None and P > x.p_cap:
+            raise RuntimeError(f"expert-parallel layer: {P} slots on this rank exceed the exchange buffers ({x.p_cap}); "
+                               "construct the layer with max_slots >= tokens*k of the largest batch")
+        try:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("first call under stream capture")
+            m = torch.tensor([max(P, self.max_slots)], dtype=torch.int64, device=self.keys.device)
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
+            self._xchg = PeerExchange(self.group, self.keys.device, int(m.item()), D, N, dtype)
+            return self._xchg
         except Exception as exc:       # no symmetric memory on this system: say so once, use NCCL from now on
             import warnings
             warnings.warn(f"expert-parallel peer exchange unavailable ({exc!r}); using NCCL all-to-all")

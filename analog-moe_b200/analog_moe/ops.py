@@ -552,6 +552,21 @@ def ep_local_plan(recv_counts: torch.Tensor, R: int) -> Tuple[torch.Tensor, torc
     return order, offsets
 
 
+def ep_plan(gathered: torch.Tensor, rank: int) -> torch.Tensor:
+    """gathered [G,G,El] int32 (source, destination, local expert) -> this rank's plan (int32 device array)."""
+    G, _, El = gathered.shape
+    plan = torch.empty(int(lib.amoe_ep_plan_ints(G, El)), dtype=torch.int32, device=gathered.device)
+    _call("amoe_ep_plan", ptr(gathered), rank, G, El, ptr(plan), stream_ptr())
+    return plan
+
+
+def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    order = torch.empty(cap, dtype=torch.int32, device=plan.device)
+    offsets = torch.empty(El + 1, dtype=torch.int32, device=plan.device)
+    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), stream_ptr())
+    return order, offsets
+
+
 def invert_index(idx: torch.Tensor) -> torch.Tensor:
     inv = torch.empty_like(idx)
     _call("amoe_invert_index", ptr(idx), idx.numel(), ptr(inv), stream_ptr())

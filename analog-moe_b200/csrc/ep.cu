@@ -1,0 +1,238 @@
+// Device-driven expert-parallel exchange: the plan of one step (who sends how many rows where) is computed on the
+// device from the all-gathered count matrix, and rows are written straight into the destination rank's buffer by
+// plain stores over NVLink (peer pointers of a symmetric allocation).  Nothing here needs a value on the host, so
+// the whole step can be captured in a CUDA graph.  No kernel waits on another rank: ordering between ranks comes
+// from the collectives the caller places between these launches.
+#include "common.cuh"
+
+namespace amoe {
+namespace {
+
+constexpr int kEpMaxRanks = 64;
+constexpr int kEpMaxBlocksDev = 4096;
+
+// plan layout (int32): [0] R = rows this rank receives, [1] rows this rank sends (= its slot count),
+// then four arrays of G: send_off (start of destination d's block in this rank's sorted slot list), off_in (start of
+// this rank's block in destination d's receive buffer), recv_off (start of source s's block in this rank's receive
+// buffer), back_off (start of this rank's block in source s's sorted slot list); then recv_counts [G, El].
+__host__ __device__ inline int plan_ints(int G, int El) { return 2 + 4 * G + G * El; }
+
+__global__ void ep_plan_kernel(const int32_t* __restrict__ gathered, int me, int G, int El, int32_t* __restrict__ plan) {
+  __shared__ int tot[kEpMaxRanks * kEpMaxRanks];
+  for (int i = threadIdx.x; i < G * G; i += blockDim.x) {
+    int acc = 0;
+    for (int e = 0; e < El; ++e) acc += gathered[i * El + e];
+    tot[i] = acc;
+  }
+  for (int i = threadIdx.x; i < G * El; i += blockDim.x) {
+    const int g = i / El, e = i - g * El;
+    plan[2 + 4 * G + i] = gathered[(g * G + me) * El + e];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int32_t* send_off = plan + 2;
+    int32_t* off_in = send_off + G;
+    int32_t* recv_off = off_in + G;
+    int32_t* back_off = recv_off + G;
+    int acc = 0;
+    for (int d = 0; d < G; ++d) { send_off[d] = acc; acc += tot[me * G + d]; }
+    plan[1] = acc;
+    acc = 0;
+    for (int s = 0; s < G; ++s) { recv_off[s] = acc; acc += tot[s * G + me]; }
+    plan[0] = acc;
+    for (int d = 0; d < G; ++d) {
+      int a = 0;
+      for (int s = 0; s < me; ++s) a += tot[s * G + d];
+      off_in[d] = a;
+    }
+    for (int s = 0; s < G; ++s) {
+      int a = 0;
+      for (int d = 0; d < me; ++d) a += tot[s * G + d];
+      back_off[s] = a;
+    }
+  }
+}
+
+// local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.
+__global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* __restrict__ plan, int G, int El, int cap,
+                                                                int32_t* __restrict__ local_order,
+                                                                int32_t* __restrict__ local_offsets) {
+  __shared__ int s_recv_start[kEpMaxBlocksDev + 1];
+  __shared__ int s_sorted_start[kEpMaxBlocksDev];
+  const int32_t* recv_counts = plan + 2 + 4 * G;
+  const int nb = G * El;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int b = 0; b < nb; ++b) { s_recv_start[b] = acc; acc += recv_counts[b]; }
+    s_recv_start[nb] = acc;
+    acc = 0;
+    for (int e = 0; e < El; ++e) {
+      if (blockIdx.x == 0) local_offsets[e] = acc;
+      for (int g = 0; g < G; ++g) { s_sorted_start[g * El + e] = acc; acc += recv_counts[g * El + e]; }
+    }
+    if (blockIdx.x == 0) local_offsets[El] = acc;
+  }
+  __syncthreads();
+  const int R = min(plan[0], cap);
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < R; r += gridDim.x * blockDim.x) {
+    int lo = 0, hi = nb;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_recv_start[mid] <= r) lo = mid; else hi = mid;
+    }
+    local_order[s_sorted_start[lo] + (r - s_recv_start[lo])] = r;
+  }
+}
+
+// One warp copies one row of K elements (16-byte pieces when `vec`), optionally scaled.
+template <typename T>
+__device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restrict__ dst, int K, bool vec, float sc,
+                                         bool scaled, int lane) {
+  if (vec) {
+    constexpr int per = 16 / sizeof(T);
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int q = lane; q < K / per; q += 32) {
+      uint4 v = __ldg(s4 + q);
+      if (scaled) {
+        if constexpr (sizeof(T) == 4) {
+          v.x = __float_as_uint(sc * __uint_as_float(v.x)); v.y = __float_as_uint(sc * __uint_as_float(v.y));
+          v.z = __float_as_uint(sc * __uint_as_float(v.z)); v.w = __float_as_uint(sc * __uint_as_float(v.w));
+        } else {
+          uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float a = sc * __uint_as_float(w[i] << 16), b = sc * __uint_as_float(w[i] & 0xffff0000u);
+            __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
+            w[i] = *reinterpret_cast<uint32_t*>(&pk);
+          }
+          v = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+      d4[q] = v;
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      if (!scaled) dst[k] = src[k];
+      else if constexpr (sizeof(T) == 4) dst[k] = sc * src[k];
+      else dst[k] = __float2bfloat16_rn(sc * __bfloat162float(src[k]));
+    }
+  }
+}
+
+// Sorted position i of this rank's slot list -> its row in the owner's receive buffer.
+template <typename T>
+__global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
+                              int src_div, const float* __restrict__ row_scale, int64_t P,
+                              const int32_t* __restrict__ sel_sorted, int El, const int32_t* __restrict__ plan,
+                              const uint64_t* __restrict__ peer_ptrs, int G, int64_t peer_rows, int64_t x_rows, int vec) {
+  const int lane = threadIdx.x & 31;
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (i >= P) return;
+  const int d = sel_sorted[i] / El;
+  const int64_t sr = src_row[i];
+  if (d < 0 || d >= G || sr < 0 || sr / src_div >= x_rows) return;
+  const int64_t dst_row = static_cast<int64_t>(plan[2 + G + d]) + (i - plan[2 + d]);
+  if (dst_row < 0 || dst_row >= peer_rows) return;
+  T* dst = reinterpret_cast<T*>(peer_ptrs[d]) + dst_row * K;
+  copy_row<T>(x + (sr / src_div) * stride, dst, K, vec != 0, row_scale ? row_scale[sr] : 1.f, row_scale != nullptr, lane);
+}
+
+// Row r of this rank's receive-ordered buffer -> its place in the source rank's sorted slot list.
+template <typename T>
+__global__ void ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, int K, const int32_t* __restrict__ plan,
+                                   const uint64_t* __restrict__ peer_ptrs, int G, int64_t cap_rows, int64_t peer_rows,
+                                   int vec) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int64_t R = min(static_cast<int64_t>(plan[0]), cap_rows);
+  const int32_t* recv_off = plan + 2 + 2 * G;
+  const int32_t* back_off = plan + 2 + 3 * G;
+  for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < R; r += warps) {
+    int s = 0;
+    for (int g = 1; g < G; ++g)
+      if (recv_off[g] <= r) s = g;                    // last source whose block starts at or before r
+    const int64_t dst_row = static_cast<int64_t>(back_off[s]) + (r - recv_off[s]);
+    if (dst_row < 0 || dst_row >= peer_rows) continue;
+    copy_row<T>(rows + r * stride, reinterpret_cast<T*>(peer_ptrs[s]) + dst_row * K, K, vec != 0, 1.f, false, lane);
+  }
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace amoe
+
+using namespace amoe;
+
+extern "C" {
+
+int64_t amoe_ep_plan_ints(int32_t G, int32_t El) { return G > 0 && El > 0 ? plan_ints(G, El) : 0; }
+
+int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, int32_t* plan, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(gathered && plan, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(G > 0 && G <= kEpMaxRanks && El > 0 && rank >= 0 && rank < G && G * El <= kEpMaxBlocksDev, AMOE_ERR_BAD_SHAPE);
+  ep_plan_kernel<<<1, 256, 0, stream>>>(gathered, rank, G, El, plan);
+  AMOE_LAUNCH_CHECK("ep_plan");
+  return AMOE_OK;
+}
+
+int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
+                           int32_t* local_offsets, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(plan && local_order && local_offsets, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(G > 0 && El > 0 && G * El <= kEpMaxBlocksDev && cap_rows > 0 && cap_rows < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
+  int64_t blocks = (cap_rows + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  ep_local_plan_dev_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(plan, G, El, static_cast<int>(cap_rows), local_order,
+                                                                             local_offsets);
+  AMOE_LAUNCH_CHECK("ep_local_plan_dev");
+  return AMOE_OK;
+}
+
+int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row,
+                int32_t src_div, const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El,
+                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && src_row && sel_sorted && plan && peer_ptrs, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && K > 0 && El > 0 && G > 0 && G <= kEpMaxRanks && src_div >= 1 && peer_rows > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
+  const int esz = dtype == AMOE_F32 ? 4 : 2;
+  const int vec = al16(x) && (stride * esz) % 16 == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;   // peer bases are page aligned
+  const unsigned blocks = static_cast<unsigned>((P * 32 + 255) / 256);
+  if (dtype == AMOE_F32)
+    ep_put_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div, row_scale, P,
+                                                     sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows, vec);
+  else if (dtype == AMOE_BF16)
+    ep_put_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K, src_row, src_div,
+                                                             row_scale, P, sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows,
+                                                             vec);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("ep_put");
+  return AMOE_OK;
+}
+
+int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K, const int32_t* plan,
+                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(rows && plan && peer_ptrs, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(K > 0 && G > 0 && G <= kEpMaxRanks && cap_rows > 0 && peer_rows > 0, AMOE_ERR_BAD_SHAPE);
+  const int esz = dtype == AMOE_F32 ? 4 : 2;
+  const int vec = al16(rows) && (stride * esz) % 16 == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;
+  int64_t blocks = (cap_rows * 32 + 255) / 256;
+  const int64_t max_blocks = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > max_blocks) blocks = max_blocks;
+  if (dtype == AMOE_F32)
+    ep_put_back_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(reinterpret_cast<const float*>(rows), stride, K, plan,
+                                                                                 peer_ptrs, G, cap_rows, peer_rows, vec);
+  else if (dtype == AMOE_BF16)
+    ep_put_back_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(rows), stride, K, plan, peer_ptrs, G, cap_rows, peer_rows, vec);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("ep_put_back");
+  return AMOE_OK;
+}
+
+}  // extern "C"

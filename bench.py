@@ -176,9 +176,10 @@ def run_ours(args, cfg, rank, world, device):
     barrier()
     # One CUDA graph per input set (whole step: routing, both projections, backward).  The Philox
     # offsets come from a device counter that the graph itself advances, so replays draw new noise.
-    # Expert-parallel runs stay eager: the exchange plan needs one host read per step.
+    # Expert-parallel runs are captured too when the exchange is device-driven (rows stored into peer memory, the plan
+    # computed on the device); the NCCL all-to-all fallback needs one host read per step and stays eager.
     graphs, ys, launches_per_step = None, None, None
-    if args.graph and world == 1:
+    if args.graph and (world == 1 or getattr(layer, "peer_exchange", False)):
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())

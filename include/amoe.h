@@ -356,6 +356,25 @@ int amoe_ep_pack(const void* x, int32_t dtype, int64_t stride, int32_t K, const 
  * buffer for each expert-sorted position (for e, for g); local_offsets [El+1].  G*El <= 4096. */
 int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_t R, int32_t* local_order,
                        int32_t* local_offsets, amoe_stream_t stream);
+/* Device-driven exchange (no value is needed on the host, so a whole step can be captured in a CUDA graph).
+ * amoe_ep_plan: from the all-gathered count matrix gathered[source][destination][local expert] (int32, [G,G,El]) to this
+ *   rank's plan, amoe_ep_plan_ints(G,El) int32 values: [0] rows received R, [1] rows sent, then arrays of G: send_off,
+ *   off_in, recv_off, back_off (block starts in this rank's sorted list / the destination's receive buffer / this rank's
+ *   receive buffer / the source's sorted list), then recv_counts [G,El].
+ * amoe_ep_local_plan_dev: amoe_ep_local_plan with counts and R taken from the plan; arrays sized for cap_rows.
+ * amoe_ep_put: row x[src_row[i]/src_div] (* row_scale[src_row[i]]) of sorted position i is stored at its place in the
+ *   receive buffer of the rank owning expert sel_sorted[i] (= sel_sorted[i]/El); peer_ptrs: device array of G base
+ *   pointers (buffers of peer_rows rows of K elements, this rank's own included).  Plain stores, no waiting.
+ * amoe_ep_put_back: the first R rows of `rows` (receive order) go back to their place in the source rank's buffer. */
+int64_t amoe_ep_plan_ints(int32_t G, int32_t El);
+int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, int32_t* plan, amoe_stream_t stream);
+int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
+                           int32_t* local_offsets, amoe_stream_t stream);
+int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row,
+                int32_t src_div, const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El,
+                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, amoe_stream_t stream);
+int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K, const int32_t* plan,
+                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, amoe_stream_t stream);
 /* inv[idx[i]] = i for a permutation idx of 0..P-1. */
 int amoe_invert_index(const int32_t* idx, int64_t P, int32_t* inv, amoe_stream_t stream);
 int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P,
