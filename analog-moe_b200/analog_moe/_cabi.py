@@ -71,7 +71,7 @@ class DwArgs(C.Structure):
         ("x", vp), ("x_dtype", C.c_int32), ("x_stride", C.c_int64), ("x_rows", C.c_int64), ("x_row", vp), ("ir", vp), ("ir_by_expert", C.c_int32),
         ("g", vp), ("g_dtype", C.c_int32), ("g_stride", C.c_int64), ("g_rows", C.c_int64), ("g_row", vp),
         ("g_div", C.c_int32), ("g_scale", vp), ("dw", vp),
-        ("x_hi", vp), ("x_lo", vp), ("g_hi", vp), ("g_lo", vp), ("cache_rows", C.c_int64),
+        ("x_hi", vp), ("x_lo", vp), ("g_hi", vp), ("g_lo", vp), ("cache_rows", C.c_int64), ("expected_rows", C.c_int64),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]
 
@@ -105,6 +105,7 @@ SIGNATURES = {
     "amoe_cvmm_dx": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dw_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "amoe_cvmm_dw": (C.c_int, [C.POINTER(DwArgs), vp]),
+    "amoe_cvmm_dw_workspace_bytes_tuned": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "amoe_combine": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
                                C.c_int64, vp]),
     "amoe_combine_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,

@@ -385,11 +385,11 @@ class _ExpertParallelStep(torch.autograd.Function):
                                      out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc)
             if need_values and cached:
                 grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, local_offsets, El, precision,
-                                                 P=R).to(values_dtype)
+                                                 P=R, expected_rows=n_rows).to(values_dtype)
             ops.set_tag("up")
             if need_keys and cached:
                 grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, local_offsets, El, precision,
-                                               P=R).to(keys_dtype)
+                                               P=R, expected_rows=n_rows).to(keys_dtype)
             elif need_keys:
                 grad_keys = ops.cvmm_dw(recv, local_order, dh, local_order, local_offsets, El, precision, P=R, ir=ir_up,
                                         ir_by_expert=True).to(keys_dtype)

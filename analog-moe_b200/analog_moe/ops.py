@@ -432,8 +432,9 @@ def operand_cache_ok(precision: int, *cols: int) -> bool:
 
 
 def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.Tensor, E: int, precision: int, *,
-                   P: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """dW [E,K,N] from two operand caches ([rows,K] and [rows,N])."""
+                   P: int, status: Optional[torch.Tensor] = None, expected_rows: int = 0) -> torch.Tensor:
+    """dW [E,K,N] from two operand caches ([rows,K] and [rows,N]).  `expected_rows`: the likely slot count when P is
+    only an upper bound (tunes the work split)."""
     K, N = x_cache.cols, g_cache.cols
     dev = x_cache.hi.device
     dw = torch.empty(E, K, N, dtype=torch.float32, device=dev)
@@ -442,9 +443,10 @@ def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.
     a.expert_offsets = ptr(offsets)
     a.x_hi, a.x_lo, a.g_hi, a.g_lo = ptr(x_cache.hi), ptr(x_cache.lo), ptr(g_cache.hi), ptr(g_cache.lo)
     a.cache_rows = x_cache.rows
+    a.expected_rows = int(expected_rows)
     a.g_div = 1
     a.dw = ptr(dw)
-    nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
+    nbytes = lib.amoe_cvmm_dw_workspace_bytes_tuned(P, int(expected_rows), E, K, N, precision)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     a.dev_status = ptr(status)

@@ -42,7 +42,13 @@ int64_t amoe_padded_rows(int64_t P, int32_t E) {
 
 size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision) {
   if (precision == AMOE_PREC_FP32_SIMT || P <= 0 || E <= 0 || K <= 0 || N <= 0) return 0;
-  return dw_tc_workspace_bytes(P, E, K, N);
+  return dw_tc_workspace_bytes(P, 0, E, K, N);
+}
+
+size_t amoe_cvmm_dw_workspace_bytes_tuned(int64_t P, int64_t expected_rows, int32_t E, int32_t K, int32_t N,
+                                          int32_t precision) {
+  if (precision == AMOE_PREC_FP32_SIMT || P <= 0 || E <= 0 || K <= 0 || N <= 0) return 0;
+  return dw_tc_workspace_bytes(P, expected_rows, E, K, N);
 }
 
 int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {

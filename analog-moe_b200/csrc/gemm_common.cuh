@@ -27,6 +27,7 @@ int launch_cvmm_simt(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi, 
 int launch_dw_simt(const amoe_dw_args* a, cudaStream_t stream);
 int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi, cudaStream_t stream);
 int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream);
-size_t dw_tc_workspace_bytes(int64_t P, int E, int K, int N);
+// `expected` (0 = P): the slot count the segment size is tuned for, when P is only an upper bound.
+size_t dw_tc_workspace_bytes(int64_t P, int64_t expected, int E, int K, int N);
 
 }  // namespace amoe

@@ -1497,8 +1497,8 @@ extern "C" int amoe_debug_timeline(long long* host, int clear) {
 }
 #endif
 
-size_t dw_tc_workspace_bytes(int64_t P, int E, int K, int N) {
-  const int seg = dw_segment_slots(P, K, N);
+size_t dw_tc_workspace_bytes(int64_t P, int64_t expected, int E, int K, int N) {
+  const int seg = dw_segment_slots(expected > 0 && expected < P ? expected : P, K, N);
   if (seg == 0) return 0;
   // segments are cut per expert, in padded row space when the operands come from the caches
   return static_cast<size_t>((P + static_cast<int64_t>(kBM) * E + seg - 1) / seg + E) * K * N * sizeof(float);
@@ -1513,8 +1513,9 @@ static int launch_dw_tma(const amoe_dw_args* a, cudaStream_t stream) {
   p.m_tiles = (a->K + kBM - 1) / kBM;
   p.offsets = a->expert_offsets;
   p.dw = a->dw; p.status = a->dev_status;
-  p.seg = dw_segment_slots(a->P, a->K, a->N);
-  const size_t need = dw_tc_workspace_bytes(a->P, a->E, a->K, a->N);
+  const int64_t tune = a->expected_rows > 0 && a->expected_rows < a->P ? a->expected_rows : a->P;
+  p.seg = dw_segment_slots(tune, a->K, a->N);
+  const size_t need = dw_tc_workspace_bytes(a->P, tune, a->E, a->K, a->N);
   if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
     p.seg = 0;
   p.partials = p.seg > 0 ? reinterpret_cast<float*>(a->workspace) : nullptr;
@@ -1586,8 +1587,9 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   // Large problems: cut every expert's slot range into segments so that the work items outnumber the
   // SMs and a popular expert does not become one long item; the partial tiles go to the workspace and
   // are summed in segment order afterwards.
-  p.seg = dw_segment_slots(a->P, a->K, a->N);
-  const size_t need = dw_tc_workspace_bytes(a->P, a->E, a->K, a->N);
+  const int64_t tune = a->expected_rows > 0 && a->expected_rows < a->P ? a->expected_rows : a->P;
+  p.seg = dw_segment_slots(tune, a->K, a->N);
+  const size_t need = dw_tc_workspace_bytes(a->P, tune, a->E, a->K, a->N);
   if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
     p.seg = 0;   // no (usable) workspace: one owner per expert tile
   p.partials = p.seg > 0 ? reinterpret_cast<float*>(a->workspace) : nullptr;

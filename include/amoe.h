@@ -268,10 +268,15 @@ typedef struct amoe_dw_args {
    * order (see amoe_cvmm_args).  With x_hi and g_hi given, x/g/x_row/g_row/ir/g_scale are not read: clamp and
    * scale are already in the caches.  Layout [ceil(cols/64)][cache_rows][64]; cache_rows >= amoe_padded_rows. */
   const void* x_hi; const void* x_lo; const void* g_hi; const void* g_lo; int64_t cache_rows;
+  int64_t expected_rows;          /* 0, or the slot count to tune the segment size for when P is only an upper bound
+                                     (buffers of worst-case size); the workspace then comes from
+                                     amoe_cvmm_dw_workspace_bytes_tuned with the same two values */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_dw_workspace_bytes, or NULL */
   int32_t* dev_status;
 } amoe_dw_args;
 size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision);
+size_t amoe_cvmm_dw_workspace_bytes_tuned(int64_t P, int64_t expected_rows, int32_t E, int32_t K, int32_t N,
+                                          int32_t precision);
 int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
