@@ -372,31 +372,40 @@ class _ExpertParallelStep(torch.autograd.Function):
             dist.all_to_all_single(g_recv, drows, recv_splits, send_splits, group=group)
             del drows
         grad_keys = grad_values = None
+        main, side = torch.cuda.current_stream(), ops.side_stream(dev)
+        forked = False
         if R > 0:
             split = xc_lo is not None
             gc = ops.OperandCache.empty(R, El, N, split, dev) if cached and need_values else None
             dhc = ops.OperandCache.empty(R, El, Fh, split, dev) if cached and need_keys else None
             if need_values and not cached:
                 grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
-                                          ir_by_expert=True).to(values_dtype)
+                                          ir_by_expert=True)
             dh, irs_dn = ops.cvmm_dx(g_recv, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
                                      x_ref=h, x_ref_row=local_order, ir=ir_dn, ir_by_expert=True, want_ir_grad=has_ir,
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
                                      out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc)
-            if need_values and cached:
-                grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, local_offsets, El, precision,
-                                                 P=R, expected_rows=n_rows).to(values_dtype)
             ops.set_tag("up")
-            if need_keys and cached:
-                grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, local_offsets, El, precision,
-                                               P=R, expected_rows=n_rows).to(keys_dtype)
-            elif need_keys:
-                grad_keys = ops.cvmm_dw(recv, local_order, dh, local_order, local_offsets, El, precision, P=R, ir=ir_up,
-                                        ir_by_expert=True).to(keys_dtype)
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
                                       ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                       keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype)
+            # the two weight gradients on a second stream, beside the exchange and the streaming kernels that follow
+            forked = cached and (need_values or need_keys)
+            if forked:
+                side.wait_stream(main)
+                with ops.launch_on(side):
+                    if need_values:
+                        ops.set_tag("down")
+                        grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, local_offsets, El, precision,
+                                                         P=R, expected_rows=n_rows)
+                    if need_keys:
+                        ops.set_tag("up")
+                        grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, local_offsets, El, precision,
+                                                       P=R, expected_rows=n_rows)
+            elif need_keys:
+                grad_keys = ops.cvmm_dw(recv, local_order, dh, local_order, local_offsets, El, precision, P=R, ir=ir_up,
+                                        ir_by_expert=True)
         else:
             dxr = recv.new_zeros((0, D))
             irs_up = irs_dn = None
@@ -428,6 +437,12 @@ class _ExpertParallelStep(torch.autograd.Function):
                                        keeps[1:] if keeps is not None else None, float(n_rows) * Fh)]).to(ir_dtype)
             else:
                 grad_ir = torch.zeros(2, El, dtype=ir_dtype, device=dev)
+        if forked:
+            main.wait_stream(side)
+        if grad_values is not None:
+            grad_values = grad_values.to(values_dtype)
+        if grad_keys is not None:
+            grad_keys = grad_keys.to(keys_dtype)
         return (None, grad_x, grad_sel, grad_keys, grad_values, grad_ir)
 
 

@@ -196,7 +196,7 @@ class _FusedAnalogStep(torch.autograd.Function):
         grad_values = None
         if need_values and not cached:
             grad_values = ops.cvmm_dw(h, slot_index, g, slot_index, offsets, E, precision, P=P, ir=ir_dn,
-                                      ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1)).to(values_dtype)
+                                      ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1))
         split = xc_lo is not None
         gc = ops.OperandCache.empty(P, E, N, split, x2.device) if cached and need_values else None
         dhc = ops.OperandCache.empty(P, E, Fh, split, x2.device) if cached and need_keys else None
@@ -205,32 +205,42 @@ class _FusedAnalogStep(torch.autograd.Function):
                                  want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                  keep_count=keeps[1:] if keeps is not None else None, out_dtype=h.dtype,
                                  x_ref_relu=True, a_cache=gc, out_cache=dhc)
-        if need_values and cached:
-            # dW = sum_slots (gate * clamp(h))^T (x) gy: both operands straight from the caches
-            grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision,
-                                             P=P).to(values_dtype)
-        if codes is not None:
-            dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
-        else:
-            dgate = ops.row_dot(res, g, k)
-        # ---- up-projection
+        # ---- up-projection's input gradient (the other kernel that fills every SM), then the two weight gradients from
+        # the caches on a second stream: the TMA-fed kernel runs six warps per SM and leaves registers and issue slots
+        # to the streaming kernels of the main stream (gate gradient, sum over k, router), which run beside it
         ops.set_tag("up")
-        grad_keys = None
-        if need_keys and cached:
-            grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P).to(keys_dtype)
-        elif need_keys:
-            grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
-                                    ir_by_expert=True).to(keys_dtype)
-        grad_x = irs_up = None
+        grad_x = irs_up = dxr = None
         if need_x or need_ir:
             dxr, irs_up = ops.cvmm_dx(dh, slot_index, slot_index, offsets, pw_up, precision, P=P, dst_rows=P,
                                       x_ref=x2 if has_ir else None, x_ref_row=token_index if has_ir else None,
                                       ir=ir_up, ir_by_expert=True, want_ir_grad=has_ir, relative=relative,
                                       grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
                                       out_dtype=x2.dtype)
-            if need_x:
-                # sum over k plus the router's own input gradient in one pass
-                grad_x = ops.combine_router(dxr, T, k, dgate, gate, raw_sel, w_sel)
+        grad_keys = None
+        main, side = torch.cuda.current_stream(), ops.side_stream(x2.device)
+        forked = cached and (need_values or need_keys)
+        if forked:
+            side.wait_stream(main)
+            with ops.launch_on(side):
+                if need_values:
+                    # dW = sum_slots (gate * clamp(h))^T (x) gy: both operands straight from the caches
+                    ops.set_tag("down")
+                    grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision, P=P)
+                if need_keys:
+                    ops.set_tag("up")
+                    grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P)
+        elif need_keys:
+            grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
+                                    ir_by_expert=True)
+        ops.set_tag("down")
+        if codes is not None:
+            dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
+        else:
+            dgate = ops.row_dot(res, g, k)
+        ops.set_tag("up")
+        if need_x:
+            # sum over k plus the router's own input gradient in one pass
+            grad_x = ops.combine_router(dxr, T, k, dgate, gate, raw_sel, w_sel)
         # ---- router
         grad_sel = None
         if need_sel:
@@ -243,6 +253,12 @@ class _FusedAnalogStep(torch.autograd.Function):
                                    float(P) * D),
                 ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
                                    float(P) * Fh)]).to(ir_dtype)
+        if forked:
+            main.wait_stream(side)
+        if grad_values is not None:
+            grad_values = grad_values.to(values_dtype)
+        if grad_keys is not None:
+            grad_keys = grad_keys.to(keys_dtype)
         return (None, grad_x.view(x_shape) if need_x else None, grad_sel, grad_keys, grad_values, grad_ir)
 
 

@@ -451,6 +451,7 @@ def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     a.dev_status = ptr(status)
     _call("amoe_cvmm_dw", C.byref(a), stream_ptr())
+    dw._amoe_workspace = ws     # alive as long as the result: the launch stream may differ from the allocating one
     return dw
 
 
