@@ -148,6 +148,10 @@ def step(layer, x, gy, bwd):
 
 def run_ours(args, cfg, rank, world, device):
     from analog_moe import ops, _cabi
+    # parameters' AccumulateGrad nodes are created during warm-up on the default stream and used again under graph
+    # capture on another stream: intended here
+    if hasattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch"):
+        torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
     dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
     precision = _cabi.PRECISION_NAMES[args.precision] if args.precision else None
     group = None
