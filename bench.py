@@ -78,7 +78,7 @@ class ClockSampler(threading.Thread):
                                      else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)))
             except Exception:
                 pass
-            time.sleep(0.05)
+            time.sleep(0.01)
 
     def result(self):
         if not self.ok or not self.samples:
