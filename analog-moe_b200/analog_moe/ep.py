@@ -157,8 +157,9 @@ def step_plan(counts: Tensor, rank: int, group=None) -> StepPlan:
     """counts [G, El]: this rank's slots per (destination rank, local expert).  One all-gather and the step's only
     device->host copy."""
     G, El = counts.shape
-    gathered = torch.empty((G, G, El), dtype=counts.dtype, device=counts.device)
-    dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
+    flat = torch.empty(G * G * El, dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(flat, counts.contiguous().view(-1), group=group)
+    gathered = flat.view(G, G, El)
     tot = gathered.sum(-1).cpu()                                  # [source, destination] row counts
     tot_l = [[int(v) for v in row] for row in tot]
     send_n = tot_l[rank]

@@ -232,12 +232,13 @@ def run_ours(args, cfg, rank, world, device):
     t_dev = torch.tensor([ms], device=device)
 
     # ---------------- end to end: pinned host inputs in, results out, every step
-    # The caller-side loop is software-pipelined over three streams (copy-in, compute, copy-out) and two
-    # buffer sets, so that the PCIe copies of neighbouring steps overlap the kernels; every step still
+    # The caller-side loop is software-pipelined over three streams (copy-in, compute, copy-out) and three
+    # buffer sets (a set is busy for copy-in + compute + copy-out, about 3 ms, so two sets cannot keep both PCIe
+    # directions full), so that the PCIe copies of neighbouring steps overlap the kernels; every step still
     # moves its own inputs from pinned host memory and its own results (y, dx) back to pinned host memory.
-    nbuf = 2
+    nbuf = 3
     if graphs is not None:
-        bx, bg = [xs[0], xs[1]], [gys[0], gys[1]]       # static buffers of graphs 0 and 1
+        bx, bg = [xs[b] for b in range(nbuf)], [gys[b] for b in range(nbuf)]    # static buffers of graphs 0..2
     else:
         bx = [torch.empty_like(xs[0]).requires_grad_(bwd) for _ in range(nbuf)]
         bg = [torch.empty_like(gys[0]) for _ in range(nbuf)]

@@ -67,3 +67,45 @@ def test_plan_from_counts_handles_empty_rank():
     p = plan_from_counts(send, recv)
     assert p.n_recv == 0 and p.local_order.numel() == 0 and p.local_offsets.tolist() == [0, 0, 0]
     assert p.send_splits == [3, 0]
+
+
+def _step_plan_worker(rank, world, port, E, k, T):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from analog_moe.ep import step_plan
+        from oracle import cvmm_oracle as O
+        g = torch.Generator().manual_seed(7 + rank)
+        logits = torch.randn(T + 5 * rank, E, generator=g)
+        s = O.select_sort(logits, k)
+        El = E // world
+        P = s.sel.numel()
+        counts = (s.expert_offsets[1:] - s.expert_offsets[:-1]).to(torch.int32).view(world, El)
+        plan = step_plan(counts, rank)
+        assert sum(plan.send_n) == P and plan.send_off[0] == 0
+        assert plan.p_max == max((T + 5 * r) * k for r in range(world))
+        assert torch.equal(plan.recv_counts[rank], counts[rank])            # what this rank keeps for itself
+        # emulate the stores of the device-driven exchange with an all-to-all of tagged rows and check that the block
+        # starts the plan predicts are where the rows land
+        rows = torch.stack([torch.full((P,), rank), torch.arange(P)], 1).double()
+        recv = torch.empty(plan.n_recv, 2, dtype=torch.float64)
+        dist.all_to_all_single(recv, rows, plan.recv_n, plan.send_n)
+        for src in range(world):
+            blk = recv[plan.recv_off[src]:plan.recv_off[src] + plan.recv_n[src]]
+            assert bool((blk[:, 0] == src).all())
+        # off_in / back_off: every rank publishes them, the owner checks its side
+        mine = torch.tensor([plan.off_in, plan.back_off, plan.send_off, plan.recv_off], dtype=torch.int64)
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        for src in range(world):
+            assert int(everyone[src][0][rank]) == plan.recv_off[src]         # source's off_in at me = my recv_off[source]
+            assert int(everyone[src][2][rank]) == plan.back_off[src]         # my back_off[source] = source's send_off[me]
+            if plan.recv_n[src]:
+                assert float(recv[plan.recv_off[src], 1]) == float(everyone[src][2][rank])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,E,k", [(2, 8, 2), (4, 16, 3)])
+def test_step_plan_block_starts_over_gloo(world, E, k):
+    mp.spawn(_step_plan_worker, args=(world, _free_port(), E, k, 29), nprocs=world, join=True)

@@ -578,3 +578,63 @@ def test_router_kernels_vs_torch(dev, T, D, E, k, dtype):
     ref_y = rows.double().view(T, k, D).sum(1) + dl @ w.double()
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert float((y.double() - ref_y).abs().max()) <= tol * max(1.0, float(ref_y.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("G,E,k,dtype", [(2, 8, 2, torch.float32), (4, 16, 4, torch.float32), (8, 16, 3, torch.bfloat16)])
+def test_device_driven_exchange_emulated_ranks(dev, G, E, k, dtype):
+    """The expert-parallel exchange kernels with G ranks emulated on one GPU (one buffer per rank, the "peer" pointers
+    are local): plan from the gathered counts, rows stored into their owners' buffers, regrouped by local expert, and
+    sent back.  Checked against the host plan (`ep.step_plan` arithmetic) and as a round trip."""
+    from analog_moe import ops
+    from analog_moe._cabi import lib, stream_ptr
+    El, D = E // G, 72
+    Ts = [150 + 37 * r for r in range(G)]                      # ragged: a different token count per rank
+    g = torch.Generator().manual_seed(G * 100 + E)
+    xs = [torch.randn(T, D, generator=g).to(dev).to(dtype) for T in Ts]
+    logits = [torch.randn(T, E, generator=g) for T in Ts]
+    logits[0][:, E - 1] = -50.0                                # nobody on rank 0 picks the last expert
+    routes = [ops.select_sort(l.to(dev), k) for l in logits]
+    counts = torch.stack([(r.expert_offsets[1:] - r.expert_offsets[:-1]).view(G, El) for r in routes]).contiguous()  # [s,d,e]
+    tot = counts.sum(-1).cpu()
+    p_cap = max(T * k for T in Ts)
+    cap = G * p_cap
+    recv = [torch.full((cap, D), float("nan"), device=dev, dtype=dtype) for _ in range(G)]
+    back = [torch.full((p_cap, D), float("nan"), device=dev, dtype=dtype) for _ in range(G)]
+    recv_ptrs = torch.tensor([t.data_ptr() for t in recv], dtype=torch.int64, device=dev)
+    back_ptrs = torch.tensor([t.data_ptr() for t in back], dtype=torch.int64, device=dev)
+    plans = [ops.ep_plan(counts, r) for r in range(G)]
+    dc = ops.dtype_code(xs[0])
+    for r in range(G):
+        st = lib.amoe_ep_put(xs[r].data_ptr(), dc, D, D, Ts[r], routes[r].token_index.data_ptr(), 1, None, Ts[r] * k,
+                             routes[r].sel.data_ptr(), El, plans[r].data_ptr(), recv_ptrs.data_ptr(), G, cap, stream_ptr())
+        assert st == 0
+    torch.cuda.synchronize()
+    for d in range(G):
+        plan = plans[d].cpu()
+        R = int(tot[:, d].sum())
+        assert int(plan[0]) == R and int(plan[1]) == Ts[d] * k
+        # receive buffer: for source s, that source's sorted rows for this rank's experts, in order
+        want = []
+        for s in range(G):
+            lo = int(tot[s, :d].sum())
+            n = int(tot[s, d])
+            want.append(xs[s][routes[s].token_index[lo:lo + n].long()])
+        want = torch.cat(want)
+        assert torch.equal(recv[d][:R], want)
+        assert torch.isnan(recv[d][R:].float()).all()          # nothing written past the rows that exist
+        order, offsets = ops.ep_local_plan_dev(plans[d], G, El, cap)
+        ref_order, ref_offsets = ops.ep_local_plan(counts[:, d, :].contiguous(), R)
+        assert torch.equal(order[:R], ref_order) and torch.equal(offsets, ref_offsets)
+        # rows regrouped by local expert really belong to that expert
+        owner = torch.cat([routes[s].sel[int(tot[s, :d].sum()):int(tot[s, :d].sum()) + int(tot[s, d])] for s in range(G)])
+        eo = offsets.cpu()
+        for e in range(El):
+            assert bool((owner[order[int(eo[e]):int(eo[e + 1])].long()] == d * El + e).all())
+        st = lib.amoe_ep_put_back(recv[d].data_ptr(), dc, D, D, plans[d].data_ptr(), back_ptrs.data_ptr(), G, cap, p_cap,
+                                  stream_ptr())
+        assert st == 0
+    torch.cuda.synchronize()
+    for r in range(G):                                         # round trip: every rank gets its sorted rows back
+        P = Ts[r] * k
+        assert torch.equal(back[r][:P], xs[r][routes[r].token_index.long()])
