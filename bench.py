@@ -24,7 +24,7 @@ for p in (ROOT, os.path.join(ROOT, "analog-moe_b200")):
 
 import torch  # noqa: E402
 
-# BASELINE.json configs: T tokens per GPU, k, D, F, E, dtype, analog settings
+# benchmark configs: T tokens per GPU, k, D, F, E, dtype, analog settings
 CONFIGS = {
     "c1": dict(T=512, k=2, D=256, F=64, E=8, dtype="fp32", out_noise=0.0, w_noise=0.0, adc=True, bwd=True),
     "c2": dict(T=8192, k=4, D=1024, F=128, E=16, dtype="fp32", out_noise=0.04, w_noise=0.02, adc=True, bwd=True),

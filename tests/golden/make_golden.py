@@ -146,7 +146,9 @@ def std_case(ref, name, T, k, D, E, seed):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference>")
+    ref = load_reference(sys.argv[1])
     q = 2.0 / 254.0
     # reference-test shape (tests/test_moe_layer_aihwkit.py:211-216) with input ranges 1+e (:248-263)
     ir_1pe = torch.stack([torch.arange(1.0, 5.0), torch.arange(1.0, 5.0)])
@@ -158,7 +160,7 @@ def main():
     layer_case(ref, "small_absmax_quant", 80, 3, 48, 40, 5, q, False, seed=3)
     layer_case(ref, "small_ir_quant_noise", 64, 2, 64, 32, 4, q, True, seed=4, noise=0.05)
     layer_case(ref, "ragged_zipf_empty", 77, 3, 40, 24, 6, q, True, seed=5, zipf=True, empty_expert=True)
-    # BASELINE config 1: d_model=256, E=8, F=64, k=2, 512 tokens, 8-bit DAC, input range 3.0
+    # benchmark config 1: d_model=256, E=8, F=64, k=2, 512 tokens, 8-bit DAC, input range 3.0
     layer_case(ref, "config1", 512, 2, 256, 64, 8, q, True, seed=0, ir_values=torch.full((2, 8), 3.0))
     std_case(ref, "expert_std", 120, 2, 96, 5, seed=7)
 

@@ -1,4 +1,4 @@
-"""Checks at BASELINE sizes, where the CPU oracle is too slow to run in full: agreement between the
+"""Checks at the full benchmark sizes, where the CPU oracle is too slow to run in full: agreement between the
 tensor-core kernels and the CUDA-core fp32 kernels (which the small-size tests pin to the reference),
 oracle checks on a sample of slots, determinism, and layer-level behaviour (stacked bf16 layers,
 input-range initialisation from data, Zipf routing)."""
