@@ -2,10 +2,10 @@
 //
 // cvmm_tc_kernel  (forward and input gradient)
 //   Persistent, warp-specialised CTA, one per SM, walking 128-row tiles of the expert-sorted slot
-//   list.  18 warps:
+//   list.  24 warps:
 //     warp 0        lane 0 issues the TMA loads of the prepared bf16 weight tiles (128B swizzle)
 //     warp 1        allocates TMEM; lane 0 issues tcgen05.mma (128 x BN x 16, fp32 accumulate in TMEM)
-//     16 workers    split per launch (4/8/12) between
+//     22 workers    split per launch between
 //       epilogue:   tcgen05.ld of the accumulator, one thread per output row and share of the
 //                   columns, then noise / ADC / rescale (forward) or clip mask / input-range
 //                   gradient (backward), stores
@@ -37,10 +37,11 @@ using namespace tc;
 
 constexpr int kBM = 128;          // rows per tile (UMMA M)
 constexpr int kBK = 64;           // bf16 elements per stage along the contraction (128 bytes)
-// forward / dX kernel geometry: 2 control warps + 16 worker warps whose split between epilogue and
-// prologue is chosen per launch (4, 8 or 12 epilogue warps)
-constexpr int kWorkerWarps = 30;
-constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 1024
+// forward / dX kernel geometry: 2 control warps + 22 worker warps whose split between epilogue and
+// prologue is chosen per launch (4 ... 20 epilogue warps).  24 warps x 80 registers measured better than 32 x 64
+// (which spilled) and than 20 x 102.
+constexpr int kWorkerWarps = 22;
+constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 768
 constexpr int kMaxEpiGroups = 6;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATile = kBM * kBK * 2;  // 16 KiB
@@ -1428,7 +1429,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
     double best = 1e300;
-    for (int ne = 4; ne <= 24; ne += 4) {
+    for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
