@@ -109,11 +109,11 @@ SIGNATURES = {
     "amoe_combine": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
                                C.c_int64, vp]),
     "amoe_combine_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int64, C.c_int32, C.c_int32, vp, C.c_int32,
-                                     C.c_int64, vp]),
+                                     C.c_int64, vp, vp]),
     "amoe_row_dot": (C.c_int, [vp, C.c_int32, C.c_int64, vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
                                vp, vp]),
     "amoe_row_dot_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
-                                     vp, vp]),
+                                     vp, vp, vp]),
     "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, vp]),
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp,

@@ -187,8 +187,11 @@ class PeerExchange:
         self.p_cap, self.cap = p_cap, self.G * p_cap
         self.key = (p_cap, D, N, dtype)
         self.buffers = {}
-        for name, (rows, cols) in {"x": (self.cap, D), "g": (self.cap, N), "y": (p_cap, N), "dx": (p_cap, D)}.items():
-            t = symm.empty(rows, cols, dtype=dtype, device=device)
+        # "yc" / "ys": the down-projection's rows as ADC codes (int8, moved as N/2 two-byte elements) and one scale per row
+        shapes = {"x": (self.cap, D, dtype), "g": (self.cap, N, dtype), "y": (p_cap, N, dtype), "dx": (p_cap, D, dtype),
+                  "yc": (p_cap, (N + 1) // 2, torch.bfloat16), "ys": (p_cap, 1, torch.float32)}
+        for name, (rows, cols, dt) in shapes.items():
+            t = symm.empty(rows, cols, dtype=dt, device=device)
             hdl = symm.rendezvous(t, group)
             self.buffers[name] = (hdl, t, int(hdl.buffer_ptrs_dev))
         self.token = torch.zeros(1, device=device)
@@ -209,13 +212,14 @@ class PeerExchange:
         self.barrier()
         return buf
 
-    def put_back(self, name: str, rows: Tensor, plan: Tensor, n_own: int) -> Tensor:
+    def put_back(self, name: str, rows: Tensor, plan: Tensor, n_own: int, barrier: bool = True) -> Tensor:
         """The first R rows of `rows` (receive order) back to their sources; returns this rank's buffer [n_own, cols]."""
         hdl, buf, ptrs = self.buffers[name]
         assert rows.shape[1] == buf.shape[1] and rows.dtype == buf.dtype and rows.stride(-1) == 1
         ops._call("amoe_ep_put_back", ops.ptr(rows), ops.dtype_code(rows), rows.stride(0), rows.shape[1], ops.ptr(plan), ptrs,
                   self.G, rows.shape[0], buf.shape[0], ops.stream_ptr())
-        self.barrier()
+        if barrier:
+            self.barrier()
         return buf[:n_own]
 
 
@@ -310,25 +314,41 @@ class _ExpertParallelStep(torch.autograd.Function):
                                 out_res=out_res, out_bound=out_bound, out_relu=True, a_cache=xc, **nz_up)
             ops.set_tag("down")
             am_dn = None if has_ir else ops.row_absmax(h)
-            out, _ = ops.cvmm_fwd(h, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
-                                  ir=ir_all[1] if has_ir else None, ir_by_expert=True, absmax=am_dn, inp_res=inp_res,
-                                  out_res=out_res, out_bound=out_bound, a_cache=hs, **nz_dn)
+            # with the ADC on and the device-driven exchange the rows travel back as int8 codes + one scale per row
+            codes_back = xchg is not None and adc_on and N % 16 == 0
+            meta = {} if codes_back else None
+            out, codes = ops.cvmm_fwd(h, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
+                                      ir=ir_all[1] if has_ir else None, ir_by_expert=True, absmax=am_dn, inp_res=inp_res,
+                                      out_res=out_res, out_bound=out_bound, a_cache=hs, want_codes=codes_back,
+                                      want_out=not codes_back, row_meta=meta, **nz_dn)
         else:
+            codes_back = False
             h = recv.new_zeros((0, Fh))
             out = recv.new_zeros((0, N))
         # ---- rows back, gate-weighted sum over k in slot order
-        if xchg is not None:
-            back = xchg.put_back("y", out, plan, P)
+        back = cs_all = scale_back = None
+        adc_step = ops.adc_step(out_res, out_bound) if adc_on else 0.0
+        if codes_back:
+            back = xchg.put_back("yc", codes.view(torch.bfloat16), plan, P, barrier=False).view(torch.int8)
+            scale_back = xchg.put_back("ys", meta["row_scale"].view(-1, 1), plan, P).view(-1)
+            cs_all = torch.empty((G * El, N), dtype=torch.float32, device=dev)       # column scales of every expert
+            dist.all_gather_into_tensor(cs_all, pw_dn.col_scale.contiguous(), group=group)
+            y = ops.combine_codes(back, cs_all, r.raw_sel, scale_back, adc_step, gate, T, k, out_dtype=x.dtype,
+                                  row_index=inv)
         else:
-            back = out.new_empty((P, N))
-            dist.all_to_all_single(back, out, send_splits, recv_splits, group=group)
-        y = ops.combine(back, gate, T, k, row_index=inv)
+            if xchg is not None:
+                back = xchg.put_back("y", out, plan, P)
+            else:
+                back = out.new_empty((P, N))
+                dist.all_to_all_single(back, out, send_splits, recv_splits, group=group)
+            y = ops.combine(back, gate, T, k, row_index=inv)
         simt = precision == ops.A.PREC_FP32_SIMT
         ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv, r.sel,
                               local_order, local_offsets, ir_all,
                               pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
-                              *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)))
+                              *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)), cs_all, scale_back)
+        ctx.adc_step = adc_step
         ctx.meta = (x.shape, El, k, precision, ir_p, keys.dtype, values.dtype, keys.shape, values.shape,
                     input_range.dtype if has_ir else None, send_splits, recv_splits, group, plan, xchg)
         return y.view(bsz, seq, N)
@@ -336,7 +356,7 @@ class _ExpertParallelStep(torch.autograd.Function):
     @staticmethod
     def backward(ctx, gy):
         (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets, ir_all,
-         w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo) = ctx.saved_tensors
+         w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo, cs_all, scale_back) = ctx.saved_tensors
         (x_shape, El, k, precision, ir_p, keys_dtype, values_dtype, kshape, vshape, ir_dtype, send_splits, recv_splits,
          group, plan, xchg) = ctx.meta
         T, D = x2.shape
@@ -364,7 +384,10 @@ class _ExpertParallelStep(torch.autograd.Function):
         gate_flat = gate.reshape(-1)
         # ---- gate gradient at the source, gate * gy rows to the owners
         ops.set_tag("down")
-        dgate = ops.row_dot(back, g, k, row_index=inv)
+        if cs_all is not None:      # `back` holds ADC codes
+            dgate = ops.row_dot_codes(back, cs_all, raw_sel.reshape(-1), scale_back, ctx.adc_step, g, k, row_index=inv)
+        else:
+            dgate = ops.row_dot(back, g, k, row_index=inv)
         if xchg is not None:
             g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat)
         else:

@@ -469,13 +469,14 @@ def combine(res: torch.Tensor, w: Optional[torch.Tensor], T: int, k: int, out_dt
 
 
 def combine_codes(codes: torch.Tensor, col_scale: torch.Tensor, raw_sel: torch.Tensor, row_mult: Optional[torch.Tensor],
-                  step: float, w: Optional[torch.Tensor], T: int, k: int, out_dtype=torch.float32) -> torch.Tensor:
+                  step: float, w: Optional[torch.Tensor], T: int, k: int, out_dtype=torch.float32,
+                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     N = codes.shape[-1]
     y = torch.empty(T, N, dtype=out_dtype, device=codes.device)
     if w is not None:
         w = w.reshape(-1).float().contiguous()
     _call("amoe_combine_codes", ptr(codes), ptr(col_scale), ptr(i32(raw_sel)), ptr(row_mult), float(step), ptr(w), T, k,
-                                 N, ptr(y), dtype_code(y), y.stride(0), stream_ptr())
+                                 N, ptr(y), dtype_code(y), y.stride(0), ptr(row_index), stream_ptr())
     return y
 
 
@@ -489,12 +490,12 @@ def row_dot(res: torch.Tensor, g: torch.Tensor, k: int, row_index: Optional[torc
 
 
 def row_dot_codes(codes: torch.Tensor, col_scale: torch.Tensor, row_expert: torch.Tensor, row_scale: torch.Tensor,
-                  step: float, g: torch.Tensor, k: int) -> torch.Tensor:
+                  step: float, g: torch.Tensor, k: int, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     g = _rows(g)
     P, N = codes.shape
     d = torch.empty(P, dtype=torch.float32, device=codes.device)
     _call("amoe_row_dot_codes", ptr(codes), ptr(col_scale), ptr(row_expert), ptr(row_scale), float(step), ptr(g),
-          dtype_code(g), g.stride(0), P, k, N, ptr(d), stream_ptr())
+          dtype_code(g), g.stride(0), P, k, N, ptr(d), ptr(row_index), stream_ptr())
     return d
 
 

@@ -83,7 +83,8 @@ template <typename TY>
 __global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
                                      const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
                                      float step, const float* __restrict__ w, int64_t T, int k, int N,
-                                     TY* __restrict__ y, int64_t y_stride, int vec) {
+                                     TY* __restrict__ y, int64_t y_stride, int vec,
+                                     const int32_t* __restrict__ row_index) {
   const int nq = (N + 3) / 4;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * nq) return;
@@ -95,10 +96,11 @@ __global__ void combine_codes_kernel(const int8_t* __restrict__ codes, const flo
   for (int j = 0; j < k; ++j) {
     const int64_t s = t * k + j;
     const float ws = w ? w[s] : 1.f;
-    const float rm = row_mult ? row_mult[s] : 1.f;
+    const int64_t rr = row_index ? row_index[s] : s;       // where the slot's row (codes, row_mult) is kept
+    const float rm = row_mult ? row_mult[rr] : 1.f;
     const int e = raw_sel[s];
     float cd[4], cs[4];
-    ld4_codes(codes + s * N + n0, vec != 0, valid, cd);
+    ld4_codes(codes + rr * N + n0, vec != 0, valid, cd);
     ld4<float>(col_scale + static_cast<int64_t>(e) * N + n0, vec != 0, valid, cs);
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -115,7 +117,7 @@ template <typename TY>
 __global__ void combine_codes16_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
                                        const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
                                        float step, const float* __restrict__ w, int64_t T, int k, int N,
-                                       TY* __restrict__ y, int64_t y_stride) {
+                                       TY* __restrict__ y, int64_t y_stride, const int32_t* __restrict__ row_index) {
   const int ng = N / 16;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * ng) return;
@@ -128,9 +130,10 @@ __global__ void combine_codes16_kernel(const int8_t* __restrict__ codes, const f
   for (int j = 0; j < k; ++j) {
     const int64_t s = t * k + j;
     const float ws = w ? w[s] : 1.f;
-    const float rm = row_mult ? row_mult[s] : 1.f;
+    const int64_t rr = row_index ? row_index[s] : s;
+    const float rm = row_mult ? row_mult[rr] : 1.f;
     const int e = raw_sel[s];
-    const uint4 cd = __ldg(reinterpret_cast<const uint4*>(codes + s * N + n0));
+    const uint4 cd = __ldg(reinterpret_cast<const uint4*>(codes + rr * N + n0));
     const float4* csp = reinterpret_cast<const float4*>(col_scale + static_cast<int64_t>(e) * N + n0);
     const uint32_t cw[4] = {cd.x, cd.y, cd.z, cd.w};
 #pragma unroll
@@ -181,13 +184,14 @@ template <typename TG>
 __global__ void row_dot_codes_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
                                      const int32_t* __restrict__ row_expert, const float* __restrict__ row_scale,
                                      float step, const TG* __restrict__ g, int64_t g_stride, int64_t P, int k, int N,
-                                     float* __restrict__ d, int vec) {
+                                     float* __restrict__ d, int vec, const int32_t* __restrict__ row_index) {
   const int lane = threadIdx.x & 31;
   const int64_t s = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (s >= P) return;
-  const int8_t* r = codes + s * N;
+  const int64_t rr = row_index ? row_index[s] : s;        // row of codes / row_scale; row_expert stays by slot
+  const int8_t* r = codes + rr * N;
   const float* cs = col_scale + static_cast<int64_t>(row_expert[s]) * N;
-  const float rs = row_scale ? row_scale[s] : 1.f;
+  const float rs = row_scale ? row_scale[rr] : 1.f;
   const TG* gr = g + (s / k) * g_stride;
   const int nq = (N + 3) / 4;
   float acc = 0.f;
@@ -414,7 +418,7 @@ int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const i
 
 int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_t* raw_sel, const float* row_mult,
                        float step, const float* w, int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype,
-                       int64_t y_stride, amoe_stream_t stream_) {
+                       int64_t y_stride, const int32_t* row_index, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(codes && col_scale && raw_sel && y, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(T > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
@@ -425,20 +429,20 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
     const unsigned b16 = blocks_for(T * (N / 16), 128);
     if (y_dtype == AMOE_F32)
       combine_codes16_kernel<float><<<b16, 128, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
-                                                             reinterpret_cast<float*>(y), y_stride);
+                                                             reinterpret_cast<float*>(y), y_stride, row_index);
     else
       combine_codes16_kernel<__nv_bfloat16><<<b16, 128, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
-                                                                     reinterpret_cast<__nv_bfloat16*>(y), y_stride);
+                                                                     reinterpret_cast<__nv_bfloat16*>(y), y_stride, row_index);
     AMOE_LAUNCH_CHECK("combine_codes16");
     return AMOE_OK;
   }
   if (y_dtype == AMOE_F32)
     combine_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
-                                                            reinterpret_cast<float*>(y), y_stride, vec);
+                                                            reinterpret_cast<float*>(y), y_stride, vec, row_index);
   else if (y_dtype == AMOE_BF16)
     combine_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T,
                                                                     k, N, reinterpret_cast<__nv_bfloat16*>(y),
-                                                                    y_stride, vec);
+                                                                    y_stride, vec, row_index);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("combine_codes");
@@ -475,7 +479,7 @@ int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const i
 
 int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_t* row_expert, const float* row_scale,
                        float step, const void* g, int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N,
-                       float* d, amoe_stream_t stream_) {
+                       float* d, const int32_t* row_index, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(codes && col_scale && row_expert && g && d, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
@@ -483,11 +487,11 @@ int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_
   const int vec = (N % 4 == 0) && (g_stride % 4 == 0) && al16(g) && al16(col_scale) && al16(codes);
   if (g_dtype == AMOE_F32)
     row_dot_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
-                                                            reinterpret_cast<const float*>(g), g_stride, P, k, N, d, vec);
+                                                            reinterpret_cast<const float*>(g), g_stride, P, k, N, d, vec, row_index);
   else if (g_dtype == AMOE_BF16)
     row_dot_codes_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
                                                                     reinterpret_cast<const __nv_bfloat16*>(g), g_stride,
-                                                                    P, k, N, d, vec);
+                                                                    P, k, N, d, vec, row_index);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("row_dot_codes");

@@ -285,7 +285,8 @@ int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
  *   row(s) = row_index[s] if row_index is given (rows kept in another order, e.g. expert-sorted), else s.  Replaces the
  *   gate-weighted reduction (cvmm.py:757-759), its backward (cvmm.py:888) and the sum over k of
  *   the up-projection's input gradient (cvmm.py:890-891).  With `codes` given instead of `res`
- *   the rows are rebuilt from ADC codes: codes*step*col_scale[raw_sel[slot],:]*row_mult[slot].
+ *   the rows are rebuilt from ADC codes: codes*step*col_scale[raw_sel[slot],:]*row_mult[row(slot)]; codes and
+ *   row_mult are indexed by row(slot) (row_index, or the slot itself), raw_sel / row_expert by slot.
  * amoe_row_dot: d[s] = res[row(s),:] . g[s/k,:]  (gate gradient, cvmm.py:889).
  * amoe_ir_grad_reduce: per-expert sum of the per-slot input-range gradients plus the decay term
  *   decay*ir_e*count_e*[keep_count/total > min_percentage] (cvmm.py:872-878 followed by autograd's
@@ -295,14 +296,14 @@ int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const i
                  int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream);
 int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_t* raw_sel, const float* row_mult,
                        float step, const float* w, int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype,
-                       int64_t y_stride, amoe_stream_t stream);
+                       int64_t y_stride, const int32_t* row_index, amoe_stream_t stream);
 int amoe_row_dot(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const void* g,
                  int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N, float* d, amoe_stream_t stream);
 /* amoe_row_dot_codes: the same gate gradient with the rows given as ADC codes:
  *   d[s] = sum_n ((codes[s,n]*step)*col_scale[row_expert[s],n])*row_scale[s] * g[s/k,n]. */
 int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_t* row_expert, const float* row_scale,
                        float step, const void* g, int32_t g_dtype, int64_t g_stride, int64_t P, int32_t k, int32_t N,
-                       float* d, amoe_stream_t stream);
+                       float* d, const int32_t* row_index, amoe_stream_t stream);
 int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range,
                         int32_t E, float decay, float min_percentage, const unsigned long long* keep_count,
                         double total_elements, float* out, amoe_stream_t stream);
