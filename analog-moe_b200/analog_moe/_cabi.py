@@ -60,6 +60,7 @@ class CvmmArgs(C.Structure):
         ("row_scale", vp), ("ir_grad", vp), ("ir_grad_relative", C.c_int32), ("ir_grad_scale", C.c_float),
         ("keep_count", vp),
         ("a_cache_hi", vp), ("a_cache_lo", vp), ("a_cache_scale", vp), ("out_cache_hi", vp), ("out_cache_lo", vp), ("cache_rows", C.c_int64),
+        ("a_tile_hi", vp), ("a_tile_lo", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]
 

@@ -211,11 +211,14 @@ class _FusedAnalogStep(torch.autograd.Function):
         ops.set_tag("up")
         grad_x = irs_up = dxr = None
         if need_x or need_ir:
+            # the hidden gradient already exists as bf16 hi/lo tiles (the dW operand the kernel above wrote): TMA feeds
+            # it, no gather/convert prologue
+            tiles = dhc if (dhc is not None and Fh % 64 == 0) else None
             dxr, irs_up = ops.cvmm_dx(dh, slot_index, slot_index, offsets, pw_up, precision, P=P, dst_rows=P,
                                       x_ref=x2 if has_ir else None, x_ref_row=token_index if has_ir else None,
                                       ir=ir_up, ir_by_expert=True, want_ir_grad=has_ir, relative=relative,
                                       grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
-                                      out_dtype=x2.dtype)
+                                      out_dtype=x2.dtype, a_tiles=tiles)
         grad_keys = None
         main, side = torch.cuda.current_stream(), ops.side_stream(x2.device)
         forked = cached and (need_values or need_keys)

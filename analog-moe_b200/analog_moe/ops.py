@@ -353,7 +353,9 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             relative: bool = True, grad_scale: float = 1.0, keep_count: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
             ir_by_expert: bool = False, x_ref_relu: bool = False, a_cache: Optional["OperandCache"] = None,
-            out_cache: Optional["OperandCache"] = None):
+            out_cache: Optional["OperandCache"] = None, a_tiles: Optional["OperandCache"] = None):
+    """`a_tiles`: the A operand as an operand cache written by an earlier kernel (TMA-fed, no gather); g2 then only
+    gives dtype and device."""
     g2 = _rows(g2)
     dev = g2.device
     out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev)
@@ -373,6 +375,9 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     if out_cache is not None:
         a.out_cache_hi, a.out_cache_lo = ptr(out_cache.hi), ptr(out_cache.lo)
         a.cache_rows = out_cache.rows
+    if a_tiles is not None:
+        a.a_tile_hi, a.a_tile_lo = ptr(a_tiles.hi), ptr(a_tiles.lo)
+        a.cache_rows = a_tiles.rows
     a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
     if x_ref is not None:
         x_ref = _rows(x_ref)

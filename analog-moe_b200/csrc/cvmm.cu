@@ -11,10 +11,11 @@ int check_common(const amoe_cvmm_args* a) {
   AMOE_REQUIRE(a != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->P > 0 && a->E > 0 && a->K > 0 && a->N > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(a->P < (int64_t{1} << 31) && a->E <= 65535, AMOE_ERR_BAD_SHAPE);
-  AMOE_REQUIRE(a->expert_offsets && a->a && a->a_row && a->dst_row && (a->out || a->out_codes), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(a->expert_offsets && a->dst_row && (a->out || a->out_codes), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE((a->a && a->a_row) || (a->a_tile_hi && a->precision != AMOE_PREC_FP32_SIMT), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->a_dtype == AMOE_F32 || a->a_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->out_dtype == AMOE_F32 || a->out_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
-  AMOE_REQUIRE(a->a_rows > 0 && a->dst_rows > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE((a->a_rows > 0 || a->a_tile_hi) && a->dst_rows > 0, AMOE_ERR_BAD_SHAPE);
   if (a->precision == AMOE_PREC_FP32_SIMT) {
     AMOE_REQUIRE(a->w != nullptr, AMOE_ERR_NULL_POINTER);
     AMOE_REQUIRE(a->w_dtype == AMOE_F32 || a->w_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);

@@ -99,6 +99,8 @@ struct TcParams {
   const float* ir; const float* a_absmax; float inp_res; int vec_ok;
   // optional operand cache: split(clamp(a, ir) * cache_scale[a_row[i]]) by padded tile row, [tiles*128, cache_stride]
   __nv_bfloat16* cache_hi; __nv_bfloat16* cache_lo; int64_t cache_stride /* rows of the cache */; const float* cache_scale;
+  int a_tma;            // the A operand exists as prepared bf16 tiles (an operand cache written by an earlier kernel):
+                        // TMA loads it, there is no prologue and every worker warp runs the epilogue
   EpiParams epi;
 };
 
@@ -440,7 +442,8 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
 
 template <int DAC, bool A_F32, int EPI>
 __global__ void __launch_bounds__(kFwdThreads, 1)
-cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo, TcParams p) {
+cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
+               const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo, TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ RowMeta s_meta[kMaxProdGroups][kBM];
   __shared__ float s_cscale[kBM];
@@ -449,7 +452,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_prod = kWorkerWarps - p.n_epi;
-  setup_cta(sm, p.stages, p.tmem_cols, n_prod / p.prod_groups, p.n_epi, n_prod, p.n_epi);
+  setup_cta(sm, p.stages, p.tmem_cols, n_prod > 0 ? n_prod / p.prod_groups : 1, p.n_epi, n_prod > 0 ? n_prod : 1, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
 
@@ -458,6 +461,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     if (lane == 0) {
       tma_prefetch_desc(&tmap_hi);
       if (p.b_split) tma_prefetch_desc(&tmap_lo);
+      if (p.a_tma) { tma_prefetch_desc(&tmap_a_hi); if (p.a_split) tma_prefetch_desc(&tmap_a_lo); }
       TileIter ti(p.offsets, p.E);
       RingPos rp(p.stages);
       bool alive = true;
@@ -470,7 +474,13 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             const uint32_t ph = rp.ph;
             if (!mbar_wait(bar_empty(sm.bars, s), ph ^ 1u, sm.abort_flag, status, 1, 64)) { alive = false; break; }
             const uint32_t dst = sm.base_u32 + s * p.stage_bytes + p.a_bytes;
-            mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (p.b_split ? 2u : 1u));
+            mbar_arrive_expect_tx(bar_full_b(sm.bars, s), p.b_bytes * (p.b_split ? 2u : 1u) + (p.a_tma ? p.a_bytes : 0u));
+            if (p.a_tma) {
+              // A tile: 128 padded tile rows x 64 columns of block kc of the cache (K-major, 128-byte swizzle)
+              const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
+              tma_load_3d(sa, &tmap_a_hi, bar_full_b(sm.bars, s), 0, static_cast<int>(t * kBM), kc);
+              if (p.a_split) tma_load_3d(sa + kATile, &tmap_a_lo, bar_full_b(sm.bars, s), 0, static_cast<int>(t * kBM), kc);
+            }
             tma_load_3d(dst, &tmap_hi, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
             if (p.b_split) tma_load_3d(dst + p.b_bytes, &tmap_lo, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
           }
@@ -498,7 +508,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             const int s = rp.s;
             const uint32_t ph = rp.ph;
             TL(1, it, 0);
-            if (!mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
+            if (!p.a_tma && !mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
             TL(1, it, 1);
             if (!mbar_wait(bar_full_b(sm.bars, s), ph, sm.abort_flag, status, 4)) { alive = false; break; }
             TL(1, it, 2);
@@ -634,7 +644,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         }
       }
     }
-  } else {
+  } else if (!p.a_tma) {
     // ---------------------------------------------------------------- operand prologue (A tiles)
     const int np_all = n_prod * 32;
     const int pt_all = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np_all-1
@@ -1406,6 +1416,13 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   p.cache_hi = reinterpret_cast<__nv_bfloat16*>(a->a_cache_hi);
   p.cache_lo = reinterpret_cast<__nv_bfloat16*>(a->a_cache_lo);
   p.cache_stride = a->cache_rows; p.cache_scale = a->a_cache_scale;
+  p.a_tma = a->a_tile_hi != nullptr;
+  if (p.a_tma) {
+    AMOE_REQUIRE(p.Kc % kBK == 0 && aligned16(a->a_tile_hi) && aligned16(a->a_tile_lo) && !p.cache_hi, AMOE_ERR_BAD_SHAPE);
+    AMOE_REQUIRE(a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
+    a_split = a->a_tile_lo != nullptr;
+    p.a_split = a_split;
+  }
   AMOE_REQUIRE(!(p.cache_hi || p.epi.out_cache_hi) || a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!p.cache_hi || (p.Kc % 8 == 0 && aligned16(p.cache_hi) && aligned16(p.cache_lo)), AMOE_ERR_BAD_SHAPE);
 
@@ -1433,10 +1450,19 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
+    if (p.a_tma) {
+      // no prologue: the epilogue groups that share the tile's 16-column chunks most evenly (fewest warps on a tie)
+      const int chunks = p.BN / 16;
+      int best_per = 1 << 30;
+      for (int ne = 4; ne <= kWorkerWarps; ne += 4) {
+        const int per = (chunks + ne / 4 - 1) / (ne / 4);
+        if (per < best_per) { best_per = per; p.n_epi = ne; }
+      }
+    }
   }
   // two prologue groups on alternate stages need a ring with an even number of stages (a stage then always
   // belongs to the same group) and enough stages per tile to alternate on
-  if (p.stages >= 4 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr) {
+  if (!p.a_tma && p.stages >= 4 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr) {
     p.prod_groups = 2;
     p.stages &= ~1;
   }
@@ -1458,6 +1484,16 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
                             static_cast<uint64_t>(a->E), kBK, static_cast<uint32_t>(p.BN));
     if (s != AMOE_OK) return s;
   }
+  CUtensorMap ma_hi = m_hi, ma_lo = m_hi;
+  if (p.a_tma) {
+    s = encode_tmap_bf16_3d(&ma_hi, a->a_tile_hi, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>(p.Kc / kBK), 64, kBM);
+    if (s != AMOE_OK) return s;
+    ma_lo = ma_hi;
+    if (a_split) {
+      s = encode_tmap_bf16_3d(&ma_lo, a->a_tile_lo, 64, static_cast<uint64_t>(a->cache_rows), static_cast<uint64_t>(p.Kc / kBK), 64, kBM);
+      if (s != AMOE_OK) return s;
+    }
+  }
   const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra + cs_bytes;
   const int64_t max_tiles = (a->P + kBM - 1) / kBM + a->E;
   const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
@@ -1471,7 +1507,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
 #define AMOE_LAUNCH_TC(DAC, F32, EPI)                                                                                  \
   do {                                                                                                                 \
     AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<DAC, F32, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    cvmm_tc_kernel<DAC, F32, EPI><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, p);                                 \
+    cvmm_tc_kernel<DAC, F32, EPI><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, ma_hi, ma_lo, p);                                 \
   } while (0)
 #define AMOE_LAUNCH_TC_DT(DAC, EPI) \
   do { if (f32) AMOE_LAUNCH_TC(DAC, true, EPI); else AMOE_LAUNCH_TC(DAC, false, EPI); } while (0)

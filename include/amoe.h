@@ -231,6 +231,11 @@ typedef struct amoe_cvmm_args {
   void* a_cache_hi; void* a_cache_lo; const float* a_cache_scale;
   void* out_cache_hi; void* out_cache_lo;
   int64_t cache_rows;
+  /* The A operand itself as such a cache (bf16 hi, optional lo; cols % 64 == 0): when a_tile_hi is given the kernel
+   * loads A through TMA, `a`/`a_row`/ir/a_absmax/inp_res are not used (whatever DAC the values need is already in
+   * them) and no a_cache_* can be written.  amoe_cvmm_dx of an up-projection takes the out_cache of the
+   * down-projection's amoe_cvmm_dx this way. */
+  const void* a_tile_hi; const void* a_tile_lo;
   /* plumbing */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
   int32_t* dev_status;            /* int32[4] or NULL */
