@@ -1,21 +1,23 @@
-"""Expert-parallel analog sigma-MoE layer: experts block-partitioned over the ranks of one node,
-tokens data-parallel, one all-to-all of routed rows each way (NCCL over NVLink).
+"""Expert-parallel analog sigma-MoE layer: experts block-partitioned over the ranks of one node, tokens
+data-parallel, routed rows exchanged once each way over NVLink.
 
-The reference is single-GPU; this module is new.  Per rank and step:
+The reference is single-GPU; this module is new.  Per rank and step (`_ExpertParallelStep`, one autograd node):
 
-  route locally (global expert ids)          amoe_select_sort
-  exchange per-expert counts                  all_to_all_single of [G, E/G] int32 + ONE host read
-  gather rows in expert-sorted order          amoe_ep_pack        (contiguous block per destination rank)
-  dispatch                                    all_to_all_single   (rows land in local HBM)
-  up-projection -> activation -> down         the same CVMM kernels on the rank's experts
-  return                                      all_to_all_single
-  gate-weighted sum over k, reading the       amoe_combine with a row index
-  sorted rows through the inverse permutation
+  route locally (global expert ids)           amoe_router_logits, amoe_select_sort
+  all-gather of the per-expert counts         NCCL, [G, E/G] int32 per rank
+  plan on the device                          amoe_ep_plan, amoe_ep_local_plan_dev   (no host read)
+  rows to their owners                        amoe_ep_put: stores into the owner's buffer (symmetric memory)
+  up-projection -> ReLU -> down-projection    the single-GPU kernels on the rank's experts, rows addressed
+                                              through local_order; operand caches for the weight gradients
+  rows back (ADC codes + one scale per row)   amoe_ep_put_back
+  gate-weighted sum over k                    amoe_combine_codes through the inverse permutation
 
-dW and the input-range gradients need no collective: every slot of an expert arrives at its owner.
-The exchange plan (split sizes and the regrouping of received rows by local expert) is plain host
-arithmetic on the count matrix, so it is tested on CPU ranks over gloo.  Kernels only ever read
-local memory.
+and the mirror image in the backward pass.  dW and the input-range gradients need no collective: every slot of
+an expert arrives at its owner.  Ordering between ranks comes from small NCCL collectives placed between the
+stores; no kernel waits on another rank and every load is local.  Without symmetric memory (or with
+AMOE_EP_NCCL=1) the rows travel by `all_to_all_single` with split sizes taken from one host read per step
+(`step_plan`); `forward_composed` keeps the composition around `CVMM.apply` for other activations.  The host-side
+plans are plain arithmetic on the count matrix and are tested on CPU ranks over gloo.
 """
 from __future__ import annotations
 

@@ -10,18 +10,26 @@
 //                   columns, then noise / ADC / rescale (forward) or clip mask / input-range
 //                   gradient (backward), stores
 //       prologue:   gather the tile's rows, clamp / scale / quantise (DAC), convert to bf16 (hi, and
-//                   lo when the operand is split) and write the swizzled K-major A tile
+//                   lo when the operand is split) and write the swizzled K-major A tile; two groups of
+//                   prologue warps take alternate ring stages; optionally the clamped rows are also
+//                   written out as the bf16 operand cache of the later weight gradient
+//   When the A operand already exists as such a cache (the up-projection's dX reads the hidden
+//   gradient the down-projection's dX left behind) warp 0 loads it by TMA and there is no prologue.
 //   A and B tiles travel through a ring of shared-memory stages guarded by mbarriers; the
 //   accumulator is double-buffered in TMEM so the epilogue of one tile overlaps the MMAs of the next.
 //   Split precision issues up to three MMAs per k-step: hi*hi + hi*lo + lo*hi.
 //   The kernel is instantiated per DAC mode, input type and epilogue family, and rarely taken paths
-//   (exact division chains, Philox rounds, unaligned loads) are out-of-line calls: the hot loops of
-//   the three roles must stay resident in the instruction cache together.
+//   (unaligned loads, the general four-column epilogue) are out-of-line or separate instantiations:
+//   the hot loops of the three roles must stay resident in the instruction cache together.
 //
-// dw_tc_mn_kernel (weight gradient)
-//   Same structure; the contraction runs over the slots of one expert, both operands are produced by
-//   the prologue warps as MN-major tiles, and one CTA owns each (expert, 128 x BN) output tile, so
-//   there are no atomics.
+// dw_tc_tma_kernel (weight gradient from the operand caches)
+//   Six warps: TMA loads of both MN-major operands (64 slots x 64 columns boxes), tcgen05.mma, four
+//   warps draining TMEM.  One work item = (segment of one expert's padded rows, two output tiles);
+//   partial tiles are summed in segment order by dw_reduce_kernel: no atomics.
+//
+// dw_tc_mn_kernel (weight gradient from fp32 / bf16 rows)
+//   The stand-alone variant: both operands are gathered, clamped / scaled and converted by 26
+//   prologue warps into the same MN-major tiles.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records AMOE_ERR_WAIT_LIMIT in the status
 // word, stops issuing work, drains and frees its TMEM.
