@@ -4,8 +4,9 @@
 (`sigma_moe.moe_layer.SigmaMoELayer`): same constructor keywords and attributes, `forward`
 returning `(out, aux)` and calling `compute_scores` then `cvmm_wrapper(scores, sel, self.values)`
 (contract: reference moe_layer_aihwkit_lightning.py:220-233, 261-276, 384-410;
-tests/test_moe_layer_aihwkit.py:60-109).  The router matmul stays a torch Linear; everything from
-the gate logits onward runs in the CUDA library.
+tests/test_moe_layer_aihwkit.py:60-109).  In the composed path the router matmul is a torch Linear and
+everything from the gate logits onward runs in the CUDA library; the single-node step of the analog layer
+(`_FusedAnalogStep`) runs the router in the library as well.
 
 `AnalogSigmaMoELayer` mirrors the non-traceable `AnalogSigmaMoELayerAIHWKITLightning`
 (moe_layer_aihwkit_lightning.py:134-543): per-expert learnable input ranges [2, E], DAC, weight
