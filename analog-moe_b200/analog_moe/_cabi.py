@@ -61,6 +61,7 @@ class CvmmArgs(C.Structure):
         ("keep_count", vp),
         ("a_cache_hi", vp), ("a_cache_lo", vp), ("a_cache_scale", vp), ("out_cache_hi", vp), ("out_cache_lo", vp), ("cache_rows", C.c_int64),
         ("a_tile_hi", vp), ("a_tile_lo", vp),
+        ("next_ir", vp), ("next_inp_res", C.c_float), ("next_codes", vp), ("out_cache_scale", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
     ]
 

@@ -133,17 +133,28 @@ class _FusedAnalogStep(torch.autograd.Function):
         split = precision == ops.A.PREC_SPLIT
         xc = ops.OperandCache.empty(P, E, D, split, x.device) if cached else None
         hs = ops.OperandCache.empty(P, E, Fh, split, x.device) if cached else None
+        # With input ranges and a quantising DAC the up-projection's epilogue also leaves the hidden rows as the
+        # down-projection wants them (integer DAC codes as bf16 tiles, and gate * clamp(h) for its weight gradient),
+        # so that the down-projection loads its A operand by TMA and runs no prologue.
+        gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
+        tiles = has_ir and inp_res >= 1.0 / 256.0 and Fh % 64 == 0 and precision != ops.A.PREC_FP32_SIMT and \
+            layer.hidden_tiles          # (codes up to 256 in magnitude are exact in one bf16 term)
+        hq = ops.OperandCache.empty(P, E, Fh, False, x.device) if tiles else None
+        nxt = dict(next_ir=ir_all[1], next_inp_res=inp_res, next_codes=hq, out_cache=hs,
+                   out_cache_scale=gate.reshape(-1) if hs is not None else None) if tiles else {}
         h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
                             ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
-                            out_bound=out_bound, out_relu=True, a_cache=xc, **nz)
+                            out_bound=out_bound, out_relu=True, a_cache=xc, **nxt, **nz)
         # ---- down-projection and the gate-weighted sum over k
         ops.set_tag("down")
         nz = nz_dn
         ir_dn = ir_all[1] if has_ir else None
         am_dn = None if has_ir else ops.row_absmax(h)
-        # the composition hands the gate over in the activation dtype (rounded for bf16 layers)
-        gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
-        cache_kw = dict(a_cache=hs, a_cache_scale=gate.reshape(-1)) if cached else {}
+        # (the composition hands the gate over in the activation dtype: rounded for bf16 layers)
+        if tiles:
+            cache_kw = dict(a_tiles=hq)
+        else:
+            cache_kw = dict(a_cache=hs, a_cache_scale=gate.reshape(-1)) if cached else {}
         adc_step = ops.adc_step(out_res, out_bound) if adc_on else 0.0
         res = codes = row_scale = row_expert = None
         if adc_on:
@@ -364,6 +375,7 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.register_buffer("_aux_zero", torch.zeros(()), persistent=False)
         self.fused = True          # one autograd node for the whole layer when the configuration allows it
         self.operand_caches = True  # forward / dX kernels leave bf16 copies of the dW operands (fused path)
+        self.hidden_tiles = True    # the up-projection leaves the hidden rows as the down-projection's A tiles
         self._noise_calls = 0
         ir = self.rpu_config.pre_post.input_range
         self.input_range = None

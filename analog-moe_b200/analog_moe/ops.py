@@ -306,7 +306,10 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
              out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
              want_out: bool = True, row_meta: Optional[dict] = None, ir_by_expert: bool = False,
              out_relu: bool = False, a_cache: Optional["OperandCache"] = None,
-             a_cache_scale: Optional[torch.Tensor] = None):
+             a_cache_scale: Optional[torch.Tensor] = None, a_tiles: Optional["OperandCache"] = None,
+             next_ir: Optional[torch.Tensor] = None, next_inp_res: float = -1.0,
+             next_codes: Optional["OperandCache"] = None, out_cache: Optional["OperandCache"] = None,
+             out_cache_scale: Optional[torch.Tensor] = None):
     """Returns (out or None, codes or None).  `row_meta` (a dict) receives `row_scale` [dst_rows] and
     `row_expert` [dst_rows], from which, with the codes, the output rows can be rebuilt."""
     x2 = _rows(x2)
@@ -327,6 +330,17 @@ def cvmm_fwd(x2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offse
     if a_cache is not None:
         a.a_cache_hi, a.a_cache_lo, a.a_cache_scale = ptr(a_cache.hi), ptr(a_cache.lo), ptr(a_cache_scale)
         a.cache_rows = a_cache.rows
+    if a_tiles is not None:          # the A operand as tiles an earlier kernel prepared (x2 only gives dtype and device)
+        a.a_tile_hi, a.a_tile_lo = ptr(a_tiles.hi), ptr(a_tiles.lo)
+        a.cache_rows = a_tiles.rows
+    if next_codes is not None or out_cache is not None:
+        a.next_ir, a.next_inp_res = ptr(next_ir), float(next_inp_res)
+        if next_codes is not None:
+            a.next_codes = ptr(next_codes.hi)
+            a.cache_rows = next_codes.rows
+        if out_cache is not None:
+            a.out_cache_hi, a.out_cache_lo, a.out_cache_scale = ptr(out_cache.hi), ptr(out_cache.lo), ptr(out_cache_scale)
+            a.cache_rows = out_cache.rows
     if noise is not None:
         noise = noise.reshape(-1, pw.N).float().contiguous()
         assert noise.shape[0] == dst_rows

@@ -81,7 +81,15 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.vec4 = (a->N % 4 == 0) && al16(a->col_scale) && al16(a->col_inv_scale) && al16(a->noise) && al16(a->out) &&
            (a->out_stride % 4 == 0) && al16(a->out_codes);
   AMOE_REQUIRE(!(a->a_cache_hi || a->out_cache_hi) || a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
-  AMOE_REQUIRE(!a->out_cache_hi, AMOE_ERR_UNSUPPORTED);
+  e.out_cache_hi = reinterpret_cast<__nv_bfloat16*>(a->out_cache_hi);
+  e.out_cache_lo = reinterpret_cast<__nv_bfloat16*>(a->out_cache_lo);
+  e.out_cache_stride = a->cache_rows;
+  e.next_ir = a->next_ir; e.next_res = a->next_inp_res; e.next_codes = reinterpret_cast<__nv_bfloat16*>(a->next_codes);
+  e.out_cache_scale = a->out_cache_scale;
+  AMOE_REQUIRE(!(a->out_cache_hi || a->next_codes) || (a->N % 16 == 0 && al16(a->out_cache_hi) && al16(a->out_cache_lo) && al16(a->next_codes)),
+               AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(!a->next_codes || (a->next_ir && a->next_inp_res > 0.f && a->precision != AMOE_PREC_FP32_SIMT && a->out), AMOE_ERR_UNSUPPORTED);
+  AMOE_REQUIRE(!a->out_cache_hi || a->out, AMOE_ERR_UNSUPPORTED);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, false, e, stream);
   return launch_cvmm_tc(a, false, e, stream);
 }

@@ -33,6 +33,8 @@ struct EpiParams {
   unsigned long long* keep_count;
   // input gradient, optional: the result rows once more as bf16 hi (+ lo) terms, by padded tile row
   __nv_bfloat16* out_cache_hi; __nv_bfloat16* out_cache_lo; int64_t out_cache_stride;
+  // forward, optional: the result as the next projection's operands (see amoe_cvmm_args)
+  const float* next_ir; float next_res; __nv_bfloat16* next_codes; const float* out_cache_scale;
   int32_t* status;
 };
 
@@ -48,6 +50,7 @@ struct RowCtx {
   unsigned keep;
   uint32_t noise_offset;   // Philox offset in effect (argument + 8 * device step counter)
   int64_t pad_row;         // tile index * 128 + row in tile (row of the operand caches)
+  float next_ir, next_rcp; // input range of the next projection for this row's expert and its reciprocal
 };
 
 __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, int e, bool in_range) {
@@ -57,6 +60,8 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0;
   c.noise_offset = p.offset;
   c.pad_row = 0;
+  c.next_ir = 1.f; c.next_rcp = 1.f;
+  if (!p.is_dx && p.next_ir) { c.next_ir = p.next_ir[e]; c.next_rcp = __frcp_rn(c.next_ir); }
   if (p.noise_std > 0.f && p.step_dev) c.noise_offset += static_cast<uint32_t>(*p.step_dev) * 8u;
   if (!in_range) return c;
   c.dst = p.dst_row[i];

@@ -107,6 +107,7 @@ struct TcParams {
   const float* ir; const float* a_absmax; float inp_res; int vec_ok;
   // optional operand cache: split(clamp(a, ir) * cache_scale[a_row[i]]) by padded tile row, [tiles*128, cache_stride]
   __nv_bfloat16* cache_hi; __nv_bfloat16* cache_lo; int64_t cache_stride /* rows of the cache */; const float* cache_scale;
+  int cw8;              // codes-only forward epilogue in 8-column chunks (more, narrower chunks for more warps)
   int a_tma;            // the A operand exists as prepared bf16 tiles (an operand cache written by an earlier kernel):
                         // TMA loads it, there is no prologue and every worker warp runs the epilogue
   EpiParams epi;
@@ -332,15 +333,18 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 // kValue = false: only the ADC codes leave the kernel, the dequantised values are not formed.
 // The ADC code rint(x) is taken as (x + 1.5*2^23) - 1.5*2^23 (exact round-to-nearest-even for |x| < 2^22; codes are
 // at most 127 in magnitude), whose low mantissa byte is the code in two's complement.
-template <bool kValue>
+// NQ = quads (four columns each) of the chunk: 4, or 2 in the codes-only variant, whose narrower chunks spread over
+// more epilogue warps.
+template <bool kValue, int NQ = 4>
 __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
-                                              float v[16], const float* cs, const float* cis, int lane) {
+                                              float* v, const float* cs, const float* cis, int lane) {
+  static_assert(NQ == 4 || !kValue, "the value path stores 16-column chunks");
   constexpr float kMagic = 12582912.f;
   const bool noise = p.noise_std > 0.f, adc = p.adc.on;
   const float post = c.absmax * c.ir;
   uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-  for (int qd = 0; qd < 4; ++qd) {
+  for (int qd = 0; qd < NQ; ++qd) {
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
     if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
@@ -372,14 +376,54 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
   if (p.out_codes && c.valid) {
     // 16 codes of the row; a row starts on a 16-byte boundary only if n_out is a multiple of 16
     int8_t* dstc = p.out_codes + c.dst * p.n_out + n0;
-    if ((p.n_out & 15) == 0) {
+    if (NQ == 2) {
+      *reinterpret_cast<uint2*>(dstc) = make_uint2(pk[0], pk[1]);        // n_out % 8 == 0 in this variant
+    } else if ((p.n_out & 15) == 0) {
       *reinterpret_cast<uint4*>(dstc) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     } else {
 #pragma unroll
       for (int qd = 0; qd < 4; ++qd) *reinterpret_cast<uint32_t*>(dstc + 4 * qd) = pk[qd];   // n_out % 4 == 0
     }
   }
-  if (kValue) store16_t(p, qr, n0, v, lane);
+  if constexpr (kValue && NQ == 4) if (p.next_codes || p.out_cache_hi) {
+    // the row once more as the next projection's operands (padded tile row, [64-column block][row][64]): DAC codes
+    // for its forward pass, clamped and scaled bf16 hi (+ lo) terms for its weight gradient
+    const int64_t co = (((n0 >> 6) * p.out_cache_stride + c.pad_row) << 6) + (n0 & 63);
+    const float rcp_res = quant_rcp(p.next_res);
+    const float sc = (p.out_cache_scale && c.valid) ? p.out_cache_scale[c.dst] : 1.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float hc[8];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        float t = c.valid ? v[8 * half + x] : 0.f;
+        if (p.out_dtype == AMOE_BF16) t = __bfloat162float(__float2bfloat16_rn(t));   // what the next kernel would read
+        hc[x] = p.next_ir ? clamp_ir(t, c.next_ir) : t;
+      }
+      if (p.next_codes) {
+        uint32_t q[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x)
+          q[x] = cvt_bf16x2(dac_code_clamped(hc[2 * x], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res),
+                            dac_code_clamped(hc[2 * x + 1], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res));
+        *reinterpret_cast<uint4*>(p.next_codes + co + 8 * half) = make_uint4(q[0], q[1], q[2], q[3]);
+      }
+      if (p.out_cache_hi) {
+        uint32_t h[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(hc[2 * x] * sc, hc[2 * x + 1] * sc);
+        *reinterpret_cast<uint4*>(p.out_cache_hi + co + 8 * half) = make_uint4(h[0], h[1], h[2], h[3]);
+        if (p.out_cache_lo) {
+          uint32_t l[4];
+#pragma unroll
+          for (int x = 0; x < 4; ++x)
+            l[x] = cvt_bf16x2(hc[2 * x] * sc - __uint_as_float(h[x] << 16), hc[2 * x + 1] * sc - __uint_as_float(h[x] & 0xffff0000u));
+          *reinterpret_cast<uint4*>(p.out_cache_lo + co + 8 * half) = make_uint4(l[0], l[1], l[2], l[3]);
+        }
+      }
+    }
+  }
+  if constexpr (kValue && NQ == 4) store16_t(p, qr, n0, v, lane);
 }
 
 __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
@@ -548,7 +592,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     const int grp = ew >> 2;
     const int groups = p.n_epi >> 2;
     const int r = q * 32 + lane;
-    const int chunks = p.BN / 16;
+    const int cw = p.cw8 ? 8 : 16;            // chunk width in columns
+    const int chunks = p.BN / cw;
     float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
     float* cis_smem = cs_smem + p.cs_per_warp;
     const bool need_cs = EPI == kEpiFwd && (p.epi.noise_std > 0.f || p.epi.adc.on);
@@ -580,11 +625,11 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           __syncwarp();
           int slot = 0;
           for (int ch = grp; ch < chunks; ch += groups, ++slot) {
-            const int n = nt * p.BN + ch * 16 + (lane & 15);
+            const int n = nt * p.BN + ch * cw + (lane & (cw - 1));
             if (n < p.epi.n_out) {
               const int64_t ci = static_cast<int64_t>(e) * p.epi.n_out + n;
-              if (lane < 16) cs_smem[slot * 16 + lane] = p.epi.col_scale[ci];
-              else if (p.epi.adc.on) cis_smem[slot * 16 + lane - 16] = p.epi.col_inv_scale[ci];
+              if (lane < cw) cs_smem[slot * cw + lane] = p.epi.col_scale[ci];
+              else if (lane >= 16 && lane < 16 + cw && p.epi.adc.on) cis_smem[slot * cw + lane - 16] = p.epi.col_inv_scale[ci];
             }
           }
           __syncwarp();
@@ -599,6 +644,13 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         int slot = 0;
 #pragma unroll 1
         for (int ch = grp; ch < chunks; ch += groups, ++slot) {
+          if (EPI == kEpiFwd && p.cw8) {
+            float v8[8];
+            tmem_ld8(taddr + ch * 8, v8);
+            tmem_ld_wait();
+            epi_chunk_fwd<false, 2>(p.epi, ctx, qr, nt * p.BN + ch * 8, v8, cs_smem + slot * 8, cis_smem + slot * 8, lane);
+            continue;
+          }
           float v[16];
           tmem_ld16(taddr + ch * 16, v);
           tmem_ld_wait();
@@ -1431,7 +1483,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     a_split = a->a_tile_lo != nullptr;
     p.a_split = a_split;
   }
-  AMOE_REQUIRE(!(p.cache_hi || p.epi.out_cache_hi) || a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(!(p.cache_hi || p.epi.out_cache_hi || p.epi.next_codes) || a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!p.cache_hi || (p.Kc % 8 == 0 && aligned16(p.cache_hi) && aligned16(p.cache_lo)), AMOE_ERR_BAD_SHAPE);
 
   p.a_bytes = a_split ? 2 * kATile : kATile;
@@ -1449,7 +1501,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
                             (p.cache_hi ? (dac ? 6.0 : 2.0) : 0.0);
     double per_epi = 8.0;
     if (!is_dx) per_epi += (a->noise_std > 0.f ? 26.0 : 0.0) + (a->noise ? 2.0 : 0.0) + (p.epi.adc.on ? 9.0 : 0.0) +
-                           (a->out_codes ? 3.0 : 0.0);
+                           (a->out_codes ? 3.0 : 0.0) + (p.epi.next_codes ? 14.0 : 0.0) + (p.epi.out_cache_hi ? 10.0 : 0.0);
     else per_epi += a->x_ref ? 12.0 : 0.0;
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
@@ -1458,9 +1510,14 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
+    // codes-only forward without a prologue: 8-column chunks, so that five groups of epilogue warps share a tile evenly
+    // (measured: slower than 16-column chunks on four groups - the epilogue is bound by instruction issue, not by the
+    // number of warps - so it stays off; AMOE_CW8=1 turns it on for experiments)
+    p.cw8 = std::getenv("AMOE_CW8") != nullptr && p.a_tma && !is_dx && a->out == nullptr && a->out_codes != nullptr &&
+            p.epi.vec4 && a->noise == nullptr && a->N % 8 == 0 && p.BN % 8 == 0 && p.BN * p.n_tiles == a->N;
     if (p.a_tma) {
-      // no prologue: the epilogue groups that share the tile's 16-column chunks most evenly (fewest warps on a tie)
-      const int chunks = p.BN / 16;
+      // no prologue: the epilogue groups that share the tile's chunks most evenly (fewest warps on a tie)
+      const int chunks = p.BN / (p.cw8 ? 8 : 16);
       int best_per = 1 << 30;
       for (int ne = 4; ne <= kWorkerWarps; ne += 4) {
         const int per = (chunks + ne / 4 - 1) / (ne / 4);
@@ -1477,7 +1534,8 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
     const int groups = p.n_epi / 4;
-    p.cs_per_warp = ((p.BN / 16 + groups - 1) / groups) * 16;
+    const int cw = p.cw8 ? 8 : 16;
+    p.cs_per_warp = ((p.BN / cw + groups - 1) / groups) * cw;
     p.cs_off = static_cast<uint32_t>(p.stages) * p.stage_bytes + 8u * kNumBars + 64u;
   }
   const uint32_t cs_bytes = static_cast<uint32_t>(p.n_epi) * 2u * p.cs_per_warp * sizeof(float);
@@ -1510,7 +1568,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   int epi = kEpiGeneric;
   if (p.epi.vec4 && !is_dx && a->noise == nullptr) epi = kEpiFwd;
   if (p.epi.vec4 && is_dx && (a->x_ref == nullptr || a->x_ref_dtype == AMOE_F32 || a->x_ref_stride % 8 == 0)) epi = kEpiDx;
-  AMOE_REQUIRE(!p.epi.out_cache_hi || epi == kEpiDx, AMOE_ERR_UNSUPPORTED);
+  AMOE_REQUIRE(!(p.epi.out_cache_hi || p.epi.next_codes) || epi == (is_dx ? kEpiDx : kEpiFwd), AMOE_ERR_UNSUPPORTED);
   const int dacm = is_dx ? kDacNone : (quant ? kDacQuant : kDacNorm);
 #define AMOE_LAUNCH_TC(DAC, F32, EPI)                                                                                  \
   do {                                                                                                                 \

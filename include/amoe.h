@@ -236,6 +236,12 @@ typedef struct amoe_cvmm_args {
    * them) and no a_cache_* can be written.  amoe_cvmm_dx of an up-projection takes the out_cache of the
    * down-projection's amoe_cvmm_dx this way. */
   const void* a_tile_hi; const void* a_tile_lo;
+  /* amoe_cvmm_fwd only: the result rows prepared as the NEXT projection's operands (same expert, e.g. the hidden
+   * activation between up- and down-projection), by padded tile row, cols % 64 == 0:
+   *   next_codes  bf16 DAC codes rint((clamp(out, +-next_ir[e]) / next_ir[e]) / next_inp_res): the next forward's a_tile_hi
+   *   out_cache_* split(clamp(out, +-next_ir[e]) * out_cache_scale[dst row]): the next weight gradient's x operand
+   * next_ir [E] per expert (required for next_codes; NULL = no clamp for out_cache_*). */
+  const float* next_ir; float next_inp_res; void* next_codes; const float* out_cache_scale;
   /* plumbing */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
   int32_t* dev_status;            /* int32[4] or NULL */

@@ -447,14 +447,16 @@ def test_layer_module_vs_oracle(dev, prec, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dims", [(384, 160, 96, 8, 3), (320, 128, 128, 4, 2)])
 @pytest.mark.parametrize("prec,dtype,use_ir", [("simt", torch.float32, True), ("split", torch.float32, True),
                                                ("split", torch.float32, False), ("bf16x1", torch.bfloat16, True)])
-def test_fused_layer_step_equals_the_composition(dev, prec, dtype, use_ir):
+def test_fused_layer_step_equals_the_composition(dev, prec, dtype, use_ir, dims):
     """The single-node layer step (ReLU, per-expert input ranges, decay term and gate backward folded into the
     kernels) against the composition route() -> CVMM -> ReLU -> CVMM with every non-ideality on: same Philox
     draws, same kernels, so everything but summation-order effects of the glue must agree exactly."""
     from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, WeightModifierType
-    T, D, F, E, k = 384, 160, 96, 8, 3
+    # (the second shape has an expert size that is a multiple of 64: the up-projection's dX then takes its A tiles by TMA)
+    T, D, F, E, k = dims
     cfg = TorchInferenceRPUConfig()
     cfg.forward.inp_res = 254.0
     cfg.forward.out_res = 254.0
