@@ -107,7 +107,6 @@ struct TcParams {
   const float* ir; const float* a_absmax; float inp_res; int vec_ok;
   // optional operand cache: split(clamp(a, ir) * cache_scale[a_row[i]]) by padded tile row, [tiles*128, cache_stride]
   __nv_bfloat16* cache_hi; __nv_bfloat16* cache_lo; int64_t cache_stride /* rows of the cache */; const float* cache_scale;
-  int cw8;              // codes-only forward epilogue in 8-column chunks (more, narrower chunks for more warps)
   int a_tma;            // the A operand exists as prepared bf16 tiles (an operand cache written by an earlier kernel):
                         // TMA loads it, there is no prologue and every worker warp runs the epilogue
   EpiParams epi;
@@ -333,18 +332,15 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 // kValue = false: only the ADC codes leave the kernel, the dequantised values are not formed.
 // The ADC code rint(x) is taken as (x + 1.5*2^23) - 1.5*2^23 (exact round-to-nearest-even for |x| < 2^22; codes are
 // at most 127 in magnitude), whose low mantissa byte is the code in two's complement.
-// NQ = quads (four columns each) of the chunk: 4, or 2 in the codes-only variant, whose narrower chunks spread over
-// more epilogue warps.
-template <bool kValue, int NQ = 4>
+template <bool kValue>
 __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
-                                              float* v, const float* cs, const float* cis, int lane) {
-  static_assert(NQ == 4 || !kValue, "the value path stores 16-column chunks");
+                                              float v[16], const float* cs, const float* cis, int lane) {
   constexpr float kMagic = 12582912.f;
   const bool noise = p.noise_std > 0.f, adc = p.adc.on;
   const float post = c.absmax * c.ir;
   uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-  for (int qd = 0; qd < NQ; ++qd) {
+  for (int qd = 0; qd < 4; ++qd) {
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
     if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
@@ -376,16 +372,14 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
   if (p.out_codes && c.valid) {
     // 16 codes of the row; a row starts on a 16-byte boundary only if n_out is a multiple of 16
     int8_t* dstc = p.out_codes + c.dst * p.n_out + n0;
-    if (NQ == 2) {
-      *reinterpret_cast<uint2*>(dstc) = make_uint2(pk[0], pk[1]);        // n_out % 8 == 0 in this variant
-    } else if ((p.n_out & 15) == 0) {
+    if ((p.n_out & 15) == 0) {
       *reinterpret_cast<uint4*>(dstc) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     } else {
 #pragma unroll
       for (int qd = 0; qd < 4; ++qd) *reinterpret_cast<uint32_t*>(dstc + 4 * qd) = pk[qd];   // n_out % 4 == 0
     }
   }
-  if constexpr (kValue && NQ == 4) if (p.next_codes || p.out_cache_hi) {
+  if (kValue && (p.next_codes || p.out_cache_hi)) {
     // the row once more as the next projection's operands (padded tile row, [64-column block][row][64]): DAC codes
     // for its forward pass, clamped and scaled bf16 hi (+ lo) terms for its weight gradient
     const int64_t co = (((n0 >> 6) * p.out_cache_stride + c.pad_row) << 6) + (n0 & 63);
@@ -423,7 +417,7 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
       }
     }
   }
-  if constexpr (kValue && NQ == 4) store16_t(p, qr, n0, v, lane);
+  if (kValue) store16_t(p, qr, n0, v, lane);
 }
 
 __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
@@ -592,7 +586,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     const int grp = ew >> 2;
     const int groups = p.n_epi >> 2;
     const int r = q * 32 + lane;
-    const int cw = p.cw8 ? 8 : 16;            // chunk width in columns
+    constexpr int cw = 16;                     // chunk width in columns
     const int chunks = p.BN / cw;
     float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
     float* cis_smem = cs_smem + p.cs_per_warp;
@@ -644,13 +638,6 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         int slot = 0;
 #pragma unroll 1
         for (int ch = grp; ch < chunks; ch += groups, ++slot) {
-          if (EPI == kEpiFwd && p.cw8) {
-            float v8[8];
-            tmem_ld8(taddr + ch * 8, v8);
-            tmem_ld_wait();
-            epi_chunk_fwd<false, 2>(p.epi, ctx, qr, nt * p.BN + ch * 8, v8, cs_smem + slot * 8, cis_smem + slot * 8, lane);
-            continue;
-          }
           float v[16];
           tmem_ld16(taddr + ch * 16, v);
           tmem_ld_wait();
@@ -1510,14 +1497,9 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; }
     }
-    // codes-only forward without a prologue: 8-column chunks, so that five groups of epilogue warps share a tile evenly
-    // (measured: slower than 16-column chunks on four groups - the epilogue is bound by instruction issue, not by the
-    // number of warps - so it stays off; AMOE_CW8=1 turns it on for experiments)
-    p.cw8 = std::getenv("AMOE_CW8") != nullptr && p.a_tma && !is_dx && a->out == nullptr && a->out_codes != nullptr &&
-            p.epi.vec4 && a->noise == nullptr && a->N % 8 == 0 && p.BN % 8 == 0 && p.BN * p.n_tiles == a->N;
     if (p.a_tma) {
       // no prologue: the epilogue groups that share the tile's chunks most evenly (fewest warps on a tie)
-      const int chunks = p.BN / (p.cw8 ? 8 : 16);
+      const int chunks = p.BN / 16;
       int best_per = 1 << 30;
       for (int ne = 4; ne <= kWorkerWarps; ne += 4) {
         const int per = (chunks + ne / 4 - 1) / (ne / 4);
@@ -1534,8 +1516,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
     const int groups = p.n_epi / 4;
-    const int cw = p.cw8 ? 8 : 16;
-    p.cs_per_warp = ((p.BN / cw + groups - 1) / groups) * cw;
+    p.cs_per_warp = ((p.BN / 16 + groups - 1) / groups) * 16;
     p.cs_off = static_cast<uint32_t>(p.stages) * p.stage_bytes + 8u * kNumBars + 64u;
   }
   const uint32_t cs_bytes = static_cast<uint32_t>(p.n_epi) * 2u * p.cs_per_warp * sizeof(float);
