@@ -415,7 +415,8 @@ class _ExpertParallelStep(torch.autograd.Function):
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
                                       ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
-                                      keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype)
+                                      keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype,
+                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None)
             # the two weight gradients on a second stream, beside the exchange and the streaming kernels that follow
             forked = cached and (need_values or need_keys)
             if forked:
