@@ -36,8 +36,8 @@ CONFIGS = {
 }
 # DRAM bytes (read + write) per launch of the config-2 kernels from the ncu capture summarised in
 # profiles/cvmm_tc_kernel_c2_ncu_full.md; other configs have no capture (traffic stays null).
-NCU_TRAFFIC_C2 = {"amoe_cvmm_fwd[up]": 173.3e6, "amoe_cvmm_fwd[down]": 27.8e6, "amoe_cvmm_dw[down]": 167.4e6,
-                  "amoe_cvmm_dx[down]": 211.1e6, "amoe_cvmm_dw[up]": 166.7e6, "amoe_cvmm_dx[up]": 181.9e6}
+NCU_TRAFFIC_C2 = {"amoe_cvmm_fwd[up]": 197.3e6, "amoe_cvmm_fwd[down]": 17.4e6, "amoe_cvmm_dw[down]": 167.4e6,
+                  "amoe_cvmm_dx[down]": 210.4e6, "amoe_cvmm_dw[up]": 167.2e6, "amoe_cvmm_dx[up]": 180.3e6}
 OUT_BOUND = 12.0     # ADC clip in units of the column weight maximum (aihwkit's default out_bound)
 SEED = 1234
 
