@@ -1507,12 +1507,10 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       }
     }
   }
-  // two prologue groups on alternate stages need a ring with an even number of stages (a stage then always
-  // belongs to the same group) and enough stages per tile to alternate on
-  if (!p.a_tma && p.stages >= 4 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr) {
+  // two prologue groups on alternate stages (both groups have the same number of warps, so every stage's barrier
+  // expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
+  if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr)
     p.prod_groups = 2;
-    p.stages &= ~1;
-  }
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
     const int groups = p.n_epi / 4;
