@@ -91,6 +91,9 @@ SIGNATURES = {
     "amoe_gate_backward": (C.c_int, [vp, vp, vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
     "amoe_router_logits": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, C.c_int32, C.c_int32, vp, C.c_int32,
                                      vp, vp]),
+    "amoe_router_select": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, C.c_int32, C.c_int32, vp, C.c_int32,
+                                     C.c_int32, C.c_int32, vp, vp, vp, vp]),
+    "amoe_sort_slots": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int32, vp, vp, vp, vp, vp, C.c_size_t, vp]),
     "amoe_router_backward_w_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "amoe_router_backward_w": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp, vp, C.c_int32, vp, vp, vp, vp,
                                          C.c_int64, C.c_int32, vp, vp, C.c_size_t, vp]),

@@ -267,11 +267,11 @@ class _ExpertParallelStep(torch.autograd.Function):
         with ops.launch_on(side):
             ops.set_tag("up")
             pw_up = prepass(keys, mod_up)
+            up_ready = side.record_event()      # the up-projection only waits for its own weights
             ops.set_tag("down")
             pw_dn = prepass(values, mod_dn)
         ops.set_tag("up")
-        logits = ops.router_logits(x2, w_sel, getattr(layer, "router_bias", None))
-        r = ops.select_sort(logits, k, apply_sigmoid=True)
+        r, _ = ops.router_select(x2, w_sel, k, getattr(layer, "router_bias", None))
         gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
         # ---- exchange plan: counts both ways, one host read
         counts = (r.expert_offsets[1:] - r.expert_offsets[:-1]).view(G, El).contiguous()
@@ -303,7 +303,7 @@ class _ExpertParallelStep(torch.autograd.Function):
         out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
         has_ir = input_range is not None
         ir_all = input_range.detach().float().contiguous() if has_ir else None
-        main.wait_stream(side)
+        main.wait_event(up_ready)
         cached = R > 0 and layer.operand_caches and ops.operand_cache_ok(precision, D, Fh, N) and \
             any(ctx.needs_input_grad[3:5])
         split = precision == ops.A.PREC_SPLIT
@@ -314,6 +314,7 @@ class _ExpertParallelStep(torch.autograd.Function):
             h, _ = ops.cvmm_fwd(recv, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                 ir=ir_all[0] if has_ir else None, ir_by_expert=True, absmax=am_up, inp_res=inp_res,
                                 out_res=out_res, out_bound=out_bound, out_relu=True, a_cache=xc, **nz_up)
+            main.wait_stream(side)
             ops.set_tag("down")
             am_dn = None if has_ir else ops.row_absmax(h)
             # with the ADC on and the device-driven exchange the rows travel back as int8 codes + one scale per row
@@ -324,6 +325,7 @@ class _ExpertParallelStep(torch.autograd.Function):
                                       out_res=out_res, out_bound=out_bound, a_cache=hs, want_codes=codes_back,
                                       want_out=not codes_back, row_meta=meta, **nz_dn)
         else:
+            main.wait_stream(side)
             codes_back = False
             h = recv.new_zeros((0, Fh))
             out = recv.new_zeros((0, N))

@@ -105,11 +105,11 @@ class _FusedAnalogStep(torch.autograd.Function):
         with ops.launch_on(side):
             ops.set_tag("up")
             pw_up = prepass(keys, mod_up)
+            up_ready = side.record_event()      # the up-projection only waits for its own weights
             ops.set_tag("down")
             pw_dn = prepass(values, mod_dn)
         ops.set_tag("up")
-        logits = ops.router_logits(x2, w_sel, getattr(layer, "router_bias", None))
-        r = ops.select_sort(logits, k, apply_sigmoid=True)
+        r, _ = ops.router_select(x2, w_sel, k, getattr(layer, "router_bias", None))
         inp_res = fwd.inp_res
         inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
         if os.environ.get("_AIHWKIT_NO_ROUNDING", False):
@@ -119,7 +119,7 @@ class _FusedAnalogStep(torch.autograd.Function):
         out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
         has_ir = input_range is not None
         ir_all = input_range.detach().float().contiguous() if has_ir else None
-        main.wait_stream(side)
+        main.wait_event(up_ready)
 
         # ---- up-projection (+ ReLU)
         nz = nz_up
@@ -146,6 +146,7 @@ class _FusedAnalogStep(torch.autograd.Function):
                             ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
                             out_bound=out_bound, out_relu=True, a_cache=xc, **nxt, **nz)
         # ---- down-projection and the gate-weighted sum over k
+        main.wait_stream(side)
         ops.set_tag("down")
         nz = nz_dn
         ir_dn = ir_all[1] if has_ir else None

@@ -17,7 +17,7 @@ from ._cabi import lib, check, ptr, stream_ptr, dtype_code, launch_on
 KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 3, "amoe_row_absmax": 1,
                     "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 2, "amoe_combine": 1,
                     "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
-                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1, "amoe_router_backward_w": 2}
+                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1, "amoe_router_backward_w": 2, "amoe_sort_slots": 4}
 
 
 class Trace:
@@ -149,6 +149,38 @@ def router_logits(x2: torch.Tensor, w_sel: torch.Tensor, bias: Optional[torch.Te
     _call("amoe_router_logits", ptr(x2), dtype_code(x2), x2.stride(0), T, D, ptr(w), dtype_code(w), E, ptr(b),
           int(x2.dtype == torch.bfloat16), ptr(out), stream_ptr())
     return out
+
+
+def router_select(x2: torch.Tensor, w_sel: torch.Tensor, k: int, bias: Optional[torch.Tensor] = None,
+                  want_logits: bool = False) -> Tuple["Routing", Optional[torch.Tensor]]:
+    """Router matmul, sigmoid, top-k (one kernel) and the expert-contiguous slot sort: the same result as
+    select_sort(router_logits(...)).  Falls back to those two calls for routers the fused kernel does not cover."""
+    x2 = _rows(x2)
+    w = w_sel.contiguous()
+    T, D = x2.shape
+    E = w.shape[0]
+    dev = x2.device
+    esz = x2.element_size()
+    fused = E <= 64 and D % 4 == 0 and (x2.stride(0) * esz) % 16 == 0 and (D * w.element_size()) % 16 == 0 and \
+        x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and ((E + 15) // 16 * 16) * D * 4 <= 200 * 1024
+    if not fused:
+        logits = router_logits(x2, w, bias)
+        return select_sort(logits, k, apply_sigmoid=True), logits
+    P = T * k
+    logits = torch.empty(T, E, dtype=torch.float32, device=dev) if want_logits else None
+    raw_sel = torch.empty(T, k, dtype=torch.int32, device=dev)
+    gate = torch.empty(T, k, dtype=torch.float32, device=dev)
+    b = None if bias is None else bias.float().contiguous()
+    _call("amoe_router_select", ptr(x2), dtype_code(x2), x2.stride(0), T, D, ptr(w), dtype_code(w), E, ptr(b),
+          int(x2.dtype == torch.bfloat16), k, 1, ptr(logits), ptr(raw_sel), ptr(gate), stream_ptr())
+    sel = torch.empty(P, dtype=torch.int32, device=dev)
+    tok = torch.empty(P, dtype=torch.int32, device=dev)
+    slot = torch.empty(P, dtype=torch.int32, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    nbytes = lib.amoe_select_sort_workspace_bytes(T, E, k)
+    ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device=dev)
+    _call("amoe_sort_slots", ptr(raw_sel), T, E, k, ptr(sel), ptr(tok), ptr(slot), ptr(off), ptr(ws), nbytes, stream_ptr())
+    return Routing(raw_sel, gate, sel, tok, slot, off), logits
 
 
 def router_backward_w(x2: torch.Tensor, dgate: torch.Tensor, gate: torch.Tensor, token_index: torch.Tensor,

@@ -126,7 +126,8 @@ template <typename TX, typename TW>
 __global__ void __launch_bounds__(256) router_logits_smem_kernel(const TX* __restrict__ x, int64_t x_stride, int64_t T, int D,
                                                                  const TW* __restrict__ w, int E,
                                                                  const float* __restrict__ bias, int round_bf16,
-                                                                 float* __restrict__ logits) {
+                                                                 float* __restrict__ logits, int k, int apply_sigmoid,
+                                                                 int32_t* __restrict__ raw_sel, float* __restrict__ gate) {
   extern __shared__ __align__(16) float s_w[];        // [ceil16(E)][D], rows past E are zero
   const int Ep = (E + 15) / 16 * 16;
   for (int i = threadIdx.x * 4; i < Ep * D; i += 1024) {
@@ -143,6 +144,7 @@ __global__ void __launch_bounds__(256) router_logits_smem_kernel(const TX* __res
     const bool two = t0 + 1 < T;
     const TX* x0 = x + t0 * x_stride;
     const TX* x1 = x + (two ? t0 + 1 : t0) * x_stride;
+    float picks[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // this lane's gate values, expert 16*i + (lane & 15)
     for (int e0 = 0; e0 < Ep; e0 += 16) {
       float v[32];
 #pragma unroll
@@ -177,7 +179,41 @@ __global__ void __launch_bounds__(256) router_logits_smem_kernel(const TX* __res
         if (round_bf16) r = __bfloat162float(__float2bfloat16_rn(r));
         if (bias) r += bias[e];
         if (round_bf16 && bias) r = __bfloat162float(__float2bfloat16_rn(r));
-        logits[t * E + e] = r;
+        if (logits) logits[t * E + e] = r;
+        const float gv = apply_sigmoid ? 1.0f / (1.0f + expf(-r)) : r;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (i == (e0 >> 4)) picks[i] = gv;
+      }
+    }
+    if (raw_sel != nullptr) {
+      // top-k of the token's gate values inside its 16-lane half of the warp: descending value, ties to the lower
+      // expert id, NaN never wins (the rules of topk_kernel)
+      const int64_t t = t0 + (lane >> 4);
+      for (int j = 0; j < k; ++j) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int e = 16 * i + (lane & 15);
+          if (e < E && (picks[i] > best || (picks[i] == best && e < best_e))) { best = picks[i]; best_e = e; }
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+          if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        if (best_e == 0x7fffffff) best_e = j;          // all-NaN row: keep indices in range
+        if ((lane & 15) == 0 && t < T) {
+          raw_sel[t * k + j] = best_e;
+          gate[t * k + j] = best;
+        }
+        if ((best_e & 15) == (lane & 15)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (i == (best_e >> 4)) picks[i] = -INFINITY;
+        }
       }
     }
   }
@@ -415,7 +451,8 @@ inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) 
 
 template <typename TX, typename TW>
 int launch_logits(const void* x, int64_t x_stride, int64_t T, int D, const void* w, int E, const float* bias, int round_bf16,
-                  float* logits, int vec, cudaStream_t stream) {
+                  float* logits, int vec, cudaStream_t stream, int k = 0, int apply_sigmoid = 0, int32_t* raw_sel = nullptr,
+                  float* gate = nullptr) {
   const TX* xp = reinterpret_cast<const TX*>(x);
   const TW* wp = reinterpret_cast<const TW*>(w);
   const size_t smem = static_cast<size_t>((E + 15) / 16 * 16) * D * sizeof(float);
@@ -427,10 +464,12 @@ int launch_logits(const void* x, int64_t x_stride, int64_t T, int D, const void*
     AMOE_CUDA(cudaFuncSetAttribute(router_logits_smem_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(smem)));
     router_logits_smem_kernel<TX, TW><<<static_cast<unsigned>(grid), 256, smem, stream>>>(xp, x_stride, T, D, wp, E, bias,
-                                                                                          round_bf16, logits);
+                                                                                          round_bf16, logits, k, apply_sigmoid,
+                                                                                          raw_sel, gate);
     AMOE_LAUNCH_CHECK("router_logits_smem");
     return AMOE_OK;
   }
+  if (raw_sel != nullptr) return AMOE_ERR_UNSUPPORTED;      // the fused select needs the shared-memory variant
 #define AMOE_RL(EQ)                                                                                              \
   do {                                                                                                           \
     constexpr int kTok = 2 * (128 / EQ);                                                                         \
@@ -470,6 +509,30 @@ int amoe_router_logits(const void* x, int32_t x_dtype, int64_t x_stride, int64_t
     return launch_logits<__nv_bfloat16, float>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream);
   if (x_dtype == AMOE_F32 && w_dtype == AMOE_BF16)
     return launch_logits<float, __nv_bfloat16>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream);
+  return AMOE_ERR_BAD_DTYPE;
+}
+
+int amoe_router_select(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const void* w,
+                       int32_t w_dtype, int32_t E, const float* bias, int32_t round_bf16, int32_t k, int32_t apply_sigmoid,
+                       float* logits, int32_t* raw_sel, float* gate, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && w && raw_sel && gate, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(T > 0 && D > 0 && E > 0 && k > 0 && k <= E, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(E <= 64, AMOE_ERR_UNSUPPORTED);
+  const int xs = x_dtype == AMOE_F32 ? 4 : 2, wsz = w_dtype == AMOE_F32 ? 4 : 2;
+  const int vec = al16(x) && al16(w) && (x_stride * xs) % 16 == 0 && (static_cast<int64_t>(D) * wsz) % 16 == 0 && D % 4 == 0;
+  AMOE_REQUIRE(vec, AMOE_ERR_UNSUPPORTED);
+  if (x_dtype == AMOE_F32 && w_dtype == AMOE_F32)
+    return launch_logits<float, float>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream, k, apply_sigmoid, raw_sel, gate);
+  if (x_dtype == AMOE_BF16 && w_dtype == AMOE_BF16)
+    return launch_logits<__nv_bfloat16, __nv_bfloat16>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream, k,
+                                                       apply_sigmoid, raw_sel, gate);
+  if (x_dtype == AMOE_BF16 && w_dtype == AMOE_F32)
+    return launch_logits<__nv_bfloat16, float>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream, k, apply_sigmoid,
+                                               raw_sel, gate);
+  if (x_dtype == AMOE_F32 && w_dtype == AMOE_BF16)
+    return launch_logits<float, __nv_bfloat16>(x, x_stride, T, D, w, E, bias, round_bf16, logits, vec, stream, k, apply_sigmoid,
+                                               raw_sel, gate);
   return AMOE_ERR_BAD_DTYPE;
 }
 

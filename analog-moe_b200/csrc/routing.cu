@@ -217,6 +217,29 @@ __global__ void gate_backward_kernel(const float* __restrict__ dgate, const floa
 
 using namespace amoe;
 
+static int sort_slots(const int32_t* raw_sel, int64_t T, int32_t E, int32_t k, int32_t* sel_sorted, int32_t* token_index,
+                      int32_t* slot_index, int32_t* expert_offsets, void* workspace, cudaStream_t stream) {
+  const int64_t P = T * k;
+  const int64_t nchunks = (P + kChunk - 1) / kChunk;
+  int32_t* hist = reinterpret_cast<int32_t*>(workspace);
+  // warps per block limited by shared memory: E ints per warp
+  int wpb = 8;
+  while (wpb > 1 && static_cast<size_t>(wpb) * E * sizeof(int32_t) > 32 * 1024) wpb >>= 1;
+  const unsigned blocks = static_cast<unsigned>((nchunks + wpb - 1) / wpb);
+  const size_t smem = static_cast<size_t>(wpb) * E * sizeof(int32_t);
+  chunk_hist_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, hist);
+  AMOE_LAUNCH_CHECK("chunk_hist");
+  int32_t* total = hist + nchunks * E;
+  chunk_scan_kernel<<<(E * 32 + 255) / 256, 256, 0, stream>>>(hist, nchunks, E, total);
+  AMOE_LAUNCH_CHECK("chunk_scan");
+  offsets_kernel<<<1, 1024, 0, stream>>>(total, E, expert_offsets);
+  AMOE_LAUNCH_CHECK("offsets");
+  scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, expert_offsets, sel_sorted, token_index,
+                                                     slot_index);
+  AMOE_LAUNCH_CHECK("scatter");
+  return AMOE_OK;
+}
+
 extern "C" {
 
 size_t amoe_select_sort_workspace_bytes(int64_t T, int32_t E, int32_t k) {
@@ -235,9 +258,6 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
   AMOE_REQUIRE(logits && raw_sel && gate && sel_sorted && token_index && slot_index && expert_offsets,
                AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(workspace && workspace_bytes >= amoe_select_sort_workspace_bytes(T, E, k), AMOE_ERR_WORKSPACE);
-  const int64_t P = T * k;
-  const int64_t nchunks = (P + kChunk - 1) / kChunk;
-  int32_t* hist = reinterpret_cast<int32_t*>(workspace);
   {
     const int threads = 256;
     const int64_t blocks = (T * 32 + threads - 1) / threads;
@@ -249,22 +269,18 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
     else topk_kernel<kMaxE / 32><<<nb, threads, 0, stream>>>(logits, T, E, k, apply_sigmoid, raw_sel, gate);
     AMOE_LAUNCH_CHECK("topk");
   }
-  // warps per block limited by shared memory: E ints per warp
-  int wpb = 8;
-  while (wpb > 1 && static_cast<size_t>(wpb) * E * sizeof(int32_t) > 32 * 1024) wpb >>= 1;
-  const unsigned blocks = static_cast<unsigned>((nchunks + wpb - 1) / wpb);
-  const size_t smem = static_cast<size_t>(wpb) * E * sizeof(int32_t);
-  chunk_hist_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, hist);
-  AMOE_LAUNCH_CHECK("chunk_hist");
-  int32_t* total = hist + nchunks * E;
-  chunk_scan_kernel<<<(E * 32 + 255) / 256, 256, 0, stream>>>(hist, nchunks, E, total);
-  AMOE_LAUNCH_CHECK("chunk_scan");
-  offsets_kernel<<<1, 1024, 0, stream>>>(total, E, expert_offsets);
-  AMOE_LAUNCH_CHECK("offsets");
-  scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, expert_offsets, sel_sorted, token_index,
-                                                     slot_index);
-  AMOE_LAUNCH_CHECK("scatter");
-  return AMOE_OK;
+  return sort_slots(raw_sel, T, E, k, sel_sorted, token_index, slot_index, expert_offsets, workspace, stream);
+}
+
+int amoe_sort_slots(const int32_t* raw_sel, int64_t T, int32_t E, int32_t k, int32_t* sel_sorted, int32_t* token_index,
+                    int32_t* slot_index, int32_t* expert_offsets, void* workspace, size_t workspace_bytes,
+                    amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(T > 0 && E > 0 && k > 0 && E <= kMaxE && k <= kMaxK && k <= E, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(T * k < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(raw_sel && sel_sorted && token_index && slot_index && expert_offsets, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(workspace && workspace_bytes >= amoe_select_sort_workspace_bytes(T, E, k), AMOE_ERR_WORKSPACE);
+  return sort_slots(raw_sel, T, E, k, sel_sorted, token_index, slot_index, expert_offsets, workspace, stream);
 }
 
 int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw_sel, int64_t T, int32_t E, int32_t k,

@@ -77,6 +77,11 @@ int amoe_select_sort(const float* logits, int64_t T, int32_t E, int32_t k, int32
                      int32_t* slot_index, int32_t* expert_offsets, void* workspace, size_t workspace_bytes,
                      amoe_stream_t stream);
 
+/* The sort half of amoe_select_sort for a raw_sel [T,k] that already exists (workspace as for amoe_select_sort). */
+int amoe_sort_slots(const int32_t* raw_sel, int64_t T, int32_t E, int32_t k, int32_t* sel_sorted, int32_t* token_index,
+                    int32_t* slot_index, int32_t* expert_offsets, void* workspace, size_t workspace_bytes,
+                    amoe_stream_t stream);
+
 /* Backward of the gate selection: dlogits [T,E] = 0 except dlogits[t, raw_sel[t,j]] = dgate[t,j]*(1-g)*g with
  * g = gate[t,j] (apply_sigmoid) or dgate[t,j].  Replaces autograd's gather/sigmoid backward of the base layer's
  * `sigmoid(logits).gather(raw_sel)`; every element of dlogits is written. */
@@ -98,6 +103,11 @@ int amoe_gate_backward(const float* dgate, const float* gate, const int32_t* raw
 int amoe_router_logits(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const void* w,
                        int32_t w_dtype, int32_t E, const float* bias, int32_t round_bf16, float* logits,
                        amoe_stream_t stream);
+/* amoe_router_select: amoe_router_logits with the gate selection in the same kernel (E <= 64, 16-byte aligned rows):
+ *   raw_sel [T,k] and gate [T,k] as amoe_select_sort writes them; logits [T,E] optional.  Follow with amoe_sort_slots. */
+int amoe_router_select(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const void* w,
+                       int32_t w_dtype, int32_t E, const float* bias, int32_t round_bf16, int32_t k, int32_t apply_sigmoid,
+                       float* logits, int32_t* raw_sel, float* gate, amoe_stream_t stream);
 size_t amoe_router_backward_w_workspace_bytes(int64_t P, int32_t E, int32_t D);
 int amoe_router_backward_w(const void* x, int32_t x_dtype, int64_t x_stride, int64_t T, int32_t D, const float* dgate,
                            const float* gate, int32_t apply_sigmoid, const int32_t* token_index,

@@ -561,6 +561,11 @@ def test_router_kernels_vs_torch(dev, T, D, E, k, dtype):
         ref = ref + bias.double()
         assert float((logits.double() - ref).abs().max()) <= 1e-5
     r = ops.select_sort(logits, k, apply_sigmoid=True)
+    # the same selection with the top-k inside the router kernel: bit-identical
+    r2, lg2 = ops.router_select(x, w, k, bias, want_logits=True)
+    assert torch.equal(lg2, logits)
+    for name in ("raw_sel", "gate", "sel", "token_index", "slot_index", "expert_offsets"):
+        assert torch.equal(getattr(r2, name), getattr(r, name)), name
     dgate = torch.randn(T * k, generator=g).to(dev)
     gate = r.gate
     c = (dgate * (1 - gate.reshape(-1)) * gate.reshape(-1)).double()
