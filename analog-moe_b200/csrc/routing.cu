@@ -175,6 +175,64 @@ __global__ void scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t P, i
   }
 }
 
+// Scan + offsets + scatter in one kernel for moderate sizes: every warp (one chunk) sums the histogram columns itself
+// (its own exclusive prefix over the earlier chunks and the experts' totals), which is nchunks * E loads per warp from
+// a table that sits in L2, instead of waiting for two more kernels.  Same positions as the three-kernel path.
+__global__ void scan_scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t P, int E, int k,
+                                    const int32_t* __restrict__ hist /*[nchunks,E] counts*/, int64_t nchunks,
+                                    int32_t* __restrict__ offsets, int32_t* __restrict__ sel_sorted,
+                                    int32_t* __restrict__ token_index, int32_t* __restrict__ slot_index) {
+  extern __shared__ int32_t cnt[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t chunk = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  const int64_t s0 = chunk * kChunk;
+  if (s0 >= P) return;
+  int32_t* my = cnt + warp * E;
+  int32_t carry = 0;                                   // total of all experts below the current group of 32
+  for (int e0 = 0; e0 < E; e0 += 32) {
+    const int e = e0 + lane;
+    int32_t tot = 0, pre = 0;
+    if (e < E) {
+#pragma unroll 8
+      for (int64_t c = 0; c < nchunks; ++c) {
+        const int32_t h = hist[c * E + e];
+        tot += h;
+        if (c < chunk) pre += h;
+      }
+    }
+    int32_t incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const int32_t start = carry + incl - tot;          // first sorted position of expert e
+    if (e < E) {
+      my[e] = start + pre;
+      if (chunk == 0) offsets[e] = start;
+    }
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (chunk == 0 && lane == 0) offsets[E] = carry;
+  __syncwarp();
+  for (int64_t s = s0 + lane; s < s0 + kChunk; s += 32) {
+    bool ok = s < P;
+    int e = ok ? raw_sel[s] : -1;
+    ok = ok && e >= 0 && e < E;
+    unsigned m = __match_any_sync(0xffffffffu, ok ? e : -1);
+    int pos = 0;
+    if (ok) pos = my[e] + __popc(m & ((1u << lane) - 1u));
+    __syncwarp();
+    if (ok && (__ffs(m) - 1) == lane) my[e] += __popc(m);
+    __syncwarp();
+    if (ok) {
+      sel_sorted[pos] = e;
+      slot_index[pos] = static_cast<int32_t>(s);
+      token_index[pos] = static_cast<int32_t>(s / k);
+    }
+  }
+}
+
 __global__ void offsets_from_sorted_kernel(const int32_t* __restrict__ sel, int64_t P, int E,
                                            int32_t* __restrict__ offsets, int32_t* status) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -229,6 +287,12 @@ static int sort_slots(const int32_t* raw_sel, int64_t T, int32_t E, int32_t k, i
   const size_t smem = static_cast<size_t>(wpb) * E * sizeof(int32_t);
   chunk_hist_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, hist);
   AMOE_LAUNCH_CHECK("chunk_hist");
+  if (nchunks * E <= 8192) {      // each warp reads the whole table: keep that to 32 KiB
+    scan_scatter_kernel<<<blocks, wpb * 32, smem, stream>>>(raw_sel, P, E, k, hist, nchunks, expert_offsets, sel_sorted,
+                                                           token_index, slot_index);
+    AMOE_LAUNCH_CHECK("scan_scatter");
+    return AMOE_OK;
+  }
   int32_t* total = hist + nchunks * E;
   chunk_scan_kernel<<<(E * 32 + 255) / 256, 256, 0, stream>>>(hist, nchunks, E, total);
   AMOE_LAUNCH_CHECK("chunk_scan");
