@@ -189,29 +189,39 @@ __global__ void scan_scatter_kernel(const int32_t* __restrict__ raw_sel, int64_t
   if (s0 >= P) return;
   int32_t* my = cnt + warp * E;
   int32_t carry = 0;                                   // total of all experts below the current group of 32
-  for (int e0 = 0; e0 < E; e0 += 32) {
-    const int e = e0 + lane;
+  // with fewer than 32 experts the lanes also split the chunk range: lane = part * ew + expert
+  int ew = 32;
+  while (ew > 1 && (ew >> 1) >= E) ew >>= 1;           // experts per group, rounded up to a power of two (<= 32)
+  const int parts = 32 / ew;
+  for (int e0 = 0; e0 < E; e0 += ew) {
+    const int e = e0 + (lane & (ew - 1));
+    const int part = lane / ew;
+    const int64_t c_lo = nchunks * part / parts, c_hi = nchunks * (part + 1) / parts;
     int32_t tot = 0, pre = 0;
     if (e < E) {
 #pragma unroll 8
-      for (int64_t c = 0; c < nchunks; ++c) {
+      for (int64_t c = c_lo; c < c_hi; ++c) {
         const int32_t h = hist[c * E + e];
         tot += h;
         if (c < chunk) pre += h;
       }
     }
-    int32_t incl = tot;
+    for (int o = ew; o < 32; o <<= 1) {                // sum over the parts: afterwards every lane of an expert has both
+      tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      pre += __shfl_xor_sync(0xffffffffu, pre, o);
+    }
+    int32_t incl = (lane < ew) ? tot : 0;              // scan over the experts in the first ew lanes
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int32_t up = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += up;
     }
-    const int32_t start = carry + incl - tot;          // first sorted position of expert e
-    if (e < E) {
+    const int32_t start = carry + incl - tot;          // first sorted position of expert e (valid for lane < ew)
+    if (lane < ew && e < E) {
       my[e] = start + pre;
       if (chunk == 0) offsets[e] = start;
     }
-    carry += __shfl_sync(0xffffffffu, incl, 31);
+    carry += __shfl_sync(0xffffffffu, incl, ew - 1);
   }
   if (chunk == 0 && lane == 0) offsets[E] = carry;
   __syncwarp();
