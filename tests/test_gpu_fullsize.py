@@ -95,6 +95,42 @@ def test_config2_layer_step_is_deterministic_without_noise(dev):
         assert torch.equal(a, b)
 
 
+def test_config2_single_node_step_equals_the_composition(dev):
+    """Config 2 shapes with every non-ideality on: the single-node layer step (router and top-k in one kernel, two-kernel
+    slot sort, hidden rows handed to the down-projection as TMA tiles, weight gradients from the operand caches on a
+    second stream) against the composition route() -> CVMM -> ReLU -> CVMM.  Same Philox draws in both."""
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, WeightModifierType
+    cfg = TorchInferenceRPUConfig()
+    cfg.forward.inp_res, cfg.forward.out_res, cfg.forward.out_bound, cfg.forward.out_noise = 254.0, 254.0, 12.0, 0.04
+    cfg.pre_post.input_range.init_value = 3.0
+    cfg.pre_post.input_range.decay = 0.01
+    cfg.modifier.type = WeightModifierType.ADD_NORMAL_PER_CHANNEL
+    cfg.modifier.std_dev = 0.02
+    torch.manual_seed(0)
+    layer = AnalogSigmaMoELayer(cfg, d_model=1024, n_experts=16, expert_size=128, k=4, noise_seed=5).to(dev)
+    layer.train()
+    x0 = torch.randn(1, 8192, 1024, device=dev)
+    gy = torch.randn(1, 8192, 1024, device=dev)
+    res = {}
+    for fused in (True, False):
+        layer.fused = fused
+        layer.noise_step.zero_()
+        layer.zero_grad()
+        x = x0.clone().requires_grad_()
+        y, _ = layer(x)
+        y.backward(gy)
+        res[fused] = dict(y=y.detach(), dx=x.grad, dkeys=layer.keys.grad.clone(), dvalues=layer.values.grad.clone(),
+                          dsel=layer.expert_sel.weight.grad.clone(), dir=layer.input_range.grad.clone())
+    for key, a in res[True].items():
+        b = res[False][key]
+        assert torch.isfinite(a).all(), key
+        # weight gradients: two factorings of the bf16 hi/lo split; the rest: gates from two sigmoid / matmul kernels
+        tol = 3e-5 if key in ("dkeys", "dvalues") else 1e-5
+        scale = max(1.0, float(b.abs().max()))
+        err = float((a - b).abs().max())
+        assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"
+
+
 def test_noise_changes_every_step_and_every_graph_replay(dev):
     """Training-mode noise: a new draw per step, also when the step is replayed from a CUDA graph
     (the Philox offset comes from a device counter that the graph advances)."""
