@@ -84,6 +84,18 @@ __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* _
   }
 }
 
+// Order in which the warps of a launch take the rows.  The slot list is sorted by expert, hence by destination rank,
+// and the receive buffer by source rank: taken in order, every rank would write to rank 0 first, then to rank 1, ...,
+// and each destination's NVLink ingress would serve all senders at once while the other links idle.  Warp w takes
+// row (w mod kSpread) * ceil(n / kSpread) + w / kSpread instead: the warps resident at any time cover all
+// destinations evenly (indices >= n fall out; spread_count(n) warps cover all rows).
+constexpr int kSpread = 64;
+__device__ __host__ __forceinline__ int64_t spread_count(int64_t n) { return (n + kSpread - 1) / kSpread * kSpread; }
+__device__ __forceinline__ int64_t spread_row(int64_t w, int64_t n) {
+  const int64_t per = (n + kSpread - 1) / kSpread;
+  return (w % kSpread) * per + w / kSpread;
+}
+
 // One warp copies one row of K elements (16-byte pieces when `vec`), optionally scaled.
 template <typename T>
 __device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restrict__ dst, int K, bool vec, float sc,
@@ -92,24 +104,34 @@ __device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restric
     constexpr int per = 16 / sizeof(T);
     const uint4* s4 = reinterpret_cast<const uint4*>(src);
     uint4* d4 = reinterpret_cast<uint4*>(dst);
-    for (int q = lane; q < K / per; q += 32) {
-      uint4 v = __ldg(s4 + q);
-      if (scaled) {
-        if constexpr (sizeof(T) == 4) {
-          v.x = __float_as_uint(sc * __uint_as_float(v.x)); v.y = __float_as_uint(sc * __uint_as_float(v.y));
-          v.z = __float_as_uint(sc * __uint_as_float(v.z)); v.w = __float_as_uint(sc * __uint_as_float(v.w));
-        } else {
-          uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const int n = K / per;
+    // four loads in flight per lane before the first store: the stores may cross NVLink, and one 16-byte piece at a
+    // time leaves the link idle between a load's return and the next one's issue
+    for (int q0 = lane; q0 < n; q0 += 128) {
+      uint4 v[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float a = sc * __uint_as_float(w[i] << 16), b = sc * __uint_as_float(w[i] & 0xffff0000u);
-            __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
-            w[i] = *reinterpret_cast<uint32_t*>(&pk);
+      for (int u = 0; u < 4; ++u)
+        if (q0 + 32 * u < n) v[u] = __ldg(s4 + q0 + 32 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (q0 + 32 * u >= n) break;
+        if (scaled) {
+          if constexpr (sizeof(T) == 4) {
+            v[u].x = __float_as_uint(sc * __uint_as_float(v[u].x)); v[u].y = __float_as_uint(sc * __uint_as_float(v[u].y));
+            v[u].z = __float_as_uint(sc * __uint_as_float(v[u].z)); v[u].w = __float_as_uint(sc * __uint_as_float(v[u].w));
+          } else {
+            uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float a = sc * __uint_as_float(w[i] << 16), b = sc * __uint_as_float(w[i] & 0xffff0000u);
+              __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
+              w[i] = *reinterpret_cast<uint32_t*>(&pk);
+            }
+            v[u] = make_uint4(w[0], w[1], w[2], w[3]);
           }
-          v = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        d4[q0 + 32 * u] = v[u];
       }
-      d4[q] = v;
     }
   } else {
     for (int k = lane; k < K; k += 32) {
@@ -127,7 +149,7 @@ __global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, co
                               const int32_t* __restrict__ sel_sorted, int El, const int32_t* __restrict__ plan,
                               const uint64_t* __restrict__ peer_ptrs, int G, int64_t peer_rows, int64_t x_rows, int vec) {
   const int lane = threadIdx.x & 31;
-  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t i = spread_row((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, P);
   if (i >= P) return;
   const int d = sel_sorted[i] / El;
   const int64_t sr = src_row[i];
@@ -148,7 +170,10 @@ __global__ void ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, i
   const int64_t R = min(static_cast<int64_t>(plan[0]), cap_rows);
   const int32_t* recv_off = plan + 2 + 2 * G;
   const int32_t* back_off = plan + 2 + 3 * G;
-  for (int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < R; r += warps) {
+  const int64_t n_spread = spread_count(R);
+  for (int64_t w = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < n_spread; w += warps) {
+    const int64_t r = spread_row(w, R);
+    if (r >= R) continue;
     int s = 0;
     for (int g = 1; g < G; ++g)
       if (recv_off[g] <= r) s = g;                    // last source whose block starts at or before r
@@ -199,7 +224,7 @@ int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t
   AMOE_REQUIRE(P > 0 && K > 0 && El > 0 && G > 0 && G <= kEpMaxRanks && src_div >= 1 && peer_rows > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
   const int esz = dtype == AMOE_F32 ? 4 : 2;
   const int vec = al16(x) && (stride * esz) % 16 == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;   // peer bases are page aligned
-  const unsigned blocks = static_cast<unsigned>((P * 32 + 255) / 256);
+  const unsigned blocks = static_cast<unsigned>((spread_count(P) * 32 + 255) / 256);
   if (dtype == AMOE_F32)
     ep_put_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div, row_scale, P,
                                                      sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows, vec);
