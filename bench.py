@@ -146,6 +146,35 @@ def step(layer, x, gy, bwd):
     return y
 
 
+def kernel_times(path, layer, xs, gys, bwd, rank, world):
+    """Device time per kernel over three eager steps (torch profiler, CUDA activity only), written to `path` by rank 0:
+    one line per rank with the totals of the kernel families, then rank 0's table.  Not a bench value: kernels of
+    different streams overlap in the step, and collectives include the time they wait for the other ranks."""
+    from torch.profiler import profile, ProfilerActivity
+    n = 3
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(n):
+            step(layer, xs[i % len(xs)], gys[i % len(xs)], bwd)
+        torch.cuda.synchronize()
+    ka = prof.key_averages()
+
+    def tot(pat):
+        return sum(e.device_time_total for e in ka if pat in e.key) / n
+
+    line = (f"rank {rank}: cvmm_tc {tot('cvmm_tc'):.0f}  dw_tc {tot('dw_tc'):.0f}  ep_put {tot('ep_put_kernel'):.0f}  "
+            f"ep_put_back {tot('ep_put_back'):.0f}  all kernels but nccl "
+            f"{sum(e.device_time_total for e in ka if 'nccl' not in e.key) / n:.0f} us per step")
+    lines = [line]
+    if world > 1:
+        import torch.distributed as dist
+        lines = [None] * world
+        dist.all_gather_object(lines, line)
+    if rank == 0:
+        with open(path, "w") as f:
+            f.write("\n".join(lines) + "\n")
+            f.write(ka.table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=80))
+
+
 def run_ours(args, cfg, rank, world, device):
     from analog_moe import ops, _cabi
     # parameters' AccumulateGrad nodes are created during warm-up on the default stream and used again under graph
@@ -178,6 +207,9 @@ def run_ours(args, cfg, rank, world, device):
     for i in range(args.warmup):
         step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
     barrier()
+    if args.kernel_times:
+        kernel_times(args.kernel_times, layer, xs, gys, bwd, rank, world)
+        return None
     # One CUDA graph per input set (whole step: routing, both projections, backward).  The Philox
     # offsets come from a device counter that the graph itself advances, so replays draw new noise.
     # Expert-parallel runs are captured too when the exchange is device-driven (rows stored into peer memory, the plan
@@ -349,6 +381,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step eagerly instead of replaying a CUDA graph of the step")
+    ap.add_argument("--kernel-times", default=None, metavar="PATH",
+                    help="instead of the timed run: write per-kernel device times of three eager steps to PATH")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", 0))
@@ -387,6 +421,11 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     r = run_ours(args, cfg, rank, world, device)
+    if r is None:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     if rank == 0:
         pk = peaks()
         ms_step = r["ms"] / args.steps
