@@ -83,6 +83,7 @@ SIGNATURES = {
     "amoe_version": (C.c_int, []),
     "amoe_status_string": (C.c_char_p, [C.c_int]),
     "amoe_last_error_string": (C.c_char_p, []),
+    "amoe_launch_count": (C.c_ulonglong, []),
     "amoe_check_device": (C.c_int, []),
     "amoe_read_device_status": (C.c_int, [vp, C.POINTER(C.c_int32 * 4), vp]),
     "amoe_select_sort_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
@@ -121,9 +122,10 @@ SIGNATURES = {
                                      vp, vp, vp]),
     "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, vp]),
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
-    "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp,
-                                  C.c_size_t, vp]),
-    "amoe_expert_std_static": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int64, C.c_int32, vp, vp]),
+    "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, vp, vp,
+                                  C.c_size_t, vp, vp]),
+    "amoe_expert_std_static": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, vp,
+                                         vp, vp]),
     "amoe_ep_pack": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, C.c_int32, vp, C.c_int64, vp, C.c_float, vp, vp,
                                vp, vp]),
     "amoe_invert_index": (C.c_int, [vp, C.c_int64, vp, vp]),

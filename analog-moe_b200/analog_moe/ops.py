@@ -13,15 +13,8 @@ from . import _cabi as A
 from ._cabi import lib, check, ptr, stream_ptr, dtype_code, launch_on
 
 
-# kernels launched by one call of each entry point (for the launch counter)
-KERNELS_PER_CALL = {"amoe_row_dot_codes": 1, "amoe_invert_index": 1, "amoe_select_sort": 5, "amoe_expert_offsets": 1, "amoe_weight_prepass": 3, "amoe_row_absmax": 1,
-                    "amoe_cvmm_fwd": 1, "amoe_cvmm_dx": 1, "amoe_cvmm_dw": 2, "amoe_combine": 1,
-                    "amoe_combine_codes": 1, "amoe_row_dot": 1, "amoe_ir_grad_reduce": 1, "amoe_expert_std": 5,
-                    "amoe_ep_pack": 1, "amoe_ep_unpack": 1, "amoe_router_backward_w": 2, "amoe_sort_slots": 4}
-
-
 class Trace:
-    """Counts library launches and, when `timed`, brackets each call with CUDA events on the
+    """Sums the library's launch counter over the calls it sees and, when `timed`, brackets each call with CUDA events on the
     launching stream (used by the bench for per-kernel durations; adds event overhead)."""
 
     def __init__(self, timed: bool = False):
@@ -43,6 +36,8 @@ class Trace:
 
 TRACE: Optional[Trace] = None
 _TAG = ""
+# NVTX range around every library call ("amoe_cvmm_fwd[up]", ...) for timeline tools; off unless AMOE_NVTX=1 or set here.
+NVTX = os.environ.get("AMOE_NVTX", "") not in ("", "0")
 
 
 def set_tag(tag: str) -> None:
@@ -51,16 +46,22 @@ def set_tag(tag: str) -> None:
 
 
 def _call(name: str, *args) -> None:
+    if NVTX:
+        torch.cuda.nvtx.range_push(name if not _TAG else f"{name}[{_TAG}]")
+        try:
+            _call_traced(name, *args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        _call_traced(name, *args)
+
+
+def _call_traced(name: str, *args) -> None:
     tr = TRACE
     if tr is None:
         check(getattr(lib, name)(*args), name)
         return
-    tr.launches += KERNELS_PER_CALL.get(name, 1)
-    if name in ("amoe_sort_slots", "amoe_select_sort"):
-        # (logits or raw_sel, T, E, k, ...): small problems sort with two kernels instead of four
-        T_, E_, k_ = args[1], args[2], args[3]
-        if ((T_ * k_ + 255) // 256) * E_ <= 8192:
-            tr.launches -= 2
+    before = lib.amoe_launch_count()
     if tr.timed:
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
@@ -72,6 +73,7 @@ def _call(name: str, *args) -> None:
     else:
         check(getattr(lib, name)(*args), name)
         tr.calls.append((name, _TAG, None, None))
+    tr.launches += lib.amoe_launch_count() - before      # the library's own count of the kernels it launched
 
 
 _SIDE_STREAMS = {}
@@ -572,14 +574,15 @@ def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_rang
     return out
 
 
-def expert_std(x: torch.Tensor, x_row: torch.Tensor, offsets: torch.Tensor, E: int) -> torch.Tensor:
+def expert_std(x: torch.Tensor, x_row: torch.Tensor, offsets: torch.Tensor, E: int,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
     x2 = _rows(x)
     P = x_row.numel()
     out = torch.empty(E, dtype=torch.float32, device=x2.device)
     nbytes = lib.amoe_expert_std_workspace_bytes(E)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)
-    _call("amoe_expert_std", ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[1], ptr(x_row), ptr(offsets), P, E,
-                              ptr(out), ptr(ws), nbytes, stream_ptr())
+    _call("amoe_expert_std", ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[1], x2.shape[0], ptr(x_row), ptr(offsets),
+          P, E, ptr(out), ptr(ws), nbytes, ptr(status), stream_ptr())
     return out
 
 

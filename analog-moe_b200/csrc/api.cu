@@ -11,6 +11,10 @@ void set_last_error(const char* what, cudaError_t err) {
   snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", what, cudaGetErrorName(err), cudaGetErrorString(err));
 }
 
+static thread_local unsigned long long g_launches = 0;
+void note_launch() { ++g_launches; }
+unsigned long long launches_so_far() { return g_launches; }
+
 int sm_count() {
   static thread_local int cached_dev = -1;
   static thread_local int cached = 0;
@@ -47,6 +51,8 @@ const char* amoe_status_string(int status) {
 }
 
 const char* amoe_last_error_string(void) { return amoe::g_last_error; }
+
+unsigned long long amoe_launch_count(void) { return amoe::launches_so_far(); }
 
 int amoe_check_device(void) {
   int dev = 0;

@@ -243,9 +243,9 @@ __global__ void __launch_bounds__(256) ir_grad_reduce_kernel(const float* __rest
 
 // ws layout: double sum[E], double sq[E]
 template <typename T>
-__global__ void std_sum_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ x_row,
-                               const int32_t* __restrict__ offsets, int E, int pass, const double* __restrict__ mean,
-                               double* __restrict__ accum) {
+__global__ void std_sum_kernel(const T* __restrict__ x, int64_t stride, int K, int64_t x_rows,
+                               const int32_t* __restrict__ x_row, const int32_t* __restrict__ offsets, int E, int pass,
+                               const double* __restrict__ mean, double* __restrict__ accum, int32_t* status) {
   // one warp per sorted position; block-level reduce per expert would need segmenting, so use one
   // double atomic per warp (count of atomics = P, all on E addresses; this runs a handful of times
   // per training run).
@@ -260,7 +260,12 @@ __global__ void std_sum_kernel(const T* __restrict__ x, int64_t stride, int K, c
     if (offsets[mid] <= i) lo = mid; else hi = mid;
   }
   const int e = lo;
-  const T* row = x + static_cast<int64_t>(x_row[i]) * stride;
+  const int64_t src = x_row[i];
+  if (src < 0 || src >= x_rows) {   // recorded and skipped, never dereferenced
+    if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 40, static_cast<int>(i), static_cast<int>(src));
+    return;
+  }
+  const T* row = x + src * stride;
   double acc = 0.0;
   if (pass == 0) {
     for (int k = lane; k < K; k += 32) acc += static_cast<double>(to_f32<T>(row[k]));
@@ -513,12 +518,12 @@ int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets
 
 size_t amoe_expert_std_workspace_bytes(int32_t E) { return E > 0 ? static_cast<size_t>(E) * 3 * sizeof(double) : 0; }
 
-int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* x_row,
                     const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out, void* workspace,
-                    size_t workspace_bytes, amoe_stream_t stream_) {
+                    size_t workspace_bytes, int32_t* dev_status, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(x && x_row && expert_offsets && std_out, AMOE_ERR_NULL_POINTER);
-  AMOE_REQUIRE(P > 0 && E > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(P > 0 && E > 0 && K > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(dtype == AMOE_F32 || dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(workspace && workspace_bytes >= amoe_expert_std_workspace_bytes(E), AMOE_ERR_WORKSPACE);
   double* sum = reinterpret_cast<double*>(workspace);
@@ -529,12 +534,12 @@ int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, con
   const unsigned eb = blocks_for(E, 128);
   for (int pass = 0; pass < 2; ++pass) {
     if (dtype == AMOE_F32)
-      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_row,
-                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq);
+      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_rows, x_row,
+                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq, dev_status);
     else
       std_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
-                                                                x_row, expert_offsets, E, pass, mean,
-                                                                pass == 0 ? sum : sq);
+                                                                x_rows, x_row, expert_offsets, E, pass, mean,
+                                                                pass == 0 ? sum : sq, dev_status);
     AMOE_LAUNCH_CHECK("std_sum");
     if (pass == 0) {
       std_mean_kernel<<<eb, 128, 0, stream>>>(sum, expert_offsets, E, K, mean);
@@ -546,12 +551,12 @@ int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, con
   return AMOE_OK;
 }
 
-int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
-                            const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
-                            amoe_stream_t stream_) {
+int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows,
+                           const int32_t* x_row, const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
+                           int32_t* dev_status, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(x && x_row && expert_offsets && std_out, AMOE_ERR_NULL_POINTER);
-  AMOE_REQUIRE(P > 0 && E > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(P > 0 && E > 0 && K > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
   if (E > kStaticStdMaxExperts) {
     set_last_error("amoe_expert_std_static: more experts than the built-in scratch holds (4096)", cudaErrorInvalidValue);
     return AMOE_ERR_BAD_SHAPE;
@@ -584,12 +589,12 @@ int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t
   const unsigned eb = blocks_for(E, 128);
   for (int pass = 0; pass < 2; ++pass) {
     if (dtype == AMOE_F32)
-      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_row,
-                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq);
+      std_sum_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, x_rows, x_row,
+                                                        expert_offsets, E, pass, mean, pass == 0 ? sum : sq, dev_status);
     else
       std_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K,
-                                                                x_row, expert_offsets, E, pass, mean,
-                                                                pass == 0 ? sum : sq);
+                                                                x_rows, x_row, expert_offsets, E, pass, mean,
+                                                                pass == 0 ? sum : sq, dev_status);
     AMOE_LAUNCH_CHECK("std_sum");
     if (pass == 0) {
       std_mean_kernel<<<eb, 128, 0, stream>>>(sum, expert_offsets, E, K, mean);

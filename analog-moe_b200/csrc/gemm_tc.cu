@@ -33,8 +33,6 @@
 //
 // Every mbarrier wait is bounded; on a time-out the CTA records AMOE_ERR_WAIT_LIMIT in the status
 // word, stops issuing work, drains and frees its TMEM.
-#include <cstdlib>
-
 #include "gemm_common.cuh"
 #include "tc_ptx.cuh"
 
@@ -248,12 +246,6 @@ __device__ __forceinline__ void teardown_cta(const SmemView& s, uint32_t tmem_ba
 }
 
 // ============================================================================ forward / dX
-#ifdef AMOE_TIMELINE
-__device__ long long g_timeline[4][512][4];
-#define TL(role, idx, k) do { if (blockIdx.x == 0 && (idx) < 512) g_timeline[role][idx][k] = clock64(); } while (0)
-#else
-#define TL(role, idx, k) do { } while (0)
-#endif
 // Rendezvous of a group of warps on an mbarrier whose arrival count is the number of warps.
 // `round` counts the uses of this barrier by the calling warp.  Returns false if the wait gave up.
 __device__ __forceinline__ bool group_sync(uint32_t bar, uint32_t round, volatile int* abort_flag, int32_t* status,
@@ -553,11 +545,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
             const int s = rp.s;
             const uint32_t ph = rp.ph;
-            TL(1, it, 0);
             if (!p.a_tma && !mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
-            TL(1, it, 1);
             if (!mbar_wait(bar_full_b(sm.bars, s), ph, sm.abort_flag, status, 4)) { alive = false; break; }
-            TL(1, it, 2);
             tc_fence_after();
             const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
             const uint64_t da_hi = make_smem_desc_sw128(sa);
@@ -572,7 +561,6 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
               if (p.a_split) umma_bf16(d_tmem, da_lo + adv, db_hi + adv, idesc, 1u);
             }
             umma_commit(bar_empty(sm.bars, s));
-            TL(1, it, 3);
           }
           if (alive) umma_commit(bar_tfull(sm.bars, buf));
         }
@@ -628,11 +616,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           }
           __syncwarp();
         }
-        if (ew == 0 && lane == 0) TL(3, acc_it, 0);
         bool ok = mbar_wait(bar_tfull(sm.bars, buf), aph, sm.abort_flag, status, 5, 128);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
-        if (ew == 0 && lane == 0) TL(3, acc_it, 1);
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(buf * p.BN);
         int slot = 0;
@@ -661,7 +647,6 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty(sm.bars, buf));
-        if (ew == 0 && lane == 0) TL(3, acc_it, 2);
       }
       if (!alive) break;
       if (p.epi.is_dx && (p.epi.ir_grad || p.epi.keep_count)) {
@@ -740,11 +725,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
           if (two && (it & 1u) != grp) continue;
           const int s = rp.s;
-          if (pt == 0) TL(2, it, 0);
           bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 6);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
-          if (pt == 0) TL(2, it, 1);
           const uint32_t a_hi = sm.base_u32 + s * p.stage_bytes;
           const uint32_t a_lo = a_hi + kATile;
           const bool full_k = (kc + 1) * kBK <= p.Kc && p.vec_ok;
@@ -834,11 +817,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
               }
             }
           }
-          if (pt == 0) TL(2, it, 2);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
-          if (pt == 0) TL(2, it, 3);
         }
       }
     }
@@ -1509,7 +1490,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   }
   // two prologue groups on alternate stages (both groups have the same number of warps, so every stage's barrier
   // expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
-  if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8 && std::getenv("AMOE_ONE_GROUP") == nullptr)
+  if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8)
     p.prod_groups = 2;
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
@@ -1568,16 +1549,6 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   AMOE_LAUNCH_CHECK("cvmm_tc");
   return AMOE_OK;
 }
-
-#ifdef AMOE_TIMELINE
-extern "C" int amoe_debug_timeline(long long* host, int clear) {
-  if (clear) {
-    static long long zeros[4 * 512 * 4] = {0};
-    return cudaMemcpyToSymbol(g_timeline, zeros, sizeof(zeros)) == cudaSuccess ? 0 : 5;
-  }
-  return cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * 4 * 512 * 4) == cudaSuccess ? 0 : 5;
-}
-#endif
 
 size_t dw_tc_workspace_bytes(int64_t P, int64_t expected, int E, int K, int N) {
   const int seg = dw_segment_slots(expected > 0 && expected < P ? expected : P, K, N);

@@ -34,10 +34,17 @@ CONFIGS = {
     "c5": dict(T=8192, k=6, D=1536, F=192, E=48, dtype="bf16", out_noise=0.02, w_noise=0.01, adc=True, bwd=True,
                out_res=62.0),
 }
-# DRAM bytes (read + write) per launch of the config-2 kernels from the ncu capture summarised in
-# profiles/cvmm_tc_kernel_c2_ncu_full.md; other configs have no capture (traffic stays null).
-NCU_TRAFFIC_C2 = {"amoe_cvmm_fwd[up]": 197.3e6, "amoe_cvmm_fwd[down]": 17.4e6, "amoe_cvmm_dw[down]": 167.4e6,
-                  "amoe_cvmm_dx[down]": 210.4e6, "amoe_cvmm_dw[up]": 167.2e6, "amoe_cvmm_dx[up]": 180.3e6}
+
+
+def ncu_traffic(config):
+    """DRAM bytes (read + write) per launch of each library call, as ncu measured them: read from the JSON file that
+    sits beside the ncu summary of the same capture (null for configurations without a capture)."""
+    path = os.path.join(ROOT, "profiles", f"dram_traffic_{config}.json")
+    if not os.path.exists(path):
+        return {}
+    return json.load(open(path)).get("bytes_per_launch", {})
+
+
 OUT_BOUND = 12.0     # ADC clip in units of the column weight maximum (aihwkit's default out_bound)
 SEED = 1234
 
@@ -146,35 +153,6 @@ def step(layer, x, gy, bwd):
     return y
 
 
-def kernel_times(path, layer, xs, gys, bwd, rank, world):
-    """Device time per kernel over three eager steps (torch profiler, CUDA activity only), written to `path` by rank 0:
-    one line per rank with the totals of the kernel families, then rank 0's table.  Not a bench value: kernels of
-    different streams overlap in the step, and collectives include the time they wait for the other ranks."""
-    from torch.profiler import profile, ProfilerActivity
-    n = 3
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for i in range(n):
-            step(layer, xs[i % len(xs)], gys[i % len(xs)], bwd)
-        torch.cuda.synchronize()
-    ka = prof.key_averages()
-
-    def tot(pat):
-        return sum(e.device_time_total for e in ka if pat in e.key) / n
-
-    line = (f"rank {rank}: cvmm_tc {tot('cvmm_tc'):.0f}  dw_tc {tot('dw_tc'):.0f}  ep_put {tot('ep_put_kernel'):.0f}  "
-            f"ep_put_back {tot('ep_put_back'):.0f}  all kernels but nccl "
-            f"{sum(e.device_time_total for e in ka if 'nccl' not in e.key) / n:.0f} us per step")
-    lines = [line]
-    if world > 1:
-        import torch.distributed as dist
-        lines = [None] * world
-        dist.all_gather_object(lines, line)
-    if rank == 0:
-        with open(path, "w") as f:
-            f.write("\n".join(lines) + "\n")
-            f.write(ka.table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=80))
-
-
 def run_ours(args, cfg, rank, world, device):
     from analog_moe import ops, _cabi
     # parameters' AccumulateGrad nodes are created during warm-up on the default stream and used again under graph
@@ -208,7 +186,8 @@ def run_ours(args, cfg, rank, world, device):
         step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
     barrier()
     if args.kernel_times:
-        kernel_times(args.kernel_times, layer, xs, gys, bwd, rank, world)
+        from analog_moe.profiling import kernel_times
+        kernel_times(args.kernel_times, lambda i: step(layer, xs[i % n_sets], gys[i % n_sets], bwd), rank, world)
         return None
     # One CUDA graph per input set (whole step: routing, both projections, backward).  The Philox
     # offsets come from a device counter that the graph itself advances, so replays draw new noise.
@@ -441,7 +420,7 @@ def main():
         if is_gemm:
             ach = gemm_flops / (kern[top]["ms_avg"] * 1e-3) / 1e12
             roof = dict(kernel=top, bound="tensor", achieved=ach, peak=pk["tf"], unit="TFLOP/s", frac=ach / pk["tf"],
-                        traffic=NCU_TRAFFIC_C2.get(top) if args.config == "c2" and world == 1 else None,
+                        traffic=ncu_traffic(args.config).get(top) if world == 1 else None,
                         peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
         else:
             roof = dict(kernel=top, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,

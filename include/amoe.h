@@ -51,6 +51,9 @@ int amoe_version(void);
 const char* amoe_status_string(int status);
 /* Text of the last CUDA error this thread's calls ran into ("" if none). */
 const char* amoe_last_error_string(void);
+/* Number of kernels the calling thread's calls into this library have launched so far (every kernel of the
+ * library is counted where it is launched; memsets and copies are not kernels and are not counted). */
+unsigned long long amoe_launch_count(void);
 /* AMOE_OK if the current CUDA device can run the kernels (compute capability 10.x). */
 int amoe_check_device(void);
 
@@ -331,14 +334,14 @@ int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets
 
 /* ------------------------------------------------------------------------------------------
  * Per-expert standard deviation of the routed rows.  Replaces cvmm_std and its two kernels
- * (cvmm.py:400-526).  x [R,K], x_row [P] by sorted position -> std [E] (NaN for experts without
+ * (cvmm.py:400-526).  x [x_rows,K], x_row [P] by sorted position -> std [E] (NaN for experts without
  * rows, as in the reference).  Workspace: amoe_expert_std_workspace_bytes(E) bytes, which the call
- * clears itself.
+ * clears itself.  A row index outside [0, x_rows) is recorded in dev_status (may be NULL) and skipped.
  * ---------------------------------------------------------------------------------------- */
 size_t amoe_expert_std_workspace_bytes(int32_t E);
-int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
+int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* x_row,
                     const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out, void* workspace,
-                    size_t workspace_bytes, amoe_stream_t stream);
+                    size_t workspace_bytes, int32_t* dev_status, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * amoe_expert_std_static: the same statistic as amoe_expert_std for callers that must not
@@ -363,9 +366,9 @@ int amoe_expert_std(const void* x, int32_t dtype, int64_t stride, int32_t K, con
  *     current).  Make that first call outside any stream capture.
  * Arguments and result are those of amoe_expert_std without the workspace pair.
  * ---------------------------------------------------------------------------------------- */
-int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, const int32_t* x_row,
-                           const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
-                           amoe_stream_t stream);
+int amoe_expert_std_static(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows,
+                           const int32_t* x_row, const int32_t* expert_offsets, int64_t P, int32_t E, float* std_out,
+                           int32_t* dev_status, amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Expert-parallel exchange helpers (no counterpart in the reference, which is single-GPU).

@@ -22,13 +22,13 @@ def _both(lib, x, x_row, off, E, use_static):
     out = torch.full((E,), -1.0, dtype=torch.float32, device=x.device)
     stream = torch.cuda.current_stream().cuda_stream
     if use_static:
-        rc = lib.amoe_expert_std_static(x.data_ptr(), 0, x.stride(0), K, x_row.data_ptr(), off.data_ptr(), P, E,
-                                        out.data_ptr(), stream)
+        rc = lib.amoe_expert_std_static(x.data_ptr(), 0, x.stride(0), K, x.shape[0], x_row.data_ptr(), off.data_ptr(),
+                                        P, E, out.data_ptr(), None, stream)
     else:
         nbytes = lib.amoe_expert_std_workspace_bytes(E)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-        rc = lib.amoe_expert_std(x.data_ptr(), 0, x.stride(0), K, x_row.data_ptr(), off.data_ptr(), P, E,
-                                 out.data_ptr(), ws.data_ptr(), nbytes, stream)
+        rc = lib.amoe_expert_std(x.data_ptr(), 0, x.stride(0), K, x.shape[0], x_row.data_ptr(), off.data_ptr(), P, E,
+                                 out.data_ptr(), ws.data_ptr(), nbytes, None, stream)
     assert rc == 0, lib.amoe_status_string(rc)
     torch.cuda.synchronize()
     return out.cpu()
@@ -60,6 +60,7 @@ def test_static_scratch_entry_point_rejects_too_many_experts():
     idx = torch.zeros(4, dtype=torch.int32, device=dev)
     off = torch.zeros(5000, dtype=torch.int32, device=dev)
     out = torch.zeros(5000, device=dev)
-    rc = lib.amoe_expert_std_static(x.data_ptr(), 0, 8, 8, idx.data_ptr(), off.data_ptr(), 4, 4097, out.data_ptr(), None)
+    rc = lib.amoe_expert_std_static(x.data_ptr(), 0, 8, 8, 4, idx.data_ptr(), off.data_ptr(), 4, 4097, out.data_ptr(), None,
+                                    None)
     assert rc == 1
     assert b"4096" in lib.amoe_last_error_string()
