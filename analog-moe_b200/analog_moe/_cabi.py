@@ -38,6 +38,7 @@ class WeightPrepassArgs(C.Structure):
         ("discretize_res", C.c_float), ("seed", C.c_uint64), ("offset", C.c_uint32), ("step_dev", vp),
         ("col_scale", vp), ("col_inv_scale", vp), ("w_out", vp), ("fwd_hi", vp), ("fwd_lo", vp), ("bwd_hi", vp), ("bwd_lo", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t),
+        ("clip_sigma", C.c_float), ("clip_per_channel", C.c_int32), ("clip_fixed", C.c_float), ("w_clip_out", vp),
     ]
 
 
@@ -102,6 +103,7 @@ SIGNATURES = {
                                       C.c_int32, C.c_int32, vp, C.c_int32, C.c_int64, vp]),
     "amoe_expert_offsets": (C.c_int, [vp, C.c_int64, C.c_int32, vp, vp, vp]),
     "amoe_weight_prepass_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "amoe_weight_prepass_clip_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "amoe_prepared_dims": (None, [C.c_int32, C.c_int32, C.POINTER(C.c_int32 * 4)]),
     "amoe_weight_prepass": (C.c_int, [C.POINTER(WeightPrepassArgs), vp]),
     "amoe_row_absmax": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp]),

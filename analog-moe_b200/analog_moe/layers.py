@@ -14,6 +14,8 @@ modifier, output noise, and - new here - ADC output quantisation.
 """
 from __future__ import annotations
 
+import re
+from functools import partial
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -21,8 +23,8 @@ import torch.nn.functional as F
 from torch import Tensor, nn
 
 from . import ops
-from .rpu_config import TorchInferenceRPUConfig, WeightClipType
-from .triton_src.cvmm import CVMM, CVMMExt, CVMMSel, PhiloxNoise, WeightModifier, cvmm_std
+from .rpu_config import TorchInferenceRPUConfig, WeightClipType, aihwkit_rpu_config
+from .triton_src.cvmm import CVMM, CVMMExt, CVMMSel, PhiloxNoise, WeightModifier, _uses_abs_max, cvmm_std, select_sort_op
 
 
 class _BroadcastInputRange(torch.autograd.Function):
@@ -79,19 +81,21 @@ class _FusedAnalogStep(torch.autograd.Function):
         if x2.stride(-1) != 1:
             x2 = x2.contiguous()
         precision = layer._precision(x)
-        per_channel = bool(getattr(fwd, "out_noise_per_channel", True))
+        per_channel = layer._scale_per_channel()
+
+        clip = layer._take_pending_clip()       # weight clipping left over from post_update_step, done in the pre-pass
 
         def prepass(w, mod):
             return ops.weight_prepass(
                 w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
                 noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,
                 seed=mod.seed if mod else 0, offset=mod.offset if mod else 0, step_dev=mod.step if mod else None,
-                need_fwd=True, need_bwd=True)
+                need_fwd=True, need_bwd=True, **clip)
 
         def noise_args():
-            if layer.training and fwd.out_noise > 0:
-                return dict(noise_std=float(fwd.out_noise), seed=layer.noise_seed, offset=layer._next_offset(),
-                            step_dev=layer.noise_step)
+            std = layer._out_noise_std()
+            if std > 0:
+                return dict(noise_std=std, seed=layer.noise_seed, offset=layer._next_offset(), step_dev=layer.noise_step)
             return {}
 
         # The two weight pre-passes depend on nothing but the weights: they run on a second stream beside the
@@ -110,8 +114,7 @@ class _FusedAnalogStep(torch.autograd.Function):
             pw_dn = prepass(values, mod_dn)
         ops.set_tag("up")
         r, _ = ops.router_select(x2, w_sel, k, getattr(layer, "router_bias", None))
-        inp_res = fwd.inp_res
-        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1.0
+        inp_res = float(layer._inp_res())
         if os.environ.get("_AIHWKIT_NO_ROUNDING", False):
             assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
             inp_res = -1.0
@@ -124,7 +127,8 @@ class _FusedAnalogStep(torch.autograd.Function):
         # ---- up-projection (+ ReLU)
         nz = nz_up
         ir_up = ir_all[0] if has_ir else None
-        am_up = None if has_ir else ops.row_absmax(x2)
+        use_am = _uses_abs_max(ir_p, fwd)
+        am_up = ops.row_absmax(x2) if use_am else None
         # operands of the two weight gradients, written while the forward kernels hold the rows anyway
         N = values.shape[-1]
         Fh = keys.shape[-1]
@@ -150,7 +154,7 @@ class _FusedAnalogStep(torch.autograd.Function):
         ops.set_tag("down")
         nz = nz_dn
         ir_dn = ir_all[1] if has_ir else None
-        am_dn = None if has_ir else ops.row_absmax(h)
+        am_dn = ops.row_absmax(h) if use_am else None
         # (the composition hands the gate over in the activation dtype: rounded for bf16 layers)
         if tiles:
             cache_kw = dict(a_tiles=hq)
@@ -278,6 +282,60 @@ class _FusedAnalogStep(torch.autograd.Function):
         return (None, grad_x.view(x_shape) if need_x else None, grad_sel, grad_keys, grad_values, grad_ir)
 
 
+class MoEConifgError(Exception):
+    """Configuration the analog sigma-MoE layers do not support (name as in the reference layers, :25/:29)."""
+
+
+# --------------------------------------------------------------------------- checkpoint formats
+# A non-traceable layer stores `input_range` [2, E] and a scalar `input_range_update_idx`; the reference's traceable
+# mode stores one analog linear module per expert instead, each with its own `input_range` [1],
+# `input_range_update_idx` [1], `x_min` [1], `x_max` [1] (reference moe_layer_aihwkit_lightning.py:33-131).
+
+def non_traceable_to_traceable(state_dict, prefix: str) -> None:
+    """In place: `input_range`/`input_range_update_idx` of a non-traceable layer as per-expert entries."""
+    ir = state_dict.pop(prefix + "input_range")
+    idx = state_dict.pop(prefix + "input_range_update_idx")
+    for row, name in enumerate(("keys", "values")):
+        for e in range(ir.shape[1]):
+            base = f"{prefix}{name}.{e}."
+            state_dict[base + "input_range"] = ir[row, e].reshape(1)
+            state_dict[base + "input_range_update_idx"] = idx.reshape(1)
+            state_dict[base + "x_min"] = torch.zeros(1, device=ir.device, dtype=ir.dtype)
+            state_dict[base + "x_max"] = torch.zeros(1, device=ir.device, dtype=ir.dtype)
+
+
+def traceable_to_non_traceable(state_dict, prefix: str) -> None:
+    """In place: per-expert entries of a traceable checkpoint as `input_range` [2, E] and one update index."""
+    pat = re.compile(rf"^{re.escape(prefix)}(keys|values)\.(\d+)\.(input_range|input_range_update_idx|x_min|x_max)$")
+    found = {}
+    for name in list(state_dict):
+        m = pat.match(name)
+        if m:
+            found[(m.group(1), int(m.group(2)), m.group(3))] = name
+    experts = sorted({e for (_, e, _) in found})
+    rows = []
+    for which in ("keys", "values"):
+        rows.append(torch.cat([state_dict[found[(which, e, "input_range")]].reshape(1) for e in experts]))
+    first_idx = state_dict[found[("keys", experts[0], "input_range_update_idx")]]
+    for name in found.values():
+        state_dict.pop(name)
+    state_dict[prefix + "input_range"] = torch.stack(rows)
+    state_dict[prefix + "input_range_update_idx"] = first_idx.reshape(())
+
+
+def _convert_checkpoint_format(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs,
+                               traceable: bool = False) -> None:
+    """Load pre-hook (reference moe_layer_aihwkit_lightning.py:107-131): bring the input-range entries into the format
+    of the layer that is loading them."""
+    if not any("input_range" in k for k in state_dict):
+        return
+    is_non_traceable = prefix + "input_range" in state_dict
+    if traceable and is_non_traceable:
+        non_traceable_to_traceable(state_dict, prefix)
+    elif not traceable and not is_non_traceable:
+        traceable_to_non_traceable(state_dict, prefix)
+
+
 class SigmaMoELayer(nn.Module):
     def __init__(self, d_model: int, n_experts: int, expert_size: int, k: int, dropout: float = 0.0,
                  selection_mode: str = "sigmoid", activation_after_topk: bool = False,
@@ -340,11 +398,11 @@ class SigmaMoELayer(nn.Module):
         if getattr(self, "router_bias", None) is not None:      # fixed per-expert logit offset (skew studies)
             logits = logits + self.router_bias
         bsz, seq, _ = inp.shape
-        r = ops.select_sort(logits.detach(), self.n_heads, apply_sigmoid=True)
-        raw_sel = r.raw_sel.view(bsz, seq, self.n_heads)
+        raw_sel, _, ssel, token_index, slot_index, offsets = select_sort_op(logits.detach(), self.n_heads, True)
+        raw_sel = raw_sel.view(bsz, seq, self.n_heads)
         # gate values with gradient: recompute the k picked sigmoids from the logits (tiny gather)
         gate = torch.sigmoid(logits.float()).gather(-1, raw_sel.long()).to(inp.dtype)
-        sel = CVMMSel(raw_sel, r.sel.view(bsz, seq, self.n_heads), r.token_index, r.slot_index, None, r.expert_offsets)
+        sel = CVMMSel(raw_sel, ssel.view(bsz, seq, self.n_heads), token_index, slot_index, None, offsets)
         return sel, gate
 
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
@@ -377,7 +435,11 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.fused = True          # one autograd node for the whole layer when the configuration allows it
         self.operand_caches = True  # forward / dX kernels leave bf16 copies of the dW operands (fused path)
         self.hidden_tiles = True    # the up-projection leaves the hidden rows as the down-projection's A tiles
+        self.fuse_clip = False      # post_update_step only records the clipping; the next forward's weight pre-pass
+                                    # clips in place while it reads the weights anyway (until then they are unclipped)
+        self._pending_clip = None
         self._noise_calls = 0
+        self._register_load_state_dict_pre_hook(partial(_convert_checkpoint_format, traceable=False))
         ir = self.rpu_config.pre_post.input_range
         self.input_range = None
         if ir.enable:
@@ -402,7 +464,25 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
     def _precision(self, inputs: Tensor) -> int:
         return self.precision if self.precision is not None else ops.default_precision(inputs.dtype)
 
+    # -- what the two reference layers decide differently lives in these four methods
+    def _inp_res(self) -> float:
+        """lightning :451-456: 254 -> 2/254 = 1/127; values below 1 are a resolution already."""
+        inp_res = self.rpu_config.forward.inp_res
+        return (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1
+
+    def _out_noise_std(self) -> float:
+        """lightning :472: output noise only while training."""
+        std = float(self.rpu_config.forward.out_noise)
+        return std if (self.training and std > 0) else 0.0
+
+    def _scale_per_channel(self) -> bool:
+        """Per-column (True) or per-expert weight maximum as the scale of output noise and ADC (lightning :480-487)."""
+        return bool(getattr(self.rpu_config.forward, "out_noise_per_channel", True))
+
     def _weight_modifier(self) -> Optional[WeightModifier]:
+        """lightning :313-382 as parameters of the weight pre-pass.  The per-channel variants use the per-column
+        maximum; the reference's lightning layer leaves ADD_NORMAL_PER_CHANNEL out of its per-channel list (:334-338)
+        and so falls back to the per-expert maximum for that type, which is not reproduced here."""
         mod = self.rpu_config.modifier
         name = _enum_name(mod.type)
         if name in ("NONE", "None") or not (self.training or mod.enable_during_test):
@@ -439,14 +519,13 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
                 bir = _BroadcastInputRange.apply(self.input_range[ir_idx], sel_indices.sel, sel_indices.expert_offsets)
             else:
                 bir = self.input_range[ir_idx][sel_indices.sel.long()]              # lightning :447-448
-        inp_res = cfg.forward.inp_res
-        inp_res = (2.0 / inp_res if inp_res > 1.0 else 2.0 * inp_res) if inp_res > 0 else -1   # lightning :451-456
+        inp_res = self._inp_res()
         noise = None
-        if self.training and cfg.forward.out_noise > 0:                             # lightning :471-492
-            noise = PhiloxNoise(float(cfg.forward.out_noise), self.noise_seed, self._next_offset(), self.noise_step)
+        std = self._out_noise_std()
+        if std > 0:                                                                 # lightning :471-492
+            noise = PhiloxNoise(std, self.noise_seed, self._next_offset(), self.noise_step)
         ext = CVMMExt(noise=noise, modifier=self._weight_modifier(), out_res=float(cfg.forward.out_res),
-                      out_bound=float(cfg.forward.out_bound),
-                      scale_per_channel=bool(getattr(cfg.forward, "out_noise_per_channel", True)),
+                      out_bound=float(cfg.forward.out_bound), scale_per_channel=self._scale_per_channel(),
                       precision=self._precision(inputs), expert_offsets=sel_indices.expert_offsets)
         return CVMM.apply(inputs, sel_indices.sel_index, sel_indices.sel, weights, inp_res, bir,
                           sel_indices.out_index, sel_indices.reduction_weight, None, ir_p, cfg.forward, ext)
@@ -455,6 +534,10 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         """The single-node path covers the common configuration; anything else takes the composition."""
         if not self.fused or type(self).cvmm_wrapper is not AnalogSigmaMoELayer.cvmm_wrapper:
             return False
+        if torch.compiler.is_compiling():
+            return False          # under torch.compile the layer is the composition of traceable operators
+        if self.input_range is not None and _uses_abs_max(self.rpu_config.pre_post.input_range, self.rpu_config.forward):
+            return False          # input range and abs-max scaling together (classic aihwkit, noise_management=ABS_MAX)
         if not (inp.is_cuda and inp.ndim == 3 and _is_relu(self.activation)) or self.bias is not None:
             return False
         if self.dropout > 0 and self.training:
@@ -469,7 +552,13 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
 
     def forward(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
         self._noise_calls = 0
-        if self._fused_ok(inp):
+        fused = self._fused_ok(inp)
+        if self._pending_clip is not None and not fused:
+            c = self._take_pending_clip()
+            for w in (self.keys, self.values):
+                ops.clip_weights_(w.data, sigma=c["clip_sigma"], per_channel=c["clip_per_channel"],
+                                  fixed_value=c["clip_fixed"])
+        if fused:
             y = _FusedAnalogStep.apply(self, inp, self.expert_sel.weight, self.keys, self.values, self.input_range)
             out = (y, self._aux_zero)
         else:
@@ -482,15 +571,145 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         if _enum_name(self.rpu_config.clip.type) not in ("NONE", "None"):
             self.clip_weights()
 
-    @torch.no_grad()
-    def clip_weights(self) -> None:
-        """lightning :519-543: clamp to +-sigma*std per expert (or per column)."""
+    def _clip_args(self) -> Optional[dict]:
+        """lightning :519-543 as arguments of the weight pre-pass: clamp to +-sigma*std per expert (LAYER_GAUSSIAN) or
+        per column (LAYER_GAUSSIAN_PER_CHANNEL)."""
         clip = self.rpu_config.clip
         name = _enum_name(clip.type)
         if name in ("NONE", "None"):
-            return
+            return None
         assert clip.sigma > 0, "Clip sigma must be greater than 0"
-        dims = (1, 2) if clip.type == WeightClipType.LAYER_GAUSSIAN or name == "LAYER_GAUSSIAN" else 1
+        if name not in ("LAYER_GAUSSIAN", "LAYER_GAUSSIAN_PER_CHANNEL"):
+            raise ValueError(f"Unknown clip type {clip.type}")
+        return dict(clip_sigma=float(clip.sigma), clip_per_channel=name.endswith("PER_CHANNEL"), clip_fixed=-1.0)
+
+    def _take_pending_clip(self) -> dict:
+        c, self._pending_clip = self._pending_clip, None
+        return c or {}
+
+    @torch.no_grad()
+    def clip_weights(self, clip=None) -> None:
+        """Statistics and clamp run in the library's weight pre-pass kernels; with `fuse_clip` they wait for the
+        pre-pass of the next forward."""
+        args = self._clip_args()
+        if args is None:
+            return
+        if self.fuse_clip:
+            self._pending_clip = args
+            return
         for w in (self.keys, self.values):
-            bound = clip.sigma * w.std(dims, keepdim=True)
-            w.data = torch.maximum(torch.minimum(w.data, bound), -bound)
+            ops.clip_weights_(w.data, sigma=args["clip_sigma"], per_channel=args["clip_per_channel"],
+                              fixed_value=args["clip_fixed"])
+
+    # -- checkpoints: the configuration travels in the state dict's metadata (lightning :545-570)
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        destination._metadata[prefix.split(".")[0]]["rpu_config"] = self.rpu_config
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        # a checkpoint written by the reference has no Philox step counter: keep the current one
+        state_dict.setdefault(prefix + "noise_step", self.noise_step)
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+        if "rpu_config" in local_metadata:
+            self.rpu_config = local_metadata["rpu_config"]
+
+
+# The reference's name for the aihwkit-lightning flavour of the layer (moe_layer_aihwkit_lightning.py:134).
+AnalogSigmaMoELayerAIHWKITLightning = AnalogSigmaMoELayer
+
+
+class AnalogSigmaMoELayerAIHWKIT(AnalogSigmaMoELayer):
+    """The classic-aihwkit flavour (reference moe_layer_aihwkit.py:28-437): same kernels, different configuration
+    policy - the weight maximum that scales weight and output noise follows `remap.type`, `forward.is_perfect`
+    switches quantisation and noise off, abs-max input scaling follows `forward.noise_management`, clipping knows
+    FIXED_VALUE, and the configuration is stored as an `analog_tile_state` entry of the state dict."""
+
+    def __init__(self, rpu_config: Optional[TorchInferenceRPUConfig] = None, *args, **kwargs):
+        cfg = rpu_config if rpu_config is not None else aihwkit_rpu_config()
+        fwd = cfg.forward
+        # reference :47-61 (the two out_* asserts are gone: the ADC is implemented here)
+        assert getattr(fwd, "inp_bound", 1.0) in [-1, 1.0], "inp_bound must be 1.0 or off (=-1)"
+        assert cfg.mapping.max_input_size == 0, "max_input_size must be 0"
+        assert getattr(cfg.mapping, "max_output_size", 0) == 0, "max_output_size must be 0"
+        assert _enum_name(getattr(fwd, "bound_management", "NONE")) in ("NONE", "None"), "bound_management must be NONE"
+        super().__init__(cfg, *args, **kwargs)
+        # aihwkit hangs an `analog_ctx` parameter on every analog layer (reference :141-142); it carries no data the
+        # kernels use, but checkpoints contain the entry
+        self.analog_ctx = nn.Parameter(torch.ones(()), requires_grad=False)
+
+    def _perfect(self) -> bool:
+        return bool(getattr(self.rpu_config.forward, "is_perfect", False))
+
+    def _remap(self) -> str:
+        return _enum_name(self.rpu_config.remap.type)
+
+    def _inp_res(self) -> float:
+        return -1 if self._perfect() else super()._inp_res()                          # reference :247-249
+
+    def _out_noise_std(self) -> float:
+        return 0.0 if self._perfect() else super()._out_noise_std()                    # reference :257-261
+
+    def _scale_per_channel(self) -> bool:
+        remap = self._remap()                                                         # reference :267-282
+        if remap in ("CHANNELWISE_SYMMETRIC", "NONE", "None"):
+            return True
+        if remap == "LAYERWISE_SYMMETRIC":
+            return False
+        raise MoEConifgError(f"Weight remap type {self.rpu_config.remap.type} not supported")
+
+    def _weight_modifier(self) -> Optional[WeightModifier]:
+        mod = self.rpu_config.modifier                                                # reference :144-196
+        if not (self.training or mod.enable_during_test):
+            return None
+        if getattr(mod, "per_batch_sample", False):
+            raise MoEConifgError("per_batch_sample not implemented")
+        name = _enum_name(mod.type)
+        if name in ("NONE", "None", "COPY"):
+            return None
+        if name != "ADD_NORMAL":
+            raise MoEConifgError(f"Weight modifier {mod.type} not supported")
+        remap = self._remap()
+        if remap not in ("CHANNELWISE_SYMMETRIC", "LAYERWISE_SYMMETRIC"):
+            raise MoEConifgError(f"Weight remap type {self.rpu_config.remap.type} not supported")
+        return WeightModifier(std_dev=float(mod.std_dev), per_channel=remap == "CHANNELWISE_SYMMETRIC",
+                              seed=self.noise_seed, offset=self._next_offset(), step=self.noise_step)
+
+    def _clip_args(self) -> Optional[dict]:
+        """reference :314-340."""
+        clip = self.rpu_config.clip
+        name = _enum_name(clip.type)
+        if name in ("NONE", "None"):
+            return None
+        if name == "FIXED_VALUE":
+            return dict(clip_sigma=-1.0, clip_per_channel=False, clip_fixed=float(clip.fixed_value))
+        if name == "LAYER_GAUSSIAN":
+            return dict(clip_sigma=float(clip.sigma), clip_per_channel=False,
+                        clip_fixed=float(clip.fixed_value) if clip.fixed_value > 0 else -1.0)
+        if name == "AVERAGE_CHANNEL_MAX":
+            raise NotImplementedError("AVERAGE_CHANNEL_MAX not implemented")
+        raise MoEConifgError(f"Unknown clip type {clip.type}")
+
+    # -- checkpoints: the configuration is an `analog_tile_state` entry (reference :372-415)
+    def load_state_dict(self, state_dict, strict: bool = True, load_rpu_config: Optional[bool] = None,
+                        strict_rpu_config_check: Optional[bool] = None):
+        tile_state = state_dict.pop("analog_tile_state", None)
+        if load_rpu_config:
+            self.rpu_config = tile_state["rpu_config"]
+        if strict_rpu_config_check and not isinstance(tile_state["rpu_config"], type(self.rpu_config)) \
+                and not isinstance(self.rpu_config, type(tile_state["rpu_config"])):
+            raise MoEConifgError(f"RPU config mismatch: cannot replace {type(tile_state['rpu_config']).__name__} "
+                                 f"with {type(self.rpu_config).__name__}")
+        return super().load_state_dict(state_dict, strict)
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        SigmaMoELayer._save_to_state_dict(self, destination, prefix, keep_vars)
+        destination[prefix + "analog_tile_state"] = {"rpu_config": self.rpu_config}
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        tile_state = state_dict.pop(prefix + "analog_tile_state", None)
+        if tile_state is not None:
+            self.rpu_config = tile_state["rpu_config"]
+        state_dict.setdefault(prefix + "noise_step", self.noise_step)
+        state_dict[prefix + "analog_ctx"] = self.analog_ctx.data      # whatever shape the writer's context had
+        SigmaMoELayer._load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys,
+                                            unexpected_keys, error_msgs)

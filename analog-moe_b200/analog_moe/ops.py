@@ -260,7 +260,10 @@ def prepared_dims(K: int, N: int) -> Tuple[int, int, int, int]:
 
 def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool = True, noise_std: float = 0.0,
                    noise_per_channel: bool = True, discretize_res: float = -1.0, seed: int = 0, offset: int = 0,
-                   step_dev: Optional[torch.Tensor] = None, need_fwd: bool = True, need_bwd: bool = True, need_w_out: bool = False) -> PreparedWeights:
+                   step_dev: Optional[torch.Tensor] = None, need_fwd: bool = True, need_bwd: bool = True,
+                   need_w_out: bool = False, clip_sigma: float = -1.0, clip_per_channel: bool = False,
+                   clip_fixed: float = -1.0) -> PreparedWeights:
+    """`clip_sigma` / `clip_fixed` > 0: the weights are clipped in place first (see clip_weights_) in the same pass."""
     A.require_cuda(w)
     E, K, N = w.shape
     dev = w.device
@@ -303,12 +306,35 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
         if need_w_out:
             out.w = torch.empty(E, K, N, dtype=torch.float32, device=dev)
             a.w_out = ptr(out.w)
-    nbytes = lib.amoe_weight_prepass_workspace_bytes(E, K, N)
+    clip = clip_sigma > 0 or clip_fixed > 0
+    if clip:
+        a.clip_sigma, a.clip_per_channel, a.clip_fixed, a.w_clip_out = float(clip_sigma), int(clip_per_channel), float(clip_fixed), ptr(w)
+        nbytes = lib.amoe_weight_prepass_clip_workspace_bytes(E, K, N)
+    else:
+        nbytes = lib.amoe_weight_prepass_workspace_bytes(E, K, N)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     _call("amoe_weight_prepass", C.byref(a), stream_ptr())
     out.workspace = ws       # stays alive with the result: the launch stream may differ from the allocating one
     return out
+
+
+def clip_weights_(w: torch.Tensor, sigma: float = -1.0, per_channel: bool = False, fixed_value: float = -1.0) -> None:
+    """In place: clamp w [E,K,N] to +-sigma*std (std of each expert, or of each column with `per_channel`), capped by
+    `fixed_value` when that is positive; sigma <= 0 clamps to +-fixed_value.  One pass for the statistics and one for
+    the clamp, both inside the weight pre-pass kernels."""
+    A.require_cuda(w)
+    E, K, N = w.shape
+    a = A.WeightPrepassArgs()
+    a.w, a.w_dtype, a.E, a.K, a.N = ptr(w), dtype_code(w), E, K, N
+    a.w_stride_e, a.w_stride_k, a.w_stride_n = w.stride()
+    a.per_channel_scale, a.noise_per_channel, a.discretize_res = 1, 1, -1.0
+    a.clip_sigma, a.clip_per_channel, a.clip_fixed, a.w_clip_out = float(sigma), int(per_channel), float(fixed_value), ptr(w)
+    nbytes = lib.amoe_weight_prepass_clip_workspace_bytes(E, K, N)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    a.workspace, a.workspace_bytes = ptr(ws), nbytes
+    _call("amoe_weight_prepass", C.byref(a), stream_ptr())
+    w._amoe_workspace = ws
 
 
 def row_absmax(x2: torch.Tensor) -> torch.Tensor:

@@ -4,7 +4,10 @@ The reference layers take an `aihwkit` / `aihwkit_lightning` `TorchInferenceRPUC
 packages are third-party.  The layer in this package only reads attributes, so a real
 `TorchInferenceRPUConfig` works in place of these dataclasses; they exist so that the layer can
 be built and tested without the third-party packages.  Field names and defaults follow what the
-reference reads (moe_layer_aihwkit_lightning.py:152-181, 433-492, 524-525).
+reference reads (moe_layer_aihwkit_lightning.py:152-181, 433-492, 524-525; the classic-aihwkit layer
+additionally reads forward.{inp_bound, bound_management, is_perfect, noise_management},
+mapping.max_output_size, modifier.per_batch_sample, remap.type and clip.fixed_value,
+moe_layer_aihwkit.py:47-61, 163, 173, 244, 267, 324-333).
 """
 from __future__ import annotations
 
@@ -24,8 +27,26 @@ class WeightModifierType(enum.Enum):
 
 class WeightClipType(enum.Enum):
     NONE = "None"
+    FIXED_VALUE = "FixedValue"
     LAYER_GAUSSIAN = "LayerGaussian"
     LAYER_GAUSSIAN_PER_CHANNEL = "LayerGaussianPerChannel"
+    AVERAGE_CHANNEL_MAX = "AverageChannelMax"
+
+
+class WeightRemapType(enum.Enum):
+    NONE = "None"
+    LAYERWISE_SYMMETRIC = "LayerwiseSymmetric"
+    CHANNELWISE_SYMMETRIC = "ChannelwiseSymmetric"
+
+
+class BoundManagementType(enum.Enum):
+    NONE = "None"
+    ITERATIVE = "Iterative"
+
+
+class NoiseManagementType(enum.Enum):
+    NONE = "None"
+    ABS_MAX = "AbsMax"
 
 
 @dataclass
@@ -35,6 +56,17 @@ class IOParameters:
     out_bound: float = -1.0
     out_noise: float = 0.0
     out_noise_per_channel: bool = True
+    # classic-aihwkit fields
+    inp_bound: float = 1.0
+    bound_management: BoundManagementType = BoundManagementType.NONE
+    noise_management: NoiseManagementType = NoiseManagementType.NONE
+
+
+@dataclass
+class AIHWKITIOParameters(IOParameters):
+    """`forward` of a classic-aihwkit configuration: the presence of `is_perfect` is what CVMM.forward
+    uses to tell the two parameter families apart (reference cvmm.py:727)."""
+    is_perfect: bool = False
 
 
 @dataclass
@@ -59,12 +91,19 @@ class WeightModifierParameter:
     res: float = 0.1
     std_dev: float = 0.0
     enable_during_test: bool = False
+    per_batch_sample: bool = False
 
 
 @dataclass
 class WeightClipParameter:
     type: WeightClipType = WeightClipType.NONE
     sigma: float = 2.5
+    fixed_value: float = -1.0
+
+
+@dataclass
+class WeightRemapParameter:
+    type: WeightRemapType = WeightRemapType.CHANNELWISE_SYMMETRIC
 
 
 @dataclass
@@ -80,3 +119,13 @@ class TorchInferenceRPUConfig:
     modifier: WeightModifierParameter = field(default_factory=WeightModifierParameter)
     clip: WeightClipParameter = field(default_factory=WeightClipParameter)
     mapping: MappingParameter = field(default_factory=MappingParameter)
+    remap: WeightRemapParameter = field(default_factory=WeightRemapParameter)
+
+
+def aihwkit_rpu_config() -> TorchInferenceRPUConfig:
+    """A configuration shaped like classic aihwkit's: `forward.is_perfect` exists, tile splitting is switched off
+    with 0 instead of -1 (reference moe_layer_aihwkit.py:57-58)."""
+    cfg = TorchInferenceRPUConfig(forward=AIHWKITIOParameters())
+    cfg.mapping.max_input_size = 0
+    cfg.mapping.max_output_size = 0
+    return cfg

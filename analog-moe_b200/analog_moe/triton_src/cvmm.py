@@ -14,9 +14,10 @@ from __future__ import annotations
 
 import os
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import List, Optional
 
 import torch
+from torch.multiprocessing.reductions import StorageWeakRef
 
 from .. import _cabi as A
 from .. import ops
@@ -44,12 +45,37 @@ def cvmm_prepare_sel(sel: torch.Tensor, n_experts: int) -> CVMMSel:
     return CVMMSel(sel, ssel.view_as(sel), sel_index, None)
 
 
+@torch.library.custom_op("amoe::cvmm_std", mutates_args=())
 def cvmm_std(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor, n_experts: int) -> torch.Tensor:
     """Per-expert std of the routed rows (reference cvmm.py:400-443)."""
     A.require_cuda(x)
     ssel = ops.i32(sel)
     off = ops.expert_offsets(ssel, n_experts)
     return ops.expert_std(x, ops.i32(sel_index), off, n_experts).to(x.dtype)
+
+
+@cvmm_std.register_fake
+def _cvmm_std_fake(x, sel_index, sel, n_experts):
+    return x.new_empty(n_experts)
+
+
+@torch.library.custom_op("amoe::select_sort", mutates_args=())
+def select_sort_op(logits: torch.Tensor, k: int, apply_sigmoid: bool) -> List[torch.Tensor]:
+    """Gate selection and expert-contiguous slot sort (the base layer's sigmoid / top-k and cvmm_prepare_sel's sort,
+    reference tests/test_moe_layer_aihwkit.py:71-76, cvmm.py:31-34) as one operator:
+    [raw_sel [T,k], gate [T,k], sel [P], token_index [P], slot_index [P], expert_offsets [E+1]]."""
+    r = ops.select_sort(logits, k, apply_sigmoid)
+    return [r.raw_sel, r.gate, r.sel, r.token_index, r.slot_index, r.expert_offsets]
+
+
+@select_sort_op.register_fake
+def _select_sort_fake(logits, k, apply_sigmoid):
+    E = logits.shape[-1]
+    T = logits.numel() // E
+    i32 = dict(dtype=torch.int32)
+    new = logits.new_empty
+    return [new(T, k, **i32), new(T, k, dtype=torch.float32), new(T * k, **i32), new(T * k, **i32), new(T * k, **i32),
+            new(E + 1, **i32)]
 
 
 @dataclass
@@ -99,158 +125,304 @@ def _uses_abs_max(ir_params, io_params) -> bool:
     return getattr(nm, "name", str(nm)).split(".")[-1] == "ABS_MAX"
 
 
+# --------------------------------------------------------------------------- the operator boundary
+# The reference registers its forward as a torch.library operator with a fake ("abstract") implementation so that
+# torch.compile can trace through CVMM.apply (cvmm.py:529, 634-642).  Here both directions are operators
+# (`amoe::cvmm_forward`, `amoe::cvmm_backward`): their real implementations drive the C ABI, their fake ones only
+# compute shapes, and the autograd.Function below is plain tensor glue around them.  Tensors an operator does not
+# produce in a given mode come back as empty (numel 0) tensors: operator outputs cannot be optional.
+
+def _none_if_empty(t: torch.Tensor) -> Optional[torch.Tensor]:
+    return t if t.numel() > 0 else None
+
+
+def _empty(like: torch.Tensor, dtype=None) -> torch.Tensor:
+    return like.new_empty(0, dtype=dtype or like.dtype)
+
+
+# prepared weights of unmodified weight tensors, kept while the tensor has not been written to
+_PREPARED = {}
+
+
+def _prepared_weights(keys: torch.Tensor, precision: int, per_channel: bool, mod_std: float, mod_per_channel: bool,
+                      mod_disc: float, mod_seed: int, mod_offset: int, mod_step: Optional[torch.Tensor]):
+    """Weight pre-pass, skipped when these exact weights (same storage, same version counter) were prepared before and
+    no modifier changes them from call to call: an inference layer pays for it once, not on every CVMM.apply."""
+    modified = mod_std > 0 or mod_disc > 0
+    if modified:
+        return ops.weight_prepass(keys, precision, per_channel_scale=per_channel, noise_std=mod_std,
+                                  noise_per_channel=mod_per_channel, discretize_res=mod_disc, seed=mod_seed,
+                                  offset=mod_offset, step_dev=mod_step, need_fwd=True, need_bwd=True)
+    key = (keys.data_ptr(), tuple(keys.shape), tuple(keys.stride()), keys.dtype, keys.device, precision, per_channel)
+    hit = _PREPARED.get(key)
+    # valid while the storage is the one that was prepared (a freed storage's address can be handed out again) and
+    # nothing has written to the tensor since
+    if hit is not None and not hit[0].expired() and hit[1] == keys._version:
+        return hit[2]
+    pw = ops.weight_prepass(keys, precision, per_channel_scale=per_channel, need_fwd=True, need_bwd=True)
+    if len(_PREPARED) >= 16:
+        _PREPARED.pop(next(iter(_PREPARED)))
+    _PREPARED[key] = (StorageWeakRef(keys.untyped_storage()), keys._version, pw)
+    return pw
+
+
+@torch.library.custom_op("amoe::cvmm_forward", mutates_args=())
+def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor, keys: torch.Tensor, inp_res: float,
+                    input_ranges: Optional[torch.Tensor], out_index: Optional[torch.Tensor],
+                    reduction_weight: Optional[torch.Tensor], out_noise: Optional[torch.Tensor], use_abs_max: bool,
+                    expert_offsets: Optional[torch.Tensor], precision: int, scale_per_channel: bool,
+                    noise_std: float, noise_seed: int, noise_offset: int, noise_step: Optional[torch.Tensor],
+                    mod_std: float, mod_per_channel: bool, mod_discretize: float, mod_seed: int, mod_offset: int,
+                    mod_step: Optional[torch.Tensor], out_res: float, out_bound: float, adc_codes_path: bool,
+                    save_codes: bool, check_status: bool) -> List[torch.Tensor]:
+    """Forward CVMM (reference cvmm.py:529-631 plus the reduction of cvmm.py:757-759).
+    Returns [out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, col_scale]."""
+    A.require_cuda(x, keys)
+    ops.set_tag("down" if reduction_weight is not None else "up")
+    E, K, N = keys.shape
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    P = sel.numel()
+    dev = x.device
+    status = ops.new_status(dev) if check_status else None
+    sel_i = ops.i32(sel)
+    sel_index_i = ops.i32(sel_index)
+    out_index_i = None if out_index is None else ops.i32(out_index)
+    if expert_offsets is not None:
+        offsets = expert_offsets
+        offsets_out = _empty(sel_i)
+    else:
+        offsets = offsets_out = ops.expert_offsets(sel_i, E, status)
+    ir = None if input_ranges is None else input_ranges.reshape(-1).float().contiguous()
+    absmax = ops.row_absmax(x2) if use_abs_max else None
+    pw = _prepared_weights(keys, precision, scale_per_channel, mod_std, mod_per_channel, mod_discretize, mod_seed,
+                           mod_offset, mod_step)
+    dst = sel_index_i if out_index_i is None else out_index_i
+    adc_on = out_res > 0 and out_bound > 0
+    codes_path = adc_on and reduction_weight is not None and adc_codes_path
+    row_meta = {} if codes_path else None
+    res, codes = ops.cvmm_fwd(
+        x2, sel_index_i, dst, offsets, pw, precision, P=P, dst_rows=P, ir=ir, absmax=absmax,
+        inp_res=float(inp_res), noise=out_noise, noise_std=noise_std, seed=noise_seed, offset=noise_offset,
+        step_dev=noise_step, out_res=out_res if adc_on else -1.0, out_bound=out_bound if adc_on else -1.0,
+        want_codes=codes_path or (adc_on and save_codes), status=status, want_out=not codes_path, row_meta=row_meta)
+    e = _empty(x2)
+    row_scale = row_expert = None
+    if reduction_weight is not None:
+        k = reduction_weight.shape[-1]
+        if codes_path:
+            # y[t] = sum_j gate * ((code*step)*col_scale)*row_scale, straight from the int8 codes
+            row_scale, row_expert = row_meta["row_scale"], row_meta["row_expert"]
+            out = ops.combine_codes(codes, pw.col_scale, row_expert, row_scale, ops.adc_step(out_res, out_bound),
+                                    reduction_weight, P // k, k, out_dtype=x.dtype).view(*reduction_weight.shape[:-1], N)
+            res_keep = e
+        else:
+            out = ops.combine(res, reduction_weight, P // k, k).view(*reduction_weight.shape[:-1], N)   # cvmm.py:757-759
+            res_keep = res.view(*reduction_weight.shape, N)
+    else:
+        out = res.view(*sel.shape, N)
+        res_keep = e
+    if status is not None:
+        ops.raise_on_device_status(status, "CVMM.forward")
+    simt = precision == A.PREC_FP32_SIMT
+    w_mod = e
+    if simt:        # the CUDA-core backward reads the (modified) weights themselves; never hand an input back
+        w_mod = pw.w if pw.w is not keys else e
+    keep_codes = codes is not None and (codes_path or save_codes)
+    return [out, offsets_out, res_keep, codes if keep_codes else _empty(x2, torch.int8),
+            row_scale if row_scale is not None else _empty(x2, torch.float32),
+            row_expert if row_expert is not None else _empty(x2, torch.int32), w_mod,
+            pw.bwd_hi if pw.bwd_hi is not None else _empty(x2, torch.bfloat16),
+            pw.bwd_lo if pw.bwd_lo is not None else _empty(x2, torch.bfloat16), pw.col_scale]
+
+
+@cvmm_forward_op.register_fake
+def _cvmm_forward_fake(x, sel_index, sel, keys, inp_res, input_ranges, out_index, reduction_weight, out_noise,
+                       use_abs_max, expert_offsets, precision, scale_per_channel, noise_std, noise_seed, noise_offset,
+                       noise_step, mod_std, mod_per_channel, mod_discretize, mod_seed, mod_offset, mod_step, out_res,
+                       out_bound, adc_codes_path, save_codes, check_status):
+    """Shapes only (reference cvmm.py:634-642)."""
+    E, K, N = keys.shape
+    P = sel.numel()
+    new = x.new_empty
+    e = new(0)
+    adc_on = out_res > 0 and out_bound > 0
+    codes_path = adc_on and reduction_weight is not None and adc_codes_path
+    if reduction_weight is not None:
+        out = new(*reduction_weight.shape[:-1], N)
+        res_keep = e if codes_path else new(*reduction_weight.shape, N)
+    else:
+        out, res_keep = new(*sel.shape, N), e
+    codes = new(P, N, dtype=torch.int8) if (codes_path or (adc_on and save_codes)) else new(0, dtype=torch.int8)
+    row_scale = new(P if codes_path else 0, dtype=torch.float32)
+    row_expert = new(P if codes_path else 0, dtype=torch.int32)
+    offsets = new(0 if expert_offsets is not None else E + 1, dtype=torch.int32)
+    simt = precision == A.PREC_FP32_SIMT
+    modified = mod_std > 0 or mod_discretize > 0
+    w_mod = new(E, K, N, dtype=torch.float32) if (simt and modified) else e
+    _, _, kpad2, npad2 = ops.prepared_dims(K, N)
+    split = precision == A.PREC_SPLIT and (keys.dtype != torch.bfloat16 or modified)
+    bwd_hi = new((0,) if simt else (E, kpad2, npad2), dtype=torch.bfloat16)
+    bwd_lo = new((E, kpad2, npad2) if (split and not simt) else (0,), dtype=torch.bfloat16)
+    return [out, offsets, res_keep, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, new(E, N, dtype=torch.float32)]
+
+
+@torch.library.custom_op("amoe::cvmm_backward", mutates_args=())
+def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tensor, sel_index: torch.Tensor,
+                     out_index: Optional[torch.Tensor], reduction_weight: Optional[torch.Tensor],
+                     input_ranges: Optional[torch.Tensor], res_into_reduction: Optional[torch.Tensor],
+                     offsets: torch.Tensor, w: Optional[torch.Tensor], bwd_hi: Optional[torch.Tensor],
+                     bwd_lo: Optional[torch.Tensor], col_scale: torch.Tensor, codes: Optional[torch.Tensor],
+                     row_scale: Optional[torch.Tensor], row_expert: Optional[torch.Tensor], n_experts: int, N: int,
+                     precision: int, decay: float, min_percentage: float, relative: bool, grad_scale: float,
+                     out_res: float, out_bound: float, need_x: bool, need_w: bool, need_ir: bool, need_gate: bool, check_status: bool
+                     ) -> List[torch.Tensor]:
+    """Backward CVMM (reference cvmm.py:771-897).  Returns [grad_x, grad_w (fp32), grad_ir (per sorted slot), grad_gate]."""
+    E = n_experts
+    K = x.shape[-1]
+    down = reduction_weight is not None
+    adc_step = ops.adc_step(out_res, out_bound) if (out_res > 0 and out_bound > 0) else 0.0
+    ops.set_tag("down" if down else "up")
+    dev = x.device
+    sel_i, sel_index_i = ops.i32(sel), ops.i32(sel_index)
+    out_index_i = None if out_index is None else ops.i32(out_index)
+    P = sel_i.numel()
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    g = grad_output.reshape(-1, N)
+    if g.stride(-1) != 1:
+        g = g.contiguous()
+    ir = None if input_ranges is None else input_ranges.reshape(-1).float().contiguous()
+    status = ops.new_status(dev) if check_status else None
+    pw = ops.PreparedWeights(E, K, N, col_scale, w=w, bwd_hi=bwd_hi, bwd_lo=bwd_lo)
+    k = reduction_weight.shape[-1] if down else max(P // x2.shape[0], 1)
+    rw = reduction_weight.reshape(-1).float().contiguous() if down else None
+    e = _empty(x2)
+    grad_w = e
+    if need_w:
+        # reference cvmm.py:785-823: the outer product rw (x) g is folded into the operand load
+        if down:
+            grad_w = ops.cvmm_dw(x2, sel_index_i, g, sel_index_i, offsets, E, precision, P=P, ir=ir, g_div=k,
+                                 g_scale=rw, status=status)
+        else:
+            g_row = out_index_i if out_index_i is not None else sel_index_i
+            grad_w = ops.cvmm_dw(x2, sel_index_i, g, g_row, offsets, E, precision, P=P, ir=ir, status=status)
+    grad_x = e
+    grad_ir = _empty(x2, torch.float32)
+    if need_x or need_ir:
+        use_decay = ir is not None and decay > 0
+        keep = torch.zeros(1, dtype=torch.int64, device=dev) if use_decay else None
+        if down:
+            # reference cvmm.py:828-846 with bw_index = sel_index // k, output rows = sel_index
+            gx, ir_slot = ops.cvmm_dx(g, sel_index_i, sel_index_i, offsets, pw, precision, P=P, dst_rows=P,
+                                      a_row_div=k, x_ref=x2 if ir is not None else None,
+                                      x_ref_row=sel_index_i if ir is not None else None, ir=ir, row_scale=rw,
+                                      want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
+                                      keep_count=keep, out_dtype=x.dtype, status=status)
+            grad_x = gx.view(x.shape)
+        else:
+            src = out_index_i if out_index_i is not None else sel_index_i
+            gx, ir_slot = ops.cvmm_dx(g, src, src, offsets, pw, precision, P=P, dst_rows=P,
+                                      x_ref=x2 if ir is not None else None,
+                                      x_ref_row=sel_index_i if ir is not None else None, ir=ir,
+                                      want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
+                                      keep_count=keep, out_dtype=x.dtype, status=status)
+            T = x2.shape[0]
+            grad_x = (ops.combine(gx, None, T, P // T) if P != T else gx).view(x.shape)               # cvmm.py:890-891
+        if ir is not None:
+            if use_decay:                                                                   # cvmm.py:872-878
+                pct = keep.double() / float(P * K)
+                ir_slot = ir_slot + decay * ir * (pct > min_percentage).float()
+            grad_ir = ir_slot
+    grad_gate = _empty(x2, torch.float32)
+    if down and need_gate:
+        if codes is not None:
+            grad_gate = ops.row_dot_codes(codes, col_scale, row_expert, row_scale, adc_step, g, k)
+        else:
+            grad_gate = ops.row_dot(res_into_reduction, g, k)                                  # cvmm.py:889
+    if status is not None:
+        ops.raise_on_device_status(status, "CVMM.backward")
+    return [grad_x, grad_w, grad_ir, grad_gate]
+
+
+@cvmm_backward_op.register_fake
+def _cvmm_backward_fake(grad_output, x, sel, sel_index, out_index, reduction_weight, input_ranges, res_into_reduction,
+                        offsets, w, bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert, n_experts, N, precision,
+                        decay, min_percentage, relative, grad_scale, out_res, out_bound, need_x, need_w, need_ir, need_gate,
+                        check_status):
+    new = x.new_empty
+    P, K = sel.numel(), x.shape[-1]
+    has_ir = input_ranges is not None
+    return [new(x.shape) if (need_x or need_ir) else new(0),
+            new(n_experts, K, N, dtype=torch.float32) if need_w else new(0),
+            new(P if (has_ir and (need_x or need_ir)) else 0, dtype=torch.float32),
+            new(P if (reduction_weight is not None and need_gate) else 0, dtype=torch.float32)]
+
+
 class CVMM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sel_index, sel, keys, inp_res, broadcasted_input_ranges=None, out_index=None,
                 reduction_weight=None, out_noise=None, ir_params=None, io_params=None, ext=None):
-        A.require_cuda(x, keys)
         if torch.is_autocast_enabled():
             raise RuntimeError("autocast is not supported by the B200 CVMM kernels; pass bf16 or fp32 tensors")
         ext = ext or CVMMExt()
-        ops.set_tag("down" if reduction_weight is not None else "up")
         E, K, N = keys.shape
         if x.shape[-1] != K:
             raise ValueError(f"x has {x.shape[-1]} features, weights expect {K}")     # reference cvmm.py:561
-        x2 = x.reshape(-1, K)
-        if x2.stride(-1) != 1:
-            x2 = x2.contiguous()
-        P = sel.numel()
-        dev = x.device
         precision = ext.precision if ext.precision is not None else ops.default_precision(x.dtype)
         if os.environ.get("_AIHWKIT_NO_ROUNDING", False):                              # reference cvmm.py:603-608
             assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
             inp_res = -1
-        status = ops.new_status(dev) if ext.check_status else None
-
-        sel_i = ops.i32(sel)
-        sel_index_i = ops.i32(sel_index)
-        out_index_i = None if out_index is None else ops.i32(out_index)
-        offsets = ext.expert_offsets if ext.expert_offsets is not None else ops.expert_offsets(sel_i, E, status)
-        ir = None if broadcasted_input_ranges is None else broadcasted_input_ranges.reshape(-1).float().contiguous()
-        absmax = ops.row_absmax(x2) if _uses_abs_max(ir_params, io_params) else None
-
-        mod = ext.modifier
-        pw = ops.weight_prepass(
-            keys, precision, per_channel_scale=ext.scale_per_channel,
-            noise_std=mod.std_dev if mod else 0.0, noise_per_channel=mod.per_channel if mod else True,
-            discretize_res=mod.discretize_res if mod else -1.0, seed=mod.seed if mod else 0,
-            offset=mod.offset if mod else 0, step_dev=mod.step if mod else None, need_fwd=True, need_bwd=any(ctx.needs_input_grad[:1]) or True)
-
-        noise_t, noise_std, seed, offset, step_dev = None, 0.0, 0, 0, None
+        noise_t, pn = None, ext.noise
         if isinstance(out_noise, PhiloxNoise):
-            ext = CVMMExt(**{**ext.__dict__, "noise": out_noise})
+            pn = out_noise
         elif out_noise is not None:
             noise_t = out_noise
-        if ext.noise is not None and ext.noise.std > 0:
-            noise_std, seed, offset, step_dev = ext.noise.std, ext.noise.seed, ext.noise.offset, ext.noise.step
-
-        dst = sel_index_i if out_index_i is None else out_index_i
-        adc_on = ext.out_res > 0 and ext.out_bound > 0
-        codes_path = adc_on and reduction_weight is not None and ext.adc_codes_path
-        row_meta = {} if codes_path else None
-        res, codes = ops.cvmm_fwd(
-            x2, sel_index_i, dst, offsets, pw, precision, P=P, dst_rows=P, ir=ir, absmax=absmax,
-            inp_res=float(inp_res), noise=noise_t, noise_std=noise_std, seed=seed, offset=offset, step_dev=step_dev,
-            out_res=ext.out_res if adc_on else -1.0, out_bound=ext.out_bound if adc_on else -1.0,
-            want_codes=codes_path or (adc_on and ext.save_codes), status=status, want_out=not codes_path,
-            row_meta=row_meta)
+        if pn is not None and not pn.std > 0:
+            pn = None
+        mod = ext.modifier
+        (out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo,
+         col_scale) = cvmm_forward_op(
+            x, sel_index, sel, keys, float(inp_res), broadcasted_input_ranges, out_index, reduction_weight, noise_t,
+            _uses_abs_max(ir_params, io_params), ext.expert_offsets, precision, ext.scale_per_channel,
+            float(pn.std) if pn else 0.0, int(pn.seed) if pn else 0, int(pn.offset) if pn else 0, pn.step if pn else None,
+            float(mod.std_dev) if mod else 0.0, bool(mod.per_channel) if mod else True,
+            float(mod.discretize_res) if mod else -1.0, int(mod.seed) if mod else 0, int(mod.offset) if mod else 0,
+            mod.step if mod else None, float(ext.out_res), float(ext.out_bound), ext.adc_codes_path, ext.save_codes,
+            ext.check_status)
         if ext.save_codes:
-            ext.last_codes = codes
-
-        res_into_reduction = None
-        row_scale = row_expert = None
-        adc_step = ops.adc_step(ext.out_res, ext.out_bound) if adc_on else 0.0
-        if reduction_weight is not None:
-            k = reduction_weight.shape[-1]
-            if codes_path:
-                # y[t] = sum_j gate * ((code*step)*col_scale)*row_scale, straight from the int8 codes
-                row_scale, row_expert = row_meta["row_scale"], row_meta["row_expert"]
-                out = ops.combine_codes(codes, pw.col_scale, row_expert, row_scale, adc_step, reduction_weight, P // k, k,
-                                        out_dtype=x.dtype).view(*reduction_weight.shape[:-1], N)
-            else:
-                res_into_reduction = res.view(*reduction_weight.shape, N)
-                out = ops.combine(res, reduction_weight, P // k, k).view(*reduction_weight.shape[:-1], N)   # cvmm.py:757-759
-        else:
-            out = res.view(*sel.shape, N)
-        if status is not None:
-            ops.raise_on_device_status(status, "CVMM.forward")
-
-        ctx.save_for_backward(x, sel_i, sel_index_i, out_index_i, reduction_weight, ir, res_into_reduction, offsets,
-                              pw.w if precision == A.PREC_FP32_SIMT else None, pw.bwd_hi, pw.bwd_lo, pw.col_scale,
-                              codes if codes_path else None, row_scale, row_expert)
-        ctx.meta = (E, K, N, precision, ir_params, keys.dtype, broadcasted_input_ranges.shape if ir is not None else None,
-                    ext.check_status, adc_step)
+            ext.last_codes = _none_if_empty(codes)
+        if ext.expert_offsets is not None:
+            offsets = ext.expert_offsets
+        simt = precision == A.PREC_FP32_SIMT
+        ctx.save_for_backward(x, sel, sel_index, out_index, reduction_weight, broadcasted_input_ranges,
+                              res_into_reduction, offsets, w_mod, keys if (simt and w_mod.numel() == 0) else None,
+                              bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert)
+        ctx.meta = (E, N, precision, ir_params, keys.dtype, ext.check_status, float(ext.out_res), float(ext.out_bound))
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
-        (x, sel_i, sel_index_i, out_index_i, reduction_weight, ir, res_into_reduction, offsets, w_mod, bwd_hi, bwd_lo,
-         col_scale, codes, row_scale, row_expert) = ctx.saved_tensors
-        E, K, N, precision, ir_params, keys_dtype, ir_shape, check_status, adc_step = ctx.meta
-        ops.set_tag("down" if reduction_weight is not None else "up")
-        dev = x.device
-        P = sel_i.numel()
-        x2 = x.reshape(-1, K)
-        g = grad_output.reshape(-1, N)
-        if g.stride(-1) != 1:
-            g = g.contiguous()
-        status = ops.new_status(dev) if check_status else None
-        pw = ops.PreparedWeights(E, K, N, col_scale, w=w_mod, bwd_hi=bwd_hi, bwd_lo=bwd_lo)
+        (x, sel, sel_index, out_index, reduction_weight, bir, res_into_reduction, offsets, w_mod, keys_simt, bwd_hi,
+         bwd_lo, col_scale, codes, row_scale, row_expert) = ctx.saved_tensors
+        E, N, precision, ir_params, keys_dtype, check_status, out_res, out_bound = ctx.meta
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[3]
-        need_ir = ir is not None and ctx.needs_input_grad[5]
-        down = reduction_weight is not None
-        k = reduction_weight.shape[-1] if down else max(P // x2.shape[0], 1)
-        rw = reduction_weight.reshape(-1).float().contiguous() if down else None
-
-        grad_w = None
-        if need_w:
-            # reference cvmm.py:785-823: the outer product rw (x) g is folded into the operand load
-            if down:
-                grad_w = ops.cvmm_dw(x2, sel_index_i, g, sel_index_i, offsets, E, precision, P=P, ir=ir, g_div=k,
-                                     g_scale=rw, status=status)
-            else:
-                g_row = out_index_i if out_index_i is not None else sel_index_i
-                grad_w = ops.cvmm_dw(x2, sel_index_i, g, g_row, offsets, E, precision, P=P, ir=ir, status=status)
-            grad_w = grad_w.to(keys_dtype)
-
-        grad_x = grad_ir = grad_gate = None
-        if need_x or need_ir:
-            decay = float(getattr(ir_params, "decay", 0.0) or 0.0) if ir is not None else 0.0
-            keep = torch.zeros(1, dtype=torch.int64, device=dev) if (ir is not None and decay > 0) else None
-            relative = bool(getattr(ir_params, "gradient_relative", True))
-            gscale = float(getattr(ir_params, "gradient_scale", 1.0)) if relative else 1.0
-            if down:
-                # reference cvmm.py:828-846 with bw_index = sel_index // k, output rows = sel_index
-                gx, ir_slot = ops.cvmm_dx(g, sel_index_i, sel_index_i, offsets, pw, precision, P=P, dst_rows=P,
-                                          a_row_div=k, x_ref=x2 if ir is not None else None,
-                                          x_ref_row=sel_index_i if ir is not None else None, ir=ir, row_scale=rw,
-                                          want_ir_grad=ir is not None, relative=relative, grad_scale=gscale,
-                                          keep_count=keep, out_dtype=x.dtype, status=status)
-                grad_x = gx.view_as(x)
-            else:
-                src = out_index_i if out_index_i is not None else sel_index_i
-                gx, ir_slot = ops.cvmm_dx(g, src, src, offsets, pw, precision, P=P, dst_rows=P,
-                                          x_ref=x2 if ir is not None else None,
-                                          x_ref_row=sel_index_i if ir is not None else None, ir=ir,
-                                          want_ir_grad=ir is not None, relative=relative, grad_scale=gscale,
-                                          keep_count=keep, out_dtype=x.dtype, status=status)
-                T = x2.shape[0]
-                if P != T:
-                    grad_x = ops.combine(gx, None, T, P // T).view_as(x)               # cvmm.py:890-891
-                else:
-                    grad_x = gx.view_as(x)
-            if ir is not None:
-                if decay > 0:                                                            # cvmm.py:872-878
-                    pct = keep.double() / float(P * K)
-                    ir_slot = ir_slot + decay * ir * (pct > ir_params.input_min_percentage).float()
-                grad_ir = ir_slot.view(ir_shape)
-        if down and ctx.needs_input_grad[7]:
-            if codes is not None:
-                d = ops.row_dot_codes(codes, col_scale, row_expert, row_scale, adc_step, g, k)
-            else:
-                d = ops.row_dot(res_into_reduction, g, k)                                     # cvmm.py:889
-            grad_gate = d.view_as(reduction_weight).to(reduction_weight.dtype)
-        if status is not None:
-            ops.raise_on_device_status(status, "CVMM.backward")
-        return (grad_x if need_x else None, None, None, grad_w, None, grad_ir if need_ir else None, None, grad_gate,
+        need_ir = bir is not None and ctx.needs_input_grad[5]
+        need_gate = reduction_weight is not None and ctx.needs_input_grad[7]
+        has_ir = bir is not None
+        decay = float(getattr(ir_params, "decay", 0.0) or 0.0) if has_ir else 0.0
+        min_pct = float(getattr(ir_params, "input_min_percentage", 0.95)) if has_ir else 0.95
+        relative = bool(getattr(ir_params, "gradient_relative", True))
+        gscale = float(getattr(ir_params, "gradient_scale", 1.0)) if relative else 1.0
+        w = keys_simt if keys_simt is not None else _none_if_empty(w_mod)
+        grad_x, grad_w, grad_ir, grad_gate = cvmm_backward_op(
+            grad_output, x, sel, sel_index, out_index, reduction_weight, bir, _none_if_empty(res_into_reduction),
+            offsets, w, _none_if_empty(bwd_hi), _none_if_empty(bwd_lo), col_scale, _none_if_empty(codes),
+            _none_if_empty(row_scale), _none_if_empty(row_expert), E, N, precision, decay, min_pct, relative, gscale,
+            out_res, out_bound, need_x, need_w, need_ir, need_gate, check_status)
+        return (grad_x if need_x else None, None, None, grad_w.to(keys_dtype) if need_w else None, None,
+                grad_ir.view(bir.shape) if need_ir else None, None,
+                grad_gate.view(reduction_weight.shape).to(reduction_weight.dtype) if need_gate else None,
                 None, None, None, None)

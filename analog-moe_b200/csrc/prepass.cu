@@ -7,25 +7,94 @@ namespace {
 // colmax[e,n] = max_k |W[e,k,n]|.  Block = 32 columns x 8 k-lanes over a slice of K; the slices meet
 // through an integer atomic max on the bit patterns of the (non-negative) floats, which is exact
 // and order-independent.  colmax must be zero-filled before the launch.
+// With `colsum`/`colsq` given ([slices,E,N] doubles) the same pass also leaves each slice's sum and sum of squares
+// per column: the statistics of the Gaussian weight clipping, summed later in slice order (no atomics).
 constexpr int kColmaxSlice = 128;
 __global__ void colmax_kernel(const void* __restrict__ w, int dtype, int E, int K, int N, int64_t se, int64_t sk,
-                              int64_t sn, float* __restrict__ colmax) {
+                              int64_t sn, float* __restrict__ colmax, double* __restrict__ colsum,
+                              double* __restrict__ colsq) {
   __shared__ float red[8][33];
+  __shared__ double red_s[8][33], red_q[8][33];
   const int e = blockIdx.y;
   const int n = blockIdx.x * 32 + threadIdx.x;
   const int kb = blockIdx.z * kColmaxSlice;
   const int ke = min(K, kb + kColmaxSlice);
   float m = 0.f;
+  double sum = 0.0, sq = 0.0;
   if (n < N) {
-    for (int k = kb + threadIdx.y; k < ke; k += 8) m = fmaxf(m, fabsf(load_elem(w, dtype, e * se + k * sk + n * sn)));
+    for (int k = kb + threadIdx.y; k < ke; k += 8) {
+      const float v = load_elem(w, dtype, e * se + k * sk + n * sn);
+      m = fmaxf(m, fabsf(v));
+      if (colsum) { sum += v; sq += static_cast<double>(v) * v; }
+    }
   }
   red[threadIdx.y][threadIdx.x] = m;
+  if (colsum) { red_s[threadIdx.y][threadIdx.x] = sum; red_q[threadIdx.y][threadIdx.x] = sq; }
   __syncthreads();
   if (threadIdx.y == 0 && n < N) {
 #pragma unroll
     for (int i = 1; i < 8; ++i) m = fmaxf(m, red[i][threadIdx.x]);
     if (m == m) atomicMax(reinterpret_cast<int*>(colmax) + static_cast<int64_t>(e) * N + n, __float_as_int(m));
     else colmax[static_cast<int64_t>(e) * N + n] = m;   // NaN weights: propagate
+    if (colsum) {
+      for (int i = 1; i < 8; ++i) { sum += red_s[i][threadIdx.x]; sq += red_q[i][threadIdx.x]; }
+      const int64_t o = (static_cast<int64_t>(blockIdx.z) * E + e) * N + n;
+      colsum[o] = sum;
+      colsq[o] = sq;
+    }
+  }
+}
+
+// Clip bounds, one block per expert: bound[e,n] = min(sigma * std, fixed) with the unbiased standard deviation of
+// the column (per_channel) or of the whole expert, and colmax[e,n] = min(colmax[e,n], bound[e,n]) - the column
+// maximum of the clipped weights.  sigma <= 0: bound = fixed.
+__global__ void __launch_bounds__(256) clip_bounds_kernel(const double* __restrict__ colsum, const double* __restrict__ colsq,
+                                                          int slices, int E, int K, int N, float sigma, int per_channel,
+                                                          float fixed, float* __restrict__ colmax,
+                                                          float* __restrict__ bound) {
+  __shared__ double s_sum[256], s_sq[256];
+  const int e = blockIdx.x;
+  double tsum = 0.0, tsq = 0.0;
+  if (sigma > 0.f) {
+    for (int n = threadIdx.x; n < N; n += 256) {
+      double a = 0.0, b = 0.0;
+      for (int sl = 0; sl < slices; ++sl) {
+        const int64_t o = (static_cast<int64_t>(sl) * E + e) * N + n;
+        a += colsum[o];
+        b += colsq[o];
+      }
+      if (per_channel) {
+        const double var = K > 1 ? (b - a * a / K) / (K - 1) : 0.0;
+        float bd = sigma * static_cast<float>(sqrt(var > 0.0 ? var : 0.0));
+        if (fixed > 0.f) bd = fminf(bd, fixed);
+        const int64_t i = static_cast<int64_t>(e) * N + n;
+        bound[i] = bd;
+        colmax[i] = fminf(colmax[i], bd);
+      } else {
+        tsum += a;
+        tsq += b;
+      }
+    }
+  }
+  if (sigma > 0.f && per_channel) return;
+  float bd = fixed;
+  if (sigma > 0.f) {
+    s_sum[threadIdx.x] = tsum;
+    s_sq[threadIdx.x] = tsq;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {        // fixed tree: the same result on every run
+      if (threadIdx.x < o) { s_sum[threadIdx.x] += s_sum[threadIdx.x + o]; s_sq[threadIdx.x] += s_sq[threadIdx.x + o]; }
+      __syncthreads();
+    }
+    const double cnt = static_cast<double>(K) * N;
+    const double var = cnt > 1 ? (s_sq[0] - s_sum[0] * s_sum[0] / cnt) / (cnt - 1) : 0.0;
+    bd = sigma * static_cast<float>(sqrt(var > 0.0 ? var : 0.0));
+    if (fixed > 0.f) bd = fminf(bd, fixed);
+  }
+  for (int n = threadIdx.x; n < N; n += 256) {
+    const int64_t i = static_cast<int64_t>(e) * N + n;
+    bound[i] = bd;
+    colmax[i] = fminf(colmax[i], bd);
   }
 }
 
@@ -66,6 +135,8 @@ struct PrepassDev {
   int noise_per_channel; float noise_std; float n_states;  // n_states<=0: no discretisation
   uint64_t seed; uint32_t offset; const long long* step_dev;
   float* w_out;
+  const float* bound;   // [E,N] clip bound, or NULL
+  void* w_clip_out;     // clamped weights in the layout and type of w (normally w itself), or NULL
   __nv_bfloat16 *fwd_hi, *fwd_lo, *bwd_hi, *bwd_lo;
   int Npad, Kpad, Kpad2, Npad2;
 };
@@ -108,6 +179,17 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           if (n + j < p.N) x[j] = load_elem(p.w, p.dtype, e * p.se + k * p.sk + (n + j) * p.sn);
+      }
+      if (p.bound) {
+        // Gaussian / fixed-value weight clipping first: everything below sees the clipped weights, and they are
+        // written back in place
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (n + j < p.N) {
+            const float bd = p.bound[static_cast<int64_t>(e) * p.N + n + j];
+            x[j] = fminf(fmaxf(x[j], -bd), bd);
+            if (p.w_clip_out) store_elem(p.w_clip_out, p.dtype, e * p.se + k * p.sk + (n + j) * p.sn, x[j]);
+          }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -202,6 +284,15 @@ size_t amoe_weight_prepass_workspace_bytes(int32_t E, int32_t K, int32_t N) {
   return (static_cast<size_t>(E) * N + E) * sizeof(float);
 }
 
+// With clipping: the same plus bound [E,N] floats and two [slices,E,N] double arrays (8-byte aligned).
+size_t amoe_weight_prepass_clip_workspace_bytes(int32_t E, int32_t K, int32_t N) {
+  if (E <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t en = static_cast<size_t>(E) * N;
+  const size_t head = ((2 * en + E) * sizeof(float) + 7) & ~static_cast<size_t>(7);
+  const size_t slices = (static_cast<size_t>(K) + kColmaxSlice - 1) / kColmaxSlice;
+  return head + 2 * slices * en * sizeof(double);
+}
+
 void amoe_prepared_dims(int32_t K, int32_t N, int32_t dims[4]) {
   dims[0] = round_up(N, 16); dims[1] = round_up(K, 64); dims[2] = round_up(K, 16); dims[3] = round_up(N, 64);
 }
@@ -214,17 +305,38 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
   AMOE_REQUIRE(a->workspace && a->workspace_bytes >= amoe_weight_prepass_workspace_bytes(a->E, a->K, a->N),
                AMOE_ERR_WORKSPACE);
   AMOE_REQUIRE(!(a->fwd_lo && !a->fwd_hi) && !(a->bwd_lo && !a->bwd_hi), AMOE_ERR_NULL_POINTER);
+  const bool clip = a->clip_sigma > 0.f || a->clip_fixed > 0.f;
+  const size_t en = static_cast<size_t>(a->E) * a->N;
+  const int slices = (a->K + kColmaxSlice - 1) / kColmaxSlice;
   float* colmax = reinterpret_cast<float*>(a->workspace);
-  float* expmax = colmax + static_cast<size_t>(a->E) * a->N;
-  AMOE_CUDA(cudaMemsetAsync(colmax, 0, static_cast<size_t>(a->E) * a->N * sizeof(float), stream));
-  colmax_kernel<<<dim3((a->N + 31) / 32, a->E, (a->K + kColmaxSlice - 1) / kColmaxSlice), dim3(32, 8), 0, stream>>>(a->w, a->w_dtype, a->E, a->K, a->N,
-                                                                          a->w_stride_e, a->w_stride_k,
-                                                                          a->w_stride_n, colmax);
+  float* expmax = colmax + en;
+  float* bound = nullptr;
+  double* colsum = nullptr;
+  double* colsq = nullptr;
+  if (clip) {
+    AMOE_REQUIRE(a->workspace_bytes >= amoe_weight_prepass_clip_workspace_bytes(a->E, a->K, a->N), AMOE_ERR_WORKSPACE);
+    AMOE_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 7u) == 0, AMOE_ERR_WORKSPACE);
+    bound = expmax + a->E;
+    if (a->clip_sigma > 0.f) {
+      const size_t head = ((2 * en + a->E) * sizeof(float) + 7) & ~static_cast<size_t>(7);
+      colsum = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(a->workspace) + head);
+      colsq = colsum + static_cast<size_t>(slices) * en;
+    }
+  }
+  AMOE_CUDA(cudaMemsetAsync(colmax, 0, en * sizeof(float), stream));
+  colmax_kernel<<<dim3((a->N + 31) / 32, a->E, slices), dim3(32, 8), 0, stream>>>(
+      a->w, a->w_dtype, a->E, a->K, a->N, a->w_stride_e, a->w_stride_k, a->w_stride_n, colmax, colsum, colsq);
   AMOE_LAUNCH_CHECK("colmax");
+  if (clip) {
+    clip_bounds_kernel<<<a->E, 256, 0, stream>>>(colsum, colsq, slices, a->E, a->K, a->N, a->clip_sigma,
+                                                 a->clip_per_channel, a->clip_fixed, colmax, bound);
+    AMOE_LAUNCH_CHECK("clip_bounds");
+  }
   scales_kernel<<<a->E, 256, 0, stream>>>(colmax, a->N, a->per_channel_scale, expmax, a->col_scale, a->col_inv_scale);
   AMOE_LAUNCH_CHECK("scales");
-  if (a->w_out || a->fwd_hi || a->bwd_hi) {
+  if (a->w_out || a->fwd_hi || a->bwd_hi || (clip && a->w_clip_out)) {
     PrepassDev p;
+    p.bound = bound; p.w_clip_out = clip ? a->w_clip_out : nullptr;
     p.w = a->w; p.dtype = a->w_dtype; p.E = a->E; p.K = a->K; p.N = a->N;
     p.se = a->w_stride_e; p.sk = a->w_stride_k; p.sn = a->w_stride_n;
     p.colmax = colmax; p.expmax = expmax;

@@ -154,9 +154,17 @@ typedef struct amoe_weight_prepass_args {
   float* w_out;                   /* [E,K,N] fp32 or NULL */
   void* fwd_hi; void* fwd_lo;     /* bf16 [E,Npad,Kpad] or NULL */
   void* bwd_hi; void* bwd_lo;     /* bf16 [E,Kpad2,Npad2] or NULL */
-  void* workspace; size_t workspace_bytes;  /* amoe_weight_prepass_workspace_bytes */
+  void* workspace; size_t workspace_bytes;  /* amoe_weight_prepass_workspace_bytes (_clip_ with clipping) */
+  /* Weight clipping in the same pass (clip_weights of the layers, moe_layer_aihwkit_lightning.py:519-543,
+   * moe_layer_aihwkit.py:314-340): W is first clamped to +-bound, bound = clip_sigma * std (unbiased; of each column
+   * over K if clip_per_channel, else of the whole expert), capped by clip_fixed when that is positive; clip_sigma <= 0
+   * with clip_fixed > 0 clamps to +-clip_fixed.  The clamped weights are written to w_clip_out (same type and strides
+   * as w; pass w itself to clip in place) and everything else - maxima, modifier, prepared copies - is computed from
+   * them.  Needs the larger workspace of amoe_weight_prepass_clip_workspace_bytes (8-byte aligned). */
+  float clip_sigma; int32_t clip_per_channel; float clip_fixed; void* w_clip_out;
 } amoe_weight_prepass_args;
 size_t amoe_weight_prepass_workspace_bytes(int32_t E, int32_t K, int32_t N);
+size_t amoe_weight_prepass_clip_workspace_bytes(int32_t E, int32_t K, int32_t N);
 /* Padded extents of the prepared copies: dims[0..1] = {Npad, Kpad} (fwd), dims[2..3] = {Kpad2, Npad2} (bwd). */
 void amoe_prepared_dims(int32_t K, int32_t N, int32_t dims[4]);
 int amoe_weight_prepass(const amoe_weight_prepass_args* args, amoe_stream_t stream);

@@ -1,0 +1,331 @@
+"""Drop-in proof: the reference's two layer files, unchanged, on top of this repository's `analog_moe.triton_src`.
+
+The files come from the reference package installed under baseline/_ref (see `__graft_entry__.install_reference`);
+`tests/standins.py` provides the third-party modules they import.  The CPU half checks that they import, bind to the
+CUDA library's `CVMM` and construct, and that checkpoints move between the reference layers and this package's
+layers in both formats.  The GPU half runs their forward + backward through THEIR `cvmm_wrapper` and compares with
+the CPU oracle and with this package's own layer classes.
+"""
+import pytest
+import torch
+
+import standins
+from oracle import cvmm_oracle as O
+
+needs_ref = pytest.mark.skipif(not standins.reference_available(),
+                               reason="baseline/_ref is not installed (python -c 'import __graft_entry__ as g; g.install_reference()')")
+
+
+def _lightning_cfg(**fwd):
+    import analog_moe
+    cfg = analog_moe.TorchInferenceRPUConfig()
+    cfg.forward.inp_res = 254.0
+    cfg.pre_post.input_range.decay = 0.01
+    for k, v in fwd.items():
+        setattr(cfg.forward, k, v)
+    return cfg
+
+
+# ----------------------------------------------------------------------------------------------- CPU
+@needs_ref
+def test_reference_layer_files_import_over_the_new_triton_src():
+    import analog_moe
+    lt = standins.load_reference_layer_module("moe_layer_aihwkit_lightning.py")
+    cl = standins.load_reference_layer_module("moe_layer_aihwkit.py")
+    for m in (lt, cl):
+        assert m.CVMM is analog_moe.CVMM and m.CVMMSel is analog_moe.CVMMSel and m.cvmm_std is analog_moe.cvmm_std
+    a = lt.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(), d_model=32, n_experts=4, expert_size=16, k=2)
+    b = cl.AnalogSigmaMoELayerAIHWKIT(analog_moe.aihwkit_rpu_config(), d_model=32, n_experts=4, expert_size=16, k=2)
+    assert a.input_range.shape == (2, 4) and b.input_range.shape == (2, 4)
+    # the reference refuses to run this layer on the CPU (lightning :390-399); so does the stand-in base
+    with pytest.raises(Exception):
+        a(torch.zeros(1, 4, 32))
+
+
+@needs_ref
+def test_checkpoints_move_between_reference_layers_and_ours():
+    import analog_moe
+    lt = standins.load_reference_layer_module("moe_layer_aihwkit_lightning.py")
+    cl = standins.load_reference_layer_module("moe_layer_aihwkit.py")
+    kw = dict(d_model=32, n_experts=4, expert_size=16, k=2)
+    torch.manual_seed(3)
+    # lightning flavour: reference -> ours, rpu_config rides in the metadata (lightning :545-570)
+    ref = lt.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(out_noise=0.03), **kw)
+    with torch.no_grad():
+        ref.input_range.copy_(torch.rand(2, 4) + 1)
+        ref.input_range_update_idx.fill_(7.0)
+    sd = ref.state_dict()
+    ours = analog_moe.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(), **kw)
+    res = ours.load_state_dict(sd)
+    assert not res.missing_keys and not res.unexpected_keys
+    assert torch.equal(ours.input_range, ref.input_range) and torch.equal(ours.keys, ref.keys)
+    assert ours.rpu_config.forward.out_noise == 0.03
+    # ours -> reference
+    back = lt.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(), **kw)
+    sd2 = ours.state_dict()
+    sd2.pop("noise_step")               # the one entry the reference layer does not know
+    res = back.load_state_dict(sd2)
+    assert not res.missing_keys and not res.unexpected_keys
+    assert torch.equal(back.values, ours.values) and float(back.input_range_update_idx.detach()) == 7.0
+    # a traceable-format checkpoint (per-expert entries, lightning :33-66) loads into the non-traceable layer
+    tr = dict(sd)
+    meta = sd._metadata
+    lt.non_traceable_to_traceable(tr, "")               # the reference's own converter writes the format
+    assert "keys.3.input_range" in tr and "input_range" not in tr
+    tr = type(sd)(tr)
+    tr._metadata = meta
+    again = analog_moe.AnalogSigmaMoELayer(_lightning_cfg(), **kw)
+    res = again.load_state_dict(tr)
+    assert not res.missing_keys and not res.unexpected_keys
+    assert torch.equal(again.input_range, ref.input_range) and float(again.input_range_update_idx.detach()) == 7.0
+    # and our converters agree with the reference's in both directions
+    a, b = dict(sd), dict(sd)
+    lt.non_traceable_to_traceable(a, "")
+    analog_moe.non_traceable_to_traceable(b, "")
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) for k in a)
+    lt.traceable_to_non_traceable(a, "")
+    analog_moe.traceable_to_non_traceable(b, "")
+    assert a.keys() == b.keys() and all(torch.equal(a[k].reshape(-1), b[k].reshape(-1)) for k in a)
+    # classic flavour: `analog_tile_state` entry (aihwkit :372-415)
+    cfg = analog_moe.aihwkit_rpu_config()
+    cfg.forward.out_noise = 0.05
+    refc = cl.AnalogSigmaMoELayerAIHWKIT(cfg, **kw)
+    sdc = refc.state_dict()
+    assert "analog_tile_state" in sdc
+    oursc = analog_moe.AnalogSigmaMoELayerAIHWKIT(analog_moe.aihwkit_rpu_config(), **kw)
+    res = oursc.load_state_dict(sdc, load_rpu_config=True)     # same keyword as the reference (:372-383)
+    assert not res.missing_keys and not res.unexpected_keys
+    assert oursc.rpu_config.forward.out_noise == 0.05 and torch.equal(oursc.keys, refc.keys)
+    assert "analog_tile_state" in oursc.state_dict()
+
+
+def test_cvmm_apply_traces_as_one_graph_with_the_fake_implementations():
+    """The autograd function is tensor glue around two torch.library operators with fake implementations
+    (reference cvmm.py:529, 634-642), so dynamo traces forward and backward without a graph break - checked here
+    without a GPU, on fake CUDA tensors."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from analog_moe import CVMM, CVMMExt
+
+    class IR:
+        enable, decay, input_min_percentage = True, 0.01, 0.95
+
+    class IO:
+        pass
+
+    def up(x, sel_index, sel, keys, bir, out_index):
+        return CVMM.apply(x, sel_index, sel, keys, 2 / 254., bir, out_index, None, None, IR, IO())
+
+    def down(h, sel_index, sel, values, bir, gate):
+        return CVMM.apply(h, sel_index, sel, values, 2 / 254., bir, None, gate, None, IR, IO(),
+                          CVMMExt(out_res=254., out_bound=12.))
+
+    with FakeTensorMode():
+        T, k, D, F, E = 64, 2, 32, 16, 4
+        c = dict(device="cuda")
+        x = torch.empty(1, T, D, requires_grad=True, **c)
+        keys = torch.empty(E, D, F, requires_grad=True, **c)
+        values = torch.empty(E, F, D, requires_grad=True, **c)
+        sel = torch.empty(1, T, k, dtype=torch.int64, **c)
+        idx = torch.empty(T * k, dtype=torch.int64, **c)
+        bir = torch.empty(1, T, k, requires_grad=True, **c)
+        gate = torch.empty(1, T, k, requires_grad=True, **c)
+        h = torch.empty(1, T, k, F, requires_grad=True, **c)
+        gm_up, _ = torch._dynamo.export(up)(x, idx, sel, keys, bir, idx)
+        gm_dn, _ = torch._dynamo.export(down)(h, idx, sel, values, bir, gate)
+    for gm, fwd_name in ((gm_up, "cvmm_forward"), (gm_dn, "cvmm_forward")):
+        text = gm.print_readable(print_output=False)
+        assert f"torch.ops.amoe.{fwd_name}" in text and "torch.ops.amoe.cvmm_backward" in text
+
+
+# ----------------------------------------------------------------------------------------------- GPU
+def _oracle(layer, x, gy, k, use_ir=True, inp_res=2.0 / 254.0, decay=0.01):
+    f = lambda t: t.detach().float().cpu()
+    lc = O.LayerConfig(k=k, inp_res=inp_res, use_ir=use_ir, ir_params=O.IRParams(decay=decay))
+    ir = f(layer.input_range) if use_ir else None
+    return O.layer_forward_backward(f(x)[0], f(layer.expert_sel.weight), f(layer.keys), f(layer.values), ir, lc,
+                                    f(gy)[0], acc_dtype=torch.float64)
+
+
+def _run(layer, x, gy):
+    for p in layer.parameters():
+        p.grad = None
+    x = x.detach().clone().requires_grad_()
+    y, _ = layer(x)
+    (y * gy).sum().backward()
+    g = lambda t: None if t is None else t.detach().float().cpu()
+    return dict(y=g(y)[0], dx=g(x.grad)[0], dkeys=g(layer.keys.grad), dvalues=g(layer.values.grad),
+                d_input_range=g(layer.input_range.grad) if getattr(layer, "input_range", None) is not None else None)
+
+
+def _close(got, want, tol, what):
+    err = float((got - want).abs().max())
+    scale = max(1.0, float(want.abs().max()))
+    assert err <= tol * scale, f"{what}: max abs err {err:.3e} > {tol:g} * {scale:.3g}"
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_reference_lightning_layer_runs_on_the_cuda_library():
+    """Forward + backward through the REFERENCE's cvmm_wrapper (moe_layer_aihwkit_lightning.py:412-507) with this
+    repository's triton_src underneath: against the oracle (1e-4 of the output scale, split precision) and against
+    this package's own layer (fused single-node step and composition), same weights."""
+    import analog_moe
+    lt = standins.load_reference_layer_module("moe_layer_aihwkit_lightning.py")
+    dev = torch.device("cuda:0")
+    T, D, F, E, k = 320, 128, 64, 8, 2
+    torch.manual_seed(0)
+    ref = lt.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(), d_model=D, n_experts=E, expert_size=F, k=k).to(dev)
+    with torch.no_grad():
+        ref.input_range.copy_(1.0 + 0.25 * torch.arange(2 * E, device=dev).view(2, E) / E)   # a different range per expert
+    ref.train()
+    x = torch.randn(1, T, D, device=dev)
+    gy = torch.randn(1, T, D, device=dev)
+    got = _run(ref, x, gy)
+    yo, go = _oracle(ref, x, gy, k)
+    _close(got["y"], yo, 1e-4, "y")
+    for name in ("dx", "dkeys", "dvalues", "d_input_range"):
+        _close(got[name], go[name], 1e-4 if name != "dx" else 1e-3, name)      # the reference's own tolerances
+    ours = analog_moe.AnalogSigmaMoELayerAIHWKITLightning(_lightning_cfg(), d_model=D, n_experts=E, expert_size=F, k=k)
+    sd = ref.state_dict()
+    ours.load_state_dict(sd)
+    ours = ours.to(dev).train()
+    for fused in (True, False):
+        ours.fused = fused
+        mine = _run(ours, x, gy)
+        for name in ("y", "dx", "dkeys", "dvalues", "d_input_range"):
+            _close(mine[name], got[name], 1e-4, f"ours(fused={fused}) vs reference layer: {name}")
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_reference_lightning_layer_noise_and_modifier_paths():
+    """The reference layer materialises its output noise with torch.randn and modifies a clone of the weights in torch
+    (lightning :458-492); both reach the kernels as plain tensors.  Statistics only: the output error has the std the
+    configuration asks for (within 5 % over 4096 x 128 samples), and the data-driven input-range initialisation
+    (lightning :432-445, cvmm_std) moves the ranges to alpha * std of the routed rows."""
+    import analog_moe
+    lt = standins.load_reference_layer_module("moe_layer_aihwkit_lightning.py")
+    dev = torch.device("cuda:0")
+    T, D, F, E, k = 4096, 128, 128, 4, 2
+    torch.manual_seed(1)
+    cfg = _lightning_cfg(out_noise=0.05)
+    cfg.forward.inp_res = -1.0
+    cfg.pre_post.input_range.enable = False
+    noisy = lt.AnalogSigmaMoELayerAIHWKITLightning(cfg, d_model=D, n_experts=E, expert_size=F, k=k).to(dev)
+    x = torch.randn(1, T, D, device=dev)
+    sel, gate = noisy.route(x)
+    noisy.train()
+    a = noisy.cvmm_wrapper(x, sel, noisy.keys)
+    noisy.eval()
+    b = noisy.cvmm_wrapper(x, sel, noisy.keys)
+    # abs-max mode: the noise is added in normalised units and rescaled by the row's abs-max (cvmm.py:215-229)
+    wmax = noisy.keys.abs().amax(1)[sel.raw_sel.long()]                 # [1,T,k,F]
+    amax = x.abs().amax(-1)[..., None, None]
+    z = (a - b) / (0.05 * wmax * amax)
+    assert abs(float(z.std()) - 1.0) < 0.05 and abs(float(z.mean())) < 0.02
+    # init_from_data
+    cfg2 = _lightning_cfg()
+    cfg2.pre_post.input_range.init_from_data = 2
+    cfg2.pre_post.input_range.init_std_alpha = 2.5
+    lay = lt.AnalogSigmaMoELayerAIHWKITLightning(cfg2, d_model=D, n_experts=E, expert_size=F, k=k).to(dev).train()
+    lay(x)
+    rows = x[0][sel.sel_index.long()]
+    for e in range(E):
+        m = rows[sel.sel.flatten() == e]
+        want = 2.5 * float(m.std())         # first update: (ir*0 + alpha*std) / 1
+        assert abs(float(lay.input_range[0, e]) - want) < 2e-3 * want
+    assert float(lay.input_range_update_idx) == 2.0          # one increment per cvmm_wrapper call (up, down)
+    # every weight-modifier type the reference knows runs (the reference's own test is a smoke test too,
+    # test_moe_layer_aihwkit_lightning.py:331-367)
+    for name in ("DISCRETIZE", "DISCRETIZE_PER_CHANNEL", "ADD_NORMAL", "ADD_NORMAL_PER_CHANNEL", "DISCRETIZE_ADD_NORMAL",
+                 "DISCRETIZE_ADD_NORMAL_PER_CHANNEL"):
+        cfg3 = _lightning_cfg()
+        cfg3.modifier.type = getattr(analog_moe.WeightModifierType, name)
+        cfg3.modifier.std_dev, cfg3.modifier.res = 0.02, 0.1
+        lay = lt.AnalogSigmaMoELayerAIHWKITLightning(cfg3, d_model=D, n_experts=E, expert_size=F, k=k).to(dev).train()
+        y, _ = lay(x)
+        y.sum().backward()
+        assert torch.isfinite(y).all() and torch.isfinite(lay.keys.grad).all()
+
+
+@pytest.mark.gpu
+@needs_ref
+def test_reference_aihwkit_layer_and_our_aihwkit_flavour():
+    """The classic-aihwkit layer file (moe_layer_aihwkit.py:198-301) over the CUDA library, with input ranges AND
+    abs-max noise management (both divisions in the kernel, cvmm.py:145-158), against this package's
+    AnalogSigmaMoELayerAIHWKIT built from the same checkpoint, and `is_perfect` against a plain (digital) layer."""
+    import analog_moe
+    cl = standins.load_reference_layer_module("moe_layer_aihwkit.py")
+    dev = torch.device("cuda:0")
+    T, D, F, E, k = 256, 128, 64, 4, 2
+    kw = dict(d_model=D, n_experts=E, expert_size=F, k=k)
+    torch.manual_seed(2)
+    x = torch.randn(1, T, D, device=dev)
+    gy = torch.randn(1, T, D, device=dev)
+    for nm in ("NONE", "ABS_MAX"):
+        cfg = analog_moe.aihwkit_rpu_config()
+        cfg.forward.noise_management = getattr(analog_moe.NoiseManagementType, nm)
+        cfg.remap.type = analog_moe.WeightRemapType.LAYERWISE_SYMMETRIC
+        ref = cl.AnalogSigmaMoELayerAIHWKIT(cfg, **kw).to(dev).train()
+        got = _run(ref, x, gy)
+        ours = analog_moe.AnalogSigmaMoELayerAIHWKIT(cfg, **kw)
+        ours.load_state_dict(ref.state_dict())
+        ours = ours.to(dev).train()
+        mine = _run(ours, x, gy)
+        for name in ("y", "dx", "dkeys", "dvalues", "d_input_range"):
+            _close(mine[name], got[name], 1e-4, f"noise_management={nm}: {name}")
+        if nm == "NONE":
+            yo, go = _oracle(ref, x, gy, k)
+            _close(got["y"], yo, 1e-4, "y vs oracle")
+            _close(got["dkeys"], go["dkeys"], 1e-4, "dkeys vs oracle")
+    cfg = analog_moe.aihwkit_rpu_config()
+    cfg.forward.is_perfect = True
+    cfg.pre_post.input_range.enable = False
+    ref = cl.AnalogSigmaMoELayerAIHWKIT(cfg, **kw).to(dev).train()
+    dig = analog_moe.SigmaMoELayer(**kw).to(dev)
+    dig.load_state_dict({k_: v for k_, v in ref.state_dict().items() if k_ in dig.state_dict()})
+    y1, _ = ref(x)
+    y2, _ = dig(x)
+    _close(y1.detach().cpu(), y2.detach().cpu(), 1e-5, "is_perfect vs digital")
+
+
+@pytest.mark.gpu
+def test_compiled_cvmm_matches_eager():
+    """torch.compile of a function that calls CVMM.apply twice (up, ReLU, down) traces into one graph through the
+    operators' fake implementations (fullgraph=True raises on a graph break) and gives the eager result bit for bit."""
+    from analog_moe import CVMM, CVMMExt, ops
+    dev = torch.device("cuda:0")
+    T, D, F, E, k = 256, 128, 64, 4, 2
+    torch.manual_seed(5)
+
+    class IR:
+        enable, decay, input_min_percentage = True, 0.0, 0.95
+
+    class IO:
+        pass
+
+    x = torch.randn(1, T, D, device=dev, requires_grad=True)
+    keys = (torch.randn(E, D, F, device=dev) / D ** 0.5).requires_grad_()
+    values = (torch.randn(E, F, D, device=dev) / F ** 0.5).requires_grad_()
+    ir = torch.full((2, E), 2.0, device=dev, requires_grad=True)
+    r = ops.select_sort(torch.randn(T, E, device=dev), k)
+    sel = r.sel.view(1, T, k).long()
+    gate = r.gate.view(1, T, k).clone().requires_grad_()
+    tok, slot = r.token_index.long(), r.slot_index.long()
+
+    def f(x, keys, values, ir, gate):
+        h = CVMM.apply(x, tok, sel, keys, 2 / 254., ir[0][sel], slot, None, None, IR, IO())
+        return CVMM.apply(torch.relu(h), slot, sel, values, 2 / 254., ir[1][sel], None, gate, None, IR, IO(),
+                          CVMMExt(out_res=254., out_bound=12.))
+
+    def grads(fn):
+        for t in (x, keys, values, ir, gate):
+            t.grad = None
+        y = fn(x, keys, values, ir, gate)
+        y.square().sum().backward()
+        return [y.detach()] + [t.grad.clone() for t in (x, keys, values, ir, gate)]
+
+    want = grads(f)
+    got = grads(torch.compile(f, backend="aot_eager", fullgraph=True))
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
