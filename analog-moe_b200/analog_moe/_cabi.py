@@ -39,6 +39,7 @@ class WeightPrepassArgs(C.Structure):
         ("col_scale", vp), ("col_inv_scale", vp), ("w_out", vp), ("fwd_hi", vp), ("fwd_lo", vp), ("bwd_hi", vp), ("bwd_lo", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t),
         ("clip_sigma", C.c_float), ("clip_per_channel", C.c_int32), ("clip_fixed", C.c_float), ("w_clip_out", vp),
+        ("expert_base", C.c_int32),
     ]
 
 
@@ -122,7 +123,7 @@ SIGNATURES = {
                                vp, vp]),
     "amoe_row_dot_codes": (C.c_int, [vp, vp, vp, vp, C.c_float, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
                                      vp, vp, vp]),
-    "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, vp]),
+    "amoe_ir_grad_reduce": (C.c_int, [vp, vp, vp, C.c_int32, C.c_float, C.c_float, vp, C.c_double, vp, C.c_int32, vp, vp]),
     "amoe_expert_std_workspace_bytes": (C.c_size_t, [C.c_int32]),
     "amoe_expert_std": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp, C.c_int64, C.c_int32, vp, vp,
                                   C.c_size_t, vp, vp]),
@@ -134,10 +135,10 @@ SIGNATURES = {
     "amoe_ep_local_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
     "amoe_ep_plan_ints": (C.c_int64, [C.c_int32, C.c_int32]),
     "amoe_ep_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
-    "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
+    "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp, vp]),
     "amoe_ep_put": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp,
-                              vp, C.c_int32, C.c_int64, vp]),
-    "amoe_ep_put_back": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int32, C.c_int64, C.c_int64, vp]),
+                              vp, C.c_int32, C.c_int64, vp, vp]),
+    "amoe_ep_put_back": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int32, C.c_int64, C.c_int64, vp, vp]),
     "amoe_ep_unpack": (C.c_int, [vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, C.c_int64, vp]),
 }
 

@@ -197,9 +197,15 @@ class PeerExchange:
             hdl = symm.rendezvous(t, group)
             self.buffers[name] = (hdl, t, int(hdl.buffer_ptrs_dev))
         self.token = torch.zeros(1, device=device)
+        self.generation = 0          # forward passes that have written into the buffers
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)   # device status word of the exchange kernels
 
     def barrier(self) -> None:
         dist.all_reduce(self.token, group=self.group)
+
+    def check(self, where: str = "expert-parallel exchange") -> None:
+        """Synchronises and raises if an exchange kernel dropped a row or saw a plan larger than its buffers."""
+        ops.raise_on_device_status(self.status, where)
 
     def put(self, name: str, src: Tensor, index: Tensor, sel_sorted: Tensor, El: int, plan: Tensor, src_div: int = 1,
             row_scale: Optional[Tensor] = None) -> Tensor:
@@ -210,7 +216,7 @@ class PeerExchange:
         assert src.shape[1] == buf.shape[1] and src.dtype == buf.dtype and src.stride(-1) == 1
         ops._call("amoe_ep_put", ops.ptr(src), ops.dtype_code(src), src.stride(0), src.shape[1], src.shape[0], ops.ptr(index),
                   src_div, ops.ptr(row_scale), index.numel(), ops.ptr(sel_sorted), El, ops.ptr(plan), ptrs, self.G,
-                  buf.shape[0], ops.stream_ptr())
+                  buf.shape[0], ops.ptr(self.status), ops.stream_ptr())
         self.barrier()
         return buf
 
@@ -219,7 +225,7 @@ class PeerExchange:
         hdl, buf, ptrs = self.buffers[name]
         assert rows.shape[1] == buf.shape[1] and rows.dtype == buf.dtype and rows.stride(-1) == 1
         ops._call("amoe_ep_put_back", ops.ptr(rows), ops.dtype_code(rows), rows.stride(0), rows.shape[1], ops.ptr(plan), ptrs,
-                  self.G, rows.shape[0], buf.shape[0], ops.stream_ptr())
+                  self.G, rows.shape[0], buf.shape[0], ops.ptr(self.status), ops.stream_ptr())
         if barrier:
             self.barrier()
         return buf[:n_own]
@@ -252,11 +258,13 @@ class _ExpertParallelStep(torch.autograd.Function):
                 w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
                 noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,
                 seed=mod.seed if mod else 0, offset=mod.offset if mod else 0, step_dev=mod.step if mod else None,
-                need_fwd=True, need_bwd=True)
+                need_fwd=True, need_bwd=True, expert_base=layer.rank * El)     # the dense layer's draws for these experts
 
         def noise_args():
+            # output noise is addressed by the row of the local receive buffer: the rank goes into the seed, or every
+            # rank would draw the same pattern
             if layer.training and fwd.out_noise > 0:
-                return dict(noise_std=float(fwd.out_noise), seed=layer.noise_seed, offset=layer._next_offset(),
+                return dict(noise_std=float(fwd.out_noise), seed=layer._rank_noise_seed(), offset=layer._next_offset(),
                             step_dev=layer.noise_step)
             return {}
 
@@ -286,7 +294,8 @@ class _ExpertParallelStep(torch.autograd.Function):
             dist.all_gather_into_tensor(gathered, counts, group=group)
             plan = ops.ep_plan(gathered, layer.rank)
             R = xchg.cap                       # rows allocated; the kernels find the real count in the plan / offsets
-            local_order, local_offsets = ops.ep_local_plan_dev(plan, G, El, R)
+            local_order, local_offsets = ops.ep_local_plan_dev(plan, G, El, R, xchg.status)
+            xchg.generation += 1
             recv = xchg.put("x", x2, r.token_index, r.sel, El, plan)
         else:
             hplan = step_plan(counts, layer.rank, group)
@@ -353,6 +362,9 @@ class _ExpertParallelStep(torch.autograd.Function):
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
                               *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)), cs_all, scale_back)
         ctx.adc_step = adc_step
+        ctx.generation = xchg.generation if xchg is not None else 0
+        if layer.keep_codes:      # ADC codes of the down-projection by flat slot (parity checks)
+            layer.last_codes = back[inv.long()] if codes_back else None
         ctx.meta = (x.shape, El, k, precision, ir_p, keys.dtype, values.dtype, keys.shape, values.shape,
                     input_range.dtype if has_ir else None, send_splits, recv_splits, group, plan, xchg)
         return y.view(bsz, seq, N)
@@ -365,8 +377,11 @@ class _ExpertParallelStep(torch.autograd.Function):
          group, plan, xchg) = ctx.meta
         T, D = x2.shape
         P, R = T * k, recv.shape[0]
+        if xchg is not None and xchg.generation != ctx.generation:
+            raise RuntimeError("expert-parallel layer: a later forward pass of this layer has overwritten the exchange "
+                               "buffers this backward pass reads (one forward/backward pair per layer may be in flight)")
         # rows routed to this rank: known exactly on the NCCL path; with the device-driven exchange the buffers have
-        # worst-case size and the balanced share P stands in (used only by the decay term's kept-fraction threshold)
+        # worst-case size and the balanced share P only tunes the work split of the weight-gradient kernels
         n_rows = P if xchg is not None else R
         Fh, N = vshape[1], vshape[2]
         need_x, need_sel, need_keys, need_values, need_ir = (ctx.needs_input_grad[i] for i in (1, 2, 3, 4, 5))
@@ -458,12 +473,21 @@ class _ExpertParallelStep(torch.autograd.Function):
                                              raw_sel=raw_sel).to(w_sel.dtype)
         grad_ir = None
         if need_ir:
+            # The decay term's threshold is one fraction over ALL routed pairs (reference cvmm.py:872-878): kept
+            # elements and rows are summed over the ranks on the device (one small all-reduce, no host read), so the
+            # result is the dense layer's whatever the load balance.
+            tot = None
+            if keeps is not None:
+                tot = torch.cat([keeps, local_offsets[-1:].to(torch.int64)])     # kept (up), kept (down), rows here
+                dist.all_reduce(tot, group=group)
             if R > 0:
                 grad_ir = torch.stack([
                     ops.ir_grad_reduce(irs_up, local_offsets, ir_up, El, decay, min_pct,
-                                       keeps[:1] if keeps is not None else None, float(n_rows) * D),
+                                       tot[0:1] if tot is not None else None, total_rows=tot[2:3] if tot is not None else None,
+                                       cols=D),
                     ops.ir_grad_reduce(irs_dn, local_offsets, ir_dn, El, decay, min_pct,
-                                       keeps[1:] if keeps is not None else None, float(n_rows) * Fh)]).to(ir_dtype)
+                                       tot[1:2] if tot is not None else None, total_rows=tot[2:3] if tot is not None else None,
+                                       cols=Fh)]).to(ir_dtype)
             else:
                 grad_ir = torch.zeros(2, El, dtype=ir_dtype, device=dev)
         if forked:
@@ -521,6 +545,9 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
             warnings.warn(f"expert-parallel peer exchange unavailable ({exc!r}); using NCCL all-to-all")
             self.peer_exchange = False
             return None
+
+    def _rank_noise_seed(self) -> int:
+        return (self.noise_seed ^ (self.rank * 0x9E3779B97F4A7C15)) & (2 ** 64 - 1)
 
     def load_global_weights(self, keys: Tensor, values: Tensor, router: Tensor, input_range: Optional[Tensor] = None):
         El = self.n_experts

@@ -169,6 +169,8 @@ class _FusedAnalogStep(torch.autograd.Function):
                                     out_bound=out_bound, want_codes=True, want_out=False, row_meta=meta, **cache_kw,
                                     **nz)
             row_scale, row_expert = meta["row_scale"], meta["row_expert"]
+            if layer.keep_codes:
+                layer.last_codes = codes
             y = ops.combine_codes(codes, pw_dn.col_scale, row_expert, row_scale, adc_step, gate, T, k, out_dtype=x.dtype)
         else:
             res, _ = ops.cvmm_fwd(h, r.slot_index, r.slot_index, r.expert_offsets, pw_dn, precision, P=P, dst_rows=P,
@@ -438,6 +440,8 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.fuse_clip = False      # post_update_step only records the clipping; the next forward's weight pre-pass
                                     # clips in place while it reads the weights anyway (until then they are unclipped)
         self._pending_clip = None
+        self.keep_codes = False     # keep the down-projection's ADC codes (int8, by flat slot) on `last_codes`
+        self.last_codes = None
         self._noise_calls = 0
         self._register_load_state_dict_pre_hook(partial(_convert_checkpoint_format, traceable=False))
         ir = self.rpu_config.pre_post.input_range

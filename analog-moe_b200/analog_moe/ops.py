@@ -262,7 +262,7 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
                    noise_per_channel: bool = True, discretize_res: float = -1.0, seed: int = 0, offset: int = 0,
                    step_dev: Optional[torch.Tensor] = None, need_fwd: bool = True, need_bwd: bool = True,
                    need_w_out: bool = False, clip_sigma: float = -1.0, clip_per_channel: bool = False,
-                   clip_fixed: float = -1.0) -> PreparedWeights:
+                   clip_fixed: float = -1.0, expert_base: int = 0) -> PreparedWeights:
     """`clip_sigma` / `clip_fixed` > 0: the weights are clipped in place first (see clip_weights_) in the same pass."""
     A.require_cuda(w)
     E, K, N = w.shape
@@ -277,6 +277,7 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     a.discretize_res = float(discretize_res)
     a.seed, a.offset = int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF
     a.step_dev = ptr(step_dev)
+    a.expert_base = int(expert_base)
     col_inv = torch.empty(E, N, dtype=torch.float32, device=dev)
     a.col_scale = ptr(col_scale)
     a.col_inv_scale = ptr(col_inv)
@@ -592,11 +593,11 @@ def adc_step(out_res: float, out_bound: float) -> float:
 
 def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_range: Optional[torch.Tensor], E: int,
                    decay: float = 0.0, min_percentage: float = 0.95, keep_count: Optional[torch.Tensor] = None,
-                   total_elements: float = 0.0) -> torch.Tensor:
+                   total_elements: float = 0.0, total_rows: Optional[torch.Tensor] = None, cols: int = 0) -> torch.Tensor:
+    """`total_rows` (int64 device scalar) * cols replaces `total_elements` as the denominator of the kept fraction."""
     out = torch.empty(E, dtype=torch.float32, device=ir_grad_slot.device)
     _call("amoe_ir_grad_reduce", ptr(ir_grad_slot), ptr(offsets), ptr(input_range), E, float(decay),
-                                  float(min_percentage), ptr(keep_count), float(total_elements), ptr(out),
-                                  stream_ptr())
+          float(min_percentage), ptr(keep_count), float(total_elements), ptr(total_rows), int(cols), ptr(out), stream_ptr())
     return out
 
 
@@ -649,10 +650,11 @@ def ep_plan(gathered: torch.Tensor, rank: int) -> torch.Tensor:
     return plan
 
 
-def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int) -> Tuple[torch.Tensor, torch.Tensor]:
+def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int,
+                      status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     order = torch.empty(cap, dtype=torch.int32, device=plan.device)
     offsets = torch.empty(El + 1, dtype=torch.int32, device=plan.device)
-    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), stream_ptr())
+    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), ptr(status), stream_ptr())
     return order, offsets
 
 

@@ -17,6 +17,8 @@ from dataclasses import dataclass, field
 
 class WeightModifierType(enum.Enum):
     NONE = "None"
+    COPY = "Copy"                    # classic aihwkit only: named by its layer, treated as NONE (moe_layer_aihwkit.py:166)
+    MULT_NORMAL = "MultNormal"       # classic aihwkit only: rejected by its layer (:169-170)
     DISCRETIZE = "Discretize"
     DISCRETIZE_PER_CHANNEL = "DiscretizePerChannel"
     ADD_NORMAL = "AddNormal"

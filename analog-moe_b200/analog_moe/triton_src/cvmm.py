@@ -207,7 +207,6 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
         inp_res=float(inp_res), noise=out_noise, noise_std=noise_std, seed=noise_seed, offset=noise_offset,
         step_dev=noise_step, out_res=out_res if adc_on else -1.0, out_bound=out_bound if adc_on else -1.0,
         want_codes=codes_path or (adc_on and save_codes), status=status, want_out=not codes_path, row_meta=row_meta)
-    e = _empty(x2)
     row_scale = row_expert = None
     if reduction_weight is not None:
         k = reduction_weight.shape[-1]
@@ -216,19 +215,19 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
             row_scale, row_expert = row_meta["row_scale"], row_meta["row_expert"]
             out = ops.combine_codes(codes, pw.col_scale, row_expert, row_scale, ops.adc_step(out_res, out_bound),
                                     reduction_weight, P // k, k, out_dtype=x.dtype).view(*reduction_weight.shape[:-1], N)
-            res_keep = e
+            res_keep = _empty(x2)
         else:
             out = ops.combine(res, reduction_weight, P // k, k).view(*reduction_weight.shape[:-1], N)   # cvmm.py:757-759
             res_keep = res.view(*reduction_weight.shape, N)
     else:
         out = res.view(*sel.shape, N)
-        res_keep = e
+        res_keep = _empty(x2)
     if status is not None:
         ops.raise_on_device_status(status, "CVMM.forward")
     simt = precision == A.PREC_FP32_SIMT
-    w_mod = e
-    if simt:        # the CUDA-core backward reads the (modified) weights themselves; never hand an input back
-        w_mod = pw.w if pw.w is not keys else e
+    w_mod = _empty(x2)      # (every absent output is its own empty tensor: operator outputs must not alias)
+    if simt and pw.w is not keys:   # the CUDA-core backward reads the (modified) weights; never hand an input back
+        w_mod = pw.w
     keep_codes = codes is not None and (codes_path or save_codes)
     return [out, offsets_out, res_keep, codes if keep_codes else _empty(x2, torch.int8),
             row_scale if row_scale is not None else _empty(x2, torch.float32),
@@ -299,8 +298,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
     pw = ops.PreparedWeights(E, K, N, col_scale, w=w, bwd_hi=bwd_hi, bwd_lo=bwd_lo)
     k = reduction_weight.shape[-1] if down else max(P // x2.shape[0], 1)
     rw = reduction_weight.reshape(-1).float().contiguous() if down else None
-    e = _empty(x2)
-    grad_w = e
+    grad_w = _empty(x2)
     if need_w:
         # reference cvmm.py:785-823: the outer product rw (x) g is folded into the operand load
         if down:
@@ -309,7 +307,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
         else:
             g_row = out_index_i if out_index_i is not None else sel_index_i
             grad_w = ops.cvmm_dw(x2, sel_index_i, g, g_row, offsets, E, precision, P=P, ir=ir, status=status)
-    grad_x = e
+    grad_x = _empty(x2)
     grad_ir = _empty(x2, torch.float32)
     if need_x or need_ir:
         use_decay = ir is not None and decay > 0

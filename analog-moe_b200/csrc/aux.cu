@@ -219,7 +219,8 @@ __global__ void __launch_bounds__(256) ir_grad_reduce_kernel(const float* __rest
                                                              const float* __restrict__ input_range, int E, float decay,
                                                              float min_pct,
                                                              const unsigned long long* __restrict__ keep_count,
-                                                             double total, float* __restrict__ out) {
+                                                             double total, const long long* __restrict__ total_rows_dev,
+                                                             int cols, float* __restrict__ out) {
   __shared__ float red[8];
   const int e = blockIdx.x;
   const int beg = offsets[e], end = offsets[e + 1];
@@ -234,7 +235,12 @@ __global__ void __launch_bounds__(256) ir_grad_reduce_kernel(const float* __rest
 #pragma unroll
     for (int w = 1; w < 8; ++w) acc += red[w];
     if (decay > 0.f && keep_count != nullptr) {
-      const float pct = static_cast<float>(static_cast<double>(*keep_count) / total);
+      // denominator: a device counter of rows (times the row length) when given, else the host's value, else the
+      // rows this slot list holds
+      double tot = total;
+      if (total_rows_dev != nullptr) tot = static_cast<double>(*total_rows_dev) * cols;
+      else if (!(tot > 0.0)) tot = static_cast<double>(offsets[E]) * cols;
+      const float pct = static_cast<float>(static_cast<double>(*keep_count) / tot);
       if (pct > min_pct) acc += (decay * input_range[e]) * static_cast<float>(end - beg);
     }
     out[e] = acc;
@@ -505,13 +511,16 @@ int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_
 
 int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range, int32_t E,
                         float decay, float min_percentage, const unsigned long long* keep_count,
-                        double total_elements, float* out, amoe_stream_t stream_) {
+                        double total_elements, const long long* total_rows_dev, int32_t cols, float* out,
+                        amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(ir_grad_slot && expert_offsets && out, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(E > 0, AMOE_ERR_BAD_SHAPE);
-  AMOE_REQUIRE(!(decay > 0.f) || (keep_count && input_range && total_elements > 0), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!(decay > 0.f) || (keep_count && input_range), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(!(decay > 0.f) || total_elements > 0 || cols > 0, AMOE_ERR_BAD_SHAPE);
   ir_grad_reduce_kernel<<<static_cast<unsigned>(E), 256, 0, stream>>>(
-      ir_grad_slot, expert_offsets, input_range, E, decay, min_percentage, keep_count, total_elements, out);
+      ir_grad_slot, expert_offsets, input_range, E, decay, min_percentage, keep_count, total_elements, total_rows_dev,
+      cols, out);
   AMOE_LAUNCH_CHECK("ir_grad_reduce");
   return AMOE_OK;
 }

@@ -56,7 +56,8 @@ __global__ void ep_plan_kernel(const int32_t* __restrict__ gathered, int me, int
 // local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.
 __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* __restrict__ plan, int G, int El, int cap,
                                                                 int32_t* __restrict__ local_order,
-                                                                int32_t* __restrict__ local_offsets) {
+                                                                int32_t* __restrict__ local_offsets,
+                                                                int32_t* __restrict__ status) {
   __shared__ int s_recv_start[kEpMaxBlocksDev + 1];
   __shared__ int s_sorted_start[kEpMaxBlocksDev];
   const int32_t* recv_counts = plan + 2 + 4 * G;
@@ -73,6 +74,7 @@ __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* _
     if (blockIdx.x == 0) local_offsets[El] = acc;
   }
   __syncthreads();
+  if (plan[0] > cap && blockIdx.x == 0 && threadIdx.x == 0) report(status, AMOE_ERR_INDEX_RANGE, 50, plan[0], cap);
   const int R = min(plan[0], cap);
   for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < R; r += gridDim.x * blockDim.x) {
     int lo = 0, hi = nb;
@@ -80,7 +82,9 @@ __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* _
       const int mid = (lo + hi) >> 1;
       if (s_recv_start[mid] <= r) lo = mid; else hi = mid;
     }
-    local_order[s_sorted_start[lo] + (r - s_recv_start[lo])] = r;
+    // a position in the full permutation of plan[0] rows: it lies inside the array only if the plan fits the buffer
+    const int pos = s_sorted_start[lo] + (r - s_recv_start[lo]);
+    if (pos < cap) local_order[pos] = r;
   }
 }
 
@@ -147,15 +151,22 @@ template <typename T>
 __global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
                               int src_div, const float* __restrict__ row_scale, int64_t P,
                               const int32_t* __restrict__ sel_sorted, int El, const int32_t* __restrict__ plan,
-                              const uint64_t* __restrict__ peer_ptrs, int G, int64_t peer_rows, int64_t x_rows, int vec) {
+                              const uint64_t* __restrict__ peer_ptrs, int G, int64_t peer_rows, int64_t x_rows, int vec,
+                              int32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const int64_t i = spread_row((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, P);
   if (i >= P) return;
   const int d = sel_sorted[i] / El;
   const int64_t sr = src_row[i];
-  if (d < 0 || d >= G || sr < 0 || sr / src_div >= x_rows) return;
+  if (d < 0 || d >= G || sr < 0 || sr / src_div >= x_rows) {
+    if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 51, static_cast<int>(i), static_cast<int>(sr));
+    return;
+  }
   const int64_t dst_row = static_cast<int64_t>(plan[2 + G + d]) + (i - plan[2 + d]);
-  if (dst_row < 0 || dst_row >= peer_rows) return;
+  if (dst_row < 0 || dst_row >= peer_rows) {      // the row is dropped, and said so
+    if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 52, static_cast<int>(i), static_cast<int>(dst_row));
+    return;
+  }
   T* dst = reinterpret_cast<T*>(peer_ptrs[d]) + dst_row * K;
   copy_row<T>(x + (sr / src_div) * stride, dst, K, vec != 0, row_scale ? row_scale[sr] : 1.f, row_scale != nullptr, lane);
 }
@@ -164,9 +175,11 @@ __global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, co
 template <typename T>
 __global__ void ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, int K, const int32_t* __restrict__ plan,
                                    const uint64_t* __restrict__ peer_ptrs, int G, int64_t cap_rows, int64_t peer_rows,
-                                   int vec) {
+                                   int vec, int32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
   const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  if (plan[0] > cap_rows && blockIdx.x == 0 && threadIdx.x == 0)
+    report(status, AMOE_ERR_INDEX_RANGE, 53, plan[0], static_cast<int>(cap_rows));
   const int64_t R = min(static_cast<int64_t>(plan[0]), cap_rows);
   const int32_t* recv_off = plan + 2 + 2 * G;
   const int32_t* back_off = plan + 2 + 3 * G;
@@ -178,7 +191,10 @@ __global__ void ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, i
     for (int g = 1; g < G; ++g)
       if (recv_off[g] <= r) s = g;                    // last source whose block starts at or before r
     const int64_t dst_row = static_cast<int64_t>(back_off[s]) + (r - recv_off[s]);
-    if (dst_row < 0 || dst_row >= peer_rows) continue;
+    if (dst_row < 0 || dst_row >= peer_rows) {
+      if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 54, static_cast<int>(r), static_cast<int>(dst_row));
+      continue;
+    }
     copy_row<T>(rows + r * stride, reinterpret_cast<T*>(peer_ptrs[s]) + dst_row * K, K, vec != 0, 1.f, false, lane);
   }
 }
@@ -204,21 +220,22 @@ int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, i
 }
 
 int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
-                           int32_t* local_offsets, amoe_stream_t stream_) {
+                           int32_t* local_offsets, int32_t* dev_status, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(plan && local_order && local_offsets, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(G > 0 && El > 0 && G * El <= kEpMaxBlocksDev && cap_rows > 0 && cap_rows < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
   int64_t blocks = (cap_rows + 255) / 256;
   if (blocks > 592) blocks = 592;
   ep_local_plan_dev_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(plan, G, El, static_cast<int>(cap_rows), local_order,
-                                                                             local_offsets);
+                                                                             local_offsets, dev_status);
   AMOE_LAUNCH_CHECK("ep_local_plan_dev");
   return AMOE_OK;
 }
 
 int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row,
                 int32_t src_div, const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El,
-                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, amoe_stream_t stream_) {
+                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, int32_t* dev_status,
+                amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(x && src_row && sel_sorted && plan && peer_ptrs, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(P > 0 && K > 0 && El > 0 && G > 0 && G <= kEpMaxRanks && src_div >= 1 && peer_rows > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
@@ -227,11 +244,11 @@ int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t
   const unsigned blocks = static_cast<unsigned>((spread_count(P) * 32 + 255) / 256);
   if (dtype == AMOE_F32)
     ep_put_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div, row_scale, P,
-                                                     sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows, vec);
+                                                     sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows, vec, dev_status);
   else if (dtype == AMOE_BF16)
     ep_put_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K, src_row, src_div,
                                                              row_scale, P, sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows,
-                                                             vec);
+                                                             vec, dev_status);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("ep_put");
@@ -239,7 +256,8 @@ int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t
 }
 
 int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K, const int32_t* plan,
-                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, amoe_stream_t stream_) {
+                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, int32_t* dev_status,
+                     amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(rows && plan && peer_ptrs, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(K > 0 && G > 0 && G <= kEpMaxRanks && cap_rows > 0 && peer_rows > 0, AMOE_ERR_BAD_SHAPE);
@@ -250,10 +268,10 @@ int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K,
   if (blocks > max_blocks) blocks = max_blocks;
   if (dtype == AMOE_F32)
     ep_put_back_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(reinterpret_cast<const float*>(rows), stride, K, plan,
-                                                                                 peer_ptrs, G, cap_rows, peer_rows, vec);
+                                                                                 peer_ptrs, G, cap_rows, peer_rows, vec, dev_status);
   else if (dtype == AMOE_BF16)
     ep_put_back_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(rows), stride, K, plan, peer_ptrs, G, cap_rows, peer_rows, vec);
+        reinterpret_cast<const __nv_bfloat16*>(rows), stride, K, plan, peer_ptrs, G, cap_rows, peer_rows, vec, dev_status);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("ep_put_back");

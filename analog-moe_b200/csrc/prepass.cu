@@ -133,7 +133,7 @@ struct PrepassDev {
   const void* w; int dtype; int E, K, N; int64_t se, sk, sn;
   const float* colmax; const float* expmax;
   int noise_per_channel; float noise_std; float n_states;  // n_states<=0: no discretisation
-  uint64_t seed; uint32_t offset; const long long* step_dev;
+  uint64_t seed; uint32_t offset; const long long* step_dev; int expert_base;
   float* w_out;
   const float* bound;   // [E,N] clip bound, or NULL
   void* w_clip_out;     // clamped weights in the layout and type of w (normally w itself), or NULL
@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
     if (k < p.K && n < p.N) {
       float z[4] = {0.f, 0.f, 0.f, 0.f};
       if (p.noise_std > 0.f) {
-        const float4 zz = philox_normal4_inline(p.seed, off, kStreamWeightNoise, static_cast<uint32_t>(e * p.K + k),
+        const float4 zz = philox_normal4_inline(p.seed, off, kStreamWeightNoise, static_cast<uint32_t>((p.expert_base + e) * p.K + k),
                                                 static_cast<uint32_t>(n >> 2));
         z[0] = zz.x; z[1] = zz.y; z[2] = zz.z; z[3] = zz.w;
       }
@@ -342,7 +342,7 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
     p.colmax = colmax; p.expmax = expmax;
     p.noise_per_channel = a->noise_per_channel; p.noise_std = a->noise_std;
     p.n_states = a->discretize_res > 0.f ? fmaxf(a->discretize_res, 1.0f / a->discretize_res) : -1.f;
-    p.seed = a->seed; p.offset = a->offset; p.step_dev = a->step_dev;
+    p.seed = a->seed; p.offset = a->offset; p.step_dev = a->step_dev; p.expert_base = a->expert_base;
     p.w_out = a->w_out;
     p.fwd_hi = reinterpret_cast<__nv_bfloat16*>(a->fwd_hi); p.fwd_lo = reinterpret_cast<__nv_bfloat16*>(a->fwd_lo);
     p.bwd_hi = reinterpret_cast<__nv_bfloat16*>(a->bwd_hi); p.bwd_lo = reinterpret_cast<__nv_bfloat16*>(a->bwd_lo);

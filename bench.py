@@ -153,6 +153,101 @@ def step(layer, x, gy, bwd):
     return y
 
 
+def ep_parity_gate(cfg, rank, world, device, group):
+    """Correctness evidence for a multi-GPU line: before anything is timed, a small noise-free expert-parallel step
+    (DAC + ADC, input ranges that differ per expert, decay on, skewed routing) is compared with a single-GPU layer that
+    holds all experts, on every rank: outputs and all gradients relative to their scale (max over ranks), and the number
+    of the down-projection's ADC codes that differ."""
+    import torch.distributed as dist
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig
+    from analog_moe.ep import ExpertParallelAnalogSigmaMoELayer
+    dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
+    D, F, E, k, T = 256, 128, max(cfg["E"], world), cfg["k"], 384 + 32 * rank
+    rc = TorchInferenceRPUConfig()
+    rc.forward.inp_res, rc.forward.out_res, rc.forward.out_bound = 254.0, cfg.get("out_res", 254.0), OUT_BOUND
+    rc.pre_post.input_range.decay = 0.01
+    torch.manual_seed(0)
+    dense = AnalogSigmaMoELayer(rc, d_model=D, n_experts=E, expert_size=F, k=k).to(device).to(dtype).train()
+    with torch.no_grad():
+        dense.input_range.copy_(torch.linspace(2.0, 3.5, 2 * E).view(2, E))
+    ep = ExpertParallelAnalogSigmaMoELayer(rc, group=group, d_model=D, n_experts=E, expert_size=F, k=k)
+    ep = ep.to(device).to(dtype).train()
+    ep.load_global_weights(dense.keys.data, dense.values.data, dense.expert_sel.weight.data, dense.input_range.data)
+    bias = (-1.2 * torch.log(torch.arange(1, E + 1, device=device, dtype=torch.float32)) * 1.6).to(dtype)
+    dense.router_bias = ep.router_bias = bias              # some experts (hence ranks) get far more rows than others
+    dense.keep_codes = ep.keep_codes = True
+    g = torch.Generator().manual_seed(10 + rank)
+    x1 = torch.randn(1, T, D, generator=g).to(device).to(dtype).requires_grad_()
+    x2 = x1.detach().clone().requires_grad_()
+    gy = torch.randn(1, T, D, generator=g).to(device).to(dtype)
+    y1, _ = dense(x1)
+    y1.backward(gy)
+    y2, _ = ep(x2)
+    y2.backward(gy)
+    rel = lambda a, b: float((a.float() - b.float()).abs().max()) / max(1.0, float(b.float().abs().max()))
+    errs = [rel(y2, y1), rel(x2.grad, x1.grad)]
+    El = E // world
+    sl = slice(rank * El, (rank + 1) * El)
+    for name in ("keys", "values"):
+        full = getattr(dense, name).grad.float().clone()
+        dist.all_reduce(full, group=group)               # the owner's gradient = sum of the dense layers' over the ranks
+        errs.append(rel(getattr(ep, name).grad, full[sl]))
+    full = dense.input_range.grad.float().clone()
+    dist.all_reduce(full, group=group)
+    errs.append(rel(ep.input_range.grad, full[:, sl]))
+    a, b = dense.expert_sel.weight.grad.float().clone(), ep.expert_sel.weight.grad.float().clone()
+    dist.all_reduce(a, group=group)
+    dist.all_reduce(b, group=group)
+    errs.append(rel(b, a))
+    mism = 0
+    if dense.last_codes is not None and ep.last_codes is not None:
+        mism = int((dense.last_codes != ep.last_codes).sum())
+    t = torch.tensor([max(errs), float(mism)], device=device, dtype=torch.float64)
+    dist.all_reduce(t[0:1], op=dist.ReduceOp.MAX, group=group)
+    dist.all_reduce(t[1:2], op=dist.ReduceOp.SUM, group=group)
+    if getattr(ep, "_xchg", None) is not None:
+        ep._xchg.check("parity gate")
+    return dict(max_rel=float(t[0]), code_mismatches=int(t[1]),
+                what=f"noise-free expert-parallel step vs one layer holding all {E} experts, skewed routing, decay on: "
+                     "y, dx, dkeys, dvalues, d_input_range, router gradient relative to their scale (max over ranks); "
+                     "ADC codes of the down-projection that differ (sum over ranks)")
+
+
+def single_gpu_parity_gate(cfg, device, precision):
+    """Beside a single-GPU line: a small noise-free layer step (DAC + ADC, decay on) in the precision that is timed
+    against the same step on the CUDA-core fp32 kernels (the reference's own fp32 arithmetic): outputs and gradients
+    relative to their scale, and the number of ADC codes of the down-projection that differ (they may, by one code,
+    where the pre-rounding value sits on a rounding tie and the summation order decides)."""
+    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, _cabi
+    dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
+    D, F, E, k, T = 256, 128, cfg["E"], cfg["k"], 512
+    rc = TorchInferenceRPUConfig()
+    rc.forward.inp_res, rc.forward.out_res, rc.forward.out_bound = 254.0, cfg.get("out_res", 254.0), OUT_BOUND
+    rc.pre_post.input_range.decay = 0.01
+    torch.manual_seed(0)
+    layer = AnalogSigmaMoELayer(rc, d_model=D, n_experts=E, expert_size=F, k=k, precision=precision).to(device).to(dtype)
+    layer.train()
+    layer.keep_codes = True
+    g = torch.Generator().manual_seed(3)
+    x0 = torch.randn(1, T, D, generator=g).to(device).to(dtype)
+    gy = torch.randn(1, T, D, generator=g).to(device).to(dtype)
+    res = {}
+    for name, prec in (("timed", precision), ("fp32", _cabi.PREC_FP32_SIMT)):
+        layer.precision = prec
+        layer.zero_grad()
+        x = x0.clone().requires_grad_()
+        y, _ = layer(x)
+        y.backward(gy)
+        res[name] = [y.detach().float(), x.grad.float(), layer.keys.grad.float().clone(), layer.values.grad.float().clone(),
+                     layer.input_range.grad.float().clone(), layer.last_codes.clone()]
+    rel = lambda a, b: float((a - b).abs().max()) / max(1.0, float(b.abs().max()))
+    errs = [rel(a, b) for a, b in zip(res["timed"][:5], res["fp32"][:5])]
+    dc = (res["timed"][5].int() - res["fp32"][5].int()).abs()
+    return dict(max_rel=max(errs), code_mismatches=int((dc > 0).sum()), codes=int(dc.numel()), max_code_distance=int(dc.max()),
+                what="noise-free layer step in the timed precision vs the CUDA-core fp32 kernels: y, dx, dkeys, dvalues, "
+                     "d_input_range relative to their scale; ADC codes of the down-projection that differ")
+
+
 def run_ours(args, cfg, rank, world, device):
     from analog_moe import ops, _cabi
     # parameters' AccumulateGrad nodes are created during warm-up on the default stream and used again under graph
@@ -165,6 +260,8 @@ def run_ours(args, cfg, rank, world, device):
     if world > 1:
         import torch.distributed as dist
         group = dist.group.WORLD
+    parity = ep_parity_gate(cfg, rank, world, device, group) if world > 1 else \
+        single_gpu_parity_gate(cfg, device, precision)
     layer = build_layer(cfg, device, dtype, precision, ep_group=group)
     n_sets = 8
     xs_h, gys_h = make_inputs(cfg, 100 + rank, device, dtype, n_sets)
@@ -317,9 +414,105 @@ def run_ours(args, cfg, rank, world, device):
         step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
     summ = ops.TRACE.summary()
     ops.TRACE = None
+    # ---------------- the drop-in composition: the layer as the reference's layer files drive it, two CVMM.apply calls
+    # with torch glue in between (eager, CUDA events)
+    dropin_ms = None
+    if world == 1 and hasattr(layer, "fused"):
+        layer.fused = False
+        for i in range(3):
+            step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+        torch.cuda.synchronize()
+        n_d = max(3, min(args.steps, 20))
+        e0.record()
+        for i in range(n_d):
+            step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+        e1.record()
+        torch.cuda.synchronize()
+        dropin_ms = e0.elapsed_time(e1) / n_d
+        layer.fused = True
     return dict(ms=ms, ms_e2e=ms_e2e, k_e2e=k_e2e, launches=launches, h2d=h2d, d2h=d2h, kernels=summ,
-                graph=graphs is not None,
+                graph=graphs is not None, dropin_ms=dropin_ms, parity=parity,
                 clocks=sampler.result(), dtype=dtype, precision=layer._precision(xs[0]))
+
+
+def run_reference_triton(cfg, device, steps, warmup):
+    """GPU baseline: the reference's own Triton kernels on this GPU.  Its `CVMM.apply` (imported by path from the pip
+    install under baseline/_ref, nothing of this repository on that path) runs the up-projection, a ReLU and the
+    down-projection, forward + backward, on tensors of the benchmark's shapes, together with what its layer does in
+    torch around the two calls: the per-slot input ranges, a noisy copy of both weight tensors and the materialised
+    output noise (moe_layer_aihwkit_lightning.py:447-492).  The reference has no ADC and no router / top-k / sort of its
+    own (those live in a third-party package), so neither is in this number; the sorted slot list is built once,
+    outside the timed region.  Autotuning happens in the warm-up."""
+    path = os.path.join(ROOT, "baseline", "_ref", "analog_moe", "triton_src", "cvmm.py")
+    if not os.path.exists(path):
+        return {"unavailable": "baseline/_ref is not installed"}
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_reference_triton_cvmm", path)
+    ref = importlib.util.module_from_spec(spec)
+    sys.modules["_reference_triton_cvmm"] = ref
+    spec.loader.exec_module(ref)
+    dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
+    T, D, F, E, k = cfg["T"], cfg["D"], cfg["F"], cfg["E"], cfg["k"]
+    g = torch.Generator().manual_seed(7)
+    mk = lambda *shape, scale=1.0: (torch.randn(*shape, generator=g) * scale).to(device=device, dtype=dtype)
+    x = mk(1, T, D).requires_grad_(cfg["bwd"])
+    gy = mk(1, T, D)
+    keys = mk(E, D, F, scale=D ** -0.5).requires_grad_(cfg["bwd"])
+    values = mk(E, F, D, scale=F ** -0.5).requires_grad_(cfg["bwd"])
+    input_range = torch.full((2, E), 3.0, device=device, dtype=dtype, requires_grad=cfg["bwd"])
+    logits = torch.randn(T, E, generator=g).to(device)
+    gate, raw_sel = torch.sigmoid(logits).topk(k, dim=-1)
+    ssel, perm = torch.sort(raw_sel.flatten(), stable=True)
+    sel3, raw3 = ssel.view(1, T, k), raw_sel.view(1, T, k)
+    gate = gate.view(1, T, k).to(dtype).requires_grad_(cfg["bwd"])
+    tok = perm // k
+
+    class IR:
+        enable, decay, input_min_percentage = True, 0.01, 0.95
+
+    class IO:
+        pass
+
+    inp_res = 2.0 / 254.0
+    training = cfg["bwd"]
+
+    def projection(inp, sel_index, w, ir_row, out_index, rw):
+        bir = input_range[ir_row][sel3]
+        wm = w
+        if training and cfg["w_noise"] > 0:
+            with torch.no_grad():
+                noise_w = cfg["w_noise"] * w.abs().amax(1, keepdim=True) * torch.randn_like(w)
+            wm = w + noise_w
+        noise = None
+        if training and cfg["out_noise"] > 0:
+            noise = torch.randn(1, T, k, w.shape[-1], device=device) * cfg["out_noise"] * w.abs().amax(1)[raw3]
+        return ref.CVMM.apply(inp, sel_index, sel3, wm, inp_res, bir, out_index, rw, noise, IR, IO())
+
+    def one_step():
+        for t in (x, keys, values, input_range, gate):
+            t.grad = None
+        h = torch.relu(projection(x, tok, keys, 0, perm, None))
+        y = projection(h, perm, values, 1, None, gate)
+        if training:
+            y.backward(gy)
+        return y
+
+    ctx = torch.enable_grad() if training else torch.no_grad()
+    with ctx:
+        for _ in range(max(warmup, 2)):
+            one_step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one_step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return dict(value=T / (ms * 1e-3), unit="tokens/s", ms_per_step=ms, steps=steps,
+                what="reference Triton CVMM.apply x2 + ReLU, fwd" + ("+bwd" if training else "") +
+                     ", with the noise tensors its layer materialises; no ADC, no router/top-k/sort (the reference has "
+                     "none); eager launches as the reference makes them")
 
 
 def run_cpu(cfg, steps, warmup, sample_tokens=None):
@@ -358,6 +551,7 @@ def main():
     ap.add_argument("--precision", default=None, help="split | bf16x1 | fp32 (default: split for fp32, bf16x1 for bf16)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the reference-Triton leg (profiling runs)")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--kernel-times", default=None, metavar="PATH",
@@ -433,6 +627,17 @@ def main():
         line["config"]["l2"] = "inputs rotate over 8 buffer sets (> 126 MB L2) and one step touches > 400 MB"
         line["config"]["cuda_graph"] = r["graph"]
         line["config"]["precision"] = {0: "bf16x1", 1: "split (bf16 hi+lo, fp32 accumulate)", 2: "fp32 CUDA cores"}[r["precision"]]
+        if r.get("parity") is not None:
+            line["parity"] = r["parity"]
+        if r.get("dropin_ms"):
+            line["dropin"] = dict(value=cfg["T"] / (r["dropin_ms"] * 1e-3), unit="tokens/s", ms_per_step=r["dropin_ms"],
+                                  what="the same step as two CVMM.apply calls with torch glue (the path the reference's "
+                                       "layer files take through triton_src), eager launches")
+        if world == 1 and not args.no_gpu_baseline:
+            try:
+                line["gpu_baseline"] = run_reference_triton(cfg, device, max(3, min(args.steps, 10)), 3)
+            except Exception as exc:       # recorded, never retried: the reference's kernels are not ours to debug
+                line["gpu_baseline"] = {"unavailable": f"reference Triton path failed: {exc!r}"[:300]}
         if world == 1 and not args.no_cpu_baseline:
             c = run_cpu(cfg, 1, 1, args.cpu_sample_tokens)
             line["cpu_baseline"] = dict(value=c["tokens_per_s"], unit="tokens/s", cores=c["cores"], kind="port",

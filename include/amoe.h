@@ -162,6 +162,9 @@ typedef struct amoe_weight_prepass_args {
    * as w; pass w itself to clip in place) and everything else - maxima, modifier, prepared copies - is computed from
    * them.  Needs the larger workspace of amoe_weight_prepass_clip_workspace_bytes (8-byte aligned). */
   float clip_sigma; int32_t clip_per_channel; float clip_fixed; void* w_clip_out;
+  /* Added to the expert index in the weight-noise counter (row (expert_base + e)*K + k): a rank that holds experts
+   * [base, base + E) of a larger layer draws the noise the whole layer would draw for them. */
+  int32_t expert_base;
 } amoe_weight_prepass_args;
 size_t amoe_weight_prepass_workspace_bytes(int32_t E, int32_t K, int32_t N);
 size_t amoe_weight_prepass_clip_workspace_bytes(int32_t E, int32_t K, int32_t N);
@@ -322,7 +325,9 @@ int amoe_cvmm_dw(const amoe_dw_args* args, amoe_stream_t stream);
  * amoe_row_dot: d[s] = res[row(s),:] . g[s/k,:]  (gate gradient, cvmm.py:889).
  * amoe_ir_grad_reduce: per-expert sum of the per-slot input-range gradients plus the decay term
  *   decay*ir_e*count_e*[keep_count/total > min_percentage] (cvmm.py:872-878 followed by autograd's
- *   index-add of input_range[ir_idx][sel]).  ir_grad_slot [P] sorted; out [E].
+ *   index-add of input_range[ir_idx][sel]).  ir_grad_slot [P] sorted; out [E].  total = total_rows_dev[0]*cols when
+ *   the device counter is given (e.g. rows summed over the ranks of an expert-parallel group), else total_elements
+ *   when positive, else expert_offsets[E]*cols.
  * ---------------------------------------------------------------------------------------- */
 int amoe_combine(const void* res, int32_t res_dtype, int64_t res_stride, const int32_t* row_index, const float* w,
                  int64_t T, int32_t k, int32_t N, void* y, int32_t y_dtype, int64_t y_stride, amoe_stream_t stream);
@@ -338,7 +343,8 @@ int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_
                        float* d, const int32_t* row_index, amoe_stream_t stream);
 int amoe_ir_grad_reduce(const float* ir_grad_slot, const int32_t* expert_offsets, const float* input_range,
                         int32_t E, float decay, float min_percentage, const unsigned long long* keep_count,
-                        double total_elements, float* out, amoe_stream_t stream);
+                        double total_elements, const long long* total_rows_dev, int32_t cols, float* out,
+                        amoe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------
  * Per-expert standard deviation of the routed rows.  Replaces cvmm_std and its two kernels
@@ -403,16 +409,20 @@ int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_
  * amoe_ep_put: row x[src_row[i]/src_div] (* row_scale[src_row[i]]) of sorted position i is stored at its place in the
  *   receive buffer of the rank owning expert sel_sorted[i] (= sel_sorted[i]/El); peer_ptrs: device array of G base
  *   pointers (buffers of peer_rows rows of K elements, this rank's own included).  Plain stores, no waiting.
- * amoe_ep_put_back: the first R rows of `rows` (receive order) go back to their place in the source rank's buffer. */
+ * amoe_ep_put_back: the first R rows of `rows` (receive order) go back to their place in the source rank's buffer.
+ * A plan that reports more rows than a buffer holds, or a row whose destination lies outside the peer's buffer, is
+ * recorded in dev_status (AMOE_ERR_INDEX_RANGE; may be NULL) and the row is dropped, never written out of bounds. */
 int64_t amoe_ep_plan_ints(int32_t G, int32_t El);
 int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, int32_t* plan, amoe_stream_t stream);
 int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
-                           int32_t* local_offsets, amoe_stream_t stream);
+                           int32_t* local_offsets, int32_t* dev_status, amoe_stream_t stream);
 int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row,
                 int32_t src_div, const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El,
-                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, amoe_stream_t stream);
+                const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, int32_t* dev_status,
+                amoe_stream_t stream);
 int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K, const int32_t* plan,
-                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, amoe_stream_t stream);
+                     const uint64_t* peer_ptrs, int32_t G, int64_t cap_rows, int64_t peer_rows, int32_t* dev_status,
+                     amoe_stream_t stream);
 /* inv[idx[i]] = i for a permutation idx of 0..P-1. */
 int amoe_invert_index(const int32_t* idx, int64_t P, int32_t* inv, amoe_stream_t stream);
 int amoe_ep_unpack(const void* recv_rows, int32_t dtype, int32_t N, const int32_t* dst_row, int64_t P,

@@ -6,7 +6,6 @@ reference layers rely on), configuration dataclasses and enums with the referenc
 `AnalogLayerBase` that does nothing, `convert_to_analog` that leaves the router Linear digital, a straight-through
 `UniformQuantize`, and an `AnalogContext` placeholder.  Test infrastructure only.
 """
-import enum
 import importlib.util
 import os
 import sys
@@ -76,14 +75,6 @@ def install() -> None:
     _module("aihwkit_lightning.nn.modules.torch_utils.torch_linear", UniformQuantize=_UniformQuantize)
     _module("aihwkit_lightning.nn.conversion", convert_to_analog=convert_to_analog)
 
-    # classic aihwkit: the modifier enum has two more members the layer names (COPY, MULT_NORMAL)
-    class WeightModifierType(enum.Enum):
-        NONE = "None"
-        COPY = "Copy"
-        DISCRETIZE = "Discretize"
-        MULT_NORMAL = "MultNormal"
-        ADD_NORMAL = "AddNormal"
-
     class AnalogContext(torch.nn.Parameter):
         def __new__(cls, layer):
             return torch.nn.Parameter.__new__(cls, torch.zeros(()), requires_grad=False)
@@ -98,7 +89,7 @@ def install() -> None:
     _module("aihwkit.simulator.configs.configs", TorchInferenceRPUConfig=R.TorchInferenceRPUConfig)
     _module("aihwkit.simulator.parameters.base", RPUConfigBase=RPUConfigBase)
     _module("aihwkit.optim.context", AnalogContext=AnalogContext)
-    _module("aihwkit.simulator.parameters.enums", WeightModifierType=WeightModifierType, WeightClipType=R.WeightClipType,
+    _module("aihwkit.simulator.parameters.enums", WeightModifierType=R.WeightModifierType, WeightClipType=R.WeightClipType,
             WeightRemapType=R.WeightRemapType, BoundManagementType=R.BoundManagementType,
             NoiseManagementType=R.NoiseManagementType)
     _module("aihwkit.simulator.parameters", WeightModifierParameter=R.WeightModifierParameter,
