@@ -14,9 +14,9 @@ import torch
 from . import _build
 
 F32, BF16 = 0, 1
-PREC_BF16X1, PREC_SPLIT, PREC_FP32_SIMT = 0, 1, 2
+PREC_BF16X1, PREC_SPLIT, PREC_FP32_SIMT, PREC_F16X1 = 0, 1, 2, 3
 PRECISION_NAMES = {"bf16": PREC_BF16X1, "bf16x1": PREC_BF16X1, "split": PREC_SPLIT, "fp32": PREC_FP32_SIMT,
-                   "simt": PREC_FP32_SIMT}
+                   "simt": PREC_FP32_SIMT, "f16": PREC_F16X1, "f16x1": PREC_F16X1, "fp16": PREC_F16X1}
 
 c_i32p = C.c_void_p
 vp = C.c_void_p
@@ -39,7 +39,7 @@ class WeightPrepassArgs(C.Structure):
         ("col_scale", vp), ("col_inv_scale", vp), ("w_out", vp), ("fwd_hi", vp), ("fwd_lo", vp), ("bwd_hi", vp), ("bwd_lo", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t),
         ("clip_sigma", C.c_float), ("clip_per_channel", C.c_int32), ("clip_fixed", C.c_float), ("w_clip_out", vp),
-        ("expert_base", C.c_int32),
+        ("expert_base", C.c_int32), ("prepared_f16", C.c_int32),
     ]
 
 
@@ -64,7 +64,7 @@ class CvmmArgs(C.Structure):
         ("a_cache_hi", vp), ("a_cache_lo", vp), ("a_cache_scale", vp), ("out_cache_hi", vp), ("out_cache_lo", vp), ("cache_rows", C.c_int64),
         ("a_tile_hi", vp), ("a_tile_lo", vp),
         ("next_ir", vp), ("next_inp_res", C.c_float), ("next_codes", vp), ("out_cache_scale", vp),
-        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp), ("a_absmax_dev", vp),
     ]
 
 
@@ -76,7 +76,7 @@ class DwArgs(C.Structure):
         ("g", vp), ("g_dtype", C.c_int32), ("g_stride", C.c_int64), ("g_rows", C.c_int64), ("g_row", vp),
         ("g_div", C.c_int32), ("g_scale", vp), ("dw", vp),
         ("x_hi", vp), ("x_lo", vp), ("g_hi", vp), ("g_lo", vp), ("cache_rows", C.c_int64), ("expected_rows", C.c_int64),
-        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp),
+        ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp), ("g_absmax_dev", vp),
     ]
 
 
@@ -107,6 +107,7 @@ SIGNATURES = {
     "amoe_weight_prepass_clip_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "amoe_prepared_dims": (None, [C.c_int32, C.c_int32, C.POINTER(C.c_int32 * 4)]),
     "amoe_weight_prepass": (C.c_int, [C.POINTER(WeightPrepassArgs), vp]),
+    "amoe_tensor_absmax": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp, vp]),
     "amoe_row_absmax": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp]),
     "amoe_cvmm_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "amoe_padded_rows": (C.c_int64, [C.c_int64, C.c_int32]),

@@ -421,19 +421,21 @@ class _ExpertParallelStep(torch.autograd.Function):
             split = xc_lo is not None
             gc = ops.OperandCache.empty(R, El, N, split, dev) if cached and need_values else None
             dhc = ops.OperandCache.empty(R, El, Fh, split, dev) if cached and need_keys else None
+            # fp16 operands: max|g| over the rows that really arrived (the buffer has worst-case size)
+            gmax = ops.grad_absmax(g_recv, precision, plan[0:1] if xchg is not None else None)
             if need_values and not cached:
                 grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
-                                          ir_by_expert=True)
+                                          ir_by_expert=True, g_absmax=gmax)
             dh, irs_dn = ops.cvmm_dx(g_recv, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
                                      x_ref=h, x_ref_row=local_order, ir=ir_dn, ir_by_expert=True, want_ir_grad=has_ir,
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
-                                     out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc)
+                                     out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc, g_absmax=gmax)
             ops.set_tag("up")
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
                                       ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                       keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype,
-                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None)
+                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None, g_absmax=gmax)
             # the two weight gradients on a second stream, beside the exchange and the streaming kernels that follow
             forked = cached and (need_values or need_keys)
             if forked:
@@ -442,14 +444,15 @@ class _ExpertParallelStep(torch.autograd.Function):
                     if need_values:
                         ops.set_tag("down")
                         grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, local_offsets, El, precision,
-                                                         P=R, expected_rows=n_rows)
+                                                         P=R, expected_rows=n_rows, g_absmax=gmax)
                     if need_keys:
                         ops.set_tag("up")
                         grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, local_offsets, El, precision,
-                                                       P=R, expected_rows=n_rows)
+                                                       P=R, expected_rows=n_rows, g_absmax=gmax)
             elif need_keys:
                 grad_keys = ops.cvmm_dw(recv, local_order, dh, local_order, local_offsets, El, precision, P=R, ir=ir_up,
-                                        ir_by_expert=True)
+                                        ir_by_expert=True,
+                                        g_absmax=ops.grad_absmax(dh, precision, plan[0:1] if xchg is not None else None))
         else:
             dxr = recv.new_zeros((0, D))
             irs_up = irs_dn = None

@@ -215,15 +215,20 @@ class _FusedAnalogStep(torch.autograd.Function):
         grad_values = None
         if need_values and not cached:
             grad_values = ops.cvmm_dw(h, slot_index, g, slot_index, offsets, E, precision, P=P, ir=ir_dn,
-                                      ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1))
+                                      ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1),
+                                      g_absmax=ops.grad_absmax(g, precision))
         split = xc_lo is not None
         gc = ops.OperandCache.empty(P, E, N, split, x2.device) if cached and need_values else None
         dhc = ops.OperandCache.empty(P, E, Fh, split, x2.device) if cached and need_keys else None
+        # fp16 operands: one scalar (max|gy|) scales every gradient operand of the step into fp16's normal range
+        gmax = ops.grad_absmax(g, precision)
+        # the hidden gradient is only needed as fp32 rows when the next kernel cannot take it as tiles
+        tiles_next = dhc is not None and Fh % 64 == 0 and (need_x or need_ir)
         dh, irs_dn = ops.cvmm_dx(g, slot_index, slot_index, offsets, pw_dn, precision, P=P, dst_rows=P, a_row_div=k,
                                  x_ref=h, x_ref_row=slot_index, ir=ir_dn, ir_by_expert=True, row_scale=gate.reshape(-1),
                                  want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                  keep_count=keeps[1:] if keeps is not None else None, out_dtype=h.dtype,
-                                 x_ref_relu=True, a_cache=gc, out_cache=dhc)
+                                 x_ref_relu=True, a_cache=gc, out_cache=dhc, g_absmax=gmax, want_out=not tiles_next)
         # ---- up-projection's input gradient (the other kernel that fills every SM), then the two weight gradients from
         # the caches on a second stream: the TMA-fed kernel runs six warps per SM and leaves registers and issue slots
         # to the streaming kernels of the main stream (gate gradient, sum over k, router), which run beside it
@@ -233,11 +238,11 @@ class _FusedAnalogStep(torch.autograd.Function):
             # the hidden gradient already exists as bf16 hi/lo tiles (the dW operand the kernel above wrote): TMA feeds
             # it, no gather/convert prologue
             tiles = dhc if (dhc is not None and Fh % 64 == 0) else None
-            dxr, irs_up = ops.cvmm_dx(dh, slot_index, slot_index, offsets, pw_up, precision, P=P, dst_rows=P,
-                                      x_ref=x2 if has_ir else None, x_ref_row=token_index if has_ir else None,
+            dxr, irs_up = ops.cvmm_dx(dh if dh is not None else h, slot_index, slot_index, offsets, pw_up, precision, P=P,
+                                      dst_rows=P, x_ref=x2 if has_ir else None, x_ref_row=token_index if has_ir else None,
                                       ir=ir_up, ir_by_expert=True, want_ir_grad=has_ir, relative=relative,
                                       grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
-                                      out_dtype=x2.dtype, a_tiles=tiles)
+                                      out_dtype=x2.dtype, a_tiles=tiles, g_absmax=gmax)
         grad_keys = None
         main, side = torch.cuda.current_stream(), ops.side_stream(x2.device)
         forked = cached and (need_values or need_keys)
@@ -247,13 +252,16 @@ class _FusedAnalogStep(torch.autograd.Function):
                 if need_values:
                     # dW = sum_slots (gate * clamp(h))^T (x) gy: both operands straight from the caches
                     ops.set_tag("down")
-                    grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision, P=P)
+                    grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision, P=P,
+                                                     g_absmax=gmax)
                 if need_keys:
                     ops.set_tag("up")
-                    grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P)
+                    grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P,
+                                                   g_absmax=gmax)
         elif need_keys:
+            # (the hidden gradient's own magnitude scales it here: it is gathered from fp32 rows)
             grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
-                                    ir_by_expert=True)
+                                    ir_by_expert=True, g_absmax=ops.grad_absmax(dh, precision))
         ops.set_tag("down")
         if codes is not None:
             dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)

@@ -100,7 +100,9 @@ def default_precision(dtype: torch.dtype) -> int:
     env = os.environ.get("AMOE_PRECISION")
     if env:
         return A.PRECISION_NAMES[env.lower()]
-    return A.PREC_BF16X1 if dtype == torch.bfloat16 else A.PREC_SPLIT
+    # bf16 data: operands are exact in one bf16 term.  fp32 data: one fp16 term (about 2e-4 of the result's scale, inside
+    # the 1e-3 the specification allows); "split" (bf16 hi+lo, about 2e-5) and "fp32" (CUDA cores) are the tighter modes.
+    return A.PREC_BF16X1 if dtype == torch.bfloat16 else A.PREC_F16X1
 
 
 def new_status(device) -> torch.Tensor:
@@ -291,6 +293,7 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     else:
         # bf16 weights are exact in one term unless the modifier adds fp32 noise on top
         split = precision == A.PREC_SPLIT and (w.dtype != torch.bfloat16 or modified)
+        a.prepared_f16 = int(precision == A.PREC_F16X1)        # (the 16-bit buffers are typed bf16 either way)
         npad, kpad, kpad2, npad2 = prepared_dims(K, N)
         if need_fwd:
             out.fwd_hi = torch.empty(E, npad, kpad, dtype=torch.bfloat16, device=dev)
@@ -336,6 +339,21 @@ def clip_weights_(w: torch.Tensor, sigma: float = -1.0, per_channel: bool = Fals
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     _call("amoe_weight_prepass", C.byref(a), stream_ptr())
     w._amoe_workspace = ws
+
+
+def tensor_absmax(x2: torch.Tensor, n_rows_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """max|x| over the rows of x2 (over the first n_rows_dev[0] rows when that int32 device tensor is given) as a
+    one-element fp32 device tensor: what scales the gradient operands of the fp16 precision."""
+    x2 = _rows(x2)
+    out = torch.empty(1, dtype=torch.float32, device=x2.device)
+    _call("amoe_tensor_absmax", ptr(x2), dtype_code(x2), x2.shape[0], x2.shape[1], x2.stride(0), ptr(n_rows_dev), ptr(out),
+          stream_ptr())
+    return out
+
+
+def grad_absmax(g2: torch.Tensor, precision: int, n_rows_dev: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The scalar the fp16 precision needs for an upstream gradient; None for the other precisions."""
+    return tensor_absmax(g2, n_rows_dev) if precision == A.PREC_F16X1 else None
 
 
 def row_absmax(x2: torch.Tensor) -> torch.Tensor:
@@ -433,12 +451,14 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             relative: bool = True, grad_scale: float = 1.0, keep_count: Optional[torch.Tensor] = None,
             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
             ir_by_expert: bool = False, x_ref_relu: bool = False, a_cache: Optional["OperandCache"] = None,
-            out_cache: Optional["OperandCache"] = None, a_tiles: Optional["OperandCache"] = None):
+            out_cache: Optional["OperandCache"] = None, a_tiles: Optional["OperandCache"] = None,
+            g_absmax: Optional[torch.Tensor] = None, want_out: bool = True):
     """`a_tiles`: the A operand as an operand cache written by an earlier kernel (TMA-fed, no gather); g2 then only
-    gives dtype and device."""
+    gives dtype and device.  `g_absmax`: the device scalar of the fp16 precision (see tensor_absmax).  `want_out=False`
+    (with `out_cache`): only the operand cache is written."""
     g2 = _rows(g2)
     dev = g2.device
-    out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev)
+    out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev) if want_out else None
     ir_grad = torch.empty(P, dtype=torch.float32, device=dev) if want_ir_grad else None
     a = A.CvmmArgs()
     a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
@@ -458,7 +478,11 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     if a_tiles is not None:
         a.a_tile_hi, a.a_tile_lo = ptr(a_tiles.hi), ptr(a_tiles.lo)
         a.cache_rows = a_tiles.rows
-    a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
+    if out is not None:
+        a.out, a.out_dtype, a.out_stride = ptr(out), dtype_code(out), out.stride(0)
+    else:
+        a.out_dtype, a.out_stride = dtype_code(g2), pw.K
+    a.a_absmax_dev = ptr(g_absmax)
     if x_ref is not None:
         x_ref = _rows(x_ref)
         a.x_ref, a.x_ref_dtype, a.x_ref_stride, a.x_ref_row = ptr(x_ref), dtype_code(x_ref), x_ref.stride(0), ptr(x_ref_row)
@@ -474,7 +498,7 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
 def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torch.Tensor, offsets: torch.Tensor,
             E: int, precision: int, *, P: int, ir: Optional[torch.Tensor] = None, g_div: int = 1,
             g_scale: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-            ir_by_expert: bool = False) -> torch.Tensor:
+            ir_by_expert: bool = False, g_absmax: Optional[torch.Tensor] = None) -> torch.Tensor:
     x2, g2 = _rows(x2), _rows(g2)
     K, N = x2.shape[1], g2.shape[1]
     dw = torch.empty(E, K, N, dtype=torch.float32, device=x2.device)
@@ -485,6 +509,7 @@ def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torc
     a.g, a.g_dtype, a.g_stride, a.g_rows, a.g_row = ptr(g2), dtype_code(g2), g2.stride(0), g2.shape[0], ptr(g_row)
     a.g_div, a.g_scale, a.dw = g_div, ptr(g_scale), ptr(dw)
     a.ir_by_expert = int(ir_by_expert)
+    a.g_absmax_dev = ptr(g_absmax)
     nbytes = lib.amoe_cvmm_dw_workspace_bytes(P, E, K, N, precision)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device) if nbytes else None
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
@@ -517,7 +542,8 @@ def operand_cache_ok(precision: int, *cols: int) -> bool:
 
 
 def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.Tensor, E: int, precision: int, *,
-                   P: int, status: Optional[torch.Tensor] = None, expected_rows: int = 0) -> torch.Tensor:
+                   P: int, status: Optional[torch.Tensor] = None, expected_rows: int = 0,
+                   g_absmax: Optional[torch.Tensor] = None) -> torch.Tensor:
     """dW [E,K,N] from two operand caches ([rows,K] and [rows,N]).  `expected_rows`: the likely slot count when P is
     only an upper bound (tunes the work split)."""
     K, N = x_cache.cols, g_cache.cols
@@ -531,6 +557,7 @@ def cvmm_dw_cached(x_cache: OperandCache, g_cache: OperandCache, offsets: torch.
     a.expected_rows = int(expected_rows)
     a.g_div = 1
     a.dw = ptr(dw)
+    a.g_absmax_dev = ptr(g_absmax)
     nbytes = lib.amoe_cvmm_dw_workspace_bytes_tuned(P, int(expected_rows), E, K, N, precision)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev) if nbytes else None
     a.workspace, a.workspace_bytes = ptr(ws), nbytes

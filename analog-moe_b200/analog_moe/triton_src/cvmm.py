@@ -298,15 +298,17 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
     pw = ops.PreparedWeights(E, K, N, col_scale, w=w, bwd_hi=bwd_hi, bwd_lo=bwd_lo)
     k = reduction_weight.shape[-1] if down else max(P // x2.shape[0], 1)
     rw = reduction_weight.reshape(-1).float().contiguous() if down else None
+    gmax = ops.grad_absmax(g, precision)        # fp16 operands: the scalar that scales the gradient rows
     grad_w = _empty(x2)
     if need_w:
         # reference cvmm.py:785-823: the outer product rw (x) g is folded into the operand load
         if down:
             grad_w = ops.cvmm_dw(x2, sel_index_i, g, sel_index_i, offsets, E, precision, P=P, ir=ir, g_div=k,
-                                 g_scale=rw, status=status)
+                                 g_scale=rw, status=status, g_absmax=gmax)
         else:
             g_row = out_index_i if out_index_i is not None else sel_index_i
-            grad_w = ops.cvmm_dw(x2, sel_index_i, g, g_row, offsets, E, precision, P=P, ir=ir, status=status)
+            grad_w = ops.cvmm_dw(x2, sel_index_i, g, g_row, offsets, E, precision, P=P, ir=ir, status=status,
+                                 g_absmax=gmax)
     grad_x = _empty(x2)
     grad_ir = _empty(x2, torch.float32)
     if need_x or need_ir:
@@ -318,7 +320,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
                                       a_row_div=k, x_ref=x2 if ir is not None else None,
                                       x_ref_row=sel_index_i if ir is not None else None, ir=ir, row_scale=rw,
                                       want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
-                                      keep_count=keep, out_dtype=x.dtype, status=status)
+                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax)
             grad_x = gx.view(x.shape)
         else:
             src = out_index_i if out_index_i is not None else sel_index_i
@@ -326,7 +328,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
                                       x_ref=x2 if ir is not None else None,
                                       x_ref_row=sel_index_i if ir is not None else None, ir=ir,
                                       want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
-                                      keep_count=keep, out_dtype=x.dtype, status=status)
+                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax)
             T = x2.shape[0]
             grad_x = (ops.combine(gx, None, T, P // T) if P != T else gx).view(x.shape)               # cvmm.py:890-891
         if ir is not None:

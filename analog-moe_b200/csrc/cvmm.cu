@@ -11,7 +11,7 @@ int check_common(const amoe_cvmm_args* a) {
   AMOE_REQUIRE(a != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->P > 0 && a->E > 0 && a->K > 0 && a->N > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(a->P < (int64_t{1} << 31) && a->E <= 65535, AMOE_ERR_BAD_SHAPE);
-  AMOE_REQUIRE(a->expert_offsets && a->dst_row && (a->out || a->out_codes), AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(a->expert_offsets && a->dst_row && (a->out || a->out_codes || a->out_cache_hi), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE((a->a && a->a_row) || (a->a_tile_hi && a->precision != AMOE_PREC_FP32_SIMT), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->a_dtype == AMOE_F32 || a->a_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->out_dtype == AMOE_F32 || a->out_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
@@ -19,7 +19,7 @@ int check_common(const amoe_cvmm_args* a) {
   if (a->precision == AMOE_PREC_FP32_SIMT) {
     AMOE_REQUIRE(a->w != nullptr, AMOE_ERR_NULL_POINTER);
     AMOE_REQUIRE(a->w_dtype == AMOE_F32 || a->w_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
-  } else if (a->precision == AMOE_PREC_BF16X1 || a->precision == AMOE_PREC_SPLIT) {
+  } else if (a->precision == AMOE_PREC_BF16X1 || a->precision == AMOE_PREC_SPLIT || a->precision == AMOE_PREC_F16X1) {
     AMOE_REQUIRE(a->w_hi != nullptr, AMOE_ERR_NULL_POINTER);
   } else {
     return AMOE_ERR_UNSUPPORTED;
@@ -115,7 +115,7 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   AMOE_REQUIRE(!a->ir_grad || (a->x_ref && a->ir), AMOE_ERR_NULL_POINTER);
   e.row_scale = a->row_scale; e.ir_grad = a->ir_grad; e.relative = a->ir_grad_relative;
   e.grad_scale = a->ir_grad_scale; e.keep_count = a->keep_count;
-  AMOE_REQUIRE(a->out != nullptr, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(a->out != nullptr || (a->out_cache_hi != nullptr && a->precision != AMOE_PREC_FP32_SIMT), AMOE_ERR_NULL_POINTER);
   e.status = a->dev_status;
   e.vec4 = (a->K % 4 == 0) && al16(a->out) && (a->out_stride % 4 == 0) &&
            (!a->x_ref || (al16(a->x_ref) && a->x_ref_stride % 4 == 0));
@@ -145,7 +145,8 @@ int amoe_cvmm_dw(const amoe_dw_args* a, amoe_stream_t stream_) {
                AMOE_ERR_BAD_DTYPE);
   AMOE_REQUIRE(a->x_rows > 0 && a->g_rows > 0 && a->g_div >= 1, AMOE_ERR_BAD_SHAPE);
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_dw_simt(a, stream);
-  if (a->precision == AMOE_PREC_BF16X1 || a->precision == AMOE_PREC_SPLIT) return launch_dw_tc(a, stream);
+  if (a->precision == AMOE_PREC_BF16X1 || a->precision == AMOE_PREC_SPLIT || a->precision == AMOE_PREC_F16X1)
+    return launch_dw_tc(a, stream);
   return AMOE_ERR_UNSUPPORTED;
 }
 

@@ -48,6 +48,10 @@ constexpr int kBK = 64;           // bf16 elements per stage along the contracti
 // (which spilled) and than 20 x 102.
 constexpr int kWorkerWarps = 22;
 constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 768
+// Staged operand prologue: raw rows travel global -> shared by cp.async, kStagePF ring stages ahead of the stage that
+// is being converted, through kStagePF + 1 staging slots of 128 rows x 64 elements.
+constexpr int kStagePF = 2;
+constexpr int kStageSlots = kStagePF + 1;
 constexpr int kMaxEpiGroups = 6;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATile = kBM * kBK * 2;  // 16 KiB
@@ -92,7 +96,8 @@ struct TileIter {
 
 struct TcParams {
   int E, Kc, Nout;
-  int n_epi;   // epilogue warps (multiple of 4); the other worker warps run the operand prologue
+  int n_epi;   // epilogue warps (multiple of 4)
+  int n_prod;  // operand-prologue warps (the staged prologue wants 8 or 16); n_epi + n_prod <= kWorkerWarps
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   int prod_groups;      // 1, or 2: the prologue warps form two groups that take alternate stages, so that one
@@ -107,8 +112,28 @@ struct TcParams {
   __nv_bfloat16* cache_hi; __nv_bfloat16* cache_lo; int64_t cache_stride /* rows of the cache */; const float* cache_scale;
   int a_tma;            // the A operand exists as prepared bf16 tiles (an operand cache written by an earlier kernel):
                         // TMA loads it, there is no prologue and every worker warp runs the epilogue
+  int item_mode;        // work item = (row tile, n-tile) instead of a row tile with all its n-tiles (only without a
+                        // prologue: the A tile is cheap to load again, and small items fill the last wave better)
+  int staged;           // operand prologue fed by cp.async through the staging slots (aligned rows, K % 8 == 0)
+  uint32_t stg_off;     // offset of the staging slots in dynamic shared memory
+  uint32_t stg_slot;    // bytes per staging slot
+  const float* g_absmax;  // fp16 operands, input gradient: device scalar max|A|; A is scaled by a power of two derived
+                          // from it before the conversion and the result scaled back (NULL: no scaling)
   EpiParams epi;
 };
+
+// Power of two s such that amax * s lies in [2^7, 2^8): gradient rows scaled by it use fp16's normal range whatever
+// their magnitude.  1 for zero or non-finite amax.  `inv` receives 1/s (exact).
+__device__ __forceinline__ float grad_pow2_scale(float amax, float& inv) {
+  inv = 1.f;
+  if (!(amax > 0.f) || !(amax < 3.0e38f)) return 1.f;
+  int ex = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
+  if (ex == 0) ex = 1;
+  int k = 7 - (ex - 127);
+  k = max(-120, min(120, k));
+  inv = __uint_as_float(static_cast<uint32_t>(127 - k) << 23);
+  return __uint_as_float(static_cast<uint32_t>(127 + k) << 23);
+}
 
 enum { kDacNone = 0, kDacNorm = 1, kDacQuant = 2 };
 // Epilogue families: forward with the vectorised fast path (optional Philox noise / ADC / codes),
@@ -163,14 +188,22 @@ __device__ __forceinline__ uint32_t cvt_bf16x2(float lo, float hi) {
   return r;
 }
 
-// Eight values -> one 16-byte chunk of bf16 (and a second chunk with the rounding residuals).
-// tile_hi / tile_lo are shared-memory addresses.
+// Two values -> one packed pair of the operand format (fp16 when F16, else bf16).
+template <bool F16>
+__device__ __forceinline__ uint32_t cvt_op2(float lo, float hi) {
+  if (F16) return cvt_f16x2(lo, hi);
+  return cvt_bf16x2(lo, hi);
+}
+
+// Eight values -> one 16-byte chunk of the operand format (and, bf16 only, a second chunk with the rounding
+// residuals).  tile_hi / tile_lo are shared-memory addresses.
+template <bool F16 = false>
 __device__ __forceinline__ void store8_rt(uint32_t tile_hi, uint32_t tile_lo, uint32_t off, const float v[8], bool split) {
   uint32_t h[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = cvt_bf16x2(v[2 * i], v[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) h[i] = cvt_op2<F16>(v[2 * i], v[2 * i + 1]);
   sts128(tile_hi + off, h[0], h[1], h[2], h[3]);
-  if (split) {
+  if (!F16 && split) {
     uint32_t l[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -324,7 +357,7 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 // kValue = false: only the ADC codes leave the kernel, the dequantised values are not formed.
 // The ADC code rint(x) is taken as (x + 1.5*2^23) - 1.5*2^23 (exact round-to-nearest-even for |x| < 2^22; codes are
 // at most 127 in magnitude), whose low mantissa byte is the code in two's complement.
-template <bool kValue>
+template <bool kValue, bool F16>
 __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
                                               float v[16], const float* cs, const float* cis, int lane) {
   constexpr float kMagic = 12582912.f;
@@ -390,16 +423,16 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
         uint32_t q[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x)
-          q[x] = cvt_bf16x2(dac_code_clamped(hc[2 * x], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res),
-                            dac_code_clamped(hc[2 * x + 1], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res));
+          q[x] = cvt_op2<F16>(dac_code_clamped(hc[2 * x], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res),
+                              dac_code_clamped(hc[2 * x + 1], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res));
         *reinterpret_cast<uint4*>(p.next_codes + co + 8 * half) = make_uint4(q[0], q[1], q[2], q[3]);
       }
       if (p.out_cache_hi) {
         uint32_t h[4];
 #pragma unroll
-        for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(hc[2 * x] * sc, hc[2 * x + 1] * sc);
+        for (int x = 0; x < 4; ++x) h[x] = cvt_op2<F16>(hc[2 * x] * sc, hc[2 * x + 1] * sc);
         *reinterpret_cast<uint4*>(p.out_cache_hi + co + 8 * half) = make_uint4(h[0], h[1], h[2], h[3]);
-        if (p.out_cache_lo) {
+        if (!F16 && p.out_cache_lo) {
           uint32_t l[4];
 #pragma unroll
           for (int x = 0; x < 4; ++x)
@@ -412,8 +445,10 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
   if (kValue) store16_t(p, qr, n0, v, lane);
 }
 
+// `cache_mul`: the operand cache keeps the result times this power of two (the gradient scale of fp16 operands).
+template <bool F16>
 __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
-                                             int lane) {
+                                             int lane, float cache_mul) {
   if (p.x_ref) {
     float xr[16];
     const int col = n0 + 4 * (lane & 3);
@@ -463,9 +498,10 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
     for (int half = 0; half < 2; ++half) {
       uint32_t h[4];
 #pragma unroll
-      for (int x = 0; x < 4; ++x) h[x] = c.valid ? cvt_bf16x2(v[8 * half + 2 * x], v[8 * half + 2 * x + 1]) : 0u;
+      for (int x = 0; x < 4; ++x)
+        h[x] = c.valid ? cvt_op2<F16>(v[8 * half + 2 * x] * cache_mul, v[8 * half + 2 * x + 1] * cache_mul) : 0u;
       *reinterpret_cast<uint4*>(p.out_cache_hi + co + 8 * half) = make_uint4(h[0], h[1], h[2], h[3]);
-      if (p.out_cache_lo) {
+      if (!F16 && p.out_cache_lo) {
         uint32_t l[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x)
@@ -478,7 +514,69 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
   store16_t(p, qr, n0, v, lane);
 }
 
-template <int DAC, bool A_F32, int EPI>
+// Work items of one CTA: row tile t with all its n-tiles, or - item mode - one (row tile, n-tile) pair.
+struct ItemWalk {
+  TileIter ti;
+  int n_tiles, item_mode;
+  int64_t w;
+  int e, row0, rows, nt0, nt1;
+  int64_t t;
+  __device__ ItemWalk(const TcParams& p) : ti(p.offsets, p.E), n_tiles(p.n_tiles), item_mode(p.item_mode), w(blockIdx.x) {}
+  __device__ bool get() {
+    t = item_mode ? w / n_tiles : w;
+    if (!ti.get(t, e, row0, rows)) return false;
+    nt0 = item_mode ? static_cast<int>(w - t * n_tiles) : 0;
+    nt1 = item_mode ? nt0 + 1 : n_tiles;
+    return true;
+  }
+  __device__ void next() { w += gridDim.x; }
+};
+
+// The ring stages of one CTA in the order the pipeline visits them: (row tile, n-tile, k-chunk).
+struct StageWalk {
+  ItemWalk it;
+  int k_chunks;
+  int nt, kc;
+  bool valid, new_tile;
+  __device__ StageWalk(const TcParams& p) : it(p), k_chunks(p.k_chunks), nt(0), kc(0), valid(false), new_tile(true) {
+    valid = it.get();
+    if (valid) nt = it.nt0;
+  }
+  __device__ void next() {
+    new_tile = false;
+    if (++kc == k_chunks) {
+      kc = 0;
+      if (++nt == it.nt1) {
+        it.next();
+        valid = it.get();
+        nt = valid ? it.nt0 : 0;
+        new_tile = true;
+      }
+    }
+  }
+};
+
+// DAC of eight clamped values as packed pairs: ((a/ir)/absmax)/res with IEEE-exact quotients, then the integer code by
+// adding and subtracting 1.5 * 2^23 (round to nearest even, exact for |code| < 2^22).  The same arithmetic as
+// dac_code_clamped, two elements per instruction.
+__device__ __forceinline__ void dac_codes8(float v[8], bool has_ir, float ir, float rcp_ir, bool has_am, float am, float rcp_am,
+                                           float res, float rcp_res) {
+  const f32x2 nir = pack2(-ir, -ir), yir = pack2(rcp_ir, rcp_ir);
+  const f32x2 nam = pack2(-am, -am), yam = pack2(rcp_am, rcp_am);
+  const f32x2 nres = pack2(-res, -res), yres = pack2(rcp_res, rcp_res);
+  const f32x2 magic = pack2(12582912.f, 12582912.f), nmagic = pack2(-12582912.f, -12582912.f);
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    f32x2 t = pack2(v[2 * x], v[2 * x + 1]);
+    if (has_ir) t = div_by_rcp2(t, nir, yir);
+    if (has_am) t = div_by_rcp2(t, nam, yam);
+    t = div_by_rcp2(t, nres, yres);
+    t = add2(add2(t, magic), nmagic);
+    unpack2(t, v[2 * x], v[2 * x + 1]);
+  }
+}
+
+template <int DAC, bool A_F32, int EPI, bool F16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
                const __grid_constant__ CUtensorMap tmap_a_hi, const __grid_constant__ CUtensorMap tmap_a_lo, TcParams p) {
@@ -489,10 +587,13 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
   __shared__ unsigned s_keep[kMaxEpiGroups][kBM];
   const SmemView sm = carve_smem(smem_raw, p.stages * p.stage_bytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_prod = kWorkerWarps - p.n_epi;
+  const int n_prod = p.a_tma ? 0 : p.n_prod;
   setup_cta(sm, p.stages, p.tmem_cols, n_prod > 0 ? n_prod / p.prod_groups : 1, p.n_epi, n_prod > 0 ? n_prod : 1, p.n_epi);
   const uint32_t tmem_base = *sm.tmem_ptr;
   int32_t* status = p.epi.status;
+  // gradient scale of fp16 operands (input gradient only): a power of two from the tensor's largest magnitude
+  float g_mul = 1.f, g_inv = 1.f;
+  if (F16 && p.g_absmax != nullptr) g_mul = grad_pow2_scale(__ldg(p.g_absmax), g_inv);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- weight tiles by TMA
@@ -500,13 +601,10 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       tma_prefetch_desc(&tmap_hi);
       if (p.b_split) tma_prefetch_desc(&tmap_lo);
       if (p.a_tma) { tma_prefetch_desc(&tmap_a_hi); if (p.a_split) tma_prefetch_desc(&tmap_a_lo); }
-      TileIter ti(p.offsets, p.E);
       RingPos rp(p.stages);
       bool alive = true;
-      for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
-        int e, row0, rows;
-        if (!ti.get(t, e, row0, rows)) break;
-        for (int nt = 0; nt < p.n_tiles && alive; ++nt) {
+      for (ItemWalk it(p); alive && it.get(); it.next()) {
+        for (int nt = it.nt0; nt < it.nt1 && alive; ++nt) {
           for (int kc = 0; kc < p.k_chunks; ++kc, rp.next()) {
             const int s = rp.s;
             const uint32_t ph = rp.ph;
@@ -516,11 +614,11 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             if (p.a_tma) {
               // A tile: 128 padded tile rows x 64 columns of block kc of the cache (K-major, 128-byte swizzle)
               const uint32_t sa = sm.base_u32 + s * p.stage_bytes;
-              tma_load_3d(sa, &tmap_a_hi, bar_full_b(sm.bars, s), 0, static_cast<int>(t * kBM), kc);
-              if (p.a_split) tma_load_3d(sa + kATile, &tmap_a_lo, bar_full_b(sm.bars, s), 0, static_cast<int>(t * kBM), kc);
+              tma_load_3d(sa, &tmap_a_hi, bar_full_b(sm.bars, s), 0, static_cast<int>(it.t * kBM), kc);
+              if (p.a_split) tma_load_3d(sa + kATile, &tmap_a_lo, bar_full_b(sm.bars, s), 0, static_cast<int>(it.t * kBM), kc);
             }
-            tma_load_3d(dst, &tmap_hi, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
-            if (p.b_split) tma_load_3d(dst + p.b_bytes, &tmap_lo, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, e);
+            tma_load_3d(dst, &tmap_hi, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, it.e);
+            if (p.b_split) tma_load_3d(dst + p.b_bytes, &tmap_lo, bar_full_b(sm.bars, s), kc * kBK, nt * p.BN, it.e);
           }
         }
       }
@@ -528,21 +626,18 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(kBM, p.BN);
-      TileIter ti(p.offsets, p.E);
+      const uint32_t idesc = F16 ? make_idesc_f16(kBM, p.BN) : make_idesc_bf16(kBM, p.BN);
       RingPos rp(p.stages);
-      uint32_t it = 0, acc_it = 0;
+      uint32_t acc_it = 0;
       bool alive = true;
-      for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
-        int e, row0, rows;
-        if (!ti.get(t, e, row0, rows)) break;
-        for (int nt = 0; nt < p.n_tiles && alive; ++nt, ++acc_it) {
+      for (ItemWalk it(p); alive && it.get(); it.next()) {
+        for (int nt = it.nt0; nt < it.nt1 && alive; ++nt, ++acc_it) {
           const int buf = acc_it & 1u;
           const uint32_t aph = (acc_it >> 1) & 1u;
           if (!mbar_wait(bar_tempty(sm.bars, buf), aph ^ 1u, sm.abort_flag, status, 2)) { alive = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * p.BN);
-          for (int kc = 0; kc < p.k_chunks; ++kc, ++it, rp.next()) {
+          for (int kc = 0; kc < p.k_chunks; ++kc, rp.next()) {
             const int s = rp.s;
             const uint32_t ph = rp.ph;
             if (!p.a_tma && !mbar_wait(bar_full_a(sm.bars, s), ph, sm.abort_flag, status, 3)) { alive = false; break; }
@@ -579,16 +674,17 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
     float* cis_smem = cs_smem + p.cs_per_warp;
     const bool need_cs = EPI == kEpiFwd && (p.epi.noise_std > 0.f || p.epi.adc.on);
-    TileIter ti(p.offsets, p.E);
     uint32_t acc_it = 0, sync_round = 0;
     bool alive = true;
-    for (int64_t t = blockIdx.x; alive; t += gridDim.x) {
-      int e, row0, rows;
-      if (!ti.get(t, e, row0, rows)) break;
-      const int64_t i = static_cast<int64_t>(row0) + r;
+    for (ItemWalk it(p); alive && it.get(); it.next()) {
+      const int e = it.e, rows = it.rows;
+      const int64_t t = it.t;
+      const int64_t i = static_cast<int64_t>(it.row0) + r;
       RowCtx ctx = epi_row_begin(p.epi, i, e, r < rows);
       ctx.pad_row = t * kBM + r;
-      if (grp == 0) epi_row_side_outputs(p.epi, ctx);
+      // the accumulator carries the gradient scale of the A operand: take it out with the row scale
+      if (EPI != kEpiFwd && p.epi.is_dx) ctx.rs *= g_inv;
+      if (grp == 0 && it.nt0 == 0) epi_row_side_outputs(p.epi, ctx);
       QuadRows qr;
       if (EPI != kEpiGeneric) {
         const int my_dst = ctx.valid ? static_cast<int>(ctx.dst) : -1;
@@ -599,7 +695,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           qr.xrow[j] = __shfl_sync(0xffffffffu, my_x, (lane & ~3) + j);
         }
       }
-      for (int nt = 0; nt < p.n_tiles && alive; ++nt, ++acc_it) {
+      for (int nt = it.nt0; nt < it.nt1 && alive; ++nt, ++acc_it) {
         const int buf = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
         if (need_cs) {
@@ -638,10 +734,10 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             }
           } else {   // all 32 lanes: the quad exchange needs every lane, invalid rows are masked inside
             if (EPI == kEpiFwd) {
-              if (p.epi.out != nullptr) epi_chunk_fwd<true>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
-              else epi_chunk_fwd<false>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+              if (p.epi.out != nullptr) epi_chunk_fwd<true, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+              else epi_chunk_fwd<false, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
             }
-            else epi_chunk_dx(p.epi, ctx, qr, n0, v, lane);
+            else epi_chunk_dx<F16>(p.epi, ctx, qr, n0, v, lane, g_mul);
           }
         }
         tc_fence_before();
@@ -650,7 +746,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       }
       if (!alive) break;
       if (p.epi.is_dx && (p.epi.ir_grad || p.epi.keep_count)) {
-        // fixed-order combination of the groups' partial row sums
+        // fixed-order combination of the groups' partial row sums (an item holds all n-tiles of its rows here:
+        // item mode is never combined with these per-row results)
         if (groups > 1) {
           s_dir[grp][r] = ctx.dir_acc;
           s_keep[grp][r] = ctx.valid ? ctx.keep : 0u;
@@ -676,8 +773,196 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         }
       }
     }
-  } else if (!p.a_tma) {
-    // ---------------------------------------------------------------- operand prologue (A tiles)
+  } else if (!p.a_tma && warp < 2 + p.n_epi + n_prod && p.staged) {
+    // ---------------------------------------------------------------- operand prologue, staged (A tiles)
+    // Thread (rg, c) owns 16-byte chunk c of rows rg, rg + np/8, ... of every stage.  For stage g it (1) issues the
+    // cp.async copies of stage g + kStagePF into a staging slot, (2) waits for its own copies of stage g, (3) reads
+    // them back, applies clamp / DAC / conversion and writes its chunks of the swizzled A tile.  A thread only ever
+    // reads staging bytes it copied itself, so cp.async.wait_group is all the synchronisation the staging needs;
+    // global-load latency is hidden by the copies in flight instead of by registers.
+    constexpr int kEsz = A_F32 ? 4 : 2;
+    constexpr uint32_t kPlane = kBM * 8 * 16;            // one 16-byte piece per (row, chunk)
+    const int pw = warp - (2 + p.n_epi);
+    const int np = n_prod * 32;
+    const int pt = pw * 32 + lane;
+    const int c = pt & 7, rg = pt >> 3, rstep = np >> 3;
+    const int tpt = (kBM * 8) / np;                      // chunks per thread and stage: 2 or 4
+    const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
+    const float rcp_res = quant_rcp(p.inp_res);
+    const uint32_t stg = sm.base_u32 + p.stg_off;
+    const uint8_t* abase = reinterpret_cast<const uint8_t*>(p.a);
+    StageWalk pre(p), cur(p);
+    // per-thread row state of the tile being prefetched (source rows) and of the tile being converted
+    int pre_src[4] = {-1, -1, -1, -1};
+    int cur_src[4] = {-1, -1, -1, -1};
+    float cur_ir[4] = {1.f, 1.f, 1.f, 1.f}, cur_am[4] = {1.f, 1.f, 1.f, 1.f}, cur_cs[4] = {1.f, 1.f, 1.f, 1.f};
+    auto rows_of = [&](const StageWalk& w, int src[4]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        src[j] = -1;
+        const int r = rg + j * rstep;
+        if (j < tpt && w.valid && r < w.it.rows) {
+          const int64_t raw = p.a_row[static_cast<int64_t>(w.it.row0) + r];
+          const int64_t sr = raw / p.a_div;
+          if (sr < 0 || sr >= p.a_rows) report(status, AMOE_ERR_INDEX_RANGE, 20, w.it.row0 + r, static_cast<int>(sr));
+          else src[j] = static_cast<int>(sr);
+        }
+      }
+    };
+    auto issue = [&](const StageWalk& w, int slot) {
+      const uint32_t sbase = stg + static_cast<uint32_t>(slot) * p.stg_slot;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < tpt) {
+          const int r = rg + j * rstep;
+          const int k = w.kc * kBK + c * 8;
+          const bool ok = pre_src[j] >= 0 && k < p.Kc;
+          const uint8_t* g = ok ? abase + (static_cast<int64_t>(pre_src[j]) * p.a_stride + k) * kEsz : abase;
+          const uint32_t d = sbase + static_cast<uint32_t>(r * 8 + c) * 16u;
+          cp_async16(d, g, ok ? 16u : 0u);
+          if (A_F32) cp_async16(d + kPlane, g + (ok ? 16 : 0), ok ? 16u : 0u);
+        }
+      }
+    };
+    // prime the pipeline
+    int pre_slot = 0;
+    for (int x = 0; x < kStagePF; ++x) {
+      if (pre.valid) {
+        if (pre.new_tile) rows_of(pre, pre_src);
+        issue(pre, pre_slot);
+        pre.next();
+      }
+      cp_async_commit();
+      pre_slot = pre_slot + 1 == kStageSlots ? 0 : pre_slot + 1;
+    }
+    RingPos rp(p.stages);
+    int cur_slot = 0;
+    bool alive = true;
+    while (alive && cur.valid) {
+      if (pre.valid) {
+        if (pre.new_tile) rows_of(pre, pre_src);
+        issue(pre, pre_slot);
+        pre.next();
+      }
+      cp_async_commit();
+      pre_slot = pre_slot + 1 == kStageSlots ? 0 : pre_slot + 1;
+      if (cur.new_tile) {
+        rows_of(cur, cur_src);      // (index errors were reported when the tile was prefetched; harmless to repeat)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j < tpt && cur_src[j] >= 0) {
+            const int64_t i = static_cast<int64_t>(cur.it.row0) + rg + j * rstep;
+            if (has_ir) cur_ir[j] = p.ir[p.epi.ir_by_expert ? cur.it.e : i];
+            if (has_am) cur_am[j] = p.a_absmax[cur_src[j]];
+            if (p.cache_scale) cur_cs[j] = p.cache_scale[p.a_row[i]];
+          }
+        }
+      }
+      cp_async_wait<kStagePF>();       // this thread's copies of the current stage have landed
+      const int s = rp.s;
+      bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 6);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      const uint32_t a_hi = sm.base_u32 + s * p.stage_bytes;
+      const uint32_t a_lo = a_hi + kATile;
+      const uint32_t sbase = stg + static_cast<uint32_t>(cur_slot) * p.stg_slot;
+      const bool do_cache = p.cache_hi != nullptr && cur.nt == 0;
+      const int kk = cur.kc * kBK + c * 8;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < tpt) {
+          const int r = rg + j * rstep;
+          const uint32_t sa = sbase + static_cast<uint32_t>(r * 8 + c) * 16u;
+          float v[8];
+          if (A_F32) {
+            const uint4 x = lds128(sa), y = lds128(sa + kPlane);
+            v[0] = __uint_as_float(x.x); v[1] = __uint_as_float(x.y); v[2] = __uint_as_float(x.z); v[3] = __uint_as_float(x.w);
+            v[4] = __uint_as_float(y.x); v[5] = __uint_as_float(y.y); v[6] = __uint_as_float(y.z); v[7] = __uint_as_float(y.w);
+          } else {
+            const uint4 x = lds128(sa);
+            v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+            v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+            v[4] = __uint_as_float(x.z << 16); v[5] = __uint_as_float(x.z & 0xffff0000u);
+            v[6] = __uint_as_float(x.w << 16); v[7] = __uint_as_float(x.w & 0xffff0000u);
+          }
+          const bool live = cur_src[j] >= 0;
+          const bool cache_now = do_cache && kk < p.Kc;
+          // cache layout: [64-column block][padded row][64]
+          const int64_t co = cache_now ? ((cur.kc * p.cache_stride + cur.it.t * kBM + r) << 6) + c * 8 : 0;
+          const uint32_t soff = sw128_offset(r, c);
+          if (DAC == kDacNone) {
+            if (F16) {
+#pragma unroll
+              for (int x = 0; x < 8; ++x) v[x] *= g_mul;
+            }
+            // the tile and the cache hold the same terms: convert once, store twice
+            uint32_t h[4], l[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int x = 0; x < 4; ++x) h[x] = cvt_op2<F16>(v[2 * x], v[2 * x + 1]);
+            if (!F16 && (p.a_split || (cache_now && p.cache_lo))) {
+#pragma unroll
+              for (int x = 0; x < 4; ++x)
+                l[x] = cvt_bf16x2(v[2 * x] - __uint_as_float(h[x] << 16), v[2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u));
+            }
+            sts128(a_hi + soff, h[0], h[1], h[2], h[3]);
+            if (!F16 && p.a_split) sts128(a_lo + soff, l[0], l[1], l[2], l[3]);
+            if (cache_now) {
+              *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
+              if (!F16 && p.cache_lo) *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
+            }
+          } else {
+            if (has_ir && live) {
+#pragma unroll
+              for (int x = 0; x < 8; ++x) v[x] = clamp_ir(v[x], cur_ir[j]);
+            }
+            if (cache_now) {
+              // the operand as dW wants it: clamped (not quantised), times the per-row scale
+              uint32_t h[4];
+#pragma unroll
+              for (int x = 0; x < 4; ++x)
+                h[x] = p.cache_scale ? cvt_op2<F16>(v[2 * x] * cur_cs[j], v[2 * x + 1] * cur_cs[j]) : cvt_op2<F16>(v[2 * x], v[2 * x + 1]);
+              *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
+              if (!F16 && p.cache_lo) {
+                uint32_t l[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                  const float a0 = p.cache_scale ? v[2 * x] * cur_cs[j] : v[2 * x];
+                  const float a1 = p.cache_scale ? v[2 * x + 1] * cur_cs[j] : v[2 * x + 1];
+                  l[x] = cvt_bf16x2(a0 - __uint_as_float(h[x] << 16), a1 - __uint_as_float(h[x] & 0xffff0000u));
+                }
+                *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
+              }
+            }
+            if (live) {
+              const float rcp_ir = has_ir ? __frcp_rn(cur_ir[j]) : 1.f;
+              const float rcp_am = has_am ? __frcp_rn(cur_am[j]) : 1.f;
+              if (DAC == kDacQuant && p.inp_res >= 4.0e-7f) {
+                dac_codes8(v, has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am, p.inp_res, rcp_res);
+              } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                  if (DAC == kDacQuant)
+                    v[x] = dac_code_clamped(v[x], has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am, p.inp_res, rcp_res);
+                  else
+                    v[x] = dac_normalise_clamped(v[x], has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am);
+                }
+              }
+            }
+            store8_rt<F16>(a_hi, a_lo, soff, v, p.a_split != 0);
+          }
+        }
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
+      cur_slot = cur_slot + 1 == kStageSlots ? 0 : cur_slot + 1;
+      rp.next();
+      cur.next();
+    }
+    cp_async_wait<0>();      // nothing of this thread may still be in flight when the CTA winds down
+  } else if (!p.a_tma && warp < 2 + p.n_epi + n_prod) {
+    // ---------------------------------------------------------------- operand prologue, direct loads (A tiles)
+    // (rows that are not 16-byte aligned, odd row lengths)
     const int np_all = n_prod * 32;
     const int pt_all = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np_all-1
     const int pw = warp - (2 + p.n_epi);
@@ -763,21 +1048,25 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                 const int64_t co = cache_now ? ((kc * p.cache_stride + t * kBM + (task >> 3)) << 6) + (task & 7) * 8 : 0;
                 const uint32_t soff = sw128_offset(task >> 3, task & 7);
                 if (DAC == kDacNone) {
+                  if (F16) {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) v[b][x] *= g_mul;
+                  }
                   // the tile and the cache hold the same terms: convert once, store twice
                   uint32_t h[4], l[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                  for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(v[b][2 * x], v[b][2 * x + 1]);
-                  if (a_split || (cache_now && p.cache_lo)) {
+                  for (int x = 0; x < 4; ++x) h[x] = cvt_op2<F16>(v[b][2 * x], v[b][2 * x + 1]);
+                  if (!F16 && (a_split || (cache_now && p.cache_lo))) {
 #pragma unroll
                     for (int x = 0; x < 4; ++x)
                       l[x] = cvt_bf16x2(v[b][2 * x] - __uint_as_float(h[x] << 16),
                                         v[b][2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u));
                   }
                   sts128(a_hi + soff, h[0], h[1], h[2], h[3]);
-                  if (a_split) sts128(a_lo + soff, l[0], l[1], l[2], l[3]);
+                  if (!F16 && a_split) sts128(a_lo + soff, l[0], l[1], l[2], l[3]);
                   if (cache_now) {
                     *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
-                    if (p.cache_lo) *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
+                    if (!F16 && p.cache_lo) *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
                   }
                 } else {
                   if (has_ir && m[b].src >= 0) {
@@ -785,16 +1074,16 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                     for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], m[b].ir);
                   }
                   if (cache_now) {
-                    // the operand as dW wants it: clamped (not quantised), times the per-row scale, hi (+ lo) bf16
+                    // the operand as dW wants it: clamped (not quantised), times the per-row scale, hi (+ lo) terms
                     float c8[8];
                     const float sc = p.cache_scale ? s_cscale[task >> 3] : 1.f;
 #pragma unroll
                     for (int x = 0; x < 8; ++x) c8[x] = p.cache_scale ? v[b][x] * sc : v[b][x];
                     uint32_t h[4];
 #pragma unroll
-                    for (int x = 0; x < 4; ++x) h[x] = cvt_bf16x2(c8[2 * x], c8[2 * x + 1]);
+                    for (int x = 0; x < 4; ++x) h[x] = cvt_op2<F16>(c8[2 * x], c8[2 * x + 1]);
                     *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
-                    if (p.cache_lo) {
+                    if (!F16 && p.cache_lo) {
                       uint32_t l[4];
 #pragma unroll
                       for (int x = 0; x < 4; ++x)
@@ -812,7 +1101,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                         v[b][x] = dac_normalise_clamped(v[b][x], has_ir, m[b].ir, m[b].rcp_ir, has_am, m[b].am, rcp_am);
                     }
                   }
-                  store8_rt(a_hi, a_lo, soff, v[b], a_split);
+                  store8_rt<F16>(a_hi, a_lo, soff, v[b], a_split);
                 }
               }
             }
@@ -845,6 +1134,8 @@ struct DwMnParams {
   float* dw;            // [E,K,N]
   float* partials;      // [segments,K,N] when the slot range of an expert is split, else NULL
   int32_t* status;
+  int f16;              // fp16 operands (one term)
+  const float* g_absmax;  // fp16: device scalar max|g|; g is scaled by the power of two derived from it, dW scaled back
 };
 
 constexpr int kDwProdWarps = 26;
@@ -893,10 +1184,13 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
   const uint32_t a_tile = (SPLIT ? 2u : 1u) * p.a_bytes;   // one A tile, all precision terms
   const uint32_t b_tile = (SPLIT ? 2u : 1u) * p.b_bytes;
   const uint32_t b_region = static_cast<uint32_t>(p.MB) * a_tile;
+  float g_mul = 1.f, g_inv = 1.f;       // gradient scale of fp16 operands; a direct store takes it out again,
+  if (p.f16 && p.g_absmax != nullptr) g_mul = grad_pow2_scale(__ldg(p.g_absmax), g_inv);
+  const float out_mul = p.partials ? 1.f : g_inv;   // partial tiles keep it until dw_reduce_kernel
 
   if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
+      const uint32_t idesc = p.f16 ? (make_idesc_f16(kBM, p.BN) | (1u << 15) | (1u << 16)) : make_idesc_bf16_mn(kBM, p.BN);
       RingPos rp(p.stages);
       SegIter si(p.offsets, p.E, p.seg);
       uint32_t acc_it = 0;
@@ -980,6 +1274,8 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
           float v[16];
           tmem_ld16(taddr + c0, v);
           tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 16; ++x) v[x] *= out_mul;
           const int n = n0 + c0;
           if (m < p.K && n < p.N) {
             if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
@@ -1096,14 +1392,17 @@ __global__ void __launch_bounds__(kDwThreads, 1) dw_tc_mn_kernel(DwMnParams p) {
 #pragma unroll
                     for (int x = 0; x < 8; ++x) v[b][x] = clamp_ir(v[b][x], aux[b]);
                   }
-                } else if (p.g_scale) {
+                } else if (p.g_scale || p.f16) {
+                  const float m = (p.g_scale ? aux[b] : 1.f) * g_mul;
 #pragma unroll
-                  for (int x = 0; x < 8; ++x) v[b][x] *= aux[b];
+                  for (int x = 0; x < 8; ++x) v[b][x] *= m;
                 }
               }
               const uint32_t hi = stage + (isb[b] ? b_region + tile[b] * b_tile : tile[b] * a_tile);
               const uint32_t lo = hi + (isb[b] ? p.b_bytes : p.a_bytes);
-              store8<SPLIT>(hi, lo, static_cast<uint32_t>((c[b] >> 3) * static_cast<int>(kMnBlock)) + sw128_offset(r[b], c[b] & 7), v[b]);
+              const uint32_t so = static_cast<uint32_t>((c[b] >> 3) * static_cast<int>(kMnBlock)) + sw128_offset(r[b], c[b] & 7);
+              if (p.f16) store8_rt<true>(hi, lo, so, v[b], false);
+              else store8<SPLIT>(hi, lo, so, v[b]);
             }
           }
         }
@@ -1135,6 +1434,8 @@ struct DwTmaParams {
   float* dw;
   float* partials;
   int32_t* status;
+  int f16;              // the caches hold fp16
+  const float* g_absmax;  // device scalar max|g| behind the scale the g cache carries (dW is scaled back), or NULL
 };
 
 // Segment `idx` in padded row space: expert e owns ceil(count_e/128)*128 padded rows.
@@ -1178,6 +1479,9 @@ dw_tc_tma_kernel(const __grid_constant__ CUtensorMap ta_hi, const __grid_constan
   const uint32_t b_tile = (SPLIT ? 2u : 1u) * p.b_bytes;
   const uint32_t b_region = static_cast<uint32_t>(p.MB) * a_tile;
   const int b_blocks = static_cast<int>(p.b_bytes / kMnBlock);
+  float g_inv = 1.f;                    // the g cache carries the gradient scale of fp16 operands
+  if (p.f16 && p.g_absmax != nullptr) grad_pow2_scale(__ldg(p.g_absmax), g_inv);
+  const float out_mul = p.partials ? 1.f : g_inv;   // partial tiles keep it until dw_reduce_kernel
 
   if (warp == 0) {
     if (lane == 0) {
@@ -1223,7 +1527,7 @@ dw_tc_tma_kernel(const __grid_constant__ CUtensorMap ta_hi, const __grid_constan
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16_mn(kBM, p.BN);
+      const uint32_t idesc = p.f16 ? (make_idesc_f16(kBM, p.BN) | (1u << 15) | (1u << 16)) : make_idesc_bf16_mn(kBM, p.BN);
       RingPos rp(p.stages);
       PadSegIter si(p.offsets, p.E, p.seg);
       uint32_t acc_it = 0;
@@ -1307,6 +1611,8 @@ dw_tc_tma_kernel(const __grid_constant__ CUtensorMap ta_hi, const __grid_constan
           float v[16];
           tmem_ld16(taddr + c0, v);
           tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 16; ++x) v[x] *= out_mul;
           const int n = n0 + c0;
           if (m < p.K && n < p.N) {
             if (n + 16 <= p.N && ((reinterpret_cast<uintptr_t>(dst + n) & 15u) == 0)) {
@@ -1333,7 +1639,7 @@ dw_tc_tma_kernel(const __grid_constant__ CUtensorMap ta_hi, const __grid_constan
 // dW[e] = sum over the expert's segments, in segment order (fixed order: bit-reproducible).  `pad`: the
 // segments were cut in padded row space (every expert's count rounded up to a multiple of `pad`).
 __global__ void dw_reduce_kernel(const float* __restrict__ partials, const int32_t* __restrict__ offsets, int E, int seg,
-                                 int64_t kn, float* __restrict__ dw, int pad) {
+                                 int64_t kn, float* __restrict__ dw, int pad, const float* __restrict__ g_absmax) {
   __shared__ int s_first, s_count;
   const int e = blockIdx.y;
   if (threadIdx.x == 0) {
@@ -1349,6 +1655,11 @@ __global__ void dw_reduce_kernel(const float* __restrict__ partials, const int32
   for (int sgm = 0; sgm < s_count; ++sgm) {
     const float4 v = *reinterpret_cast<const float4*>(partials + (static_cast<int64_t>(s_first) + sgm) * kn + i);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  if (g_absmax != nullptr) {      // fp16 operands: the partial tiles still carry the gradient scale
+    float inv;
+    grad_pow2_scale(__ldg(g_absmax), inv);
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
   }
   *reinterpret_cast<float4*>(dw + static_cast<int64_t>(e) * kn + i) = acc;
 }
@@ -1414,6 +1725,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   int s = amoe_check_device();
   if (s != AMOE_OK) return s;
   TcParams p{};
+  const bool f16 = a->precision == AMOE_PREC_F16X1;
   p.E = a->E;
   p.Kc = is_dx ? a->N : a->K;
   p.Nout = is_dx ? a->K : a->N;
@@ -1431,10 +1743,11 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   const int esz = a->a_dtype == AMOE_F32 ? 4 : 2;
   p.vec_ok = aligned16(a->a) && ((a->a_stride * esz) % 16 == 0);
   p.epi = epi_in;
+  p.g_absmax = (f16 && is_dx) ? a->a_absmax_dev : nullptr;
   const bool dac = !is_dx;
   const bool quant = dac && p.inp_res > 0.f;
-  // Integer DAC codes up to 256 in magnitude are exact in bf16; anything else needs the hi+lo pair
-  // when split precision is asked for.  bf16 inputs that are not quantised are exact as they are.
+  // Integer DAC codes up to 256 in magnitude are exact in bf16 (up to 2048 in fp16); anything else needs the hi+lo
+  // pair when split precision is asked for.  bf16 inputs that are not quantised are exact as they are.
   bool a_split = a->precision == AMOE_PREC_SPLIT;
   if (quant && p.inp_res >= 1.0f / 256.0f) a_split = false;
   if (!quant && a->a_dtype == AMOE_BF16 && !(dac && (p.ir || p.a_absmax))) a_split = false;
@@ -1442,31 +1755,41 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   p.a_split = a_split; p.b_split = b_split;
   p.epi.acc_mul = quant ? p.inp_res : 1.f;
   p.cache_hi = reinterpret_cast<__nv_bfloat16*>(a->a_cache_hi);
-  p.cache_lo = reinterpret_cast<__nv_bfloat16*>(a->a_cache_lo);
+  p.cache_lo = f16 ? nullptr : reinterpret_cast<__nv_bfloat16*>(a->a_cache_lo);
   p.cache_stride = a->cache_rows; p.cache_scale = a->a_cache_scale;
   p.a_tma = a->a_tile_hi != nullptr;
   if (p.a_tma) {
     AMOE_REQUIRE(p.Kc % kBK == 0 && aligned16(a->a_tile_hi) && aligned16(a->a_tile_lo) && !p.cache_hi, AMOE_ERR_BAD_SHAPE);
     AMOE_REQUIRE(a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
-    a_split = a->a_tile_lo != nullptr;
+    a_split = !f16 && a->a_tile_lo != nullptr;
     p.a_split = a_split;
   }
   AMOE_REQUIRE(!(p.cache_hi || p.epi.out_cache_hi || p.epi.next_codes) || a->cache_rows >= (a->P / kBM + a->E) * kBM, AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!p.cache_hi || (p.Kc % 8 == 0 && aligned16(p.cache_hi) && aligned16(p.cache_lo)), AMOE_ERR_BAD_SHAPE);
+  if (f16) p.epi.out_cache_lo = nullptr;
 
+  // The staged prologue needs 16-byte aligned rows whose length is a multiple of 8 elements.
+  p.staged = !p.a_tma && p.vec_ok && p.Kc % 8 == 0;
+  p.item_mode = p.a_tma && !is_dx && p.n_tiles > 1;
   p.a_bytes = a_split ? 2 * kATile : kATile;
   p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
   p.stage_bytes = p.a_bytes + p.b_bytes * (b_split ? 2u : 1u);
   p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
-  p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
+  p.stg_slot = p.staged ? static_cast<uint32_t>(kBM * kBK * esz) : 0u;
+  if (p.staged && (kSmemBudget - p.stg_slot * kStageSlots) / p.stage_bytes < 2) {
+    p.staged = 0;               // wide split-precision stages leave no room for the staging slots
+    p.stg_slot = 0;
+  }
+  const uint32_t stg_bytes = p.stg_slot * kStageSlots;
+  p.stages = static_cast<int>((kSmemBudget - stg_bytes) / p.stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
   p.prod_groups = 1;
   {
-    // Split the 16 worker warps between epilogue and prologue by estimated instruction counts.
-    const double per_prod = (quant ? 13.0 : (dac && (p.ir || p.a_absmax) ? 18.0 : 3.0)) + (a_split ? 5.0 : 2.0) +
-                            (p.cache_hi ? (dac ? 6.0 : 2.0) : 0.0);
+    // Split the worker warps between epilogue and prologue by estimated instruction counts.
+    const double per_prod = (quant ? 8.0 : (dac && (p.ir || p.a_absmax) ? 10.0 : 2.0)) + (a_split ? 5.0 : 2.0) +
+                            (p.cache_hi ? (f16 ? 2.0 : 5.0) : 0.0);
     double per_epi = 8.0;
     if (!is_dx) per_epi += (a->noise_std > 0.f ? 26.0 : 0.0) + (a->noise ? 2.0 : 0.0) + (p.epi.adc.on ? 9.0 : 0.0) +
                            (a->out_codes ? 3.0 : 0.0) + (p.epi.next_codes ? 14.0 : 0.0) + (p.epi.out_cache_hi ? 10.0 : 0.0);
@@ -1474,9 +1797,18 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
     double best = 1e300;
-    for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
-      const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
-      if (t < best) { best = t; p.n_epi = ne; }
+    if (p.staged) {
+      // the staged prologue runs on 8 or 16 warps (a thread owns whole 16-byte chunks of 4 or 2 rows)
+      const int cand[2][2] = {{16, 4}, {8, 12}};
+      for (const auto& c : cand) {
+        const double t = fmax(work_p / c[0], work_e / c[1]);
+        if (t < best) { best = t; p.n_prod = c[0]; p.n_epi = c[1]; }
+      }
+    } else {
+      for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
+        const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
+        if (t < best) { best = t; p.n_epi = ne; p.n_prod = kWorkerWarps - ne; }
+      }
     }
     if (p.a_tma) {
       // no prologue: the epilogue groups that share the tile's chunks most evenly (fewest warps on a tie)
@@ -1486,11 +1818,12 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
         const int per = (chunks + ne / 4 - 1) / (ne / 4);
         if (per < best_per) { best_per = per; p.n_epi = ne; }
       }
+      p.n_prod = 0;
     }
   }
-  // two prologue groups on alternate stages (both groups have the same number of warps, so every stage's barrier
-  // expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
-  if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && kWorkerWarps - p.n_epi >= 8)
+  // direct-load prologue: two groups on alternate stages (both groups have the same number of warps, so every stage's
+  // barrier expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
+  if (!p.a_tma && !p.staged && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && p.n_prod >= 8 && p.n_prod % 2 == 0)
     p.prod_groups = 2;
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
@@ -1499,6 +1832,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     p.cs_off = static_cast<uint32_t>(p.stages) * p.stage_bytes + 8u * kNumBars + 64u;
   }
   const uint32_t cs_bytes = static_cast<uint32_t>(p.n_epi) * 2u * p.cs_per_warp * sizeof(float);
+  p.stg_off = (p.cs_off + cs_bytes + 127u) & ~127u;
 
   CUtensorMap m_hi, m_lo;
   s = encode_tmap_bf16_3d(&m_hi, a->w_hi, static_cast<uint64_t>(k_pad), static_cast<uint64_t>(n_pad),
@@ -1520,8 +1854,8 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       if (s != AMOE_OK) return s;
     }
   }
-  const uint32_t smem = p.stages * p.stage_bytes + kSmemExtra + cs_bytes;
-  const int64_t max_tiles = (a->P + kBM - 1) / kBM + a->E;
+  const uint32_t smem = p.stg_off + stg_bytes + kSmemExtra;
+  const int64_t max_tiles = ((a->P + kBM - 1) / kBM + a->E) * (p.item_mode ? p.n_tiles : 1);
   const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
   const bool f32 = a->a_dtype == AMOE_F32;
   // epilogue family: the fast routines need 16-byte alignment everywhere and no materialised noise
@@ -1529,14 +1863,18 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (p.epi.vec4 && !is_dx && a->noise == nullptr) epi = kEpiFwd;
   if (p.epi.vec4 && is_dx && (a->x_ref == nullptr || a->x_ref_dtype == AMOE_F32 || a->x_ref_stride % 8 == 0)) epi = kEpiDx;
   AMOE_REQUIRE(!(p.epi.out_cache_hi || p.epi.next_codes) || epi == (is_dx ? kEpiDx : kEpiFwd), AMOE_ERR_UNSUPPORTED);
+  AMOE_REQUIRE(a->out != nullptr || epi != kEpiGeneric, AMOE_ERR_UNSUPPORTED);
   const int dacm = is_dx ? kDacNone : (quant ? kDacQuant : kDacNorm);
-#define AMOE_LAUNCH_TC(DAC, F32, EPI)                                                                                  \
-  do {                                                                                                                 \
-    AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<DAC, F32, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    cvmm_tc_kernel<DAC, F32, EPI><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, ma_hi, ma_lo, p);                                 \
+#define AMOE_LAUNCH_TC(DAC, F32, EPI, F16)                                                                                  \
+  do {                                                                                                                      \
+    AMOE_CUDA(cudaFuncSetAttribute(cvmm_tc_kernel<DAC, F32, EPI, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    cvmm_tc_kernel<DAC, F32, EPI, F16><<<grid, kFwdThreads, smem, stream>>>(m_hi, m_lo, ma_hi, ma_lo, p);                   \
   } while (0)
-#define AMOE_LAUNCH_TC_DT(DAC, EPI) \
-  do { if (f32) AMOE_LAUNCH_TC(DAC, true, EPI); else AMOE_LAUNCH_TC(DAC, false, EPI); } while (0)
+#define AMOE_LAUNCH_TC_DT(DAC, EPI)                                                                 \
+  do {                                                                                              \
+    if (f16) { if (f32) AMOE_LAUNCH_TC(DAC, true, EPI, true); else AMOE_LAUNCH_TC(DAC, false, EPI, true); }   \
+    else { if (f32) AMOE_LAUNCH_TC(DAC, true, EPI, false); else AMOE_LAUNCH_TC(DAC, false, EPI, false); }     \
+  } while (0)
   if (is_dx) {
     if (epi == kEpiDx) AMOE_LAUNCH_TC_DT(kDacNone, kEpiDx); else AMOE_LAUNCH_TC_DT(kDacNone, kEpiGeneric);
   } else if (dacm == kDacQuant) {
@@ -1566,14 +1904,15 @@ static int launch_dw_tma(const amoe_dw_args* a, cudaStream_t stream) {
   p.m_tiles = (a->K + kBM - 1) / kBM;
   p.offsets = a->expert_offsets;
   p.dw = a->dw; p.status = a->dev_status;
+  p.f16 = a->precision == AMOE_PREC_F16X1; p.g_absmax = a->g_absmax_dev;
   const int64_t tune = a->expected_rows > 0 && a->expected_rows < a->P ? a->expected_rows : a->P;
   p.seg = dw_segment_slots(tune, a->K, a->N);
   const size_t need = dw_tc_workspace_bytes(a->P, tune, a->E, a->K, a->N);
   if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
     p.seg = 0;
   p.partials = p.seg > 0 ? reinterpret_cast<float*>(a->workspace) : nullptr;
-  const bool split = a->x_lo != nullptr && a->g_lo != nullptr;
-  AMOE_REQUIRE(split || (a->x_lo == nullptr && a->g_lo == nullptr), AMOE_ERR_NULL_POINTER);
+  const bool split = !p.f16 && a->x_lo != nullptr && a->g_lo != nullptr;
+  AMOE_REQUIRE(split || p.f16 || (a->x_lo == nullptr && a->g_lo == nullptr), AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(aligned16(a->x_hi) && aligned16(a->x_lo) && aligned16(a->g_hi) && aligned16(a->g_lo), AMOE_ERR_BAD_SHAPE);
   p.a_bytes = 2 * kMnBlock;
   p.b_bytes = static_cast<uint32_t>((p.BN + 63) / 64) * kMnBlock;
@@ -1613,7 +1952,7 @@ static int launch_dw_tma(const amoe_dw_args* a, cudaStream_t stream) {
   if (p.seg > 0) {
     const int64_t kn = static_cast<int64_t>(a->K) * a->N;
     dim3 rg(static_cast<unsigned>((kn / 4 + 255) / 256), a->E);
-    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, kBM);
+    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, kBM, p.f16 ? p.g_absmax : nullptr);
     AMOE_LAUNCH_CHECK("dw_reduce");
   }
   return AMOE_OK;
@@ -1636,6 +1975,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   p.x_vec_ok = aligned16(a->x) && ((a->x_stride * (a->x_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.g_vec_ok = aligned16(a->g) && ((a->g_stride * (a->g_dtype == AMOE_F32 ? 4 : 2)) % 16 == 0);
   p.dw = a->dw; p.status = a->dev_status;
+  p.f16 = a->precision == AMOE_PREC_F16X1; p.g_absmax = a->g_absmax_dev;
   if (a->x_hi != nullptr) return launch_dw_tma(a, stream);
   // Large problems: cut every expert's slot range into segments so that the work items outnumber the
   // SMs and a popular expert does not become one long item; the partial tiles go to the workspace and
@@ -1681,7 +2021,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   if (p.seg > 0) {
     const int64_t kn = static_cast<int64_t>(a->K) * a->N;
     dim3 rg(static_cast<unsigned>((kn / 4 + 255) / 256), a->E);
-    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, 1);
+    dw_reduce_kernel<<<rg, 256, 0, stream>>>(p.partials, p.offsets, a->E, p.seg, kn, a->dw, 1, p.f16 ? p.g_absmax : nullptr);
     AMOE_LAUNCH_CHECK("dw_reduce");
   }
   return AMOE_OK;

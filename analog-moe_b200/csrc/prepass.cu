@@ -139,6 +139,7 @@ struct PrepassDev {
   void* w_clip_out;     // clamped weights in the layout and type of w (normally w itself), or NULL
   __nv_bfloat16 *fwd_hi, *fwd_lo, *bwd_hi, *bwd_lo;
   int Npad, Kpad, Kpad2, Npad2;
+  int f16;              // the prepared copies hold IEEE fp16 (saturating at +-65504) instead of bf16; no lo terms
 };
 
 constexpr int kTK = 32, kTN = 128;
@@ -147,6 +148,12 @@ __device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
 }
+__device__ __forceinline__ uint32_t pack2_f16(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack2_op(float a, float b, int f16) { return f16 ? pack2_f16(a, b) : pack2_bf16(a, b); }
 
 // Block (32,8): tile of 32 k-rows x 128 n-columns of expert blockIdx.z.  Loads, the modifier and the
 // natural-orientation copy work on four consecutive columns per thread (16-byte loads, 8-byte bf16
@@ -219,7 +226,7 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
     for (int j = 0; j < 4; ++j) tile[r][tx * 4 + j] = v[j];
     // natural orientation: row k, n contiguous (Npad2 is a multiple of 64, so whole quads fit)
     if (p.bwd_hi && k < p.Kpad2 && n < p.Npad2) {
-      const uint32_t h0 = pack2_bf16(v[0], v[1]), h1 = pack2_bf16(v[2], v[3]);
+      const uint32_t h0 = pack2_op(v[0], v[1], p.f16), h1 = pack2_op(v[2], v[3], p.f16);
       const int64_t o = (static_cast<int64_t>(e) * p.Kpad2 + k) * p.Npad2 + n;
       *reinterpret_cast<uint2*>(p.bwd_hi + o) = make_uint2(h0, h1);
       if (p.bwd_lo) {
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float a = tile[half * 16 + 2 * i][c], b2 = tile[half * 16 + 2 * i + 1][c];
-        h[i] = pack2_bf16(a, b2);
+        h[i] = pack2_op(a, b2, p.f16);
         l[i] = pack2_bf16(a - __uint_as_float(h[i] << 16), b2 - __uint_as_float(h[i] & 0xffff0000u));
       }
       const int64_t o = (static_cast<int64_t>(e) * p.Npad + nn) * p.Kpad + kb;
@@ -256,6 +263,28 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
       }
     }
   }
+}
+
+// max|x| of a whole tensor through an integer atomic max on the bit patterns (non-negative floats order like
+// integers; NaNs are skipped).  `out` must be zero before the launch.
+template <typename T>
+__global__ void tensor_absmax_kernel(const T* __restrict__ x, int64_t rows, int K, int64_t stride,
+                                     const int32_t* __restrict__ n_rows_dev, float* __restrict__ out) {
+  int64_t n = rows;
+  if (n_rows_dev != nullptr) n = min(static_cast<int64_t>(max(*n_rows_dev, 0)), rows);
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  float m = 0.f;
+  for (int64_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += warps) {
+    const T* row = x + r * stride;
+    for (int k = lane; k < K; k += 32) {
+      const float v = fabsf(to_f32<T>(row[k]));
+      if (v == v) m = fmaxf(m, v);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
 }
 
 template <typename T>
@@ -346,6 +375,8 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
     p.w_out = a->w_out;
     p.fwd_hi = reinterpret_cast<__nv_bfloat16*>(a->fwd_hi); p.fwd_lo = reinterpret_cast<__nv_bfloat16*>(a->fwd_lo);
     p.bwd_hi = reinterpret_cast<__nv_bfloat16*>(a->bwd_hi); p.bwd_lo = reinterpret_cast<__nv_bfloat16*>(a->bwd_lo);
+    p.f16 = a->prepared_f16;
+    AMOE_REQUIRE(!p.f16 || (!a->fwd_lo && !a->bwd_lo), AMOE_ERR_UNSUPPORTED);
     p.Npad = round_up(a->N, 16); p.Kpad = round_up(a->K, 64);
     p.Kpad2 = round_up(a->K, 16); p.Npad2 = round_up(a->N, 64);
     const int kext = p.Kpad, next = p.Npad2;  // Kpad >= Kpad2, Npad2 >= Npad
@@ -354,6 +385,24 @@ int amoe_weight_prepass(const amoe_weight_prepass_args* a, amoe_stream_t stream_
     transform_kernel<<<grid, dim3(32, 8), 0, stream>>>(p);
     AMOE_LAUNCH_CHECK("transform");
   }
+  return AMOE_OK;
+}
+
+int amoe_tensor_absmax(const void* x, int32_t dtype, int64_t rows, int32_t K, int64_t stride, const int32_t* n_rows_dev,
+                       float* absmax, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && absmax, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(rows > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
+  AMOE_CUDA(cudaMemsetAsync(absmax, 0, sizeof(float), stream));
+  const unsigned blocks = static_cast<unsigned>(sm_count()) * 8u;
+  if (dtype == AMOE_F32)
+    tensor_absmax_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), rows, K, stride, n_rows_dev, absmax);
+  else if (dtype == AMOE_BF16)
+    tensor_absmax_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, K, stride,
+                                                                    n_rows_dev, absmax);
+  else
+    return AMOE_ERR_BAD_DTYPE;
+  AMOE_LAUNCH_CHECK("tensor_absmax");
   return AMOE_OK;
 }
 

@@ -67,6 +67,57 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// ------------------------------------------------------------------ cp.async (16-byte asynchronous copies, per thread)
+// Global -> shared without a register in between; `bytes` = 16 copies, 0 zero-fills the 16 bytes without reading.
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc, uint32_t bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// ------------------------------------------------------------------ packed fp32 pairs (sm_100: two lanes per instruction)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// a / b for both lanes, IEEE-exact, from y = RN(1/b): the packed form of div_by_rcp (nb = -b).
+__device__ __forceinline__ f32x2 div_by_rcp2(f32x2 a, f32x2 nb, f32x2 y) {
+  const f32x2 q0 = mul2(a, y);
+  const f32x2 r = fma2(nb, q0, a);
+  return fma2(r, y, q0);
+}
+
+// Two fp32 values -> packed fp16 (low half = first value), round to nearest even, saturating at +-65504.
+__device__ __forceinline__ uint32_t cvt_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 // ------------------------------------------------------------------ TMA (tiled, no multicast)
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar, int c0, int c1,
                                             int c2) {
@@ -130,6 +181,10 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
          | (0u << 15) | (0u << 16)                  // A, B K-major
          | (static_cast<uint32_t>(N >> 3) << 17)    // N / 8
          | (static_cast<uint32_t>(M >> 4) << 24);   // M / 16
+}
+// The same with IEEE fp16 operands (format code 0 for A and B).
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N) {
+  return make_idesc_bf16(M, N) & ~((7u << 7) | (7u << 10));
 }
 
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes

@@ -44,7 +44,12 @@ typedef enum amoe_dtype { AMOE_F32 = 0, AMOE_BF16 = 1 } amoe_dtype;
 typedef enum amoe_precision {
   AMOE_PREC_BF16X1 = 0, /* one tcgen05 bf16 pass; exact when both operands are bf16-representable */
   AMOE_PREC_SPLIT = 1,  /* fp32 operands split into bf16 hi+lo terms, 2-3 tcgen05 passes, fp32 accumulate */
-  AMOE_PREC_FP32_SIMT = 2 /* CUDA-core fp32 FMA (the arithmetic the reference's fp32 kernel uses) */
+  AMOE_PREC_FP32_SIMT = 2, /* CUDA-core fp32 FMA (the arithmetic the reference's fp32 kernel uses) */
+  AMOE_PREC_F16X1 = 3   /* fp32 data as IEEE fp16 operands (11-bit significands: ~2e-4 of the result's scale), one
+                           tcgen05 pass, fp32 accumulate.  Integer DAC codes are exact.  Gradient operands are scaled
+                           by a power of two taken from the tensor's largest magnitude (amoe_tensor_absmax) so that
+                           they sit in fp16's normal range whatever their size; conversions saturate at +-65504.
+                           The prepared weight copies and operand caches hold fp16 instead of bf16. */
 } amoe_precision;
 
 int amoe_version(void);
@@ -165,12 +170,18 @@ typedef struct amoe_weight_prepass_args {
   /* Added to the expert index in the weight-noise counter (row (expert_base + e)*K + k): a rank that holds experts
    * [base, base + E) of a larger layer draws the noise the whole layer would draw for them. */
   int32_t expert_base;
+  int32_t prepared_f16;  /* non-zero: fwd_hi / bwd_hi receive IEEE fp16 (for AMOE_PREC_F16X1; lo pointers must be NULL) */
 } amoe_weight_prepass_args;
 size_t amoe_weight_prepass_workspace_bytes(int32_t E, int32_t K, int32_t N);
 size_t amoe_weight_prepass_clip_workspace_bytes(int32_t E, int32_t K, int32_t N);
 /* Padded extents of the prepared copies: dims[0..1] = {Npad, Kpad} (fwd), dims[2..3] = {Kpad2, Npad2} (bwd). */
 void amoe_prepared_dims(int32_t K, int32_t N, int32_t dims[4]);
 int amoe_weight_prepass(const amoe_weight_prepass_args* args, amoe_stream_t stream);
+
+/* max|x| over the first n_rows rows of x [rows,K] into one device float (n_rows_dev: optional device int32 that holds
+ * the row count, capped at rows; NULL = all rows).  NaNs are ignored.  The scalar that scales fp16 gradient operands. */
+int amoe_tensor_absmax(const void* x, int32_t dtype, int64_t rows, int32_t K, int64_t stride, const int32_t* n_rows_dev,
+                       float* absmax, amoe_stream_t stream);
 
 /* |x| maximum of every row, x [R,K] -> absmax [R].  Replaces x.abs().amax(-1) (cvmm.py:733,737). */
 int amoe_row_absmax(const void* x, int32_t dtype, int64_t R, int32_t K, int64_t stride, float* absmax,
@@ -269,6 +280,13 @@ typedef struct amoe_cvmm_args {
   /* plumbing */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_workspace_bytes */
   int32_t* dev_status;            /* int32[4] or NULL */
+  /* AMOE_PREC_F16X1, amoe_cvmm_dx: device scalar max|A| (amoe_tensor_absmax of the upstream gradient, or of the tensor
+   * the A tiles were derived from).  With s = 2^k chosen so that max|A|*s lies in [2^7, 2^8): rows gathered from `a`
+   * are multiplied by s before the conversion, A tiles (a_tile_hi) are taken to carry the factor s already, the
+   * result is multiplied by 1/s, and out_cache_* keeps the result times s (so that it can serve as the next call's
+   * A tiles and as a weight-gradient operand with the same scalar).  NULL: no scaling.
+   * amoe_cvmm_dx accepts out == NULL when out_cache_hi is given (only the operand cache is wanted). */
+  const float* a_absmax_dev;
 } amoe_cvmm_args;
 size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E);
 /* Rows to allocate for an operand cache: (P/128 + E) * 128, an upper bound on the padded tile rows. */
@@ -308,6 +326,9 @@ typedef struct amoe_dw_args {
                                      amoe_cvmm_dw_workspace_bytes_tuned with the same two values */
   void* workspace; size_t workspace_bytes;  /* amoe_cvmm_dw_workspace_bytes, or NULL */
   int32_t* dev_status;
+  /* AMOE_PREC_F16X1: device scalar max|g| (see amoe_cvmm_args.a_absmax_dev).  Gathered g rows are multiplied by the
+   * power of two s derived from it, a g cache is taken to carry s already, and dW is multiplied by 1/s. */
+  const float* g_absmax_dev;
 } amoe_dw_args;
 size_t amoe_cvmm_dw_workspace_bytes(int64_t P, int32_t E, int32_t K, int32_t N, int32_t precision);
 size_t amoe_cvmm_dw_workspace_bytes_tuned(int64_t P, int64_t expected_rows, int32_t E, int32_t K, int32_t N,

@@ -16,6 +16,12 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True)
+def split_precision_by_default(monkeypatch):
+    """The tolerances in this file are those of the bf16 hi+lo split; tests of the fp16 default say so."""
+    monkeypatch.setenv("AMOE_PRECISION", "split")
+
+
 def _route(T, E, k, seed, dev, zipf=0.0):
     from analog_moe import ops
     g = torch.Generator().manual_seed(seed)
@@ -95,7 +101,8 @@ def test_config2_layer_step_is_deterministic_without_noise(dev):
         assert torch.equal(a, b)
 
 
-def test_config2_single_node_step_equals_the_composition(dev):
+@pytest.mark.parametrize("prec", ["split", "f16"])
+def test_config2_single_node_step_equals_the_composition(dev, prec, monkeypatch):
     """Config 2 shapes with every non-ideality on: the single-node layer step (router and top-k in one kernel, two-kernel
     slot sort, hidden rows handed to the down-projection as TMA tiles, weight gradients from the operand caches on a
     second stream) against the composition route() -> CVMM -> ReLU -> CVMM.  Same Philox draws in both."""
@@ -106,6 +113,7 @@ def test_config2_single_node_step_equals_the_composition(dev):
     cfg.pre_post.input_range.decay = 0.01
     cfg.modifier.type = WeightModifierType.ADD_NORMAL_PER_CHANNEL
     cfg.modifier.std_dev = 0.02
+    monkeypatch.setenv("AMOE_PRECISION", prec)
     torch.manual_seed(0)
     layer = AnalogSigmaMoELayer(cfg, d_model=1024, n_experts=16, expert_size=128, k=4, noise_seed=5).to(dev)
     layer.train()
@@ -126,6 +134,8 @@ def test_config2_single_node_step_equals_the_composition(dev):
         assert torch.isfinite(a).all(), key
         # weight gradients: two factorings of the bf16 hi/lo split; the rest: gates from two sigmoid / matmul kernels
         tol = 3e-5 if key in ("dkeys", "dvalues") else 1e-5
+        if prec == "f16" and key in ("dkeys", "dvalues"):
+            tol = 5e-4       # gate * h (cache) against gate * gy (rows), each rounded to fp16's 11 bits
         scale = max(1.0, float(b.abs().max()))
         err = float((a - b).abs().max())
         assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"
