@@ -88,6 +88,7 @@ SIGNATURES = {
     "amoe_launch_count": (C.c_ulonglong, []),
     "amoe_check_device": (C.c_int, []),
     "amoe_read_device_status": (C.c_int, [vp, C.POINTER(C.c_int32 * 4), vp]),
+    "amoe_selftest_bounded_wait": (C.c_int, [vp, C.c_longlong, vp]),
     "amoe_select_sort_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32]),
     "amoe_select_sort": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int32, C.c_int32, vp, vp, vp, vp, vp, vp, vp,
                                    C.c_size_t, vp]),

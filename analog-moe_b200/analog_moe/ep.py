@@ -155,13 +155,23 @@ class StepPlan:
         return int(sum(self.recv_n))
 
 
-def step_plan(counts: Tensor, rank: int, group=None) -> StepPlan:
+def step_plan(counts: Tensor, rank: int, group=None, expect_rows: Optional[int] = None) -> StepPlan:
     """counts [G, El]: this rank's slots per (destination rank, local expert).  One all-gather and the step's only
-    device->host copy."""
+    device->host copy.  With `expect_rows` (the slots this rank really routes) the counts are checked on the host and
+    all ranks raise `ExchangeMismatchError` together if any rank's do not add up - before a row is sent."""
     G, El = counts.shape
     flat = torch.empty(G * G * El, dtype=counts.dtype, device=counts.device)
-    dist.all_gather_into_tensor(flat, counts.contiguous().view(-1), group=group)
+    if counts.is_cuda:
+        dist.all_gather_into_tensor(flat, counts.contiguous().view(-1), group=group)
+    else:       # gloo has no all_gather_into_tensor
+        parts = [torch.empty(G * El, dtype=counts.dtype) for _ in range(G)]
+        dist.all_gather(parts, counts.contiguous().view(-1), group=group)
+        flat = torch.cat(parts)
     gathered = flat.view(G, G, El)
+    if expect_rows is not None:
+        from .health import agree_or_raise, counts_consistent
+        agree_or_raise(counts_consistent(gathered.cpu(), rank, expect_rows), group, "expert-parallel exchange",
+                       counts.device)
     tot = gathered.sum(-1).cpu()                                  # [source, destination] row counts
     tot_l = [[int(v) for v in row] for row in tot]
     send_n = tot_l[rank]
@@ -298,7 +308,7 @@ class _ExpertParallelStep(torch.autograd.Function):
             xchg.generation += 1
             recv = xchg.put("x", x2, r.token_index, r.sel, El, plan)
         else:
-            hplan = step_plan(counts, layer.rank, group)
+            hplan = step_plan(counts, layer.rank, group, expect_rows=P)
             send_splits, recv_splits = hplan.send_n, hplan.recv_n
             R = hplan.n_recv
             local_order, local_offsets = ops.ep_local_plan(hplan.recv_counts, R)

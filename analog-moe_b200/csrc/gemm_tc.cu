@@ -1888,6 +1888,41 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   return AMOE_OK;
 }
 
+// A wait that nothing ends: one warp waits, with the kernels' own bounded wait, on an mbarrier that no one arrives
+// at; the wait gives up after `limit_cycles`, records AMOE_ERR_WAIT_LIMIT in the status word and the kernel returns
+// normally.  This is how the give-up path of the pipelines is exercised without stalling a GPU.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, long long limit_cycles) {
+  using namespace tc;
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x < 32) ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, status, 99, 32, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0 && ok) report(status, AMOE_ERR_UNSUPPORTED, 99, 0, 0);   // the wait must not have succeeded
+}
+
+}  // namespace amoe
+
+extern "C" int amoe_selftest_bounded_wait(int32_t* dev_status, long long limit_cycles, amoe_stream_t stream_) {
+  using namespace amoe;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(dev_status != nullptr, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(limit_cycles > 0 && limit_cycles <= 4000000000LL, AMOE_ERR_BAD_SHAPE);
+  int s = amoe_check_device();
+  if (s != AMOE_OK) return s;
+  bounded_wait_selftest_kernel<<<1, 64, 0, stream>>>(dev_status, limit_cycles);
+  AMOE_LAUNCH_CHECK("bounded_wait_selftest");
+  return AMOE_OK;
+}
+
+namespace amoe {
+
 size_t dw_tc_workspace_bytes(int64_t P, int64_t expected, int E, int K, int N) {
   const int seg = dw_segment_slots(expected > 0 && expected < P ? expected : P, K, N);
   if (seg == 0) return 0;

@@ -49,7 +49,7 @@ constexpr long long kWaitLimitCycles = 4000000000LL;
 // `backoff_ns` > 0 makes the waiter sleep between polls (for long, non-critical waits, so that it does
 // not compete for issue slots with the warps that are doing the work).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int where, unsigned backoff_ns = 0) {
+                                          int where, unsigned backoff_ns = 0, long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -58,7 +58,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         report(status, AMOE_ERR_WAIT_LIMIT, where, static_cast<int>(blockIdx.x), static_cast<int>(parity));
         return false;

@@ -548,7 +548,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
-    ap.add_argument("--precision", default=None, help="split | bf16x1 | fp32 (default: split for fp32, bf16x1 for bf16)")
+    ap.add_argument("--precision", default=None, help="f16 | split | bf16x1 | fp32 (default: f16 for fp32 data, bf16x1 for bf16 data)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the reference-Triton leg (profiling runs)")
@@ -626,7 +626,8 @@ def main():
                     kernels={k_: round(v["ms_avg"] * 1e3, 1) for k_, v in sorted(kern.items())})
         line["config"]["l2"] = "inputs rotate over 8 buffer sets (> 126 MB L2) and one step touches > 400 MB"
         line["config"]["cuda_graph"] = r["graph"]
-        line["config"]["precision"] = {0: "bf16x1", 1: "split (bf16 hi+lo, fp32 accumulate)", 2: "fp32 CUDA cores"}[r["precision"]]
+        line["config"]["precision"] = {0: "bf16x1", 1: "split (bf16 hi+lo, fp32 accumulate)", 2: "fp32 CUDA cores",
+                                       3: "f16x1 (fp16 operands, fp32 accumulate; parity key: distance to the fp32 kernels)"}[r["precision"]]
         if r.get("parity") is not None:
             line["parity"] = r["parity"]
         if r.get("dropin_ms"):

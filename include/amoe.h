@@ -70,6 +70,11 @@ int amoe_check_device(void);
  * ---------------------------------------------------------------------------------------- */
 int amoe_read_device_status(const int32_t* dev_status, int32_t host_copy[4], amoe_stream_t stream);
 
+/* Exercises the give-up path of the kernels' bounded waits without stalling anything: a one-block kernel waits on a
+ * barrier nobody arrives at, with a limit of `limit_cycles` GPU clock cycles (<= 4e9; a few million is a millisecond or
+ * two), records AMOE_ERR_WAIT_LIMIT {where = 99} in dev_status and returns normally.  (No counterpart in the reference.) */
+int amoe_selftest_bounded_wait(int32_t* dev_status, long long limit_cycles, amoe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * Routing.  Replaces the sigmoid/top-k of the sigma-MoE base layer (restated in the reference at
  * tests/test_moe_layer_aihwkit.py:71-76) and cvmm_prepare_sel's flatten+sort (cvmm.py:31-34).
