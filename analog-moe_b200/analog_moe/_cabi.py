@@ -43,6 +43,22 @@ class WeightPrepassArgs(C.Structure):
     ]
 
 
+class OperandTilesArgs(C.Structure):
+    _fields_ = [
+        ("P", C.c_int64), ("E", C.c_int32), ("K", C.c_int32), ("precision", C.c_int32),
+        ("expert_offsets", vp),
+        ("a", vp), ("a_dtype", C.c_int32), ("a_stride", C.c_int64), ("a_rows", C.c_int64),
+        ("a_row", vp), ("a_row_div", C.c_int32),
+        ("dac", C.c_int32),
+        ("ir", vp), ("ir_by_expert", C.c_int32), ("a_absmax", vp), ("inp_res", C.c_float),
+        ("tile_hi", vp), ("tile_lo", vp),
+        ("cache_hi", vp), ("cache_lo", vp), ("cache_scale", vp),
+        ("cache_rows", C.c_int64),
+        ("g_absmax_dev", vp),
+        ("dev_status", vp),
+    ]
+
+
 class CvmmArgs(C.Structure):
     _fields_ = [
         ("P", C.c_int64), ("E", C.c_int32), ("K", C.c_int32), ("N", C.c_int32), ("precision", C.c_int32),
@@ -112,6 +128,7 @@ SIGNATURES = {
     "amoe_row_absmax": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, vp]),
     "amoe_cvmm_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "amoe_padded_rows": (C.c_int64, [C.c_int64, C.c_int32]),
+    "amoe_operand_tiles": (C.c_int, [C.POINTER(OperandTilesArgs), vp]),
     "amoe_cvmm_fwd": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dx": (C.c_int, [C.POINTER(CvmmArgs), vp]),
     "amoe_cvmm_dw_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

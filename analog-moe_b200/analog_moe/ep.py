@@ -248,7 +248,9 @@ class _ExpertParallelStep(torch.autograd.Function):
     no bias, no dropout (the composition in `forward_composed` covers the rest)."""
 
     @staticmethod
-    def forward(ctx, layer, x, w_sel, keys, values, input_range):
+    def forward(ctx, layer, x, w_sel, keys, values, input_range, part=0, shared=None):
+        """`part`: which micro-batch of the layer call this is (selects the exchange buffers); `shared`: prepared weights
+        of both projections computed once for all micro-batches (`ExpertParallelAnalogSigmaMoELayer._prepare_weights`)."""
         cfg = layer.rpu_config
         fwd, ir_p = cfg.forward, cfg.pre_post.input_range
         group, G = layer.group, layer.world
@@ -278,16 +280,20 @@ class _ExpertParallelStep(torch.autograd.Function):
                             step_dev=layer.noise_step)
             return {}
 
-        nz_up, mod_up = noise_args(), layer._weight_modifier()
-        nz_dn, mod_dn = noise_args(), layer._weight_modifier()
         main, side = torch.cuda.current_stream(), ops.side_stream(dev)
-        side.wait_stream(main)
-        with ops.launch_on(side):
-            ops.set_tag("up")
-            pw_up = prepass(keys, mod_up)
-            up_ready = side.record_event()      # the up-projection only waits for its own weights
-            ops.set_tag("down")
-            pw_dn = prepass(values, mod_dn)
+        if shared is None:
+            nz_up, mod_up = noise_args(), layer._weight_modifier()
+            nz_dn, mod_dn = noise_args(), layer._weight_modifier()
+            side.wait_stream(main)
+            with ops.launch_on(side):
+                ops.set_tag("up")
+                pw_up = prepass(keys, mod_up)
+                up_ready = side.record_event()      # the up-projection only waits for its own weights
+                ops.set_tag("down")
+                pw_dn = prepass(values, mod_dn)
+        else:
+            nz_up, nz_dn = noise_args(), noise_args()
+            pw_up, pw_dn, up_ready = shared["pw_up"], shared["pw_dn"], shared["up_ready"]
         ops.set_tag("up")
         r, _ = ops.router_select(x2, w_sel, k, getattr(layer, "router_bias", None))
         gate = r.gate if x.dtype == torch.float32 else r.gate.to(x.dtype).float()
@@ -295,7 +301,7 @@ class _ExpertParallelStep(torch.autograd.Function):
         counts = (r.expert_offsets[1:] - r.expert_offsets[:-1]).view(G, El).contiguous()
         N, Fh = values.shape[-1], keys.shape[-1]
         inv = ops.invert_index(r.slot_index)
-        xchg = layer._peer_exchange(P, D, N, x.dtype)
+        xchg = layer._peer_exchange(P, D, N, x.dtype, part)
         plan = send_splits = recv_splits = None
         # ---- rows to their owners
         if xchg is not None:
@@ -333,7 +339,10 @@ class _ExpertParallelStep(torch.autograd.Function):
             h, _ = ops.cvmm_fwd(recv, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                 ir=ir_all[0] if has_ir else None, ir_by_expert=True, absmax=am_up, inp_res=inp_res,
                                 out_res=out_res, out_bound=out_bound, out_relu=True, a_cache=xc, **nz_up)
-            main.wait_stream(side)
+            if shared is None:
+                main.wait_stream(side)
+            else:
+                main.wait_event(shared["dn_ready"])
             ops.set_tag("down")
             am_dn = None if has_ir else ops.row_absmax(h)
             # with the ADC on and the device-driven exchange the rows travel back as int8 codes + one scale per row
@@ -344,7 +353,10 @@ class _ExpertParallelStep(torch.autograd.Function):
                                       out_res=out_res, out_bound=out_bound, a_cache=hs, want_codes=codes_back,
                                       want_out=not codes_back, row_meta=meta, **nz_dn)
         else:
-            main.wait_stream(side)
+            if shared is None:
+                main.wait_stream(side)
+            else:
+                main.wait_event(shared["dn_ready"])
             codes_back = False
             h = recv.new_zeros((0, Fh))
             out = recv.new_zeros((0, N))
@@ -509,7 +521,7 @@ class _ExpertParallelStep(torch.autograd.Function):
             grad_values = grad_values.to(values_dtype)
         if grad_keys is not None:
             grad_keys = grad_keys.to(keys_dtype)
-        return (None, grad_x, grad_sel, grad_keys, grad_values, grad_ir)
+        return (None, grad_x, grad_sel, grad_keys, grad_values, grad_ir, None, None)
 
 
 class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
@@ -523,6 +535,12 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         self.n_experts_global = n_experts
         self.peer_exchange = os.environ.get("AMOE_EP_NCCL") is None    # rows by stores into peer memory (else NCCL)
         self._xchg = None
+        self._xchgs = {}               # exchange buffers per micro-batch
+        self._mb_streams = {}
+        # Micro-batches per layer call (single-node step only).  Each runs on its own stream with its own exchange
+        # buffers, so the rows of one travel over NVLink while the other's projections occupy the tensor cores; the
+        # exchange kernels are small enough (128 threads, 32 registers) to share an SM with a CVMM CTA.
+        self.micro_batches = int(kwargs.pop("micro_batches", os.environ.get("AMOE_EP_MICRO_BATCHES", 2)))
         self.max_slots = int(kwargs.pop("max_slots", 0))
         if kwargs.get("bias"):
             raise NotImplementedError("expert-parallel layer: bias is not built")
@@ -534,13 +552,13 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         with torch.no_grad():
             self.expert_sel.weight.copy_(torch.randn(n_experts, d_model, generator=g) * d_model ** -0.5)
 
-    def _peer_exchange(self, P: int, D: int, N: int, dtype) -> Optional["PeerExchange"]:
-        """The symmetric-memory exchange; None when peer access is off (`peer_exchange=False`, or symmetric memory could
-        not be set up: NCCL all-to-all with one host read then).  The buffers are sized at the first call from the
-        largest slot count over the ranks (one all-reduce and host read, once) or from `max_slots`."""
+    def _peer_exchange(self, P: int, D: int, N: int, dtype, part: int = 0) -> Optional["PeerExchange"]:
+        """The symmetric-memory exchange of micro-batch `part`; None when peer access is off (`peer_exchange=False`, or
+        symmetric memory could not be set up: NCCL all-to-all with one host read then).  The buffers are sized at the
+        first call from the largest slot count over the ranks (one all-reduce and host read, once) or from `max_slots`."""
         if not self.peer_exchange:
             return None
-        x = self._xchg
+        x = self._xchgs.get(part)
         if x is not None and x.key[1:] == (D, N, dtype) and P <= x.p_cap:
             return x
         if x is not None and P > x.p_cap:
@@ -551,8 +569,10 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
                 raise RuntimeError("first call under stream capture")
             m = torch.tensor([max(P, self.max_slots)], dtype=torch.int64, device=self.keys.device)
             dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
-            self._xchg = PeerExchange(self.group, self.keys.device, int(m.item()), D, N, dtype)
-            return self._xchg
+            self._xchgs[part] = PeerExchange(self.group, self.keys.device, int(m.item()), D, N, dtype)
+            if part == 0:
+                self._xchg = self._xchgs[0]
+            return self._xchgs[part]
         except Exception as exc:       # no symmetric memory on this system: say so once, use NCCL from now on
             import warnings
             warnings.warn(f"expert-parallel peer exchange unavailable ({exc!r}); using NCCL all-to-all")
@@ -581,10 +601,65 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         if not single_node:
             return self.forward_composed(inp)
         self._noise_calls = 0
-        y = _ExpertParallelStep.apply(self, inp, self.expert_sel.weight, self.keys, self.values, self.input_range)
+        bsz, seq, D = inp.shape
+        T = bsz * seq
+        mb = self.micro_batches if (self.micro_batches > 1 and T >= 256 * self.micro_batches) else 1
+        if mb == 1:
+            y = _ExpertParallelStep.apply(self, inp, self.expert_sel.weight, self.keys, self.values, self.input_range,
+                                          0, None)
+        else:
+            y = self._forward_micro_batches(inp, mb)
         if self.training:
             self.noise_step += 1
         return y, self._aux_zero
+
+    def _prepare_weights(self, x: Tensor) -> dict:
+        """Both weight pre-passes once per layer call, on the side stream (every micro-batch sees the same modified
+        weights, as the whole batch does in the reference's layer, moe_layer_aihwkit_lightning.py:458-469)."""
+        fwd = self.rpu_config.forward
+        precision = self._precision(x)
+        per_channel = bool(getattr(fwd, "out_noise_per_channel", True))
+        main, side = torch.cuda.current_stream(), ops.side_stream(x.device)
+        mods = [self._weight_modifier(), self._weight_modifier()]
+        side.wait_stream(main)
+        out = {}
+        with ops.launch_on(side):
+            for name, w, mod, tag in (("pw_up", self.keys, mods[0], "up"), ("pw_dn", self.values, mods[1], "down")):
+                ops.set_tag(tag)
+                out[name] = ops.weight_prepass(
+                    w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
+                    noise_per_channel=mod.per_channel if mod else True,
+                    discretize_res=mod.discretize_res if mod else -1.0, seed=mod.seed if mod else 0,
+                    offset=mod.offset if mod else 0, step_dev=mod.step if mod else None, need_fwd=True, need_bwd=True,
+                    expert_base=self.rank * self.n_experts)
+                out["up_ready" if name == "pw_up" else "dn_ready"] = side.record_event()
+        return out
+
+    def _forward_micro_batches(self, inp: Tensor, mb: int) -> Tensor:
+        bsz, seq, D = inp.shape
+        T = bsz * seq
+        main = torch.cuda.current_stream()
+        shared = self._prepare_weights(inp)
+        parts = torch.chunk(inp.reshape(1, T, D), mb, dim=1)
+        outs = []
+        for h, xh in enumerate(parts):
+            st = self._mb_streams.get(h)
+            if st is None:
+                st = self._mb_streams[h] = torch.cuda.Stream(device=inp.device)
+            st.wait_stream(main)
+            for name in ("pw_up", "pw_dn"):        # allocated for the calling stream, read by this one until backward ends
+                for t in vars(shared[name]).values():
+                    if torch.is_tensor(t):
+                        t.record_stream(st)
+            with torch.cuda.stream(st):
+                yh = _ExpertParallelStep.apply(self, xh, self.expert_sel.weight, self.keys, self.values, self.input_range,
+                                               h, shared)
+            outs.append((st, yh))
+        for st, yh in outs:
+            main.wait_stream(st)
+            yh.record_stream(main)
+        main.wait_stream(ops.side_stream(inp.device))
+        return torch.cat([yh for _, yh in outs], dim=1).view(bsz, seq, -1)
 
     def forward_composed(self, inp: Tensor) -> Tuple[Tensor, Tensor]:
         """The same step composed from autograd functions around CVMM.apply (any activation, dropout)."""

@@ -34,10 +34,12 @@ class StepHeartbeat:
         return f"{self.prefix}/{r}"
 
     def announce(self, step: int) -> None:
+        self._last = int(step)
         self.store.set(self._key(self.rank), str(int(step)))
 
     def leave(self) -> None:
-        self.store.set(self._key(self.rank), "left")
+        # the last step this rank ran travels with the note: a slower peer still checking that step is not misled
+        self.store.set(self._key(self.rank), f"left:{getattr(self, '_last', -1)}")
 
     def check(self, step: int) -> None:
         deadline = time.monotonic() + self.timeout_s
@@ -48,7 +50,9 @@ class StepHeartbeat:
                 val = None
                 if self.store.check([self._key(r)]):
                     val = self.store.get(self._key(r)).decode()
-                if val == "left":
+                if val is not None and val.startswith("left"):
+                    if int(val.partition(":")[2] or -1) >= step:
+                        break                       # it ran this step and left afterwards: the next check reports it
                     raise PeerLostError(f"rank {r} left the group before step {step}")
                 if val is not None and int(val) >= step:
                     break

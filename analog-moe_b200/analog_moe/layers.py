@@ -135,7 +135,8 @@ class _FusedAnalogStep(torch.autograd.Function):
         cached = layer.operand_caches and ops.operand_cache_ok(precision, D, Fh, N) and \
             any(ctx.needs_input_grad[3:5])
         split = precision == ops.A.PREC_SPLIT
-        xc = ops.OperandCache.empty(P, E, D, split, x.device) if cached else None
+        pre_up = layer.operand_prepass and ops.operand_tiles_ok(x2, precision)
+        xc = ops.OperandCache.empty(P, E, D, split, x.device) if (cached and not pre_up) else None
         hs = ops.OperandCache.empty(P, E, Fh, split, x.device) if cached else None
         # With input ranges and a quantising DAC the up-projection's epilogue also leaves the hidden rows as the
         # down-projection wants them (integer DAC codes as bf16 tiles, and gate * clamp(h) for its weight gradient),
@@ -146,9 +147,20 @@ class _FusedAnalogStep(torch.autograd.Function):
         hq = ops.OperandCache.empty(P, E, Fh, False, x.device) if tiles else None
         nxt = dict(next_ir=ir_all[1], next_inp_res=inp_res, next_codes=hq, out_cache=hs,
                    out_cache_scale=gate.reshape(-1) if hs is not None else None) if tiles else {}
+        # The DAC of the gathered input rows runs as a streaming pass of its own (full occupancy, HBM-bound) that leaves
+        # the codes as TMA tiles and the clamped rows as the weight gradient's operand; the tensor-core kernel then
+        # runs no operand prologue.
+        if pre_up:
+            xq, xc_pre = ops.operand_tiles(x2, r.token_index, r.expert_offsets, E, precision, P=P, dac=True, ir=ir_up,
+                                           ir_by_expert=True, absmax=am_up, inp_res=inp_res, want_cache=cached)
+            if cached:
+                xc = xc_pre
+            a_kw = dict(a_tiles=xq)
+        else:
+            a_kw = dict(a_cache=xc)
         h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
                             ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
-                            out_bound=out_bound, out_relu=True, a_cache=xc, **nxt, **nz)
+                            out_bound=out_bound, out_relu=True, **a_kw, **nxt, **nz)
         # ---- down-projection and the gate-weighted sum over k
         main.wait_stream(side)
         ops.set_tag("down")
@@ -182,6 +194,7 @@ class _FusedAnalogStep(torch.autograd.Function):
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
                               codes, row_scale, row_expert, res,
                               *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)))
+        ctx.operand_prepass = layer.operand_prepass
         ctx.meta = (x.shape, E, k, precision, ir_p, keys.dtype, values.dtype, adc_step, keys.shape, values.shape,
                     input_range.dtype if has_ir else None)
         return y.view(bsz, seq, N)
@@ -218,17 +231,25 @@ class _FusedAnalogStep(torch.autograd.Function):
                                       ir_by_expert=True, g_div=k, g_scale=gate.reshape(-1),
                                       g_absmax=ops.grad_absmax(g, precision))
         split = xc_lo is not None
-        gc = ops.OperandCache.empty(P, E, N, split, x2.device) if cached and need_values else None
+        # the upstream gradient rows, gathered per slot and converted by the operand pre-pass: the A tiles of the input
+        # gradient below and the weight gradient's operand at once
+        pre_dn = ctx.operand_prepass and ops.operand_tiles_ok(g, precision)
+        gc = ops.OperandCache.empty(P, E, N, split, x2.device) if cached and need_values and not pre_dn else None
         dhc = ops.OperandCache.empty(P, E, Fh, split, x2.device) if cached and need_keys else None
         # fp16 operands: one scalar (max|gy|) scales every gradient operand of the step into fp16's normal range
         gmax = ops.grad_absmax(g, precision)
         # the hidden gradient is only needed as fp32 rows when the next kernel cannot take it as tiles
         tiles_next = dhc is not None and Fh % 64 == 0 and (need_x or need_ir)
+        if pre_dn:
+            gc, _ = ops.operand_tiles(g, slot_index, offsets, E, precision, P=P, a_row_div=k, dac=False, g_absmax=gmax)
+            a_kw = dict(a_tiles=gc)
+        else:
+            a_kw = dict(a_cache=gc)
         dh, irs_dn = ops.cvmm_dx(g, slot_index, slot_index, offsets, pw_dn, precision, P=P, dst_rows=P, a_row_div=k,
                                  x_ref=h, x_ref_row=slot_index, ir=ir_dn, ir_by_expert=True, row_scale=gate.reshape(-1),
                                  want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                  keep_count=keeps[1:] if keeps is not None else None, out_dtype=h.dtype,
-                                 x_ref_relu=True, a_cache=gc, out_cache=dhc, g_absmax=gmax, want_out=not tiles_next)
+                                 x_ref_relu=True, out_cache=dhc, g_absmax=gmax, want_out=not tiles_next, **a_kw)
         # ---- up-projection's input gradient (the other kernel that fills every SM), then the two weight gradients from
         # the caches on a second stream: the TMA-fed kernel runs six warps per SM and leaves registers and issue slots
         # to the streaming kernels of the main stream (gate gradient, sum over k, router), which run beside it
@@ -445,6 +466,7 @@ class AnalogSigmaMoELayer(SigmaMoELayer):
         self.fused = True          # one autograd node for the whole layer when the configuration allows it
         self.operand_caches = True  # forward / dX kernels leave bf16 copies of the dW operands (fused path)
         self.hidden_tiles = True    # the up-projection leaves the hidden rows as the down-projection's A tiles
+        self.operand_prepass = True  # DAC of gathered rows as a streaming pass; the CVMM kernels load A tiles by TMA
         self.fuse_clip = False      # post_update_step only records the clipping; the next forward's weight pre-pass
                                     # clips in place while it reads the weights anyway (until then they are unclipped)
         self._pending_clip = None

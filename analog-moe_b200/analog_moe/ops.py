@@ -537,6 +537,49 @@ class OperandCache:
         return OperandCache(hi, torch.empty_like(hi) if split else None, cols)
 
 
+def operand_tiles_ok(x2: torch.Tensor, precision: int) -> bool:
+    """Rows the operand pre-pass can take: a tensor-core precision, 64-column blocks, 16-byte aligned rows."""
+    return precision != A.PREC_FP32_SIMT and x2.shape[-1] % 64 == 0 and x2.data_ptr() % 16 == 0 and \
+        (x2.stride(0) * x2.element_size()) % 16 == 0
+
+
+def operand_tiles(x2: torch.Tensor, a_row: torch.Tensor, offsets: torch.Tensor, E: int, precision: int, *, P: int,
+                  a_row_div: int = 1, dac: bool = True, ir: Optional[torch.Tensor] = None, ir_by_expert: bool = False,
+                  absmax: Optional[torch.Tensor] = None, inp_res: float = -1.0, want_tiles: bool = True,
+                  want_cache: bool = False, cache_scale: Optional[torch.Tensor] = None,
+                  g_absmax: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+    """The A operand of a CVMM call as TMA tiles, by a streaming pre-pass (amoe_operand_tiles).  Returns
+    (tiles or None, cache or None): `tiles` goes to cvmm_fwd / cvmm_dx as `a_tiles`, `cache` (forward operands only:
+    the clamped, unquantised rows) to cvmm_dw_cached.  For gradient rows (dac=False) the tiles are both."""
+    x2 = _rows(x2)
+    K = x2.shape[-1]
+    split = precision == A.PREC_SPLIT
+    # integer codes up to 256 in magnitude are exact in one bf16 term; anything else in split precision takes hi + lo
+    quant = dac and inp_res > 0
+    tile_split = split and not (quant and inp_res >= 1.0 / 256.0) and \
+        not (x2.dtype == torch.bfloat16 and dac and ir is None and absmax is None)
+    # (gradient rows always carry their residual term in split precision - zeros for bf16 rows: the weight gradient
+    # takes both operands with or both without one)
+    tiles = OperandCache.empty(P, E, K, tile_split, x2.device) if want_tiles else None
+    cache = OperandCache.empty(P, E, K, split, x2.device) if (want_cache and dac) else None
+    a = A.OperandTilesArgs()
+    a.P, a.E, a.K, a.precision = P, E, K, precision
+    a.expert_offsets = ptr(offsets)
+    a.a, a.a_dtype, a.a_stride, a.a_rows = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0]
+    a.a_row, a.a_row_div, a.dac = ptr(a_row), a_row_div, int(dac)
+    a.ir, a.ir_by_expert, a.a_absmax, a.inp_res = ptr(ir), int(ir_by_expert), ptr(absmax), float(inp_res)
+    if tiles is not None:
+        a.tile_hi, a.tile_lo = ptr(tiles.hi), ptr(tiles.lo)
+        a.cache_rows = tiles.rows
+    if cache is not None:
+        a.cache_hi, a.cache_lo, a.cache_scale = ptr(cache.hi), ptr(cache.lo), ptr(cache_scale)
+        a.cache_rows = cache.rows
+    a.g_absmax_dev = ptr(g_absmax)
+    a.dev_status = ptr(status)
+    _call("amoe_operand_tiles", C.byref(a), stream_ptr())
+    return tiles, cache
+
+
 def operand_cache_ok(precision: int, *cols: int) -> bool:
     return precision != A.PREC_FP32_SIMT and all(c % 16 == 0 for c in cols)
 

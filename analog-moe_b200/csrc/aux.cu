@@ -25,11 +25,19 @@ __device__ __forceinline__ void ld4(const T* p, bool vec, int valid, float o[4])
     for (int c = 0; c < 4; ++c) o[c] = c < valid ? to_f32<T>(p[c]) : 0.f;
   }
 }
+// Four int8 codes packed in a word as floats, without integer->float conversions: flipping each byte's top bit turns
+// the code c into the unsigned byte c + 128; dropped into the low byte of 0x4B400000 (= 1.5 * 2^23) that is the float
+// 1.5 * 2^23 + c + 128 exactly, and one subtraction leaves c.
+__device__ __forceinline__ void codes4_to_float(uint32_t u, float o[4]) {
+  const uint32_t x = u ^ 0x80808080u;
+  o[0] = __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7650)) - 12583040.f;
+  o[1] = __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7651)) - 12583040.f;
+  o[2] = __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7652)) - 12583040.f;
+  o[3] = __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7653)) - 12583040.f;
+}
 __device__ __forceinline__ void ld4_codes(const int8_t* p, bool vec, int valid, float o[4]) {
   if (vec) {
-    const uint32_t u = __ldg(reinterpret_cast<const uint32_t*>(p));
-#pragma unroll
-    for (int c = 0; c < 4; ++c) o[c] = static_cast<float>(static_cast<int8_t>((u >> (8 * c)) & 0xffu));
+    codes4_to_float(__ldg(reinterpret_cast<const uint32_t*>(p)), o);
   } else {
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[c] = c < valid ? static_cast<float>(p[c]) : 0.f;
@@ -140,9 +148,11 @@ __global__ void combine_codes16_kernel(const int8_t* __restrict__ codes, const f
     for (int q = 0; q < 4; ++q) {
       const float4 cs = __ldg(csp + q);
       const float csv[4] = {cs.x, cs.y, cs.z, cs.w};
+      float cdq[4];
+      codes4_to_float(cw[q], cdq);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const float cdv = static_cast<float>(static_cast<int8_t>((cw[q] >> (8 * c)) & 0xffu));
+        const float cdv = cdq[c];
         const float v = __fmul_rn(__fmul_rn(__fmul_rn(cdv, step), csv[c]), rm);
         acc[4 * q + c] = fmaf(ws, v, acc[4 * q + c]);
       }
@@ -210,6 +220,75 @@ __global__ void row_dot_codes_kernel(const int8_t* __restrict__ codes, const flo
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) d[s] = acc;
+}
+
+// The same dot products with one warp per TOKEN: the gradient row is loaded once for the token's k slots (it was the
+// largest stream of the slot-per-warp kernel above) and stays in registers, 1024 columns at a time.  Per slot the
+// lane's products are added in the same order as above, so the results are bit-identical.  k <= KMAX.
+template <typename TG, int KMAX>
+__global__ void __launch_bounds__(256) row_dot_codes_token_kernel(
+    const int8_t* __restrict__ codes, const float* __restrict__ col_scale, const int32_t* __restrict__ row_expert,
+    const float* __restrict__ row_scale, float step, const TG* __restrict__ g, int64_t g_stride, int64_t T, int k, int N,
+    float* __restrict__ d, const int32_t* __restrict__ row_index) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (t >= T) return;
+  const TG* gr = g + t * g_stride;
+  const int nq = N / 4;
+  float acc[KMAX];
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) acc[j] = 0.f;
+  for (int q0 = 0; q0 < nq; q0 += 256) {
+    float b[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int q = q0 + lane + 32 * i;
+      if (q < nq) ld4<TG>(gr + 4 * q, true, 4, b[i]);
+    }
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < k) {
+        const int64_t s = t * k + j;
+        const int64_t rr = row_index ? row_index[s] : s;
+        const int8_t* r = codes + rr * N;
+        const float* cs = col_scale + static_cast<int64_t>(row_expert[s]) * N;
+        const float rs = row_scale ? row_scale[rr] : 1.f;
+        uint32_t cw[8];
+        float4 sc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int q = q0 + lane + 32 * i;
+          if (q < nq) {
+            cw[i] = __ldg(reinterpret_cast<const uint32_t*>(r + 4 * q));
+            sc[i] = __ldg(reinterpret_cast<const float4*>(cs + 4 * q));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int q = q0 + lane + 32 * i;
+          if (q < nq) {
+            float cd[4];
+            codes4_to_float(cw[i], cd);
+            const float scv[4] = {sc[i].x, sc[i].y, sc[i].z, sc[i].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float v = __fmul_rn(__fmul_rn(__fmul_rn(cd[c], step), scv[c]), rs);
+              acc[j] = fmaf(v, b[i][c], acc[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    if (j < k) {
+      float a = acc[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0) d[t * k + j] = a;
+    }
+  }
 }
 
 // One CTA of 256 threads per expert: fixed-order (thread-strided, butterfly inside each warp, then across the
@@ -496,6 +575,24 @@ int amoe_row_dot_codes(const int8_t* codes, const float* col_scale, const int32_
   AMOE_REQUIRE(P > 0 && k > 0 && N > 0, AMOE_ERR_BAD_SHAPE);
   const unsigned blocks = blocks_for(P * 32, 256);
   const int vec = (N % 4 == 0) && (g_stride % 4 == 0) && al16(g) && al16(col_scale) && al16(codes);
+  if (vec && k <= 8 && P % k == 0 && (g_dtype == AMOE_F32 || g_dtype == AMOE_BF16)) {
+    // one warp per token (g_stride % 8 == 0 for bf16 rows: 8-byte loads)
+    const int64_t T = P / k;
+    const unsigned tb = blocks_for(T * 32, 256);
+    if (g_dtype == AMOE_F32) {
+      row_dot_codes_token_kernel<float, 8><<<tb, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
+                                                                   reinterpret_cast<const float*>(g), g_stride, T, k, N, d, row_index);
+      AMOE_LAUNCH_CHECK("row_dot_codes_token");
+      return AMOE_OK;
+    }
+    if (g_stride % 8 == 0) {
+      row_dot_codes_token_kernel<__nv_bfloat16, 8><<<tb, 256, 0, stream>>>(
+          codes, col_scale, row_expert, row_scale, step, reinterpret_cast<const __nv_bfloat16*>(g), g_stride, T, k, N, d,
+          row_index);
+      AMOE_LAUNCH_CHECK("row_dot_codes_token");
+      return AMOE_OK;
+    }
+  }
   if (g_dtype == AMOE_F32)
     row_dot_codes_kernel<float><<<blocks, 256, 0, stream>>>(codes, col_scale, row_expert, row_scale, step,
                                                             reinterpret_cast<const float*>(g), g_stride, P, k, N, d, vec, row_index);

@@ -147,8 +147,11 @@ __device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restric
 }
 
 // Sorted position i of this rank's slot list -> its row in the owner's receive buffer.
+// The two exchange kernels run with 128 threads and at most 32 registers per thread, so that a block of them fits on
+// an SM beside a 768-thread, 80-register CVMM block: rows of one micro-batch cross NVLink while the other
+// micro-batch's projections run.
 template <typename T>
-__global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
+__global__ void __launch_bounds__(128, 16) ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, const int32_t* __restrict__ src_row,
                               int src_div, const float* __restrict__ row_scale, int64_t P,
                               const int32_t* __restrict__ sel_sorted, int El, const int32_t* __restrict__ plan,
                               const uint64_t* __restrict__ peer_ptrs, int G, int64_t peer_rows, int64_t x_rows, int vec,
@@ -173,7 +176,7 @@ __global__ void ep_put_kernel(const T* __restrict__ x, int64_t stride, int K, co
 
 // Row r of this rank's receive-ordered buffer -> its place in the source rank's sorted slot list.
 template <typename T>
-__global__ void ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, int K, const int32_t* __restrict__ plan,
+__global__ void __launch_bounds__(128, 16) ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, int K, const int32_t* __restrict__ plan,
                                    const uint64_t* __restrict__ peer_ptrs, int G, int64_t cap_rows, int64_t peer_rows,
                                    int vec, int32_t* __restrict__ status) {
   const int lane = threadIdx.x & 31;
@@ -241,12 +244,12 @@ int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t
   AMOE_REQUIRE(P > 0 && K > 0 && El > 0 && G > 0 && G <= kEpMaxRanks && src_div >= 1 && peer_rows > 0 && x_rows > 0, AMOE_ERR_BAD_SHAPE);
   const int esz = dtype == AMOE_F32 ? 4 : 2;
   const int vec = al16(x) && (stride * esz) % 16 == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;   // peer bases are page aligned
-  const unsigned blocks = static_cast<unsigned>((spread_count(P) * 32 + 255) / 256);
+  const unsigned blocks = static_cast<unsigned>((spread_count(P) * 32 + 127) / 128);
   if (dtype == AMOE_F32)
-    ep_put_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div, row_scale, P,
+    ep_put_kernel<float><<<blocks, 128, 0, stream>>>(reinterpret_cast<const float*>(x), stride, K, src_row, src_div, row_scale, P,
                                                      sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows, vec, dev_status);
   else if (dtype == AMOE_BF16)
-    ep_put_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K, src_row, src_div,
+    ep_put_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), stride, K, src_row, src_div,
                                                              row_scale, P, sel_sorted, El, plan, peer_ptrs, G, peer_rows, x_rows,
                                                              vec, dev_status);
   else
@@ -263,14 +266,14 @@ int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K,
   AMOE_REQUIRE(K > 0 && G > 0 && G <= kEpMaxRanks && cap_rows > 0 && peer_rows > 0, AMOE_ERR_BAD_SHAPE);
   const int esz = dtype == AMOE_F32 ? 4 : 2;
   const int vec = al16(rows) && (stride * esz) % 16 == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;
-  int64_t blocks = (cap_rows * 32 + 255) / 256;
+  int64_t blocks = (cap_rows * 32 + 127) / 128;
   const int64_t max_blocks = static_cast<int64_t>(sm_count()) * 16;
   if (blocks > max_blocks) blocks = max_blocks;
   if (dtype == AMOE_F32)
-    ep_put_back_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(reinterpret_cast<const float*>(rows), stride, K, plan,
+    ep_put_back_kernel<float><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(reinterpret_cast<const float*>(rows), stride, K, plan,
                                                                                  peer_ptrs, G, cap_rows, peer_rows, vec, dev_status);
   else if (dtype == AMOE_BF16)
-    ep_put_back_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+    ep_put_back_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(rows), stride, K, plan, peer_ptrs, G, cap_rows, peer_rows, vec, dev_status);
   else
     return AMOE_ERR_BAD_DTYPE;

@@ -48,10 +48,6 @@ constexpr int kBK = 64;           // bf16 elements per stage along the contracti
 // (which spilled) and than 20 x 102.
 constexpr int kWorkerWarps = 22;
 constexpr int kFwdThreads = (2 + kWorkerWarps) * 32;      // 768
-// Staged operand prologue: raw rows travel global -> shared by cp.async, kStagePF ring stages ahead of the stage that
-// is being converted, through kStagePF + 1 staging slots of 128 rows x 64 elements.
-constexpr int kStagePF = 2;
-constexpr int kStageSlots = kStagePF + 1;
 constexpr int kMaxEpiGroups = 6;
 constexpr int kMaxStages = 8;
 constexpr uint32_t kATile = kBM * kBK * 2;  // 16 KiB
@@ -97,7 +93,7 @@ struct TileIter {
 struct TcParams {
   int E, Kc, Nout;
   int n_epi;   // epilogue warps (multiple of 4)
-  int n_prod;  // operand-prologue warps (the staged prologue wants 8 or 16); n_epi + n_prod <= kWorkerWarps
+  int n_prod;  // operand-prologue warps; n_epi + n_prod <= kWorkerWarps
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   int prod_groups;      // 1, or 2: the prologue warps form two groups that take alternate stages, so that one
@@ -114,26 +110,10 @@ struct TcParams {
                         // TMA loads it, there is no prologue and every worker warp runs the epilogue
   int item_mode;        // work item = (row tile, n-tile) instead of a row tile with all its n-tiles (only without a
                         // prologue: the A tile is cheap to load again, and small items fill the last wave better)
-  int staged;           // operand prologue fed by cp.async through the staging slots (aligned rows, K % 8 == 0)
-  uint32_t stg_off;     // offset of the staging slots in dynamic shared memory
-  uint32_t stg_slot;    // bytes per staging slot
   const float* g_absmax;  // fp16 operands, input gradient: device scalar max|A|; A is scaled by a power of two derived
                           // from it before the conversion and the result scaled back (NULL: no scaling)
   EpiParams epi;
 };
-
-// Power of two s such that amax * s lies in [2^7, 2^8): gradient rows scaled by it use fp16's normal range whatever
-// their magnitude.  1 for zero or non-finite amax.  `inv` receives 1/s (exact).
-__device__ __forceinline__ float grad_pow2_scale(float amax, float& inv) {
-  inv = 1.f;
-  if (!(amax > 0.f) || !(amax < 3.0e38f)) return 1.f;
-  int ex = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu);
-  if (ex == 0) ex = 1;
-  int k = 7 - (ex - 127);
-  k = max(-120, min(120, k));
-  inv = __uint_as_float(static_cast<uint32_t>(127 - k) << 23);
-  return __uint_as_float(static_cast<uint32_t>(127 + k) << 23);
-}
 
 enum { kDacNone = 0, kDacNorm = 1, kDacQuant = 2 };
 // Epilogue families: forward with the vectorised fast path (optional Philox noise / ADC / codes),
@@ -226,9 +206,9 @@ struct SmemView {
 
 __device__ __forceinline__ SmemView carve_smem(uint8_t* raw, uint32_t ring_bytes) {
   SmemView s;
-  uintptr_t p = reinterpret_cast<uintptr_t>(raw);
-  p = (p + 1023) & ~static_cast<uintptr_t>(1023);
-  s.base = reinterpret_cast<uint8_t*>(p);
+  // (pointer arithmetic on the shared array itself, so that accesses through `base` stay shared-memory accesses)
+  const uint32_t pad = (1024u - (smem_u32(raw) & 1023u)) & 1023u;
+  s.base = raw + pad;
   s.base_u32 = smem_u32(s.base);
   uint8_t* tail = s.base + ring_bytes;
   s.bars = smem_u32(tail);
@@ -357,40 +337,54 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 // kValue = false: only the ADC codes leave the kernel, the dequantised values are not formed.
 // The ADC code rint(x) is taken as (x + 1.5*2^23) - 1.5*2^23 (exact round-to-nearest-even for |x| < 2^22; codes are
 // at most 127 in magnitude), whose low mantissa byte is the code in two's complement.
-template <bool kValue, bool F16>
-__device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
-                                              float v[16], const float* cs, const float* cis, int lane) {
+// NOISE / ADC are compile-time copies of the launch's options (the caller dispatches once per chunk): the arithmetic
+// runs as packed pairs (two columns per instruction) with the rounding of the scalar definition - every product and
+// sum below is one IEEE operation in the order (acc*res + (std*s)*z) * (1/s) -> clamp -> * (1/step) -> round.
+template <bool kValue, bool F16, bool NOISE, bool ADC>
+__device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
+                                                float v[16], const float* cs, const float* cis, int lane) {
   constexpr float kMagic = 12582912.f;
-  const bool noise = p.noise_std > 0.f, adc = p.adc.on;
   const float post = c.absmax * c.ir;
+  const f32x2 accmul2 = pack2(p.acc_mul, p.acc_mul), nstd2 = pack2(p.noise_std, p.noise_std);
+  const f32x2 istep2 = pack2(p.adc.inv_step, p.adc.inv_step), step2 = pack2(p.adc.step, p.adc.step);
+  const f32x2 magic2 = pack2(kMagic, kMagic), nmagic2 = pack2(-kMagic, -kMagic), post2 = pack2(post, post);
   uint32_t pk[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
   for (int qd = 0; qd < 4; ++qd) {
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 s4 = make_float4(1.f, 1.f, 1.f, 1.f), i4 = s4;
-    if (noise | adc) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
-    if (adc) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
-    if (noise) {
+    if (NOISE || ADC) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
+    if (ADC) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
+    if (NOISE) {
       const uint4 w = philox4x32_10_keys(static_cast<uint32_t>(c.dst), static_cast<uint32_t>((n0 >> 2) + qd), kStreamOutNoise,
                                          c.noise_offset, p.pkeys);
       box_muller(w.x, w.y, z.x, z.y);
       box_muller(w.z, w.w, z.z, z.w);
     }
-    const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, iv[4] = {i4.x, i4.y, i4.z, i4.w}, zv[4] = {z.x, z.y, z.z, z.w};
+    const f32x2 sp[2] = {pack2(s4.x, s4.y), pack2(s4.z, s4.w)}, ip[2] = {pack2(i4.x, i4.y), pack2(i4.z, i4.w)};
+    const f32x2 zp[2] = {pack2(z.x, z.y), pack2(z.z, z.w)};
     float tb[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float acc = v[4 * qd + j] * p.acc_mul;
-      if (noise) acc += (p.noise_std * sv[j]) * zv[j];
-      if (adc) {
-        float x = acc * iv[j];
-        x = fminf(fmaxf(x, -p.adc.out_bound), p.adc.out_bound);
-        tb[j] = __fadd_rn(__fmul_rn(x, p.adc.inv_step), kMagic);
-        if (kValue) acc = ((tb[j] - kMagic) * p.adc.step) * sv[j];
+    for (int h = 0; h < 2; ++h) {
+      f32x2 acc = mul2(pack2(v[4 * qd + 2 * h], v[4 * qd + 2 * h + 1]), accmul2);
+      if (NOISE) acc = add2(acc, mul2(mul2(nstd2, sp[h]), zp[h]));
+      if (ADC) {
+        float x0, x1;
+        unpack2(mul2(acc, ip[h]), x0, x1);
+        x0 = fminf(fmaxf(x0, -p.adc.out_bound), p.adc.out_bound);
+        x1 = fminf(fmaxf(x1, -p.adc.out_bound), p.adc.out_bound);
+        const f32x2 t = add2(mul2(pack2(x0, x1), istep2), magic2);
+        unpack2(t, tb[2 * h], tb[2 * h + 1]);
+        if (kValue) acc = mul2(mul2(add2(t, nmagic2), step2), sp[h]);
       }
-      if (kValue) v[4 * qd + j] = p.out_relu ? fmaxf(acc * post, 0.f) : acc * post;
+      if (kValue) {
+        float y0, y1;
+        unpack2(mul2(acc, post2), y0, y1);
+        v[4 * qd + 2 * h] = p.out_relu ? fmaxf(y0, 0.f) : y0;
+        v[4 * qd + 2 * h + 1] = p.out_relu ? fmaxf(y1, 0.f) : y1;
+      }
     }
-    if (adc)
+    if (ADC)
       pk[qd] = __byte_perm(__byte_perm(__float_as_uint(tb[0]), __float_as_uint(tb[1]), 0x0040),
                            __byte_perm(__float_as_uint(tb[2]), __float_as_uint(tb[3]), 0x0040), 0x5410);
   }
@@ -422,9 +416,15 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
       if (p.next_codes) {
         uint32_t q[4];
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-          q[x] = cvt_op2<F16>(dac_code_clamped(hc[2 * x], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res),
-                              dac_code_clamped(hc[2 * x + 1], true, c.next_ir, c.next_rcp, false, 1.f, 1.f, p.next_res, rcp_res));
+        for (int x = 0; x < 4; ++x) {
+          // rint((h / ir) / res) with IEEE-exact quotients, as packed pairs (dac_code_clamped, two at a time)
+          f32x2 t = div_by_rcp2(pack2(hc[2 * x], hc[2 * x + 1]), pack2(-c.next_ir, -c.next_ir), pack2(c.next_rcp, c.next_rcp));
+          t = div_by_rcp2(t, pack2(-p.next_res, -p.next_res), pack2(rcp_res, rcp_res));
+          t = add2(add2(t, pack2(12582912.f, 12582912.f)), pack2(-12582912.f, -12582912.f));
+          float q0, q1;
+          unpack2(t, q0, q1);
+          q[x] = cvt_op2<F16>(q0, q1);
+        }
         *reinterpret_cast<uint4*>(p.next_codes + co + 8 * half) = make_uint4(q[0], q[1], q[2], q[3]);
       }
       if (p.out_cache_hi) {
@@ -443,6 +443,16 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
     }
   }
   if (kValue) store16_t(p, qr, n0, v, lane);
+}
+
+template <bool kValue, bool F16>
+__device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
+                                              float v[16], const float* cs, const float* cis, int lane) {
+  const bool noise = p.noise_std > 0.f, adc = p.adc.on;
+  if (noise && adc) epi_chunk_fwd_t<kValue, F16, true, true>(p, c, qr, n0, v, cs, cis, lane);
+  else if (adc) epi_chunk_fwd_t<kValue, F16, false, true>(p, c, qr, n0, v, cs, cis, lane);
+  else if (noise) epi_chunk_fwd_t<kValue, F16, true, false>(p, c, qr, n0, v, cs, cis, lane);
+  else epi_chunk_fwd_t<kValue, F16, false, false>(p, c, qr, n0, v, cs, cis, lane);
 }
 
 // `cache_mul`: the operand cache keeps the result times this power of two (the gradient scale of fp16 operands).
@@ -469,12 +479,15 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
     }
     quad_transpose(xr, lane);     // back to "my row, 16 columns"
     if (p.ir) {
+      // up = x >= ir adds min(g, 0), low = x <= -ir subtracts max(g, 0), everything else is kept (cvmm.py:863-870).
+      // With t = g carrying x's sign flipped in (exact), both clipped cases are min(t, 0): one compare, one min.
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        float gs = v[j] * c.rs;
-        const bool up = xr[j] >= c.ir, low = xr[j] <= -c.ir, keep = fabsf(xr[j]) < c.ir;
-        if (up) c.dir_acc += fminf(gs, 0.f);
-        if (low) c.dir_acc -= fmaxf(gs, 0.f);
+        const float gs = v[j] * c.rs;
+        const bool keep = fabsf(xr[j]) < c.ir;
+        const float t = __uint_as_float(__float_as_uint(gs) ^ (__float_as_uint(xr[j]) & 0x80000000u));
+        const bool clipped = fabsf(xr[j]) >= c.ir;      // (false for a NaN reference, like `up` and `low`)
+        if (clipped) c.dir_acc += fminf(t, 0.f);
         c.keep += keep ? 1u : 0u;
         v[j] = keep ? gs : 0.f;
       }
@@ -531,50 +544,6 @@ struct ItemWalk {
   }
   __device__ void next() { w += gridDim.x; }
 };
-
-// The ring stages of one CTA in the order the pipeline visits them: (row tile, n-tile, k-chunk).
-struct StageWalk {
-  ItemWalk it;
-  int k_chunks;
-  int nt, kc;
-  bool valid, new_tile;
-  __device__ StageWalk(const TcParams& p) : it(p), k_chunks(p.k_chunks), nt(0), kc(0), valid(false), new_tile(true) {
-    valid = it.get();
-    if (valid) nt = it.nt0;
-  }
-  __device__ void next() {
-    new_tile = false;
-    if (++kc == k_chunks) {
-      kc = 0;
-      if (++nt == it.nt1) {
-        it.next();
-        valid = it.get();
-        nt = valid ? it.nt0 : 0;
-        new_tile = true;
-      }
-    }
-  }
-};
-
-// DAC of eight clamped values as packed pairs: ((a/ir)/absmax)/res with IEEE-exact quotients, then the integer code by
-// adding and subtracting 1.5 * 2^23 (round to nearest even, exact for |code| < 2^22).  The same arithmetic as
-// dac_code_clamped, two elements per instruction.
-__device__ __forceinline__ void dac_codes8(float v[8], bool has_ir, float ir, float rcp_ir, bool has_am, float am, float rcp_am,
-                                           float res, float rcp_res) {
-  const f32x2 nir = pack2(-ir, -ir), yir = pack2(rcp_ir, rcp_ir);
-  const f32x2 nam = pack2(-am, -am), yam = pack2(rcp_am, rcp_am);
-  const f32x2 nres = pack2(-res, -res), yres = pack2(rcp_res, rcp_res);
-  const f32x2 magic = pack2(12582912.f, 12582912.f), nmagic = pack2(-12582912.f, -12582912.f);
-#pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    f32x2 t = pack2(v[2 * x], v[2 * x + 1]);
-    if (has_ir) t = div_by_rcp2(t, nir, yir);
-    if (has_am) t = div_by_rcp2(t, nam, yam);
-    t = div_by_rcp2(t, nres, yres);
-    t = add2(add2(t, magic), nmagic);
-    unpack2(t, v[2 * x], v[2 * x + 1]);
-  }
-}
 
 template <int DAC, bool A_F32, int EPI, bool F16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
@@ -773,196 +742,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         }
       }
     }
-  } else if (!p.a_tma && warp < 2 + p.n_epi + n_prod && p.staged) {
-    // ---------------------------------------------------------------- operand prologue, staged (A tiles)
-    // Thread (rg, c) owns 16-byte chunk c of rows rg, rg + np/8, ... of every stage.  For stage g it (1) issues the
-    // cp.async copies of stage g + kStagePF into a staging slot, (2) waits for its own copies of stage g, (3) reads
-    // them back, applies clamp / DAC / conversion and writes its chunks of the swizzled A tile.  A thread only ever
-    // reads staging bytes it copied itself, so cp.async.wait_group is all the synchronisation the staging needs;
-    // global-load latency is hidden by the copies in flight instead of by registers.
-    constexpr int kEsz = A_F32 ? 4 : 2;
-    constexpr uint32_t kPlane = kBM * 8 * 16;            // one 16-byte piece per (row, chunk)
-    const int pw = warp - (2 + p.n_epi);
-    const int np = n_prod * 32;
-    const int pt = pw * 32 + lane;
-    const int c = pt & 7, rg = pt >> 3, rstep = np >> 3;
-    const int tpt = (kBM * 8) / np;                      // chunks per thread and stage: 2 or 4
-    const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
-    const float rcp_res = quant_rcp(p.inp_res);
-    const uint32_t stg = sm.base_u32 + p.stg_off;
-    const uint8_t* abase = reinterpret_cast<const uint8_t*>(p.a);
-    StageWalk pre(p), cur(p);
-    // per-thread row state of the tile being prefetched (source rows) and of the tile being converted
-    int pre_src[4] = {-1, -1, -1, -1};
-    int cur_src[4] = {-1, -1, -1, -1};
-    float cur_ir[4] = {1.f, 1.f, 1.f, 1.f}, cur_am[4] = {1.f, 1.f, 1.f, 1.f}, cur_cs[4] = {1.f, 1.f, 1.f, 1.f};
-    auto rows_of = [&](const StageWalk& w, int src[4]) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        src[j] = -1;
-        const int r = rg + j * rstep;
-        if (j < tpt && w.valid && r < w.it.rows) {
-          const int64_t raw = p.a_row[static_cast<int64_t>(w.it.row0) + r];
-          const int64_t sr = raw / p.a_div;
-          if (sr < 0 || sr >= p.a_rows) report(status, AMOE_ERR_INDEX_RANGE, 20, w.it.row0 + r, static_cast<int>(sr));
-          else src[j] = static_cast<int>(sr);
-        }
-      }
-    };
-    auto issue = [&](const StageWalk& w, int slot) {
-      const uint32_t sbase = stg + static_cast<uint32_t>(slot) * p.stg_slot;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (j < tpt) {
-          const int r = rg + j * rstep;
-          const int k = w.kc * kBK + c * 8;
-          const bool ok = pre_src[j] >= 0 && k < p.Kc;
-          const uint8_t* g = ok ? abase + (static_cast<int64_t>(pre_src[j]) * p.a_stride + k) * kEsz : abase;
-          const uint32_t d = sbase + static_cast<uint32_t>(r * 8 + c) * 16u;
-          cp_async16(d, g, ok ? 16u : 0u);
-          if (A_F32) cp_async16(d + kPlane, g + (ok ? 16 : 0), ok ? 16u : 0u);
-        }
-      }
-    };
-    // prime the pipeline
-    int pre_slot = 0;
-    for (int x = 0; x < kStagePF; ++x) {
-      if (pre.valid) {
-        if (pre.new_tile) rows_of(pre, pre_src);
-        issue(pre, pre_slot);
-        pre.next();
-      }
-      cp_async_commit();
-      pre_slot = pre_slot + 1 == kStageSlots ? 0 : pre_slot + 1;
-    }
-    RingPos rp(p.stages);
-    int cur_slot = 0;
-    bool alive = true;
-    while (alive && cur.valid) {
-      if (pre.valid) {
-        if (pre.new_tile) rows_of(pre, pre_src);
-        issue(pre, pre_slot);
-        pre.next();
-      }
-      cp_async_commit();
-      pre_slot = pre_slot + 1 == kStageSlots ? 0 : pre_slot + 1;
-      if (cur.new_tile) {
-        rows_of(cur, cur_src);      // (index errors were reported when the tile was prefetched; harmless to repeat)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j < tpt && cur_src[j] >= 0) {
-            const int64_t i = static_cast<int64_t>(cur.it.row0) + rg + j * rstep;
-            if (has_ir) cur_ir[j] = p.ir[p.epi.ir_by_expert ? cur.it.e : i];
-            if (has_am) cur_am[j] = p.a_absmax[cur_src[j]];
-            if (p.cache_scale) cur_cs[j] = p.cache_scale[p.a_row[i]];
-          }
-        }
-      }
-      cp_async_wait<kStagePF>();       // this thread's copies of the current stage have landed
-      const int s = rp.s;
-      bool ok = mbar_wait(bar_empty(sm.bars, s), rp.ph ^ 1u, sm.abort_flag, status, 6);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { alive = false; break; }
-      const uint32_t a_hi = sm.base_u32 + s * p.stage_bytes;
-      const uint32_t a_lo = a_hi + kATile;
-      const uint32_t sbase = stg + static_cast<uint32_t>(cur_slot) * p.stg_slot;
-      const bool do_cache = p.cache_hi != nullptr && cur.nt == 0;
-      const int kk = cur.kc * kBK + c * 8;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        if (j < tpt) {
-          const int r = rg + j * rstep;
-          const uint32_t sa = sbase + static_cast<uint32_t>(r * 8 + c) * 16u;
-          float v[8];
-          if (A_F32) {
-            const uint4 x = lds128(sa), y = lds128(sa + kPlane);
-            v[0] = __uint_as_float(x.x); v[1] = __uint_as_float(x.y); v[2] = __uint_as_float(x.z); v[3] = __uint_as_float(x.w);
-            v[4] = __uint_as_float(y.x); v[5] = __uint_as_float(y.y); v[6] = __uint_as_float(y.z); v[7] = __uint_as_float(y.w);
-          } else {
-            const uint4 x = lds128(sa);
-            v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
-            v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
-            v[4] = __uint_as_float(x.z << 16); v[5] = __uint_as_float(x.z & 0xffff0000u);
-            v[6] = __uint_as_float(x.w << 16); v[7] = __uint_as_float(x.w & 0xffff0000u);
-          }
-          const bool live = cur_src[j] >= 0;
-          const bool cache_now = do_cache && kk < p.Kc;
-          // cache layout: [64-column block][padded row][64]
-          const int64_t co = cache_now ? ((cur.kc * p.cache_stride + cur.it.t * kBM + r) << 6) + c * 8 : 0;
-          const uint32_t soff = sw128_offset(r, c);
-          if (DAC == kDacNone) {
-            if (F16) {
-#pragma unroll
-              for (int x = 0; x < 8; ++x) v[x] *= g_mul;
-            }
-            // the tile and the cache hold the same terms: convert once, store twice
-            uint32_t h[4], l[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-            for (int x = 0; x < 4; ++x) h[x] = cvt_op2<F16>(v[2 * x], v[2 * x + 1]);
-            if (!F16 && (p.a_split || (cache_now && p.cache_lo))) {
-#pragma unroll
-              for (int x = 0; x < 4; ++x)
-                l[x] = cvt_bf16x2(v[2 * x] - __uint_as_float(h[x] << 16), v[2 * x + 1] - __uint_as_float(h[x] & 0xffff0000u));
-            }
-            sts128(a_hi + soff, h[0], h[1], h[2], h[3]);
-            if (!F16 && p.a_split) sts128(a_lo + soff, l[0], l[1], l[2], l[3]);
-            if (cache_now) {
-              *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
-              if (!F16 && p.cache_lo) *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
-            }
-          } else {
-            if (has_ir && live) {
-#pragma unroll
-              for (int x = 0; x < 8; ++x) v[x] = clamp_ir(v[x], cur_ir[j]);
-            }
-            if (cache_now) {
-              // the operand as dW wants it: clamped (not quantised), times the per-row scale
-              uint32_t h[4];
-#pragma unroll
-              for (int x = 0; x < 4; ++x)
-                h[x] = p.cache_scale ? cvt_op2<F16>(v[2 * x] * cur_cs[j], v[2 * x + 1] * cur_cs[j]) : cvt_op2<F16>(v[2 * x], v[2 * x + 1]);
-              *reinterpret_cast<uint4*>(p.cache_hi + co) = make_uint4(h[0], h[1], h[2], h[3]);
-              if (!F16 && p.cache_lo) {
-                uint32_t l[4];
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                  const float a0 = p.cache_scale ? v[2 * x] * cur_cs[j] : v[2 * x];
-                  const float a1 = p.cache_scale ? v[2 * x + 1] * cur_cs[j] : v[2 * x + 1];
-                  l[x] = cvt_bf16x2(a0 - __uint_as_float(h[x] << 16), a1 - __uint_as_float(h[x] & 0xffff0000u));
-                }
-                *reinterpret_cast<uint4*>(p.cache_lo + co) = make_uint4(l[0], l[1], l[2], l[3]);
-              }
-            }
-            if (live) {
-              const float rcp_ir = has_ir ? __frcp_rn(cur_ir[j]) : 1.f;
-              const float rcp_am = has_am ? __frcp_rn(cur_am[j]) : 1.f;
-              if (DAC == kDacQuant && p.inp_res >= 4.0e-7f) {
-                dac_codes8(v, has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am, p.inp_res, rcp_res);
-              } else {
-#pragma unroll
-                for (int x = 0; x < 8; ++x) {
-                  if (DAC == kDacQuant)
-                    v[x] = dac_code_clamped(v[x], has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am, p.inp_res, rcp_res);
-                  else
-                    v[x] = dac_normalise_clamped(v[x], has_ir, cur_ir[j], rcp_ir, has_am, cur_am[j], rcp_am);
-                }
-              }
-            }
-            store8_rt<F16>(a_hi, a_lo, soff, v, p.a_split != 0);
-          }
-        }
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_full_a(sm.bars, s));
-      cur_slot = cur_slot + 1 == kStageSlots ? 0 : cur_slot + 1;
-      rp.next();
-      cur.next();
-    }
-    cp_async_wait<0>();      // nothing of this thread may still be in flight when the CTA winds down
   } else if (!p.a_tma && warp < 2 + p.n_epi + n_prod) {
-    // ---------------------------------------------------------------- operand prologue, direct loads (A tiles)
-    // (rows that are not 16-byte aligned, odd row lengths)
+    // ---------------------------------------------------------------- operand prologue (A tiles from rows)
     const int np_all = n_prod * 32;
     const int pt_all = threadIdx.x - (2 + p.n_epi) * 32;  // 0..np_all-1
     const int pw = warp - (2 + p.n_epi);
@@ -1768,20 +1549,12 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   AMOE_REQUIRE(!p.cache_hi || (p.Kc % 8 == 0 && aligned16(p.cache_hi) && aligned16(p.cache_lo)), AMOE_ERR_BAD_SHAPE);
   if (f16) p.epi.out_cache_lo = nullptr;
 
-  // The staged prologue needs 16-byte aligned rows whose length is a multiple of 8 elements.
-  p.staged = !p.a_tma && p.vec_ok && p.Kc % 8 == 0;
-  p.item_mode = p.a_tma && !is_dx && p.n_tiles > 1;
   p.a_bytes = a_split ? 2 * kATile : kATile;
   p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
   p.stage_bytes = p.a_bytes + p.b_bytes * (b_split ? 2u : 1u);
   p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
-  p.stg_slot = p.staged ? static_cast<uint32_t>(kBM * kBK * esz) : 0u;
-  if (p.staged && (kSmemBudget - p.stg_slot * kStageSlots) / p.stage_bytes < 2) {
-    p.staged = 0;               // wide split-precision stages leave no room for the staging slots
-    p.stg_slot = 0;
-  }
-  const uint32_t stg_bytes = p.stg_slot * kStageSlots;
-  p.stages = static_cast<int>((kSmemBudget - stg_bytes) / p.stage_bytes);
+  p.item_mode = p.a_tma && !is_dx && p.n_tiles > 1;
+  p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
@@ -1797,18 +1570,9 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
     double best = 1e300;
-    if (p.staged) {
-      // the staged prologue runs on 8 or 16 warps (a thread owns whole 16-byte chunks of 4 or 2 rows)
-      const int cand[2][2] = {{16, 4}, {8, 12}};
-      for (const auto& c : cand) {
-        const double t = fmax(work_p / c[0], work_e / c[1]);
-        if (t < best) { best = t; p.n_prod = c[0]; p.n_epi = c[1]; }
-      }
-    } else {
-      for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
-        const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
-        if (t < best) { best = t; p.n_epi = ne; p.n_prod = kWorkerWarps - ne; }
-      }
+    for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
+      const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
+      if (t < best) { best = t; p.n_epi = ne; p.n_prod = kWorkerWarps - ne; }
     }
     if (p.a_tma) {
       // no prologue: the epilogue groups that share the tile's chunks most evenly (fewest warps on a tie)
@@ -1821,9 +1585,9 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       p.n_prod = 0;
     }
   }
-  // direct-load prologue: two groups on alternate stages (both groups have the same number of warps, so every stage's
+  // prologue warps: two groups on alternate stages (both groups have the same number of warps, so every stage's
   // barrier expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
-  if (!p.a_tma && !p.staged && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && p.n_prod >= 8 && p.n_prod % 2 == 0)
+  if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && p.n_prod >= 8 && p.n_prod % 2 == 0)
     p.prod_groups = 2;
   // per-warp staging of the column scales: chunks per warp x 16 floats, two arrays
   {
@@ -1832,7 +1596,6 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     p.cs_off = static_cast<uint32_t>(p.stages) * p.stage_bytes + 8u * kNumBars + 64u;
   }
   const uint32_t cs_bytes = static_cast<uint32_t>(p.n_epi) * 2u * p.cs_per_warp * sizeof(float);
-  p.stg_off = (p.cs_off + cs_bytes + 127u) & ~127u;
 
   CUtensorMap m_hi, m_lo;
   s = encode_tmap_bf16_3d(&m_hi, a->w_hi, static_cast<uint64_t>(k_pad), static_cast<uint64_t>(n_pad),
@@ -1854,7 +1617,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       if (s != AMOE_OK) return s;
     }
   }
-  const uint32_t smem = p.stg_off + stg_bytes + kSmemExtra;
+  const uint32_t smem = p.cs_off + cs_bytes + kSmemExtra;
   const int64_t max_tiles = ((a->P + kBM - 1) / kBM + a->E) * (p.item_mode ? p.n_tiles : 1);
   const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
   const bool f32 = a->a_dtype == AMOE_F32;

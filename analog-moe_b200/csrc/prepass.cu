@@ -269,22 +269,50 @@ __global__ void __launch_bounds__(256) transform_kernel(PrepassDev p) {
 // integers; NaNs are skipped).  `out` must be zero before the launch.
 template <typename T>
 __global__ void tensor_absmax_kernel(const T* __restrict__ x, int64_t rows, int K, int64_t stride,
-                                     const int32_t* __restrict__ n_rows_dev, float* __restrict__ out) {
+                                     const int32_t* __restrict__ n_rows_dev, float* __restrict__ out, int vec) {
   int64_t n = rows;
   if (n_rows_dev != nullptr) n = min(static_cast<int64_t>(max(*n_rows_dev, 0)), rows);
-  const int warps = (gridDim.x * blockDim.x) >> 5;
-  const int lane = threadIdx.x & 31;
   float m = 0.f;
-  for (int64_t r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += warps) {
-    const T* row = x + r * stride;
-    for (int k = lane; k < K; k += 32) {
-      const float v = fabsf(to_f32<T>(row[k]));
-      if (v == v) m = fmaxf(m, v);
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthr = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  if (vec) {
+    // rows are contiguous and 16-byte aligned: one flat stream of 16-byte pieces, four in flight per thread
+    constexpr int per = 16 / sizeof(T);
+    const uint4* p = reinterpret_cast<const uint4*>(x);
+    const int64_t total = n * K / per;
+    for (int64_t i = tid; i < total; i += 4 * nthr) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = (i + u * nthr < total) ? __ldg(p + i + u * nthr) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (sizeof(T) == 4) {
+            const float f = fabsf(__uint_as_float(w[j]));
+            if (f == f) m = fmaxf(m, f);
+          } else {
+            const float a = fabsf(__uint_as_float(w[j] << 16)), b2 = fabsf(__uint_as_float(w[j] & 0xffff0000u));
+            if (a == a) m = fmaxf(m, a);
+            if (b2 == b2) m = fmaxf(m, b2);
+          }
+        }
+      }
+    }
+  } else {
+    const int lane = threadIdx.x & 31;
+    for (int64_t r = tid >> 5; r < n; r += nthr >> 5) {
+      const T* row = x + r * stride;
+      for (int k = lane; k < K; k += 32) {
+        const float v = fabsf(to_f32<T>(row[k]));
+        if (v == v) m = fmaxf(m, v);
+      }
     }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
 }
 
 template <typename T>
@@ -395,11 +423,14 @@ int amoe_tensor_absmax(const void* x, int32_t dtype, int64_t rows, int32_t K, in
   AMOE_REQUIRE(rows > 0 && K > 0, AMOE_ERR_BAD_SHAPE);
   AMOE_CUDA(cudaMemsetAsync(absmax, 0, sizeof(float), stream));
   const unsigned blocks = static_cast<unsigned>(sm_count()) * 8u;
+  const int esz = dtype == AMOE_F32 ? 4 : 2;
+  const int vec = stride == K && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (static_cast<int64_t>(K) * esz) % 16 == 0;
   if (dtype == AMOE_F32)
-    tensor_absmax_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), rows, K, stride, n_rows_dev, absmax);
+    tensor_absmax_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const float*>(x), rows, K, stride, n_rows_dev, absmax,
+                                                            vec);
   else if (dtype == AMOE_BF16)
     tensor_absmax_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), rows, K, stride,
-                                                                    n_rows_dev, absmax);
+                                                                    n_rows_dev, absmax, vec);
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("tensor_absmax");

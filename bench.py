@@ -214,38 +214,47 @@ def ep_parity_gate(cfg, rank, world, device, group):
 
 
 def single_gpu_parity_gate(cfg, device, precision):
-    """Beside a single-GPU line: a small noise-free layer step (DAC + ADC, decay on) in the precision that is timed
-    against the same step on the CUDA-core fp32 kernels (the reference's own fp32 arithmetic): outputs and gradients
-    relative to their scale, and the number of ADC codes of the down-projection that differ (they may, by one code,
-    where the pre-rounding value sits on a rounding tie and the summation order decides)."""
-    from analog_moe import AnalogSigmaMoELayer, TorchInferenceRPUConfig, _cabi
+    """Beside a single-GPU line: one projection of the benchmark's kind (DAC + ADC, per-expert input ranges, no noise) in
+    the precision that is timed against the same calls on the CUDA-core fp32 kernels (the reference's own fp32
+    arithmetic), call by call on the same inputs - forward, input gradient with clip mask and per-slot input-range
+    gradient, weight gradient.  Reported: the ADC codes that differ (they may, by one code, where the pre-rounding
+    value sits next to a rounding tie) and the largest error of each result relative to its scale; forward values are
+    compared where the codes agree.  (Whole layers are not compared here: a hidden activation that crosses a DAC tie
+    changes the second projection's input by a whole quantisation step, which says nothing about the kernels.)"""
+    from analog_moe import ops, _cabi
     dtype = torch.float32 if cfg["dtype"] == "fp32" else torch.bfloat16
-    D, F, E, k, T = 256, 128, cfg["E"], cfg["k"], 512
-    rc = TorchInferenceRPUConfig()
-    rc.forward.inp_res, rc.forward.out_res, rc.forward.out_bound = 254.0, cfg.get("out_res", 254.0), OUT_BOUND
-    rc.pre_post.input_range.decay = 0.01
-    torch.manual_seed(0)
-    layer = AnalogSigmaMoELayer(rc, d_model=D, n_experts=E, expert_size=F, k=k, precision=precision).to(device).to(dtype)
-    layer.train()
-    layer.keep_codes = True
+    T, k, D, F, E = 1024, cfg["k"], 512, cfg["F"], cfg["E"]
+    P = T * k
     g = torch.Generator().manual_seed(3)
-    x0 = torch.randn(1, T, D, generator=g).to(device).to(dtype)
-    gy = torch.randn(1, T, D, generator=g).to(device).to(dtype)
+    mk = lambda *shape, scale=1.0: (torch.randn(*shape, generator=g) * scale).to(device).to(dtype)
+    r = ops.select_sort(torch.randn(T, E, generator=g).to(device), k)
+    x, W, gy = mk(T, D), mk(E, D, F, scale=D ** -0.5), mk(P, F)
+    ir = torch.linspace(2.0, 3.5, E, device=device)
+    out_res = cfg.get("out_res", 254.0)
     res = {}
+    if precision is None:
+        precision = ops.default_precision(dtype)
     for name, prec in (("timed", precision), ("fp32", _cabi.PREC_FP32_SIMT)):
-        layer.precision = prec
-        layer.zero_grad()
-        x = x0.clone().requires_grad_()
-        y, _ = layer(x)
-        y.backward(gy)
-        res[name] = [y.detach().float(), x.grad.float(), layer.keys.grad.float().clone(), layer.values.grad.float().clone(),
-                     layer.input_range.grad.float().clone(), layer.last_codes.clone()]
-    rel = lambda a, b: float((a - b).abs().max()) / max(1.0, float(b.abs().max()))
-    errs = [rel(a, b) for a, b in zip(res["timed"][:5], res["fp32"][:5])]
-    dc = (res["timed"][5].int() - res["fp32"][5].int()).abs()
-    return dict(max_rel=max(errs), code_mismatches=int((dc > 0).sum()), codes=int(dc.numel()), max_code_distance=int(dc.max()),
-                what="noise-free layer step in the timed precision vs the CUDA-core fp32 kernels: y, dx, dkeys, dvalues, "
-                     "d_input_range relative to their scale; ADC codes of the down-projection that differ")
+        pw = ops.weight_prepass(W, prec)
+        out, codes = ops.cvmm_fwd(x, r.token_index, r.slot_index, r.expert_offsets, pw, prec, P=P, dst_rows=P, ir=ir,
+                                  ir_by_expert=True, inp_res=2.0 / 254.0, out_res=out_res, out_bound=OUT_BOUND,
+                                  want_codes=True)
+        dx, irg = ops.cvmm_dx(gy, r.slot_index, r.slot_index, r.expert_offsets, pw, prec, P=P, dst_rows=P, x_ref=x,
+                              x_ref_row=r.token_index, ir=ir, ir_by_expert=True, want_ir_grad=True,
+                              g_absmax=ops.grad_absmax(gy, prec))
+        dw = ops.cvmm_dw(x, r.token_index, gy, r.slot_index, r.expert_offsets, E, prec, P=P, ir=ir, ir_by_expert=True,
+                         g_absmax=ops.grad_absmax(gy, prec))
+        res[name] = dict(out=out.float(), codes=codes.int(), dx=dx.float(), ir_grad=irg.float(), dw=dw.float())
+    a, b = res["timed"], res["fp32"]
+    dc = (a["codes"] - b["codes"]).abs()
+    same = dc == 0
+    rel = lambda u, v: float((u - v).abs().max()) / max(float(v.abs().max()), 1e-30)
+    per = dict(forward=float(((a["out"] - b["out"]).abs() * same).max()) / float(b["out"].abs().max()),
+               dx=rel(a["dx"], b["dx"]), ir_grad=rel(a["ir_grad"], b["ir_grad"]), dw=rel(a["dw"], b["dw"]))
+    return dict(max_rel=max(per.values()), per_result=per, code_mismatches=int((dc > 0).sum()), codes=int(dc.numel()),
+                max_code_distance=int(dc.max()),
+                what="timed precision vs the CUDA-core fp32 kernels, call by call on the same inputs (noise off): errors "
+                     "relative to each result's scale; ADC codes that differ")
 
 
 def run_ours(args, cfg, rank, world, device):
@@ -260,8 +269,10 @@ def run_ours(args, cfg, rank, world, device):
     if world > 1:
         import torch.distributed as dist
         group = dist.group.WORLD
-    parity = ep_parity_gate(cfg, rank, world, device, group) if world > 1 else \
-        single_gpu_parity_gate(cfg, device, precision)
+    parity = None
+    if not args.steps_only:
+        parity = ep_parity_gate(cfg, rank, world, device, group) if world > 1 else \
+            single_gpu_parity_gate(cfg, device, precision)
     layer = build_layer(cfg, device, dtype, precision, ep_group=group)
     n_sets = 8
     xs_h, gys_h = make_inputs(cfg, 100 + rank, device, dtype, n_sets)
@@ -282,6 +293,12 @@ def run_ours(args, cfg, rank, world, device):
     for i in range(args.warmup):
         step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
     barrier()
+    if args.steps_only:
+        # the command to put under a profiler: warm-up, then the steps themselves, eagerly, and nothing else
+        for i in range(args.steps):
+            step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
+        barrier()
+        return None
     if args.kernel_times:
         from analog_moe.profiling import kernel_times
         kernel_times(args.kernel_times, lambda i: step(layer, xs[i % n_sets], gys[i % n_sets], bwd), rank, world)
@@ -552,6 +569,8 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--no-gpu-baseline", action="store_true", help="skip the reference-Triton leg (profiling runs)")
+    ap.add_argument("--steps-only", action="store_true",
+                    help="run warm-up and the steps eagerly and exit (no parity gate, baselines or other legs): for profilers")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every step eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--kernel-times", default=None, metavar="PATH",

@@ -299,6 +299,36 @@ int64_t amoe_padded_rows(int64_t P, int32_t E);
 int amoe_cvmm_fwd(const amoe_cvmm_args* args, amoe_stream_t stream);
 int amoe_cvmm_dx(const amoe_cvmm_args* args, amoe_stream_t stream);
 
+/* Operand pre-pass: the A operand of amoe_cvmm_fwd / amoe_cvmm_dx as the tiles those calls take through a_tile_hi /
+ * a_tile_lo, written by a streaming kernel of its own.  It is the top of the reference's matmul loop - load the
+ * gathered row, clamp to +-ir, divide by ir and the abs-max, divide by the resolution, round (cvmm.py:139-172) - taken
+ * out of the tensor-core kernel, where it runs on few threads and is latency-bound, into a pass that is HBM-bound.
+ * Same arithmetic, same IEEE-exact quotients, same integer codes as the in-kernel path.
+ *   dac != 0 (forward operand): tile = DAC codes (inp_res > 0) or the normalised rows, `cache` (optional) =
+ *     clamp(A[r,:], +-ir) * cache_scale[a_row[i]]: the x operand of amoe_cvmm_dw from caches;
+ *   dac == 0 (gradient operand): tile = the gathered rows converted (AMOE_PREC_F16X1: times the power of two derived
+ *     from *g_absmax_dev, see amoe_cvmm_args.a_absmax_dev); the same array serves amoe_cvmm_dx as a_tile_hi and
+ *     amoe_cvmm_dw as its g operand.  cache_hi must be NULL.
+ * Element type of the arrays: IEEE fp16 for AMOE_PREC_F16X1, bf16 otherwise (`lo` arrays: bf16 rounding residuals,
+ * AMOE_PREC_SPLIT only, may be NULL).  Layout [K/64][cache_rows][64] by padded tile row, rows past an expert's last
+ * slot written as zeros; needs K % 64 == 0, 16-byte aligned rows, cache_rows >= amoe_padded_rows(P, E).
+ * Source rows out of range are reported in dev_status (AMOE_ERR_INDEX_RANGE) and written as zeros. */
+typedef struct amoe_operand_tiles_args {
+  int64_t P; int32_t E; int32_t K;
+  int32_t precision;              /* amoe_precision (not AMOE_PREC_FP32_SIMT) */
+  const int32_t* expert_offsets;  /* [E+1] */
+  const void* a; int32_t a_dtype; int64_t a_stride; int64_t a_rows;
+  const int32_t* a_row; int32_t a_row_div;
+  int32_t dac;
+  const float* ir; int32_t ir_by_expert; const float* a_absmax; float inp_res;   /* as in amoe_cvmm_args */
+  void* tile_hi; void* tile_lo;
+  void* cache_hi; void* cache_lo; const float* cache_scale;
+  int64_t cache_rows;
+  const float* g_absmax_dev;
+  int32_t* dev_status;
+} amoe_operand_tiles_args;
+int amoe_operand_tiles(const amoe_operand_tiles_args* args, amoe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------
  * dW.  Replaces cvmm_backward_kernel3 + cvmm_triton_backward (cvmm.py:234-397, 645-696) and the
  * outer product that feeds it in the down-projection (cvmm.py:789):

@@ -134,8 +134,8 @@ def test_config2_single_node_step_equals_the_composition(dev, prec, monkeypatch)
         assert torch.isfinite(a).all(), key
         # weight gradients: two factorings of the bf16 hi/lo split; the rest: gates from two sigmoid / matmul kernels
         tol = 3e-5 if key in ("dkeys", "dvalues") else 1e-5
-        if prec == "f16" and key in ("dkeys", "dvalues"):
-            tol = 5e-4       # gate * h (cache) against gate * gy (rows), each rounded to fp16's 11 bits
+        if prec == "f16" and key != "y":
+            tol = 1e-3       # fp16 tiles of the hidden gradient / gate * h in one path, fp32 rows / gate * gy in the other
         scale = max(1.0, float(b.abs().max()))
         err = float((a - b).abs().max())
         assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"

@@ -440,6 +440,10 @@ def test_layer_module_vs_oracle(dev, prec, dtype):
     # fp32: 1e-4 of the scale, except where the hidden activation's DAC code flips (see the call-by-call
     # test); bf16: activations are rounded to 8 bits between the calls
     tol = 2e-3 if dtype == torch.float32 else 3e-2
+    if prec == "f16x1":
+        # fp16 weights move a hidden activation by ~2e-4 of its scale; where that crosses a DAC rounding tie the second
+        # call sees a whole quantisation step (1/127 of the range), a few per cent of the hidden units
+        tol = 1e-2
     for name, got, want in [("y", f(y).view(T, D), yo), ("dx", f(x.grad).view(T, D), go["dx"]),
                             ("dkeys", f(layer.keys.grad), go["dkeys"]), ("dvalues", f(layer.values.grad), go["dvalues"]),
                             ("d_ir", f(layer.input_range.grad), go["d_input_range"]),
@@ -502,8 +506,10 @@ def test_fused_layer_step_equals_the_composition(dev, prec, dtype, use_ir, dims)
         assert torch.isfinite(a).all(), key
         # (and the gate logits come from two different matmul kernels, so the gates differ in their last bits)
         tol = 2e-2 if dtype != torch.float32 else (3e-5 if key in ("dkeys", "dvalues") and prec != "simt" else 1e-5)
-        if prec == "f16x1":     # the two paths round gate * h (cache) and gate * gy (rows) to fp16 in different places
-            tol = 5e-4 if key in ("dkeys", "dvalues") else 1e-5
+        if prec == "f16x1":
+            # the fused step hands the hidden gradient on as fp16 tiles and multiplies the gate into h before the fp16
+            # rounding; the composition passes fp32 rows and multiplies it into gy: 2^-12 per operand either way
+            tol = 1e-5 if key == "y" else 1e-3
         scale = max(1.0, float(b.abs().max()))
         err = float((a - b).abs().max())
         assert err <= tol * scale, f"{key}: {err:.3e} vs scale {scale:.3g}"
@@ -620,9 +626,11 @@ def test_device_driven_exchange_emulated_ranks(dev, G, E, k, dtype):
     back_ptrs = torch.tensor([t.data_ptr() for t in back], dtype=torch.int64, device=dev)
     plans = [ops.ep_plan(counts, r) for r in range(G)]
     dc = ops.dtype_code(xs[0])
+    status = ops.new_status(dev)
     for r in range(G):
         st = lib.amoe_ep_put(xs[r].data_ptr(), dc, D, D, Ts[r], routes[r].token_index.data_ptr(), 1, None, Ts[r] * k,
-                             routes[r].sel.data_ptr(), El, plans[r].data_ptr(), recv_ptrs.data_ptr(), G, cap, stream_ptr())
+                             routes[r].sel.data_ptr(), El, plans[r].data_ptr(), recv_ptrs.data_ptr(), G, cap,
+                             status.data_ptr(), stream_ptr())
         assert st == 0
     torch.cuda.synchronize()
     for d in range(G):
@@ -647,9 +655,27 @@ def test_device_driven_exchange_emulated_ranks(dev, G, E, k, dtype):
         for e in range(El):
             assert bool((owner[order[int(eo[e]):int(eo[e + 1])].long()] == d * El + e).all())
         st = lib.amoe_ep_put_back(recv[d].data_ptr(), dc, D, D, plans[d].data_ptr(), back_ptrs.data_ptr(), G, cap, p_cap,
-                                  stream_ptr())
+                                  status.data_ptr(), stream_ptr())
         assert st == 0
     torch.cuda.synchronize()
     for r in range(G):                                         # round trip: every rank gets its sorted rows back
         P = Ts[r] * k
         assert torch.equal(back[r][:P], xs[r][routes[r].token_index.long()])
+    ops.raise_on_device_status(status, "exchange")             # nothing was dropped
+    # buffers too small for the plan: the kernels say so in the status word and write nothing out of bounds
+    small = torch.full((8, D), float("nan"), device=dev, dtype=dtype)
+    small_ptrs = torch.tensor([small.data_ptr()] * G, dtype=torch.int64, device=dev)
+    st = lib.amoe_ep_put(xs[0].data_ptr(), dc, D, D, Ts[0], routes[0].token_index.data_ptr(), 1, None, Ts[0] * k,
+                         routes[0].sel.data_ptr(), El, plans[0].data_ptr(), small_ptrs.data_ptr(), G, 8,
+                         status.data_ptr(), stream_ptr())
+    assert st == 0
+    import ctypes as C
+    host = (C.c_int32 * 4)()
+    assert lib.amoe_read_device_status(status.data_ptr(), C.byref(host), stream_ptr()) == 8    # AMOE_ERR_INDEX_RANGE
+    order = torch.full((16,), -7, dtype=torch.int32, device=dev)
+    offs = torch.empty(El + 1, dtype=torch.int32, device=dev)
+    status.zero_()
+    assert lib.amoe_ep_local_plan_dev(plans[1].data_ptr(), G, El, 8, order.data_ptr(), offs.data_ptr(), status.data_ptr(),
+                                      stream_ptr()) == 0
+    assert lib.amoe_read_device_status(status.data_ptr(), C.byref(host), stream_ptr()) == 8
+    assert bool((order[8:] == -7).all())                       # nothing written past the 8 rows the array holds

