@@ -94,6 +94,7 @@ struct TcParams {
   int E, Kc, Nout;
   int n_epi;   // epilogue warps (multiple of 4)
   int n_prod;  // operand-prologue warps; n_epi + n_prod <= kWorkerWarps
+  uint32_t tr_off;  // offset of the epilogue warps' exchange blocks (kTrBytesPerWarp each) in dynamic shared memory
   int a_split, b_split;
   int BN, n_tiles, k_chunks, stages;
   int prod_groups;      // 1, or 2: the prologue warps form two groups that take alternate stages, so that one
@@ -280,33 +281,40 @@ struct __align__(16) RowMeta {
 // chunk entirely inside the row).
 //
 // A thread owns one row of the accumulator, so a plain vector store would touch 32 different cache
-// lines per instruction.  Instead the four threads of a quad exchange 4x4 blocks (two butterfly
-// rounds of shuffles): afterwards thread j of the quad holds columns 4j..4j+3 of the quad's four rows
-// and every store instruction writes 64 contiguous bytes per row, eight rows at a time.  The same
-// exchange (it is its own inverse) turns coalesced loads of the clip reference into the row-owner
-// layout.  All 32 lanes take part; rows that must not be written carry dst = -1.
-__device__ __forceinline__ void quad_transpose(float v[16], int lane) {
-  const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+// lines per instruction.  Instead the warp turns its 32 x 16 block through a private piece of shared
+// memory (32 rows of 80 bytes: 64 of data, 16 of padding that keeps both access patterns free of bank
+// conflicts): written by row owners, read back so that thread j of a quad holds columns 4j..4j+3 of the
+// quad's four rows - every global store then writes 64 contiguous bytes per row, eight rows at a time.
+// The reverse exchange turns coalesced loads of the clip reference into the row-owner layout.  Eight
+// shared-memory instructions per thread and exchange (a shuffle network took 16 shuffles and 48 selects).
+// All 32 lanes take part; rows that must not be written carry dst = -1.
+constexpr int kTrRowFloats = 20;                          // 80 bytes
+constexpr uint32_t kTrBytesPerWarp = 32 * kTrRowFloats * 4;   // 2560
+
+// t[i] = columns 4*(lane&3).. of row (lane & ~3) + i   ->   v = the 16 columns of row `lane`
+__device__ __forceinline__ void rows_to_owner(float* tr, const float4 t[4], float v[16], int lane) {
+  float* w = tr + (lane & ~3) * kTrRowFloats + 4 * (lane & 3);
 #pragma unroll
-  for (int pr = 0; pr < 2; ++pr) {          // blocks (0,1) and (2,3) across lanes differing in bit 0
-    const int lo = 8 * pr, hi = 8 * pr + 4;
+  for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(w + i * kTrRowFloats) = t[i];
+  __syncwarp();
+  const float* r = tr + lane * kTrRowFloats;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float send = b0 ? v[lo + c] : v[hi + c];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-      if (b0) v[lo + c] = recv; else v[hi + c] = recv;
-    }
+  for (int c = 0; c < 4; ++c) {
+    const float4 u = *reinterpret_cast<const float4*>(r + 4 * c);
+    v[4 * c] = u.x; v[4 * c + 1] = u.y; v[4 * c + 2] = u.z; v[4 * c + 3] = u.w;
   }
+  __syncwarp();
+}
+// the inverse: v = the 16 columns of row `lane`   ->   t[i] = columns 4*(lane&3).. of row (lane & ~3) + i
+__device__ __forceinline__ void owner_to_rows(float* tr, const float v[16], float4 t[4], int lane) {
+  float* w = tr + lane * kTrRowFloats;
 #pragma unroll
-  for (int pr = 0; pr < 2; ++pr) {          // blocks (0,2) and (1,3) across lanes differing in bit 1
-    const int lo = 4 * pr, hi = 4 * pr + 8;
+  for (int c = 0; c < 4; ++c) *reinterpret_cast<float4*>(w + 4 * c) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  __syncwarp();
+  const float* r = tr + (lane & ~3) * kTrRowFloats + 4 * (lane & 3);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const float send = b1 ? v[lo + c] : v[hi + c];
-      const float recv = __shfl_xor_sync(0xffffffffu, send, 2);
-      if (b1) v[lo + c] = recv; else v[hi + c] = recv;
-    }
-  }
+  for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const float4*>(r + i * kTrRowFloats);
+  __syncwarp();
 }
 
 // Rows of the quad this lane belongs to: destination rows (or -1) and clip-reference rows.
@@ -315,20 +323,21 @@ struct QuadRows {
   int xrow[4];
 };
 
-__device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr, int n0, float v[16], int lane) {
+__device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr, int n0, const float v[16], int lane,
+                                          float* tr) {
   if (p.out == nullptr) return;     // codes only (uniform across the kernel)
-  quad_transpose(v, lane);
+  float4 t[4];
+  owner_to_rows(tr, v, t, lane);
   const int col = n0 + 4 * (lane & 3);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (qr.dst[i] >= 0) {
       const int64_t base = static_cast<int64_t>(qr.dst[i]) * p.out_stride + col;
       if (p.out_dtype == AMOE_F32)
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) =
-            make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = t[i];
       else
         *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) =
-            make_uint2(cvt_bf16x2(v[4 * i], v[4 * i + 1]), cvt_bf16x2(v[4 * i + 2], v[4 * i + 3]));
+            make_uint2(cvt_bf16x2(t[i].x, t[i].y), cvt_bf16x2(t[i].z, t[i].w));
     }
   }
 }
@@ -342,7 +351,7 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
 // sum below is one IEEE operation in the order (acc*res + (std*s)*z) * (1/s) -> clamp -> * (1/step) -> round.
 template <bool kValue, bool F16, bool NOISE, bool ADC>
 __device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
-                                                float v[16], const float* cs, const float* cis, int lane) {
+                                                float v[16], const float* cs, const float* cis, int lane, float* tr) {
   constexpr float kMagic = 12582912.f;
   const float post = c.absmax * c.ir;
   const f32x2 accmul2 = pack2(p.acc_mul, p.acc_mul), nstd2 = pack2(p.noise_std, p.noise_std);
@@ -442,52 +451,54 @@ __device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx
       }
     }
   }
-  if (kValue) store16_t(p, qr, n0, v, lane);
+  if (kValue) store16_t(p, qr, n0, v, lane, tr);
 }
 
 template <bool kValue, bool F16>
 __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& c, const QuadRows& qr, int n0,
-                                              float v[16], const float* cs, const float* cis, int lane) {
+                                              float v[16], const float* cs, const float* cis, int lane, float* tr) {
   const bool noise = p.noise_std > 0.f, adc = p.adc.on;
-  if (noise && adc) epi_chunk_fwd_t<kValue, F16, true, true>(p, c, qr, n0, v, cs, cis, lane);
-  else if (adc) epi_chunk_fwd_t<kValue, F16, false, true>(p, c, qr, n0, v, cs, cis, lane);
-  else if (noise) epi_chunk_fwd_t<kValue, F16, true, false>(p, c, qr, n0, v, cs, cis, lane);
-  else epi_chunk_fwd_t<kValue, F16, false, false>(p, c, qr, n0, v, cs, cis, lane);
+  if (noise && adc) epi_chunk_fwd_t<kValue, F16, true, true>(p, c, qr, n0, v, cs, cis, lane, tr);
+  else if (adc) epi_chunk_fwd_t<kValue, F16, false, true>(p, c, qr, n0, v, cs, cis, lane, tr);
+  else if (noise) epi_chunk_fwd_t<kValue, F16, true, false>(p, c, qr, n0, v, cs, cis, lane, tr);
+  else epi_chunk_fwd_t<kValue, F16, false, false>(p, c, qr, n0, v, cs, cis, lane, tr);
 }
 
 // `cache_mul`: the operand cache keeps the result times this power of two (the gradient scale of fp16 operands).
-template <bool F16>
-__device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
-                                             int lane, float cache_mul) {
-  if (p.x_ref) {
+// XREF / IR / RELU / CACHE are compile-time copies of the launch's options (x_ref given, input ranges given, ReLU
+// mask, result rows also written as an operand cache); the caller dispatches once per chunk.
+template <bool F16, bool XREF, bool IR, bool RELU, bool CACHE>
+__device__ __forceinline__ void epi_chunk_dx_t(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
+                                               int lane, float cache_mul, float* tr) {
+  if (XREF) {
     float xr[16];
+    float4 t[4];
     const int col = n0 + 4 * (lane & 3);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (qr.xrow[i] >= 0) {
         const int64_t xi = static_cast<int64_t>(qr.xrow[i]) * p.x_ref_stride + col;
         if (p.x_ref_dtype == AMOE_F32) {
-          t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + xi));
+          t[i] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + xi));
         } else {
           const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.x_ref) + xi));
-          t = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
-                          __uint_as_float(u.y & 0xffff0000u));
+          t[i] = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
+                             __uint_as_float(u.y & 0xffff0000u));
         }
       }
-      xr[4 * i] = t.x; xr[4 * i + 1] = t.y; xr[4 * i + 2] = t.z; xr[4 * i + 3] = t.w;
     }
-    quad_transpose(xr, lane);     // back to "my row, 16 columns"
-    if (p.ir) {
+    rows_to_owner(tr, t, xr, lane);     // "my row, 16 columns"
+    if (IR) {
       // up = x >= ir adds min(g, 0), low = x <= -ir subtracts max(g, 0), everything else is kept (cvmm.py:863-870).
       // With t = g carrying x's sign flipped in (exact), both clipped cases are min(t, 0): one compare, one min.
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const float gs = v[j] * c.rs;
         const bool keep = fabsf(xr[j]) < c.ir;
-        const float t = __uint_as_float(__float_as_uint(gs) ^ (__float_as_uint(xr[j]) & 0x80000000u));
+        const float tj = __uint_as_float(__float_as_uint(gs) ^ (__float_as_uint(xr[j]) & 0x80000000u));
         const bool clipped = fabsf(xr[j]) >= c.ir;      // (false for a NaN reference, like `up` and `low`)
-        if (clipped) c.dir_acc += fminf(t, 0.f);
+        if (clipped) c.dir_acc += fminf(tj, 0.f);
         c.keep += keep ? 1u : 0u;
         v[j] = keep ? gs : 0.f;
       }
@@ -495,7 +506,7 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] *= c.rs;
     }
-    if (p.x_ref_relu) {
+    if (RELU) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) v[j] = xr[j] > 0.f ? v[j] : 0.f;
     }
@@ -503,7 +514,7 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] *= c.rs;
   }
-  if (p.out_cache_hi) {
+  if (CACHE) {
     // the row once more as bf16 hi (+ lo) terms at its padded tile row: the B operand of the next dW
     // layout [64-column block][padded row][64]; n0 is a multiple of 16, so the chunk stays inside one block
     const int64_t co = (((n0 >> 6) * p.out_cache_stride + c.pad_row) << 6) + (n0 & 63);
@@ -524,7 +535,23 @@ __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, cons
       }
     }
   }
-  store16_t(p, qr, n0, v, lane);
+  store16_t(p, qr, n0, v, lane, tr);
+}
+
+template <bool F16>
+__device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
+                                             int lane, float cache_mul, float* tr) {
+  const bool xref = p.x_ref != nullptr, ir = xref && p.ir != nullptr, relu = xref && p.x_ref_relu != 0;
+  const bool cache = p.out_cache_hi != nullptr;
+  // the two launches of a layer step, then the remaining combinations
+  if (xref && ir && relu && cache) epi_chunk_dx_t<F16, true, true, true, true>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (xref && ir && !relu && !cache) epi_chunk_dx_t<F16, true, true, false, false>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (!xref && !cache) epi_chunk_dx_t<F16, false, false, false, false>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (!xref) epi_chunk_dx_t<F16, false, false, false, true>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (ir && relu) epi_chunk_dx_t<F16, true, true, true, false>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (ir) epi_chunk_dx_t<F16, true, true, false, true>(p, c, qr, n0, v, lane, cache_mul, tr);
+  else if (cache) epi_chunk_dx_t<F16, true, false, true, true>(p, c, qr, n0, v, lane, cache_mul, tr);   // x_ref without ir: ReLU mask only
+  else epi_chunk_dx_t<F16, true, false, true, false>(p, c, qr, n0, v, lane, cache_mul, tr);
 }
 
 // Work items of one CTA: row tile t with all its n-tiles, or - item mode - one (row tile, n-tile) pair.
@@ -642,6 +669,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     const int chunks = p.BN / cw;
     float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
     float* cis_smem = cs_smem + p.cs_per_warp;
+    float* tr = reinterpret_cast<float*>(sm.base + p.tr_off) + ew * (kTrBytesPerWarp / 4);   // this warp's exchange block
     const bool need_cs = EPI == kEpiFwd && (p.epi.noise_std > 0.f || p.epi.adc.on);
     uint32_t acc_it = 0, sync_round = 0;
     bool alive = true;
@@ -703,10 +731,10 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             }
           } else {   // all 32 lanes: the quad exchange needs every lane, invalid rows are masked inside
             if (EPI == kEpiFwd) {
-              if (p.epi.out != nullptr) epi_chunk_fwd<true, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
-              else epi_chunk_fwd<false, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane);
+              if (p.epi.out != nullptr) epi_chunk_fwd<true, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane, tr);
+              else epi_chunk_fwd<false, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane, tr);
             }
-            else epi_chunk_dx<F16>(p.epi, ctx, qr, n0, v, lane, g_mul);
+            else epi_chunk_dx<F16>(p.epi, ctx, qr, n0, v, lane, g_mul, tr);
           }
         }
         tc_fence_before();
@@ -1550,13 +1578,17 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (f16) p.epi.out_cache_lo = nullptr;
 
   p.a_bytes = a_split ? 2 * kATile : kATile;
-  p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
-  p.stage_bytes = p.a_bytes + p.b_bytes * (b_split ? 2u : 1u);
-  p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
+  // two ring stages must fit beside the epilogue warps' exchange blocks: wide weight tiles in two terms are cut into
+  // narrower n-tiles where they do not
+  for (;;) {
+    p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
+    p.stage_bytes = p.a_bytes + p.b_bytes * (b_split ? 2u : 1u);
+    p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
+    if ((kSmemBudget - kWorkerWarps * kTrBytesPerWarp) / p.stage_bytes >= 2 || p.BN <= 64) break;
+    p.n_tiles *= 2;
+    p.BN = round_up((n_pad + p.n_tiles - 1) / p.n_tiles, 16);
+  }
   p.item_mode = p.a_tma && !is_dx && p.n_tiles > 1;
-  p.stages = static_cast<int>(kSmemBudget / p.stage_bytes);
-  if (p.stages > kMaxStages) p.stages = kMaxStages;
-  AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   p.tmem_cols = pow2_cols(2 * p.BN);
   p.prod_groups = 1;
   {
@@ -1585,6 +1617,11 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       p.n_prod = 0;
     }
   }
+  // the ring takes what the epilogue warps' exchange blocks leave of the budget
+  const uint32_t tr_bytes = static_cast<uint32_t>(p.n_epi) * kTrBytesPerWarp;
+  p.stages = static_cast<int>((kSmemBudget - tr_bytes) / p.stage_bytes);
+  if (p.stages > kMaxStages) p.stages = kMaxStages;
+  AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
   // prologue warps: two groups on alternate stages (both groups have the same number of warps, so every stage's
   // barrier expects the same number of arrivals whichever group fills it); needs enough stages per tile to alternate on
   if (!p.a_tma && p.stages >= 3 && p.k_chunks * p.n_tiles >= 4 && p.n_prod >= 8 && p.n_prod % 2 == 0)
@@ -1617,7 +1654,8 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       if (s != AMOE_OK) return s;
     }
   }
-  const uint32_t smem = p.cs_off + cs_bytes + kSmemExtra;
+  p.tr_off = (p.cs_off + cs_bytes + 15u) & ~15u;
+  const uint32_t smem = p.tr_off + tr_bytes + kSmemExtra;
   const int64_t max_tiles = ((a->P + kBM - 1) / kBM + a->E) * (p.item_mode ? p.n_tiles : 1);
   const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
   const bool f32 = a->a_dtype == AMOE_F32;

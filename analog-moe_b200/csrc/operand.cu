@@ -103,9 +103,107 @@ __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float 
   }
 }
 
+// The rows of one warp: rows w, w + 8, ... of the tile, four at a time (eight 16-byte loads in flight per lane); lane l
+// holds columns 8l .. 8l+7 of the block's column group.  IR / AM / CSC are compile-time copies of "input ranges
+// given", "abs-max given", "cache scale given" (kept as run-time flags they turn into selects inside the unrolled
+// element loops).
+template <int DAC, bool A_F32, bool F16, bool IR, bool AM, bool CSC>
+__device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row0, int rows, int64_t t, int w, int lane) {
+  const int k = blockIdx.y * kColsPerBlock + lane * 8;
+  const bool k_in = k < p.K;          // (all lanes stay for the shuffles; K % 64 == 0, so whole groups of 8 lanes leave)
+  const float rcp_res = quant_rcp(p.inp_res);
+  float g_mul = 1.f;
+  if (DAC == kDacNone && F16 && p.g_absmax != nullptr) { float inv; g_mul = grad_pow2_scale(__ldg(p.g_absmax), inv); }
+  float ir_e = 1.f;
+  if (IR && p.ir_by_expert) ir_e = p.ir[e];
+  const int64_t blk = static_cast<int64_t>(k >> 6) * p.cache_rows + t * kRows;    // + row, then * 64 + column in block
+  const int kin = k & 63;
+
+  // Row parameters once per row, not once per lane: lane l < 16 prepares row w + 8 l of this warp (source row - an
+  // integer division -, input range, abs-max and their correctly rounded reciprocals), the row loop fetches them by
+  // shuffle.
+  int m_src = -1;
+  float m_ir = ir_e, m_am = 1.f, m_csc = 1.f;
+  if (lane < 16) {
+    const int r = w + 8 * lane;
+    if (r < rows) {
+      const int64_t i = static_cast<int64_t>(row0) + r;
+      const int raw = p.a_row[i];
+      const int s = p.a_div == 1 ? raw : raw / p.a_div;
+      if (s < 0 || s >= p.a_rows) {
+        if (blockIdx.y == 0) report(p.status, AMOE_ERR_INDEX_RANGE, 30, static_cast<int>(i), s);
+      } else {
+        m_src = s;
+        if (IR && !p.ir_by_expert) m_ir = p.ir[i];
+        if (AM) m_am = p.a_absmax[s];
+        if (CSC) m_csc = p.cache_scale[raw];
+      }
+    }
+  }
+  const float m_rcp_ir = IR ? __frcp_rn(m_ir) : 1.f, m_rcp_am = AM ? __frcp_rn(m_am) : 1.f;
+
+#pragma unroll 1
+  for (int it = 0; it < 4; ++it) {
+    const int rb = w + 32 * it;
+    float v[4][8];
+    int src[4];
+    float irv[4], rirv[4], amv[4], ramv[4], csc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int l = 4 * it + j;
+      src[j] = __shfl_sync(0xffffffffu, m_src, l);
+      irv[j] = IR ? __shfl_sync(0xffffffffu, m_ir, l) : 1.f;
+      rirv[j] = IR ? __shfl_sync(0xffffffffu, m_rcp_ir, l) : 1.f;
+      amv[j] = AM ? __shfl_sync(0xffffffffu, m_am, l) : 1.f;
+      ramv[j] = AM ? __shfl_sync(0xffffffffu, m_rcp_am, l) : 1.f;
+      csc[j] = CSC ? __shfl_sync(0xffffffffu, m_csc, l) : 1.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (src[j] >= 0 && k_in) {
+        load8<A_F32>(p.a, static_cast<int64_t>(src[j]) * p.a_stride + k, v[j]);
+      } else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) v[j][x] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = rb + 8 * j;
+      const int64_t off = ((blk + r) << 6) + kin;
+      if (!k_in) continue;
+      if (DAC == kDacNone) {
+        if (F16) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) v[j][x] *= g_mul;
+        }
+        store8<F16>(p.tile_hi, p.tile_lo, off, v[j]);
+      } else {
+        if (IR) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) v[j][x] = clamp_ir(v[j][x], irv[j]);
+        }
+        if (p.cache_hi != nullptr) {
+          if (CSC) {
+            float c8[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) c8[x] = v[j][x] * csc[j];
+            store8<F16>(p.cache_hi, p.cache_lo, off, c8);
+          } else {
+            store8<F16>(p.cache_hi, p.cache_lo, off, v[j]);
+          }
+        }
+        if (p.tile_hi != nullptr) {
+          // (a row that is not read holds zeros, whose code is zero)
+          dac8(v[j], IR, irv[j], rirv[j], AM, amv[j], ramv[j], DAC == kDacQuant, p.inp_res, rcp_res);
+          store8<F16>(p.tile_hi, p.tile_lo, off, v[j]);
+        }
+      }
+    }
+  }
+}
+
 // grid.x = row tile (an upper bound: blocks past the last tile return), grid.y = group of 256 columns.
-// A warp takes rows w, w + 8, ... of the tile, four at a time (eight 16-byte loads in flight per lane); lane l
-// holds columns 8l .. 8l+7 of the block's column group.
 template <int DAC, bool A_F32, bool F16>
 __global__ void __launch_bounds__(kThreads, 3) operand_tiles_kernel(const OperandParams p) {
   __shared__ int s_tile[3];
@@ -143,94 +241,19 @@ __global__ void __launch_bounds__(kThreads, 3) operand_tiles_kernel(const Operan
   __syncthreads();
   const int e = s_tile[0], row0 = s_tile[1], rows = s_tile[2];
   if (e < 0) return;
-  const int k = blockIdx.y * kColsPerBlock + lane * 8;
-  const bool k_in = k < p.K;          // (all lanes stay for the shuffles; K % 64 == 0, so whole groups of 8 lanes leave)
-  const bool has_ir = DAC != kDacNone && p.ir != nullptr, has_am = DAC != kDacNone && p.a_absmax != nullptr;
-  const float rcp_res = quant_rcp(p.inp_res);
-  float g_mul = 1.f;
-  if (DAC == kDacNone && F16 && p.g_absmax != nullptr) { float inv; g_mul = grad_pow2_scale(__ldg(p.g_absmax), inv); }
-  float ir_e = 1.f;
-  if (has_ir && p.ir_by_expert) ir_e = p.ir[e];
-  const int64_t blk = static_cast<int64_t>(k >> 6) * p.cache_rows + t * kRows;    // + row, then * 64 + column in block
-  const int kin = k & 63;
-
-  // Row parameters once per row, not once per lane: lane l < 16 prepares row w + 8 l of this warp (source row - an
-  // integer division -, input range, abs-max and their correctly rounded reciprocals), the row loop fetches them by
-  // shuffle.
-  int m_src = -1;
-  float m_ir = ir_e, m_am = 1.f, m_csc = 1.f;
-  if (lane < 16) {
-    const int r = w + 8 * lane;
-    if (r < rows) {
-      const int64_t i = static_cast<int64_t>(row0) + r;
-      const int raw = p.a_row[i];
-      const int s = p.a_div == 1 ? raw : raw / p.a_div;
-      if (s < 0 || s >= p.a_rows) {
-        if (blockIdx.y == 0) report(p.status, AMOE_ERR_INDEX_RANGE, 30, static_cast<int>(i), s);
-      } else {
-        m_src = s;
-        if (has_ir && !p.ir_by_expert) m_ir = p.ir[i];
-        if (has_am) m_am = p.a_absmax[s];
-        if (DAC != kDacNone && p.cache_scale) m_csc = p.cache_scale[raw];
-      }
+  if (DAC == kDacNone) {
+    tile_rows<DAC, A_F32, F16, false, false, false>(p, e, row0, rows, t, w, lane);
+  } else {
+    const bool ir = p.ir != nullptr, am = p.a_absmax != nullptr, csc = p.cache_scale != nullptr && p.cache_hi != nullptr;
+#define AMOE_ROWS(IR, AM, CSC) tile_rows<DAC, A_F32, F16, IR, AM, CSC>(p, e, row0, rows, t, w, lane)
+    if (ir) {
+      if (am) { if (csc) AMOE_ROWS(true, true, true); else AMOE_ROWS(true, true, false); }
+      else { if (csc) AMOE_ROWS(true, false, true); else AMOE_ROWS(true, false, false); }
+    } else {
+      if (am) { if (csc) AMOE_ROWS(false, true, true); else AMOE_ROWS(false, true, false); }
+      else { if (csc) AMOE_ROWS(false, false, true); else AMOE_ROWS(false, false, false); }
     }
-  }
-  const float m_rcp_ir = has_ir ? __frcp_rn(m_ir) : 1.f, m_rcp_am = has_am ? __frcp_rn(m_am) : 1.f;
-
-#pragma unroll 1
-  for (int it = 0; it < 4; ++it) {
-    const int rb = w + 32 * it;
-    float v[4][8];
-    int src[4];
-    float irv[4], rirv[4], amv[4], ramv[4], csc[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int l = 4 * it + j;
-      src[j] = __shfl_sync(0xffffffffu, m_src, l);
-      irv[j] = has_ir ? __shfl_sync(0xffffffffu, m_ir, l) : 1.f;
-      rirv[j] = has_ir ? __shfl_sync(0xffffffffu, m_rcp_ir, l) : 1.f;
-      amv[j] = has_am ? __shfl_sync(0xffffffffu, m_am, l) : 1.f;
-      ramv[j] = has_am ? __shfl_sync(0xffffffffu, m_rcp_am, l) : 1.f;
-      csc[j] = (DAC != kDacNone && p.cache_scale) ? __shfl_sync(0xffffffffu, m_csc, l) : 1.f;
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (src[j] >= 0 && k_in) {
-        load8<A_F32>(p.a, static_cast<int64_t>(src[j]) * p.a_stride + k, v[j]);
-      } else {
-#pragma unroll
-        for (int x = 0; x < 8; ++x) v[j][x] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int r = rb + 8 * j;
-      const int64_t off = ((blk + r) << 6) + kin;
-      if (!k_in) continue;
-      if (DAC == kDacNone) {
-        if (F16) {
-#pragma unroll
-          for (int x = 0; x < 8; ++x) v[j][x] *= g_mul;
-        }
-        store8<F16>(p.tile_hi, p.tile_lo, off, v[j]);
-      } else {
-        if (has_ir) {
-#pragma unroll
-          for (int x = 0; x < 8; ++x) v[j][x] = clamp_ir(v[j][x], irv[j]);
-        }
-        if (p.cache_hi != nullptr) {
-          float c8[8];
-#pragma unroll
-          for (int x = 0; x < 8; ++x) c8[x] = p.cache_scale ? v[j][x] * csc[j] : v[j][x];
-          store8<F16>(p.cache_hi, p.cache_lo, off, c8);
-        }
-        if (p.tile_hi != nullptr) {
-          if (src[j] >= 0)
-            dac8(v[j], has_ir, irv[j], rirv[j], has_am, amv[j], ramv[j], DAC == kDacQuant, p.inp_res, rcp_res);
-          store8<F16>(p.tile_hi, p.tile_lo, off, v[j]);
-        }
-      }
-    }
+#undef AMOE_ROWS
   }
 }
 
