@@ -147,12 +147,55 @@ def select_sort(logits: torch.Tensor, k: int, apply_sigmoid: bool = True) -> Rou
     return Routing(raw_sel, gate, sel, tok, slot, off)
 
 
+_ROUTER_SMEM_LIMIT = 200 * 1024      # the router kernels that keep the whole [E, D] weight (or its gradient) in shared memory
+
+
+def _router_fits_smem(E: int, D: int) -> bool:
+    return E <= 64 and ((E + 15) // 16 * 16) * D * 4 <= _ROUTER_SMEM_LIMIT
+
+
+def _router_on_tensor_cores(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    """Routers too large for the shared-memory kernels run as one-expert CVMM calls on the tensor cores."""
+    E, D = w.shape
+    return not _router_fits_smem(E, D) and x2.dtype == w.dtype and D % 8 == 0 and x2.data_ptr() % 16 == 0 and \
+        (x2.stride(0) * x2.element_size()) % 16 == 0
+
+
+_IDENTITY_ROWS = {}
+
+
+def _identity_rows(T: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(0 .. T-1, [0, T]) as int32 device tensors: the row lists of a CVMM call whose single expert takes every row."""
+    key = (T, device)
+    hit = _IDENTITY_ROWS.get(key)
+    if hit is None:
+        if len(_IDENTITY_ROWS) >= 8:
+            _IDENTITY_ROWS.pop(next(iter(_IDENTITY_ROWS)))
+        hit = _IDENTITY_ROWS[key] = (torch.arange(T, dtype=torch.int32, device=device),
+                                     torch.tensor([0, T], dtype=torch.int32, device=device))
+    return hit
+
+
+def _router_precision(x2: torch.Tensor) -> int:
+    # fp32 routers: bf16 hi + lo terms (about 1e-5 of the logits' scale); bf16 routers: exact products
+    return A.PREC_SPLIT if x2.dtype == torch.float32 else A.PREC_BF16X1
+
+
 def router_logits(x2: torch.Tensor, w_sel: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """fp32 gate logits [T,E] of x2 [T,D] and w_sel [E,D] (rounded through bf16 when x2 is bf16)."""
     x2 = _rows(x2)
     w = w_sel.contiguous()
     T, D = x2.shape
     E = w.shape[0]
+    if _router_on_tensor_cores(x2, w):
+        # logits = x @ w^T as a CVMM with one expert that owns all T rows: weight [1, D, E] (a strided view, the weight
+        # pre-pass reads it in place), no DAC, no noise; bf16 routers round the result through bf16 like torch's matmul
+        prec = _router_precision(x2)
+        pw = weight_prepass(w.t().unsqueeze(0), prec, need_fwd=True, need_bwd=False)
+        rows, offsets = _identity_rows(T, x2.device)
+        out, _ = cvmm_fwd(x2, rows, rows, offsets, pw, prec, P=T, dst_rows=T)
+        out = out.float()
+        return out if bias is None else out + bias.float()
     out = torch.empty(T, E, dtype=torch.float32, device=x2.device)
     b = None if bias is None else bias.float().contiguous()
     _call("amoe_router_logits", ptr(x2), dtype_code(x2), x2.stride(0), T, D, ptr(w), dtype_code(w), E, ptr(b),
@@ -170,8 +213,8 @@ def router_select(x2: torch.Tensor, w_sel: torch.Tensor, k: int, bias: Optional[
     E = w.shape[0]
     dev = x2.device
     esz = x2.element_size()
-    fused = E <= 64 and D % 4 == 0 and (x2.stride(0) * esz) % 16 == 0 and (D * w.element_size()) % 16 == 0 and \
-        x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and ((E + 15) // 16 * 16) * D * 4 <= 200 * 1024
+    fused = _router_fits_smem(E, D) and D % 4 == 0 and (x2.stride(0) * esz) % 16 == 0 and \
+        (D * w.element_size()) % 16 == 0 and x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
     if not fused:
         logits = router_logits(x2, w, bias)
         return select_sort(logits, k, apply_sigmoid=True), logits
@@ -199,6 +242,15 @@ def router_backward_w(x2: torch.Tensor, dgate: torch.Tensor, gate: torch.Tensor,
     x2 = _rows(x2)
     T, D = x2.shape
     P = token_index.numel()
+    if raw_sel is not None and not _router_fits_smem(E, D) and D % 8 == 0 and x2.data_ptr() % 16 == 0 and \
+            (x2.stride(0) * x2.element_size()) % 16 == 0:
+        # dW = dlogits^T @ x as a one-expert weight gradient on the tensor cores: dlogits [T,E] dense (k non-zeros per
+        # row), contraction over the T rows; result [1, D, E] transposed back
+        prec = _router_precision(x2)
+        dl = gate_backward(dgate, gate, raw_sel, E, apply_sigmoid)
+        rows, off1 = _identity_rows(T, x2.device)
+        dw = cvmm_dw(x2, rows, dl, rows, off1, 1, prec, P=T)
+        return dw[0].t().contiguous()
     out = torch.empty(E, D, dtype=torch.float32, device=x2.device)
     nbytes = lib.amoe_router_backward_w_workspace_bytes(P, E, D)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=x2.device)

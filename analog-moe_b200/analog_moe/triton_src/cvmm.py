@@ -140,6 +140,14 @@ def _empty(like: torch.Tensor, dtype=None) -> torch.Tensor:
     return like.new_empty(0, dtype=dtype or like.dtype)
 
 
+def _tiles_eligible(x2: torch.Tensor, precision: int) -> bool:
+    """Whether the operand pre-pass feeds this call (decided from metadata only, so that the fake implementations agree
+    with the real ones): a tensor-core precision, 64-column blocks, rows that start on 16-byte boundaries."""
+    esz = x2.element_size()
+    return precision != A.PREC_FP32_SIMT and x2.shape[-1] % 64 == 0 and x2.stride(-1) == 1 and \
+        (x2.stride(0) * esz) % 16 == 0 and (x2.storage_offset() * esz) % 16 == 0
+
+
 # prepared weights of unmodified weight tensors, kept while the tensor has not been written to
 _PREPARED = {}
 
@@ -174,9 +182,11 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
                     noise_std: float, noise_seed: int, noise_offset: int, noise_step: Optional[torch.Tensor],
                     mod_std: float, mod_per_channel: bool, mod_discretize: float, mod_seed: int, mod_offset: int,
                     mod_step: Optional[torch.Tensor], out_res: float, out_bound: float, adc_codes_path: bool,
-                    save_codes: bool, check_status: bool) -> List[torch.Tensor]:
+                    save_codes: bool, check_status: bool, save_operands: bool) -> List[torch.Tensor]:
     """Forward CVMM (reference cvmm.py:529-631 plus the reduction of cvmm.py:757-759).
-    Returns [out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, col_scale]."""
+    Returns [out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, col_scale,
+    x_cache_hi, x_cache_lo]; the last two (with `save_operands`) hold the clamped input rows - times the reduction
+    weight, where there is one - as the weight gradient's operand."""
     A.require_cuda(x, keys)
     ops.set_tag("down" if reduction_weight is not None else "up")
     E, K, N = keys.shape
@@ -202,11 +212,21 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
     adc_on = out_res > 0 and out_bound > 0
     codes_path = adc_on and reduction_weight is not None and adc_codes_path
     row_meta = {} if codes_path else None
+    # The DAC of the gathered rows runs as a streaming pass of its own that leaves the A operand as TMA tiles (and, for
+    # the backward pass, the clamped rows as the weight gradient's operand); the tensor-core kernel runs no prologue.
+    a_kw, x_cache = {}, None
+    if _tiles_eligible(x2, precision):
+        csc = None if reduction_weight is None else reduction_weight.reshape(-1).float().contiguous()
+        tiles, x_cache = ops.operand_tiles(x2, sel_index_i, offsets, E, precision, P=P, dac=True, ir=ir, absmax=absmax,
+                                           inp_res=float(inp_res), want_cache=save_operands, cache_scale=csc,
+                                           status=status)
+        a_kw = dict(a_tiles=tiles)
     res, codes = ops.cvmm_fwd(
         x2, sel_index_i, dst, offsets, pw, precision, P=P, dst_rows=P, ir=ir, absmax=absmax,
         inp_res=float(inp_res), noise=out_noise, noise_std=noise_std, seed=noise_seed, offset=noise_offset,
         step_dev=noise_step, out_res=out_res if adc_on else -1.0, out_bound=out_bound if adc_on else -1.0,
-        want_codes=codes_path or (adc_on and save_codes), status=status, want_out=not codes_path, row_meta=row_meta)
+        want_codes=codes_path or (adc_on and save_codes), status=status, want_out=not codes_path, row_meta=row_meta,
+        **a_kw)
     row_scale = row_expert = None
     if reduction_weight is not None:
         k = reduction_weight.shape[-1]
@@ -233,14 +253,16 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
             row_scale if row_scale is not None else _empty(x2, torch.float32),
             row_expert if row_expert is not None else _empty(x2, torch.int32), w_mod,
             pw.bwd_hi if pw.bwd_hi is not None else _empty(x2, torch.bfloat16),
-            pw.bwd_lo if pw.bwd_lo is not None else _empty(x2, torch.bfloat16), pw.col_scale]
+            pw.bwd_lo if pw.bwd_lo is not None else _empty(x2, torch.bfloat16), pw.col_scale,
+            x_cache.hi if x_cache is not None else _empty(x2, torch.bfloat16),
+            x_cache.lo if (x_cache is not None and x_cache.lo is not None) else _empty(x2, torch.bfloat16)]
 
 
 @cvmm_forward_op.register_fake
 def _cvmm_forward_fake(x, sel_index, sel, keys, inp_res, input_ranges, out_index, reduction_weight, out_noise,
                        use_abs_max, expert_offsets, precision, scale_per_channel, noise_std, noise_seed, noise_offset,
                        noise_step, mod_std, mod_per_channel, mod_discretize, mod_seed, mod_offset, mod_step, out_res,
-                       out_bound, adc_codes_path, save_codes, check_status):
+                       out_bound, adc_codes_path, save_codes, check_status, save_operands):
     """Shapes only (reference cvmm.py:634-642)."""
     E, K, N = keys.shape
     P = sel.numel()
@@ -264,7 +286,13 @@ def _cvmm_forward_fake(x, sel_index, sel, keys, inp_res, input_ranges, out_index
     split = precision == A.PREC_SPLIT and (keys.dtype != torch.bfloat16 or modified)
     bwd_hi = new((0,) if simt else (E, kpad2, npad2), dtype=torch.bfloat16)
     bwd_lo = new((E, kpad2, npad2) if (split and not simt) else (0,), dtype=torch.bfloat16)
-    return [out, offsets, res_keep, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, new(E, N, dtype=torch.float32)]
+    x2 = x.reshape(-1, K)
+    cached = save_operands and _tiles_eligible(x2, precision)
+    cshape = (K // 64, int(ops.lib.amoe_padded_rows(P, E)), 64)
+    xc_hi = new(cshape if cached else (0,), dtype=torch.bfloat16)
+    xc_lo = new(cshape if (cached and precision == A.PREC_SPLIT) else (0,), dtype=torch.bfloat16)
+    return [out, offsets, res_keep, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo, new(E, N, dtype=torch.float32),
+            xc_hi, xc_lo]
 
 
 @torch.library.custom_op("amoe::cvmm_backward", mutates_args=())
@@ -275,8 +303,8 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
                      bwd_lo: Optional[torch.Tensor], col_scale: torch.Tensor, codes: Optional[torch.Tensor],
                      row_scale: Optional[torch.Tensor], row_expert: Optional[torch.Tensor], n_experts: int, N: int,
                      precision: int, decay: float, min_percentage: float, relative: bool, grad_scale: float,
-                     out_res: float, out_bound: float, need_x: bool, need_w: bool, need_ir: bool, need_gate: bool, check_status: bool
-                     ) -> List[torch.Tensor]:
+                     out_res: float, out_bound: float, need_x: bool, need_w: bool, need_ir: bool, need_gate: bool, check_status: bool,
+                     x_cache_hi: Optional[torch.Tensor], x_cache_lo: Optional[torch.Tensor]) -> List[torch.Tensor]:
     """Backward CVMM (reference cvmm.py:771-897).  Returns [grad_x, grad_w (fp32), grad_ir (per sorted slot), grad_gate]."""
     E = n_experts
     K = x.shape[-1]
@@ -300,7 +328,17 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
     rw = reduction_weight.reshape(-1).float().contiguous() if down else None
     gmax = ops.grad_absmax(g, precision)        # fp16 operands: the scalar that scales the gradient rows
     grad_w = _empty(x2)
-    if need_w:
+    # The upstream gradient rows, gathered per slot and converted by the operand pre-pass, serve both as the A tiles of
+    # the input gradient and - with the operand the forward pass saved - as the weight gradient's operands.
+    g_tiles = None
+    g_row_all = sel_index_i if down or out_index_i is None else out_index_i
+    if _tiles_eligible(g, precision) and (need_x or need_ir or (need_w and x_cache_hi is not None)):
+        g_tiles, _ = ops.operand_tiles(g, g_row_all, offsets, E, precision, P=P, a_row_div=k if down else 1, dac=False,
+                                       g_absmax=gmax, status=status)
+    if need_w and g_tiles is not None and x_cache_hi is not None:
+        grad_w = ops.cvmm_dw_cached(ops.OperandCache(x_cache_hi, x_cache_lo, K), g_tiles, offsets, E, precision, P=P,
+                                    status=status, g_absmax=gmax)
+    elif need_w:
         # reference cvmm.py:785-823: the outer product rw (x) g is folded into the operand load
         if down:
             grad_w = ops.cvmm_dw(x2, sel_index_i, g, sel_index_i, offsets, E, precision, P=P, ir=ir, g_div=k,
@@ -320,7 +358,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
                                       a_row_div=k, x_ref=x2 if ir is not None else None,
                                       x_ref_row=sel_index_i if ir is not None else None, ir=ir, row_scale=rw,
                                       want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
-                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax)
+                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax, a_tiles=g_tiles)
             grad_x = gx.view(x.shape)
         else:
             src = out_index_i if out_index_i is not None else sel_index_i
@@ -328,7 +366,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
                                       x_ref=x2 if ir is not None else None,
                                       x_ref_row=sel_index_i if ir is not None else None, ir=ir,
                                       want_ir_grad=ir is not None, relative=relative, grad_scale=grad_scale,
-                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax)
+                                      keep_count=keep, out_dtype=x.dtype, status=status, g_absmax=gmax, a_tiles=g_tiles)
             T = x2.shape[0]
             grad_x = (ops.combine(gx, None, T, P // T) if P != T else gx).view(x.shape)               # cvmm.py:890-891
         if ir is not None:
@@ -351,7 +389,7 @@ def cvmm_backward_op(grad_output: torch.Tensor, x: torch.Tensor, sel: torch.Tens
 def _cvmm_backward_fake(grad_output, x, sel, sel_index, out_index, reduction_weight, input_ranges, res_into_reduction,
                         offsets, w, bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert, n_experts, N, precision,
                         decay, min_percentage, relative, grad_scale, out_res, out_bound, need_x, need_w, need_ir, need_gate,
-                        check_status):
+                        check_status, x_cache_hi, x_cache_lo):
     new = x.new_empty
     P, K = sel.numel(), x.shape[-1]
     has_ir = input_ranges is not None
@@ -383,15 +421,16 @@ class CVMM(torch.autograd.Function):
         if pn is not None and not pn.std > 0:
             pn = None
         mod = ext.modifier
+        save_operands = bool(ctx.needs_input_grad[3])       # the weight gradient will want the clamped rows
         (out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo,
-         col_scale) = cvmm_forward_op(
+         col_scale, xc_hi, xc_lo) = cvmm_forward_op(
             x, sel_index, sel, keys, float(inp_res), broadcasted_input_ranges, out_index, reduction_weight, noise_t,
             _uses_abs_max(ir_params, io_params), ext.expert_offsets, precision, ext.scale_per_channel,
             float(pn.std) if pn else 0.0, int(pn.seed) if pn else 0, int(pn.offset) if pn else 0, pn.step if pn else None,
             float(mod.std_dev) if mod else 0.0, bool(mod.per_channel) if mod else True,
             float(mod.discretize_res) if mod else -1.0, int(mod.seed) if mod else 0, int(mod.offset) if mod else 0,
             mod.step if mod else None, float(ext.out_res), float(ext.out_bound), ext.adc_codes_path, ext.save_codes,
-            ext.check_status)
+            ext.check_status, save_operands)
         if ext.save_codes:
             ext.last_codes = _none_if_empty(codes)
         if ext.expert_offsets is not None:
@@ -399,14 +438,14 @@ class CVMM(torch.autograd.Function):
         simt = precision == A.PREC_FP32_SIMT
         ctx.save_for_backward(x, sel, sel_index, out_index, reduction_weight, broadcasted_input_ranges,
                               res_into_reduction, offsets, w_mod, keys if (simt and w_mod.numel() == 0) else None,
-                              bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert)
+                              bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert, xc_hi, xc_lo)
         ctx.meta = (E, N, precision, ir_params, keys.dtype, ext.check_status, float(ext.out_res), float(ext.out_bound))
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
         (x, sel, sel_index, out_index, reduction_weight, bir, res_into_reduction, offsets, w_mod, keys_simt, bwd_hi,
-         bwd_lo, col_scale, codes, row_scale, row_expert) = ctx.saved_tensors
+         bwd_lo, col_scale, codes, row_scale, row_expert, xc_hi, xc_lo) = ctx.saved_tensors
         E, N, precision, ir_params, keys_dtype, check_status, out_res, out_bound = ctx.meta
         need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[3]
         need_ir = bir is not None and ctx.needs_input_grad[5]
@@ -421,7 +460,8 @@ class CVMM(torch.autograd.Function):
             grad_output, x, sel, sel_index, out_index, reduction_weight, bir, _none_if_empty(res_into_reduction),
             offsets, w, _none_if_empty(bwd_hi), _none_if_empty(bwd_lo), col_scale, _none_if_empty(codes),
             _none_if_empty(row_scale), _none_if_empty(row_expert), E, N, precision, decay, min_pct, relative, gscale,
-            out_res, out_bound, need_x, need_w, need_ir, need_gate, check_status)
+            out_res, out_bound, need_x, need_w, need_ir, need_gate, check_status, _none_if_empty(xc_hi),
+            _none_if_empty(xc_lo))
         return (grad_x if need_x else None, None, None, grad_w.to(keys_dtype) if need_w else None, None,
                 grad_ir.view(bir.shape) if need_ir else None, None,
                 grad_gate.view(reduction_weight.shape).to(reduction_weight.dtype) if need_gate else None,
