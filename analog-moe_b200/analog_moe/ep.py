@@ -332,13 +332,25 @@ class _ExpertParallelStep(torch.autograd.Function):
         cached = R > 0 and layer.operand_caches and ops.operand_cache_ok(precision, D, Fh, N) and \
             any(ctx.needs_input_grad[3:5])
         split = precision == ops.A.PREC_SPLIT
-        xc = ops.OperandCache.empty(R, El, D, split, dev) if cached else None
+        pre_up = R > 0 and layer.operand_prepass and ops.operand_tiles_ok(recv, precision)
+        xc = ops.OperandCache.empty(R, El, D, split, dev) if (cached and not pre_up) else None
         hs = ops.OperandCache.empty(R, El, Fh, split, dev) if cached else None
         if R > 0:
             am_up = None if has_ir else ops.row_absmax(recv)
+            # the received rows go through the operand pre-pass (DAC as a streaming kernel, A tiles by TMA) like the
+            # single-GPU step's; rows the pre-pass cannot take keep the in-kernel prologue
+            if pre_up:
+                xq, xc_pre = ops.operand_tiles(recv, local_order, local_offsets, El, precision, P=R, dac=True,
+                                               ir=ir_all[0] if has_ir else None, ir_by_expert=True, absmax=am_up,
+                                               inp_res=inp_res, want_cache=cached)
+                if cached:
+                    xc = xc_pre
+                a_kw = dict(a_tiles=xq)
+            else:
+                a_kw = dict(a_cache=xc)
             h, _ = ops.cvmm_fwd(recv, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                 ir=ir_all[0] if has_ir else None, ir_by_expert=True, absmax=am_up, inp_res=inp_res,
-                                out_res=out_res, out_bound=out_bound, out_relu=True, a_cache=xc, **nz_up)
+                                out_res=out_res, out_bound=out_bound, out_relu=True, **a_kw, **nz_up)
             if shared is None:
                 main.wait_stream(side)
             else:
@@ -384,6 +396,7 @@ class _ExpertParallelStep(torch.autograd.Function):
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
                               *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)), cs_all, scale_back)
         ctx.adc_step = adc_step
+        ctx.operand_prepass = layer.operand_prepass
         ctx.generation = xchg.generation if xchg is not None else 0
         if layer.keep_codes:      # ADC codes of the down-projection by flat slot (parity checks)
             layer.last_codes = back[inv.long()] if codes_back else None
@@ -448,10 +461,15 @@ class _ExpertParallelStep(torch.autograd.Function):
             if need_values and not cached:
                 grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
                                           ir_by_expert=True, g_absmax=gmax)
+            if ctx.operand_prepass and ops.operand_tiles_ok(g_recv, precision):
+                gc, _ = ops.operand_tiles(g_recv, local_order, local_offsets, El, precision, P=R, dac=False, g_absmax=gmax)
+                a_kw = dict(a_tiles=gc)
+            else:
+                a_kw = dict(a_cache=gc)
             dh, irs_dn = ops.cvmm_dx(g_recv, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
                                      x_ref=h, x_ref_row=local_order, ir=ir_dn, ir_by_expert=True, want_ir_grad=has_ir,
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
-                                     out_dtype=h.dtype, x_ref_relu=True, a_cache=gc, out_cache=dhc, g_absmax=gmax)
+                                     out_dtype=h.dtype, x_ref_relu=True, out_cache=dhc, g_absmax=gmax, **a_kw)
             ops.set_tag("up")
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,

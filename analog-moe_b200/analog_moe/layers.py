@@ -299,11 +299,12 @@ class _FusedAnalogStep(torch.autograd.Function):
                                              raw_sel=raw_sel).to(w_sel.dtype)
         grad_ir = None
         if need_ir:
-            grad_ir = torch.stack([
-                ops.ir_grad_reduce(irs_up, offsets, ir_up, E, decay, min_pct, keeps[:1] if keeps is not None else None,
-                                   float(P) * D),
-                ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
-                                   float(P) * Fh)]).to(ir_dtype)
+            grad_ir = torch.empty(2, E, dtype=torch.float32, device=x2.device)      # both rows written in place
+            ops.ir_grad_reduce(irs_up, offsets, ir_up, E, decay, min_pct, keeps[:1] if keeps is not None else None,
+                               float(P) * D, out=grad_ir[0])
+            ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
+                               float(P) * Fh, out=grad_ir[1])
+            grad_ir = grad_ir.to(ir_dtype)
         if forked:
             main.wait_stream(side)
         if grad_values is not None:

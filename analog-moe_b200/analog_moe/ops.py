@@ -715,9 +715,12 @@ def adc_step(out_res: float, out_bound: float) -> float:
 
 def ir_grad_reduce(ir_grad_slot: torch.Tensor, offsets: torch.Tensor, input_range: Optional[torch.Tensor], E: int,
                    decay: float = 0.0, min_percentage: float = 0.95, keep_count: Optional[torch.Tensor] = None,
-                   total_elements: float = 0.0, total_rows: Optional[torch.Tensor] = None, cols: int = 0) -> torch.Tensor:
-    """`total_rows` (int64 device scalar) * cols replaces `total_elements` as the denominator of the kept fraction."""
-    out = torch.empty(E, dtype=torch.float32, device=ir_grad_slot.device)
+                   total_elements: float = 0.0, total_rows: Optional[torch.Tensor] = None, cols: int = 0,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`total_rows` (int64 device scalar) * cols replaces `total_elements` as the denominator of the kept fraction.
+    `out`: a contiguous fp32 [E] tensor (e.g. one row of a [2, E] gradient) to write into."""
+    if out is None:
+        out = torch.empty(E, dtype=torch.float32, device=ir_grad_slot.device)
     _call("amoe_ir_grad_reduce", ptr(ir_grad_slot), ptr(offsets), ptr(input_range), E, float(decay),
           float(min_percentage), ptr(keep_count), float(total_elements), ptr(total_rows), int(cols), ptr(out), stream_ptr())
     return out
