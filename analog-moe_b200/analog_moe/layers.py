@@ -86,6 +86,8 @@ class _FusedAnalogStep(torch.autograd.Function):
         clip = layer._take_pending_clip()       # weight clipping left over from post_update_step, done in the pre-pass
 
         def prepass(w, mod):
+            if mod is None and not clip:
+                return ops.weight_prepass_cached(w, precision, per_channel)      # unchanged weights: prepared once
             return ops.weight_prepass(
                 w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
                 noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,

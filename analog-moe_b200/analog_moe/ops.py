@@ -375,6 +375,32 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     return out
 
 
+# prepared weights of unmodified weight tensors, kept while the tensor has not been written to
+_PREPARED = {}
+
+
+def weight_prepass_cached(w: torch.Tensor, precision: int, per_channel_scale: bool = True) -> PreparedWeights:
+    """Weight pre-pass without modifier or clipping, skipped when these exact weights (same storage, same version
+    counter) were prepared before: an inference layer pays for it once, not on every call."""
+    from torch.multiprocessing.reductions import StorageWeakRef
+    # Inside a CUDA-graph capture the check below would be frozen into the graph: a replay after an optimizer step would
+    # use stale copies.  Trainable weights are therefore always prepared inside a captured graph; frozen ones may be
+    # taken from the cache there too.
+    if w.requires_grad and w.is_cuda and torch.cuda.is_current_stream_capturing():
+        return weight_prepass(w, precision, per_channel_scale=per_channel_scale, need_fwd=True, need_bwd=True)
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()), w.dtype, w.device, precision, per_channel_scale)
+    hit = _PREPARED.get(key)
+    # valid while the storage is the one that was prepared (a freed storage's address can be handed out again) and
+    # nothing has written to the tensor since
+    if hit is not None and not hit[0].expired() and hit[1] == w._version:
+        return hit[2]
+    pw = weight_prepass(w, precision, per_channel_scale=per_channel_scale, need_fwd=True, need_bwd=True)
+    if len(_PREPARED) >= 16:
+        _PREPARED.pop(next(iter(_PREPARED)))
+    _PREPARED[key] = (StorageWeakRef(w.untyped_storage()), w._version, pw)
+    return pw
+
+
 def clip_weights_(w: torch.Tensor, sigma: float = -1.0, per_channel: bool = False, fixed_value: float = -1.0) -> None:
     """In place: clamp w [E,K,N] to +-sigma*std (std of each expert, or of each column with `per_channel`), capped by
     `fixed_value` when that is positive; sigma <= 0 clamps to +-fixed_value.  One pass for the statistics and one for

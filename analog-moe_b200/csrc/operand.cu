@@ -103,8 +103,8 @@ __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float 
   }
 }
 
-// The rows of one warp: rows w, w + 8, ... of the tile, four at a time (eight 16-byte loads in flight per lane); lane l
-// holds columns 8l .. 8l+7 of the block's column group.  IR / AM / CSC are compile-time copies of "input ranges
+// The rows of one warp: rows w, w + 8, ... of the tile, four or eight at a time (eight or sixteen 16-byte loads in flight
+// per lane); lane l holds columns 8l .. 8l+7 of the block's column group.  IR / AM / CSC are compile-time copies of "input ranges
 // given", "abs-max given", "cache scale given" (kept as run-time flags they turn into selects inside the unrolled
 // element loops).
 template <int DAC, bool A_F32, bool F16, bool IR, bool AM, bool CSC>
@@ -142,15 +142,18 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
   }
   const float m_rcp_ir = IR ? __frcp_rn(m_ir) : 1.f, m_rcp_am = AM ? __frcp_rn(m_am) : 1.f;
 
+  // rows per round: eight for the plain conversion (sixteen 16-byte loads in flight per lane hide the latency of
+  // the gather), four where the DAC arithmetic needs the registers
+  constexpr int kRpi = DAC == kDacNone ? 8 : 4;
 #pragma unroll 1
-  for (int it = 0; it < 4; ++it) {
-    const int rb = w + 32 * it;
-    float v[4][8];
-    int src[4];
-    float irv[4], rirv[4], amv[4], ramv[4], csc[4];
+  for (int it = 0; it < 16 / kRpi; ++it) {
+    const int rb = w + 8 * kRpi * it;
+    float v[kRpi][8];
+    int src[kRpi];
+    float irv[kRpi], rirv[kRpi], amv[kRpi], ramv[kRpi], csc[kRpi];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int l = 4 * it + j;
+    for (int j = 0; j < kRpi; ++j) {
+      const int l = kRpi * it + j;
       src[j] = __shfl_sync(0xffffffffu, m_src, l);
       irv[j] = IR ? __shfl_sync(0xffffffffu, m_ir, l) : 1.f;
       rirv[j] = IR ? __shfl_sync(0xffffffffu, m_rcp_ir, l) : 1.f;
@@ -159,7 +162,7 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
       csc[j] = CSC ? __shfl_sync(0xffffffffu, m_csc, l) : 1.f;
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kRpi; ++j) {
       if (src[j] >= 0 && k_in) {
         load8<A_F32>(p.a, static_cast<int64_t>(src[j]) * p.a_stride + k, v[j]);
       } else {
@@ -168,7 +171,7 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < kRpi; ++j) {
       const int r = rb + 8 * j;
       const int64_t off = ((blk + r) << 6) + kin;
       if (!k_in) continue;

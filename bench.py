@@ -274,6 +274,8 @@ def run_ours(args, cfg, rank, world, device):
         parity = ep_parity_gate(cfg, rank, world, device, group) if world > 1 else \
             single_gpu_parity_gate(cfg, device, precision)
     layer = build_layer(cfg, device, dtype, precision, ep_group=group)
+    if not cfg["bwd"]:
+        layer.requires_grad_(False)        # forward-only configuration: an inference layer, its weights are frozen
     n_sets = 8
     xs_h, gys_h = make_inputs(cfg, 100 + rank, device, dtype, n_sets)
     xs_h = [t.pin_memory() for t in xs_h]

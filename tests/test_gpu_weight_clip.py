@@ -1,8 +1,8 @@
 """Weight clipping (reference moe_layer_aihwkit_lightning.py:509-543, moe_layer_aihwkit.py:303-340) inside the weight
 pre-pass kernels, against the reference's torch formulas: clamp to +-sigma * std per expert (LAYER_GAUSSIAN), per
 column (LAYER_GAUSSIAN_PER_CHANNEL), capped by or equal to a fixed value (classic flavour).  torch.std is the
-unbiased sample standard deviation; the kernels accumulate sums and sums of squares in fp64, so the bound agrees to
-fp32 rounding and all but bound-straddling elements are bit-identical."""
+unbiased sample standard deviation; the kernels accumulate sums and sums of squares in fp64, so the bound - and with it
+every clamped element - agrees to fp32 rounding."""
 import pytest
 import torch
 
@@ -10,10 +10,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _check(got, want, what):
+    # the bound itself agrees with torch's to an ulp or two (fp64 sums here, fp32 there), and with it every clamped element
     diff = (got - want).abs()
-    # an element whose magnitude is within an ulp of the bound may be clamped in one and kept in the other
-    assert float(diff.max()) <= 1e-6 * float(want.abs().max()), what
-    assert float((diff > 0).float().mean()) <= 1e-3, what
+    assert float(diff.max()) <= 2e-6 * float(want.abs().max()), what
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
