@@ -225,6 +225,25 @@ class _FusedAnalogStep(torch.autograd.Function):
         keeps = torch.zeros(2, dtype=torch.int64, device=x2.device) if (has_ir and decay > 0) else None
         ir_up, ir_dn = (ir_all[0], ir_all[1]) if has_ir else (None, None)
 
+        # ---- gate gradient and the router's weight gradient: they need only the saved codes and the upstream gradient, so
+        # they start at once on the second stream, beside the light kernels that open the main chain (max|gy|, the
+        # operand pre-pass), instead of queueing behind the input-gradient kernels
+        main, side = torch.cuda.current_stream(), ops.side_stream(x2.device)
+        side.wait_stream(main)
+        grad_sel = None
+        with ops.launch_on(side):
+            ops.set_tag("down")
+            if codes is not None:
+                dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
+            else:
+                dgate = ops.row_dot(res, g, k)
+            dgate_ready = side.record_event()
+            # (routers too large for the shared-memory kernel go through torch glue on the main stream further down)
+            sel_early = need_sel and ops._router_fits_smem(w_sel.shape[0], D)
+            if sel_early:
+                ops.set_tag("up")
+                grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
+                                                 raw_sel=raw_sel)
         # ---- down-projection
         ops.set_tag("down")
         grad_values = None
@@ -267,7 +286,6 @@ class _FusedAnalogStep(torch.autograd.Function):
                                       grad_scale=gscale, keep_count=keeps[:1] if keeps is not None else None,
                                       out_dtype=x2.dtype, a_tiles=tiles, g_absmax=gmax)
         grad_keys = None
-        main, side = torch.cuda.current_stream(), ops.side_stream(x2.device)
         forked = cached and (need_values or need_keys)
         if forked:
             side.wait_stream(main)
@@ -285,20 +303,15 @@ class _FusedAnalogStep(torch.autograd.Function):
             # (the hidden gradient's own magnitude scales it here: it is gathered from fp32 rows)
             grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
                                     ir_by_expert=True, g_absmax=ops.grad_absmax(dh, precision))
-        ops.set_tag("down")
-        if codes is not None:
-            dgate = ops.row_dot_codes(codes, dn_cs, row_expert, row_scale, adc_step, g, k)
-        else:
-            dgate = ops.row_dot(res, g, k)
+        main.wait_event(dgate_ready)
         ops.set_tag("up")
         if need_x:
             # sum over k plus the router's own input gradient in one pass
             grad_x = ops.combine_router(dxr, T, k, dgate, gate, raw_sel, w_sel)
         # ---- router
-        grad_sel = None
-        if need_sel:
+        if need_sel and not sel_early:
             grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
-                                             raw_sel=raw_sel).to(w_sel.dtype)
+                                             raw_sel=raw_sel)
         grad_ir = None
         if need_ir:
             grad_ir = torch.empty(2, E, dtype=torch.float32, device=x2.device)      # both rows written in place
@@ -307,8 +320,9 @@ class _FusedAnalogStep(torch.autograd.Function):
             ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
                                float(P) * Fh, out=grad_ir[1])
             grad_ir = grad_ir.to(ir_dtype)
-        if forked:
-            main.wait_stream(side)
+        main.wait_stream(side)
+        if grad_sel is not None:
+            grad_sel = grad_sel.to(w_sel.dtype)
         if grad_values is not None:
             grad_values = grad_values.to(values_dtype)
         if grad_keys is not None:

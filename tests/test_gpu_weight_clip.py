@@ -9,10 +9,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _check(got, want, what):
+def _check(got, want, what, tol=2e-6):
     # the bound itself agrees with torch's to an ulp or two (fp64 sums here, fp32 there), and with it every clamped element
+    # (bf16 weights: the clamped value is rounded to bf16, so an ulp of the bound can become a bf16 ulp)
     diff = (got - want).abs()
-    assert float(diff.max()) <= 2e-6 * float(want.abs().max()), what
+    assert float(diff.max()) <= tol * float(want.abs().max()), what
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -23,25 +24,26 @@ def test_clip_against_the_reference_formulas(dtype):
     E, K, N = 5, 200, 136
     w0 = (torch.randn(E, K, N, generator=g) * torch.linspace(0.5, 2.0, E).view(E, 1, 1)).to(dev).to(dtype)
     sigma = 1.7
+    tol = 2e-6 if dtype == torch.float32 else 2.0 ** -7
     # per expert
     w = w0.clone()
     ops.clip_weights_(w, sigma=sigma)
     b = sigma * w0.float().std((1, 2), keepdim=True)
-    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN")
+    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN", tol)
     assert float((w != w0).float().mean()) > 0.05            # something was clipped
     # per column
     w = w0.clone()
     ops.clip_weights_(w, sigma=sigma, per_channel=True)
     b = sigma * w0.float().std(1, keepdim=True)
-    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN_PER_CHANNEL")
+    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN_PER_CHANNEL", tol)
     # fixed value, and sigma capped by a fixed value (classic flavour)
     w = w0.clone()
     ops.clip_weights_(w, fixed_value=0.8)
-    _check(w.float(), w0.float().clamp(-0.8, 0.8), "FIXED_VALUE")
+    _check(w.float(), w0.float().clamp(-0.8, 0.8), "FIXED_VALUE", tol)
     w = w0.clone()
     ops.clip_weights_(w, sigma=sigma, fixed_value=1.1)
     b = (sigma * w0.float().std((1, 2), keepdim=True)).clamp(max=1.1)
-    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN capped")
+    _check(w.float(), w0.float().clamp(-b, b).to(dtype).float(), "LAYER_GAUSSIAN capped", tol)
 
 
 def test_clip_fused_into_the_weight_prepass_and_the_layer_hook():
