@@ -372,6 +372,8 @@ def weight_prepass(w: torch.Tensor, precision: int, *, per_channel_scale: bool =
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     _call("amoe_weight_prepass", C.byref(a), stream_ptr())
     out.workspace = ws       # stays alive with the result: the launch stream may differ from the allocating one
+    if clip:
+        forget_prepared(w)   # the weights were clamped in place
     return out
 
 
@@ -401,6 +403,14 @@ def weight_prepass_cached(w: torch.Tensor, precision: int, per_channel_scale: bo
     return pw
 
 
+def forget_prepared(w: torch.Tensor) -> None:
+    """Drops the cached prepared copies of `w`: for writes that do not move the tensor's version counter (through
+    `.data`, or by a kernel of this library writing in place)."""
+    ptr_ = w.data_ptr()
+    for key in [k for k in _PREPARED if k[0] == ptr_]:
+        del _PREPARED[key]
+
+
 def clip_weights_(w: torch.Tensor, sigma: float = -1.0, per_channel: bool = False, fixed_value: float = -1.0) -> None:
     """In place: clamp w [E,K,N] to +-sigma*std (std of each expert, or of each column with `per_channel`), capped by
     `fixed_value` when that is positive; sigma <= 0 clamps to +-fixed_value.  One pass for the statistics and one for
@@ -417,6 +427,7 @@ def clip_weights_(w: torch.Tensor, sigma: float = -1.0, per_channel: bool = Fals
     a.workspace, a.workspace_bytes = ptr(ws), nbytes
     _call("amoe_weight_prepass", C.byref(a), stream_ptr())
     w._amoe_workspace = ws
+    forget_prepared(w)
 
 
 def tensor_absmax(x2: torch.Tensor, n_rows_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
