@@ -387,13 +387,28 @@ class CVMM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sel_index, sel, keys, inp_res, broadcasted_input_ranges=None, out_index=None,
                 reduction_weight=None, out_noise=None, ir_params=None, io_params=None, ext=None):
-        if torch.is_autocast_enabled():
-            raise RuntimeError("autocast is not supported by the B200 CVMM kernels; pass bf16 or fp32 tensors")
         ext = ext or CVMMExt()
         E, K, N = keys.shape
         if x.shape[-1] != K:
             raise ValueError(f"x has {x.shape[-1]} features, weights expect {K}")     # reference cvmm.py:561
-        precision = ext.precision if ext.precision is not None else ops.default_precision(x.dtype)
+        # Half path (reference cvmm.py:177-179, 188-189, 716): under autocast - or for fp16 tensors - the reference casts
+        # both operands to fp16 whatever their storage type, accumulates in fp32 and returns fp16.  That is the fp16
+        # operand precision of the tensor-core kernels; fp16 tensors cross the boundary as fp32 (an exact widening).
+        half_path = torch.is_autocast_enabled() or x.dtype == torch.float16 or keys.dtype == torch.float16
+        out_type = torch.float16 if half_path else x.dtype
+        x_dtype_in = x.dtype
+        widen = lambda t: t.float() if (t is not None and t.dtype == torch.float16) else t
+        if half_path:
+            x, keys_k = widen(x), widen(keys)
+            broadcasted_input_ranges, reduction_weight = widen(broadcasted_input_ranges), widen(reduction_weight)
+            if isinstance(out_noise, torch.Tensor):
+                out_noise = widen(out_noise)
+        else:
+            keys_k = keys
+        if ext.precision is not None:
+            precision = ext.precision
+        else:
+            precision = A.PREC_F16X1 if (half_path and x.dtype == torch.float32) else ops.default_precision(x.dtype)
         if os.environ.get("_AIHWKIT_NO_ROUNDING", False):                              # reference cvmm.py:603-608
             assert os.environ.get("AIHWKIT_TESTING", False), "Skipping rounding but AIHWKIT_TESTING not set"
             inp_res = -1
@@ -408,7 +423,7 @@ class CVMM(torch.autograd.Function):
         save_operands = bool(ctx.needs_input_grad[3])       # the weight gradient will want the clamped rows
         (out, offsets, res_into_reduction, codes, row_scale, row_expert, w_mod, bwd_hi, bwd_lo,
          col_scale, xc_hi, xc_lo) = cvmm_forward_op(
-            x, sel_index, sel, keys, float(inp_res), broadcasted_input_ranges, out_index, reduction_weight, noise_t,
+            x, sel_index, sel, keys_k, float(inp_res), broadcasted_input_ranges, out_index, reduction_weight, noise_t,
             _uses_abs_max(ir_params, io_params), ext.expert_offsets, precision, ext.scale_per_channel,
             float(pn.std) if pn else 0.0, int(pn.seed) if pn else 0, int(pn.offset) if pn else 0, pn.step if pn else None,
             float(mod.std_dev) if mod else 0.0, bool(mod.per_channel) if mod else True,
@@ -421,10 +436,11 @@ class CVMM(torch.autograd.Function):
             offsets = ext.expert_offsets
         simt = precision == A.PREC_FP32_SIMT
         ctx.save_for_backward(x, sel, sel_index, out_index, reduction_weight, broadcasted_input_ranges,
-                              res_into_reduction, offsets, w_mod, keys if (simt and w_mod.numel() == 0) else None,
+                              res_into_reduction, offsets, w_mod, keys_k if (simt and w_mod.numel() == 0) else None,
                               bwd_hi, bwd_lo, col_scale, codes, row_scale, row_expert, xc_hi, xc_lo)
         ctx.meta = (E, N, precision, ir_params, keys.dtype, ext.check_status, float(ext.out_res), float(ext.out_bound))
-        return out
+        ctx.x_dtype_in = x_dtype_in
+        return out if out.dtype == out_type else out.to(out_type)
 
     @staticmethod
     def backward(ctx, grad_output):
@@ -440,13 +456,15 @@ class CVMM(torch.autograd.Function):
         relative = bool(getattr(ir_params, "gradient_relative", True))
         gscale = float(getattr(ir_params, "gradient_scale", 1.0)) if relative else 1.0
         w = keys_simt if keys_simt is not None else _none_if_empty(w_mod)
+        if grad_output.dtype == torch.float16:
+            grad_output = grad_output.float()
         grad_x, grad_w, grad_ir, grad_gate = cvmm_backward_op(
             grad_output, x, sel, sel_index, out_index, reduction_weight, bir, _none_if_empty(res_into_reduction),
             offsets, w, _none_if_empty(bwd_hi), _none_if_empty(bwd_lo), col_scale, _none_if_empty(codes),
             _none_if_empty(row_scale), _none_if_empty(row_expert), E, N, precision, decay, min_pct, relative, gscale,
             out_res, out_bound, need_x, need_w, need_ir, need_gate, check_status, _none_if_empty(xc_hi),
             _none_if_empty(xc_lo))
-        return (grad_x if need_x else None, None, None, grad_w.to(keys_dtype) if need_w else None, None,
+        return (grad_x.to(ctx.x_dtype_in) if need_x else None, None, None, grad_w.to(keys_dtype) if need_w else None, None,
                 grad_ir.view(bir.shape) if need_ir else None, None,
                 grad_gate.view(reduction_weight.shape).to(reduction_weight.dtype) if need_gate else None,
                 None, None, None, None)

@@ -355,3 +355,52 @@ def test_compiled_cvmm_matches_eager():
     got = grads(torch.compile(f, backend="aot_eager", fullgraph=True))
     for a, b in zip(got, want):
         assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_half_path_under_autocast_and_for_fp16_tensors():
+    """The reference's half path (cvmm.py:177-179, 188-189, 716): under autocast - or for fp16 tensors - both operands
+    are cast to fp16 whatever their storage type, accumulated in fp32, and the result is fp16.  Here that is the fp16
+    operand precision of the tensor-core kernels; fp16 tensors are widened on the way in.  Compared with the same call
+    outside autocast in the bf16 hi + lo precision: 2e-3 of the scale (fp16 operands and an fp16 result)."""
+    from analog_moe import CVMM, CVMMExt, ops, _cabi
+    dev = torch.device("cuda:0")
+    T, D, F, E, k = 256, 128, 64, 4, 2
+    torch.manual_seed(6)
+
+    class IR:
+        enable, decay, input_min_percentage = True, 0.0, 0.95
+
+    class IO:
+        pass
+
+    x0 = torch.randn(1, T, D, device=dev)
+    keys0 = torch.randn(E, D, F, device=dev) / D ** 0.5
+    ir0 = torch.full((E,), 2.0, device=dev)
+    r = ops.select_sort(torch.randn(T, E, device=dev), k)
+    sel = r.sel.view(1, T, k).long()
+    tok, slot = r.token_index.long(), r.slot_index.long()
+    gy = torch.randn(1, T, k, F, device=dev)
+
+    def run(x, keys, ext=None):
+        x, keys = x.clone().requires_grad_(), keys.clone().requires_grad_()
+        ir = ir0.clone().requires_grad_()
+        e = (ext,) if ext is not None else ()
+        out = CVMM.apply(x, tok, sel, keys, 2 / 254., ir[sel], slot, None, None, IR, IO(), *e)
+        out.backward(gy.to(out.dtype))
+        return out, x.grad, keys.grad, ir.grad
+
+    want = run(x0, keys0, CVMMExt(precision=_cabi.PREC_SPLIT))
+    with torch.autocast("cuda", dtype=torch.float16):
+        got = run(x0, keys0)
+    assert got[0].dtype == torch.float16 and got[1].dtype == torch.float32 and got[2].dtype == torch.float32
+    for a, b, name in zip(got, want, ("out", "dx", "dkeys", "d_input_range")):
+        scale = max(1.0, float(b.abs().max()))
+        assert float((a.float() - b.float()).abs().max()) <= 2e-3 * scale, name
+    # fp16 tensors outside autocast: fp16 result, gradients in the tensors' own type
+    got = run(x0.half(), keys0.half())
+    assert got[0].dtype == torch.float16 and got[1].dtype == torch.float16 and got[2].dtype == torch.float16
+    want16 = run(x0.half().float(), keys0.half().float(), CVMMExt(precision=_cabi.PREC_SPLIT))
+    for a, b, name in zip(got, want16, ("out", "dx", "dkeys", "d_input_range")):
+        scale = max(1.0, float(b.abs().max()))
+        assert float((a.float() - b.float()).abs().max()) <= 3e-3 * scale, name
