@@ -285,27 +285,14 @@ struct __align__(16) RowMeta {
 // memory (32 rows of 80 bytes: 64 of data, 16 of padding that keeps both access patterns free of bank
 // conflicts): written by row owners, read back so that thread j of a quad holds columns 4j..4j+3 of the
 // quad's four rows - every global store then writes 64 contiguous bytes per row, eight rows at a time.
-// The reverse exchange turns coalesced loads of the clip reference into the row-owner layout.  Eight
-// shared-memory instructions per thread and exchange (a shuffle network took 16 shuffles and 48 selects).
+// The clip reference of the input-gradient launches comes the other way through a second such block, filled by
+// cp.async one chunk ahead (xref_prefetch).  Eight shared-memory instructions per thread and exchange (a shuffle
+// network took 16 shuffles and 48 selects).
 // All 32 lanes take part; rows that must not be written carry dst = -1.
 constexpr int kTrRowFloats = 20;                          // 80 bytes
 constexpr uint32_t kTrBytesPerWarp = 32 * kTrRowFloats * 4;   // 2560
 
-// t[i] = columns 4*(lane&3).. of row (lane & ~3) + i   ->   v = the 16 columns of row `lane`
-__device__ __forceinline__ void rows_to_owner(float* tr, const float4 t[4], float v[16], int lane) {
-  float* w = tr + (lane & ~3) * kTrRowFloats + 4 * (lane & 3);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(w + i * kTrRowFloats) = t[i];
-  __syncwarp();
-  const float* r = tr + lane * kTrRowFloats;
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const float4 u = *reinterpret_cast<const float4*>(r + 4 * c);
-    v[4 * c] = u.x; v[4 * c + 1] = u.y; v[4 * c + 2] = u.z; v[4 * c + 3] = u.w;
-  }
-  __syncwarp();
-}
-// the inverse: v = the 16 columns of row `lane`   ->   t[i] = columns 4*(lane&3).. of row (lane & ~3) + i
+// v = the 16 columns of row `lane`   ->   t[i] = columns 4*(lane&3).. of row (lane & ~3) + i
 __device__ __forceinline__ void owner_to_rows(float* tr, const float v[16], float4 t[4], int lane) {
   float* w = tr + lane * kTrRowFloats;
 #pragma unroll
@@ -465,30 +452,48 @@ __device__ __forceinline__ void epi_chunk_fwd(const EpiParams& p, const RowCtx& 
 }
 
 // `cache_mul`: the operand cache keeps the result times this power of two (the gradient scale of fp16 operands).
+// Clip-reference rows of one 16-column chunk, asynchronously into the warp's reference block: lane l copies columns
+// 4*(l&3).. of the quad's rows (l & ~3) + i, 16 bytes each for fp32 (8 for bf16), zero-filled for rows that are not
+// read.  Issued one chunk ahead, so that the latency of these gathered loads overlaps the previous chunk's arithmetic.
+__device__ __forceinline__ void xref_prefetch(const EpiParams& p, const QuadRows& qr, int n0, float* xb, int lane) {
+  const int col = n0 + 4 * (lane & 3);
+  float* w = xb + (lane & ~3) * kTrRowFloats + 4 * (lane & 3);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const bool on = qr.xrow[i] >= 0;
+    const int64_t xi = on ? static_cast<int64_t>(qr.xrow[i]) * p.x_ref_stride + col : 0;
+    const uint32_t dst = smem_u32(w + i * kTrRowFloats);
+    if (p.x_ref_dtype == AMOE_F32) cp_async16(dst, reinterpret_cast<const float*>(p.x_ref) + xi, on ? 16u : 0u);
+    else cp_async8(dst, reinterpret_cast<const __nv_bfloat16*>(p.x_ref) + xi, on ? 8u : 0u);
+  }
+  cp_async_commit();
+}
+
 // XREF / IR / RELU / CACHE are compile-time copies of the launch's options (x_ref given, input ranges given, ReLU
 // mask, result rows also written as an operand cache); the caller dispatches once per chunk.
 template <bool F16, bool XREF, bool IR, bool RELU, bool CACHE>
 __device__ __forceinline__ void epi_chunk_dx_t(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
-                                               int lane, float cache_mul, float* tr) {
+                                               int lane, float cache_mul, float* tr, float* xb, int next_n0) {
   if (XREF) {
+    // this chunk's reference rows were requested one chunk ago (xref_prefetch): wait for them, take "my row, 16
+    // columns" out of the block, then request the next chunk's before the arithmetic starts
     float xr[16];
-    float4 t[4];
-    const int col = n0 + 4 * (lane & 3);
+    cp_async_wait<0>();
+    __syncwarp();
+    const float* rp = xb + lane * kTrRowFloats;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (qr.xrow[i] >= 0) {
-        const int64_t xi = static_cast<int64_t>(qr.xrow[i]) * p.x_ref_stride + col;
-        if (p.x_ref_dtype == AMOE_F32) {
-          t[i] = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.x_ref) + xi));
-        } else {
-          const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.x_ref) + xi));
-          t[i] = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u), __uint_as_float(u.y << 16),
-                             __uint_as_float(u.y & 0xffff0000u));
-        }
+    for (int cc = 0; cc < 4; ++cc) {
+      const float4 u = *reinterpret_cast<const float4*>(rp + 4 * cc);
+      if (p.x_ref_dtype == AMOE_F32) {
+        xr[4 * cc] = u.x; xr[4 * cc + 1] = u.y; xr[4 * cc + 2] = u.z; xr[4 * cc + 3] = u.w;
+      } else {      // four bf16 in the first eight bytes
+        const uint32_t a = __float_as_uint(u.x), b = __float_as_uint(u.y);
+        xr[4 * cc] = __uint_as_float(a << 16); xr[4 * cc + 1] = __uint_as_float(a & 0xffff0000u);
+        xr[4 * cc + 2] = __uint_as_float(b << 16); xr[4 * cc + 3] = __uint_as_float(b & 0xffff0000u);
       }
     }
-    rows_to_owner(tr, t, xr, lane);     // "my row, 16 columns"
+    __syncwarp();
+    if (next_n0 >= 0) xref_prefetch(p, qr, next_n0, xb, lane);
     if (IR) {
       // up = x >= ir adds min(g, 0), low = x <= -ir subtracts max(g, 0), everything else is kept (cvmm.py:863-870).
       // With t = g carrying x's sign flipped in (exact), both clipped cases are min(t, 0): one compare, one min.
@@ -540,18 +545,18 @@ __device__ __forceinline__ void epi_chunk_dx_t(const EpiParams& p, RowCtx& c, co
 
 template <bool F16>
 __device__ __forceinline__ void epi_chunk_dx(const EpiParams& p, RowCtx& c, const QuadRows& qr, int n0, float v[16],
-                                             int lane, float cache_mul, float* tr) {
+                                             int lane, float cache_mul, float* tr, float* xb, int next_n0) {
   const bool xref = p.x_ref != nullptr, ir = xref && p.ir != nullptr, relu = xref && p.x_ref_relu != 0;
   const bool cache = p.out_cache_hi != nullptr;
   // the two launches of a layer step, then the remaining combinations
-  if (xref && ir && relu && cache) epi_chunk_dx_t<F16, true, true, true, true>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (xref && ir && !relu && !cache) epi_chunk_dx_t<F16, true, true, false, false>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (!xref && !cache) epi_chunk_dx_t<F16, false, false, false, false>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (!xref) epi_chunk_dx_t<F16, false, false, false, true>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (ir && relu) epi_chunk_dx_t<F16, true, true, true, false>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (ir) epi_chunk_dx_t<F16, true, true, false, true>(p, c, qr, n0, v, lane, cache_mul, tr);
-  else if (cache) epi_chunk_dx_t<F16, true, false, true, true>(p, c, qr, n0, v, lane, cache_mul, tr);   // x_ref without ir: ReLU mask only
-  else epi_chunk_dx_t<F16, true, false, true, false>(p, c, qr, n0, v, lane, cache_mul, tr);
+  if (xref && ir && relu && cache) epi_chunk_dx_t<F16, true, true, true, true>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (xref && ir && !relu && !cache) epi_chunk_dx_t<F16, true, true, false, false>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (!xref && !cache) epi_chunk_dx_t<F16, false, false, false, false>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (!xref) epi_chunk_dx_t<F16, false, false, false, true>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (ir && relu) epi_chunk_dx_t<F16, true, true, true, false>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (ir) epi_chunk_dx_t<F16, true, true, false, true>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
+  else if (cache) epi_chunk_dx_t<F16, true, false, true, true>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);   // x_ref without ir: ReLU mask only
+  else epi_chunk_dx_t<F16, true, false, true, false>(p, c, qr, n0, v, lane, cache_mul, tr, xb, next_n0);
 }
 
 // Work items of one CTA: row tile t with all its n-tiles, or - item mode - one (row tile, n-tile) pair.
@@ -670,6 +675,9 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     float* cs_smem = reinterpret_cast<float*>(sm.base + p.cs_off) + ew * 2 * p.cs_per_warp;
     float* cis_smem = cs_smem + p.cs_per_warp;
     float* tr = reinterpret_cast<float*>(sm.base + p.tr_off) + ew * (kTrBytesPerWarp / 4);   // this warp's exchange block
+    // a second block per warp receives the clip-reference rows one chunk ahead (input-gradient launches with x_ref)
+    float* xb = tr + p.n_epi * (kTrBytesPerWarp / 4);
+    const bool xpre = EPI == kEpiDx && p.epi.x_ref != nullptr;
     const bool need_cs = EPI == kEpiFwd && (p.epi.noise_std > 0.f || p.epi.adc.on);
     uint32_t acc_it = 0, sync_round = 0;
     bool alive = true;
@@ -692,6 +700,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
           qr.xrow[j] = __shfl_sync(0xffffffffu, my_x, (lane & ~3) + j);
         }
       }
+      if (xpre && grp < chunks && it.nt0 * p.BN + grp * cw + cw <= p.epi.n_out)
+        xref_prefetch(p.epi, qr, it.nt0 * p.BN + grp * cw, xb, lane);     // the item's first chunk, before its accumulator is ready
       for (int nt = it.nt0; nt < it.nt1 && alive; ++nt, ++acc_it) {
         const int buf = acc_it & 1u;
         const uint32_t aph = (acc_it >> 1) & 1u;
@@ -734,7 +744,16 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
               if (p.epi.out != nullptr) epi_chunk_fwd<true, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane, tr);
               else epi_chunk_fwd<false, F16>(p.epi, ctx, qr, n0, v, cs_smem + slot * 16, cis_smem + slot * 16, lane, tr);
             }
-            else epi_chunk_dx<F16>(p.epi, ctx, qr, n0, v, lane, g_mul, tr);
+            else {
+              // the chunk this warp takes next (same n-tile, or the first of the next n-tile), if it is a whole one
+              int next_n0 = -1;
+              if (xpre) {
+                if (ch + groups < chunks) next_n0 = n0 + groups * cw;
+                else if (nt + 1 < it.nt1) next_n0 = (nt + 1) * p.BN + grp * cw;
+                if (next_n0 + cw > p.epi.n_out) next_n0 = -1;
+              }
+              epi_chunk_dx<F16>(p.epi, ctx, qr, n0, v, lane, g_mul, tr, xb, next_n0);
+            }
           }
         }
         tc_fence_before();
@@ -1578,13 +1597,16 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (f16) p.epi.out_cache_lo = nullptr;
 
   p.a_bytes = a_split ? 2 * kATile : kATile;
+  // exchange blocks per epilogue warp: one, or two where the clip-reference rows are prefetched
+  const bool xpre = is_dx && a->x_ref != nullptr;
+  const uint32_t tr_unit = kTrBytesPerWarp * (xpre ? 2u : 1u);
   // two ring stages must fit beside the epilogue warps' exchange blocks: wide weight tiles in two terms are cut into
   // narrower n-tiles where they do not
   for (;;) {
     p.b_bytes = static_cast<uint32_t>(p.BN) * 128u;
     p.stage_bytes = p.a_bytes + p.b_bytes * (b_split ? 2u : 1u);
     p.stage_bytes = (p.stage_bytes + 1023u) & ~1023u;
-    if ((kSmemBudget - kWorkerWarps * kTrBytesPerWarp) / p.stage_bytes >= 2 || p.BN <= 64) break;
+    if ((kSmemBudget - 4u * tr_unit) / p.stage_bytes >= 2 || p.BN <= 64) break;     // (four epilogue warps at the least)
     p.n_tiles *= 2;
     p.BN = round_up((n_pad + p.n_tiles - 1) / p.n_tiles, 16);
   }
@@ -1602,7 +1624,10 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     const double work_p = static_cast<double>(p.n_tiles) * p.k_chunks * kBK * per_prod;
     const double work_e = static_cast<double>(p.n_tiles) * p.BN * per_epi;
     double best = 1e300;
+    auto fits = [&](int ne) { return (kSmemBudget - static_cast<uint32_t>(ne) * tr_unit) / p.stage_bytes >= 2; };
+    p.n_epi = 4; p.n_prod = kWorkerWarps - 4;
     for (int ne = 4; ne <= kWorkerWarps - 2 && ne <= 24; ne += 4) {
+      if (!fits(ne)) continue;
       const double t = fmax(work_p / (kWorkerWarps - ne), work_e / ne);
       if (t < best) { best = t; p.n_epi = ne; p.n_prod = kWorkerWarps - ne; }
     }
@@ -1611,6 +1636,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
       const int chunks = p.BN / 16;
       int best_per = 1 << 30;
       for (int ne = 4; ne <= kWorkerWarps; ne += 4) {
+        if (!fits(ne)) continue;
         const int per = (chunks + ne / 4 - 1) / (ne / 4);
         if (per < best_per) { best_per = per; p.n_epi = ne; }
       }
@@ -1618,7 +1644,7 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
     }
   }
   // the ring takes what the epilogue warps' exchange blocks leave of the budget
-  const uint32_t tr_bytes = static_cast<uint32_t>(p.n_epi) * kTrBytesPerWarp;
+  const uint32_t tr_bytes = static_cast<uint32_t>(p.n_epi) * tr_unit;
   p.stages = static_cast<int>((kSmemBudget - tr_bytes) / p.stage_bytes);
   if (p.stages > kMaxStages) p.stages = kMaxStages;
   AMOE_REQUIRE(p.stages >= 2, AMOE_ERR_UNSUPPORTED);
