@@ -1493,12 +1493,25 @@ __global__ void dw_reduce_kernel(const float* __restrict__ partials, const int32
 }
 
 // Slots per segment for the split, or 0 when the work is too small to be worth splitting.
-int dw_segment_slots(int64_t P, int K, int N) {
+// A work item is (segment, pair of output tiles).  The segment length is chosen so that the items of a balanced
+// routing fill the SMs about once - every further wave adds a set of partial tiles to write and sum, and short items
+// (a few 64-slot stages) do not amortise the latency of their first loads - and so that an expert's expected share
+// divides into equal segments.  Experts with more rows simply get more segments.
+int dw_segment_slots(int64_t P, int E, int K, int N) {
   if (P <= 4096 || (static_cast<int64_t>(K) * N) % 4 != 0) return 0;
   const int n_pad = round_up(N, 16);
   const int n_tiles = (n_pad + 127) / 128;
   const int m_tiles = (K + kBM - 1) / kBM;
-  int64_t seg = P * m_tiles * n_tiles / (4 * 148);
+  int MB = 1, NB = 1;
+  if (m_tiles >= 2 && m_tiles >= n_tiles) MB = 2;
+  else if (n_tiles >= 2) NB = 2;
+  const int64_t pairs = static_cast<int64_t>((m_tiles + MB - 1) / MB) * ((n_tiles + NB - 1) / NB);
+  const int64_t per_expert = P / (E > 0 ? E : 1) + kBM;          // expected padded rows of an expert
+  int64_t target = (P + static_cast<int64_t>(kBM) * E) * pairs / 148;   // rows per item for one wave
+  if (target < 512) target = 512;
+  int64_t n = (per_expert + target / 2) / target;                 // segments per (balanced) expert, rounded
+  if (n < 1) n = 1;
+  int64_t seg = (per_expert + n - 1) / n;
   seg = (seg + 63) / 64 * 64;
   if (seg < 256) seg = 256;
   if (seg > 4096) seg = 4096;
@@ -1751,7 +1764,7 @@ extern "C" int amoe_selftest_bounded_wait(int32_t* dev_status, long long limit_c
 namespace amoe {
 
 size_t dw_tc_workspace_bytes(int64_t P, int64_t expected, int E, int K, int N) {
-  const int seg = dw_segment_slots(expected > 0 && expected < P ? expected : P, K, N);
+  const int seg = dw_segment_slots(expected > 0 && expected < P ? expected : P, E, K, N);
   if (seg == 0) return 0;
   // segments are cut per expert, in padded row space when the operands come from the caches
   return static_cast<size_t>((P + static_cast<int64_t>(kBM) * E + seg - 1) / seg + E) * K * N * sizeof(float);
@@ -1768,7 +1781,7 @@ static int launch_dw_tma(const amoe_dw_args* a, cudaStream_t stream) {
   p.dw = a->dw; p.status = a->dev_status;
   p.f16 = a->precision == AMOE_PREC_F16X1; p.g_absmax = a->g_absmax_dev;
   const int64_t tune = a->expected_rows > 0 && a->expected_rows < a->P ? a->expected_rows : a->P;
-  p.seg = dw_segment_slots(tune, a->K, a->N);
+  p.seg = dw_segment_slots(tune, a->E, a->K, a->N);
   const size_t need = dw_tc_workspace_bytes(a->P, tune, a->E, a->K, a->N);
   if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
     p.seg = 0;
@@ -1843,7 +1856,7 @@ int launch_dw_tc(const amoe_dw_args* a, cudaStream_t stream) {
   // SMs and a popular expert does not become one long item; the partial tiles go to the workspace and
   // are summed in segment order afterwards.
   const int64_t tune = a->expected_rows > 0 && a->expected_rows < a->P ? a->expected_rows : a->P;
-  p.seg = dw_segment_slots(tune, a->K, a->N);
+  p.seg = dw_segment_slots(tune, a->E, a->K, a->N);
   const size_t need = dw_tc_workspace_bytes(a->P, tune, a->E, a->K, a->N);
   if (p.seg > 0 && (a->workspace == nullptr || a->workspace_bytes < need || !aligned16(a->workspace) || !aligned16(a->dw)))
     p.seg = 0;   // no (usable) workspace: one owner per expert tile
