@@ -51,6 +51,7 @@ struct RowCtx {
   uint32_t noise_offset;   // Philox offset in effect (argument + 8 * device step counter)
   int64_t pad_row;         // tile index * 128 + row in tile (row of the operand caches)
   float next_ir, next_rcp; // input range of the next projection for this row's expert and its reciprocal
+  float out_cache_sc;      // out_cache_scale of this row (1 when absent), fetched once per tile
 };
 
 __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, int e, bool in_range) {
@@ -60,7 +61,7 @@ __device__ __forceinline__ RowCtx epi_row_begin(const EpiParams& p, int64_t i, i
   c.dst = 0; c.ir = 1.f; c.absmax = 1.f; c.rs = 1.f; c.xrow = 0; c.dir_acc = 0.f; c.keep = 0;
   c.noise_offset = p.offset;
   c.pad_row = 0;
-  c.next_ir = 1.f; c.next_rcp = 1.f;
+  c.next_ir = 1.f; c.next_rcp = 1.f; c.out_cache_sc = 1.f;
   if (!p.is_dx && p.next_ir) { c.next_ir = p.next_ir[e]; c.next_rcp = __frcp_rn(c.next_ir); }
   if (p.noise_std > 0.f && p.step_dev) c.noise_offset += static_cast<uint32_t>(*p.step_dev) * 8u;
   if (!in_range) return c;

@@ -399,7 +399,7 @@ __device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx
     // for its forward pass, clamped and scaled bf16 hi (+ lo) terms for its weight gradient
     const int64_t co = (((n0 >> 6) * p.out_cache_stride + c.pad_row) << 6) + (n0 & 63);
     const float rcp_res = quant_rcp(p.next_res);
-    const float sc = (p.out_cache_scale && c.valid) ? p.out_cache_scale[c.dst] : 1.f;
+    const float sc = c.out_cache_sc;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       float hc[8];
@@ -687,6 +687,8 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       const int64_t i = static_cast<int64_t>(it.row0) + r;
       RowCtx ctx = epi_row_begin(p.epi, i, e, r < rows);
       ctx.pad_row = t * kBM + r;
+      if (EPI == kEpiFwd && p.epi.out_cache_hi && p.epi.out_cache_scale && ctx.valid)
+        ctx.out_cache_sc = p.epi.out_cache_scale[ctx.dst];      // once per tile, not once per chunk
       // the accumulator carries the gradient scale of the A operand: take it out with the row scale
       if (EPI != kEpiFwd && p.epi.is_dx) ctx.rs *= g_inv;
       if (grp == 0 && it.nt0 == 0) epi_row_side_outputs(p.epi, ctx);
