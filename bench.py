@@ -665,7 +665,11 @@ def main():
         else:
             roof = dict(kernel=top, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
                         peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
-        line = dict(base, value=value, ms_per_step=ms_step, dtype="f32" if cfg["dtype"] == "fp32" else "bf16",
+        # the arithmetic type of the contraction (not of the stored tensors): operand type x accumulator type
+        # (f32 accumulation throughout; config.precision spells the mode out)
+        arith = {0: "bf16", 1: "bf16x2", 2: "f32", 3: "f16"}[r["precision"]]
+        line = dict(base, value=value, ms_per_step=ms_step, dtype=arith,
+                    data_dtype="f32" if cfg["dtype"] == "fp32" else "bf16",
                     tflops=value * flops_per_token / 1e12, tflops_frac_of_peak=value * flops_per_token / 1e12 / pk["tf"] / world,
                     e2e=dict(value=e2e_val, unit="tokens/s", h2d_bytes_per_step=r["h2d"], d2h_bytes_per_step=r["d2h"]),
                     gpu_launches=r["launches"], roofline=roof, clocks=r["clocks"],
