@@ -287,15 +287,20 @@ class _FusedAnalogStep(torch.autograd.Function):
                                       out_dtype=x2.dtype, a_tiles=tiles, g_absmax=gmax)
         grad_keys = None
         forked = cached and (need_values or need_keys)
+        side2 = ops.side_stream(x2.device, 1)
         if forked:
+            # each weight gradient is a TMA-fed kernel followed by the ordered sum of its partial tiles: on two streams
+            # the second kernel starts while the first one's partial tiles are being summed
             side.wait_stream(main)
-            with ops.launch_on(side):
-                if need_values:
+            side2.wait_stream(main)
+            if need_values:
+                with ops.launch_on(side):
                     # dW = sum_slots (gate * clamp(h))^T (x) gy: both operands straight from the caches
                     ops.set_tag("down")
                     grad_values = ops.cvmm_dw_cached(ops.OperandCache(hs_hi, hs_lo, Fh), gc, offsets, E, precision, P=P,
                                                      g_absmax=gmax)
-                if need_keys:
+            if need_keys:
+                with ops.launch_on(side2):
                     ops.set_tag("up")
                     grad_keys = ops.cvmm_dw_cached(ops.OperandCache(xc_hi, xc_lo, D), dhc, offsets, E, precision, P=P,
                                                    g_absmax=gmax)
@@ -321,6 +326,7 @@ class _FusedAnalogStep(torch.autograd.Function):
                                float(P) * Fh, out=grad_ir[1])
             grad_ir = grad_ir.to(ir_dtype)
         main.wait_stream(side)
+        main.wait_stream(side2)
         if grad_sel is not None:
             grad_sel = grad_sel.to(w_sel.dtype)
         if grad_values is not None:

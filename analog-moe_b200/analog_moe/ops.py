@@ -79,15 +79,16 @@ def _call_traced(name: str, *args) -> None:
 _SIDE_STREAMS = {}
 
 
-def side_stream(device: torch.device) -> torch.cuda.Stream:
-    """One extra stream per device for work that runs beside the main chain (the weight pre-passes, the weight
+def side_stream(device: torch.device, index: int = 0) -> torch.cuda.Stream:
+    """Extra streams per device (`index` 0, 1, ...) for work that runs beside the main chain (the weight pre-passes, the weight
     gradients).  It has the higher priority: its kernels are few and small in thread blocks (a TMA-fed dW kernel is one
     CTA of six warps per SM), and what waits for them sits on the critical path, so their blocks should get the SMs
     ahead of the main stream's large streaming grids, which then fill in beside them."""
-    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    dev = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    key = (dev, index)
     st = _SIDE_STREAMS.get(key)
     if st is None:
-        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=key, priority=-1)
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=dev, priority=-1)
     return st
 
 
