@@ -124,7 +124,6 @@ class _FusedAnalogStep(torch.autograd.Function):
         out_res, out_bound = (float(fwd.out_res), float(fwd.out_bound)) if adc_on else (-1.0, -1.0)
         has_ir = input_range is not None
         ir_all = input_range.detach().float().contiguous() if has_ir else None
-        main.wait_event(up_ready)
 
         # ---- up-projection (+ ReLU)
         nz = nz_up
@@ -160,6 +159,7 @@ class _FusedAnalogStep(torch.autograd.Function):
             a_kw = dict(a_tiles=xq)
         else:
             a_kw = dict(a_cache=xc)
+        main.wait_event(up_ready)       # (only now: the operand pre-pass above does not read the weights)
         h, _ = ops.cvmm_fwd(x2, r.token_index, r.slot_index, r.expert_offsets, pw_up, precision, P=P, dst_rows=P,
                             ir=ir_up, ir_by_expert=True, absmax=am_up, inp_res=inp_res, out_res=out_res,
                             out_bound=out_bound, out_relu=True, **a_kw, **nxt, **nz)
