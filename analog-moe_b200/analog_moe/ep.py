@@ -192,7 +192,8 @@ class PeerExchange:
     (every slot of every rank routed to one rank) and reused every step; reuse across steps is ordered by the next
     step's count all-gather.  One forward/backward pair may be in flight per layer."""
 
-    def __init__(self, group, device, p_cap: int, D: int, N: int, dtype):
+    def __init__(self, group, device, p_cap: int, D: int, N: int, dtype, small_bytes: int = 0):
+        """`small_bytes`: the largest payload `share` will carry."""
         import torch.distributed._symmetric_memory as symm
         self.group, self.device = group, device
         self.G, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -209,25 +210,67 @@ class PeerExchange:
         self.token = torch.zeros(1, device=device)
         self.generation = 0          # forward passes that have written into the buffers
         self.status = torch.zeros(4, dtype=torch.int32, device=device)   # device status word of the exchange kernels
+        # small values between the ranks (counts, a maximum, column scales) and the ordering points after the row
+        # exchanges: one kernel over peer memory each (`share`) instead of a collective of the communication library
+        self.peer_sync = os.environ.get("AMOE_EP_NCCL_SYNC", "0") != "1"
+        self.slot_bytes = 0
+        if self.peer_sync:
+            self.slot_bytes = (max(small_bytes, 64) + 15) // 16 * 16
+            slots = symm.empty(2 * self.G * self.slot_bytes, dtype=torch.uint8, device=device)
+            flags = symm.empty(max(self.G, 4), dtype=torch.int32, device=device)
+            flags.zero_()
+            torch.cuda.synchronize(device)
+            self._slots = (symm.rendezvous(slots, group), slots)
+            self._flags = (symm.rendezvous(flags, group), flags)
+            self._epoch = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+            dist.barrier(group)          # every rank's flags are zero before the first exchange
 
     def barrier(self) -> None:
-        dist.all_reduce(self.token, group=self.group)
+        if self.peer_sync:
+            self.share(None)
+        else:
+            dist.all_reduce(self.token, group=self.group)
+
+    def share(self, value: Optional[Tensor]) -> Optional[Tensor]:
+        """All-gather of a small tensor (the same shape on every rank) and a barrier, one kernel over peer memory; returns
+        [G, *value.shape].  `None`: barrier only.  Stream-ordered, no host value, capturable."""
+        if not self.peer_sync:
+            if value is None:
+                dist.all_reduce(self.token, group=self.group)
+                return None
+            out = torch.empty((self.G,) + tuple(value.shape), dtype=value.dtype, device=value.device)
+            dist.all_gather_into_tensor(out, value.contiguous(), group=self.group)
+            return out
+        out, nbytes = None, 0
+        if value is not None:
+            value = value.contiguous()
+            nbytes = value.numel() * value.element_size()
+            if nbytes > self.slot_bytes or nbytes % 4:
+                raise ValueError(f"share: {nbytes} bytes do not fit the {self.slot_bytes}-byte slots (or are not whole words)")
+            out = torch.empty((self.G,) + tuple(value.shape), dtype=value.dtype, device=value.device)
+        ops._call("amoe_ep_share", ops.ptr(value), nbytes, int(self._slots[0].buffer_ptrs_dev), self.slot_bytes,
+                  int(self._flags[0].buffer_ptrs_dev), ops.ptr(self._epoch), self.rank, self.G, ops.ptr(out), 1 << 24,
+                  ops.ptr(self.status), ops.stream_ptr())
+        return out
 
     def check(self, where: str = "expert-parallel exchange") -> None:
         """Synchronises and raises if an exchange kernel dropped a row or saw a plan larger than its buffers."""
         ops.raise_on_device_status(self.status, where)
 
     def put(self, name: str, src: Tensor, index: Tensor, sel_sorted: Tensor, El: int, plan: Tensor, src_div: int = 1,
-            row_scale: Optional[Tensor] = None) -> Tensor:
+            row_scale: Optional[Tensor] = None, barrier: bool = True) -> Tensor:
         """Row src[index[i] // src_div] (* row_scale[index[i]]) of every sorted position i to the rank that owns expert
-        sel_sorted[i]; returns this rank's whole receive buffer [cap, cols] (its first R rows are valid)."""
+        sel_sorted[i]; returns this rank's whole receive buffer [cap, cols] (its first R rows are valid).  With
+        `barrier=False` the caller issues the collective that orders the stores (one that also carries a value)."""
         hdl, buf, ptrs = self.buffers[name]
         src = src.reshape(-1, src.shape[-1])
         assert src.shape[1] == buf.shape[1] and src.dtype == buf.dtype and src.stride(-1) == 1
         ops._call("amoe_ep_put", ops.ptr(src), ops.dtype_code(src), src.stride(0), src.shape[1], src.shape[0], ops.ptr(index),
                   src_div, ops.ptr(row_scale), index.numel(), ops.ptr(sel_sorted), El, ops.ptr(plan), ptrs, self.G,
                   buf.shape[0], ops.ptr(self.status), ops.stream_ptr())
-        self.barrier()
+        if barrier:
+            self.barrier()
         return buf
 
     def put_back(self, name: str, rows: Tensor, plan: Tensor, n_own: int, barrier: bool = True) -> Tensor:
@@ -302,15 +345,14 @@ class _ExpertParallelStep(torch.autograd.Function):
         N, Fh = values.shape[-1], keys.shape[-1]
         inv = ops.invert_index(r.slot_index)
         xchg = layer._peer_exchange(P, D, N, x.dtype, part)
-        plan = send_splits = recv_splits = None
+        plan = send_splits = recv_splits = back_dst = None
         # ---- rows to their owners
         if xchg is not None:
             # everything on the device: all-gather of the counts -> plan -> stores into the owners' buffers
-            gathered = torch.empty((G, G, El), dtype=counts.dtype, device=dev)
-            dist.all_gather_into_tensor(gathered, counts, group=group)
+            gathered = xchg.share(counts)             # [G, G, El]: source, destination, local expert
             plan = ops.ep_plan(gathered, layer.rank)
             R = xchg.cap                       # rows allocated; the kernels find the real count in the plan / offsets
-            local_order, local_offsets = ops.ep_local_plan_dev(plan, G, El, R, xchg.status)
+            local_order, local_offsets, back_dst = ops.ep_local_plan_dev(plan, G, El, R, xchg.status, want_back_dst=True)
             xchg.generation += 1
             recv = xchg.put("x", x2, r.token_index, r.sel, El, plan)
         else:
@@ -377,9 +419,9 @@ class _ExpertParallelStep(torch.autograd.Function):
         adc_step = ops.adc_step(out_res, out_bound) if adc_on else 0.0
         if codes_back:
             back = xchg.put_back("yc", codes.view(torch.bfloat16), plan, P, barrier=False).view(torch.int8)
-            scale_back = xchg.put_back("ys", meta["row_scale"].view(-1, 1), plan, P).view(-1)
-            cs_all = torch.empty((G * El, N), dtype=torch.float32, device=dev)       # column scales of every expert
-            dist.all_gather_into_tensor(cs_all, pw_dn.col_scale.contiguous(), group=group)
+            scale_back = xchg.put_back("ys", meta["row_scale"].view(-1, 1), plan, P, barrier=False).view(-1)
+            # column scales of every expert; the exchange is also the point that orders the two sets of stores above
+            cs_all = xchg.share(pw_dn.col_scale.float()).view(G * El, N)
             y = ops.combine_codes(back, cs_all, r.raw_sel, scale_back, adc_step, gate, T, k, out_dtype=x.dtype,
                                   row_index=inv)
         else:
@@ -391,12 +433,13 @@ class _ExpertParallelStep(torch.autograd.Function):
             y = ops.combine(back, gate, T, k, row_index=inv)
         simt = precision == ops.A.PREC_FP32_SIMT
         ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv, r.sel,
-                              local_order, local_offsets, ir_all,
+                              local_order, local_offsets, back_dst, ir_all,
                               pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
                               *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)), cs_all, scale_back)
         ctx.adc_step = adc_step
         ctx.operand_prepass = layer.operand_prepass
+        ctx.fused_back = getattr(layer, "fused_put_back", True)
         ctx.generation = xchg.generation if xchg is not None else 0
         if layer.keep_codes:      # ADC codes of the down-projection by flat slot (parity checks)
             layer.last_codes = back[inv.long()] if codes_back else None
@@ -406,12 +449,14 @@ class _ExpertParallelStep(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets, ir_all,
+        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets,
+         back_dst, ir_all,
          w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo, cs_all, scale_back) = ctx.saved_tensors
         (x_shape, El, k, precision, ir_p, keys_dtype, values_dtype, kshape, vshape, ir_dtype, send_splits, recv_splits,
          group, plan, xchg) = ctx.meta
         T, D = x2.shape
         P, R = T * k, recv.shape[0]
+        layer_fused_back = ctx.fused_back
         if xchg is not None and xchg.generation != ctx.generation:
             raise RuntimeError("expert-parallel layer: a later forward pass of this layer has overwritten the exchange "
                                "buffers this backward pass reads (one forward/backward pair per layer may be in flight)")
@@ -436,28 +481,56 @@ class _ExpertParallelStep(torch.autograd.Function):
         keeps = torch.zeros(2, dtype=torch.int64, device=dev) if (has_ir and decay > 0) else None
         ir_up, ir_dn = (ir_all[0], ir_all[1]) if has_ir else (None, None)
         gate_flat = gate.reshape(-1)
-        # ---- gate gradient at the source, gate * gy rows to the owners
+        # ---- gate gradient and the router's weight gradient at the source: they need only what this rank saved and the
+        # upstream gradient, so they run on a stream of their own beside the exchange of the gradient rows (whose kernel
+        # waits on NVLink, not on the SMs).  That stream has the main chain's priority: these are large grids off the
+        # critical path, and at the higher priority they held back the small kernels that follow the exchange.
+        main, side, bg = torch.cuda.current_stream(), ops.side_stream(dev), ops.side_stream(dev, 2, high_priority=False)
+        side.wait_stream(main)
+        bg.wait_stream(main)
+        grad_sel = None
+        f16_peer = xchg is not None and precision == ops.A.PREC_F16X1
+        if f16_peer:
+            # fp16 operands need max|gate * gy| over the rows a rank receives.  Any bound shared by the ranks serves (it only
+            # picks a power-of-two scale): max|gy| * max|gate| of this rank, turned into the maximum over the ranks by the
+            # all-reduce that orders the stores anyway - no pass over the received rows
+            with ops.launch_on(side):
+                ops.set_tag("down")
+                gm_g, gm_gate = ops.tensor_absmax(g), ops.tensor_absmax(gate)
+                gm_ready = side.record_event()
+        with ops.launch_on(bg):
+            ops.set_tag("down")
+            if cs_all is not None:      # `back` holds ADC codes
+                dgate = ops.row_dot_codes(back, cs_all, raw_sel.reshape(-1), scale_back, ctx.adc_step, g, k, row_index=inv)
+            else:
+                dgate = ops.row_dot(back, g, k, row_index=inv)
+            dgate_ready = bg.record_event()
+            if need_sel and ops._router_fits_smem(w_sel.shape[0], D):
+                ops.set_tag("up")
+                grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
+                                                 raw_sel=raw_sel)
+        # ---- gate * gy rows to the owners
         ops.set_tag("down")
-        if cs_all is not None:      # `back` holds ADC codes
-            dgate = ops.row_dot_codes(back, cs_all, raw_sel.reshape(-1), scale_back, ctx.adc_step, g, k, row_index=inv)
-        else:
-            dgate = ops.row_dot(back, g, k, row_index=inv)
+        gmax = None
         if xchg is not None:
-            g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat)
+            g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat, barrier=not f16_peer)
+            if f16_peer:
+                main.wait_event(gm_ready)
+                gmax = xchg.share(gm_g * gm_gate).max().reshape(1)
         else:
             drows, _ = ops.ep_pack(g, slot_index, src_div=k, row_scale=gate_flat)
             g_recv = drows.new_empty((R, N))
             dist.all_to_all_single(g_recv, drows, recv_splits, send_splits, group=group)
             del drows
         grad_keys = grad_values = None
-        main, side = torch.cuda.current_stream(), ops.side_stream(dev)
-        forked = False
+        dx_to_peers = (xchg is not None and need_x and layer_fused_back and precision != ops.A.PREC_FP32_SIMT and D % 16 == 0
+                       and P < (1 << 24) and x2.dtype in (torch.float32, torch.bfloat16))
         if R > 0:
             split = xc_lo is not None
             gc = ops.OperandCache.empty(R, El, N, split, dev) if cached and need_values else None
             dhc = ops.OperandCache.empty(R, El, Fh, split, dev) if cached and need_keys else None
-            # fp16 operands: max|g| over the rows that really arrived (the buffer has worst-case size)
-            gmax = ops.grad_absmax(g_recv, precision, plan[0:1] if xchg is not None else None)
+            if xchg is None:
+                gmax = ops.grad_absmax(g_recv, precision)      # fp16 operands: max|g| over the rows that arrived
             if need_values and not cached:
                 grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
                                           ir_by_expert=True, g_absmax=gmax)
@@ -471,14 +544,20 @@ class _ExpertParallelStep(torch.autograd.Function):
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
                                      out_dtype=h.dtype, x_ref_relu=True, out_cache=dhc, g_absmax=gmax, **a_kw)
             ops.set_tag("up")
+            # The input-gradient rows leave the kernel's epilogue for the buffers of the ranks they belong to (stores over
+            # NVLink while the next tiles' MMAs run) instead of a local buffer and a copy kernel afterwards.
+            peer_out = None
+            if dx_to_peers:
+                _, dx_buf, dx_ptrs = xchg.buffers["dx"]
+                peer_out = (dx_buf, dx_ptrs, xchg.G, back_dst)
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
                                       ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                       keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype,
-                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None, g_absmax=gmax)
+                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None, g_absmax=gmax,
+                                      peer_out=peer_out)
             # the two weight gradients on a second stream, beside the exchange and the streaming kernels that follow
-            forked = cached and (need_values or need_keys)
-            if forked:
+            if cached and (need_values or need_keys):
                 side.wait_stream(main)
                 with ops.launch_on(side):
                     if need_values:
@@ -503,25 +582,36 @@ class _ExpertParallelStep(torch.autograd.Function):
         # ---- input-gradient rows back to the source; sum over k plus the router's term
         ops.set_tag("up")
         grad_x = None
+        # The input-range decay term's threshold is one fraction over ALL routed pairs (reference cvmm.py:872-878): kept
+        # elements and rows are summed over the ranks on the device (one small all-reduce, no host read), so the result is
+        # the dense layer's whatever the load balance.  With rows going back through peer memory that all-reduce is also
+        # the point that orders the stores.
+        tot, tot_summed = None, False
+        if need_ir and keeps is not None:
+            tot = torch.cat([keeps, local_offsets[-1:].to(torch.int64)])     # kept (up), kept (down), rows here
         if need_x:
             if xchg is not None:
-                dback = xchg.put_back("dx", dxr, plan, P)
+                if dx_to_peers:
+                    dback = xchg.buffers["dx"][1][:P]
+                    if tot is None:
+                        xchg.barrier()
+                else:
+                    dback = xchg.put_back("dx", dxr, plan, P, barrier=tot is None)
+                if tot is not None:
+                    tot = xchg.share(tot).sum(0)
+                    tot_summed = True
             else:
                 dback = dxr.new_empty((P, D))
                 dist.all_to_all_single(dback, dxr, send_splits, recv_splits, group=group)
+            main.wait_event(dgate_ready)
             grad_x = ops.combine_router(dback, T, k, dgate, gate, raw_sel, w_sel, row_index=inv).view(x_shape)
-        grad_sel = None
-        if need_sel:
+        if need_sel and grad_sel is None:
+            main.wait_event(dgate_ready)
             grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
                                              raw_sel=raw_sel).to(w_sel.dtype)
         grad_ir = None
         if need_ir:
-            # The decay term's threshold is one fraction over ALL routed pairs (reference cvmm.py:872-878): kept
-            # elements and rows are summed over the ranks on the device (one small all-reduce, no host read), so the
-            # result is the dense layer's whatever the load balance.
-            tot = None
-            if keeps is not None:
-                tot = torch.cat([keeps, local_offsets[-1:].to(torch.int64)])     # kept (up), kept (down), rows here
+            if tot is not None and not tot_summed:
                 dist.all_reduce(tot, group=group)
             if R > 0:
                 grad_ir = torch.stack([
@@ -533,8 +623,10 @@ class _ExpertParallelStep(torch.autograd.Function):
                                        cols=Fh)]).to(ir_dtype)
             else:
                 grad_ir = torch.zeros(2, El, dtype=ir_dtype, device=dev)
-        if forked:
-            main.wait_stream(side)
+        main.wait_stream(side)
+        main.wait_stream(bg)
+        if grad_sel is not None:
+            grad_sel = grad_sel.to(w_sel.dtype)
         if grad_values is not None:
             grad_values = grad_values.to(values_dtype)
         if grad_keys is not None:
@@ -560,6 +652,9 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         # step against 1.05 ms for one - the CVMM kernels hold every SM's registers and shared memory, so the other
         # micro-batch's exchange kernels wait for them instead of running beside them, and every kernel is paid twice.
         self.micro_batches = int(kwargs.pop("micro_batches", os.environ.get("AMOE_EP_MICRO_BATCHES", 1)))
+        # input-gradient rows go back to their sources from the CVMM kernel's epilogue (peer stores) rather than through a
+        # local buffer and a copy kernel
+        self.fused_put_back = os.environ.get("AMOE_EP_FUSED_BACK", "0") == "1"
         self.max_slots = int(kwargs.pop("max_slots", 0))
         if kwargs.get("bias"):
             raise NotImplementedError("expert-parallel layer: bias is not built")
@@ -588,7 +683,8 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
                 raise RuntimeError("first call under stream capture")
             m = torch.tensor([max(P, self.max_slots)], dtype=torch.int64, device=self.keys.device)
             dist.all_reduce(m, op=dist.ReduceOp.MAX, group=self.group)
-            self._xchgs[part] = PeerExchange(self.group, self.keys.device, int(m.item()), D, N, dtype)
+            small = max(self.n_experts * N * 4, self.world * self.n_experts * 4, 64)   # column scales / count matrix
+            self._xchgs[part] = PeerExchange(self.group, self.keys.device, int(m.item()), D, N, dtype, small_bytes=small)
             if part == 0:
                 self._xchg = self._xchgs[0]
             return self._xchgs[part]

@@ -79,16 +79,19 @@ def _call_traced(name: str, *args) -> None:
 _SIDE_STREAMS = {}
 
 
-def side_stream(device: torch.device, index: int = 0) -> torch.cuda.Stream:
+def side_stream(device: torch.device, index: int = 0, high_priority: bool = True) -> torch.cuda.Stream:
     """Extra streams per device (`index` 0, 1, ...) for work that runs beside the main chain (the weight pre-passes, the weight
-    gradients).  It has the higher priority: its kernels are few and small in thread blocks (a TMA-fed dW kernel is one
-    CTA of six warps per SM), and what waits for them sits on the critical path, so their blocks should get the SMs
-    ahead of the main stream's large streaming grids, which then fill in beside them."""
+    gradients).  By default a stream has the higher priority: its kernels are few and small in thread blocks (a TMA-fed dW
+    kernel is one CTA of six warps per SM), and what waits for them sits on the critical path, so their blocks should get
+    the SMs ahead of the main stream's large streaming grids, which then fill in beside them.  `high_priority=False`: for
+    large grids that are NOT on the critical path - at the higher priority they would hold back every small kernel of the
+    main chain until their last block has been placed."""
     dev = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
-    key = (dev, index)
+    key = (dev, index, high_priority)
     st = _SIDE_STREAMS.get(key)
     if st is None:
-        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=dev, priority=-1)
+        prio = int(os.environ.get("AMOE_SIDE_PRIORITY", "-1")) if high_priority else 0
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device=dev, priority=prio)
     return st
 
 
@@ -545,13 +548,20 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
             ir_by_expert: bool = False, x_ref_relu: bool = False, a_cache: Optional["OperandCache"] = None,
             out_cache: Optional["OperandCache"] = None, a_tiles: Optional["OperandCache"] = None,
-            g_absmax: Optional[torch.Tensor] = None, want_out: bool = True):
+            g_absmax: Optional[torch.Tensor] = None, want_out: bool = True, peer_out=None):
     """`a_tiles`: the A operand as an operand cache written by an earlier kernel (TMA-fed, no gather); g2 then only
     gives dtype and device.  `g_absmax`: the device scalar of the fp16 precision (see tensor_absmax).  `want_out=False`
-    (with `out_cache`): only the operand cache is written."""
+    (with `out_cache`): only the operand cache is written.  `peer_out=(own_buffer, peer_ptrs_dev, n_peers, peer_dst)`:
+    the result rows are stored from the epilogue into the peers' buffers (`own_buffer` is this rank's one, all of
+    the same shape; peer_ptrs_dev the device address of the array of their base addresses); the first result is None."""
     g2 = _rows(g2)
     dev = g2.device
-    out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev) if want_out else None
+    if peer_out is not None:
+        out = peer_out[0]
+        if out.dtype != (out_dtype or g2.dtype) or out.shape[1] != pw.K or out.stride(1) != 1:
+            raise ValueError("peer_out: the buffers must hold rows of the result's width and type")
+    else:
+        out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev) if want_out else None
     ir_grad = torch.empty(P, dtype=torch.float32, device=dev) if want_ir_grad else None
     a = A.CvmmArgs()
     a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
@@ -584,8 +594,10 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     a.ir_grad_relative, a.ir_grad_scale = int(relative), float(grad_scale)
     a.keep_count = ptr(keep_count)
     a.dev_status = ptr(status)
+    if peer_out is not None:
+        a.peer_ptrs, a.n_peers, a.peer_dst, a.peer_rows = int(peer_out[1]), int(peer_out[2]), ptr(peer_out[3]), out.shape[0]
     _call("amoe_cvmm_dx", C.byref(a), stream_ptr())
-    return out, ir_grad
+    return (None if peer_out is not None else out), ir_grad
 
 
 def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torch.Tensor, offsets: torch.Tensor,
@@ -816,12 +828,15 @@ def ep_plan(gathered: torch.Tensor, rank: int) -> torch.Tensor:
     return plan
 
 
-def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int,
-                      status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int, status: Optional[torch.Tensor] = None,
+                      want_back_dst: bool = False):
+    """(local_order, local_offsets[, back_dst]) of this step's plan.  back_dst: for every expert-sorted position, the
+    rank the row came from and its place there, as `cvmm_dx(peer_out=...)` takes it."""
     order = torch.empty(cap, dtype=torch.int32, device=plan.device)
     offsets = torch.empty(El + 1, dtype=torch.int32, device=plan.device)
-    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), ptr(status), stream_ptr())
-    return order, offsets
+    back = torch.empty(cap, dtype=torch.int32, device=plan.device) if want_back_dst else None
+    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), ptr(back), ptr(status), stream_ptr())
+    return (order, offsets, back) if want_back_dst else (order, offsets)
 
 
 def invert_index(idx: torch.Tensor) -> torch.Tensor:

@@ -53,10 +53,12 @@ __global__ void ep_plan_kernel(const int32_t* __restrict__ gathered, int me, int
   }
 }
 
-// local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.
+// local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.  back_dst (optional):
+// for every expert-sorted position, the rank its row came from and the row's place there.
 __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* __restrict__ plan, int G, int El, int cap,
                                                                 int32_t* __restrict__ local_order,
                                                                 int32_t* __restrict__ local_offsets,
+                                                                int32_t* __restrict__ back_dst,
                                                                 int32_t* __restrict__ status) {
   __shared__ int s_recv_start[kEpMaxBlocksDev + 1];
   __shared__ int s_sorted_start[kEpMaxBlocksDev];
@@ -84,7 +86,15 @@ __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* _
     }
     // a position in the full permutation of plan[0] rows: it lies inside the array only if the plan fits the buffer
     const int pos = s_sorted_start[lo] + (r - s_recv_start[lo]);
-    if (pos < cap) local_order[pos] = r;
+    if (pos < cap) {
+      local_order[pos] = r;
+      if (back_dst != nullptr) {
+        // where the row goes back to: its place in the source rank's sorted slot list, as (rank << 24) | row
+        const int g = lo / El;
+        const int row = plan[2 + 3 * G + g] + (r - s_recv_start[g * El]);
+        back_dst[pos] = (row >= 0 && row < (1 << 24)) ? ((g << 24) | row) : -1;
+      }
+    }
   }
 }
 
@@ -202,6 +212,66 @@ __global__ void __launch_bounds__(128, 16) ep_put_back_kernel(const T* __restric
   }
 }
 
+
+// ---------------------------------------------------------------------------- small exchange + barrier in one launch
+// Every rank hands a few bytes to every other rank and learns that all ranks have arrived: the count matrix of a step,
+// a per-rank maximum, the column scales of the local experts - or nothing at all, when only the ordering of earlier
+// peer stores matters.  One CTA: (1) this rank's payload is stored into slot [parity][rank] of every rank's slot
+// buffer; (2) thread p raises this rank's flag in rank p's flag array to the new epoch (release, system scope) and waits
+// until rank p's flag in the own array has reached it (acquire, system scope); (3) the G payloads are copied out of the
+// own slot buffer.  Epochs only grow (a device counter per rank, advanced by this kernel, so a captured graph replays
+// correctly); payload slots alternate with the epoch's parity: a rank can only be one exchange ahead of the slowest
+// reader, never two.  Every wait is bounded: after `spin_limit` polls the kernel records AMOE_ERR_WAIT_LIMIT and returns.
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) ep_share_kernel(const uint32_t* __restrict__ payload, int words,
+                                                       const uint64_t* __restrict__ slot_ptrs, int64_t slot_words,
+                                                       const uint64_t* __restrict__ flag_ptrs, uint32_t* __restrict__ epoch_ctr,
+                                                       int me, int G, uint32_t* __restrict__ out, long long spin_limit,
+                                                       int32_t* __restrict__ status) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_gave_up;
+  // an earlier exchange that gave up is latched in the status word: do not wait the limit out again on every call
+  if (threadIdx.x == 0) { s_epoch = *epoch_ctr + 1u; s_gave_up = (status != nullptr && status[0] == AMOE_ERR_WAIT_LIMIT) ? 1 : 0; }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int64_t par = epoch & 1u;
+  for (int p = 0; p < G; ++p) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(slot_ptrs[p]) + (par * G + me) * slot_words;
+    for (int w = threadIdx.x; w < words; w += blockDim.x) dst[w] = payload[w];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < G) {
+    const int p = threadIdx.x;
+    st_release_sys(reinterpret_cast<uint32_t*>(flag_ptrs[p]) + me, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(flag_ptrs[me]) + p;
+    long long polls = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if (s_gave_up || ++polls > spin_limit) {
+        s_gave_up = 1;
+        report(status, AMOE_ERR_WAIT_LIMIT, 55, p, static_cast<int>(epoch));
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *epoch_ctr = epoch;
+  if (out != nullptr && !s_gave_up) {
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(slot_ptrs[me]) + par * G * slot_words;
+    for (int g = 0; g < G; ++g)
+      for (int w = threadIdx.x; w < words; w += blockDim.x) out[static_cast<int64_t>(g) * words + w] = src[g * slot_words + w];
+  }
+}
+
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -223,14 +293,14 @@ int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, i
 }
 
 int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
-                           int32_t* local_offsets, int32_t* dev_status, amoe_stream_t stream_) {
+                           int32_t* local_offsets, int32_t* back_dst, int32_t* dev_status, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(plan && local_order && local_offsets, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(G > 0 && El > 0 && G * El <= kEpMaxBlocksDev && cap_rows > 0 && cap_rows < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
   int64_t blocks = (cap_rows + 255) / 256;
   if (blocks > 592) blocks = 592;
   ep_local_plan_dev_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(plan, G, El, static_cast<int>(cap_rows), local_order,
-                                                                             local_offsets, dev_status);
+                                                                             local_offsets, back_dst, dev_status);
   AMOE_LAUNCH_CHECK("ep_local_plan_dev");
   return AMOE_OK;
 }
@@ -278,6 +348,21 @@ int amoe_ep_put_back(const void* rows, int32_t dtype, int64_t stride, int32_t K,
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("ep_put_back");
+  return AMOE_OK;
+}
+
+int amoe_ep_share(const void* payload, int64_t nbytes, const uint64_t* slot_ptrs, int64_t slot_bytes,
+                  const uint64_t* flag_ptrs, uint32_t* epoch, int32_t rank, int32_t G, void* gathered,
+                  int64_t spin_limit, int32_t* dev_status, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(slot_ptrs && flag_ptrs && epoch, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(nbytes == 0 || payload != nullptr, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(G > 0 && G <= kEpMaxRanks && rank >= 0 && rank < G && nbytes >= 0 && nbytes % 4 == 0 && slot_bytes % 4 == 0 &&
+               nbytes <= slot_bytes && spin_limit > 0, AMOE_ERR_BAD_SHAPE);
+  ep_share_kernel<<<1, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(payload), static_cast<int>(nbytes / 4), slot_ptrs,
+                                         slot_bytes / 4, flag_ptrs, epoch, rank, G, reinterpret_cast<uint32_t*>(gathered),
+                                         spin_limit, dev_status);
+  AMOE_LAUNCH_CHECK("ep_share");
   return AMOE_OK;
 }
 

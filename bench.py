@@ -270,7 +270,7 @@ def run_ours(args, cfg, rank, world, device):
         import torch.distributed as dist
         group = dist.group.WORLD
     parity = None
-    if not args.steps_only:
+    if not args.steps_only and not args.timeline:
         parity = ep_parity_gate(cfg, rank, world, device, group) if world > 1 else \
             single_gpu_parity_gate(cfg, device, precision)
     layer = build_layer(cfg, device, dtype, precision, ep_group=group)
@@ -341,6 +341,12 @@ def run_ours(args, cfg, rank, world, device):
             return ys[i % n_sets]
         return step(layer, xs[i % n_sets], gys[i % n_sets], bwd)
 
+    if args.timeline:
+        from analog_moe.profiling import timeline
+        barrier()
+        timeline(args.timeline, run_step, rank)
+        barrier()
+        return None
     barrier()
     sampler = ClockSampler(device.index or 0)
     sampler.start()
@@ -602,6 +608,8 @@ def main():
                     help="launch every step eagerly instead of replaying a CUDA graph of the step")
     ap.add_argument("--kernel-times", default=None, metavar="PATH",
                     help="instead of the timed run: write per-kernel device times of three eager steps to PATH")
+    ap.add_argument("--timeline", default=None, metavar="PATH",
+                    help="instead of the timed run: write rank 0's kernel timeline of one (graph-replayed) step to PATH")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     rank = int(os.environ.get("RANK", 0))
