@@ -13,7 +13,7 @@ import torch
 
 from . import _build
 
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
 PREC_BF16X1, PREC_SPLIT, PREC_FP32_SIMT, PREC_F16X1 = 0, 1, 2, 3
 PRECISION_NAMES = {"bf16": PREC_BF16X1, "bf16x1": PREC_BF16X1, "split": PREC_SPLIT, "fp32": PREC_FP32_SIMT,
                    "simt": PREC_FP32_SIMT, "f16": PREC_F16X1, "f16x1": PREC_F16X1, "fp16": PREC_F16X1}
@@ -56,6 +56,7 @@ class OperandTilesArgs(C.Structure):
         ("cache_rows", C.c_int64),
         ("g_absmax_dev", vp),
         ("dev_status", vp),
+        ("a_row_absmax", vp),
     ]
 
 
@@ -155,6 +156,8 @@ SIGNATURES = {
     "amoe_ep_local_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp]),
     "amoe_ep_plan_ints": (C.c_int64, [C.c_int32, C.c_int32]),
     "amoe_ep_plan": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int32, vp, vp]),
+    "amoe_ep_put_f16": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp, vp, vp,
+                                  C.c_int32, C.c_int64, vp, vp]),
     "amoe_ep_share": (C.c_int, [vp, C.c_int64, vp, C.c_int64, vp, vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, vp]),
     "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp, vp, vp]),
     "amoe_ep_put": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp,

@@ -203,6 +203,9 @@ class PeerExchange:
         # "yc" / "ys": the down-projection's rows as ADC codes (int8, moved as N/2 two-byte elements) and one scale per row
         shapes = {"x": (self.cap, D, dtype), "g": (self.cap, N, dtype), "y": (p_cap, N, dtype), "dx": (p_cap, D, dtype),
                   "yc": (p_cap, (N + 1) // 2, torch.bfloat16), "ys": (p_cap, 1, torch.float32)}
+        if dtype == torch.float32:
+            # gradient rows of the fp16 precision: fp16, each scaled for its own maximum, and the maxima
+            shapes.update({"g16": (self.cap, N, torch.float16), "g16m": (self.cap, 1, torch.float32)})
         for name, (rows, cols, dt) in shapes.items():
             t = symm.empty(rows, cols, dtype=dt, device=device)
             hdl = symm.rendezvous(t, group)
@@ -272,6 +275,19 @@ class PeerExchange:
         if barrier:
             self.barrier()
         return buf
+
+    def put_f16(self, src: Tensor, index: Tensor, sel_sorted: Tensor, El: int, plan: Tensor, src_div: int = 1,
+                row_scale: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+        """`put` of fp32 gradient rows as fp16 (half the bytes over NVLink): every row scaled by the power of two of its
+        own maximum.  Returns this rank's receive buffers (rows [cap, cols] fp16, maxima [cap] fp32); no barrier."""
+        _, buf, ptrs = self.buffers["g16"]
+        _, mbuf, mptrs = self.buffers["g16m"]
+        src = src.reshape(-1, src.shape[-1])
+        assert src.shape[1] == buf.shape[1] and src.dtype == torch.float32 and src.stride(-1) == 1
+        ops._call("amoe_ep_put_f16", ops.ptr(src), src.stride(0), src.shape[1], src.shape[0], ops.ptr(index), src_div,
+                  ops.ptr(row_scale), index.numel(), ops.ptr(sel_sorted), El, ops.ptr(plan), ptrs, mptrs, self.G, buf.shape[0],
+                  ops.ptr(self.status), ops.stream_ptr())
+        return buf, mbuf.view(-1)
 
     def put_back(self, name: str, rows: Tensor, plan: Tensor, n_own: int, barrier: bool = True) -> Tensor:
         """The first R rows of `rows` (receive order) back to their sources; returns this rank's buffer [n_own, cols]."""
@@ -512,8 +528,15 @@ class _ExpertParallelStep(torch.autograd.Function):
         # ---- gate * gy rows to the owners
         ops.set_tag("down")
         gmax = None
+        g_rowmax = None
+        # fp32 gradient rows of the fp16 precision cross NVLink as fp16 when everything downstream takes tiles
+        g_half = (f16_peer and "g16" in xchg.buffers and ctx.operand_prepass and N % 64 == 0 and g.dtype == torch.float32
+                  and (cached or not need_values) and g.data_ptr() % 16 == 0 and (g.stride(0) * 4) % 16 == 0)
         if xchg is not None:
-            g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat, barrier=not f16_peer)
+            if g_half:
+                g_recv, g_rowmax = xchg.put_f16(g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat)
+            else:
+                g_recv = xchg.put("g", g, slot_index, sel_sorted, El, plan, src_div=k, row_scale=gate_flat, barrier=not f16_peer)
             if f16_peer:
                 main.wait_event(gm_ready)
                 gmax = xchg.share(gm_g * gm_gate).max().reshape(1)
@@ -535,10 +558,13 @@ class _ExpertParallelStep(torch.autograd.Function):
                 grad_values = ops.cvmm_dw(h, local_order, g_recv, local_order, local_offsets, El, precision, P=R, ir=ir_dn,
                                           ir_by_expert=True, g_absmax=gmax)
             if ctx.operand_prepass and ops.operand_tiles_ok(g_recv, precision):
-                gc, _ = ops.operand_tiles(g_recv, local_order, local_offsets, El, precision, P=R, dac=False, g_absmax=gmax)
+                gc, _ = ops.operand_tiles(g_recv, local_order, local_offsets, El, precision, P=R, dac=False, g_absmax=gmax,
+                                          row_absmax=g_rowmax)
                 a_kw = dict(a_tiles=gc)
             else:
                 a_kw = dict(a_cache=gc)
+            if g_half:
+                g_recv = xchg.buffers["g"][1]       # (with tiles the kernel takes only type and shape from this argument)
             dh, irs_dn = ops.cvmm_dx(g_recv, local_order, local_order, local_offsets, pw_dn, precision, P=R, dst_rows=R,
                                      x_ref=h, x_ref_row=local_order, ir=ir_dn, ir_by_expert=True, want_ir_grad=has_ir,
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,

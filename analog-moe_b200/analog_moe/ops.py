@@ -652,10 +652,12 @@ def operand_tiles(x2: torch.Tensor, a_row: torch.Tensor, offsets: torch.Tensor, 
                   a_row_div: int = 1, dac: bool = True, ir: Optional[torch.Tensor] = None, ir_by_expert: bool = False,
                   absmax: Optional[torch.Tensor] = None, inp_res: float = -1.0, want_tiles: bool = True,
                   want_cache: bool = False, cache_scale: Optional[torch.Tensor] = None,
-                  g_absmax: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None):
+                  g_absmax: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                  row_absmax: Optional[torch.Tensor] = None):
     """The A operand of a CVMM call as TMA tiles, by a streaming pre-pass (amoe_operand_tiles).  Returns
     (tiles or None, cache or None): `tiles` goes to cvmm_fwd / cvmm_dx as `a_tiles`, `cache` (forward operands only:
-    the clamped, unquantised rows) to cvmm_dw_cached.  For gradient rows (dac=False) the tiles are both."""
+    the clamped, unquantised rows) to cvmm_dw_cached.  For gradient rows (dac=False) the tiles are both.
+    fp16 rows (gradient rows of the fp16 precision that arrived scaled row by row) come with `row_absmax`."""
     x2 = _rows(x2)
     K = x2.shape[-1]
     split = precision == A.PREC_SPLIT
@@ -670,7 +672,9 @@ def operand_tiles(x2: torch.Tensor, a_row: torch.Tensor, offsets: torch.Tensor, 
     a = A.OperandTilesArgs()
     a.P, a.E, a.K, a.precision = P, E, K, precision
     a.expert_offsets = ptr(offsets)
-    a.a, a.a_dtype, a.a_stride, a.a_rows = ptr(x2), dtype_code(x2), x2.stride(0), x2.shape[0]
+    a.a, a.a_stride, a.a_rows = ptr(x2), x2.stride(0), x2.shape[0]
+    a.a_dtype = A.F16 if x2.dtype == torch.float16 else dtype_code(x2)
+    a.a_row_absmax = ptr(row_absmax)
     a.a_row, a.a_row_div, a.dac = ptr(a_row), a_row_div, int(dac)
     a.ir, a.ir_by_expert, a.a_absmax, a.inp_res = ptr(ir), int(ir_by_expert), ptr(absmax), float(inp_res)
     if tiles is not None:

@@ -184,6 +184,63 @@ __global__ void __launch_bounds__(128, 16) ep_put_kernel(const T* __restrict__ x
   copy_row<T>(x + (sr / src_div) * stride, dst, K, vec != 0, row_scale ? row_scale[sr] : 1.f, row_scale != nullptr, lane);
 }
 
+
+// ep_put_kernel for fp32 gradient rows of the fp16 precision: the row (times its gate) is stored as fp16, scaled by the
+// power of two of its own maximum, and the maximum goes to the same row of the destination's scale buffer.  Two passes
+// over the source row (maximum, then conversion): the second one hits L1/L2.  Eight elements per lane and step, one
+// 16-byte store each: a warp writes 512 contiguous bytes, as the plain copy does.
+__global__ void __launch_bounds__(128, 16) ep_put_f16_kernel(const float* __restrict__ x, int64_t stride, int K,
+                              const int32_t* __restrict__ src_row, int src_div, const float* __restrict__ row_scale, int64_t P,
+                              const int32_t* __restrict__ sel_sorted, int El, const int32_t* __restrict__ plan,
+                              const uint64_t* __restrict__ peer_ptrs, const uint64_t* __restrict__ scale_ptrs, int G,
+                              int64_t peer_rows, int64_t x_rows, int32_t* __restrict__ status) {
+  const int lane = threadIdx.x & 31;
+  const int64_t i = spread_row((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, P);
+  if (i >= P) return;
+  const int d = sel_sorted[i] / El;
+  const int64_t sr = src_row[i];
+  if (d < 0 || d >= G || sr < 0 || sr / src_div >= x_rows) {
+    if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 56, static_cast<int>(i), static_cast<int>(sr));
+    return;
+  }
+  const int64_t dst_row = static_cast<int64_t>(plan[2 + G + d]) + (i - plan[2 + d]);
+  if (dst_row < 0 || dst_row >= peer_rows) {      // the row is dropped, and said so
+    if (lane == 0) report(status, AMOE_ERR_INDEX_RANGE, 57, static_cast<int>(i), static_cast<int>(dst_row));
+    return;
+  }
+  const float4* s4 = reinterpret_cast<const float4*>(x + (sr / src_div) * stride);
+  const float sc = row_scale ? row_scale[sr] : 1.f;
+  const int n8 = K / 8;
+  float amax = 0.f;
+  for (int q = lane; q < n8; q += 32) {
+    const float4 a = __ldg(s4 + 2 * q), b = __ldg(s4 + 2 * q + 1);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  amax *= fabsf(sc);        // max|sc * v| (rounding of the product aside: a bound with a factor of two to spare)
+  float inv;
+  const float mul = sc * grad_pow2_scale(amax, inv);
+  uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(peer_ptrs[d]) + dst_row * K);
+  for (int q0 = lane; q0 < n8; q0 += 64) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (q0 + 32 * u < n8) { v[2 * u] = __ldg(s4 + 2 * (q0 + 32 * u)); v[2 * u + 1] = __ldg(s4 + 2 * (q0 + 32 * u) + 1); }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (q0 + 32 * u >= n8) break;
+      const float4 a = v[2 * u], b = v[2 * u + 1];
+      __half2 h0 = __floats2half2_rn(a.x * mul, a.y * mul), h1 = __floats2half2_rn(a.z * mul, a.w * mul);
+      __half2 h2 = __floats2half2_rn(b.x * mul, b.y * mul), h3 = __floats2half2_rn(b.z * mul, b.w * mul);
+      d4[q0 + 32 * u] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                   *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    }
+  }
+  if (lane == 0) reinterpret_cast<float*>(scale_ptrs[d])[dst_row] = amax;
+}
+
 // Row r of this rank's receive-ordered buffer -> its place in the source rank's sorted slot list.
 template <typename T>
 __global__ void __launch_bounds__(128, 16) ep_put_back_kernel(const T* __restrict__ rows, int64_t stride, int K, const int32_t* __restrict__ plan,
@@ -325,6 +382,22 @@ int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t
   else
     return AMOE_ERR_BAD_DTYPE;
   AMOE_LAUNCH_CHECK("ep_put");
+  return AMOE_OK;
+}
+
+int amoe_ep_put_f16(const float* x, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row, int32_t src_div,
+                    const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El, const int32_t* plan,
+                    const uint64_t* peer_ptrs, const uint64_t* scale_ptrs, int32_t G, int64_t peer_rows,
+                    int32_t* dev_status, amoe_stream_t stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  AMOE_REQUIRE(x && src_row && sel_sorted && plan && peer_ptrs && scale_ptrs, AMOE_ERR_NULL_POINTER);
+  AMOE_REQUIRE(P > 0 && K > 0 && K % 8 == 0 && El > 0 && G > 0 && G <= kEpMaxRanks && src_div >= 1 && peer_rows > 0 && x_rows > 0,
+               AMOE_ERR_BAD_SHAPE);
+  AMOE_REQUIRE(al16(x) && (stride * 4) % 16 == 0, AMOE_ERR_BAD_SHAPE);      // peer bases are page aligned
+  const unsigned blocks = static_cast<unsigned>((spread_count(P) * 32 + 127) / 128);
+  ep_put_f16_kernel<<<blocks, 128, 0, stream>>>(x, stride, K, src_row, src_div, row_scale, P, sel_sorted, El, plan, peer_ptrs,
+                                                scale_ptrs, G, peer_rows, x_rows, dev_status);
+  AMOE_LAUNCH_CHECK("ep_put_f16");
   return AMOE_OK;
 }
 

@@ -37,6 +37,7 @@ struct OperandParams {
   uint16_t* cache_hi; uint16_t* cache_lo; const float* cache_scale;
   int64_t cache_rows;
   const float* g_absmax;
+  const float* a_row_absmax;   // fp16 input rows: the maximum each row was scaled for
   int32_t* status;
 };
 
@@ -86,9 +87,18 @@ __device__ __forceinline__ void dac8(float v[8], bool has_ir, float ir, float rc
   }
 }
 
-template <bool A_F32>
+// A_T: element type of the input rows - 0 bf16, 1 fp32, 2 fp16
+template <int A_T>
 __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float v[8]) {
-  if (A_F32) {
+  if (A_T == 2) {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + elem_off));
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[x]));
+      v[2 * x] = f.x; v[2 * x + 1] = f.y;
+    }
+  } else if (A_T == 1) {
     const float4* q = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + elem_off);
     const float4 x = __ldg(q), y = __ldg(q + 1);
     v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
@@ -107,13 +117,14 @@ __device__ __forceinline__ void load8(const void* base, int64_t elem_off, float 
 // per lane); lane l holds columns 8l .. 8l+7 of the block's column group.  IR / AM / CSC are compile-time copies of "input ranges
 // given", "abs-max given", "cache scale given" (kept as run-time flags they turn into selects inside the unrolled
 // element loops).
-template <int DAC, bool A_F32, bool F16, bool IR, bool AM, bool CSC>
+template <int DAC, int A_T, bool F16, bool IR, bool AM, bool CSC>
 __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row0, int rows, int64_t t, int w, int lane) {
   const int k = blockIdx.y * kColsPerBlock + lane * 8;
   const bool k_in = k < p.K;          // (all lanes stay for the shuffles; K % 64 == 0, so whole groups of 8 lanes leave)
   const float rcp_res = quant_rcp(p.inp_res);
   float g_mul = 1.f;
   if (DAC == kDacNone && F16 && p.g_absmax != nullptr) { float inv; g_mul = grad_pow2_scale(__ldg(p.g_absmax), inv); }
+  constexpr bool kRowMul = DAC == kDacNone && A_T == 2;   // fp16 rows, each with a power-of-two scale of its own
   float ir_e = 1.f;
   if (IR && p.ir_by_expert) ir_e = p.ir[e];
   const int64_t blk = static_cast<int64_t>(k >> 6) * p.cache_rows + t * kRows;    // + row, then * 64 + column in block
@@ -134,6 +145,12 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
         if (blockIdx.y == 0) report(p.status, AMOE_ERR_INDEX_RANGE, 30, static_cast<int>(i), s);
       } else {
         m_src = s;
+        if (kRowMul && p.a_row_absmax != nullptr) {
+          // from the row's own power of two to the tensor's: a power of two <= 1, the product is exact
+          float inv;
+          grad_pow2_scale(p.a_row_absmax[s], inv);
+          m_csc = g_mul * inv;
+        }
         if (IR && !p.ir_by_expert) m_ir = p.ir[i];
         if (AM) m_am = p.a_absmax[s];
         if (CSC) m_csc = p.cache_scale[raw];
@@ -159,12 +176,12 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
       rirv[j] = IR ? __shfl_sync(0xffffffffu, m_rcp_ir, l) : 1.f;
       amv[j] = AM ? __shfl_sync(0xffffffffu, m_am, l) : 1.f;
       ramv[j] = AM ? __shfl_sync(0xffffffffu, m_rcp_am, l) : 1.f;
-      csc[j] = CSC ? __shfl_sync(0xffffffffu, m_csc, l) : 1.f;
+      csc[j] = (CSC || kRowMul) ? __shfl_sync(0xffffffffu, m_csc, l) : 1.f;
     }
 #pragma unroll
     for (int j = 0; j < kRpi; ++j) {
       if (src[j] >= 0 && k_in) {
-        load8<A_F32>(p.a, static_cast<int64_t>(src[j]) * p.a_stride + k, v[j]);
+        load8<A_T>(p.a, static_cast<int64_t>(src[j]) * p.a_stride + k, v[j]);
       } else {
 #pragma unroll
         for (int x = 0; x < 8; ++x) v[j][x] = 0.f;
@@ -177,8 +194,9 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
       if (!k_in) continue;
       if (DAC == kDacNone) {
         if (F16) {
+          const float mul = kRowMul ? csc[j] : g_mul;
 #pragma unroll
-          for (int x = 0; x < 8; ++x) v[j][x] *= g_mul;
+          for (int x = 0; x < 8; ++x) v[j][x] *= mul;
         }
         store8<F16>(p.tile_hi, p.tile_lo, off, v[j]);
       } else {
@@ -207,7 +225,7 @@ __device__ __forceinline__ void tile_rows(const OperandParams& p, int e, int row
 }
 
 // grid.x = row tile (an upper bound: blocks past the last tile return), grid.y = group of 256 columns.
-template <int DAC, bool A_F32, bool F16>
+template <int DAC, int A_T, bool F16>
 __global__ void __launch_bounds__(kThreads, 3) operand_tiles_kernel(const OperandParams p) {
   __shared__ int s_tile[3];
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -245,10 +263,10 @@ __global__ void __launch_bounds__(kThreads, 3) operand_tiles_kernel(const Operan
   const int e = s_tile[0], row0 = s_tile[1], rows = s_tile[2];
   if (e < 0) return;
   if (DAC == kDacNone) {
-    tile_rows<DAC, A_F32, F16, false, false, false>(p, e, row0, rows, t, w, lane);
+    tile_rows<DAC, A_T, F16, false, false, false>(p, e, row0, rows, t, w, lane);
   } else {
     const bool ir = p.ir != nullptr, am = p.a_absmax != nullptr, csc = p.cache_scale != nullptr && p.cache_hi != nullptr;
-#define AMOE_ROWS(IR, AM, CSC) tile_rows<DAC, A_F32, F16, IR, AM, CSC>(p, e, row0, rows, t, w, lane)
+#define AMOE_ROWS(IR, AM, CSC) tile_rows<DAC, A_T, F16, IR, AM, CSC>(p, e, row0, rows, t, w, lane)
     if (ir) {
       if (am) { if (csc) AMOE_ROWS(true, true, true); else AMOE_ROWS(true, true, false); }
       else { if (csc) AMOE_ROWS(true, false, true); else AMOE_ROWS(true, false, false); }
@@ -273,7 +291,10 @@ extern "C" int amoe_operand_tiles(const amoe_operand_tiles_args* a, cudaStream_t
   AMOE_REQUIRE(a->precision == AMOE_PREC_BF16X1 || a->precision == AMOE_PREC_SPLIT || a->precision == AMOE_PREC_F16X1,
                AMOE_ERR_UNSUPPORTED);
   AMOE_REQUIRE(a->a != nullptr && a->a_row != nullptr && a->expert_offsets != nullptr, AMOE_ERR_NULL_POINTER);
-  AMOE_REQUIRE(a->a_dtype == AMOE_F32 || a->a_dtype == AMOE_BF16, AMOE_ERR_BAD_DTYPE);
+  AMOE_REQUIRE(a->a_dtype == AMOE_F32 || a->a_dtype == AMOE_BF16 || a->a_dtype == AMOE_F16, AMOE_ERR_BAD_DTYPE);
+  // fp16 rows: pre-scaled gradient rows of the fp16 precision only
+  AMOE_REQUIRE(a->a_dtype != AMOE_F16 || (a->dac == 0 && a->precision == AMOE_PREC_F16X1 && a->a_row_absmax && a->g_absmax_dev),
+               AMOE_ERR_UNSUPPORTED);
   AMOE_REQUIRE(a->tile_hi != nullptr || a->cache_hi != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(a->dac != 0 || (a->cache_hi == nullptr && a->tile_hi != nullptr), AMOE_ERR_UNSUPPORTED);
   const int esz = a->a_dtype == AMOE_F32 ? 4 : 2;
@@ -300,6 +321,7 @@ extern "C" int amoe_operand_tiles(const amoe_operand_tiles_args* a, cudaStream_t
   p.cache_scale = a->cache_scale;
   p.cache_rows = a->cache_rows;
   p.g_absmax = a->g_absmax_dev;
+  p.a_row_absmax = a->a_dtype == AMOE_F16 ? a->a_row_absmax : nullptr;
   p.status = a->dev_status;
   const int64_t max_tiles = a->P / kRows + a->E;
   AMOE_REQUIRE(max_tiles < (1ll << 31), AMOE_ERR_BAD_SHAPE);
@@ -312,7 +334,8 @@ extern "C" int amoe_operand_tiles(const amoe_operand_tiles_args* a, cudaStream_t
     if (f16) { if (f32) AMOE_OPERAND(DAC, true, true); else AMOE_OPERAND(DAC, false, true); }   \
     else { if (f32) AMOE_OPERAND(DAC, true, false); else AMOE_OPERAND(DAC, false, false); }     \
   } while (0)
-  if (dac == kDacNone) AMOE_OPERAND_DT(kDacNone);
+  if (a->a_dtype == AMOE_F16) operand_tiles_kernel<kDacNone, 2, true><<<grid, kThreads, 0, stream>>>(p);
+  else if (dac == kDacNone) AMOE_OPERAND_DT(kDacNone);
   else if (dac == kDacQuant) AMOE_OPERAND_DT(kDacQuant);
   else AMOE_OPERAND_DT(kDacNorm);
 #undef AMOE_OPERAND_DT

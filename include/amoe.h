@@ -38,7 +38,9 @@ typedef enum amoe_status {
   AMOE_ERR_WAIT_LIMIT = 9     /* a bounded device-side wait gave up (amoe_read_device_status) */
 } amoe_status;
 
-typedef enum amoe_dtype { AMOE_F32 = 0, AMOE_BF16 = 1 } amoe_dtype;
+typedef enum amoe_dtype { AMOE_F32 = 0, AMOE_BF16 = 1,
+                          AMOE_F16 = 2   /* IEEE half: only where a function says so (amoe_operand_tiles, gradient rows) */
+} amoe_dtype;
 
 /* How the contraction is carried out. */
 typedef enum amoe_precision {
@@ -334,6 +336,11 @@ typedef struct amoe_operand_tiles_args {
   int64_t cache_rows;
   const float* g_absmax_dev;
   int32_t* dev_status;
+  /* dac == 0, AMOE_PREC_F16X1, a_dtype == AMOE_F16: the rows are fp16 already, row r scaled by the power of two that
+   * amoe_cvmm_args.a_absmax_dev describes for a_row_absmax[r] (amoe_ep_put_f16 writes such rows).  Each row is rescaled
+   * to the power of two of *g_absmax_dev (>= every a_row_absmax), which is exact: the tiles equal those made from the
+   * fp32 rows.  [a_rows] by source row; NULL otherwise. */
+  const float* a_row_absmax;
 } amoe_operand_tiles_args;
 int amoe_operand_tiles(const amoe_operand_tiles_args* args, amoe_stream_t stream);
 
@@ -493,6 +500,14 @@ int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t c
 int amoe_ep_share(const void* payload, int64_t nbytes, const uint64_t* slot_ptrs, int64_t slot_bytes,
                   const uint64_t* flag_ptrs, uint32_t* epoch, int32_t rank, int32_t G, void* gathered,
                   int64_t spin_limit, int32_t* dev_status, amoe_stream_t stream);
+/* amoe_ep_put for fp32 gradient rows of the AMOE_PREC_F16X1 precision: half the bytes over NVLink.  The row
+ * v = row_scale * x[src_row/src_div] is stored as fp16(v * s), s the power of two (amoe_cvmm_args.a_absmax_dev) of its
+ * own max|v|, and that maximum goes to the same row of a second set of buffers (scale_ptrs: [peer_rows] floats per rank)
+ * for amoe_operand_tiles (a_row_absmax).  K % 8 == 0, rows 16-byte aligned. */
+int amoe_ep_put_f16(const float* x, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row, int32_t src_div,
+                    const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El, const int32_t* plan,
+                    const uint64_t* peer_ptrs, const uint64_t* scale_ptrs, int32_t G, int64_t peer_rows,
+                    int32_t* dev_status, amoe_stream_t stream);
 int amoe_ep_put(const void* x, int32_t dtype, int64_t stride, int32_t K, int64_t x_rows, const int32_t* src_row,
                 int32_t src_div, const float* row_scale, int64_t P, const int32_t* sel_sorted, int32_t El,
                 const int32_t* plan, const uint64_t* peer_ptrs, int32_t G, int64_t peer_rows, int32_t* dev_status,
