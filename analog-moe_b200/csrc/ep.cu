@@ -288,7 +288,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-__global__ void __launch_bounds__(256) ep_share_kernel(const uint32_t* __restrict__ payload, int words,
+__global__ void __launch_bounds__(1024) ep_share_kernel(const uint32_t* __restrict__ payload, int words,
                                                        const uint64_t* __restrict__ slot_ptrs, int64_t slot_words,
                                                        const uint64_t* __restrict__ flag_ptrs, uint32_t* __restrict__ epoch_ctr,
                                                        int me, int G, uint32_t* __restrict__ out, long long spin_limit,
@@ -300,9 +300,16 @@ __global__ void __launch_bounds__(256) ep_share_kernel(const uint32_t* __restric
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int64_t par = epoch & 1u;
+  // (16-byte pieces when everything is aligned for them: the larger payloads are a few tens of KB)
+  const bool vec = (words % 4 == 0) && (slot_words % 4 == 0) && ((reinterpret_cast<uintptr_t>(payload) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
   for (int p = 0; p < G; ++p) {
     uint32_t* dst = reinterpret_cast<uint32_t*>(slot_ptrs[p]) + (par * G + me) * slot_words;
-    for (int w = threadIdx.x; w < words; w += blockDim.x) dst[w] = payload[w];
+    if (vec) {
+      for (int w = threadIdx.x; w < words / 4; w += blockDim.x)
+        reinterpret_cast<uint4*>(dst)[w] = __ldg(reinterpret_cast<const uint4*>(payload) + w);
+    } else {
+      for (int w = threadIdx.x; w < words; w += blockDim.x) dst[w] = payload[w];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -324,8 +331,15 @@ __global__ void __launch_bounds__(256) ep_share_kernel(const uint32_t* __restric
   if (threadIdx.x == 0) *epoch_ctr = epoch;
   if (out != nullptr && !s_gave_up) {
     const uint32_t* src = reinterpret_cast<const uint32_t*>(slot_ptrs[me]) + par * G * slot_words;
-    for (int g = 0; g < G; ++g)
-      for (int w = threadIdx.x; w < words; w += blockDim.x) out[static_cast<int64_t>(g) * words + w] = src[g * slot_words + w];
+    for (int g = 0; g < G; ++g) {
+      if (vec) {
+        // (plain loads: the other ranks wrote these slots during this kernel)
+        for (int w = threadIdx.x; w < words / 4; w += blockDim.x)
+          reinterpret_cast<uint4*>(out + static_cast<int64_t>(g) * words)[w] = reinterpret_cast<const uint4*>(src + g * slot_words)[w];
+      } else {
+        for (int w = threadIdx.x; w < words; w += blockDim.x) out[static_cast<int64_t>(g) * words + w] = src[g * slot_words + w];
+      }
+    }
   }
 }
 
@@ -432,7 +446,7 @@ int amoe_ep_share(const void* payload, int64_t nbytes, const uint64_t* slot_ptrs
   AMOE_REQUIRE(nbytes == 0 || payload != nullptr, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(G > 0 && G <= kEpMaxRanks && rank >= 0 && rank < G && nbytes >= 0 && nbytes % 4 == 0 && slot_bytes % 4 == 0 &&
                nbytes <= slot_bytes && spin_limit > 0, AMOE_ERR_BAD_SHAPE);
-  ep_share_kernel<<<1, 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(payload), static_cast<int>(nbytes / 4), slot_ptrs,
+  ep_share_kernel<<<1, nbytes > 4096 ? 1024 : 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(payload), static_cast<int>(nbytes / 4), slot_ptrs,
                                          slot_bytes / 4, flag_ptrs, epoch, rank, G, reinterpret_cast<uint32_t*>(gathered),
                                          spin_limit, dev_status);
   AMOE_LAUNCH_CHECK("ep_share");
