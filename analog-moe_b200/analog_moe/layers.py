@@ -85,9 +85,11 @@ class _FusedAnalogStep(torch.autograd.Function):
 
         clip = layer._take_pending_clip()       # weight clipping left over from post_update_step, done in the pre-pass
 
-        def prepass(w, mod):
-            if mod is None and not clip:
-                return ops.weight_prepass_cached(w, precision, per_channel)      # unchanged weights: prepared once
+        def prepass(w, mod, trained):
+            # unchanged weights of a call that does not train them: prepared once (a training loop may write weights in
+            # ways the version counter does not see, so a call that wants their gradient always prepares them)
+            if mod is None and not clip and not trained:
+                return ops.weight_prepass_cached(w, precision, per_channel)
             return ops.weight_prepass(
                 w, precision, per_channel_scale=per_channel, noise_std=mod.std_dev if mod else 0.0,
                 noise_per_channel=mod.per_channel if mod else True, discretize_res=mod.discretize_res if mod else -1.0,
@@ -110,10 +112,10 @@ class _FusedAnalogStep(torch.autograd.Function):
         side.wait_stream(main)
         with ops.launch_on(side):
             ops.set_tag("up")
-            pw_up = prepass(keys, mod_up)
+            pw_up = prepass(keys, mod_up, bool(ctx.needs_input_grad[3]))
             up_ready = side.record_event()      # the up-projection only waits for its own weights
             ops.set_tag("down")
-            pw_dn = prepass(values, mod_dn)
+            pw_dn = prepass(values, mod_dn, bool(ctx.needs_input_grad[4]))
         ops.set_tag("up")
         r, _ = ops.router_select(x2, w_sel, k, getattr(layer, "router_bias", None))
         inp_res = float(layer._inp_res())

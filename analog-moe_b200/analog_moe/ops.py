@@ -390,7 +390,9 @@ _PREPARED = {}
 
 def weight_prepass_cached(w: torch.Tensor, precision: int, per_channel_scale: bool = True) -> PreparedWeights:
     """Weight pre-pass without modifier or clipping, skipped when these exact weights (same storage, same version
-    counter) were prepared before: an inference layer pays for it once, not on every call."""
+    counter) were prepared before: an inference layer pays for it once, not on every call.  For calls that do not train
+    the weights (the callers decide): a write through `.data` does not move the version counter - `forget_prepared`
+    is for those."""
     from torch.multiprocessing.reductions import StorageWeakRef
     # Inside a CUDA-graph capture the check below would be frozen into the graph: a replay after an optimizer step would
     # use stale copies.  Trainable weights are therefore always prepared inside a captured graph; frozen ones may be

@@ -148,10 +148,13 @@ def _tiles_eligible(x2: torch.Tensor, precision: int) -> bool:
 
 
 def _prepared_weights(keys: torch.Tensor, precision: int, per_channel: bool, mod_std: float, mod_per_channel: bool,
-                      mod_disc: float, mod_seed: int, mod_offset: int, mod_step: Optional[torch.Tensor]):
-    """Weight pre-pass, skipped when these exact weights (same storage, same version counter) were prepared before and
-    no modifier changes them from call to call: an inference layer pays for it once, not on every CVMM.apply."""
-    if mod_std > 0 or mod_disc > 0:
+                      mod_disc: float, mod_seed: int, mod_offset: int, mod_step: Optional[torch.Tensor],
+                      training_call: bool = False):
+    """Weight pre-pass, skipped when these exact weights (same storage, same version counter) were prepared before, no
+    modifier changes them from call to call and the call does not train them: an inference layer pays for it once, not on
+    every CVMM.apply.  A call whose weight gradient is wanted always prepares them: training loops also write weights in
+    ways the version counter does not see (`p.data.add_(...)`)."""
+    if mod_std > 0 or mod_disc > 0 or training_call:
         return ops.weight_prepass(keys, precision, per_channel_scale=per_channel, noise_std=mod_std,
                                   noise_per_channel=mod_per_channel, discretize_res=mod_disc, seed=mod_seed,
                                   offset=mod_offset, step_dev=mod_step, need_fwd=True, need_bwd=True)
@@ -191,7 +194,7 @@ def cvmm_forward_op(x: torch.Tensor, sel_index: torch.Tensor, sel: torch.Tensor,
     ir = None if input_ranges is None else input_ranges.reshape(-1).float().contiguous()
     absmax = ops.row_absmax(x2) if use_abs_max else None
     pw = _prepared_weights(keys, precision, scale_per_channel, mod_std, mod_per_channel, mod_discretize, mod_seed,
-                           mod_offset, mod_step)
+                           mod_offset, mod_step, training_call=save_operands)
     dst = sel_index_i if out_index_i is None else out_index_i
     adc_on = out_res > 0 and out_bound > 0
     codes_path = adc_on and reduction_weight is not None and adc_codes_path

@@ -316,16 +316,26 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
   float4 t[4];
   owner_to_rows(tr, v, t, lane);
   const int col = n0 + 4 * (lane & 3);
+  if (p.peer_ptrs == nullptr) {     // (uniform across the kernel)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (qr.dst[i] >= 0) {
+        const int64_t base = static_cast<int64_t>(qr.dst[i]) * p.out_stride + col;
+        if (p.out_dtype == AMOE_F32)
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = t[i];
+        else
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) =
+              make_uint2(cvt_bf16x2(t[i].x, t[i].y), cvt_bf16x2(t[i].z, t[i].w));
+      }
+    }
+    return;
+  }
+  // the rows live in other GPUs' buffers: (rank << 24) | row
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (qr.dst[i] >= 0) {
-      int row = qr.dst[i];
-      void* out = p.out;
-      if (p.peer_ptrs != nullptr) {   // the row lives in another GPU's buffer (uniform across the kernel)
-        out = reinterpret_cast<void*>(__ldg(p.peer_ptrs + (row >> 24)));
-        row &= 0xffffff;
-      }
-      const int64_t base = static_cast<int64_t>(row) * p.out_stride + col;
+      void* out = reinterpret_cast<void*>(__ldg(p.peer_ptrs + (qr.dst[i] >> 24)));
+      const int64_t base = static_cast<int64_t>(qr.dst[i] & 0xffffff) * p.out_stride + col;
       if (p.out_dtype == AMOE_F32)
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + base) = t[i];
       else
