@@ -82,7 +82,6 @@ class CvmmArgs(C.Structure):
         ("a_tile_hi", vp), ("a_tile_lo", vp),
         ("next_ir", vp), ("next_inp_res", C.c_float), ("next_codes", vp), ("out_cache_scale", vp),
         ("workspace", vp), ("workspace_bytes", C.c_size_t), ("dev_status", vp), ("a_absmax_dev", vp),
-        ("peer_dst", vp), ("peer_ptrs", vp), ("n_peers", C.c_int32), ("peer_rows", C.c_int64),
     ]
 
 
@@ -159,7 +158,7 @@ SIGNATURES = {
     "amoe_ep_put_f16": (C.c_int, [vp, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp, vp, vp,
                                   C.c_int32, C.c_int64, vp, vp]),
     "amoe_ep_share": (C.c_int, [vp, C.c_int64, vp, C.c_int64, vp, vp, C.c_int32, C.c_int32, vp, C.c_int64, vp, vp]),
-    "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp, vp, vp]),
+    "amoe_ep_local_plan_dev": (C.c_int, [vp, C.c_int32, C.c_int32, C.c_int64, vp, vp, vp, vp]),
     "amoe_ep_put": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, C.c_int64, vp, C.c_int32, vp, C.c_int64, vp, C.c_int32, vp,
                               vp, C.c_int32, C.c_int64, vp, vp]),
     "amoe_ep_put_back": (C.c_int, [vp, C.c_int32, C.c_int64, C.c_int32, vp, vp, C.c_int32, C.c_int64, C.c_int64, vp, vp]),

@@ -4,17 +4,19 @@ data-parallel, routed rows exchanged once each way over NVLink.
 The reference is single-GPU; this module is new.  Per rank and step (`_ExpertParallelStep`, one autograd node):
 
   route locally (global expert ids)           amoe_router_logits, amoe_select_sort
-  all-gather of the per-expert counts         NCCL, [G, E/G] int32 per rank
+  all-gather of the per-expert counts         amoe_ep_share, [G, E/G] int32 per rank (payload and flags in peer memory)
   plan on the device                          amoe_ep_plan, amoe_ep_local_plan_dev   (no host read)
   rows to their owners                        amoe_ep_put: stores into the owner's buffer (symmetric memory)
   up-projection -> ReLU -> down-projection    the single-GPU kernels on the rank's experts, rows addressed
                                               through local_order; operand caches for the weight gradients
-  rows back (ADC codes + one scale per row)   amoe_ep_put_back
+  rows back (ADC codes + one scale per row)   amoe_ep_put_back, then amoe_ep_share (orders the stores, carries the
+                                              experts' column scales)
   gate-weighted sum over k                    amoe_combine_codes through the inverse permutation
 
-and the mirror image in the backward pass.  dW and the input-range gradients need no collective: every slot of
-an expert arrives at its owner.  Ordering between ranks comes from small NCCL collectives placed between the
-stores; no kernel waits on another rank and every load is local.  Without symmetric memory (or with
+and the mirror image in the backward pass (gradient rows as fp16 with a scale per row: amoe_ep_put_f16).  dW and the
+input-range gradients need no collective: every slot of an expert arrives at its owner.  Ordering between ranks comes
+from `amoe_ep_share` launches placed after the stores: the only kernel that waits for other ranks, by polling flags in
+its own memory, with a limit; every load is local.  (AMOE_EP_NCCL_SYNC=1: small NCCL collectives instead.)  Without symmetric memory (or with
 AMOE_EP_NCCL=1) the rows travel by `all_to_all_single` with split sizes taken from one host read per step
 (`step_plan`); `forward_composed` keeps the composition around `CVMM.apply` for other activations.  The host-side
 plans are plain arithmetic on the count matrix and are tested on CPU ranks over gloo.
@@ -187,10 +189,10 @@ class PeerExchange:
     """Rows travel by plain stores into the destination rank's receive buffer (symmetric memory over NVLink), written by
     the gather kernel itself: no send buffer, no separate collective, no self-copy.  Where each row goes is computed on
     the device from the all-gathered counts (`amoe_ep_plan`), so the step needs no value on the host and can be captured
-    in a CUDA graph.  A one-element NCCL all-reduce after the writes is the cross-rank ordering point (stream-ordered
-    after this rank's writes, complete only once every rank has reached it).  Buffers are sized for the worst case
-    (every slot of every rank routed to one rank) and reused every step; reuse across steps is ordered by the next
-    step's count all-gather.  One forward/backward pair may be in flight per layer."""
+    in a CUDA graph.  A `share` after the writes is the cross-rank ordering point (stream-ordered after this rank's
+    writes, complete only once every rank has reached it; it can carry a small value at no extra cost).  Buffers are
+    sized for the worst case (every slot of every rank routed to one rank) and reused every step; reuse across steps
+    is ordered by the next step's count exchange.  One forward/backward pair may be in flight per layer."""
 
     def __init__(self, group, device, p_cap: int, D: int, N: int, dtype, small_bytes: int = 0):
         """`small_bytes`: the largest payload `share` will carry."""
@@ -361,14 +363,14 @@ class _ExpertParallelStep(torch.autograd.Function):
         N, Fh = values.shape[-1], keys.shape[-1]
         inv = ops.invert_index(r.slot_index)
         xchg = layer._peer_exchange(P, D, N, x.dtype, part)
-        plan = send_splits = recv_splits = back_dst = None
+        plan = send_splits = recv_splits = None
         # ---- rows to their owners
         if xchg is not None:
             # everything on the device: all-gather of the counts -> plan -> stores into the owners' buffers
             gathered = xchg.share(counts)             # [G, G, El]: source, destination, local expert
             plan = ops.ep_plan(gathered, layer.rank)
             R = xchg.cap                       # rows allocated; the kernels find the real count in the plan / offsets
-            local_order, local_offsets, back_dst = ops.ep_local_plan_dev(plan, G, El, R, xchg.status, want_back_dst=True)
+            local_order, local_offsets = ops.ep_local_plan_dev(plan, G, El, R, xchg.status)
             xchg.generation += 1
             recv = xchg.put("x", x2, r.token_index, r.sel, El, plan)
         else:
@@ -449,13 +451,12 @@ class _ExpertParallelStep(torch.autograd.Function):
             y = ops.combine(back, gate, T, k, row_index=inv)
         simt = precision == ops.A.PREC_FP32_SIMT
         ctx.save_for_backward(x2, w_sel, recv, h, back, gate, r.raw_sel, r.token_index, r.slot_index, r.expert_offsets, inv, r.sel,
-                              local_order, local_offsets, back_dst, ir_all,
+                              local_order, local_offsets, ir_all,
                               pw_up.w if simt else None, pw_up.bwd_hi, pw_up.bwd_lo, pw_up.col_scale,
                               pw_dn.w if simt else None, pw_dn.bwd_hi, pw_dn.bwd_lo, pw_dn.col_scale,
                               *((xc.hi, xc.lo, hs.hi, hs.lo) if cached else (None, None, None, None)), cs_all, scale_back)
         ctx.adc_step = adc_step
         ctx.operand_prepass = layer.operand_prepass
-        ctx.fused_back = getattr(layer, "fused_put_back", True)
         ctx.generation = xchg.generation if xchg is not None else 0
         if layer.keep_codes:      # ADC codes of the down-projection by flat slot (parity checks)
             layer.last_codes = back[inv.long()] if codes_back else None
@@ -465,14 +466,12 @@ class _ExpertParallelStep(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets,
-         back_dst, ir_all,
+        (x2, w_sel, recv, h, back, gate, raw_sel, token_index, slot_index, offsets, inv, sel_sorted, local_order, local_offsets, ir_all,
          w_up, up_hi, up_lo, up_cs, w_dn, dn_hi, dn_lo, dn_cs, xc_hi, xc_lo, hs_hi, hs_lo, cs_all, scale_back) = ctx.saved_tensors
         (x_shape, El, k, precision, ir_p, keys_dtype, values_dtype, kshape, vshape, ir_dtype, send_splits, recv_splits,
          group, plan, xchg) = ctx.meta
         T, D = x2.shape
         P, R = T * k, recv.shape[0]
-        layer_fused_back = ctx.fused_back
         if xchg is not None and xchg.generation != ctx.generation:
             raise RuntimeError("expert-parallel layer: a later forward pass of this layer has overwritten the exchange "
                                "buffers this backward pass reads (one forward/backward pair per layer may be in flight)")
@@ -546,8 +545,6 @@ class _ExpertParallelStep(torch.autograd.Function):
             dist.all_to_all_single(g_recv, drows, recv_splits, send_splits, group=group)
             del drows
         grad_keys = grad_values = None
-        dx_to_peers = (xchg is not None and need_x and layer_fused_back and precision != ops.A.PREC_FP32_SIMT and D % 16 == 0
-                       and P < (1 << 24) and x2.dtype in (torch.float32, torch.bfloat16))
         if R > 0:
             split = xc_lo is not None
             gc = ops.OperandCache.empty(R, El, N, split, dev) if cached and need_values else None
@@ -570,18 +567,11 @@ class _ExpertParallelStep(torch.autograd.Function):
                                      relative=relative, grad_scale=gscale, keep_count=keeps[1:] if keeps is not None else None,
                                      out_dtype=h.dtype, x_ref_relu=True, out_cache=dhc, g_absmax=gmax, **a_kw)
             ops.set_tag("up")
-            # The input-gradient rows leave the kernel's epilogue for the buffers of the ranks they belong to (stores over
-            # NVLink while the next tiles' MMAs run) instead of a local buffer and a copy kernel afterwards.
-            peer_out = None
-            if dx_to_peers:
-                _, dx_buf, dx_ptrs = xchg.buffers["dx"]
-                peer_out = (dx_buf, dx_ptrs, xchg.G, back_dst)
             dxr, irs_up = ops.cvmm_dx(dh, local_order, local_order, local_offsets, pw_up, precision, P=R, dst_rows=R,
                                       x_ref=recv if has_ir else None, x_ref_row=local_order if has_ir else None, ir=ir_up,
                                       ir_by_expert=True, want_ir_grad=has_ir, relative=relative, grad_scale=gscale,
                                       keep_count=keeps[:1] if keeps is not None else None, out_dtype=x2.dtype,
-                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None, g_absmax=gmax,
-                                      peer_out=peer_out)
+                                      a_tiles=dhc if (dhc is not None and Fh % 64 == 0) else None, g_absmax=gmax)
             # the two weight gradients on a second stream, beside the exchange and the streaming kernels that follow
             if cached and (need_values or need_keys):
                 side.wait_stream(main)
@@ -617,12 +607,7 @@ class _ExpertParallelStep(torch.autograd.Function):
             tot = torch.cat([keeps, local_offsets[-1:].to(torch.int64)])     # kept (up), kept (down), rows here
         if need_x:
             if xchg is not None:
-                if dx_to_peers:
-                    dback = xchg.buffers["dx"][1][:P]
-                    if tot is None:
-                        xchg.barrier()
-                else:
-                    dback = xchg.put_back("dx", dxr, plan, P, barrier=tot is None)
+                dback = xchg.put_back("dx", dxr, plan, P, barrier=tot is None)
                 if tot is not None:
                     tot = xchg.share(tot).sum(0)
                     tot_summed = True
@@ -678,9 +663,6 @@ class ExpertParallelAnalogSigmaMoELayer(AnalogSigmaMoELayer):
         # step against 1.05 ms for one - the CVMM kernels hold every SM's registers and shared memory, so the other
         # micro-batch's exchange kernels wait for them instead of running beside them, and every kernel is paid twice.
         self.micro_batches = int(kwargs.pop("micro_batches", os.environ.get("AMOE_EP_MICRO_BATCHES", 1)))
-        # input-gradient rows go back to their sources from the CVMM kernel's epilogue (peer stores) rather than through a
-        # local buffer and a copy kernel
-        self.fused_put_back = os.environ.get("AMOE_EP_FUSED_BACK", "0") == "1"
         self.max_slots = int(kwargs.pop("max_slots", 0))
         if kwargs.get("bias"):
             raise NotImplementedError("expert-parallel layer: bias is not built")

@@ -550,20 +550,13 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
             out_dtype: Optional[torch.dtype] = None, status: Optional[torch.Tensor] = None,
             ir_by_expert: bool = False, x_ref_relu: bool = False, a_cache: Optional["OperandCache"] = None,
             out_cache: Optional["OperandCache"] = None, a_tiles: Optional["OperandCache"] = None,
-            g_absmax: Optional[torch.Tensor] = None, want_out: bool = True, peer_out=None):
+            g_absmax: Optional[torch.Tensor] = None, want_out: bool = True):
     """`a_tiles`: the A operand as an operand cache written by an earlier kernel (TMA-fed, no gather); g2 then only
     gives dtype and device.  `g_absmax`: the device scalar of the fp16 precision (see tensor_absmax).  `want_out=False`
-    (with `out_cache`): only the operand cache is written.  `peer_out=(own_buffer, peer_ptrs_dev, n_peers, peer_dst)`:
-    the result rows are stored from the epilogue into the peers' buffers (`own_buffer` is this rank's one, all of
-    the same shape; peer_ptrs_dev the device address of the array of their base addresses); the first result is None."""
+    (with `out_cache`): only the operand cache is written."""
     g2 = _rows(g2)
     dev = g2.device
-    if peer_out is not None:
-        out = peer_out[0]
-        if out.dtype != (out_dtype or g2.dtype) or out.shape[1] != pw.K or out.stride(1) != 1:
-            raise ValueError("peer_out: the buffers must hold rows of the result's width and type")
-    else:
-        out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev) if want_out else None
+    out = torch.empty(dst_rows, pw.K, dtype=out_dtype or g2.dtype, device=dev) if want_out else None
     ir_grad = torch.empty(P, dtype=torch.float32, device=dev) if want_ir_grad else None
     a = A.CvmmArgs()
     a.P, a.E, a.K, a.N, a.precision = P, pw.E, pw.K, pw.N, precision
@@ -596,10 +589,8 @@ def cvmm_dx(g2: torch.Tensor, a_row: torch.Tensor, dst_row: torch.Tensor, offset
     a.ir_grad_relative, a.ir_grad_scale = int(relative), float(grad_scale)
     a.keep_count = ptr(keep_count)
     a.dev_status = ptr(status)
-    if peer_out is not None:
-        a.peer_ptrs, a.n_peers, a.peer_dst, a.peer_rows = int(peer_out[1]), int(peer_out[2]), ptr(peer_out[3]), out.shape[0]
     _call("amoe_cvmm_dx", C.byref(a), stream_ptr())
-    return (None if peer_out is not None else out), ir_grad
+    return out, ir_grad
 
 
 def cvmm_dw(x2: torch.Tensor, x_row: torch.Tensor, g2: torch.Tensor, g_row: torch.Tensor, offsets: torch.Tensor,
@@ -834,15 +825,12 @@ def ep_plan(gathered: torch.Tensor, rank: int) -> torch.Tensor:
     return plan
 
 
-def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int, status: Optional[torch.Tensor] = None,
-                      want_back_dst: bool = False):
-    """(local_order, local_offsets[, back_dst]) of this step's plan.  back_dst: for every expert-sorted position, the
-    rank the row came from and its place there, as `cvmm_dx(peer_out=...)` takes it."""
+def ep_local_plan_dev(plan: torch.Tensor, G: int, El: int, cap: int,
+                      status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     order = torch.empty(cap, dtype=torch.int32, device=plan.device)
     offsets = torch.empty(El + 1, dtype=torch.int32, device=plan.device)
-    back = torch.empty(cap, dtype=torch.int32, device=plan.device) if want_back_dst else None
-    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), ptr(back), ptr(status), stream_ptr())
-    return (order, offsets, back) if want_back_dst else (order, offsets)
+    _call("amoe_ep_local_plan_dev", ptr(plan), G, El, cap, ptr(order), ptr(offsets), ptr(status), stream_ptr())
+    return order, offsets
 
 
 def invert_index(idx: torch.Tensor) -> torch.Tensor:

@@ -90,12 +90,6 @@ int amoe_cvmm_fwd(const amoe_cvmm_args* a, amoe_stream_t stream_) {
                AMOE_ERR_BAD_SHAPE);
   AMOE_REQUIRE(!a->next_codes || (a->next_ir && a->next_inp_res > 0.f && a->precision != AMOE_PREC_FP32_SIMT && a->out), AMOE_ERR_UNSUPPORTED);
   AMOE_REQUIRE(!a->out_cache_hi || a->out, AMOE_ERR_UNSUPPORTED);
-  if (a->peer_dst != nullptr) {
-    AMOE_REQUIRE(a->peer_ptrs != nullptr, AMOE_ERR_NULL_POINTER);
-    AMOE_REQUIRE(a->n_peers > 0 && a->n_peers <= 128 && a->peer_rows > 0 && a->peer_rows < (int64_t{1} << 24), AMOE_ERR_BAD_SHAPE);
-    AMOE_REQUIRE(a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
-    e.peer_dst = a->peer_dst; e.peer_ptrs = a->peer_ptrs; e.n_peers = a->n_peers; e.peer_rows = a->peer_rows;
-  }
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, false, e, stream);
   return launch_cvmm_tc(a, false, e, stream);
 }
@@ -130,12 +124,6 @@ int amoe_cvmm_dx(const amoe_cvmm_args* a, amoe_stream_t stream_) {
   e.out_cache_lo = reinterpret_cast<__nv_bfloat16*>(a->out_cache_lo);
   e.out_cache_stride = a->cache_rows;
   AMOE_REQUIRE(!a->out_cache_hi || (a->K % 16 == 0 && al16(a->out_cache_hi) && al16(a->out_cache_lo)), AMOE_ERR_BAD_SHAPE);
-  if (a->peer_dst != nullptr) {
-    AMOE_REQUIRE(a->peer_ptrs != nullptr, AMOE_ERR_NULL_POINTER);
-    AMOE_REQUIRE(a->n_peers > 0 && a->n_peers <= 128 && a->peer_rows > 0 && a->peer_rows < (int64_t{1} << 24), AMOE_ERR_BAD_SHAPE);
-    AMOE_REQUIRE(a->precision != AMOE_PREC_FP32_SIMT, AMOE_ERR_UNSUPPORTED);
-    e.peer_dst = a->peer_dst; e.peer_ptrs = a->peer_ptrs; e.n_peers = a->n_peers; e.peer_rows = a->peer_rows;
-  }
   if (a->precision == AMOE_PREC_FP32_SIMT) return launch_cvmm_simt(a, true, e, stream);
   return launch_cvmm_tc(a, true, e, stream);
 }

@@ -53,12 +53,10 @@ __global__ void ep_plan_kernel(const int32_t* __restrict__ gathered, int me, int
   }
 }
 
-// local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.  back_dst (optional):
-// for every expert-sorted position, the rank its row came from and the row's place there.
+// local_order / local_offsets as ep_local_plan_kernel, with the counts and R read from the plan.
 __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* __restrict__ plan, int G, int El, int cap,
                                                                 int32_t* __restrict__ local_order,
                                                                 int32_t* __restrict__ local_offsets,
-                                                                int32_t* __restrict__ back_dst,
                                                                 int32_t* __restrict__ status) {
   __shared__ int s_recv_start[kEpMaxBlocksDev + 1];
   __shared__ int s_sorted_start[kEpMaxBlocksDev];
@@ -86,15 +84,7 @@ __global__ void __launch_bounds__(256) ep_local_plan_dev_kernel(const int32_t* _
     }
     // a position in the full permutation of plan[0] rows: it lies inside the array only if the plan fits the buffer
     const int pos = s_sorted_start[lo] + (r - s_recv_start[lo]);
-    if (pos < cap) {
-      local_order[pos] = r;
-      if (back_dst != nullptr) {
-        // where the row goes back to: its place in the source rank's sorted slot list, as (rank << 24) | row
-        const int g = lo / El;
-        const int row = plan[2 + 3 * G + g] + (r - s_recv_start[g * El]);
-        back_dst[pos] = (row >= 0 && row < (1 << 24)) ? ((g << 24) | row) : -1;
-      }
-    }
+    if (pos < cap) local_order[pos] = r;
   }
 }
 
@@ -364,14 +354,14 @@ int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, i
 }
 
 int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
-                           int32_t* local_offsets, int32_t* back_dst, int32_t* dev_status, amoe_stream_t stream_) {
+                           int32_t* local_offsets, int32_t* dev_status, amoe_stream_t stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   AMOE_REQUIRE(plan && local_order && local_offsets, AMOE_ERR_NULL_POINTER);
   AMOE_REQUIRE(G > 0 && El > 0 && G * El <= kEpMaxBlocksDev && cap_rows > 0 && cap_rows < (int64_t{1} << 31), AMOE_ERR_BAD_SHAPE);
   int64_t blocks = (cap_rows + 255) / 256;
   if (blocks > 592) blocks = 592;
   ep_local_plan_dev_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(plan, G, El, static_cast<int>(cap_rows), local_order,
-                                                                             local_offsets, back_dst, dev_status);
+                                                                             local_offsets, dev_status);
   AMOE_LAUNCH_CHECK("ep_local_plan_dev");
   return AMOE_OK;
 }

@@ -35,8 +35,6 @@ struct EpiParams {
   __nv_bfloat16* out_cache_hi; __nv_bfloat16* out_cache_lo; int64_t out_cache_stride;
   // forward, optional: the result as the next projection's operands (see amoe_cvmm_args)
   const float* next_ir; float next_res; __nv_bfloat16* next_codes; const float* out_cache_scale;
-  // optional: result rows go to other GPUs' buffers, (rank << 24) | row by sorted position (tensor-core kernel only)
-  const int32_t* peer_dst; const uint64_t* peer_ptrs; int n_peers; int64_t peer_rows;
   int32_t* status;
 };
 

@@ -316,30 +316,14 @@ __device__ __forceinline__ void store16_t(const EpiParams& p, const QuadRows& qr
   float4 t[4];
   owner_to_rows(tr, v, t, lane);
   const int col = n0 + 4 * (lane & 3);
-  if (p.peer_ptrs == nullptr) {     // (uniform across the kernel)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (qr.dst[i] >= 0) {
-        const int64_t base = static_cast<int64_t>(qr.dst[i]) * p.out_stride + col;
-        if (p.out_dtype == AMOE_F32)
-          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = t[i];
-        else
-          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) =
-              make_uint2(cvt_bf16x2(t[i].x, t[i].y), cvt_bf16x2(t[i].z, t[i].w));
-      }
-    }
-    return;
-  }
-  // the rows live in other GPUs' buffers: (rank << 24) | row
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (qr.dst[i] >= 0) {
-      void* out = reinterpret_cast<void*>(__ldg(p.peer_ptrs + (qr.dst[i] >> 24)));
-      const int64_t base = static_cast<int64_t>(qr.dst[i] & 0xffffff) * p.out_stride + col;
+      const int64_t base = static_cast<int64_t>(qr.dst[i]) * p.out_stride + col;
       if (p.out_dtype == AMOE_F32)
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + base) = t[i];
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + base) = t[i];
       else
-        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + base) =
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + base) =
             make_uint2(cvt_bf16x2(t[i].x, t[i].y), cvt_bf16x2(t[i].z, t[i].w));
     }
   }
@@ -710,14 +694,7 @@ cvmm_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
       if (grp == 0 && it.nt0 == 0) epi_row_side_outputs(p.epi, ctx);
       QuadRows qr;
       if (EPI != kEpiGeneric) {
-        int my_dst = ctx.valid ? static_cast<int>(ctx.dst) : -1;
-        if (p.epi.peer_dst != nullptr && ctx.valid) {
-          my_dst = p.epi.peer_dst[i];
-          if (my_dst < 0 || (my_dst >> 24) >= p.epi.n_peers || (my_dst & 0xffffff) >= p.epi.peer_rows) {
-            report(status, AMOE_ERR_INDEX_RANGE, 12, static_cast<int>(i), my_dst);   // the row is dropped, and said so
-            my_dst = -1;
-          }
-        }
+        const int my_dst = ctx.valid ? static_cast<int>(ctx.dst) : -1;
         const int my_x = (ctx.valid && p.epi.is_dx && p.epi.x_ref) ? static_cast<int>(ctx.xrow) : -1;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -1729,8 +1706,6 @@ int launch_cvmm_tc(const amoe_cvmm_args* a, bool is_dx, const EpiParams& epi_in,
   if (p.epi.vec4 && is_dx && (a->x_ref == nullptr || a->x_ref_dtype == AMOE_F32 || a->x_ref_stride % 8 == 0)) epi = kEpiDx;
   AMOE_REQUIRE(!(p.epi.out_cache_hi || p.epi.next_codes) || epi == (is_dx ? kEpiDx : kEpiFwd), AMOE_ERR_UNSUPPORTED);
   AMOE_REQUIRE(a->out != nullptr || epi != kEpiGeneric, AMOE_ERR_UNSUPPORTED);
-  // rows to other GPUs' buffers: only the whole-chunk store path decodes the destination
-  AMOE_REQUIRE(p.epi.peer_dst == nullptr || (epi != kEpiGeneric && p.epi.n_out % 16 == 0 && a->out != nullptr), AMOE_ERR_UNSUPPORTED);
   const int dacm = is_dx ? kDacNone : (quant ? kDacQuant : kDacNorm);
 #define AMOE_LAUNCH_TC(DAC, F32, EPI, F16)                                                                                  \
   do {                                                                                                                      \

@@ -294,14 +294,6 @@ typedef struct amoe_cvmm_args {
    * A tiles and as a weight-gradient operand with the same scalar).  NULL: no scaling.
    * amoe_cvmm_dx accepts out == NULL when out_cache_hi is given (only the operand cache is wanted). */
   const float* a_absmax_dev;
-  /* Result rows stored straight into other GPUs' buffers (expert parallelism: the rows go back to the ranks that sent
-   * the inputs, from the kernel's epilogue instead of through a local buffer and a copy kernel).  peer_dst[i] =
-   * (rank << 24) | row for sorted position i; peer_ptrs: DEVICE array of n_peers base addresses, each a buffer of
-   * [peer_rows, out_stride] elements of out_dtype mapped into this process (this rank's own buffer included).  `out`
-   * must be non-NULL and is not written; dst_row keeps its meaning for everything else (noise, row_scale, codes).
-   * Tensor-core precisions only, result width a multiple of 16, peer_rows < 2^24; NULL = rows go to `out`.
-   * Plain stores: visible to the peer once this kernel has completed and a collective has ordered the two ranks. */
-  const int32_t* peer_dst; const uint64_t* peer_ptrs; int32_t n_peers; int64_t peer_rows;
 } amoe_cvmm_args;
 size_t amoe_cvmm_workspace_bytes(int64_t P, int32_t E);
 /* Rows to allocate for an operand cache: (P/128 + E) * 128, an upper bound on the padded tile rows. */
@@ -477,8 +469,6 @@ int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_
  *   off_in, recv_off, back_off (block starts in this rank's sorted list / the destination's receive buffer / this rank's
  *   receive buffer / the source's sorted list), then recv_counts [G,El].
  * amoe_ep_local_plan_dev: amoe_ep_local_plan with counts and R taken from the plan; arrays sized for cap_rows.
- *   back_dst (optional, [cap_rows]): for every expert-sorted position (source rank << 24) | the row's place in that
- *   rank's sorted slot list - amoe_cvmm_args.peer_dst of a call whose result rows go straight back to their sources.
  * amoe_ep_put: row x[src_row[i]/src_div] (* row_scale[src_row[i]]) of sorted position i is stored at its place in the
  *   receive buffer of the rank owning expert sel_sorted[i] (= sel_sorted[i]/El); peer_ptrs: device array of G base
  *   pointers (buffers of peer_rows rows of K elements, this rank's own included).  Plain stores, no waiting.
@@ -496,7 +486,7 @@ int amoe_ep_local_plan(const int32_t* recv_counts, int32_t G, int32_t El, int64_
 int64_t amoe_ep_plan_ints(int32_t G, int32_t El);
 int amoe_ep_plan(const int32_t* gathered, int32_t rank, int32_t G, int32_t El, int32_t* plan, amoe_stream_t stream);
 int amoe_ep_local_plan_dev(const int32_t* plan, int32_t G, int32_t El, int64_t cap_rows, int32_t* local_order,
-                           int32_t* local_offsets, int32_t* back_dst, int32_t* dev_status, amoe_stream_t stream);
+                           int32_t* local_offsets, int32_t* dev_status, amoe_stream_t stream);
 int amoe_ep_share(const void* payload, int64_t nbytes, const uint64_t* slot_ptrs, int64_t slot_bytes,
                   const uint64_t* flag_ptrs, uint32_t* epoch, int32_t rank, int32_t G, void* gathered,
                   int64_t spin_limit, int32_t* dev_status, amoe_stream_t stream);

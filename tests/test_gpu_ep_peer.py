@@ -2,8 +2,6 @@
 rank, the "peer" pointers are local; nothing here waits for another launch):
   * gradient rows sent as fp16 with a power-of-two scale per row (amoe_ep_put_f16) give, through the operand pre-pass,
     the tiles that the fp32 rows give;
-  * result rows stored from the CVMM kernel's epilogue straight into the source ranks' buffers (amoe_cvmm_args.peer_dst)
-    equal the rows a local result and amoe_ep_put_back deliver;
   * the small exchange (amoe_ep_share) on one rank, and its bounded wait when a rank never arrives."""
 import ctypes as C
 
@@ -72,50 +70,6 @@ def test_fp16_gradient_rows_give_the_tiles_of_the_fp32_rows(G, E, k):
         assert float((a - b).abs().max()) <= 2.0 ** -24
         assert float((a != b).float().mean()) < 1e-4
         assert float(a.abs().max()) >= 16.0                                    # the scale put the rows into fp16's range
-
-
-@pytest.mark.parametrize("G,E,k,dtype", [(2, 8, 2, torch.float32), (4, 8, 3, torch.bfloat16)])
-def test_result_rows_stored_from_the_epilogue_into_the_sources_buffers(G, E, k, dtype):
-    from analog_moe import ops, _cabi
-    from analog_moe._cabi import lib, stream_ptr
-    dev = torch.device("cuda:0")
-    N, D = 128, 192
-    El, Ts, routes, counts, plans, gys, gates = _setup(G, E, k, N, dev, 11)
-    gen = torch.Generator().manual_seed(3)
-    prec = _cabi.PREC_F16X1 if dtype == torch.float32 else _cabi.PREC_BF16X1
-    p_cap = max(T * k for T in Ts)
-    cap = G * p_cap
-    recv = [torch.zeros(cap, N, device=dev, dtype=dtype) for _ in range(G)]
-    pr = torch.tensor([t.data_ptr() for t in recv], dtype=torch.int64, device=dev)
-    back = [torch.full((p_cap, D), float("nan"), device=dev, dtype=dtype) for _ in range(G)]
-    back_ref = [torch.full((p_cap, D), float("nan"), device=dev, dtype=dtype) for _ in range(G)]
-    pb = torch.tensor([t.data_ptr() for t in back], dtype=torch.int64, device=dev)
-    pbr = torch.tensor([t.data_ptr() for t in back_ref], dtype=torch.int64, device=dev)
-    status = ops.new_status(dev)
-    gys = [t.to(dtype) for t in gys]
-    dc = ops.dtype_code(gys[0])
-    for r in range(G):
-        assert lib.amoe_ep_put(gys[r].data_ptr(), dc, N, N, Ts[r], routes[r].slot_index.data_ptr(), k, None, Ts[r] * k,
-                               routes[r].sel.data_ptr(), El, plans[r].data_ptr(), pr.data_ptr(), G, cap, status.data_ptr(),
-                               stream_ptr()) == 0
-    for d in range(G):
-        W = (torch.randn(El, D, N, generator=gen) / N ** 0.5).to(dev).to(dtype)       # out = rows @ W[e]^T
-        pw = ops.weight_prepass(W, prec)
-        order, offsets, back_dst = ops.ep_local_plan_dev(plans[d], G, El, cap, status, want_back_dst=True)
-        gmax = ops.grad_absmax(recv[d], prec, plans[d][0:1])
-        kw = dict(P=cap, dst_rows=cap, ir_by_expert=True, g_absmax=gmax, status=status)
-        ref, _ = ops.cvmm_dx(recv[d], order, order, offsets, pw, prec, **kw)
-        assert lib.amoe_ep_put_back(ref.data_ptr(), dc, D, D, plans[d].data_ptr(), pbr.data_ptr(), G, cap, p_cap,
-                                    status.data_ptr(), stream_ptr()) == 0
-        none, _ = ops.cvmm_dx(recv[d], order, order, offsets, pw, prec, peer_out=(back[d], pb.data_ptr(), G, back_dst), **kw)
-        assert none is None
-    torch.cuda.synchronize()
-    ops.raise_on_device_status(status, "exchange")
-    for r in range(G):
-        P = Ts[r] * k
-        assert not torch.isnan(back_ref[r][:P].float()).any()
-        assert torch.equal(back[r][:P], back_ref[r][:P])
-        assert torch.isnan(back[r][P:].float()).all()                             # nothing written past a rank's own rows
 
 
 def test_small_exchange_on_one_rank_and_its_bounded_wait():

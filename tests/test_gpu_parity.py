@@ -675,7 +675,7 @@ def test_device_driven_exchange_emulated_ranks(dev, G, E, k, dtype):
     order = torch.full((16,), -7, dtype=torch.int32, device=dev)
     offs = torch.empty(El + 1, dtype=torch.int32, device=dev)
     status.zero_()
-    assert lib.amoe_ep_local_plan_dev(plans[1].data_ptr(), G, El, 8, order.data_ptr(), offs.data_ptr(), None,
-                                      status.data_ptr(), stream_ptr()) == 0
+    assert lib.amoe_ep_local_plan_dev(plans[1].data_ptr(), G, El, 8, order.data_ptr(), offs.data_ptr(), status.data_ptr(),
+                                      stream_ptr()) == 0
     assert lib.amoe_read_device_status(status.data_ptr(), C.byref(host), stream_ptr()) == 8
     assert bool((order[8:] == -7).all())                       # nothing written past the 8 rows the array holds
