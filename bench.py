@@ -670,6 +670,18 @@ def main():
             roof = dict(kernel=top, bound="tensor", achieved=ach, peak=pk["tf"], unit="TFLOP/s", frac=ach / pk["tf"],
                         traffic=ncu_traffic(args.config).get(top) if world == 1 else None,
                         peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
+        elif top.startswith("amoe_ep_put") and world > 1:
+            # a row exchange: bytes that leave this GPU over NVLink (balanced routing: (G-1)/G of the rows) against the
+            # 770 GB/s per direction a peer copy reaches on this pool
+            esz = 4 if cfg["dtype"] == "fp32" else 2
+            if top.startswith("amoe_ep_put_f16"):
+                esz = 2
+            elif top.startswith("amoe_ep_put_back") and top.endswith("[down]") and cfg["adc"]:
+                esz = 1                                  # ADC codes
+            nbytes = cfg["T"] * cfg["k"] * cfg["D"] * esz * (world - 1) / world
+            ach = nbytes / (kern[top]["ms_avg"] * 1e-3) / 1e9
+            roof = dict(kernel=top, bound="nvlink", achieved=ach, peak=770.0, unit="GB/s", frac=ach / 770.0, traffic=None,
+                        peak_source="peer copy per direction measured on this pool", share_of_step=kern[top]["ms_total"] / total_ms)
         else:
             roof = dict(kernel=top, bound="hbm", achieved=None, peak=pk["hbm"], unit="GB/s", frac=None, traffic=None,
                         peak_source=pk["src"], share_of_step=kern[top]["ms_total"] / total_ms)
