@@ -113,8 +113,8 @@ __device__ __forceinline__ void epi_quad(const EpiParams& p, RowCtx& c, int n0, 
     if (p.adc.on) load4(p.col_inv_scale, cidx, n0, p.n_out, vec, is, 0.f);
     if (p.noise) load4(p.noise, c.dst * p.n_out + n0, n0, p.n_out, vec, nz, 0.f);
     if (p.noise_std > 0.f) {
-      const float4 zz = philox_normal4(p.seed, c.noise_offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
-                                       static_cast<uint32_t>(n0 >> 2));
+      const float4 zz = philox_normal8_half(p.seed, c.noise_offset, kStreamOutNoise, static_cast<uint32_t>(c.dst),
+                                            static_cast<uint32_t>(n0 >> 2));
       nz[0] += (p.noise_std * s[0]) * zz.x;
       nz[1] += (p.noise_std * s[1]) * zz.y;
       nz[2] += (p.noise_std * s[2]) * zz.z;

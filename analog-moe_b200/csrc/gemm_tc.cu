@@ -345,6 +345,7 @@ __device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx
   const f32x2 istep2 = pack2(p.adc.inv_step, p.adc.inv_step), step2 = pack2(p.adc.step, p.adc.step);
   const f32x2 magic2 = pack2(kMagic, kMagic), nmagic2 = pack2(-kMagic, -kMagic), post2 = pack2(post, post);
   uint32_t pk[4] = {0u, 0u, 0u, 0u};
+  uint4 w = make_uint4(0u, 0u, 0u, 0u);      // one Philox call gives the noise of eight columns: two quads
 #pragma unroll
   for (int qd = 0; qd < 4; ++qd) {
     float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -352,10 +353,11 @@ __device__ __forceinline__ void epi_chunk_fwd_t(const EpiParams& p, const RowCtx
     if (NOISE || ADC) s4 = *reinterpret_cast<const float4*>(cs + 4 * qd);
     if (ADC) i4 = *reinterpret_cast<const float4*>(cis + 4 * qd);
     if (NOISE) {
-      const uint4 w = philox4x32_10_keys(static_cast<uint32_t>(c.dst), static_cast<uint32_t>((n0 >> 2) + qd), kStreamOutNoise,
-                                         c.noise_offset, p.pkeys);
-      box_muller(w.x, w.y, z.x, z.y);
-      box_muller(w.z, w.w, z.z, z.w);
+      if ((qd & 1) == 0)
+        w = philox4x32_10_keys(static_cast<uint32_t>(c.dst), static_cast<uint32_t>((n0 >> 3) + (qd >> 1)), kStreamOutNoise,
+                               c.noise_offset, p.pkeys);
+      box_muller16((qd & 1) ? w.z : w.x, z.x, z.y);
+      box_muller16((qd & 1) ? w.w : w.y, z.z, z.w);
     }
     const f32x2 sp[2] = {pack2(s4.x, s4.y), pack2(s4.z, s4.w)}, ip[2] = {pack2(i4.x, i4.y), pack2(i4.z, i4.w)};
     const f32x2 zp[2] = {pack2(z.x, z.y), pack2(z.z, z.w)};

@@ -202,7 +202,9 @@ int amoe_row_absmax(const void* x, int32_t dtype, int64_t R, int32_t K, int64_t 
  *   for sorted position i (expert e, source row r=a_row[i], destination row c=dst_row[i]):
  *     a   = A[r,:]; clamp to +-ir[i]; /ir[i]; /a_absmax[r]; round(a/inp_res)  (integer DAC code)
  *     acc = inp_res * sum_k code_k W'[e,k,:]             (fp32 accumulate)
- *     acc += noise[c,:]  |  noise_std*col_scale[e,:]*z(c,:)            (Philox, seed/offset)
+ *     acc += noise[c,:]  |  noise_std*col_scale[e,:]*z(c,:)            (Philox, seed/offset; z(c,n): Philox4x32-10 with
+ *            counter (c, n/8, 0x0A0E, offset) and key (seed lo, seed hi); output word j gives columns 8*(n/8)+2j, +2j+1 as
+ *            r*cos(t), r*sin(t) with r = sqrt(-2 ln((lo16+0.5)/2^16)), t = 2 pi (hi16+0.5)/2^16 of the word's halves)
  *     ADC: q = rint(clamp(acc*(1/col_scale[e,:]), +-out_bound) * (1/step)), acc = q*step*col_scale[e,:]
  *     out[c,:] = acc * a_absmax[r] * ir[i];  out_codes[c,:] = q
  *

@@ -101,6 +101,37 @@ def philox_normal(seed: int, offset: int, stream: int, rows: int, cols: int) -> 
     return torch.from_numpy(np.ascontiguousarray(z))
 
 
+def _box_muller16(w: np.ndarray) -> Tuple[np.ndarray, np.ndarray]:
+    """One uint32 word -> two standard normals: 16-bit uniforms (k + 0.5) * 2^-16, the radius from the low half of
+    the word, the angle from the high half (fp32 arithmetic)."""
+    f = np.float32(2.0 ** -16)
+    ua = ((w & np.uint32(0xFFFF)).astype(np.float32) + np.float32(0.5)) * f
+    ub = ((w >> np.uint32(16)).astype(np.float32) + np.float32(0.5)) * f
+    r = np.sqrt(np.float32(-2.0) * np.log(ua)).astype(np.float32)
+    th = (np.float32(2.0 * math.pi) * ub).astype(np.float32)
+    return (r * np.cos(th)).astype(np.float32), (r * np.sin(th)).astype(np.float32)
+
+
+def philox_normal8(seed: int, offset: int, stream: int, rows: int, cols: int) -> torch.Tensor:
+    """Standard normals addressed by (row, column), eight per Philox call: the generator of the CVMM kernels' output
+    noise (this library's own definition: the reference draws its output noise from torch's generator, which no
+    kernel can reproduce element by element).
+
+    Element (r, c) uses counter (r, c // 8, stream, offset) and key (seed & 0xffffffff, seed >> 32); output word j
+    gives columns 8*(c//8) + 2j and + 2j + 1 through one Box-Muller pair on its two 16-bit halves.
+    """
+    octs = (cols + 7) // 8
+    r = np.arange(rows, dtype=np.uint32)[:, None]
+    q = np.arange(octs, dtype=np.uint32)[None, :]
+    ws = philox4x32_10(r, q, np.uint32(stream), np.uint32(offset & 0xFFFFFFFF), seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    zs = []
+    for w in ws:
+        z0, z1 = _box_muller16(w)
+        zs += [z0, z1]
+    z = np.stack(zs, axis=-1).reshape(rows, octs * 8)[:, :cols]
+    return torch.from_numpy(np.ascontiguousarray(z))
+
+
 # --------------------------------------------------------------------------- #
 # Routing: gate select + expert-contiguous sort
 # --------------------------------------------------------------------------- #
@@ -484,7 +515,7 @@ def layer_forward_backward(x, w_gate, keys, values, input_range, cfg: LayerConfi
     def noise(off, wmax, N):
         if cfg.out_noise <= 0:
             return None
-        z = philox_normal(cfg.seed, off, STREAM_OUT_NOISE, P, N)
+        z = philox_normal8(cfg.seed, off, STREAM_OUT_NOISE, P, N)
         return z * cfg.out_noise * wmax[s.raw_sel.flatten().long()]
 
     adc_up = (cfg.out_res, cfg.out_bound, kmax) if cfg.out_res > 0 else None

@@ -306,7 +306,7 @@ def test_philox_noise_elementwise_and_statistics(dev):
     for seed in range(8):
         noisy, _ = ops.cvmm_fwd(*args, P=P, dst_rows=P, noise_std=0.04, seed=1234 + seed, offset=3)
         z = ((noisy - clean).cpu() / (0.04 * wmax))
-        want = O.philox_normal(1234 + seed, 3, O.STREAM_OUT_NOISE, P, N)
+        want = O.philox_normal8(1234 + seed, 3, O.STREAM_OUT_NOISE, P, N)
         assert float((z - want).abs().max()) < 2e-3   # fp32 cancellation in (noisy-clean) on top of 1e-4
         zs.append(z)
     z = torch.stack(zs)

@@ -109,6 +109,23 @@ def test_box_muller_extreme_words_are_finite():
             assert abs(float(z0[0])) < 6.0 and abs(float(z1[0])) < 6.0
 
 
+def test_output_noise_generator_moments_and_range():
+    """Eight normals per Philox call from 16-bit uniforms: moments of a standard normal, |z| bounded by
+    sqrt(2 ln 2^17), finite for every word."""
+    z = O.philox_normal8(1234, 0, O.STREAM_OUT_NOISE, 2048, 256)
+    assert abs(float(z.mean())) < 5e-3
+    assert abs(float(z.std()) - 1.0) < 5e-3
+    assert abs(float((z ** 4).mean()) - 3.0) < 5e-2
+    assert float(z.abs().max()) <= (2 * np.log(2.0 ** 17)) ** 0.5 + 1e-3
+    for w in (0, 0xFFFFFFFF, 0x0000FFFF, 0xFFFF0000):
+        z0, z1 = O._box_muller16(np.array([w], dtype=np.uint32))
+        assert np.isfinite(z0).all() and np.isfinite(z1).all()
+    # columns 0..7 of a row come from one counter, column 8 from the next
+    a = O.philox_normal8(7, 1, O.STREAM_OUT_NOISE, 4, 16)
+    b = O.philox_normal8(7, 1, O.STREAM_OUT_NOISE, 4, 9)
+    assert torch.equal(a[:, :9], b)
+
+
 def test_philox_normal_moments():
     z = O.philox_normal(1234, 0, O.STREAM_OUT_NOISE, 2048, 256)
     assert abs(float(z.mean())) < 5e-3
