@@ -162,6 +162,56 @@ __global__ void combine_codes16_kernel(const int8_t* __restrict__ codes, const f
   for (int q = 0; q < 4; ++q) st4<TY>(y + t * y_stride + n0 + 4 * q, true, 4, acc + 4 * q);
 }
 
+// The same sum with N % 512 == 0: a warp owns 512 columns of a token, lane l the four column quads 4l + 128q (q = 0..3),
+// so that every load and store of a warp covers contiguous memory (128 bytes of codes, 512 bytes of column scales
+// and of the result per instruction) while the per-slot scalars are still fetched once per 16 columns.  Per element the
+// arithmetic and its order are unchanged.
+template <typename TY>
+__global__ void __launch_bounds__(256) combine_codes512_kernel(const int8_t* __restrict__ codes, const float* __restrict__ col_scale,
+                                        const int32_t* __restrict__ raw_sel, const float* __restrict__ row_mult,
+                                        float step, const float* __restrict__ w, int64_t T, int k, int N,
+                                        TY* __restrict__ y, int64_t y_stride, const int32_t* __restrict__ row_index) {
+  const int lane = threadIdx.x & 31;
+  const int nb = N / 512;
+  const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= T * nb) return;
+  const int64_t t = wid / nb;
+  const int n0 = static_cast<int>(wid - t * nb) * 512 + 4 * lane;
+  float acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+#pragma unroll 2
+  for (int j = 0; j < k; ++j) {
+    const int64_t s = t * k + j;
+    const float ws = w ? w[s] : 1.f;
+    const int64_t rr = row_index ? row_index[s] : s;
+    const float rm = row_mult ? row_mult[rr] : 1.f;
+    const int e = raw_sel[s];
+    const int8_t* cp = codes + rr * N + n0;
+    const float* csp = col_scale + static_cast<int64_t>(e) * N + n0;
+    uint32_t cw[4];
+    float4 cs[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      cw[q] = __ldg(reinterpret_cast<const uint32_t*>(cp + 128 * q));
+      cs[q] = __ldg(reinterpret_cast<const float4*>(csp + 128 * q));
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float csv[4] = {cs[q].x, cs[q].y, cs[q].z, cs[q].w};
+      float cdq[4];
+      codes4_to_float(cw[q], cdq);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float v = __fmul_rn(__fmul_rn(__fmul_rn(cdq[c], step), csv[c]), rm);
+        acc[4 * q + c] = fmaf(ws, v, acc[4 * q + c]);
+      }
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < 4; ++q) st4<TY>(y + t * y_stride + n0 + 128 * q, true, 4, acc + 4 * q);
+}
+
 // d[s] = res[row(s),:] . g[s/k,:]; one warp per slot; lane l walks the column quads l, l+32, ... and adds their
 // four products in column order into one accumulator (the same order in the kernel below, so that rows rebuilt
 // from codes give the same bits as materialised rows).
@@ -515,6 +565,17 @@ int amoe_combine_codes(const int8_t* codes, const float* col_scale, const int32_
   const int64_t n = T * ((N + 3) / 4);
   const unsigned blocks = blocks_for(n, 256);
   const int vec = (N % 4 == 0) && (y_stride % 4 == 0) && al16(y) && al16(col_scale) && al16(codes);
+  if (vec && N % 512 == 0 && (y_dtype == AMOE_F32 || y_dtype == AMOE_BF16)) {
+    const unsigned b512 = blocks_for(T * (N / 512) * 32, 256);
+    if (y_dtype == AMOE_F32)
+      combine_codes512_kernel<float><<<b512, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
+                                                               reinterpret_cast<float*>(y), y_stride, row_index);
+    else
+      combine_codes512_kernel<__nv_bfloat16><<<b512, 256, 0, stream>>>(codes, col_scale, raw_sel, row_mult, step, w, T, k, N,
+                                                                       reinterpret_cast<__nv_bfloat16*>(y), y_stride, row_index);
+    AMOE_LAUNCH_CHECK("combine_codes512");
+    return AMOE_OK;
+  }
   if (vec && N % 16 == 0 && (y_dtype == AMOE_F32 || y_dtype == AMOE_BF16)) {
     const unsigned b16 = blocks_for(T * (N / 16), 128);
     if (y_dtype == AMOE_F32)
