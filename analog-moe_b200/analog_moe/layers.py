@@ -310,6 +310,20 @@ class _FusedAnalogStep(torch.autograd.Function):
             # (the hidden gradient's own magnitude scales it here: it is gathered from fp32 rows)
             grad_keys = ops.cvmm_dw(x2, token_index, dh, slot_index, offsets, E, precision, P=P, ir=ir_up,
                                     ir_by_expert=True, g_absmax=ops.grad_absmax(dh, precision))
+        # ---- input-range gradients: two small reductions over the per-slot sums the input-gradient kernels left, on a
+        # stream of their own beside the last large kernel of the main chain instead of behind it
+        grad_ir = None
+        side3 = None
+        if need_ir:
+            side3 = ops.side_stream(x2.device, 2)
+            side3.wait_stream(main)
+            grad_ir = torch.empty(2, E, dtype=torch.float32, device=x2.device)      # both rows written in place
+            with ops.launch_on(side3):
+                ops.set_tag("up")
+                ops.ir_grad_reduce(irs_up, offsets, ir_up, E, decay, min_pct, keeps[:1] if keeps is not None else None,
+                                   float(P) * D, out=grad_ir[0])
+                ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
+                                   float(P) * Fh, out=grad_ir[1])
         main.wait_event(dgate_ready)
         ops.set_tag("up")
         if need_x:
@@ -319,13 +333,8 @@ class _FusedAnalogStep(torch.autograd.Function):
         if need_sel and not sel_early:
             grad_sel = ops.router_backward_w(x2, dgate, gate, token_index, slot_index, offsets, w_sel.shape[0],
                                              raw_sel=raw_sel)
-        grad_ir = None
-        if need_ir:
-            grad_ir = torch.empty(2, E, dtype=torch.float32, device=x2.device)      # both rows written in place
-            ops.ir_grad_reduce(irs_up, offsets, ir_up, E, decay, min_pct, keeps[:1] if keeps is not None else None,
-                               float(P) * D, out=grad_ir[0])
-            ops.ir_grad_reduce(irs_dn, offsets, ir_dn, E, decay, min_pct, keeps[1:] if keeps is not None else None,
-                               float(P) * Fh, out=grad_ir[1])
+        if side3 is not None:
+            main.wait_stream(side3)
             grad_ir = grad_ir.to(ir_dtype)
         main.wait_stream(side)
         main.wait_stream(side2)
