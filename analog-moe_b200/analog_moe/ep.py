@@ -345,11 +345,15 @@ class _ExpertParallelStep(torch.autograd.Function):
         if shared is None:
             nz_up, mod_up = noise_args(), layer._weight_modifier()
             nz_dn, mod_dn = noise_args(), layer._weight_modifier()
+            # (side by side on two streams: both done before the large kernels of the main chain take every SM)
+            side2 = ops.side_stream(dev, 1)
             side.wait_stream(main)
+            side2.wait_stream(main)
             with ops.launch_on(side):
                 ops.set_tag("up")
                 pw_up = prepass(keys, mod_up)
                 up_ready = side.record_event()      # the up-projection only waits for its own weights
+            with ops.launch_on(side2):
                 ops.set_tag("down")
                 pw_dn = prepass(values, mod_dn)
         else:
@@ -413,6 +417,7 @@ class _ExpertParallelStep(torch.autograd.Function):
                                 out_res=out_res, out_bound=out_bound, out_relu=True, **a_kw, **nz_up)
             if shared is None:
                 main.wait_stream(side)
+                main.wait_stream(side2)
             else:
                 main.wait_event(shared["dn_ready"])
             ops.set_tag("down")
@@ -427,6 +432,7 @@ class _ExpertParallelStep(torch.autograd.Function):
         else:
             if shared is None:
                 main.wait_stream(side)
+                main.wait_stream(side2)
             else:
                 main.wait_event(shared["dn_ready"])
             codes_back = False

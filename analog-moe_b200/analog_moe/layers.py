@@ -102,18 +102,22 @@ class _FusedAnalogStep(torch.autograd.Function):
                 return dict(noise_std=std, seed=layer.noise_seed, offset=layer._next_offset(), step_dev=layer.noise_step)
             return {}
 
-        # The two weight pre-passes depend on nothing but the weights: they run on a second stream beside the
-        # router matmul and the select/sort (small kernels that leave most of the GPU idle).
+        # The two weight pre-passes depend on nothing but the weights: they run on two streams of their own beside the
+        # router matmul and the select/sort (small kernels that leave most of the GPU idle).  Side by side rather than one
+        # after the other: what has not finished when the operand pre-pass and the up-projection take every SM waits
+        # for them to end, and the down-projection then waits for its weights.
         nz_up = noise_args()
         mod_up = layer._weight_modifier()
         nz_dn = noise_args()
         mod_dn = layer._weight_modifier()
-        main, side = torch.cuda.current_stream(), ops.side_stream(x.device)
+        main, side, side2 = torch.cuda.current_stream(), ops.side_stream(x.device), ops.side_stream(x.device, 1)
         side.wait_stream(main)
+        side2.wait_stream(main)
         with ops.launch_on(side):
             ops.set_tag("up")
             pw_up = prepass(keys, mod_up, bool(ctx.needs_input_grad[3]))
             up_ready = side.record_event()      # the up-projection only waits for its own weights
+        with ops.launch_on(side2):
             ops.set_tag("down")
             pw_dn = prepass(values, mod_dn, bool(ctx.needs_input_grad[4]))
         ops.set_tag("up")
@@ -167,6 +171,7 @@ class _FusedAnalogStep(torch.autograd.Function):
                             out_bound=out_bound, out_relu=True, **a_kw, **nxt, **nz)
         # ---- down-projection and the gate-weighted sum over k
         main.wait_stream(side)
+        main.wait_stream(side2)
         ops.set_tag("down")
         nz = nz_dn
         ir_dn = ir_all[1] if has_ir else None
